@@ -1,0 +1,71 @@
+"""Per-TTT-step loss and accuracy for EAGLE-3.
+
+Step ``s`` compares ``logits[:T-s]`` with ``targets[s:]`` under ``loss_mask[s:]``
+(src/speculators/models/eagle3/metrics.py:16-119).  The fused path passes the
+shift to the row-loss kernel instead of slicing, so the gradient comes back for
+the full ``[T, V]`` logits without a padded copy, and both argmaxes for the
+accuracy counters are produced by the same kernel launch.
+"""
+
+from __future__ import annotations
+
+from functools import partial
+
+import torch
+
+from speculators_b200.losses import LossConfig, exp_loss_decay, kl_div_loss, reduce_masked
+from speculators_b200.losses.rowwise import rowwise_terms
+from speculators_b200.models.metrics import compute_accuracy_single_step
+
+__all__ = ["align_for_step", "compute_metrics"]
+
+
+def align_for_step(logits, targets, loss_mask, prev_correct, ttt_step: int):
+    """Slice views that line up draft step ``ttt_step`` with its targets."""
+    if ttt_step > 0:
+        logits = logits[:, :-ttt_step]
+        prev_correct = prev_correct[:, :-ttt_step] if prev_correct is not None else None
+    targets = targets[:, ttt_step:]
+    loss_mask = loss_mask[:, ttt_step:] if loss_mask is not None else None
+    return logits, targets, loss_mask, prev_correct
+
+
+def compute_metrics(logits, targets, loss_mask, prev_correct, ttt_step: int, ttt_step_loss_decay: float, loss_config: LossConfig | None = None):
+    """Returns ``(step_loss, metrics)``; updates ``prev_correct`` in place."""
+    if loss_config is None:
+        loss_config = {"kl_div": (kl_div_loss, 1.0)}
+    T = logits.shape[1]
+    rows = T - ttt_step
+    device = logits.device
+    s_mask = loss_mask[:, ttt_step:] if loss_mask is not None else torch.ones(1, rows, dtype=torch.bool, device=device)
+    s_prev = prev_correct[:, :rows] if prev_correct is not None else None
+    active = s_mask.to(torch.bool).reshape(-1)
+    if s_prev is not None:
+        active = active | s_prev.reshape(-1)
+    pos_idx = torch.full((1, rows), ttt_step, device=device, dtype=torch.long)
+    decay = partial(exp_loss_decay, gamma=ttt_step_loss_decay)
+
+    per_term, pred_ids, target_ids = rowwise_terms(
+        loss_config, logits.reshape(T, -1), targets.reshape(targets.shape[1], -1), shift=ttt_step, rows=rows, active=active
+    )
+    total = torch.zeros((), device=device, dtype=torch.float32)
+    term_scalars = {}
+    for name, (_, weight) in loss_config.items():
+        term = reduce_masked(per_term[name].unsqueeze(0), s_mask, pos_idx, decay)
+        if len(loss_config) > 1:
+            term_scalars[f"{name}_loss"] = term.detach()
+        total = total + weight * term
+
+    full_c, full_t, cond_c, cond_t = compute_accuracy_single_step(
+        pred_ids.unsqueeze(0), target_ids.unsqueeze(0), s_mask, s_prev
+    )
+    one = torch.ones((), device=device)
+    metrics = {f"loss_{ttt_step}_sum": total.detach().clone(), f"loss_{ttt_step}_total": one}
+    for name, value in term_scalars.items():
+        metrics[f"{name}_{ttt_step}_sum"] = value
+        metrics[f"{name}_{ttt_step}_total"] = one.clone()
+    metrics[f"full_acc_{ttt_step}_sum"] = full_c
+    metrics[f"full_acc_{ttt_step}_total"] = full_t
+    metrics[f"cond_acc_{ttt_step}_sum"] = cond_c
+    metrics[f"cond_acc_{ttt_step}_total"] = cond_t
+    return total, metrics

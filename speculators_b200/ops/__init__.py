@@ -1,0 +1,324 @@
+"""Hot operators of the framework.
+
+Every function here has two implementations behind one signature:
+
+* CUDA tensors run the hand-written sm_100a kernels of ``csrc/`` through
+  ``torch.ops.sb200`` (bf16 storage, fp32 math).  There is no fallback on a GPU:
+  a missing extension is a hard error.
+* CPU tensors (any float dtype) run a plain PyTorch formulation.  That path is the
+  numerical oracle the kernel tests compare against, and it is what the gloo /
+  world_size > 1 plumbing tests execute.
+
+All functions are differentiable; the CUDA paths carry their own backward
+kernels via ``torch.autograd.Function``.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from speculators_b200.ops import _ext
+from speculators_b200.ops.attention import AttnSpec, masked_attention, masked_attention_reference
+
+__all__ = [
+    "AttnSpec",
+    "LOSS_OPS",
+    "adamw_step_",
+    "eagle3_input_concat",
+    "fused_row_loss",
+    "linear",
+    "masked_attention",
+    "masked_attention_reference",
+    "native",
+    "rms_norm",
+    "rope_",
+    "sum_of_squares",
+    "swiglu",
+]
+
+LOSS_OPS = {"kl_div": 0, "rkl": 1, "jsd": 2, "ce": 3, "tv": 4}
+
+
+def native():
+    """``torch.ops.sb200`` (builds / loads the extension on first use)."""
+    return _ext.lib()
+
+
+def _use_native(t: torch.Tensor) -> bool:
+    return t.is_cuda
+
+
+# --------------------------------------------------------------------------- linear
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """``x @ weight.T (+ bias)``: a plain library GEMM (cuBLASLt through ATen)."""
+    return F.linear(x, weight, bias)
+
+
+# --------------------------------------------------------------------------- rmsnorm
+def _rms_norm_ref(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    dt = x.dtype
+    xf = x.float()
+    xf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    return weight * xf.to(dt)
+
+
+class _RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps):
+        H = x.shape[-1]
+        x2 = x.reshape(-1, H)
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        y = torch.empty((x2.shape[0], H), dtype=x.dtype, device=x.device)
+        rstd = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device)
+        native().rmsnorm_fwd(x2, weight, None, y, rstd, eps)
+        ctx.save_for_backward(x2, weight, rstd)
+        ctx.shape = x.shape
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight, rstd = ctx.saved_tensors
+        H = x2.shape[-1]
+        dy2 = dy.reshape(-1, H)
+        if dy2.stride(-1) != 1 or dy2.stride(0) % 8:
+            dy2 = dy2.contiguous()
+        dx = torch.empty_like(x2)
+        dw = None
+        if ctx.needs_input_grad[1]:
+            dw = torch.empty(H, dtype=torch.float32, device=x2.device)
+        native().rmsnorm_bwd(dy2, x2, weight, rstd, dx, dw, False, False)
+        return dx.view(ctx.shape), (dw.to(weight.dtype) if dw is not None else None), None
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """RMSNorm over the last dim: ``weight * (x / rms(x))`` with fp32 statistics."""
+    if _use_native(x):
+        return _RMSNormFn.apply(x, weight, eps)
+    return _rms_norm_ref(x, weight, eps)
+
+
+class _Eagle3InputFn(torch.autograd.Function):
+    """``cat([rmsnorm(embeds; w_e), rmsnorm(hidden; w_h)], -1)`` written by two
+    strided launches into one [T, 2H] buffer (no separate concat copy)."""
+
+    @staticmethod
+    def forward(ctx, embeds, hidden, w_e, w_h, eps):
+        T, H = hidden.shape
+        out = torch.empty((T, 2 * H), dtype=hidden.dtype, device=hidden.device)
+        rs_e = torch.empty(T, dtype=torch.float32, device=hidden.device)
+        rs_h = torch.empty(T, dtype=torch.float32, device=hidden.device)
+        nat = native()
+        nat.rmsnorm_fwd(embeds, w_e, None, out[:, :H], rs_e, eps)
+        nat.rmsnorm_fwd(hidden, w_h, None, out[:, H:], rs_h, eps)
+        ctx.save_for_backward(embeds, hidden, w_e, w_h, rs_e, rs_h)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        embeds, hidden, w_e, w_h, rs_e, rs_h = ctx.saved_tensors
+        T, H = hidden.shape
+        if dout.stride(1) != 1 or dout.stride(0) % 8:
+            dout = dout.contiguous()
+        nat = native()
+        need_e, need_h, need_we, need_wh = ctx.needs_input_grad[:4]
+        d_e = d_h = dw_e = dw_h = None
+        if need_e or need_we:
+            d_e = torch.empty_like(embeds)
+            dw_e = torch.empty(H, dtype=torch.float32, device=hidden.device) if need_we else None
+            nat.rmsnorm_bwd(dout[:, :H], embeds, w_e, rs_e, d_e, dw_e, False, False)
+        if need_h or need_wh:
+            d_h = torch.empty_like(hidden)
+            dw_h = torch.empty(H, dtype=torch.float32, device=hidden.device) if need_wh else None
+            nat.rmsnorm_bwd(dout[:, H:], hidden, w_h, rs_h, d_h, dw_h, False, False)
+        return (
+            d_e if need_e else None,
+            d_h if need_h else None,
+            dw_e.to(w_e.dtype) if dw_e is not None else None,
+            dw_h.to(w_h.dtype) if dw_h is not None else None,
+            None,
+        )
+
+
+def eagle3_input_concat(embeds, hidden, w_embed_norm, w_hidden_norm, eps):
+    """First-layer input of an EAGLE-3 draft: both halves normalised, concatenated."""
+    if _use_native(hidden):
+        return _Eagle3InputFn.apply(embeds.contiguous(), hidden.contiguous(), w_embed_norm, w_hidden_norm, eps)
+    return torch.cat(
+        [_rms_norm_ref(embeds, w_embed_norm, eps), _rms_norm_ref(hidden, w_hidden_norm, eps)], dim=-1
+    )
+
+
+# --------------------------------------------------------------------------- swiglu
+class _SwiGLUFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate_up):
+        ctx.save_for_backward(gate_up)
+        return native().swiglu_fwd(gate_up)
+
+    @staticmethod
+    def backward(ctx, dh):
+        (gate_up,) = ctx.saved_tensors
+        return native().swiglu_bwd(dh.contiguous(), gate_up)
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up`` where ``gate_up = [gate | up]`` along the last dim."""
+    if _use_native(gate_up):
+        shape = gate_up.shape
+        out = _SwiGLUFn.apply(gate_up.reshape(-1, shape[-1]).contiguous())
+        return out.view(*shape[:-1], shape[-1] // 2)
+    gate, up = gate_up.chunk(2, dim=-1)
+    return F.silu(gate) * up
+
+
+# --------------------------------------------------------------------------- rope
+def _rope_ref(x, positions, cos_t, sin_t, heads, hd, rot, sign):
+    T = x.shape[0]
+    xv = x[:, : heads * hd].reshape(T, heads, hd)
+    pos = positions.clamp(0, cos_t.shape[0] - 1)
+    c = cos_t[pos].unsqueeze(1).to(torch.float32)
+    s = (sin_t[pos] * sign).unsqueeze(1).to(torch.float32)
+    half = rot // 2
+    x1 = xv[..., :half].float()
+    x2 = xv[..., half:rot].float()
+    y = torch.cat([x1 * c - x2 * s, x2 * c + x1 * s, xv[..., rot:].float()], dim=-1).to(x.dtype)
+    return torch.cat([y.reshape(T, heads * hd), x[:, heads * hd :]], dim=-1)
+
+
+class _RopeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, positions, cos_t, sin_t, heads, hd, rot):
+        ctx.save_for_backward(positions, cos_t, sin_t)
+        ctx.cfg = (heads, hd, rot)
+        native().rope_(x, positions, cos_t, sin_t, heads, hd, rot, 1.0)
+        ctx.mark_dirty(x)
+        return x
+
+    @staticmethod
+    def backward(ctx, dx):
+        positions, cos_t, sin_t = ctx.saved_tensors
+        heads, hd, rot = ctx.cfg
+        dx = dx.clone() if not dx.is_contiguous() else dx.clone()
+        native().rope_(dx, positions, cos_t, sin_t, heads, hd, rot, -1.0)
+        return dx, None, None, None, None, None, None
+
+
+def rope_(x, positions, cos_t, sin_t, heads: int, hd: int, rot: int):
+    """Neox rotary embedding of the first ``heads`` heads of every row of ``x``
+    (``[T, >= heads*hd]``), rotating the first ``rot`` channels of each head.
+    In place on CUDA; returns the rotated tensor."""
+    if _use_native(x):
+        return _RopeFn.apply(x, positions, cos_t, sin_t, heads, hd, rot)
+    return _rope_ref(x, positions, cos_t, sin_t, heads, hd, rot, 1.0)
+
+
+# --------------------------------------------------------------------------- losses
+def _row_loss_ref(op: str, logits, targets):
+    """fp32 per-row loss and both argmaxes (``logits``/``targets``: [rows, V])."""
+    lq = torch.log_softmax(logits.float(), dim=-1)
+    lp = torch.log_softmax(targets.float(), dim=-1)
+    if op == "kl_div":
+        p = lp.exp()
+        loss = torch.where(p > 0, p * (lp - lq), torch.zeros_like(p)).sum(-1)
+    elif op == "rkl":
+        q = lq.exp()
+        loss = torch.where(q > 0, q * (lq - lp), torch.zeros_like(q)).sum(-1)
+    elif op == "jsd":
+        lm = torch.logaddexp(lq, lp) - 0.6931471805599453
+        p, q = lp.exp(), lq.exp()
+        loss = 0.5 * ((p * (lp - lm)).sum(-1) + (q * (lq - lm)).sum(-1))
+    elif op == "ce":
+        loss = -lq.gather(-1, targets.argmax(-1, keepdim=True)).squeeze(-1)
+    elif op == "tv":
+        loss = 1.0 - torch.minimum(lq.exp(), lp.exp()).sum(-1)
+    else:
+        raise ValueError(f"unknown loss op {op!r}")
+    return loss
+
+
+class _RowLossFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, targets, op, shift, rows, active):
+        loss, stats, am_d, am_t = native().loss_fwd(op, logits, targets, active, shift, rows)
+        ctx.save_for_backward(logits, targets, stats)
+        ctx.cfg = (op, shift, rows)
+        ctx.mark_non_differentiable(am_d, am_t)
+        return loss, am_d, am_t
+
+    @staticmethod
+    def backward(ctx, dloss, _a, _b):
+        logits, targets, stats = ctx.saved_tensors
+        op, shift, rows = ctx.cfg
+        d = native().loss_bwd(op, logits, targets, dloss.contiguous().float(), stats, shift, rows)
+        return d, None, None, None, None, None
+
+
+def fused_row_loss(op: str, logits, targets, shift: int = 0, rows: int | None = None, active=None):
+    """Per-row loss between ``logits[r]`` and ``targets[r + shift]`` for ``r < rows``.
+
+    Returns ``(loss[rows] fp32, argmax_logits[rows], argmax_targets[rows])``.
+    ``active`` (bool[rows], optional) marks rows worth computing; inactive rows get
+    loss 0 and sentinel argmaxes (-1 / -2, never equal).  Gradients flow to
+    ``logits`` only; the buffer that comes back has ``logits.shape`` with rows
+    ``>= rows`` zeroed.
+    """
+    if logits.dim() != 2 or targets.dim() != 2:
+        raise ValueError("fused_row_loss expects [rows, V] inputs")
+    if rows is None:
+        rows = min(logits.shape[0], targets.shape[0] - shift)
+    if _use_native(logits):
+        if logits.stride(-1) != 1:
+            logits = logits.contiguous()
+        if targets.stride(-1) != 1:
+            targets = targets.contiguous()
+        loss, am_d, am_t = _RowLossFn.apply(logits, targets, LOSS_OPS[op], shift, rows, active)
+        return loss, am_d.long(), am_t.long()
+    lg = logits[:rows]
+    tg = targets[shift : shift + rows]
+    loss = _row_loss_ref(op, lg, tg)
+    am_d, am_t = lg.argmax(-1), tg.argmax(-1)
+    if active is not None:
+        act = active.bool()
+        loss = torch.where(act, loss, torch.zeros_like(loss))
+        am_d = torch.where(act, am_d, torch.full_like(am_d, -1))
+        am_t = torch.where(act, am_t, torch.full_like(am_t, -2))
+    return loss, am_d, am_t
+
+
+# --------------------------------------------------------------------------- optimizer
+def sum_of_squares(flat: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> torch.Tensor:
+    """``out[0] (+)= sum(flat**2)`` in fp32, deterministic two-stage reduction."""
+    if _use_native(flat):
+        native().sumsq(flat, out, accumulate)
+    else:
+        s = flat.float().pow(2).sum()
+        out[0] = out[0] + s if accumulate else s
+    return out
+
+
+HYPER_LEN = 16
+
+
+def adamw_step_(master, m, v, grad, w16, hyper, norm_sq=None) -> None:
+    """One fused AdamW step over flat buffers.  ``hyper`` (fp32[16], same device):
+    lr, beta1, beta2, eps, weight_decay, bias_correction1, bias_correction2,
+    max_grad_norm (<= 0 disables clipping), grad_scale.  ``norm_sq`` holds the global
+    sum of squared (unscaled) gradients.  ``w16`` (optional) receives the bf16 copy."""
+    if _use_native(master):
+        native().adamw(master, m, v, grad, w16, hyper, norm_sq)
+        return
+    lr, b1, b2, eps, wd, bc1, bc2, max_norm, gscale = (float(hyper[i]) for i in range(9))
+    if max_norm > 0 and norm_sq is not None:
+        coef = max_norm / (gscale * float(norm_sq[0]) ** 0.5 + 1e-6)
+        if coef < 1.0:
+            gscale *= coef
+    g = grad.float() * gscale
+    master.mul_(1 - lr * wd)
+    m.mul_(b1).add_(g, alpha=1 - b1)
+    v.mul_(b2).addcmul_(g, g, value=1 - b2)
+    denom = v.sqrt() / (bc2**0.5) + eps
+    master.addcdiv_(m, denom, value=-lr / bc1)
+    if w16 is not None:
+        w16.copy_(master)

@@ -1,0 +1,113 @@
+"""In-tree build of the native extension (``speculators_b200/ops/_sb200.so``).
+
+The kernels are plain CUDA translation units (no torch headers, so each compiles
+in seconds) built with ``nvcc -gencode arch=compute_100a,code=sm_100a``; only
+``bindings.cpp`` sees torch.  Objects and a source hash are kept under
+``ops/build/`` so an unchanged tree is not rebuilt, and the shared object sits
+next to this file so that a snapshot of the source tree carries it along.
+"""
+
+from __future__ import annotations
+
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+CSRC = HERE / "csrc"
+BUILD = HERE / "build"
+LIB = HERE / "_sb200.so"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "--use_fast_math", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-diag-suppress", "177",
+]
+
+
+def _nvcc() -> str:
+    cand = os.environ.get("NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(cand):
+        raise RuntimeError("nvcc not found; set NVCC or install the CUDA toolkit")
+    return cand
+
+
+def _sources() -> tuple[list[Path], list[Path]]:
+    cu = sorted(CSRC.glob("*.cu"))
+    cpp = sorted(CSRC.glob("*.cpp"))
+    return cu, cpp
+
+
+def _digest(extra: str = "") -> str:
+    h = hashlib.sha256()
+    for p in sorted(CSRC.glob("*")):
+        if p.is_file():
+            h.update(p.name.encode())
+            h.update(p.read_bytes())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(extra.encode())
+    return h.hexdigest()
+
+
+def _run(cmd: list[str]) -> None:
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError(f"command failed: {' '.join(cmd)}\n{proc.stdout}\n{proc.stderr}")
+
+
+def is_current() -> bool:
+    import torch
+
+    stamp = BUILD / "stamp"
+    return LIB.exists() and stamp.exists() and stamp.read_text() == _digest(torch.__version__)
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    """Compile every kernel for sm_100a and link the extension; returns the .so path."""
+    import torch
+    from torch.utils import cpp_extension
+
+    if not force and is_current():
+        return LIB
+    BUILD.mkdir(exist_ok=True)
+    cu, cpp = _sources()
+    nvcc = _nvcc()
+    cuda_home = Path(nvcc).resolve().parent.parent
+    torch_inc = cpp_extension.include_paths()
+    abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)  # noqa: SLF001
+
+    jobs: list[list[str]] = []
+    objs: list[Path] = []
+    for src in cu:
+        obj = BUILD / (src.stem + ".o")
+        objs.append(obj)
+        jobs.append([nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)])
+    for src in cpp:
+        obj = BUILD / (src.stem + ".cpp.o")
+        objs.append(obj)
+        cmd = ["g++", "-O2", "-std=c++17", "-fPIC", f"-D_GLIBCXX_USE_CXX11_ABI={abi}",
+               "-I", str(CSRC), "-I", str(cuda_home / "include")]
+        for inc in torch_inc:
+            cmd += ["-isystem", inc]
+        cmd += ["-c", str(src), "-o", str(obj)]
+        jobs.append(cmd)
+    if verbose:
+        for j in jobs:
+            print(" ".join(j), file=sys.stderr)
+    with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as pool:
+        list(pool.map(_run, jobs))
+
+    torch_lib = Path(torch.__file__).parent / "lib"
+    link = ["g++", "-shared", "-o", str(LIB), *map(str, objs), f"-L{torch_lib}",
+            f"-L{cuda_home / 'lib64'}", "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch",
+            "-lcudart", f"-Wl,-rpath,{torch_lib}", f"-Wl,-rpath,{cuda_home / 'lib64'}"]
+    _run(link)
+    (BUILD / "stamp").write_text(_digest(torch.__version__))
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose=True))

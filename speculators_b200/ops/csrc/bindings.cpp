@@ -1,0 +1,224 @@
+// Torch operator registration for the sm_100a kernels of this package.
+// Every op validates device / dtype / layout, then launches on the current stream.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+#include <ATen/ATen.h>
+
+namespace sb200 {
+int rmsnorm_bwd_partial_rows(int rows);
+void launch_rmsnorm_fwd(const void*, const void*, const int64_t*, void*, float*, int, int, int64_t,
+                        int64_t, float, cudaStream_t);
+void launch_rmsnorm_bwd(const void*, const void*, const void*, const float*, void*, float*, float*,
+                        int, int, int64_t, int64_t, int64_t, int, int, cudaStream_t);
+void launch_swiglu_fwd(const void*, void*, int64_t, int, cudaStream_t);
+void launch_swiglu_bwd(const void*, const void*, void*, int64_t, int, cudaStream_t);
+void launch_rope(void*, const int64_t*, const float*, const float*, int64_t, int, int, int, int64_t,
+                 int64_t, float, cudaStream_t);
+int launch_loss_fwd(int, const void*, const void*, const uint8_t*, float*, float*, int*, int*, int,
+                    int, int64_t, int64_t, int, cudaStream_t);
+int launch_loss_bwd(int, const void*, const void*, const float*, const float*, void*, int, int, int,
+                    int64_t, int64_t, int64_t, int, cudaStream_t);
+int sumsq_num_partials();
+void launch_sumsq(const void*, int, int64_t, float*, float*, int, cudaStream_t);
+void launch_adamw(float*, float*, float*, const void*, int, void*, int64_t, const float*,
+                  const float*, cudaStream_t);
+}  // namespace sb200
+
+namespace {
+
+using at::Tensor;
+
+inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+void check_rows(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.scalar_type() == at::kBFloat16, name, " must be bfloat16");
+  TORCH_CHECK(t.dim() == 2 && t.stride(1) == 1, name, " must be 2-D with unit inner stride");
+  TORCH_CHECK(t.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0, name,
+              " rows must be 16-byte aligned");
+}
+
+void rmsnorm_fwd(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& row_index, Tensor y,
+                 c10::optional<Tensor> rstd, double eps) {
+  check_rows(x, "x");
+  check_rows(y, "y");
+  const int H = (int)y.size(1);
+  const int rows = (int)y.size(0);
+  TORCH_CHECK(x.size(1) == H && w.numel() == H && w.is_contiguous() &&
+                  w.scalar_type() == at::kBFloat16,
+              "rmsnorm: shape/dtype mismatch");
+  TORCH_CHECK(H % 8 == 0 && H <= 16384, "rmsnorm: H must be a multiple of 8 and <= 16384");
+  const int64_t* idx = nullptr;
+  if (row_index.has_value()) {
+    TORCH_CHECK(row_index->scalar_type() == at::kLong && row_index->is_contiguous() &&
+                    row_index->numel() == rows,
+                "rmsnorm: row_index must be int64[rows]");
+    idx = row_index->data_ptr<int64_t>();
+  } else {
+    TORCH_CHECK(x.size(0) == rows, "rmsnorm: row count mismatch");
+  }
+  float* rs = nullptr;
+  if (rstd.has_value()) {
+    TORCH_CHECK(rstd->scalar_type() == at::kFloat && rstd->numel() == rows && rstd->is_contiguous());
+    rs = rstd->data_ptr<float>();
+  }
+  c10::cuda::CUDAGuard guard(x.device());
+  sb200::launch_rmsnorm_fwd(x.data_ptr(), w.data_ptr(), idx, y.data_ptr(), rs, rows, H, x.stride(0),
+                            y.stride(0), (float)eps, cur_stream());
+}
+
+void rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd, Tensor dx,
+                 c10::optional<Tensor> dw, bool accumulate_dx, bool accumulate_dw) {
+  check_rows(dy, "dy");
+  check_rows(x, "x");
+  check_rows(dx, "dx");
+  const int rows = (int)x.size(0), H = (int)x.size(1);
+  TORCH_CHECK(dy.size(0) == rows && dy.size(1) == H && dx.size(0) == rows && dx.size(1) == H);
+  TORCH_CHECK(H % 8 == 0 && H <= 16384);
+  c10::cuda::CUDAGuard guard(x.device());
+  float* dwp = nullptr;
+  float* dwo = nullptr;
+  Tensor partial;
+  if (dw.has_value()) {
+    TORCH_CHECK(dw->scalar_type() == at::kFloat && dw->numel() == H && dw->is_contiguous());
+    partial = at::empty({sb200::rmsnorm_bwd_partial_rows(rows), H}, dw->options());
+    dwp = partial.data_ptr<float>();
+    dwo = dw->data_ptr<float>();
+  }
+  sb200::launch_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(),
+                            dx.data_ptr(), dwp, dwo, rows, H, dy.stride(0), x.stride(0),
+                            dx.stride(0), accumulate_dx, accumulate_dw, cur_stream());
+}
+
+Tensor swiglu_fwd(const Tensor& gate_up) {
+  check_rows(gate_up, "gate_up");
+  TORCH_CHECK(gate_up.is_contiguous() && gate_up.size(1) % 16 == 0);
+  const int64_t rows = gate_up.size(0);
+  const int I = (int)(gate_up.size(1) / 2);
+  c10::cuda::CUDAGuard guard(gate_up.device());
+  Tensor h = at::empty({rows, I}, gate_up.options());
+  sb200::launch_swiglu_fwd(gate_up.data_ptr(), h.data_ptr(), rows, I, cur_stream());
+  return h;
+}
+
+Tensor swiglu_bwd(const Tensor& dh, const Tensor& gate_up) {
+  check_rows(gate_up, "gate_up");
+  check_rows(dh, "dh");
+  TORCH_CHECK(gate_up.is_contiguous() && dh.is_contiguous() && dh.size(1) * 2 == gate_up.size(1));
+  c10::cuda::CUDAGuard guard(gate_up.device());
+  Tensor out = at::empty_like(gate_up);
+  sb200::launch_swiglu_bwd(dh.data_ptr(), gate_up.data_ptr(), out.data_ptr(), gate_up.size(0),
+                           (int)dh.size(1), cur_stream());
+  return out;
+}
+
+// x: [tokens, >= heads*hd] view (row stride arbitrary); rotates the first `heads` heads in place.
+void rope_(Tensor x, const Tensor& positions, const Tensor& cos_t, const Tensor& sin_t, int64_t heads,
+           int64_t hd, int64_t rot, double sign) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1);
+  TORCH_CHECK(x.size(1) >= heads * hd && rot % 2 == 0 && rot <= hd);
+  TORCH_CHECK(positions.scalar_type() == at::kLong && positions.is_contiguous() &&
+              positions.numel() == x.size(0));
+  TORCH_CHECK(cos_t.scalar_type() == at::kFloat && sin_t.scalar_type() == at::kFloat &&
+              cos_t.is_contiguous() && sin_t.is_contiguous() && cos_t.dim() == 2 &&
+              cos_t.size(1) == rot / 2 && sin_t.sizes() == cos_t.sizes());
+  c10::cuda::CUDAGuard guard(x.device());
+  sb200::launch_rope(x.data_ptr(), positions.data_ptr<int64_t>(), cos_t.data_ptr<float>(),
+                     sin_t.data_ptr<float>(), x.size(0), (int)heads, (int)hd, (int)rot, x.stride(0),
+                     cos_t.size(0), (float)sign, cur_stream());
+}
+
+std::tuple<Tensor, Tensor, Tensor, Tensor> loss_fwd(int64_t op, const Tensor& logits,
+                                                    const Tensor& targets,
+                                                    const c10::optional<Tensor>& active,
+                                                    int64_t shift, int64_t rows) {
+  TORCH_CHECK(logits.is_cuda() && targets.is_cuda());
+  TORCH_CHECK(logits.scalar_type() == at::kBFloat16 && targets.scalar_type() == at::kBFloat16);
+  TORCH_CHECK(logits.dim() == 2 && targets.dim() == 2 && logits.stride(1) == 1 &&
+              targets.stride(1) == 1 && logits.size(1) == targets.size(1));
+  TORCH_CHECK(rows >= 0 && rows <= logits.size(0) && rows + shift <= targets.size(0) && shift >= 0);
+  c10::cuda::CUDAGuard guard(logits.device());
+  auto fopt = logits.options().dtype(at::kFloat);
+  Tensor loss = at::empty({rows}, fopt);
+  Tensor stats = at::empty({5, rows}, fopt);
+  Tensor am_d = at::empty({rows}, logits.options().dtype(at::kInt));
+  Tensor am_t = at::empty({rows}, logits.options().dtype(at::kInt));
+  const uint8_t* act = nullptr;
+  if (active.has_value()) {
+    TORCH_CHECK((active->scalar_type() == at::kBool || active->scalar_type() == at::kByte) &&
+                active->is_contiguous() && active->numel() == rows);
+    act = reinterpret_cast<const uint8_t*>(active->data_ptr());
+  }
+  const int rc = sb200::launch_loss_fwd((int)op, logits.data_ptr(), targets.data_ptr(), act,
+                                        loss.data_ptr<float>(), stats.data_ptr<float>(),
+                                        am_d.data_ptr<int>(), am_t.data_ptr<int>(), (int)rows,
+                                        (int)logits.size(1), logits.stride(0), targets.stride(0),
+                                        (int)shift, cur_stream());
+  TORCH_CHECK(rc == 0, "loss_fwd: unknown op ", op);
+  return {loss, stats, am_d, am_t};
+}
+
+Tensor loss_bwd(int64_t op, const Tensor& logits, const Tensor& targets, const Tensor& grad_out,
+                const Tensor& stats, int64_t shift, int64_t rows) {
+  TORCH_CHECK(grad_out.scalar_type() == at::kFloat && grad_out.is_contiguous() &&
+              grad_out.numel() == rows);
+  TORCH_CHECK(stats.scalar_type() == at::kFloat && stats.is_contiguous() && stats.size(0) == 5 &&
+              stats.size(1) == rows);
+  c10::cuda::CUDAGuard guard(logits.device());
+  Tensor d = at::empty({logits.size(0), logits.size(1)}, logits.options());
+  const int rc = sb200::launch_loss_bwd(
+      (int)op, logits.data_ptr(), targets.data_ptr(), grad_out.data_ptr<float>(),
+      stats.data_ptr<float>(), d.data_ptr(), (int)rows, (int)logits.size(0), (int)logits.size(1),
+      logits.stride(0), targets.stride(0), d.stride(0), (int)shift, cur_stream());
+  TORCH_CHECK(rc == 0, "loss_bwd: unknown op ", op);
+  return d;
+}
+
+void sumsq(const Tensor& g, Tensor out, bool accumulate) {
+  TORCH_CHECK(g.is_cuda() && g.is_contiguous() && out.scalar_type() == at::kFloat && out.numel() >= 1);
+  TORCH_CHECK(g.scalar_type() == at::kBFloat16 || g.scalar_type() == at::kFloat);
+  c10::cuda::CUDAGuard guard(g.device());
+  Tensor partial = at::empty({sb200::sumsq_num_partials()}, out.options());
+  sb200::launch_sumsq(g.data_ptr(), g.scalar_type() == at::kBFloat16, g.numel(),
+                      partial.data_ptr<float>(), out.data_ptr<float>(), accumulate, cur_stream());
+}
+
+void adamw(Tensor master, Tensor m, Tensor v, const Tensor& grad, c10::optional<Tensor> w16,
+           const Tensor& hyper, const c10::optional<Tensor>& norm_sq) {
+  const int64_t n = master.numel();
+  TORCH_CHECK(master.is_cuda() && master.scalar_type() == at::kFloat && master.is_contiguous());
+  TORCH_CHECK(m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat && m.numel() == n &&
+              v.numel() == n && m.is_contiguous() && v.is_contiguous());
+  TORCH_CHECK(grad.numel() == n && grad.is_contiguous() &&
+              (grad.scalar_type() == at::kBFloat16 || grad.scalar_type() == at::kFloat));
+  TORCH_CHECK(hyper.scalar_type() == at::kFloat && hyper.numel() >= 9 && hyper.is_cuda());
+  void* w = nullptr;
+  if (w16.has_value()) {
+    TORCH_CHECK(w16->scalar_type() == at::kBFloat16 && w16->numel() == n && w16->is_contiguous());
+    w = w16->data_ptr();
+  }
+  const float* ns = nullptr;
+  if (norm_sq.has_value()) {
+    TORCH_CHECK(norm_sq->scalar_type() == at::kFloat && norm_sq->is_cuda());
+    ns = norm_sq->data_ptr<float>();
+  }
+  c10::cuda::CUDAGuard guard(master.device());
+  sb200::launch_adamw(master.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(),
+                      grad.data_ptr(), grad.scalar_type() == at::kBFloat16, w, n,
+                      hyper.data_ptr<float>(), ns, cur_stream());
+}
+
+}  // namespace
+
+TORCH_LIBRARY(sb200, m) {
+  m.def("rmsnorm_fwd", &rmsnorm_fwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("rope_", &rope_);
+  m.def("loss_fwd", &loss_fwd);
+  m.def("loss_bwd", &loss_bwd);
+  m.def("sumsq", &sumsq);
+  m.def("adamw", &adamw);
+}

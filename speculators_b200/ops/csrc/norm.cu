@@ -1,0 +1,181 @@
+// RMSNorm forward / backward for bf16 activations (fp32 statistics).
+//
+// Forward:  y[r, :] = x[src(r), :] * rsqrt(mean(x^2) + eps) * w
+//   * `row_index` (optional) gathers the input row, which turns the kernel into
+//     "embedding lookup + RMSNorm" for the EAGLE-3 first layer;
+//   * separate row strides for x and y let the caller write straight into one half
+//     of a [T, 2H] buffer, so the concat of normalised embeddings and normalised
+//     hidden states never exists as a separate copy.
+// Backward: dx = rstd * (g - xhat * mean(g * xhat)),  g = dy * w,  xhat = x * rstd
+//           dw[c] = sum_r dy[r, c] * xhat[r, c]   (two-stage: per-CTA partials,
+//           then a column reduce; the partial buffer is caller-provided scratch).
+#include "common.cuh"
+
+namespace sb200 {
+
+constexpr int kNormThreads = 256;
+// Vectors (8 x bf16) handled per thread are a template parameter NV in {2, 4, 8}:
+// H <= 256 * 8 * NV, i.e. 4096 / 8192 / 16384 columns.
+
+template <int NV>
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                   const int64_t* __restrict__ row_index, __nv_bfloat16* __restrict__ y,
+                   float* __restrict__ rstd_out, int rows, int H, int64_t x_stride,
+                   int64_t y_stride, float eps) {
+  __shared__ float scratch[33];
+  const int nvec = H >> 3;
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    const int64_t src = row_index ? row_index[r] : (int64_t)r;
+    const __nv_bfloat16* xr = x + src * x_stride;
+    float cache[NV][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
+        unpack8(ld8(xr + (v << 3)), cache[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += cache[i][j] * cache[i][j];
+      }
+    }
+    ss = block_sum(ss, scratch);
+    const float rstd = rsqrtf(ss / (float)H + eps);
+    if (threadIdx.x == 0 && rstd_out) rstd_out[r] = rstd;
+    __nv_bfloat16* yr = y + (int64_t)r * y_stride;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
+        float wv[8], o[8];
+        unpack8(ld8(w + (v << 3)), wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          // match the eager module: normalise in fp32, round to bf16, then scale
+          o[j] = __bfloat162float(__float2bfloat16(cache[i][j] * rstd)) * wv[j];
+        }
+        st8(yr + (v << 3), pack8(o));
+      }
+    }
+  }
+}
+
+// One CTA walks rows blockIdx.x, +gridDim.x, ... and keeps its dw partial in registers.
+template <int NV>
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                   const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
+                   __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, int rows, int H,
+                   int64_t dy_stride, int64_t x_stride, int64_t dx_stride, int accumulate_dx) {
+  __shared__ float scratch[33];
+  const int nvec = H >> 3;
+  float dwacc[NV][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
+
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    const float rstd = rstd_in[r];
+    const __nv_bfloat16* xr = x + (int64_t)r * x_stride;
+    const __nv_bfloat16* dyr = dy + (int64_t)r * dy_stride;
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
+        float xv[8], dv[8], wv[8];
+        unpack8(ld8(xr + (v << 3)), xv);
+        unpack8(ld8(dyr + (v << 3)), dv);
+        unpack8(ld8(w + (v << 3)), wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xh = xv[j] * rstd;
+          dot += dv[j] * wv[j] * xh;
+          dwacc[i][j] += dv[j] * xh;
+        }
+      }
+    }
+    dot = block_sum(dot, scratch) / (float)H;
+    __nv_bfloat16* dxr = dx + (int64_t)r * dx_stride;
+    // second pass re-reads the row (L1/L2 resident) instead of holding it in registers
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
+        float xv[8], dv[8], wv[8], o[8];
+        unpack8(ld8(xr + (v << 3)), xv);
+        unpack8(ld8(dyr + (v << 3)), dv);
+        unpack8(ld8(w + (v << 3)), wv);
+        if (accumulate_dx) unpack8(ld8(dxr + (v << 3)), o);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float d = rstd * (dv[j] * wv[j] - xv[j] * rstd * dot);
+          o[j] = accumulate_dx ? o[j] + d : d;
+        }
+        st8(dxr + (v << 3), pack8(o));
+      }
+    }
+  }
+  if (dw_partial) {
+    float* out = dw_partial + (int64_t)blockIdx.x * H;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) out[(v << 3) + j] = dwacc[i][j];
+      }
+    }
+  }
+}
+
+// dw[c] (+)= sum_p partial[p, c]
+__global__ void colsum_kernel(const float* __restrict__ partial, float* __restrict__ dw, int P,
+                              int H, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= H) return;
+  float s = 0.f;
+  for (int p = 0; p < P; ++p) s += partial[(int64_t)p * H + c];
+  dw[c] = accumulate ? dw[c] + s : s;
+}
+
+int rmsnorm_bwd_partial_rows(int rows) {
+  int g = 2 * kNumSM;
+  return rows < g ? rows : g;
+}
+
+void launch_rmsnorm_fwd(const void* x, const void* w, const int64_t* row_index, void* y,
+                        float* rstd, int rows, int H, int64_t x_stride, int64_t y_stride, float eps,
+                        cudaStream_t stream) {
+  if (rows <= 0) return;
+  int grid = rows < 8 * kNumSM ? rows : 8 * kNumSM;
+#define SB200_FWD(NVV)                                                                         \
+  rmsnorm_fwd_kernel<NVV><<<grid, kNormThreads, 0, stream>>>(                                    \
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, row_index, (__nv_bfloat16*)y, rstd, rows, \
+      H, x_stride, y_stride, eps)
+  if (H <= 4096) SB200_FWD(2);
+  else if (H <= 8192) SB200_FWD(4);
+  else SB200_FWD(8);
+#undef SB200_FWD
+}
+
+void launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
+                        float* dw_partial, float* dw, int rows, int H, int64_t dy_stride,
+                        int64_t x_stride, int64_t dx_stride, int accumulate_dx, int accumulate_dw,
+                        cudaStream_t stream) {
+  if (rows <= 0) return;
+  const int grid = rmsnorm_bwd_partial_rows(rows);
+#define SB200_BWD(NVV)                                                                       \
+  rmsnorm_bwd_kernel<NVV><<<grid, kNormThreads, 0, stream>>>(                                  \
+      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd,         \
+      (__nv_bfloat16*)dx, dw_partial, rows, H, dy_stride, x_stride, dx_stride, accumulate_dx)
+  if (H <= 4096) SB200_BWD(2);
+  else if (H <= 8192) SB200_BWD(4);
+  else SB200_BWD(8);
+#undef SB200_BWD
+  if (dw_partial && dw)
+    colsum_kernel<<<(H + 255) / 256, 256, 0, stream>>>(dw_partial, dw, grid, H, accumulate_dw);
+}
+
+}  // namespace sb200

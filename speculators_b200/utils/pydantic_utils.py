@@ -1,0 +1,66 @@
+"""Polymorphic pydantic models keyed by a discriminator field.
+
+``Base.model_validate({"kind": "x", ...})`` returns an instance of the subclass
+registered as ``"x"``.  The reference gets this by rebuilding a tagged-union core
+schema every time the registry changes (src/speculators/utils/pydantic_utils.py:
+41-194, ``reload_schema``).  Here the dispatch happens at validation time in a
+``wrap`` validator on the base class, so a subclass registered after import is
+picked up without any schema rebuild; ``reload_schema`` is kept as a cheap
+``model_rebuild`` for API parity.
+"""
+
+from __future__ import annotations
+
+from typing import Any, ClassVar
+
+from pydantic import BaseModel, model_validator
+
+from speculators_b200.utils.registry import ClassRegistryMixin
+
+__all__ = ["PydanticClassRegistryMixin", "ReloadableBaseModel"]
+
+
+class ReloadableBaseModel(BaseModel):
+    @classmethod
+    def reload_schema(cls) -> None:
+        cls.model_rebuild(force=True)
+
+
+class PydanticClassRegistryMixin(ReloadableBaseModel, ClassRegistryMixin):
+    schema_discriminator: ClassVar[str] = "model_type"
+
+    @classmethod
+    def __pydantic_schema_base_type__(cls) -> type[Any]:
+        """Root of the polymorphic family: the first class in the MRO (walking up
+        from ``cls``) that declares ``schema_discriminator`` in its own body."""
+        root = cls
+        for klass in cls.__mro__:
+            if "schema_discriminator" in vars(klass) and klass is not PydanticClassRegistryMixin:
+                root = klass
+        return root
+
+    @classmethod
+    def register_decorator(cls, clazz: type[Any], name: str | None = None) -> type[Any]:
+        if not (isinstance(clazz, type) and issubclass(clazz, BaseModel)):
+            raise TypeError(f"{clazz!r} is not a pydantic BaseModel subclass")
+        return super().register_decorator(clazz, name=name)
+
+    @model_validator(mode="wrap")
+    @classmethod
+    def _dispatch_on_discriminator(cls, value: Any, handler):  # noqa: ANN001
+        if isinstance(value, cls) or not isinstance(value, dict):
+            return handler(value)
+        root = cls.__pydantic_schema_base_type__()
+        if cls is not root:
+            return handler(value)  # already the concrete class
+        table = root.registry or {}
+        tag = value.get(root.schema_discriminator)
+        target = table.get(tag) if isinstance(tag, str) else None
+        if target is None or target is cls:
+            if table and tag is not None and tag not in table and tag != "":
+                raise ValueError(
+                    f"unknown {root.schema_discriminator}={tag!r}; registered: "
+                    f"{sorted(table)}"
+                )
+            return handler(value)
+        return target.model_validate(value)

@@ -1,0 +1,32 @@
+"""Small device helpers (parity: src/speculators/utils/util.py).  This framework
+targets CUDA (B200) with a CPU path for tests; there is no NPU branch."""
+
+from __future__ import annotations
+
+import torch
+
+__all__ = ["empty_cache", "get_current_device", "get_device_name", "mem_get_info"]
+
+
+def get_device_name() -> str:
+    return "cuda" if torch.cuda.is_available() else "cpu"
+
+
+def get_current_device() -> torch.device:
+    if torch.cuda.is_available():
+        return torch.device("cuda", torch.cuda.current_device())
+    return torch.device("cpu")
+
+
+def mem_get_info() -> tuple[int, int]:
+    if torch.cuda.is_available():
+        return torch.cuda.mem_get_info()
+    import psutil
+
+    vm = psutil.virtual_memory()
+    return vm.available, vm.total
+
+
+def empty_cache() -> None:
+    if torch.cuda.is_available():
+        torch.cuda.empty_cache()
