@@ -19,6 +19,7 @@ int launch_loss_fwd(int, const void*, const void*, const uint8_t*, float*, float
                     int, int64_t, int64_t, int, cudaStream_t);
 int launch_loss_bwd(int, const void*, const void*, const float*, const float*, void*, int, int, int,
                     int64_t, int64_t, int64_t, int, cudaStream_t);
+int64_t launch_count();
 int sumsq_num_partials();
 void launch_sumsq(const void*, int, int64_t, float*, float*, int, cudaStream_t);
 void launch_adamw(float*, float*, float*, const void*, int, void*, int64_t, const float*,
@@ -209,6 +210,8 @@ void adamw(Tensor master, Tensor m, Tensor v, const Tensor& grad, c10::optional<
                       hyper.data_ptr<float>(), ns, cur_stream());
 }
 
+int64_t launch_count() { return sb200::launch_count(); }
+
 }  // namespace
 
 TORCH_LIBRARY(sb200, m) {
@@ -221,4 +224,5 @@ TORCH_LIBRARY(sb200, m) {
   m.def("loss_bwd", &loss_bwd);
   m.def("sumsq", &sumsq);
   m.def("adamw", &adamw);
+  m.def("launch_count", &launch_count);
 }

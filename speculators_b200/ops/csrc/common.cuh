@@ -6,6 +6,8 @@
 
 namespace sb200 {
 
+void count_launch(int n);
+
 constexpr int kWarp = 32;
 // B200: 148 SMs.  Persistent / grid-stride kernels size their grids from this.
 constexpr int kNumSM = 148;

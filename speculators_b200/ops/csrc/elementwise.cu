@@ -92,12 +92,14 @@ static inline int grid_for(int64_t total, int threads) {
 
 void launch_swiglu_fwd(const void* gate_up, void* h, int64_t rows, int I, cudaStream_t stream) {
   if (rows <= 0) return;
+  count_launch(1);
   swiglu_fwd_kernel<<<grid_for(rows * (I >> 3), 256), 256, 0, stream>>>(
       (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)h, rows, I);
 }
 void launch_swiglu_bwd(const void* dh, const void* gate_up, void* dgate_up, int64_t rows, int I,
                        cudaStream_t stream) {
   if (rows <= 0) return;
+  count_launch(1);
   swiglu_bwd_kernel<<<grid_for(rows * (I >> 3), 256), 256, 0, stream>>>(
       (const __nv_bfloat16*)dh, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)dgate_up, rows, I);
 }
@@ -105,6 +107,7 @@ void launch_rope(void* x, const int64_t* positions, const float* cos_t, const fl
                  int64_t tokens, int heads, int hd, int rot, int64_t row_stride, int64_t max_pos,
                  float sign, cudaStream_t stream) {
   if (tokens <= 0) return;
+  count_launch(1);
   rope_kernel<<<grid_for(tokens * heads * (rot >> 1), 256), 256, 0, stream>>>(
       (__nv_bfloat16*)x, positions, cos_t, sin_t, tokens, heads, hd, rot, row_stride, max_pos, sign);
 }

@@ -273,6 +273,7 @@ int launch_loss_fwd(int op, const void* logits, const void* targets, const uint8
                     float* loss, float* stats, int* argmax_d, int* argmax_t, int rows, int V,
                     int64_t ld_logits, int64_t ld_targets, int shift, cudaStream_t stream) {
   if (rows <= 0) return 0;
+  count_launch(1);
 #define SB200_LF(OPV)                                                                            \
   loss_fwd_kernel<OPV><<<rows, kLossThreads, 0, stream>>>(                                        \
       (const __nv_bfloat16*)logits, (const __nv_bfloat16*)targets, active, loss, stats, argmax_d, \
@@ -294,6 +295,7 @@ int launch_loss_bwd(int op, const void* logits, const void* targets, const float
                     int64_t ld_logits, int64_t ld_targets, int64_t ld_dlogits, int shift,
                     cudaStream_t stream) {
   if (total_rows <= 0) return 0;
+  count_launch(1);
 #define SB200_LB(OPV)                                                                         \
   loss_bwd_kernel<OPV><<<total_rows, kLossThreads, 0, stream>>>(                               \
       (const __nv_bfloat16*)logits, (const __nv_bfloat16*)targets, grad_out, stats,            \

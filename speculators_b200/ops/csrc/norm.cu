@@ -154,6 +154,7 @@ void launch_rmsnorm_fwd(const void* x, const void* w, const int64_t* row_index, 
   rmsnorm_fwd_kernel<NVV><<<grid, kNormThreads, 0, stream>>>(                                    \
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, row_index, (__nv_bfloat16*)y, rstd, rows, \
       H, x_stride, y_stride, eps)
+  count_launch(1);
   if (H <= 4096) SB200_FWD(2);
   else if (H <= 8192) SB200_FWD(4);
   else SB200_FWD(8);
@@ -170,10 +171,12 @@ void launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const floa
   rmsnorm_bwd_kernel<NVV><<<grid, kNormThreads, 0, stream>>>(                                  \
       (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd,         \
       (__nv_bfloat16*)dx, dw_partial, rows, H, dy_stride, x_stride, dx_stride, accumulate_dx)
+  count_launch(1);
   if (H <= 4096) SB200_BWD(2);
   else if (H <= 8192) SB200_BWD(4);
   else SB200_BWD(8);
 #undef SB200_BWD
+  if (dw_partial && dw) count_launch(1);
   if (dw_partial && dw)
     colsum_kernel<<<(H + 255) / 256, 256, 0, stream>>>(dw_partial, dw, grid, H, accumulate_dw);
 }

@@ -113,6 +113,7 @@ int sumsq_num_partials() { return 4 * kNumSM; }
 void launch_sumsq(const void* g, int is_bf16, int64_t n, float* partial, float* out, int accumulate,
                   cudaStream_t stream) {
   const int P = sumsq_num_partials();
+  count_launch(2);
   if (is_bf16)
     sumsq_partial_kernel<__nv_bfloat16><<<P, kOptThreads, 0, stream>>>((const __nv_bfloat16*)g, n,
                                                                         partial);
@@ -127,6 +128,7 @@ void launch_adamw(float* master, float* m, float* v, const void* grad, int grad_
   int64_t blocks = (n + kOptThreads - 1) / kOptThreads;
   const int64_t cap = (int64_t)kNumSM * 16;
   const int grid = (int)(blocks < cap ? blocks : cap);
+  count_launch(1);
   if (grad_is_bf16)
     adamw_kernel<__nv_bfloat16><<<grid, kOptThreads, 0, stream>>>(
         master, m, v, (const __nv_bfloat16*)grad, (__nv_bfloat16*)w16, n, hyper, norm_sq);

@@ -1,0 +1,323 @@
+"""Flat-buffer training engine: mixed precision, data parallelism and the
+optimizer in one place.
+
+Layout.  Every trainable parameter of the model becomes a view into one
+contiguous *compute* buffer (bf16 on GPU) and its ``.grad`` a view into a parallel
+gradient buffer, so backward accumulates straight into memory that is already
+laid out for a single collective.  The optimizer keeps fp32 master weights and
+AdamW moments for the slice ``[lo, hi)`` of that buffer owned by this rank:
+
+* replicated mode (the reference's DDP, src/speculators/train/trainer.py:323-336):
+  every rank owns everything; gradients are all-reduced.
+* sharded mode (the reference's ``--fsdp-shard``,
+  src/speculators/train/distributed.py:197-216): each rank owns ``1/world`` of the
+  buffer; gradients are reduce-scattered, the owner runs AdamW on its slice and
+  the refreshed bf16 weights are all-gathered.  Unlike FSDP2, parameters are
+  gathered once per optimizer step, not once per layer call, so the ``S``
+  TTT passes of EAGLE-3 reuse resident weights; with 180 GB of HBM per GPU the
+  resident bf16 copy of a draft model is negligible.
+
+A step is: (sum of squares of the owned gradient slice -> all-reduce of one
+scalar) -> fused AdamW with the clip coefficient applied in-kernel -> all-gather.
+No value is read back to the host, so the whole step can be captured in a CUDA
+graph.  Muon (the reference's default optimizer for 2-D weights) is supported in
+replicated mode through a Newton-Schulz update on the matrix views.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from speculators_b200 import ops
+
+__all__ = ["EngineConfig", "TrainEngine", "split_named_params_for_muon"]
+
+_ALIGN = 128  # elements; keeps every parameter and every shard 16-byte aligned
+_ADAMW_NAME_HINTS = ("embed_tokens", "lm_head")
+
+
+def split_named_params_for_muon(model: nn.Module):
+    """(muon, adamw) named-parameter lists: Muon takes trainable 2-D matrices with
+    both dims > 1 that are neither embeddings nor LM heads
+    (src/speculators/train/optimizers.py:32-58)."""
+    muon, adamw = [], []
+    for name, p in model.named_parameters():
+        if not p.requires_grad:
+            continue
+        is_matrix = p.ndim == 2 and min(p.shape) > 1 and not any(h in name for h in _ADAMW_NAME_HINTS)
+        (muon if is_matrix else adamw).append((name, p))
+    return muon, adamw
+
+
+@dataclass
+class EngineConfig:
+    lr: float = 1e-4
+    betas: tuple[float, float] = (0.9, 0.999)
+    eps: float = 1e-8
+    weight_decay: float = 0.01
+    max_grad_norm: float = 1.0
+    optimizer: str = "adamw"  # "adamw" | "muon"
+    muon_lr: float = 0.02
+    muon_momentum: float = 0.95
+    muon_weight_decay: float = 0.1
+    muon_ns_steps: int = 5
+    muon_adjust_lr_fn: str = "match_rms_adamw"
+    compute_dtype: torch.dtype = torch.bfloat16
+    shard: bool = False
+    group: object | None = None
+    broadcast_from_rank0: bool = True
+    extra: dict = field(default_factory=dict)
+
+
+class TrainEngine:
+    def __init__(self, model: nn.Module, config: EngineConfig, device: torch.device | str | None = None):
+        self.model = model
+        self.cfg = config
+        self.device = torch.device(device) if device is not None else next(model.parameters()).device
+        self.group = config.group
+        self.distributed = dist.is_available() and dist.is_initialized()
+        self.world = dist.get_world_size(self.group) if self.distributed else 1
+        self.rank = dist.get_rank(self.group) if self.distributed else 0
+        self.sharded = bool(config.shard) and self.world > 1
+        self.step_count = 0
+        self._flatten()
+        self._init_state()
+
+    # ------------------------------------------------------------------ layout
+    def _flatten(self) -> None:
+        cfg, dev = self.cfg, self.device
+        model = self.model
+        # frozen tensors: move + cast, they never enter the flat buffers
+        for p in model.parameters():
+            if not p.requires_grad:
+                p.data = p.data.to(device=dev, dtype=cfg.compute_dtype if p.is_floating_point() else p.dtype)
+        for mod in model.modules():
+            for key, buf in list(mod._buffers.items()):  # noqa: SLF001
+                if buf is not None:
+                    mod._buffers[key] = buf.to(dev)  # noqa: SLF001
+        named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
+        if not named:
+            raise ValueError("No trainable parameters found to optimize.")
+        use_muon = cfg.optimizer == "muon"
+        muon_names = {n for n, _ in split_named_params_for_muon(model)[0]} if use_muon else set()
+        # Muon matrices first, then the AdamW tail: two contiguous regions
+        named.sort(key=lambda np_: 0 if np_[0] in muon_names else 1)
+        self.names: list[str] = []
+        self.params: list[nn.Parameter] = []
+        self.offsets: list[int] = []
+        off = 0
+        self.muon_end = 0
+        for name, p in named:
+            self.names.append(name)
+            self.params.append(p)
+            self.offsets.append(off)
+            off += (p.numel() + _ALIGN - 1) // _ALIGN * _ALIGN
+            if name in muon_names:
+                self.muon_end = off
+        unit = _ALIGN * self.world
+        self.total = (off + unit - 1) // unit * unit
+        self.flat_w = torch.zeros(self.total, dtype=cfg.compute_dtype, device=dev)
+        self.flat_g = torch.zeros(self.total, dtype=cfg.compute_dtype, device=dev)
+        init32 = torch.zeros(self.total, dtype=torch.float32, device=dev)
+        for p, o in zip(self.params, self.offsets):
+            init32[o : o + p.numel()].copy_(p.data.detach().reshape(-1).to(device=dev, dtype=torch.float32))
+        if self.distributed and cfg.broadcast_from_rank0:
+            dist.broadcast(init32, src=dist.get_global_rank(self.group, 0) if self.group is not None else 0, group=self.group)
+            for p in model.parameters():  # frozen weights too: every rank trains the same model
+                if not p.requires_grad:
+                    dist.broadcast(p.data, src=dist.get_global_rank(self.group, 0) if self.group is not None else 0, group=self.group)
+        self.flat_w.copy_(init32)
+        for p, o in zip(self.params, self.offsets):
+            p.data = self.flat_w[o : o + p.numel()].view(p.shape)
+            p.grad = self.flat_g[o : o + p.numel()].view(p.shape)
+        self._init32 = init32
+
+    def _init_state(self) -> None:
+        if self.sharded:
+            per = self.total // self.world
+            self.lo, self.hi = self.rank * per, (self.rank + 1) * per
+        else:
+            self.lo, self.hi = 0, self.total
+        n = self.hi - self.lo
+        dev = self.device
+        fp32_compute = self.cfg.compute_dtype == torch.float32
+        # with fp32 compute weights the flat buffer *is* the master copy
+        self.master = self.flat_w[self.lo : self.hi] if fp32_compute else self._init32[self.lo : self.hi].clone()
+        del self._init32
+        self.exp_avg = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.norm_sq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.hyper = torch.zeros(ops.HYPER_LEN, dtype=torch.float32, device=dev)
+        self._hyper_host = torch.zeros(ops.HYPER_LEN, dtype=torch.float32)
+        if dev.type == "cuda":
+            self._hyper_host = self._hyper_host.pin_memory()
+        self.grad_shard = (
+            torch.zeros(n, dtype=self.cfg.compute_dtype, device=dev) if self.sharded else self.flat_g
+        )
+        self.base_lr = self.cfg.lr
+        self.base_muon_lr = self.cfg.muon_lr
+
+    # ------------------------------------------------------------------ step
+    def zero_grad(self) -> None:
+        self.flat_g.zero_()
+        for p, o in zip(self.params, self.offsets):  # re-attach if something replaced .grad
+            if p.grad is None or p.grad.data_ptr() != self.flat_g.data_ptr() + o * self.flat_g.element_size():
+                p.grad = self.flat_g[o : o + p.numel()].view(p.shape)
+
+    def prepare_hyper(self, lr: float | None = None) -> None:
+        """Host side of a step: bump the step counter and stage lr / bias corrections
+        (async copy from pinned memory).  Call before ``apply`` (or before a graph
+        replay that contains ``apply``)."""
+        self.step_count += 1
+        b1, b2 = self.cfg.betas
+        lr = self.base_lr if lr is None else lr
+        h = self._hyper_host
+        h[0], h[1], h[2], h[3], h[4] = lr, b1, b2, self.cfg.eps, self.cfg.weight_decay
+        h[5] = 1.0 - b1**self.step_count
+        h[6] = 1.0 - b2**self.step_count
+        h[7] = self.cfg.max_grad_norm if self.cfg.max_grad_norm else 0.0
+        h[8] = 1.0 / self.world
+        self.hyper.copy_(h, non_blocking=True)
+
+    def apply(self) -> None:
+        """Device side of a step (capturable): reduce, norm, update, gather."""
+        if self.distributed and self.world > 1:
+            if self.sharded:
+                dist.reduce_scatter_tensor(self.grad_shard, self.flat_g, op=dist.ReduceOp.SUM, group=self.group)
+            else:
+                dist.all_reduce(self.flat_g, op=dist.ReduceOp.SUM, group=self.group)
+        g = self.grad_shard if self.sharded else self.flat_g
+        ops.sum_of_squares(g, self.norm_sq, accumulate=False)
+        if self.sharded:
+            dist.all_reduce(self.norm_sq, op=dist.ReduceOp.SUM, group=self.group)
+        w16 = None if self.cfg.compute_dtype == torch.float32 else self.flat_w[self.lo : self.hi]
+        if self.cfg.optimizer == "muon" and self.muon_end > 0:
+            self._muon_update(g)
+            a, b = self.muon_end - self.lo, self.hi - self.lo
+            if b > a >= 0:
+                ops.adamw_step_(self.master[a:b], self.exp_avg[a:b], self.exp_avg_sq[a:b], g[a:b],
+                                None if w16 is None else w16[a:b], self.hyper, self.norm_sq)
+        else:
+            ops.adamw_step_(self.master, self.exp_avg, self.exp_avg_sq, g, w16, self.hyper, self.norm_sq)
+        if self.sharded:
+            dist.all_gather_into_tensor(self.flat_w, self.flat_w[self.lo : self.hi], group=self.group)
+
+    def step(self, lr: float | None = None) -> None:
+        self.prepare_hyper(lr)
+        self.apply()
+
+    # ------------------------------------------------------------------ muon
+    def _muon_update(self, g: torch.Tensor) -> None:
+        """Momentum + Newton-Schulz orthogonalised update for the matrix region
+        (replicated mode).  Mirrors ``torch.optim.Muon`` semantics: nesterov
+        momentum, quintic NS iteration, decoupled weight decay and the
+        ``match_rms_adamw`` learning-rate adjustment ``0.2 * sqrt(max(m, n))``."""
+        if self.sharded:
+            raise NotImplementedError("Muon with --fsdp-shard: use --optimizer adamw or drop --fsdp-shard")
+        cfg = self.cfg
+        coef_scale = 1.0 / self.world
+        total_norm = coef_scale * self.norm_sq.sqrt()
+        clip = torch.clamp(cfg.max_grad_norm / (total_norm + 1e-6), max=1.0) if cfg.max_grad_norm else torch.ones_like(total_norm)
+        lr_scale = self.hyper[0] / max(self.base_lr, 1e-30)  # follow the schedule of the AdamW group
+        for p, o in zip(self.params, self.offsets):
+            if o >= self.muon_end:
+                break
+            n = p.numel()
+            grad = g[o : o + n].view(p.shape).float() * (coef_scale * clip)
+            buf = self.exp_avg[o : o + n].view(p.shape)
+            buf.lerp_(grad, 1 - cfg.muon_momentum)
+            update = grad.lerp(buf, cfg.muon_momentum)
+            update = _newton_schulz(update, cfg.muon_ns_steps)
+            rows, cols = p.shape
+            if cfg.muon_adjust_lr_fn == "match_rms_adamw":
+                adj = 0.2 * math.sqrt(max(rows, cols))
+            else:
+                adj = math.sqrt(max(1.0, rows / cols))
+            lr = self.base_muon_lr * lr_scale
+            master = self.master[o : o + n].view(p.shape)
+            master.mul_(1 - lr * cfg.muon_weight_decay)
+            master.sub_(update * (lr * adj))
+            if self.cfg.compute_dtype != torch.float32:
+                self.flat_w[o : o + n].view(p.shape).copy_(master)
+
+    # ------------------------------------------------------------------ state
+    def grad_norm(self) -> torch.Tensor:
+        """Global gradient norm of the last ``apply`` (device scalar)."""
+        return self.norm_sq.sqrt() / self.world
+
+    def _gather_full(self, shard: torch.Tensor) -> torch.Tensor:
+        if not self.sharded:
+            return shard
+        full = torch.empty(self.total, dtype=shard.dtype, device=shard.device)
+        dist.all_gather_into_tensor(full, shard.contiguous(), group=self.group)
+        return full
+
+    def optimizer_state_dict(self) -> dict:
+        """Full (unsharded) optimizer state keyed by parameter name; every rank
+        participates in the gathers, all ranks receive the result."""
+        master, m, v = (self._gather_full(t) for t in (self.master, self.exp_avg, self.exp_avg_sq))
+        state = {}
+        for name, p, o in zip(self.names, self.params, self.offsets):
+            n = p.numel()
+            state[name] = {
+                "master": master[o : o + n].view(p.shape).cpu().clone(),
+                "exp_avg": m[o : o + n].view(p.shape).cpu().clone(),
+                "exp_avg_sq": v[o : o + n].view(p.shape).cpu().clone(),
+            }
+        return {"step": self.step_count, "optimizer": self.cfg.optimizer, "state": state}
+
+    def load_optimizer_state_dict(self, sd: dict) -> None:
+        self.step_count = int(sd.get("step", 0))
+        for name, p, o in zip(self.names, self.params, self.offsets):
+            entry = sd["state"].get(name)
+            if entry is None:
+                continue
+            n = p.numel()
+            a, b = max(o, self.lo), min(o + n, self.hi)
+            if a >= b:
+                continue
+            for key, dst in (("master", self.master), ("exp_avg", self.exp_avg), ("exp_avg_sq", self.exp_avg_sq)):
+                src = entry[key].reshape(-1).float()[a - o : b - o].to(self.device)
+                dst[a - self.lo : b - self.lo].copy_(src)
+        self.sync_compute_weights()
+
+    def sync_compute_weights(self) -> None:
+        """Refresh the compute buffer from the master weights (after loading state)."""
+        if self.cfg.compute_dtype != torch.float32:
+            self.flat_w[self.lo : self.hi].copy_(self.master)
+        if self.sharded:
+            dist.all_gather_into_tensor(self.flat_w, self.flat_w[self.lo : self.hi].clone(), group=self.group)
+
+    def load_model_weights_into_master(self) -> None:
+        """After ``model.load_state_dict`` wrote new values through the parameter
+        views, make them the master copy."""
+        if self.cfg.compute_dtype != torch.float32:
+            self.master.copy_(self.flat_w[self.lo : self.hi])
+
+    def master_state_dict(self) -> dict[str, torch.Tensor]:
+        """fp32 master weights keyed by parameter name (full tensors)."""
+        master = self._gather_full(self.master)
+        return {
+            name: master[o : o + p.numel()].view(p.shape).clone()
+            for name, p, o in zip(self.names, self.params, self.offsets)
+        }
+
+
+def _newton_schulz(g: torch.Tensor, steps: int) -> torch.Tensor:
+    a, b, c = 3.4445, -4.7750, 2.0315
+    x = g.bfloat16() if g.is_cuda else g.clone()
+    transposed = x.shape[0] > x.shape[1]
+    if transposed:
+        x = x.t()
+    x = x / (x.norm() + 1e-7)
+    for _ in range(steps):
+        gram = x @ x.t()
+        x = a * x + (b * gram + c * gram @ gram) @ x
+    if transposed:
+        x = x.t()
+    return x.to(g.dtype)

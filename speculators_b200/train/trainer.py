@@ -1,0 +1,500 @@
+"""Training loop.
+
+Same contract as src/speculators/train/trainer.py (``Trainer(model,
+TrainerConfig, train_loader, val_loader).run_training()``, one optimizer step per
+packed batch, gradient clipping at 1.0, metric reduction every ``log_freq`` steps,
+epoch / fractional-epoch checkpoints, mid-epoch resume, best-epoch tracking), with
+a different execution model:
+
+* mixed precision, data parallelism and the optimizer live in ``TrainEngine``
+  (flat bf16 compute weights, fp32 master + AdamW/Muon state, one collective per
+  step) instead of autocast + DDP/FSDP2 wrappers + ``torch.optim``;
+* on a GPU the step (zero-grad, forward, backward and, single-process, the
+  optimizer) is captured once per input signature into a CUDA graph and replayed;
+  batches are copied into the graph's static inputs from pinned host memory;
+* step timing uses CUDA events on the training stream (device time), not
+  ``synchronize`` + ``perf_counter``.
+"""
+
+from __future__ import annotations
+
+import json
+import logging
+import os
+import time
+import warnings
+from pathlib import Path
+from typing import Literal, NamedTuple
+
+import torch
+import torch.distributed as dist
+
+from speculators_b200.model import SpeculatorModel
+from speculators_b200.parallel.distributed import get_local_rank, get_rank, is_distributed
+from speculators_b200.parallel.engine import EngineConfig, TrainEngine
+from speculators_b200.train.checkpointer import Checkpointer
+from speculators_b200.train.graceful_shutdown import with_graceful_shutdown
+from speculators_b200.train.schedule import LRSchedule, resolve_scheduler_steps
+from speculators_b200.train.utils import normalize_counted_metrics
+
+root_logger = logging.getLogger("speculators")
+metric_logger = logging.getLogger("speculators.metrics")
+
+__all__ = ["Trainer", "TrainerConfig"]
+
+MIN_STEP_PCT = 0.25
+_VAL_SYNC_INTERVAL = 50  # barrier every N validation batches to bound rank skew
+
+
+class TrainerConfig(NamedTuple):
+    lr: float
+    num_epochs: int
+    save_path: str
+    resume_from_checkpoint: bool = False
+    train_call_kwargs: dict | None = None
+    val_call_kwargs: dict | None = None
+    optimizer: Literal["adamw", "muon"] = "adamw"
+    weight_decay: float = 0.01
+    muon_lr: float = 0.02
+    muon_momentum: float = 0.95
+    muon_weight_decay: float = 0.1
+    muon_ns_steps: int = 5
+    muon_adjust_lr_fn: str = "match_rms_adamw"
+    scheduler_type: Literal["linear", "cosine", "none"] = "linear"
+    scheduler_warmup_steps: int | None = None
+    scheduler_warmup_ratio: float | None = None
+    scheduler_total_steps: int | None = None
+    scheduler_num_cosine_cycles: float = 0.5
+    checkpoint_freq: float = 1
+    save_best: bool = False
+    hidden_states_dtype: torch.dtype = torch.bfloat16
+    log_freq: int = 1
+    fsdp_shard: bool = False
+    max_steps: int | None = None
+    max_grad_norm: float = 1.0
+    use_cuda_graph: bool | None = None  # None: on when training on a GPU
+    device: str | None = None  # None: cuda:<local_rank> when available, else cpu
+
+
+class _StepTimer:
+    """Phase marks of one training step.  On CUDA each mark records an event on the
+    current stream (no synchronisation until ``profile`` is read); on CPU it reads
+    ``perf_counter``.  Enabled only on steps that will be logged."""
+
+    def __init__(self, enabled: bool = False, device_type: str = "cpu"):
+        self.enabled = enabled
+        self.cuda = device_type == "cuda"
+        self._marks: dict[str, object] = {}
+
+    def reset(self, enabled: bool) -> None:
+        self.enabled = enabled
+        self._marks.clear()
+
+    def mark(self, name: str) -> None:
+        if not self.enabled:
+            return
+        if self.cuda:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self._marks[name] = ev
+        else:
+            self._marks[name] = time.perf_counter()
+
+    def _between(self, a: str, b: str) -> float:
+        ma, mb = self._marks.get(a), self._marks.get(b)
+        if ma is None or mb is None:
+            return 0.0
+        if self.cuda:
+            return float(ma.elapsed_time(mb))
+        return (mb - ma) * 1000.0
+
+    def profile(self, num_tokens: int) -> dict[str, float] | None:
+        if not self.enabled:
+            return None
+        if self.cuda:
+            torch.cuda.current_stream().synchronize()
+        fetch = self._between("start", "fetch")
+        fwd = self._between("fetch", "fwd")
+        bwd = self._between("fwd", "bwd")
+        opt = self._between("bwd", "opt")
+        step = self._between("start", "opt")
+        return {
+            "fetch_ms": fetch, "fwd_ms": fwd, "bwd_ms": bwd, "opt_ms": opt, "step_ms": step,
+            "tokens_per_s": num_tokens / (step / 1000.0) if step > 0 else 0.0,
+            "fetch_frac": fetch / step if step > 0 else 0.0,
+        }
+
+
+class _GraphedStep:
+    """CUDA-graph capture of forward + backward (+ optimizer) per input signature."""
+
+    def __init__(self, trainer: "Trainer", capture_optimizer: bool):
+        self.trainer = trainer
+        self.capture_optimizer = capture_optimizer
+        self.cache: dict[tuple, tuple] = {}
+        self.launches_per_capture: dict[tuple, int] = {}  # own-kernel launches recorded per graph
+        self.capture_launch_total = 0  # launches issued while warming up / capturing
+
+    @staticmethod
+    def signature(batch: dict) -> tuple:
+        return tuple(sorted((k, tuple(v.shape), str(v.dtype)) for k, v in batch.items() if isinstance(v, torch.Tensor)))
+
+    def _capture(self, batch: dict):
+        tr = self.trainer
+        dev = tr.device
+        from speculators_b200 import ops
+
+        count_before = ops.native().launch_count()
+        static_in = {k: torch.empty(v.shape, dtype=v.dtype, device=dev) for k, v in batch.items() if isinstance(v, torch.Tensor)}
+        for k, v in static_in.items():
+            v.copy_(batch[k], non_blocking=True)
+        kwargs = tr.config.train_call_kwargs or {}
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):  # warm-up without touching the weights
+                tr.engine.zero_grad()
+                _, loss, _ = tr.model(**static_in, **kwargs)
+                loss.backward()
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        count_capture = ops.native().launch_count()
+        with torch.cuda.graph(graph):
+            tr.engine.flat_g.zero_()
+            _, loss, metrics = tr.model(**static_in, **kwargs)
+            loss.backward()
+            if self.capture_optimizer:
+                tr.engine.apply()
+        count_after = ops.native().launch_count()
+        self.launches_per_capture[self.signature(batch)] = count_after - count_capture
+        self.capture_launch_total += count_after - count_before
+        return graph, static_in, loss, metrics
+
+    def run(self, batch: dict, lr: float | None):
+        sig = self.signature(batch)
+        entry = self.cache.get(sig)
+        tr = self.trainer
+        if entry is None:
+            entry = self._capture(batch)
+            self.cache[sig] = entry
+        graph, static_in, loss, metrics = entry
+        for k, v in static_in.items():
+            v.copy_(batch[k], non_blocking=True)
+        tr.timer.mark("fetch")
+        tr.engine.prepare_hyper(lr)
+        graph.replay()
+        tr.timer.mark("fwd")
+        tr.timer.mark("bwd")
+        if not self.capture_optimizer:
+            tr.engine.apply()
+        return loss, metrics
+
+
+class Trainer:
+    def __init__(self, model: SpeculatorModel, config: TrainerConfig, train_loader, val_loader=None):
+        self.model = model
+        self.config = config
+        self.local_rank = get_local_rank()
+        self.rank = get_rank()
+        self.train_loader = train_loader
+        self.val_loader = val_loader
+        self.is_distributed = is_distributed() or (dist.is_available() and dist.is_initialized())
+        self.resume_from_checkpoint = config.resume_from_checkpoint
+        if config.device is not None:
+            self.device = torch.device(config.device)
+        elif torch.cuda.is_available():
+            self.device = torch.device("cuda", self.local_rank)
+        else:
+            self.device = torch.device("cpu")
+        self.device_type = self.device.type
+        self.checkpointer = Checkpointer(config.save_path)
+        self.timer = _StepTimer(False, self.device_type)
+        self.setup_trainer()
+        self.setup_model()
+        self.setup_optimizer()
+
+    # ------------------------------------------------------------------ setup
+    def _training_state_path(self, epoch) -> Path:
+        return self.checkpointer.path / str(epoch) / "training_state.json"
+
+    def _save_training_state(self, epoch: int, local_step: int) -> None:
+        if not self.is_distributed or dist.get_rank() == 0:
+            path = self._training_state_path(epoch)
+            path.parent.mkdir(parents=True, exist_ok=True)
+            path.write_text(json.dumps({"epoch": epoch, "local_step": local_step, "global_step": self.global_step}))
+
+    def _load_training_state(self) -> dict:
+        path = self._training_state_path(self.checkpointer.previous_epoch)
+        if path.exists():
+            try:
+                return json.loads(path.read_text())
+            except (json.JSONDecodeError, OSError) as err:
+                root_logger.warning("Failed to read training state %s: %s", path, err)
+        return {}
+
+    def setup_trainer(self) -> None:
+        """Decide where training starts: fresh, next epoch, or inside an epoch."""
+        self.current_epoch = 0
+        self._resume_local_step = 0
+        self._resume_global_step = 0
+        prev = self.checkpointer.previous_epoch
+        if prev == -1:
+            root_logger.info("No previous training checkpoint found in '%s'. Starting fresh training run.", self.checkpointer.path)
+        elif not self.resume_from_checkpoint:
+            root_logger.warning(
+                "`resume_from_checkpoint` is False, starting training from scratch. This will overwrite the "
+                "existing checkpoints in %s.", self.checkpointer.path,
+            )
+        else:
+            root_logger.info("Found checkpoint at %s.", self.checkpointer.prev_path)
+            state = self._load_training_state()
+            mid_epoch = bool(state) and state.get("epoch") == prev and state.get("local_step", 0) > 0
+            self._resume_global_step = state.get("global_step", 0) if state else 0
+            if mid_epoch:
+                self.current_epoch = state["epoch"]
+                self._resume_local_step = state["local_step"]
+                root_logger.info(
+                    "Resuming mid-epoch from epoch=%d local_step=%d global_step=%d.",
+                    self.current_epoch, self._resume_local_step, self._resume_global_step,
+                )
+            else:
+                self.current_epoch = prev + 1
+                root_logger.info("Resuming training on epoch %d.", self.current_epoch)
+        self.global_step = self._resume_global_step
+        self.best_val_loss = float("inf")
+        if self.resume_from_checkpoint and prev != -1:
+            saved = self.checkpointer.load_best_val_loss()
+            if saved is not None:
+                self.best_val_loss = saved
+                root_logger.info("Restored best_val_loss=%.6f from checkpoint", saved)
+
+    def _loading_checkpoint(self) -> bool:
+        return self.resume_from_checkpoint and self.checkpointer.previous_epoch != -1
+
+    def setup_model(self) -> None:
+        SpeculatorModel.verify_training_compatible(self.model)
+        if self._loading_checkpoint():
+            self.checkpointer.load_model_state_dict(self.model)
+
+    def setup_optimizer(self) -> None:
+        cfg = self.config
+        compute_dtype = cfg.hidden_states_dtype if self.device_type == "cuda" else torch.float32
+        self.engine = TrainEngine(
+            self.model,
+            EngineConfig(
+                lr=cfg.lr, weight_decay=cfg.weight_decay, max_grad_norm=cfg.max_grad_norm, optimizer=cfg.optimizer,
+                muon_lr=cfg.muon_lr, muon_momentum=cfg.muon_momentum, muon_weight_decay=cfg.muon_weight_decay,
+                muon_ns_steps=cfg.muon_ns_steps, muon_adjust_lr_fn=cfg.muon_adjust_lr_fn,
+                compute_dtype=compute_dtype, shard=cfg.fsdp_shard, broadcast_from_rank0=True,
+            ),
+            device=self.device,
+        )
+        self.optimizers = [self.engine]
+        if self._loading_checkpoint():
+            self.checkpointer.load_optimizer_state_dict(self.model, self.engine)
+        if cfg.scheduler_type == "none":
+            self.schedulers: list[LRSchedule] = []
+        else:
+            warmup, total = resolve_scheduler_steps(cfg, len(self.train_loader))
+            self.schedulers = [LRSchedule(cfg.scheduler_type, cfg.lr, warmup, total, cfg.scheduler_num_cosine_cycles)]
+            if self._loading_checkpoint():
+                self.checkpointer.load_scheduler_state_dict(self.schedulers)
+        use_graph = cfg.use_cuda_graph if cfg.use_cuda_graph is not None else self.device_type == "cuda"
+        if os.environ.get("SB200_DISABLE_CUDA_GRAPH") == "1":
+            use_graph = False
+        self._graphed = None
+        if use_graph and self.device_type == "cuda":
+            capture_opt = (not self.is_distributed) or os.environ.get("SB200_GRAPH_COLLECTIVES") == "1"
+            self._graphed = _GraphedStep(self, capture_optimizer=capture_opt)
+
+    # ------------------------------------------------------------------ one step
+    def _current_lr(self) -> float:
+        return self.schedulers[0].current_lr() if self.schedulers else self.config.lr
+
+    def train_step(self, batch: dict) -> tuple[torch.Tensor, dict[str, torch.Tensor]]:
+        """One optimizer step on ``batch`` (host or device tensors).  Returns the
+        loss and metric tensors on the training device."""
+        lr = self._current_lr()
+        if self._graphed is not None:
+            loss, metrics = self._graphed.run(batch, lr)
+        else:
+            dev_batch = {k: v.to(self.device, non_blocking=True) if isinstance(v, torch.Tensor) else v for k, v in batch.items()}
+            self.timer.mark("fetch")
+            self.engine.zero_grad()
+            _, loss, metrics = self.model(**dev_batch, **(self.config.train_call_kwargs or {}))
+            self.timer.mark("fwd")
+            loss.backward()
+            self.timer.mark("bwd")
+            self.engine.step(lr)
+        for sched in self.schedulers:
+            sched.step()
+        self.timer.mark("opt")
+        return loss, metrics
+
+    # ------------------------------------------------------------------ epochs
+    def _prepare_resume_skip(self, epoch: int) -> int:
+        skip = 0
+        if epoch == getattr(self, "current_epoch", epoch):
+            skip = getattr(self, "_resume_local_step", 0)
+            self._resume_local_step = 0
+        sampler = getattr(self.train_loader, "batch_sampler", None)
+        fast = hasattr(sampler, "_generate_batches") and hasattr(sampler, "_cached_generated_batches")
+        if skip > 0 and fast:
+            remaining = sampler._generate_batches(epoch)[skip:]  # noqa: SLF001
+            sampler._cached_generated_batches = (epoch, remaining)  # noqa: SLF001
+            root_logger.info("Fast-skipping %d batches via sampler slice. epoch=%d, global_step=%d.", skip, epoch, self.global_step)
+        elif skip > 0:
+            root_logger.warning("Sampler lacks fast-skip API; resume will replay %d batches from the start of the epoch.", skip)
+        return skip
+
+    def train_epoch(self, epoch: int) -> None:
+        self.model.train()
+        sampler = getattr(self.train_loader, "batch_sampler", None)
+        if hasattr(sampler, "set_epoch"):
+            sampler.set_epoch(epoch)
+        num_steps = len(self.train_loader)
+        skip_steps = self._prepare_resume_skip(epoch)
+        cfg = self.config
+        step_interval = max(1, round(num_steps * cfg.checkpoint_freq)) if cfg.checkpoint_freq < 1 else None
+        loader = self.train_loader
+        if self.rank == 0 and os.environ.get("SB200_NO_TQDM") != "1":
+            try:
+                from tqdm import tqdm
+
+                loader = tqdm(loader, desc=f"Epoch {epoch}")
+            except ImportError:
+                pass
+        self.timer.reset(self.global_step % cfg.log_freq == 0)
+        self.timer.mark("start")
+        for rel, batch in enumerate(loader, 1):
+            local_step = rel + skip_steps
+            loss, metrics = self.train_step(batch)
+            lr_now = self._current_lr()
+            if self.timer.enabled:
+                doc = batch.get("document_ids") if isinstance(batch, dict) else None
+                num_tokens = int((doc != -1).sum().item()) if doc is not None else 0
+                profile = self.timer.profile(num_tokens)
+                if self.is_distributed and metrics:
+                    keys = list(metrics)
+                    stacked = torch.stack([metrics[k].float().reshape(()) for k in keys])
+                    dist.reduce(stacked, dst=0, op=dist.ReduceOp.SUM)
+                    values = dict(zip(keys, stacked.tolist()))
+                else:
+                    values = {k: float(v) for k, v in metrics.items()}
+                world = dist.get_world_size() if self.is_distributed else 1
+                metric_logger.info(
+                    {"train": normalize_counted_metrics(values, world), "profile": profile, "epoch": epoch,
+                     "lr": lr_now, "global_step": self.global_step},
+                    extra={"step": self.global_step},
+                )
+            self.global_step += 1
+            self.timer.reset(self.global_step % cfg.log_freq == 0)
+            self.timer.mark("start")
+            if cfg.max_steps is not None and self.global_step >= cfg.max_steps:
+                break
+            if (
+                step_interval is not None and not cfg.save_best and local_step % step_interval == 0
+                and num_steps - local_step >= step_interval * MIN_STEP_PCT
+            ):
+                self.maybe_save_checkpoint(epoch, local_step=local_step)
+
+    def _maybe_val_sync(self, batch_index: int) -> None:
+        if not self.is_distributed or _VAL_SYNC_INTERVAL <= 0:
+            return
+        if batch_index > 0 and batch_index % _VAL_SYNC_INTERVAL == 0:
+            dist.barrier()
+
+    @torch.no_grad()
+    def val_epoch(self, epoch: int) -> dict[str, float] | None:
+        if self.val_loader is None:
+            return None
+        self.model.eval()
+        sampler = getattr(self.val_loader, "batch_sampler", None)
+        if hasattr(sampler, "set_epoch"):
+            sampler.set_epoch(epoch)
+        accumulated: dict[str, torch.Tensor] = {}
+        num_batches = len(self.val_loader)
+        for i, batch in enumerate(self.val_loader):
+            self._maybe_val_sync(i)
+            dev_batch = {k: v.to(self.device, non_blocking=True) if isinstance(v, torch.Tensor) else v for k, v in batch.items()}
+            _, _loss, metrics = self.model(**dev_batch, **(self.config.val_call_kwargs or {}))
+            for k, v in metrics.items():
+                accumulated[k] = v.float() if k not in accumulated else accumulated[k] + v.float()
+        val_metrics: dict[str, float] = {}
+        if accumulated:
+            stacked = torch.stack([v.reshape(()) for v in accumulated.values()])
+            if self.is_distributed:
+                dist.all_reduce(stacked, op=dist.ReduceOp.SUM)
+            val_metrics = dict(zip(accumulated, stacked.tolist(), strict=True))
+        world = dist.get_world_size() if self.is_distributed else 1
+        val_metrics = {k: v / max(1, num_batches) for k, v in val_metrics.items()}
+        val_metrics = {f"{k}_epoch": v for k, v in normalize_counted_metrics(val_metrics, world).items()}
+        metric_logger.info({"val": val_metrics, "epoch": epoch}, extra={"step": self.global_step})
+        return val_metrics
+
+    # ------------------------------------------------------------------ checkpoints
+    def maybe_save_checkpoint(self, epoch, local_step: int = 0) -> None:
+        cfg = self.config
+        if epoch != "interrupted" and (
+            cfg.save_best
+            or (cfg.checkpoint_freq >= 1 and isinstance(epoch, int) and epoch != 0 and (epoch + 1) % cfg.checkpoint_freq != 0)
+        ):
+            return
+        root_logger.info("Saving checkpoint to %s", self.checkpointer.path / str(epoch))
+        self.checkpointer.save_checkpoint(self.model, self.engine, epoch)
+        if self.schedulers:
+            self.checkpointer.save_scheduler_state_dict(self.schedulers, epoch)
+        if isinstance(epoch, int):
+            self._save_training_state(epoch, local_step)
+            if not self.is_distributed or dist.get_rank() == 0:
+                root = self.checkpointer.path
+                for old in root.glob(f"epoch{epoch}_*"):
+                    if old.is_symlink():
+                        old.unlink()
+                suffix = f"step{local_step}" if local_step > 0 else "end"
+                (root / f"epoch{epoch}_{suffix}").symlink_to(Path(str(epoch)))
+        root_logger.info("Checkpoint saved to %s", self.checkpointer.path / str(epoch))
+
+    def maybe_update_best(self, epoch: int, val_metrics: dict | None) -> None:
+        if val_metrics is None or "loss_epoch" not in val_metrics:
+            return
+        if val_metrics["loss_epoch"] >= self.best_val_loss:
+            return
+        cfg = self.config
+        if cfg.save_best:
+            self.checkpointer.save_checkpoint(self.model, self.engine, epoch)
+            if self.schedulers:
+                self.checkpointer.save_scheduler_state_dict(self.schedulers, epoch)
+        elif cfg.checkpoint_freq >= 1 and not (epoch == 0 or (epoch + 1) % int(cfg.checkpoint_freq) == 0):
+            return
+        self.best_val_loss = val_metrics["loss_epoch"]
+        self.checkpointer.save_val_metrics(epoch, val_metrics)
+        self.checkpointer.update_best_symlink(epoch)
+        root_logger.info("Updated checkpoint_best -> %s (loss_epoch=%.6f)", epoch, self.best_val_loss)
+        if cfg.save_best:
+            self.checkpointer.cleanup_keep_only_best(best_epoch=epoch)
+
+    def _barrier(self) -> None:
+        if self.is_distributed:
+            dist.barrier()
+
+    @with_graceful_shutdown()
+    def run_training(self) -> None:
+        n_epochs = self.config.num_epochs
+        for epoch in range(self.current_epoch, n_epochs):
+            root_logger.info("Training epoch %d/%d started", epoch + 1, n_epochs)
+            self.train_epoch(epoch)
+            root_logger.info("Training epoch %d/%d completed", epoch + 1, n_epochs)
+            self._barrier()
+            self.maybe_save_checkpoint(epoch)
+            self._barrier()
+            val_metrics = None
+            if self.val_loader is None:
+                root_logger.warning("No val loader, skipping validation epoch")
+            else:
+                val_metrics = self.val_epoch(epoch)
+            self._barrier()
+            self.maybe_update_best(epoch, val_metrics)
+            self._barrier()
+            if self.config.max_steps is not None and self.global_step >= self.config.max_steps:
+                break

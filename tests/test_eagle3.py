@@ -1,0 +1,140 @@
+import os
+import sys
+
+import pytest
+import torch
+
+import speculators_b200 as sb
+from speculators_b200.models.eagle3.attention import causal_document_interval, dense_ttt_mask, ttt_attn_spec
+from speculators_b200.models.eagle3.data import shift_batch
+from speculators_b200.ops import masked_attention_reference
+
+from conftest import ROOT, TINY_VERIFIER, make_tiny_batch, make_tiny_eagle3
+
+
+@pytest.mark.parametrize("window", [None, 5])
+@pytest.mark.parametrize("step", [0, 1, 3])
+def test_ttt_spec_equals_mask_definition(step, window):
+    doc = torch.tensor([0] * 7 + [1] * 9 + [2] * 3 + [-1] * 4)
+    spec = ttt_attn_spec(doc, step, sliding_window=window)
+    T = doc.numel()
+    assert torch.equal(spec.dense(T, step * T), dense_ttt_mask(doc, step, window))
+
+
+def test_interval_padding_and_restart():
+    doc = torch.tensor([3, 3, 3, 8, 8, -1, -1])
+    lo, hi = causal_document_interval(doc)
+    assert lo.tolist() == [0, 0, 0, 3, 3, 5, 6] and hi.tolist() == [1, 2, 3, 4, 5, 6, 7]
+
+
+def test_attention_oracle_with_extras_matches_dense_softmax():
+    torch.manual_seed(0)
+    T, nh, nkv, hd, s = 12, 4, 2, 8, 2
+    doc = torch.tensor([0] * 5 + [1] * 5 + [-1] * 2)
+    q = torch.randn(T, nh, hd)
+    ks = [torch.randn(T, nkv, hd) for _ in range(s + 1)]
+    vs = [torch.randn(T, nkv, hd) for _ in range(s + 1)]
+    out = masked_attention_reference(q, ks[0], vs[0], ttt_attn_spec(doc, s), torch.cat(ks[1:]), torch.cat(vs[1:]))
+    mask = dense_ttt_mask(doc, s)
+    K = torch.cat(ks).repeat_interleave(2, 1)
+    V = torch.cat(vs).repeat_interleave(2, 1)
+    sc = torch.einsum("qhd,khd->hqk", q, K) * hd**-0.5
+    ref = torch.einsum("hqk,khd->qhd", sc.masked_fill(~mask[None], float("-inf")).softmax(-1), V)
+    assert torch.allclose(out, ref, atol=1e-5)
+
+
+def test_shift_batch():
+    b = dict(input_ids=torch.arange(5), hidden_states=torch.arange(10.0).reshape(5, 2),
+             verifier_last_hidden_states=torch.arange(5.0).reshape(5, 1), loss_mask=torch.ones(5), lengths=torch.tensor([5]),
+             position_ids=torch.arange(5))
+    s = shift_batch(b)
+    assert s["input_ids"].tolist() == [1, 2, 3, 4] and s["hidden_states"][:, 0].tolist() == [0, 2, 4, 6]
+    assert s["position_ids"].tolist() == [1, 2, 3, 4] and s["lengths"].item() == 4
+    assert shift_batch(dict(b, lengths=torch.tensor([0])))["lengths"].item() == 0
+
+
+def test_forward_backward_metrics_and_frozen_params(tiny_verifier_dir, tiny_vocab_maps):
+    model = make_tiny_eagle3(tiny_verifier_dir, tiny_vocab_maps, num_layers=2)
+    kwargs, _ = sb.Eagle3DraftModel.get_trainer_kwargs(loss_fn="kl_div", ttt_steps=3, ttt_step_loss_decay=0.8)
+    toks, loss, metrics = model(**make_tiny_batch(), **kwargs)
+    assert len(toks) == 3 and toks[0].shape == (1, 40)
+    for s in range(3):
+        for key in ("loss", "full_acc", "cond_acc"):
+            assert f"{key}_{s}_sum" in metrics and f"{key}_{s}_total" in metrics
+    assert torch.isclose(metrics["loss_sum"], loss.detach())
+    loss.backward()
+    trainable = {n for n, p in model.named_parameters() if p.requires_grad}
+    assert not {"embed_tokens.weight", "lm_head.weight", "verifier_lm_head.weight", "verifier_norm.weight"} & trainable
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for n, p in model.named_parameters() if p.requires_grad)
+    assert not torch.isnan(model.lm_head.weight).any()  # verifier weights were loaded over the NaN sentinels
+
+
+def test_save_load_round_trip_and_key_layout(tiny_verifier_dir, tiny_vocab_maps, tmp_path):
+    from safetensors.torch import load_file
+
+    model = make_tiny_eagle3(tiny_verifier_dir, tiny_vocab_maps)
+    model.save_pretrained(tmp_path)
+    keys = set(load_file(str(tmp_path / "model.safetensors")))
+    assert {"fc.weight", "layers.0.self_attn.q_proj.weight", "layers.0.self_attn.k_proj.weight", "layers.0.mlp.gate_proj.weight",
+            "layers.0.mlp.up_proj.weight", "layers.0.hidden_norm.weight", "norm.weight", "d2t", "t2d", "embed_tokens.weight",
+            "lm_head.weight", "input_norm.weight"} <= keys
+    assert not {"verifier_lm_head.weight", "verifier_norm.weight"} & keys
+    assert not any("qkv_proj" in k or "gate_up_proj" in k for k in keys)
+    loaded = sb.SpeculatorModel.from_pretrained(str(tmp_path))
+    assert isinstance(loaded, sb.Eagle3DraftModel)
+    kwargs, _ = sb.Eagle3DraftModel.get_trainer_kwargs(loss_fn="ce", ttt_steps=2, ttt_step_loss_decay=1.0)
+    batch = make_tiny_batch()
+    assert torch.allclose(model(**batch, **kwargs)[1], loaded(**batch, **kwargs)[1])
+
+
+def test_vocab_mapping_validation(tiny_verifier_dir, tiny_vocab_maps):
+    model = make_tiny_eagle3(tiny_verifier_dir, tiny_vocab_maps)
+    t2d, d2t = tiny_vocab_maps
+    with pytest.raises(ValueError):
+        model.load_vocab_mappings(t2d, None)
+    with pytest.raises(ValueError):
+        model.load_vocab_mappings(t2d[:-1], d2t)
+    bad = t2d.clone(); bad[:] = False
+    with pytest.raises(ValueError):
+        model.load_vocab_mappings(bad, d2t)
+
+
+REF = os.path.join(ROOT, "baseline", "_ref")
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "speculators")), reason="reference not installed under baseline/_ref")
+@pytest.mark.parametrize("loss_fn", ["kl_div", '{"ce": 0.3, "jsd": 0.7}'])
+def test_numerical_parity_with_reference_sdpa_path(tiny_verifier_dir, tiny_vocab_maps, loss_fn):
+    """Same weights, same batch: loss, every metric and the gradients agree with
+    the reference implementation (its sdpa attention path, eager losses)."""
+    sys.path.insert(0, REF)
+    try:
+        from transformers import LlamaConfig
+
+        from speculators.models.eagle3.core import Eagle3DraftModel as RefModel
+    except Exception as err:  # noqa: BLE001
+        pytest.skip(f"reference import failed: {err}")
+    finally:
+        sys.path.remove(REF)
+    t2d, d2t = tiny_vocab_maps
+    mine = make_tiny_eagle3(tiny_verifier_dir, tiny_vocab_maps, num_layers=2)
+    rc = LlamaConfig(**{k: v for k, v in TINY_VERIFIER.items() if k not in ("model_type", "architectures")})
+    rc.num_hidden_layers = 2
+    ref = RefModel.from_training_args(
+        rc, t2d=t2d, d2t=d2t, draft_attn_impl="sdpa", draft_vocab_size=32, norm_before_residual=True, ttt_steps=3,
+        verifier_name_or_path=tiny_verifier_dir, target_layer_ids=[1, 2, 3], norm_before_fc=True, norm_output=True,
+    )
+    assert not ref.load_state_dict(mine.state_dict(), strict=False).unexpected_keys
+    batch = make_tiny_batch()
+    mk, _ = sb.Eagle3DraftModel.get_trainer_kwargs(loss_fn=loss_fn, ttt_steps=3, ttt_step_loss_decay=0.8)
+    rk, _ = RefModel.get_trainer_kwargs(loss_fn=loss_fn, loss_implementation="eager", ttt_steps=3, ttt_step_loss_decay=0.8)
+    _, l1, m1 = mine(**batch, **mk)
+    _, l2, m2 = ref(**{k: v.clone() for k, v in batch.items()}, **rk)
+    assert torch.allclose(l1, l2, atol=1e-5)
+    assert set(m1) == set(m2)
+    for k in m1:
+        assert abs(float(m1[k]) - float(m2[k])) < 1e-4, k
+    l1.backward(); l2.backward()
+    assert torch.allclose(mine.fc.weight.grad, ref.fc.weight.grad, atol=1e-5)
+    nq = ref.layers[0].self_attn.q_proj.weight.shape[0]
+    assert torch.allclose(mine.layers[0].self_attn.qkv_proj.weight.grad[:nq], ref.layers[0].self_attn.q_proj.weight.grad, atol=1e-6)
