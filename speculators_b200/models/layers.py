@@ -188,6 +188,14 @@ class RotaryTable(nn.Module):
         self.sin = ang.sin().float().to(device).contiguous()
         self.max_positions = n
 
+    def _apply(self, fn, recurse=True):  # noqa: ANN001
+        """Keep the tables in fp32 whatever dtype the owning model is cast to."""
+        super()._apply(fn, recurse)
+        if self.cos.dtype != torch.float32:
+            self.cos, self.sin = self.cos.float(), self.sin.float()
+            self._build(self.max_positions)
+        return self
+
     def ensure(self, max_pos: int) -> None:
         """Grow the tables (host side, outside any captured region) to cover ``max_pos``."""
         if max_pos >= self.max_positions:

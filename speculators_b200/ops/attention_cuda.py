@@ -1,7 +1,54 @@
-"""CUDA entry of masked attention (temporary dense path until the kernel lands)."""
+"""CUDA path of ``masked_attention``: autograd wrapper around the sm_100a kernels
+in ``csrc/attention.cu`` (head dims 64 and 128).  Other head dims use the dense
+formulation."""
 
-from speculators_b200.ops.attention import masked_attention_reference
+from __future__ import annotations
+
+import torch
+
+from speculators_b200.ops import _ext
+from speculators_b200.ops.attention import AttnSpec, masked_attention_reference
+
+_SUPPORTED_HEAD_DIMS = (64, 128)
 
 
-def masked_attention_cuda(q, k_ctx, v_ctx, spec, k_ext=None, v_ext=None, scale=None):
-    return masked_attention_reference(q, k_ctx, v_ctx, spec, k_ext, v_ext, scale)
+def _rows_ok(t: torch.Tensor) -> torch.Tensor:
+    """[T, heads, hd] with contiguous heads and 16-byte aligned rows (views into a
+    fused projection buffer qualify as they are)."""
+    hd = t.shape[2]
+    if t.stride(2) == 1 and t.stride(1) == hd and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0:
+        return t
+    return t.contiguous()
+
+
+class _MaskedAttentionFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, lo, hi, k_ext, v_ext, ext_idx, scale):
+        q, k, v = _rows_ok(q), _rows_ok(k), _rows_ok(v)
+        if ext_idx is not None:
+            k_ext, v_ext = _rows_ok(k_ext), _rows_ok(v_ext)
+        out, lse2 = _ext.lib().attn_fwd(q, k, v, lo, hi, k_ext, v_ext, ext_idx, scale)
+        ctx.save_for_backward(q, k, v, out, lse2, lo, hi, k_ext, v_ext, ext_idx)
+        ctx.scale = scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse2, lo, hi, k_ext, v_ext, ext_idx = ctx.saved_tensors
+        dq, dk, dv, dke, dve = _ext.lib().attn_bwd(_rows_ok(dout), q, k, v, out, lse2, lo, hi, k_ext, v_ext, ext_idx, ctx.scale)
+        if ext_idx is not None:
+            return dq, dk, dv, None, None, dke.to(q.dtype), dve.to(q.dtype), None, None
+        return dq, dk, dv, None, None, None, None, None, None
+
+
+def masked_attention_cuda(q, k_ctx, v_ctx, spec: AttnSpec, k_ext=None, v_ext=None, scale=None):
+    hd = q.shape[-1]
+    scale = hd**-0.5 if scale is None else float(scale)
+    if hd not in _SUPPORTED_HEAD_DIMS or q.dtype != torch.bfloat16:
+        return masked_attention_reference(q, k_ctx, v_ctx, spec, k_ext, v_ext, scale)
+    ext_idx = spec.extra_idx
+    if ext_idx is None or k_ext is None or ext_idx.shape[1] == 0:
+        ext_idx = k_ext = v_ext = None
+    else:
+        ext_idx = ext_idx.to(torch.int32).contiguous()
+    return _MaskedAttentionFn.apply(q, k_ctx, v_ctx, spec.lo, spec.hi, k_ext, v_ext, ext_idx, scale)

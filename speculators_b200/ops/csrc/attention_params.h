@@ -1,0 +1,43 @@
+// Parameter block of the masked-attention kernels (shared by the launchers and the
+// torch bindings).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace sb200 {
+
+struct AttnParams {
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* k;
+  const __nv_bfloat16* v;
+  const __nv_bfloat16* ke;
+  const __nv_bfloat16* ve;
+  const int* lo;
+  const int* hi;
+  const int* ext_idx;
+  __nv_bfloat16* out;
+  float* lse2;  // [nh, Tq] log2-domain logsumexp of the scaled scores
+  int Tq, Tc, Te, E, nh, nkv;
+  int64_t q_rs, k_rs, v_rs, ke_rs, ve_rs, o_rs;
+  float scale;
+  // backward only
+  const __nv_bfloat16* dout;
+  int64_t do_rs;
+  float* delta;          // [nh, Tq]
+  __nv_bfloat16* dq;     // [Tq, nh, HD] row stride dq_rs
+  int64_t dq_rs;
+  float* dke;            // [Te, nkv, HD] fp32 (atomics)
+  float* dve;
+  __nv_bfloat16* dk;     // [Tc, nkv, HD] contiguous
+  __nv_bfloat16* dv;
+  const int* tile_qmin;  // [ceil(Tc / kBN)] first / one-past-last query row that can see the kv tile
+  const int* tile_qmax;
+};
+
+int launch_attn_fwd(const AttnParams& p, int hd, cudaStream_t stream);
+// tile_qmin must hold INT_MAX and tile_qmax 0 in every entry (one per 64-key tile).
+int launch_attn_bwd(const AttnParams& p, int hd, int* tile_qmin, int* tile_qmax, cudaStream_t stream);
+constexpr int kAttnKeyTile = 64;
+
+}  // namespace sb200

@@ -3,6 +3,8 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/library.h>
+
+#include "attention_params.h"
 #include <ATen/ATen.h>
 
 namespace sb200 {
@@ -212,6 +214,115 @@ void adamw(Tensor master, Tensor m, Tensor v, const Tensor& grad, c10::optional<
 
 int64_t launch_count() { return sb200::launch_count(); }
 
+// ---- masked attention ------------------------------------------------------------------
+void check_heads(const Tensor& t, const char* name, int64_t hd) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.dim() == 3, name, ": bf16 CUDA [T, heads, hd] expected");
+  TORCH_CHECK(t.size(2) == hd && t.stride(2) == 1 && t.stride(1) == hd, name, ": heads must be contiguous");
+  TORCH_CHECK(t.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0, name, ": rows must be 16-byte aligned");
+}
+
+sb200::AttnParams make_params(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& lo, const Tensor& hi,
+                              const c10::optional<Tensor>& ke, const c10::optional<Tensor>& ve,
+                              const c10::optional<Tensor>& ext_idx, double scale) {
+  const int64_t hd = q.size(2);
+  check_heads(q, "q", hd);
+  check_heads(k, "k", hd);
+  check_heads(v, "v", hd);
+  TORCH_CHECK(hd == 64 || hd == 128, "attention: head_dim must be 64 or 128");
+  TORCH_CHECK(k.size(0) == v.size(0) && k.size(1) == v.size(1) && q.size(1) % k.size(1) == 0);
+  TORCH_CHECK(lo.scalar_type() == at::kInt && hi.scalar_type() == at::kInt && lo.is_contiguous() && hi.is_contiguous() &&
+              lo.numel() == q.size(0) && hi.numel() == q.size(0), "lo/hi must be int32[Tq]");
+  sb200::AttnParams p{};
+  p.q = (const __nv_bfloat16*)q.data_ptr();
+  p.k = (const __nv_bfloat16*)k.data_ptr();
+  p.v = (const __nv_bfloat16*)v.data_ptr();
+  p.lo = lo.data_ptr<int>();
+  p.hi = hi.data_ptr<int>();
+  p.Tq = (int)q.size(0);
+  p.Tc = (int)k.size(0);
+  p.nh = (int)q.size(1);
+  p.nkv = (int)k.size(1);
+  p.q_rs = q.stride(0);
+  p.k_rs = k.stride(0);
+  p.v_rs = v.stride(0);
+  p.scale = (float)scale;
+  if (ext_idx.has_value() && ext_idx->numel() > 0) {
+    TORCH_CHECK(ke.has_value() && ve.has_value(), "extra keys need k_ext and v_ext");
+    check_heads(*ke, "k_ext", hd);
+    check_heads(*ve, "v_ext", hd);
+    TORCH_CHECK(ke->size(0) == ve->size(0) && ke->size(1) == p.nkv && ve->size(1) == p.nkv);
+    TORCH_CHECK(ext_idx->scalar_type() == at::kInt && ext_idx->is_contiguous() && ext_idx->dim() == 2 && ext_idx->size(0) == p.Tq);
+    p.ke = (const __nv_bfloat16*)ke->data_ptr();
+    p.ve = (const __nv_bfloat16*)ve->data_ptr();
+    p.ext_idx = ext_idx->data_ptr<int>();
+    p.Te = (int)ke->size(0);
+    p.E = (int)ext_idx->size(1);
+    p.ke_rs = ke->stride(0);
+    p.ve_rs = ve->stride(0);
+  }
+  return p;
+}
+
+std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& lo, const Tensor& hi,
+                                    const c10::optional<Tensor>& ke, const c10::optional<Tensor>& ve,
+                                    const c10::optional<Tensor>& ext_idx, double scale) {
+  sb200::AttnParams p = make_params(q, k, v, lo, hi, ke, ve, ext_idx, scale);
+  c10::cuda::CUDAGuard guard(q.device());
+  Tensor out = at::empty({q.size(0), q.size(1), q.size(2)}, q.options());
+  Tensor lse2 = at::empty({q.size(1), q.size(0)}, q.options().dtype(at::kFloat));
+  p.out = (__nv_bfloat16*)out.data_ptr();
+  p.o_rs = out.stride(0);
+  p.lse2 = lse2.data_ptr<float>();
+  const int rc = sb200::launch_attn_fwd(p, (int)q.size(2), cur_stream());
+  TORCH_CHECK(rc == 0, "attn_fwd launch failed (", rc, ")");
+  return {out, lse2};
+}
+
+std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> attn_bwd(
+    const Tensor& dout, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out, const Tensor& lse2,
+    const Tensor& lo, const Tensor& hi, const c10::optional<Tensor>& ke, const c10::optional<Tensor>& ve,
+    const c10::optional<Tensor>& ext_idx, double scale) {
+  sb200::AttnParams p = make_params(q, k, v, lo, hi, ke, ve, ext_idx, scale);
+  const int64_t hd = q.size(2);
+  check_heads(dout, "dout", hd);
+  check_heads(out, "out", hd);
+  TORCH_CHECK(dout.size(0) == q.size(0) && dout.size(1) == q.size(1) && out.sizes() == dout.sizes());
+  TORCH_CHECK(lse2.scalar_type() == at::kFloat && lse2.is_contiguous() && lse2.numel() == q.size(0) * q.size(1));
+  c10::cuda::CUDAGuard guard(q.device());
+  Tensor dq = at::empty({q.size(0), q.size(1), hd}, q.options());
+  Tensor dk = at::empty({k.size(0), k.size(1), hd}, q.options());
+  Tensor dv = at::empty({k.size(0), k.size(1), hd}, q.options());
+  Tensor delta = at::empty({q.size(1), q.size(0)}, lse2.options());
+  Tensor dke, dve;
+  if (p.E > 0) {
+    dke = at::zeros({p.Te, p.nkv, hd}, lse2.options());
+    dve = at::zeros({p.Te, p.nkv, hd}, lse2.options());
+    p.dke = dke.data_ptr<float>();
+    p.dve = dve.data_ptr<float>();
+  } else {
+    dke = at::empty({0}, lse2.options());
+    dve = at::empty({0}, lse2.options());
+  }
+  const int n_tiles = (p.Tc + sb200::kAttnKeyTile - 1) / sb200::kAttnKeyTile;
+  Tensor qmin = at::full({n_tiles}, 0x7fffffff, lo.options());
+  Tensor qmax = at::zeros({n_tiles}, lo.options());
+  p.out = (__nv_bfloat16*)out.data_ptr();
+  p.o_rs = out.stride(0);
+  p.lse2 = lse2.data_ptr<float>();
+  p.dout = (const __nv_bfloat16*)dout.data_ptr();
+  p.do_rs = dout.stride(0);
+  p.delta = delta.data_ptr<float>();
+  p.dq = (__nv_bfloat16*)dq.data_ptr();
+  p.dq_rs = dq.stride(0);
+  p.dk = (__nv_bfloat16*)dk.data_ptr();
+  p.dv = (__nv_bfloat16*)dv.data_ptr();
+  p.tile_qmin = qmin.data_ptr<int>();
+  p.tile_qmax = qmax.data_ptr<int>();
+  const int rc = sb200::launch_attn_bwd(p, (int)hd, qmin.data_ptr<int>(), qmax.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(rc == 0, "attn_bwd launch failed (", rc, ")");
+  return {dq, dk, dv, dke, dve};
+}
+
 }  // namespace
 
 TORCH_LIBRARY(sb200, m) {
@@ -225,4 +336,6 @@ TORCH_LIBRARY(sb200, m) {
   m.def("sumsq", &sumsq);
   m.def("adamw", &adamw);
   m.def("launch_count", &launch_count);
+  m.def("attn_fwd", &attn_fwd);
+  m.def("attn_bwd", &attn_bwd);
 }

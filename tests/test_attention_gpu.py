@@ -1,0 +1,85 @@
+"""Masked-attention kernels (forward + backward) against the dense fp32 oracle."""
+
+import pytest
+import torch
+
+from speculators_b200.models.eagle3.attention import ttt_attn_spec
+from speculators_b200.ops import AttnSpec, masked_attention, masked_attention_reference
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _docs(T, pattern):
+    if pattern == "single":
+        return torch.zeros(T, dtype=torch.long)
+    if pattern == "multi_pad":
+        a, b = T // 3, T // 2
+        return torch.cat([torch.zeros(a), torch.ones(b), torch.full((T - a - b - 5,), 2), torch.full((5,), -1)]).long()
+    raise ValueError(pattern)
+
+
+def _run(T, nh, nkv, hd, step, window, pattern, fused_buffer=False, seed=0):
+    torch.manual_seed(seed)
+    doc = _docs(T, pattern).to(DEV)
+    spec = ttt_attn_spec(doc, step, sliding_window=window)
+    if fused_buffer:
+        width = (nh + 2 * nkv) * hd
+        qkv = torch.randn(T, width, device=DEV).to(torch.bfloat16)
+        q = qkv[:, : nh * hd].view(T, nh, hd)
+        k = qkv[:, nh * hd: (nh + nkv) * hd].view(T, nkv, hd)
+        v = qkv[:, (nh + nkv) * hd:].view(T, nkv, hd)
+    else:
+        q = torch.randn(T, nh, hd, device=DEV).to(torch.bfloat16)
+        k = torch.randn(T, nkv, hd, device=DEV).to(torch.bfloat16)
+        v = torch.randn(T, nkv, hd, device=DEV).to(torch.bfloat16)
+    ke = ve = None
+    if step > 0:
+        ke = torch.randn(step * T, nkv, hd, device=DEV).to(torch.bfloat16)
+        ve = torch.randn(step * T, nkv, hd, device=DEV).to(torch.bfloat16)
+    leaves = [t.detach().clone().requires_grad_() for t in (q, k, v) + ((ke, ve) if step else ())]
+    out = masked_attention(leaves[0], leaves[1], leaves[2], spec, *(leaves[3:] if step else (None, None)))
+    dout = torch.randn_like(out)
+    out.backward(dout)
+    ref_leaves = [t.detach().float().requires_grad_() for t in (q, k, v) + ((ke, ve) if step else ())]
+    ref = masked_attention_reference(ref_leaves[0], ref_leaves[1], ref_leaves[2], spec, *(ref_leaves[3:] if step else (None, None)))
+    ref.backward(dout.float())
+    torch.testing.assert_close(out.float(), ref, atol=2e-2, rtol=2e-2)
+    names = ["dq", "dk", "dv", "dk_ext", "dv_ext"]
+    for name, a, b in zip(names, leaves, ref_leaves):
+        tol = 3e-2 * float(b.grad.abs().max()) + 2e-2
+        assert float((a.grad.float() - b.grad).abs().max()) < tol, (name, float((a.grad.float() - b.grad).abs().max()), tol)
+
+
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("T", [64, 200, 257])
+def test_causal_single_document(T, hd):
+    _run(T, 4, 2, hd, step=0, window=None, pattern="single")
+
+
+@pytest.mark.parametrize("step", [1, 2])
+@pytest.mark.parametrize("window", [None, 48])
+def test_ttt_steps_multi_document_padding(step, window):
+    _run(330, 8, 2, 128, step=step, window=window, pattern="multi_pad")
+
+
+def test_views_into_fused_projection_buffer():
+    _run(192, 4, 1, 64, step=1, window=None, pattern="multi_pad", fused_buffer=True)
+
+
+def test_no_gqa_and_sliding_window():
+    _run(300, 2, 2, 128, step=0, window=17, pattern="single")
+
+
+def test_rows_without_any_key_return_zero():
+    T, nh, hd = 70, 2, 64
+    q = torch.randn(T, nh, hd, device=DEV).to(torch.bfloat16).requires_grad_()
+    k = torch.randn(T, nh, hd, device=DEV).to(torch.bfloat16).requires_grad_()
+    v = torch.randn(T, nh, hd, device=DEV).to(torch.bfloat16).requires_grad_()
+    lo = torch.zeros(T, dtype=torch.int32, device=DEV)
+    hi = torch.arange(1, T + 1, dtype=torch.int32, device=DEV)
+    hi[10:20] = 0  # empty interval
+    out = masked_attention(q, k, v, AttnSpec(lo=lo, hi=hi))
+    assert (out[10:20] == 0).all() and torch.isfinite(out).all()
+    out.sum().backward()
+    assert torch.isfinite(q.grad).all() and (q.grad[10:20] == 0).all()
