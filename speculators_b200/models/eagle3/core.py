@@ -59,13 +59,13 @@ class Eagle3FirstLayer(nn.Module):
         self.hidden_norm = RMSNorm(H, config.rms_norm_eps)
         self.post_attention_layernorm = RMSNorm(H, config.rms_norm_eps)
 
-    def forward(self, embeds, hidden, positions, rotary, spec, past=None):
+    def forward(self, embeds, hidden, positions, rotary, spec, past=None, ctx_len=None):
         H = self.hidden_size
         x = ops.eagle3_input_concat(
             embeds, hidden, self.input_layernorm.weight, self.hidden_norm.weight, self.hidden_norm.variance_epsilon
         )
         residual = x[:, H:] if self.norm_before_residual else hidden
-        h = residual + self.self_attn(x, positions, rotary, spec, past)
+        h = residual + self.self_attn(x, positions, rotary, spec, past, ctx_len)
         return h + self.mlp(self.post_attention_layernorm(h))
 
 
@@ -76,6 +76,8 @@ class Eagle3DraftModel(DraftVocabMixin, SpeculatorModel):
         "embed_tokens.weight", "verifier_norm.weight", "verifier_lm_head.weight", "d2t", "t2d", "input_norm.weight",
     ]
     _keys_to_ignore_on_save: ClassVar[list[str]] = ["verifier_lm_head.weight", "verifier_norm.weight"]
+    # forward has fixed shapes and no host synchronisation: a step can be captured in a CUDA graph
+    cuda_graph_safe: ClassVar[bool] = True
 
     def __init__(self, config: Eagle3SpeculatorConfig):
         SpeculatorModel.__init__(self, config)

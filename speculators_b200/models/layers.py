@@ -245,14 +245,19 @@ class Attention(nn.Module):
             q, k, v = qkv[:, :nq], qkv[:, nq : nq + nk], qkv[:, nq + nk :]
         return q.view(T, self.nh, self.hd), k.view(T, self.nkv, self.hd), v.view(T, self.nkv, self.hd)
 
-    def forward(self, x, positions, rotary, spec: AttnSpec, past: list | None = None) -> torch.Tensor:
+    def forward(self, x, positions, rotary, spec: AttnSpec, past: list | None = None, ctx_len: int | None = None) -> torch.Tensor:
         """``past`` (EAGLE-3 TTT): list of (k, v) of earlier passes over the same
         positions.  Entry 0 is the context the interval part of ``spec`` indexes;
         later entries and this pass's own keys are reachable through
-        ``spec.extra_idx`` (row ``(j-1)*T + i`` = key ``i`` of pass ``j``)."""
+        ``spec.extra_idx`` (row ``(j-1)*T + i`` = key ``i`` of pass ``j``).
+
+        ``ctx_len`` (P-EAGLE): the first ``ctx_len`` rows of this pass are the
+        interval-addressed context, the remaining rows are the extra keys."""
         T = x.shape[0]
         q, k, v = self.project_qkv(x, positions, rotary)
-        if past is None:
+        if ctx_len is not None and ctx_len < T:
+            out = ops.masked_attention(q, k[:ctx_len], v[:ctx_len], spec, k[ctx_len:], v[ctx_len:], scale=self.scaling)
+        elif past is None:
             out = ops.masked_attention(q, k, v, spec, scale=self.scaling)
         else:
             past.append((k, v))
@@ -289,6 +294,6 @@ class DecoderLayer(nn.Module):
         self.input_layernorm = RMSNorm(config.hidden_size, config.rms_norm_eps)
         self.post_attention_layernorm = RMSNorm(config.hidden_size, config.rms_norm_eps)
 
-    def forward(self, x, positions, rotary, spec, past=None) -> torch.Tensor:
-        x = x + self.self_attn(self.input_layernorm(x), positions, rotary, spec, past)
+    def forward(self, x, positions, rotary, spec, past=None, ctx_len=None) -> torch.Tensor:
+        x = x + self.self_attn(self.input_layernorm(x), positions, rotary, spec, past, ctx_len)
         return x + self.mlp(self.post_attention_layernorm(x))

@@ -35,6 +35,7 @@ __all__ = [
     "rope_",
     "sum_of_squares",
     "swiglu",
+    "token_cross_entropy",
 ]
 
 LOSS_OPS = {"kl_div": 0, "rkl": 1, "jsd": 2, "ce": 3, "tv": 4}
@@ -285,6 +286,33 @@ def fused_row_loss(op: str, logits, targets, shift: int = 0, rows: int | None = 
         am_d = torch.where(act, am_d, torch.full_like(am_d, -1))
         am_t = torch.where(act, am_t, torch.full_like(am_t, -2))
     return loss, am_d, am_t
+
+
+class _TokenCEFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, labels, keep):
+        loss, stats = native().ce_label_fwd(logits, labels, keep)
+        ctx.save_for_backward(logits, stats)
+        return loss
+
+    @staticmethod
+    def backward(ctx, dloss):
+        logits, stats = ctx.saved_tensors
+        # the CE backward only needs the saved label (stats[4]) and the draft statistics
+        d = native().loss_bwd(LOSS_OPS["ce"], logits, logits, dloss.contiguous().float(), stats, 0, logits.shape[0])
+        return d, None, None
+
+
+def token_cross_entropy(logits: torch.Tensor, labels: torch.Tensor, keep: torch.Tensor | None = None) -> torch.Tensor:
+    """Per-row cross-entropy of ``logits [n, V]`` against integer ``labels [n]``;
+    rows with ``keep == False`` contribute 0 (and no gradient)."""
+    if _use_native(logits):
+        if logits.stride(-1) != 1:
+            logits = logits.contiguous()
+        keep_b = keep.to(torch.bool).contiguous() if keep is not None else None
+        return _TokenCEFn.apply(logits, labels.long().contiguous(), keep_b)
+    loss = F.cross_entropy(logits.float(), labels.long(), reduction="none")
+    return loss if keep is None else torch.where(keep.bool(), loss, torch.zeros_like(loss))
 
 
 # --------------------------------------------------------------------------- optimizer

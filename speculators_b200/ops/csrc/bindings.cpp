@@ -17,8 +17,8 @@ void launch_swiglu_fwd(const void*, void*, int64_t, int, cudaStream_t);
 void launch_swiglu_bwd(const void*, const void*, void*, int64_t, int, cudaStream_t);
 void launch_rope(void*, const int64_t*, const float*, const float*, int64_t, int, int, int, int64_t,
                  int64_t, float, cudaStream_t);
-int launch_loss_fwd(int, const void*, const void*, const uint8_t*, float*, float*, int*, int*, int,
-                    int, int64_t, int64_t, int, cudaStream_t);
+int launch_loss_fwd(int, const void*, const void*, const uint8_t*, const int64_t*, float*, float*, int*,
+                    int*, int, int, int64_t, int64_t, int, cudaStream_t);
 int launch_loss_bwd(int, const void*, const void*, const float*, const float*, void*, int, int, int,
                     int64_t, int64_t, int64_t, int, cudaStream_t);
 int64_t launch_count();
@@ -153,13 +153,34 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> loss_fwd(int64_t op, const Tensor& lo
                 active->is_contiguous() && active->numel() == rows);
     act = reinterpret_cast<const uint8_t*>(active->data_ptr());
   }
-  const int rc = sb200::launch_loss_fwd((int)op, logits.data_ptr(), targets.data_ptr(), act,
+  const int rc = sb200::launch_loss_fwd((int)op, logits.data_ptr(), targets.data_ptr(), act, nullptr,
                                         loss.data_ptr<float>(), stats.data_ptr<float>(),
                                         am_d.data_ptr<int>(), am_t.data_ptr<int>(), (int)rows,
                                         (int)logits.size(1), logits.stride(0), targets.stride(0),
                                         (int)shift, cur_stream());
   TORCH_CHECK(rc == 0, "loss_fwd: unknown op ", op);
   return {loss, stats, am_d, am_t};
+}
+
+// Token cross-entropy: labels int64[rows]; rows with keep == 0 cost nothing and get loss 0.
+std::tuple<Tensor, Tensor> ce_label_fwd(const Tensor& logits, const Tensor& labels, const c10::optional<Tensor>& keep) {
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kBFloat16 && logits.dim() == 2 && logits.stride(1) == 1);
+  const int64_t rows = logits.size(0);
+  TORCH_CHECK(labels.scalar_type() == at::kLong && labels.is_contiguous() && labels.numel() == rows);
+  c10::cuda::CUDAGuard guard(logits.device());
+  auto fopt = logits.options().dtype(at::kFloat);
+  Tensor loss = at::empty({rows}, fopt);
+  Tensor stats = at::empty({5, rows}, fopt);
+  const uint8_t* act = nullptr;
+  if (keep.has_value()) {
+    TORCH_CHECK((keep->scalar_type() == at::kBool || keep->scalar_type() == at::kByte) && keep->is_contiguous() && keep->numel() == rows);
+    act = reinterpret_cast<const uint8_t*>(keep->data_ptr());
+  }
+  const int rc = sb200::launch_loss_fwd(3, logits.data_ptr(), nullptr, act, labels.data_ptr<int64_t>(), loss.data_ptr<float>(),
+                                        stats.data_ptr<float>(), nullptr, nullptr, (int)rows, (int)logits.size(1),
+                                        logits.stride(0), logits.stride(0), 0, cur_stream());
+  TORCH_CHECK(rc == 0, "ce_label_fwd failed (", rc, ")");
+  return {loss, stats};
 }
 
 Tensor loss_bwd(int64_t op, const Tensor& logits, const Tensor& targets, const Tensor& grad_out,
@@ -333,6 +354,7 @@ TORCH_LIBRARY(sb200, m) {
   m.def("rope_", &rope_);
   m.def("loss_fwd", &loss_fwd);
   m.def("loss_bwd", &loss_bwd);
+  m.def("ce_label_fwd", &ce_label_fwd);
   m.def("sumsq", &sumsq);
   m.def("adamw", &adamw);
   m.def("launch_count", &launch_count);

@@ -111,9 +111,10 @@ __device__ __forceinline__ void block_combine(RowStats& s, float* scratch, int* 
 template <int OP>
 __global__ void __launch_bounds__(kLossThreads)
 loss_fwd_kernel(const __nv_bfloat16* __restrict__ logits, const __nv_bfloat16* __restrict__ targets,
-                const uint8_t* __restrict__ active, float* __restrict__ loss,
-                float* __restrict__ stats, int* __restrict__ argmax_d, int* __restrict__ argmax_t,
-                int rows, int V, int64_t ld_logits, int64_t ld_targets, int shift) {
+                const uint8_t* __restrict__ active, const int64_t* __restrict__ labels,
+                float* __restrict__ loss, float* __restrict__ stats, int* __restrict__ argmax_d,
+                int* __restrict__ argmax_t, int rows, int V, int64_t ld_logits, int64_t ld_targets,
+                int shift) {
   __shared__ float scratch[33];
   __shared__ int iscratch[33];
   const int r = blockIdx.x;
@@ -130,7 +131,9 @@ loss_fwd_kernel(const __nv_bfloat16* __restrict__ logits, const __nv_bfloat16* _
     return;
   }
   const __nv_bfloat16* x = logits + (int64_t)r * ld_logits;
-  const __nv_bfloat16* t = targets + (int64_t)(r + shift) * ld_targets;
+  // with integer labels (token cross-entropy) there is no target row to read
+  const bool has_t = targets != nullptr;
+  const __nv_bfloat16* t = has_t ? targets + (int64_t)(r + shift) * ld_targets : x;
   const bool vec_ok = ((V & 7) == 0) && ((ld_logits & 7) == 0) && ((ld_targets & 7) == 0);
   const int nvec = vec_ok ? (V >> 3) : 0;
 
@@ -138,16 +141,25 @@ loss_fwd_kernel(const __nv_bfloat16* __restrict__ logits, const __nv_bfloat16* _
   for (int v = threadIdx.x; v < nvec; v += kLossThreads) {
     float a[8], b[8];
     unpack8(ld8(x + (v << 3)), a);
-    unpack8(ld8(t + (v << 3)), b);
     online_update(sd, a, v << 3);
-    online_update(stt, b, v << 3);
+    if (has_t) {
+      unpack8(ld8(t + (v << 3)), b);
+      online_update(stt, b, v << 3);
+    }
   }
   for (int c = (nvec << 3) + threadIdx.x; c < V; c += kLossThreads) {
     online_update_scalar(sd, __bfloat162float(x[c]), c);
-    online_update_scalar(stt, __bfloat162float(t[c]), c);
+    if (has_t) online_update_scalar(stt, __bfloat162float(t[c]), c);
   }
   block_combine(sd, scratch, iscratch);
-  block_combine(stt, scratch, iscratch);
+  if (has_t) {
+    block_combine(stt, scratch, iscratch);
+  } else {
+    stt.m = 0.f;
+    stt.z = 1.f;
+    int lab = labels ? (int)labels[r + shift] : 0;
+    stt.best_idx = lab < 0 ? 0 : (lab >= V ? V - 1 : lab);
+  }
   const float lse_d = sd.m + __logf(sd.z);
   const float lse_t = stt.m + __logf(stt.z);
 
@@ -270,14 +282,15 @@ loss_bwd_kernel(const __nv_bfloat16* __restrict__ logits, const __nv_bfloat16* _
 }
 
 int launch_loss_fwd(int op, const void* logits, const void* targets, const uint8_t* active,
-                    float* loss, float* stats, int* argmax_d, int* argmax_t, int rows, int V,
+                    const int64_t* labels, float* loss, float* stats, int* argmax_d, int* argmax_t, int rows, int V,
                     int64_t ld_logits, int64_t ld_targets, int shift, cudaStream_t stream) {
   if (rows <= 0) return 0;
+  if (targets == nullptr && (labels == nullptr || op != kOpCE)) return -3;
   count_launch(1);
 #define SB200_LF(OPV)                                                                            \
   loss_fwd_kernel<OPV><<<rows, kLossThreads, 0, stream>>>(                                        \
-      (const __nv_bfloat16*)logits, (const __nv_bfloat16*)targets, active, loss, stats, argmax_d, \
-      argmax_t, rows, V, ld_logits, ld_targets, shift)
+      (const __nv_bfloat16*)logits, (const __nv_bfloat16*)targets, active, labels, loss, stats,   \
+      argmax_d, argmax_t, rows, V, ld_logits, ld_targets, shift)
   switch (op) {
     case kOpKL: SB200_LF(kOpKL); break;
     case kOpRKL: SB200_LF(kOpRKL); break;

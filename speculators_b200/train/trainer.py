@@ -300,6 +300,8 @@ class Trainer:
             if self._loading_checkpoint():
                 self.checkpointer.load_scheduler_state_dict(self.schedulers)
         use_graph = cfg.use_cuda_graph if cfg.use_cuda_graph is not None else self.device_type == "cuda"
+        # only models whose forward has fixed shapes and no host synchronisation can be replayed
+        use_graph = use_graph and bool(getattr(type(self.model), "cuda_graph_safe", False))
         if os.environ.get("SB200_DISABLE_CUDA_GRAPH") == "1":
             use_graph = False
         self._graphed = None
