@@ -32,7 +32,7 @@ class DFlashAttention(nn.Module):
         self.q_norm = RMSNorm(self.hd, config.rms_norm_eps)
         self.k_norm = RMSNorm(self.hd, config.rms_norm_eps)
 
-    def forward(self, noise, target_hidden, noise_positions, all_positions, rotary: RotaryTable, spec: AttnSpec):
+    def forward(self, noise, target_hidden, noise_positions, all_positions, rotary: RotaryTable, spec: AttnSpec, residual=None):
         nq = noise.shape[0]
         T = target_hidden.shape[0]
         q = self.qkv_proj.forward_parts(noise, 0, 1).view(nq, self.nh, self.hd)
@@ -44,7 +44,7 @@ class DFlashAttention(nn.Module):
         q = ops.rope_(q, noise_positions, rotary.cos, rotary.sin, self.nh, self.hd, self.rot).view(nq, self.nh, self.hd)
         k = ops.rope_(k, all_positions, rotary.cos, rotary.sin, self.nkv, self.hd, self.rot).view(T + nq, self.nkv, self.hd)
         out = ops.masked_attention(q, k[:T], v[:T], spec, k[T:], v[T:], scale=self.scaling)
-        return self.o_proj(out.reshape(nq, self.nh * self.hd))
+        return self.o_proj(out.reshape(nq, self.nh * self.hd), residual=residual)
 
 
 class DFlashDecoderLayer(nn.Module):
@@ -56,5 +56,5 @@ class DFlashDecoderLayer(nn.Module):
         self.post_attention_layernorm = RMSNorm(config.hidden_size, config.rms_norm_eps)
 
     def forward(self, noise, target_hidden, noise_positions, all_positions, rotary, spec):
-        noise = noise + self.self_attn(self.input_layernorm(noise), target_hidden, noise_positions, all_positions, rotary, spec)
-        return noise + self.mlp(self.post_attention_layernorm(noise))
+        noise = self.self_attn(self.input_layernorm(noise), target_hidden, noise_positions, all_positions, rotary, spec, residual=noise)
+        return self.mlp(self.post_attention_layernorm(noise), residual=noise)

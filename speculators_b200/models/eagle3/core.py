@@ -65,8 +65,8 @@ class Eagle3FirstLayer(nn.Module):
             embeds, hidden, self.input_layernorm.weight, self.hidden_norm.weight, self.hidden_norm.variance_epsilon
         )
         residual = x[:, H:] if self.norm_before_residual else hidden
-        h = residual + self.self_attn(x, positions, rotary, spec, past, ctx_len)
-        return h + self.mlp(self.post_attention_layernorm(h))
+        h = self.self_attn(x, positions, rotary, spec, past, ctx_len, residual=residual)
+        return self.mlp(self.post_attention_layernorm(h), residual=h)
 
 
 @SpeculatorModel.register("eagle3")

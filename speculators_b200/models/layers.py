@@ -63,8 +63,8 @@ class Linear(nn.Module):
         self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
         _init_linear_(self.weight, std)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return ops.linear(x, self.weight, self.bias)
+    def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        return ops.linear(x, self.weight, self.bias, residual=residual)
 
     def extra_repr(self) -> str:
         return f"in={self.in_features}, out={self.out_features}, bias={self.bias is not None}"
@@ -116,9 +116,7 @@ class FusedLinear(nn.Module):
     def forward_parts(self, x: torch.Tensor, first: int, last: int) -> torch.Tensor:
         """Apply only parts ``first .. last-1`` (row slice of the fused weight)."""
         offs = self.offsets() + [sum(self.sizes)]
-        w = self.weight[offs[first] : offs[last]]
-        b = self.bias[offs[first] : offs[last]] if self.bias is not None else None
-        return ops.linear(x, w, b)
+        return ops.linear(x, self.weight, self.bias, rows=(offs[first], offs[last]))
 
     # the hooks see keys like "<prefix>weight"; the parent prefix (without this
     # module's own attribute name) is where the split names live.
@@ -245,7 +243,8 @@ class Attention(nn.Module):
             q, k, v = qkv[:, :nq], qkv[:, nq : nq + nk], qkv[:, nq + nk :]
         return q.view(T, self.nh, self.hd), k.view(T, self.nkv, self.hd), v.view(T, self.nkv, self.hd)
 
-    def forward(self, x, positions, rotary, spec: AttnSpec, past: list | None = None, ctx_len: int | None = None) -> torch.Tensor:
+    def forward(self, x, positions, rotary, spec: AttnSpec, past: list | None = None, ctx_len: int | None = None,
+                residual: torch.Tensor | None = None) -> torch.Tensor:
         """``past`` (EAGLE-3 TTT): list of (k, v) of earlier passes over the same
         positions.  Entry 0 is the context the interval part of ``spec`` indexes;
         later entries and this pass's own keys are reachable through
@@ -268,7 +267,7 @@ class Attention(nn.Module):
                 out = ops.masked_attention(q, k_ctx, v_ctx, spec, k_ext, v_ext, scale=self.scaling)
             else:
                 out = ops.masked_attention(q, k_ctx, v_ctx, spec, scale=self.scaling)
-        return self.o_proj(out.reshape(T, self.nh * self.hd))
+        return self.o_proj(out.reshape(T, self.nh * self.hd), residual=residual)
 
 
 class MLP(nn.Module):
@@ -280,8 +279,8 @@ class MLP(nn.Module):
         self.gate_up_proj = FusedLinear(config.hidden_size, ["gate_proj", "up_proj"], [inter, inter], bias=bool(config.mlp_bias)).attach(self, "gate_up_proj")
         self.down_proj = Linear(inter, config.hidden_size, bias=bool(config.mlp_bias))
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.down_proj(ops.swiglu(self.gate_up_proj(x)))
+    def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        return self.down_proj(ops.swiglu(self.gate_up_proj(x)), residual=residual)
 
 
 class DecoderLayer(nn.Module):
@@ -295,5 +294,5 @@ class DecoderLayer(nn.Module):
         self.post_attention_layernorm = RMSNorm(config.hidden_size, config.rms_norm_eps)
 
     def forward(self, x, positions, rotary, spec, past=None, ctx_len=None) -> torch.Tensor:
-        x = x + self.self_attn(self.input_layernorm(x), positions, rotary, spec, past, ctx_len)
-        return x + self.mlp(self.post_attention_layernorm(x))
+        x = self.self_attn(self.input_layernorm(x), positions, rotary, spec, past, ctx_len, residual=x)
+        return self.mlp(self.post_attention_layernorm(x), residual=x)

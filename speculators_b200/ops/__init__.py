@@ -51,9 +51,68 @@ def _use_native(t: torch.Tensor) -> bool:
 
 
 # --------------------------------------------------------------------------- linear
-def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
-    """``x @ weight.T (+ bias)``: a plain library GEMM (cuBLASLt through ATen)."""
-    return F.linear(x, weight, bias)
+class _LinearFn(torch.autograd.Function):
+    """``y = x @ W[rows].T (+ residual)`` with the weight gradient accumulated in place.
+
+    When the training engine has attached a flat gradient view to the weight
+    (``weight._flat_grad``), backward runs ``grad[rows].addmm_(dy.T, x)``: one GEMM
+    whose epilogue adds into the gradient buffer, instead of a GEMM into a temporary
+    followed by autograd's separate accumulation pass over the whole weight.  The
+    residual, when given, rides in the forward GEMM's epilogue (``beta = 1``).
+    """
+
+    @staticmethod
+    def forward(ctx, x, weight, residual, r0, r1):
+        w = weight if r0 is None else weight[r0:r1]
+        x2 = x.reshape(-1, x.shape[-1])
+        if residual is not None:
+            y = torch.addmm(residual.reshape(-1, w.shape[0]), x2, w.t())
+        else:
+            y = x2 @ w.t()
+        ctx.save_for_backward(x2, weight)
+        ctx.rows = (r0, r1)
+        ctx.x_shape = x.shape
+        ctx.has_residual = residual is not None
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight = ctx.saved_tensors
+        r0, r1 = ctx.rows
+        w = weight if r0 is None else weight[r0:r1]
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = (dy2 @ w).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            flat = getattr(weight, "_flat_grad", None)
+            if flat is not None:
+                target = flat if r0 is None else flat[r0:r1]
+                target.addmm_(dy2.t(), x2)
+            elif r0 is None:
+                dw = dy2.t() @ x2
+            else:
+                dw = torch.zeros_like(weight)
+                dw[r0:r1] = dy2.t() @ x2
+        dres = dy if ctx.has_residual and ctx.needs_input_grad[2] else None
+        return dx, dw, dres, None, None
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None, residual: torch.Tensor | None = None,
+           rows: tuple[int, int] | None = None) -> torch.Tensor:
+    """``x @ weight[rows].T (+ bias) (+ residual)``.  The matrix products are plain
+    library GEMMs (cuBLASLt through ATen); what this wrapper adds is epilogue
+    fusion of the residual and in-place weight-gradient accumulation."""
+    if x.is_cuda and (weight.requires_grad or x.requires_grad) and torch.is_grad_enabled():
+        r0, r1 = rows if rows is not None else (None, None)
+        y = _LinearFn.apply(x, weight, residual, r0, r1)
+        if bias is not None:
+            y = y + (bias if rows is None else bias[rows[0] : rows[1]])
+        return y
+    w = weight if rows is None else weight[rows[0] : rows[1]]
+    b = bias if (bias is None or rows is None) else bias[rows[0] : rows[1]]
+    y = F.linear(x, w, b)
+    return y if residual is None else y + residual
 
 
 # --------------------------------------------------------------------------- rmsnorm

@@ -130,14 +130,24 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   }
 }
 
-// dw[c] (+)= sum_p partial[p, c]
+// dw[c] (+)= sum_p partial[p, c].  Block = 32 columns x 8 row-groups; the row-groups
+// split P and meet in shared memory, so each column is summed by 8 threads in a
+// fixed order (deterministic) and a launch has H/32 CTAs instead of H/256.
 __global__ void colsum_kernel(const float* __restrict__ partial, float* __restrict__ dw, int P,
                               int H, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= H) return;
+  __shared__ float tile[8][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
   float s = 0.f;
-  for (int p = 0; p < P; ++p) s += partial[(int64_t)p * H + c];
-  dw[c] = accumulate ? dw[c] + s : s;
+  if (c < H)
+    for (int p = threadIdx.y; p < P; p += 8) s += partial[(int64_t)p * H + c];
+  tile[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < H) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += tile[i][threadIdx.x];
+    dw[c] = accumulate ? dw[c] + t : t;
+  }
 }
 
 int rmsnorm_bwd_partial_rows(int rows) {
@@ -178,7 +188,7 @@ void launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const floa
 #undef SB200_BWD
   if (dw_partial && dw) count_launch(1);
   if (dw_partial && dw)
-    colsum_kernel<<<(H + 255) / 256, 256, 0, stream>>>(dw_partial, dw, grid, H, accumulate_dw);
+    colsum_kernel<<<(H + 31) / 32, dim3(32, 8), 0, stream>>>(dw_partial, dw, grid, H, accumulate_dw);
 }
 
 }  // namespace sb200

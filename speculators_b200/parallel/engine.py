@@ -135,6 +135,8 @@ class TrainEngine:
         for p, o in zip(self.params, self.offsets):
             p.data = self.flat_w[o : o + p.numel()].view(p.shape)
             p.grad = self.flat_g[o : o + p.numel()].view(p.shape)
+            if p.ndim == 2:  # ops.linear accumulates weight gradients straight into this view
+                p._flat_grad = p.grad
         self._init32 = init32
 
     def _init_state(self) -> None:
@@ -168,6 +170,8 @@ class TrainEngine:
         for p, o in zip(self.params, self.offsets):  # re-attach if something replaced .grad
             if p.grad is None or p.grad.data_ptr() != self.flat_g.data_ptr() + o * self.flat_g.element_size():
                 p.grad = self.flat_g[o : o + p.numel()].view(p.shape)
+                if p.ndim == 2:
+                    p._flat_grad = p.grad
 
     def prepare_hyper(self, lr: float | None = None) -> None:
         """Host side of a step: bump the step counter and stage lr / bias corrections
