@@ -63,27 +63,27 @@ class _LinearFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, weight, residual, r0, r1):
+        # x is [rows, in]; the result is a fresh tensor (never a view), so callers may
+        # rotate / normalise it in place
         w = weight if r0 is None else weight[r0:r1]
-        x2 = x.reshape(-1, x.shape[-1])
         if residual is not None:
-            y = torch.addmm(residual.reshape(-1, w.shape[0]), x2, w.t())
+            y = torch.addmm(residual, x, w.t())
         else:
-            y = x2 @ w.t()
-        ctx.save_for_backward(x2, weight)
+            y = x @ w.t()
+        ctx.save_for_backward(x, weight)
         ctx.rows = (r0, r1)
-        ctx.x_shape = x.shape
         ctx.has_residual = residual is not None
-        return y.view(*x.shape[:-1], w.shape[0])
+        return y
 
     @staticmethod
     def backward(ctx, dy):
         x2, weight = ctx.saved_tensors
         r0, r1 = ctx.rows
         w = weight if r0 is None else weight[r0:r1]
-        dy2 = dy.reshape(-1, dy.shape[-1])
+        dy2 = dy if dy.is_contiguous() else dy.contiguous()
         dx = dw = None
         if ctx.needs_input_grad[0]:
-            dx = (dy2 @ w).view(ctx.x_shape)
+            dx = dy2 @ w
         if ctx.needs_input_grad[1]:
             flat = getattr(weight, "_flat_grad", None)
             if flat is not None:
@@ -105,7 +105,12 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
     fusion of the residual and in-place weight-gradient accumulation."""
     if x.is_cuda and (weight.requires_grad or x.requires_grad) and torch.is_grad_enabled():
         r0, r1 = rows if rows is not None else (None, None)
-        y = _LinearFn.apply(x, weight, residual, r0, r1)
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1])
+        res2 = residual.reshape(-1, residual.shape[-1]) if residual is not None else None
+        y = _LinearFn.apply(x2, weight, res2, r0, r1)
+        if len(lead) != 1:
+            y = y.view(*lead, y.shape[-1])
         if bias is not None:
             y = y + (bias if rows is None else bias[rows[0] : rows[1]])
         return y
