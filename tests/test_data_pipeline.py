@@ -1,0 +1,240 @@
+import os
+import sys
+import warnings
+
+import numpy as np
+import pytest
+import torch
+from safetensors.torch import save_file
+
+from speculators_b200.data_generation.offline import check_hidden_states, get_existing_hidden_state_indices, get_indices_to_process
+from speculators_b200.data_generation.vllm_client import InvalidResponseError, extract_output, with_retries
+from speculators_b200.hs_connectors import (
+    DictStoreClient, FileBackend, FileTransfer, HiddenStatesBackend, HiddenStatesStore, MooncakeIntegrityError, wait_for_lock,
+)
+from speculators_b200.models.eagle3.data import shift_batch
+from speculators_b200.train.data import ArrowDataset, CollateFn, create_empty_sample
+from speculators_b200.train.distributed_batch_sampler import MultipackDistributedBatchSamplerV2, lpt_bins
+from speculators_b200.train.noise_transforms import AddGaussianNoise, AddUniformNoise
+from speculators_b200.train.vocab_mapping import build_vocab_mappings_from_distribution, token_frequency_from_ids
+
+from conftest import ROOT
+
+
+# ---- sampler -------------------------------------------------------------------------------
+def test_sampler_balance_partition_and_budget():
+    rng = np.random.default_rng(0)
+    lengths = rng.integers(16, 2000, size=400)
+    R = 4
+    per_rank = []
+    for rank in range(R):
+        s = MultipackDistributedBatchSamplerV2(4096, lengths, R, rank, seed=1)
+        per_rank.append([list(map(int, b)) for b in s])
+    counts = {len(b) for b in per_rank}
+    assert len(counts) == 1  # every rank gets the same number of batches
+    seen = [i for batches in per_rank for b in batches for i in b]
+    assert len(seen) == len(set(seen))  # no sample on two ranks / in two batches
+    for batches in per_rank:
+        assert all(lengths[b].sum() <= 4096 for b in batches)
+    s = MultipackDistributedBatchSamplerV2(4096, lengths, R, 0, seed=1)
+    first = [list(map(int, b)) for b in s]
+    s.set_epoch(1)
+    assert [list(map(int, b)) for b in s] != first  # reshuffled per epoch
+    assert s._generate_batches(1) is s._cached_generated_batches[1]
+
+
+def test_sampler_truncates_or_drops_long_samples():
+    lengths = [10, 5000, 20, 30]
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        s = MultipackDistributedBatchSamplerV2(100, lengths, 1, 0)
+        assert s.lengths.max() == 100 and len(s.valid_indices) == 4 and "truncated" in str(w[0].message)
+        s2 = MultipackDistributedBatchSamplerV2(100, lengths, 1, 0, truncate_long_samples=False)
+        assert 1 not in s2.valid_indices
+    assert lpt_bins(np.array([60, 60]), 100, 1) is None
+    assert lpt_bins(np.array([60, 50, 40]), 100, 2) == [[0], [1, 2]]
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "speculators")), reason="reference not installed")
+def test_sampler_assignment_identical_to_reference():
+    sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+    try:
+        from speculators.train.distributed_batch_sampler import MultipackDistributedBatchSamplerV2 as Ref
+    finally:
+        sys.path.pop(0)
+    lengths = np.random.default_rng(5).integers(10, 3000, size=300)
+    for R in (1, 3):
+        for rank in range(R):
+            a, b = Ref(4096, lengths, R, rank, seed=2), MultipackDistributedBatchSamplerV2(4096, lengths, R, rank, seed=2)
+            assert [list(map(int, x)) for x in a] == [list(map(int, x)) for x in b]
+
+
+# ---- collate ---------------------------------------------------------------------------------
+def _sample(n, H=4, layers=3):
+    return {"hidden_states": torch.randn(n, layers * H), "input_ids": torch.arange(n), "verifier_last_hidden_states": torch.randn(n, H),
+            "loss_mask": torch.ones(n, dtype=torch.bool), "lengths": torch.tensor([n]), "position_ids": torch.arange(n)}
+
+
+def test_collate_packs_pads_and_builds_document_ids():
+    col = CollateFn(max_len=16, hidden_size=4, num_target_layers=3, dtype=torch.bfloat16, preprocess=shift_batch)
+    out = col([_sample(6), None, _sample(5)])
+    assert out["hidden_states"].shape == (1, 16, 12) and out["hidden_states"].dtype == torch.bfloat16
+    assert out["document_ids"][0].tolist() == [0] * 5 + [1] * 4 + [-1] * 7
+    assert out["position_ids"][0, :5].tolist() == [1, 2, 3, 4, 5] and out["input_ids"][0, 5:9].tolist() == [1, 2, 3, 4]
+    assert "lengths" not in out
+
+
+def test_collate_truncates_at_max_len_and_handles_empty_batches():
+    col = CollateFn(max_len=8, hidden_size=4)
+    out = col([_sample(6), _sample(6)])
+    assert out["document_ids"][0].tolist() == [0] * 6 + [1] * 2
+    empty = CollateFn(max_len=8, hidden_size=4, preprocess=shift_batch)([None, None])
+    assert (empty["document_ids"] == -1).all() and empty["hidden_states"].shape == (1, 8, 12)
+    assert create_empty_sample(4)["lengths"].item() == 0
+
+
+def test_noise_transforms():
+    x = {"hidden_states": torch.zeros(1000, 4), "other": torch.zeros(3)}
+    y = AddUniformNoise(std=0.1)(dict(x))
+    assert y["hidden_states"].abs().max() <= 0.1 and y["hidden_states"].abs().mean() > 0.02 and (y["other"] == 0).all()
+    z = AddGaussianNoise(std=0.1)(dict(x))
+    assert 0.05 < z["hidden_states"].std() < 0.15
+
+
+# ---- dataset over the file backend ---------------------------------------------------------------
+def test_arrow_dataset_cached_hidden_states(tmp_path):
+    from datasets import Dataset
+
+    rows = [{"input_ids": list(range(i, i + 5 + i)), "loss_mask": [1] * (5 + i), "seq_len": 5 + i} for i in range(6)]
+    Dataset.from_list(rows).save_to_disk(str(tmp_path / "ds"))
+    hs_dir = tmp_path / "ds" / "hidden_states"
+    hs_dir.mkdir()
+    for i, r in enumerate(rows):
+        if i == 3:
+            continue  # missing sample
+        save_file({"hidden_states": torch.randn(r["seq_len"], 4, 8).to(torch.bfloat16), "token_ids": torch.tensor(r["input_ids"])}, str(hs_dir / f"hs_{i}.safetensors"))
+    train = ArrowDataset(32, tmp_path / "ds", on_missing="skip", train_ratio=0.67, split="train")
+    val = ArrowDataset(32, tmp_path / "ds", on_missing="skip", train_ratio=0.67, split="val")
+    assert len(train) == 4 and len(val) == 2 and val.start_file_idx == 4 and train.approx_lengths == [5, 6, 7, 8]
+    item = train[1]
+    assert item["hidden_states"].shape == (6, 24) and item["verifier_last_hidden_states"].shape == (6, 8) and item["lengths"].item() == 6
+    assert train[3] is None
+    with pytest.raises(RuntimeError):
+        ArrowDataset(32, tmp_path / "ds", on_missing="raise")[3]
+    assert val[0]["input_ids"].tolist() == rows[4]["input_ids"]
+    with pytest.raises(ValueError):
+        ArrowDataset(32, tmp_path / "ds", train_ratio=1.0, split="val")
+
+
+# ---- transports -------------------------------------------------------------------------------------
+def test_file_transfer_and_lock(tmp_path):
+    t = FileTransfer(tmp_path / "hs")
+    assert t.get_cached(0) is None
+    gen = tmp_path / "gen.safetensors"
+    save_file({"hidden_states": torch.zeros(2, 2, 2), "token_ids": torch.arange(2)}, str(gen))
+    assert t.get_generated(str(gen))["token_ids"].tolist() == [0, 1]
+    t.cache(str(gen), 7)
+    assert not gen.exists() and t.get_cached(7) is not None
+    lock = tmp_path / "x.lock"
+    lock.write_text("")
+    wait_for_lock(str(lock))
+    assert not lock.exists()
+    assert set(HiddenStatesBackend.registry) >= {"file", "mooncake"}
+    with pytest.raises(ValueError):
+        HiddenStatesBackend.register("file")(FileBackend)
+
+
+class _FailingClient(DictStoreClient):
+    def __init__(self, fail_on):
+        super().__init__()
+        self.fail_on = fail_on
+
+    def put_tensor(self, key, tensor):
+        if key.endswith(self.fail_on):
+            return -5
+        return super().put_tensor(key, tensor)
+
+
+def test_store_manifest_last_integrity_and_cleanup():
+    client = DictStoreClient()
+    store = HiddenStatesStore(client=client)
+    sample = {"hidden_states": torch.randn(3, 4).to(torch.bfloat16), "token_ids": torch.arange(3)}
+    store.put_sample("k", sample)
+    got = store.get_sample("k")
+    assert torch.equal(got["hidden_states"], sample["hidden_states"])
+    client._data["k:hidden_states"][0, 0] += 1  # corrupt payload
+    with pytest.raises(MooncakeIntegrityError, match="checksum"):
+        store.get_sample("k")
+    store.delete_sample("k")
+    assert not client._data
+    with pytest.raises(TimeoutError):
+        store.get_sample("missing", timeout=0.05, poll_interval=0.01)
+    store.put_error("bad", "producer failed")
+    with pytest.raises(MooncakeIntegrityError, match="producer failed"):
+        store.get_sample("bad")
+    failing = _FailingClient(":token_ids")
+    with pytest.raises(RuntimeError, match="status=-5"):
+        HiddenStatesStore(client=failing).put_sample("p", sample)
+    assert not failing._data  # partial write removed
+    with pytest.raises(RuntimeError, match="setup"):
+        HiddenStatesStore().put_sample("x", sample)
+
+
+# ---- client / offline helpers ----------------------------------------------------------------------------
+def test_retries_and_response_validation(monkeypatch):
+    monkeypatch.setattr("time.sleep", lambda s: None)
+    calls = {"n": 0}
+
+    @with_retries
+    def flaky():
+        calls["n"] += 1
+        if calls["n"] < 3:
+            raise TimeoutError("slow")
+        return "ok"
+
+    assert flaky(max_retries=3) == "ok" and calls["n"] == 3
+
+    @with_retries
+    def invalid():
+        calls["n"] += 1
+        raise InvalidResponseError("bad")
+
+    calls["n"] = 0
+    with pytest.raises(InvalidResponseError):
+        invalid(max_retries=5)
+    assert calls["n"] == 1  # deterministic errors are not retried
+
+    class R:
+        prompt_token_ids = [1, 2]
+        kv_transfer_params = {"handle": "h"}
+        choices = None
+
+    assert extract_output(R(), [1, 2]) == "h"
+    with pytest.raises(InvalidResponseError):
+        extract_output(R(), [1, 3])
+
+
+def test_check_hidden_states_and_index_split(tmp_path):
+    good = {"token_ids": torch.arange(4), "hidden_states": torch.zeros(4, 3, 2)}
+    check_hidden_states(good, [0, 1, 2, 3])
+    bad = {"token_ids": torch.arange(4), "hidden_states": torch.zeros(4, 3, 2)}
+    bad["hidden_states"][2, 1, 0] = float("nan")
+    with pytest.raises(ValueError, match=r"affected layer slots=\[1\]"):
+        check_hidden_states(bad, [0, 1, 2, 3])
+    with pytest.raises(ValueError):
+        check_hidden_states(good, [0, 1, 2])
+    (tmp_path / "hs_3.safetensors").write_text("")
+    (tmp_path / "hs_x.safetensors").write_text("")
+    assert get_existing_hidden_state_indices(tmp_path) == [3]
+    assert get_indices_to_process(10, None, [], 3, 0) == [0, 1, 2, 3]
+    assert get_indices_to_process(10, None, [4, 5], 3, 1) == [6]
+    assert get_indices_to_process(10, 5, [], 2, 1) == [3, 4]
+
+
+def test_vocab_mapping_offsets_and_ties():
+    freq = token_frequency_from_ids(torch.tensor([5, 5, 5, 2, 2, 9, 7]), torch.tensor([1, 1, 1, 1, 1, 1, 0]))
+    assert freq == {2: 2, 5: 3, 9: 1}
+    d2t, t2d = build_vocab_mappings_from_distribution(freq, 4, 12)
+    kept = torch.nonzero(t2d).squeeze(1)
+    assert kept.tolist() == [0, 2, 5, 9]  # top-3 by count, then the lowest unseen id
+    assert (torch.arange(4) + d2t).tolist() == kept.tolist()  # d2t stores offsets
