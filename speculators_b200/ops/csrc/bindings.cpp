@@ -22,6 +22,8 @@ int launch_loss_fwd(int, const void*, const void*, const uint8_t*, const int64_t
 int launch_loss_bwd(int, const void*, const void*, const float*, const float*, void*, int, int, int,
                     int64_t, int64_t, int64_t, int, cudaStream_t);
 int64_t launch_count();
+int launch_gemm_tn_tcgen05(const void*, const void*, void*, const void*, int, int, int, int64_t, int64_t, int64_t, int64_t, int,
+                           int*, cudaStream_t);
 int sumsq_num_partials();
 void launch_sumsq(const void*, int, int64_t, float*, float*, int, cudaStream_t);
 void launch_adamw(float*, float*, float*, const void*, int, void*, int64_t, const float*,
@@ -235,6 +237,31 @@ void adamw(Tensor master, Tensor m, Tensor v, const Tensor& grad, c10::optional<
 
 int64_t launch_count() { return sb200::launch_count(); }
 
+// ---- tcgen05 GEMM ------------------------------------------------------------------------
+// out[M,N] = a[M,K] @ b[N,K]^T; epilogue 0 = store, 1 = out += result, 2 = result + residual.
+// `status` (int32[1], device) receives a non-zero code if a bounded wait in the kernel ran out.
+void gemm_tn(const Tensor& a, const Tensor& b, Tensor out, const c10::optional<Tensor>& residual, int64_t epilogue, Tensor status) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && out.is_cuda() && status.is_cuda());
+  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16);
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && out.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && out.stride(1) == 1);
+  TORCH_CHECK(a.size(1) == b.size(1) && out.size(0) == a.size(0) && out.size(1) == b.size(0), "gemm_tn: shape mismatch");
+  TORCH_CHECK(status.scalar_type() == at::kInt && status.numel() >= 1);
+  const void* res = nullptr;
+  int64_t ldr = 0;
+  if (residual.has_value()) {
+    TORCH_CHECK(residual->scalar_type() == at::kBFloat16 && residual->dim() == 2 && residual->stride(1) == 1 &&
+                residual->size(0) == out.size(0) && residual->size(1) == out.size(1));
+    res = residual->data_ptr();
+    ldr = residual->stride(0);
+  }
+  TORCH_CHECK(epilogue != 2 || res != nullptr, "gemm_tn: epilogue 2 needs a residual");
+  c10::cuda::CUDAGuard guard(a.device());
+  const int rc = sb200::launch_gemm_tn_tcgen05(a.data_ptr(), b.data_ptr(), out.data_ptr(), res, (int)a.size(0), (int)b.size(0),
+                                               (int)a.size(1), a.stride(0), b.stride(0), out.stride(0), ldr, (int)epilogue,
+                                               status.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(rc == 0, "gemm_tn launch failed (", rc, ")");
+}
+
 // ---- masked attention ------------------------------------------------------------------
 void check_heads(const Tensor& t, const char* name, int64_t hd) {
   TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.dim() == 3, name, ": bf16 CUDA [T, heads, hd] expected");
@@ -358,6 +385,7 @@ TORCH_LIBRARY(sb200, m) {
   m.def("sumsq", &sumsq);
   m.def("adamw", &adamw);
   m.def("launch_count", &launch_count);
+  m.def("gemm_tn", &gemm_tn);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);
 }

@@ -1,0 +1,339 @@
+// bf16 GEMM on the 5th-generation tensor cores:  C[M,N] = A[M,K] * B[N,K]^T  (+ epilogue)
+//
+// This is the nn.Linear forward shape: both operands are K-major (row-major with K
+// contiguous), the accumulator is fp32.  Structure of one persistent CTA (192 threads):
+//
+//   warp 0  TMA producer : cp.async.bulk.tensor (128B-swizzled boxes, no multicast) into a
+//                          4-stage shared-memory ring, completion counted on mbarriers
+//   warp 1  MMA issuer   : allocates all 512 TMEM columns (two 128x256 fp32 accumulators),
+//                          one elected thread issues tcgen05.mma (M=128, N=256, K=16) from
+//                          shared-memory descriptors and tcgen05.commit's to free ring slots
+//   warps 2-5 epilogue   : tcgen05.ld the finished accumulator (each warp its own 32 TMEM
+//                          lanes = 32 output rows), convert to bf16, apply the epilogue and
+//                          store; the MMA warp meanwhile fills the other accumulator
+//
+// Tiles are walked n-major so that CTAs running at the same time share B (weight) tiles in
+// L2.  Ragged M / N / K are handled by TMA zero fill and masked stores.
+//
+// Every wait is bounded: a thread that exhausts its poll budget records a code in the
+// caller's status word and leaves its loop; the other roles then run out of budget (or
+// see the status word) too, the CTA meets at the final barrier, frees its TMEM and
+// returns.  Nothing traps and nothing spins forever.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace sb200 {
+
+namespace tc {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr uint32_t POLL_LIMIT = 1u << 22;
+
+enum Epilogue : int { kStore = 0, kAccumulate = 1, kAddResidual = 2 };
+enum Status : int { kOk = 0, kTimeoutProducer = 1, kTimeoutMma = 2, kTimeoutEpilogue = 3 };
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Bounded wait; false = gave up (status word set) or another role already failed.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+  for (uint32_t i = 0; i < POLL_LIMIT; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if ((i & 0xfff) == 0xfff && *reinterpret_cast<volatile int*>(status) != kOk) return false;
+  }
+  atomicCAS(status, kOk, code);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+// K-major operand tile, 128-byte swizzle: rows of 128 B, 8-row groups 1024 B apart.
+__device__ __forceinline__ uint64_t smem_desc_kmajor_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3ffff) >> 4);        // start address
+  d |= (uint64_t)1 << 16;                         // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;               // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                         // descriptor version (sm_100)
+  d |= (uint64_t)2 << 61;                         // SWIZZLE_128B
+  return d;
+}
+
+// kind::f16 instruction descriptor: D fp32, A/B bf16, both K-major, M x N tile.
+__host__ __device__ constexpr uint32_t instr_desc_bf16(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+struct Params {
+  __nv_bfloat16* c;
+  const __nv_bfloat16* residual;
+  int M, N, K;
+  int64_t ldc, ldr;
+  int epilogue;
+  int* status;
+};
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
+  extern __shared__ unsigned char smem_raw[];
+  // 1024-byte alignment for the swizzled tiles
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ __align__(8) uint64_t bar_full[STAGES], bar_empty[STAGES], bar_acc_full[2], bar_acc_empty[2];
+  __shared__ uint32_t tmem_base_slot;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_addr(&bar_full[s]), 1);
+      mbar_init(smem_addr(&bar_empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_addr(&bar_acc_full[a]), 1);
+      mbar_init(smem_addr(&bar_acc_empty[a]), 128);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!(ok = mbar_wait(smem_addr(&bar_empty[stage]), phase ^ 1, p.status, kTimeoutProducer))) break;
+          const uint32_t full = smem_addr(&bar_full[stage]);
+          mbar_expect_tx(full, STAGE_BYTES);
+          const uint32_t sa = smem_addr(smem + stage * STAGE_BYTES);
+          tma_load_2d(sa, &map_a, full, kb * BK, m0);
+          tma_load_2d(sa + A_BYTES, &map_b, full, kb * BK, n0);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc_bf16(BM, BN);
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      int local = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const int acc = local & 1;
+        if (!(ok = mbar_wait(smem_addr(&bar_acc_empty[acc]), ((local >> 1) & 1) ^ 1, p.status, kTimeoutMma))) break;
+        fence_after_sync();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!(ok = mbar_wait(smem_addr(&bar_full[stage]), phase, p.status, kTimeoutMma))) break;
+          fence_after_sync();
+          const uint32_t sa = smem_addr(smem + stage * STAGE_BYTES);
+          const uint64_t adesc = smem_desc_kmajor_sw128(sa), bdesc = smem_desc_kmajor_sw128(sa + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            // advancing 16 K-elements = 32 bytes inside the 128-byte swizzled row: +2 in 16-byte units
+            umma_bf16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+          }
+          umma_commit(smem_addr(&bar_empty[stage]));  // frees the ring slot once these MMAs retire
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(smem_addr(&bar_acc_full[acc]));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;  // TMEM lanes this warp may touch: 32*quarter .. +31
+    bool ok = true;
+    int local = 0;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      const int acc = local & 1;
+      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+      ok = mbar_wait(smem_addr(&bar_acc_full[acc]), (local >> 1) & 1, p.status, kTimeoutEpilogue);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      fence_after_sync();
+      const int row = m0 + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+      __nv_bfloat16* crow = p.c + (int64_t)row * p.ldc + n0;
+      const __nv_bfloat16* rrow = p.residual ? p.residual + (int64_t)row * p.ldr + n0 : nullptr;
+      const bool vec_ok = ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0) &&
+                          (p.epilogue != kAddResidual || (((p.ldr & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0)));
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c * 32, r);
+        tmem_ld_wait();
+        if (row < p.M) {
+          const int col0 = n0 + c * 32;
+          if (vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              float f[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]);
+              if (p.epilogue == kAccumulate) {
+                float o[8];
+                unpack8(ld8(crow + c * 32 + v * 8), o);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] += o[j];
+              } else if (p.epilogue == kAddResidual) {
+                float o[8];
+                unpack8(ld8(rrow + c * 32 + v * 8), o);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] += o[j];
+              }
+              st8(crow + c * 32 + v * 8, pack8(f));
+            }
+          } else {
+            for (int j = 0; j < 32; ++j) {
+              if (col0 + j < p.N) {
+                float f = __uint_as_float(r[j]);
+                if (p.epilogue == kAccumulate) f += __bfloat162float(crow[c * 32 + j]);
+                else if (p.epilogue == kAddResidual) f += __bfloat162float(rrow[c * 32 + j]);
+                crow[c * 32 + j] = __float2bfloat16(f);
+              }
+            }
+          }
+        }
+      }
+      fence_before_sync();
+      mbar_arrive(smem_addr(&bar_acc_empty[acc]));
+    }
+  }
+
+  // A role that gave up did so after seconds of polling, far beyond the lifetime of any
+  // bulk copy it had issued, so no copy is still writing shared memory at this point.
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    fence_after_sync();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ---- host side ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor map over a row-major [rows, cols] matrix with row stride `ld` elements;
+// box = 64 columns x `box_rows` rows, 128-byte swizzle, zero fill outside the matrix.
+static int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return -10;
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS ? 0 : -11;
+}
+
+}  // namespace tc
+
+// C[M,N] = A[M,K] * B[N,K]^T with epilogue (0 store, 1 C += result, 2 result + residual).
+// lda / ldb / ldc / ldr in elements; A, B rows must be 16-byte aligned (ld multiple of 8).
+// `status` is a device int the kernel writes a non-zero code to if a bounded wait ran out.
+int launch_gemm_tn_tcgen05(const void* a, const void* b, void* c, const void* residual, int M, int N, int K, int64_t lda,
+                           int64_t ldb, int64_t ldc, int64_t ldr, int epilogue, int* status, cudaStream_t stream) {
+  using namespace tc;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda & 7) || (ldb & 7) || (reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15)) return -1;
+  CUtensorMap map_a, map_b;
+  int rc = make_map(&map_a, a, M, K, lda, BM);
+  if (rc) return rc;
+  rc = make_map(&map_b, b, N, K, ldb, BN);
+  if (rc) return rc;
+  static bool configured = false;
+  constexpr int smem_bytes = STAGES * STAGE_BYTES + 1024;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return -2;
+    configured = true;
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int grid = tiles < kNumSM ? tiles : kNumSM;
+  Params p{(__nv_bfloat16*)c, (const __nv_bfloat16*)residual, M, N, K, ldc, ldr, epilogue, status};
+  count_launch(1);
+  gemm_tn_kernel<<<grid, THREADS, smem_bytes, stream>>>(map_a, map_b, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+}  // namespace sb200
