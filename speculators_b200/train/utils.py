@@ -9,7 +9,7 @@ import sys
 
 from speculators_b200 import provenance
 
-__all__ = ["normalize_counted_metrics", "save_train_command"]
+__all__ = ["normalize_counted_metrics", "resolve_mask_token_id", "save_train_command"]
 
 
 def normalize_counted_metrics(metrics: dict[str, float], world_size: int = 1) -> dict[str, float]:
@@ -44,3 +44,36 @@ def save_train_command(save_dir: str | os.PathLike, argv: list[str] | None = Non
     path = os.path.join(save_dir, "train_command.txt")
     provenance.atomic_write(path, "\n".join(lines) + "\n")
     return path
+
+
+def resolve_mask_token_id(verifier_name_or_path: str, vocab_size: int, mask_token_id: int | None = None, *, trust_remote_code: bool = False) -> int:
+    """Mask token for P-EAGLE / DFlash / DSpark.  Order: the explicit value; the
+    tokenizer's own mask token; a new ``<|MASK|>`` token if the embedding table has
+    unused rows; else pad / eos / unk (with a warning).  Passing ``--mask-token-id``
+    avoids loading a tokenizer altogether (src/speculators/train/utils.py:17-68)."""
+    import logging
+    import warnings
+
+    log = logging.getLogger("speculators")
+    if mask_token_id is not None:
+        log.info("Using explicit mask_token_id=%d", mask_token_id)
+        return mask_token_id
+    from transformers import AutoTokenizer
+
+    tokenizer = AutoTokenizer.from_pretrained(verifier_name_or_path, trust_remote_code=trust_remote_code)
+    if tokenizer.mask_token_id is not None:
+        log.info("Using tokenizer mask_token_id=%d", tokenizer.mask_token_id)
+        return tokenizer.mask_token_id
+    if len(tokenizer) < vocab_size:
+        tokenizer.add_special_tokens({"mask_token": "<|MASK|>"})
+        log.warning("Added <|MASK|> to tokenizer, mask_token_id=%d (tokenizer len=%d, vocab_size=%d)", tokenizer.mask_token_id, len(tokenizer), vocab_size)
+        return tokenizer.mask_token_id
+    for name in ("pad_token_id", "eos_token_id", "unk_token_id"):
+        token_id = getattr(tokenizer, name, None)
+        if token_id is not None:
+            warnings.warn(f"Tokenizer does not have mask_token and no unused embedding slots. Using {name}={token_id} as fallback.", stacklevel=2)
+            return token_id
+    raise ValueError(
+        "Could not resolve mask_token_id: no --mask-token-id provided, tokenizer has no mask_token, no unused "
+        "embedding slots, and no pad/eos/unk fallback tokens."
+    )
