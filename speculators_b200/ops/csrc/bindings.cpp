@@ -25,7 +25,17 @@ int64_t launch_count();
 int launch_gemm_tn_tcgen05(const void*, const void*, void*, const void*, int, int, int, int64_t, int64_t, int64_t, int64_t, int,
                            int*, cudaStream_t);
 int sumsq_num_partials();
+int peer_malloc(int64_t, void**);
+int peer_free(void*);
+int peer_export(void*, unsigned char*);
+int peer_import(const unsigned char*, void**);
+int peer_close(void*);
+int fused_optim_ctl_words();
+int fused_optim_num_partials();
+int launch_fused_sharded_adamw(int, int, int64_t, const void* const*, void* const*, void* const*, float*, float*, float*, float*,
+                               float*, const float*, int*, cudaStream_t);
 void launch_sumsq(const void*, int, int64_t, float*, float*, int, cudaStream_t);
+void launch_set_hyper(float*, const float*, cudaStream_t);
 void launch_adamw(float*, float*, float*, const void*, int, void*, int64_t, const float*,
                   const float*, cudaStream_t);
 }  // namespace sb200
@@ -210,6 +220,16 @@ void sumsq(const Tensor& g, Tensor out, bool accumulate) {
                       partial.data_ptr<float>(), out.data_ptr<float>(), accumulate, cur_stream());
 }
 
+// hyper (fp32[16], CUDA) <- vals (<= 16 host doubles), passed as kernel arguments.
+void set_hyper(Tensor hyper, std::vector<double> vals) {
+  TORCH_CHECK(hyper.is_cuda() && hyper.scalar_type() == at::kFloat && hyper.numel() >= 16 && hyper.is_contiguous());
+  TORCH_CHECK(vals.size() <= 16);
+  float host[16] = {0};
+  for (size_t i = 0; i < vals.size(); ++i) host[i] = (float)vals[i];
+  c10::cuda::CUDAGuard guard(hyper.device());
+  sb200::launch_set_hyper(hyper.data_ptr<float>(), host, at::cuda::getCurrentCUDAStream());
+}
+
 void adamw(Tensor master, Tensor m, Tensor v, const Tensor& grad, c10::optional<Tensor> w16,
            const Tensor& hyper, const c10::optional<Tensor>& norm_sq) {
   const int64_t n = master.numel();
@@ -236,6 +256,58 @@ void adamw(Tensor master, Tensor m, Tensor v, const Tensor& grad, c10::optional<
 }
 
 int64_t launch_count() { return sb200::launch_count(); }
+
+// ---- peer memory + fused sharded optimizer -------------------------------------------------
+int64_t peer_alloc(int64_t nbytes) {
+  void* p = nullptr;
+  TORCH_CHECK(sb200::peer_malloc(nbytes, &p) == 0, "peer_alloc: cudaMalloc of ", nbytes, " bytes failed");
+  return reinterpret_cast<int64_t>(p);
+}
+void peer_release(int64_t ptr) { sb200::peer_free(reinterpret_cast<void*>(ptr)); }
+Tensor peer_handle(int64_t ptr) {
+  Tensor h = at::empty({64}, at::TensorOptions().dtype(at::kByte));
+  TORCH_CHECK(sb200::peer_export(reinterpret_cast<void*>(ptr), h.data_ptr<uint8_t>()) == 0, "peer_handle: cudaIpcGetMemHandle failed");
+  return h;
+}
+int64_t peer_open(const Tensor& handle) {
+  TORCH_CHECK(handle.device().is_cpu() && handle.scalar_type() == at::kByte && handle.numel() == 64 && handle.is_contiguous());
+  void* p = nullptr;
+  TORCH_CHECK(sb200::peer_import(handle.data_ptr<uint8_t>(), &p) == 0, "peer_open: cudaIpcOpenMemHandle failed");
+  return reinterpret_cast<int64_t>(p);
+}
+void peer_close(int64_t ptr) { sb200::peer_close(reinterpret_cast<void*>(ptr)); }
+// Non-owning tensor over raw device memory (the caller keeps the allocation alive).
+Tensor peer_tensor(int64_t ptr, int64_t numel, at::ScalarType dtype, int64_t device) {
+  auto opts = at::TensorOptions().dtype(dtype).device(at::kCUDA, (c10::DeviceIndex)device);
+  return at::from_blob(reinterpret_cast<void*>(ptr), {numel}, opts);
+}
+int64_t fused_optim_ctl_words() { return sb200::fused_optim_ctl_words(); }
+
+// g_ptrs / w_ptrs / ctl_ptrs: int64 CPU tensors [world] of device addresses valid on this rank.
+void fused_sharded_adamw(int64_t world, int64_t rank, int64_t shard, const Tensor& g_ptrs, const Tensor& w_ptrs, const Tensor& ctl_ptrs,
+                         Tensor master, Tensor m, Tensor v, Tensor gred, const Tensor& hyper, Tensor status) {
+  TORCH_CHECK(g_ptrs.device().is_cpu() && g_ptrs.scalar_type() == at::kLong && g_ptrs.numel() == world);
+  TORCH_CHECK(w_ptrs.device().is_cpu() && w_ptrs.scalar_type() == at::kLong && w_ptrs.numel() == world);
+  TORCH_CHECK(ctl_ptrs.device().is_cpu() && ctl_ptrs.scalar_type() == at::kLong && ctl_ptrs.numel() == world);
+  for (const Tensor* t : {&master, &m, &v, &gred})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kFloat && t->is_contiguous() && t->numel() == shard, "shard buffers must be fp32[shard]");
+  TORCH_CHECK(hyper.is_cuda() && hyper.scalar_type() == at::kFloat && hyper.numel() >= 9);
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == at::kInt);
+  c10::cuda::CUDAGuard guard(master.device());
+  const void* g[8];
+  void* w[8];
+  void* c[8];
+  for (int q = 0; q < world; ++q) {
+    g[q] = reinterpret_cast<const void*>(g_ptrs.data_ptr<int64_t>()[q]);
+    w[q] = reinterpret_cast<void*>(w_ptrs.data_ptr<int64_t>()[q]);
+    c[q] = reinterpret_cast<void*>(ctl_ptrs.data_ptr<int64_t>()[q]);
+  }
+  Tensor partial = at::empty({sb200::fused_optim_num_partials()}, master.options());
+  const int rc = sb200::launch_fused_sharded_adamw((int)world, (int)rank, shard, g, w, c, master.data_ptr<float>(), m.data_ptr<float>(),
+                                                   v.data_ptr<float>(), gred.data_ptr<float>(), partial.data_ptr<float>(),
+                                                   hyper.data_ptr<float>(), status.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(rc == 0, "fused_sharded_adamw launch failed (", rc, ")");
+}
 
 // ---- tcgen05 GEMM ------------------------------------------------------------------------
 // out[M,N] = a[M,K] @ b[N,K]^T; epilogue 0 = store, 1 = out += result, 2 = result + residual.
@@ -384,7 +456,16 @@ TORCH_LIBRARY(sb200, m) {
   m.def("ce_label_fwd", &ce_label_fwd);
   m.def("sumsq", &sumsq);
   m.def("adamw", &adamw);
+  m.def("set_hyper", &set_hyper);
   m.def("launch_count", &launch_count);
+  m.def("peer_alloc", &peer_alloc);
+  m.def("peer_release", &peer_release);
+  m.def("peer_handle", &peer_handle);
+  m.def("peer_open", &peer_open);
+  m.def("peer_close", &peer_close);
+  m.def("peer_tensor", &peer_tensor);
+  m.def("fused_optim_ctl_words", &fused_optim_ctl_words);
+  m.def("fused_sharded_adamw", &fused_sharded_adamw);
   m.def("gemm_tn", &gemm_tn);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);

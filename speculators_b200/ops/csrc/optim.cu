@@ -108,6 +108,22 @@ adamw_kernel(float* __restrict__ master, float* __restrict__ m, float* __restric
   }
 }
 
+// Hyper-parameters travel as kernel arguments (copied at launch), so the host can
+// prepare step k+1 while step k is still queued: no staging buffer to overwrite.
+struct HyperVals {
+  float v[16];
+};
+__global__ void set_hyper_kernel(float* __restrict__ hyper, const HyperVals vals) {
+  if (threadIdx.x < 16) hyper[threadIdx.x] = vals.v[threadIdx.x];
+}
+
+void launch_set_hyper(float* hyper, const float* host_vals16, cudaStream_t stream) {
+  HyperVals vals;
+  for (int i = 0; i < 16; ++i) vals.v[i] = host_vals16[i];
+  count_launch(1);
+  set_hyper_kernel<<<1, 32, 0, stream>>>(hyper, vals);
+}
+
 int sumsq_num_partials() { return 4 * kNumSM; }
 
 void launch_sumsq(const void* g, int is_bf16, int64_t n, float* partial, float* out, int accumulate,

@@ -69,6 +69,11 @@ class EngineConfig:
     muon_adjust_lr_fn: str = "match_rms_adamw"
     compute_dtype: torch.dtype = torch.bfloat16
     shard: bool = False
+    # "nccl": reduce-scatter / all-gather through torch.distributed.  "p2p": the sharded
+    # step runs as two fused kernels that read peers' gradients and write peers' weights
+    # through NVLink peer mappings (single node, AdamW, bf16 compute).  "auto": p2p when
+    # it applies, else nccl.
+    comm: str = "auto"
     group: object | None = None
     broadcast_from_rank0: bool = True
     extra: dict = field(default_factory=dict)
@@ -84,9 +89,50 @@ class TrainEngine:
         self.world = dist.get_world_size(self.group) if self.distributed else 1
         self.rank = dist.get_rank(self.group) if self.distributed else 0
         self.sharded = bool(config.shard) and self.world > 1
+        self.p2p = self._want_p2p()
         self.step_count = 0
         self._flatten()
         self._init_state()
+
+    def _want_p2p(self) -> bool:
+        import os
+
+        mode = os.environ.get("SB200_COMM", self.cfg.comm)
+        if mode not in ("auto", "p2p", "nccl"):
+            raise ValueError(f"comm must be auto, p2p or nccl, got {mode!r}")
+        applicable = (
+            self.sharded and self.device.type == "cuda" and self.cfg.optimizer == "adamw"
+            and self.cfg.compute_dtype == torch.bfloat16 and self.world <= 8
+        )
+        if mode == "p2p" and not applicable:
+            raise ValueError("comm='p2p' needs sharded multi-rank CUDA training with AdamW in bf16 on one node (<= 8 ranks)")
+        return applicable and mode in ("auto", "p2p")
+
+    def _alloc_flat(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        """Flat buffer in ordinary allocator memory, or (p2p) in cudaMalloc'ed memory
+        that is exported to the peers."""
+        if not self.p2p:
+            return torch.zeros(numel, dtype=dtype, device=self.device)
+        nat = ops.native()
+        ptr = nat.peer_alloc(numel * torch.empty((), dtype=dtype).element_size())
+        self._peer_local.append(ptr)
+        return nat.peer_tensor(ptr, numel, dtype, self.device.index or 0)
+
+    def _exchange(self, local_ptr: int) -> list[int]:
+        """All ranks publish the IPC handle of ``local_ptr``; returns the address of
+        every rank's buffer as mapped into this process (own buffer: the local address)."""
+        nat = ops.native()
+        handles: list = [None] * self.world
+        dist.all_gather_object(handles, nat.peer_handle(local_ptr), group=self.group)
+        out = []
+        for q, h in enumerate(handles):
+            if q == self.rank:
+                out.append(local_ptr)
+            else:
+                mapped = nat.peer_open(h)
+                self._peer_mapped.append(mapped)
+                out.append(mapped)
+        return out
 
     # ------------------------------------------------------------------ layout
     def _flatten(self) -> None:
@@ -121,8 +167,10 @@ class TrainEngine:
                 self.muon_end = off
         unit = _ALIGN * self.world
         self.total = (off + unit - 1) // unit * unit
-        self.flat_w = torch.zeros(self.total, dtype=cfg.compute_dtype, device=dev)
-        self.flat_g = torch.zeros(self.total, dtype=cfg.compute_dtype, device=dev)
+        self._peer_local: list[int] = []
+        self._peer_mapped: list[int] = []
+        self.flat_w = self._alloc_flat(self.total, cfg.compute_dtype)
+        self.flat_g = self._alloc_flat(self.total, cfg.compute_dtype)
         init32 = torch.zeros(self.total, dtype=torch.float32, device=dev)
         for p, o in zip(self.params, self.offsets):
             init32[o : o + p.numel()].copy_(p.data.detach().reshape(-1).to(device=dev, dtype=torch.float32))
@@ -155,14 +203,21 @@ class TrainEngine:
         self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev)
         self.norm_sq = torch.zeros(1, dtype=torch.float32, device=dev)
         self.hyper = torch.zeros(ops.HYPER_LEN, dtype=torch.float32, device=dev)
-        self._hyper_host = torch.zeros(ops.HYPER_LEN, dtype=torch.float32)
-        if dev.type == "cuda":
-            self._hyper_host = self._hyper_host.pin_memory()
         self.grad_shard = (
             torch.zeros(n, dtype=self.cfg.compute_dtype, device=dev) if self.sharded else self.flat_g
         )
         self.base_lr = self.cfg.lr
         self.base_muon_lr = self.cfg.muon_lr
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        if self.p2p:
+            nat = ops.native()
+            ctl = nat.peer_alloc(int(nat.fused_optim_ctl_words()) * 4)
+            self._peer_local.append(ctl)
+            self._g_ptrs = torch.tensor(self._exchange(self.flat_g.data_ptr()), dtype=torch.int64)
+            self._w_ptrs = torch.tensor(self._exchange(self.flat_w.data_ptr()), dtype=torch.int64)
+            self._ctl_ptrs = torch.tensor(self._exchange(ctl), dtype=torch.int64)
+            self.grad_reduced = torch.zeros(n, dtype=torch.float32, device=dev)
+            dist.barrier(group=self.group)
 
     # ------------------------------------------------------------------ step
     def zero_grad(self) -> None:
@@ -175,21 +230,32 @@ class TrainEngine:
 
     def prepare_hyper(self, lr: float | None = None) -> None:
         """Host side of a step: bump the step counter and stage lr / bias corrections
-        (async copy from pinned memory).  Call before ``apply`` (or before a graph
+        (a one-block kernel that takes them by value).  Call before ``apply`` (or before a graph
         replay that contains ``apply``)."""
         self.step_count += 1
         b1, b2 = self.cfg.betas
         lr = self.base_lr if lr is None else lr
-        h = self._hyper_host
-        h[0], h[1], h[2], h[3], h[4] = lr, b1, b2, self.cfg.eps, self.cfg.weight_decay
-        h[5] = 1.0 - b1**self.step_count
-        h[6] = 1.0 - b2**self.step_count
-        h[7] = self.cfg.max_grad_norm if self.cfg.max_grad_norm else 0.0
-        h[8] = 1.0 / self.world
-        self.hyper.copy_(h, non_blocking=True)
+        vals = [
+            lr, b1, b2, self.cfg.eps, self.cfg.weight_decay,
+            1.0 - b1**self.step_count, 1.0 - b2**self.step_count,
+            self.cfg.max_grad_norm if self.cfg.max_grad_norm else 0.0,
+            1.0 / self.world,
+        ]
+        if self.hyper.is_cuda:
+            # by-value kernel arguments: a pinned staging row would be overwritten by
+            # the next call while this step's copy is still queued
+            ops.native().set_hyper(self.hyper, vals)
+        else:
+            self.hyper[: len(vals)] = torch.tensor(vals, dtype=torch.float32)
 
     def apply(self) -> None:
         """Device side of a step (capturable): reduce, norm, update, gather."""
+        if self.p2p:
+            ops.native().fused_sharded_adamw(
+                self.world, self.rank, self.hi - self.lo, self._g_ptrs, self._w_ptrs, self._ctl_ptrs, self.master, self.exp_avg,
+                self.exp_avg_sq, self.grad_reduced, self.hyper, self.status,
+            )
+            return
         if self.distributed and self.world > 1:
             if self.sharded:
                 dist.reduce_scatter_tensor(self.grad_shard, self.flat_g, op=dist.ReduceOp.SUM, group=self.group)
@@ -248,6 +314,26 @@ class TrainEngine:
             master.sub_(update * (lr * adj))
             if self.cfg.compute_dtype != torch.float32:
                 self.flat_w[o : o + n].view(p.shape).copy_(master)
+
+    def check_status(self) -> None:
+        """Raise if a bounded device-side wait of the fused step ran out (a peer did
+        not arrive).  Reads one int from the device, so call it where a host sync is
+        acceptable (logging steps, checkpoints)."""
+        code = int(self.status.item())
+        if code != 0:
+            names = {11: "gradient barrier", 12: "norm barrier", 13: "closing barrier", 14: "local release"}
+            raise RuntimeError(f"fused optimizer step timed out waiting at the {names.get(code, code)}: a peer rank did not arrive")
+
+    def close(self) -> None:
+        """Unmap peers' buffers and free exported memory (p2p mode)."""
+        if getattr(self, "_peer_mapped", None) or getattr(self, "_peer_local", None):
+            nat = ops.native()
+            if self.distributed:
+                torch.cuda.synchronize(self.device)
+                dist.barrier(group=self.group)
+            for ptr in self._peer_mapped:
+                nat.peer_close(ptr)
+            self._peer_mapped = []
 
     # ------------------------------------------------------------------ state
     def grad_norm(self) -> torch.Tensor:

@@ -306,7 +306,13 @@ class Trainer:
             use_graph = False
         self._graphed = None
         if use_graph and self.device_type == "cuda":
-            capture_opt = (not self.is_distributed) or os.environ.get("SB200_GRAPH_COLLECTIVES") == "1"
+            # the fused peer-memory optimizer step is two plain kernels: capturable as is
+            capture_opt = (
+                (not self.is_distributed) or getattr(self.engine, "p2p", False)
+                or os.environ.get("SB200_GRAPH_COLLECTIVES") == "1"
+            )
+            if os.environ.get("SB200_GRAPH_OPTIMIZER") == "0":
+                capture_opt = False
             self._graphed = _GraphedStep(self, capture_optimizer=capture_opt)
 
     # ------------------------------------------------------------------ one step
