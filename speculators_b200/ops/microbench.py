@@ -1,0 +1,172 @@
+"""Kernel microbenchmarks: ``python -m speculators_b200.ops.microbench --op <name>``.
+
+Each op runs the package's own CUDA kernel on one GPU at the shapes it sees in an
+EAGLE-3 step for an 8B verifier (overridable), times it with CUDA events on the
+launching stream (warm-up first, an L2-sized buffer rewritten between iterations) and
+prints one JSON line with the median time, the algorithmic bytes / FLOPs and, when
+``--peaks <json>`` names a file with ``hbm_gbs`` and ``bf16_tflops``, the fraction of
+those measured peaks.  ``--iters 1 --warmup 0`` gives a short run for a profiler.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import sys
+
+import torch
+
+
+def _timeit(fn, iters: int, warmup: int, flush: torch.Tensor | None) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        fn()
+        stop.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(stop))
+    return statistics.median(times)
+
+
+def _bf16(*shape, scale: float = 1.0) -> torch.Tensor:
+    return (torch.randn(*shape, device="cuda") * scale).bfloat16()
+
+
+def _no_grad(fn):
+    def run():
+        with torch.no_grad():
+            return fn()
+
+    return run
+
+
+def op_gemm(a):
+    from speculators_b200 import ops
+
+    nat = ops.native()
+    M, N, K = a.m, a.n, a.k
+    x, w, out = _bf16(M, K), _bf16(N, K, scale=0.05), torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    fn = lambda: nat.gemm_tn(x, w, out, None, 0, status)  # noqa: E731
+    return fn, 2.0 * M * N * K, 2.0 * (M * K + N * K + M * N), lambda: {"status": int(status.item())}
+
+
+def op_gemm_cublas(a):
+    M, N, K = a.m, a.n, a.k
+    x, w, out = _bf16(M, K), _bf16(N, K, scale=0.05), torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    return (lambda: torch.matmul(x, w.t(), out=out)), 2.0 * M * N * K, 2.0 * (M * K + N * K + M * N), dict
+
+
+def _attn_inputs(a):
+    from speculators_b200.models.eagle3.attention import ttt_attn_spec
+
+    T, nh, nkv, hd, step = a.t, a.heads, a.kv_heads, a.head_dim, a.ttt_step
+    doc = torch.zeros(T, dtype=torch.long, device="cuda")
+    spec = ttt_attn_spec(doc, step)
+    q, k, v = (_bf16(T, h, hd).requires_grad_() for h in (nh, nkv, nkv))
+    ke = _bf16(step * T, nkv, hd).requires_grad_() if step else None
+    ve = _bf16(step * T, nkv, hd).requires_grad_() if step else None
+    flops = 4.0 * T * T * nh * hd / 2 + 4.0 * T * step * nh * hd  # causal half + one extra key per earlier pass
+    nbytes = 2.0 * hd * (2 * T * nh + 2 * T * nkv * (1 + step))
+    return q, k, v, ke, ve, spec, flops, nbytes
+
+
+def op_attn_fwd(a):
+    from speculators_b200.ops import masked_attention
+
+    q, k, v, ke, ve, spec, flops, nbytes = _attn_inputs(a)
+    return _no_grad(lambda: masked_attention(q, k, v, spec, ke, ve)), flops, nbytes, dict
+
+
+def op_attn_bwd(a):
+    from speculators_b200.ops import masked_attention
+
+    q, k, v, ke, ve, spec, flops, nbytes = _attn_inputs(a)
+    out = masked_attention(q, k, v, spec, ke, ve)
+    go = torch.ones_like(out)
+    return (lambda: out.backward(go, retain_graph=True)), 2.5 * flops, 2.5 * nbytes, dict
+
+
+def op_loss(a):
+    from speculators_b200 import ops
+
+    T, V = a.t, a.vocab
+    logits, targets = _bf16(T, V), _bf16(T, V)
+    active = torch.ones(T, dtype=torch.bool, device="cuda")
+    return _no_grad(lambda: ops.fused_row_loss("kl_div", logits, targets, 0, None, active)), 0.0, 2.0 * 2 * T * V, dict
+
+
+def op_rmsnorm(a):
+    from speculators_b200 import ops
+
+    T, H = a.t, a.hidden
+    x, w = _bf16(T, H), torch.ones(H, device="cuda", dtype=torch.bfloat16)
+    return _no_grad(lambda: ops.rms_norm(x, w, 1e-5)), 0.0, 2.0 * 2 * T * H, dict
+
+
+def op_adamw(a):
+    from speculators_b200 import ops
+
+    n = a.numel
+    master, m, v = (torch.zeros(n, device="cuda") for _ in range(3))
+    g, w16 = _bf16(n, scale=0.01), torch.zeros(n, device="cuda", dtype=torch.bfloat16)
+    hyper = torch.zeros(ops.HYPER_LEN, device="cuda")
+    ops.native().set_hyper(hyper, [1e-4, 0.9, 0.999, 1e-8, 0.01, 0.1, 0.001, 1.0, 1.0])
+    norm_sq = torch.ones(1, device="cuda")
+    fn = lambda: ops.adamw_step_(master, m, v, g, w16, hyper, norm_sq)  # noqa: E731
+    return fn, 0.0, n * (3 * 4 * 2 + 2 + 2.0), dict
+
+
+OPS = {"gemm": op_gemm, "gemm_cublas": op_gemm_cublas, "attn_fwd": op_attn_fwd, "attn_bwd": op_attn_bwd, "loss": op_loss,
+       "rmsnorm": op_rmsnorm, "adamw": op_adamw}
+
+
+def main(argv: list[str] | None = None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--op", choices=sorted(OPS), required=True)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-flush", action="store_true", help="do not rewrite an L2-sized buffer between iterations")
+    ap.add_argument("--peaks", default=None, help="JSON file with measured hbm_gbs and bf16_tflops")
+    ap.add_argument("-m", type=int, default=2048)
+    ap.add_argument("-n", type=int, default=6144)
+    ap.add_argument("-k", type=int, default=8192)
+    ap.add_argument("-t", type=int, default=2048, help="tokens")
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--ttt-step", type=int, default=0)
+    ap.add_argument("--vocab", type=int, default=32000)
+    ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--numel", type=int, default=1 << 28)
+    args = ap.parse_args(argv)
+    if not torch.cuda.is_available():
+        print(json.dumps({"op": args.op, "unavailable": "no CUDA device"}))
+        return 0
+    torch.manual_seed(0)
+    fn, flops, nbytes, extra = OPS[args.op](args)
+    flush = None if args.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    ms = _timeit(fn, args.iters, args.warmup, flush)
+    rec = {"op": args.op, "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1), "gbs": round(nbytes / ms / 1e6, 1),
+           "iters": args.iters, "warmup": args.warmup, "l2_flush": not args.no_flush}
+    rec.update(extra())
+    if args.peaks:
+        with open(args.peaks) as fh:
+            peaks = json.load(fh)
+        if flops and peaks.get("bf16_tflops"):
+            rec["frac_of_measured_bf16"] = round(rec["tflops"] / peaks["bf16_tflops"], 3)
+        if peaks.get("hbm_gbs"):
+            rec["frac_of_measured_hbm"] = round(rec["gbs"] / peaks["hbm_gbs"], 3)
+    print(json.dumps(rec))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

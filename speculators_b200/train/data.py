@@ -53,7 +53,8 @@ def build_client_item(dataset_item: dict) -> ClientItem:
     for multimodal conversations (content given as a list of typed parts): the
     chat endpoint re-tokenises the untruncated conversation, which is required
     for images but would overflow ``max_model_len`` for truncated text samples."""
-    item: dict = {"input_ids": dataset_item["input_ids"].tolist()}
+    ids = dataset_item["input_ids"]
+    item: dict = {"input_ids": ids.tolist() if hasattr(ids, "tolist") else [int(t) for t in ids]}
     messages = dataset_item.get("messages")
     if messages and any(isinstance(m.get("content"), list) for m in messages):
         item["messages"] = messages
