@@ -520,8 +520,13 @@ __global__ void kv_tile_range_kernel(const int* __restrict__ lo, const int* __re
 }
 
 // ----------------------------------------------------------------------------------------
-// Backward, part 2: dK / dV of the context keys.  One CTA per (kv tile, kv head); each warp
-// owns 16 keys and accumulates over the query heads of the group and over query tiles.
+// Backward, part 2: dK / dV of the context keys.  One CTA per (query head, kv tile); each
+// warp owns 16 keys and accumulates over the query tiles that can see them.  Under a
+// causal mask the work per kv tile falls linearly with its index, so the grid is ordered
+// heaviest tile first and split by query head (1..n_qt iterations per CTA instead of
+// group * n_qt): the tail of light CTAs fills the SMs the heavy ones leave.  With grouped
+// queries the CTAs of a group write fp32 partials that dkv_reduce_kernel sums in fixed
+// order (deterministic), otherwise the bf16 result is written directly.
 template <int HD>
 __global__ void __launch_bounds__(kAttnThreads)
 attn_bwd_dkv_kernel(const AttnParams p) {
@@ -535,8 +540,9 @@ attn_bwd_dkv_kernel(const AttnParams p) {
   float* rowf = reinterpret_cast<float*>(dOs + 2 * kTile);  // [2][2][64]: lse2, delta
   int* rowi = reinterpret_cast<int*>(rowf + 2 * 2 * kBM);   // [2][2][64]: lo, hi
 
-  const int tile_n = blockIdx.x, kvh = blockIdx.y;
+  const int hq = blockIdx.x, tile_n = blockIdx.y;
   const int group = p.nh / p.nkv;
+  const int kvh = hq / group;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int key0 = tile_n * kBN;
@@ -545,16 +551,14 @@ attn_bwd_dkv_kernel(const AttnParams p) {
   const int qmin = p.tile_qmin[tile_n], qmax = p.tile_qmax[tile_n];
   const int i0 = qmax > qmin ? qmin / kBM : 0;
   const int i1 = qmax > qmin ? (qmax + kBM - 1) / kBM : 0;
-  const int n_qt = i1 - i0;
-  const int n_iter = n_qt * group;
+  const int n_iter = i1 - i0;
 
   load_tile_async<HD>(Kt, p.k, p.k_rs, key0, p.Tc, kvh * HD);
   load_tile_async<HD>(Vt, p.v, p.v_rs, key0, p.Tc, kvh * HD);
   cp_async_commit();
 
   auto issue = [&](int it, int buf) {
-    const int hq = kvh * group + it / n_qt;
-    const int qrow0 = (i0 + it % n_qt) * kBM;
+    const int qrow0 = (i0 + it) * kBM;
     load_tile_async<HD>(Qs + buf * kTile, p.q, p.q_rs, qrow0, p.Tq, hq * HD);
     load_tile_async<HD>(dOs + buf * kTile, p.dout, p.do_rs, qrow0, p.Tq, hq * HD);
     if (threadIdx.x < kBM) {
@@ -674,23 +678,56 @@ attn_bwd_dkv_kernel(const AttnParams p) {
   }
   cp_async_wait<0>();
 
-  if (ka < p.Tc) {
-    __nv_bfloat16* rk = p.dk + ((int64_t)ka * p.nkv + kvh) * HD;
-    __nv_bfloat16* rv = p.dv + ((int64_t)ka * p.nkv + kvh) * HD;
+  if (p.dkv_part != nullptr) {
+    const int64_t plane = (int64_t)p.Tc * p.nkv * HD;
+    float* base = p.dkv_part + (int64_t)(hq - kvh * group) * 2 * plane;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int key = half ? kb : ka;
+      if (key >= p.Tc) continue;
+      float* rk = base + ((int64_t)key * p.nkv + kvh) * HD;
+      float* rv = rk + plane;
+#pragma unroll
+      for (int nt = 0; nt < HD / 8; ++nt) {
+        *reinterpret_cast<float2*>(rk + nt * 8 + 2 * t) = make_float2(dk_acc[nt][2 * half] * p.scale, dk_acc[nt][2 * half + 1] * p.scale);
+        *reinterpret_cast<float2*>(rv + nt * 8 + 2 * t) = make_float2(dv_acc[nt][2 * half], dv_acc[nt][2 * half + 1]);
+      }
+    }
+    return;
+  }
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int key = half ? kb : ka;
+    if (key >= p.Tc) continue;
+    __nv_bfloat16* rk = p.dk + ((int64_t)key * p.nkv + kvh) * HD;
+    __nv_bfloat16* rv = p.dv + ((int64_t)key * p.nkv + kvh) * HD;
 #pragma unroll
     for (int nt = 0; nt < HD / 8; ++nt) {
-      *reinterpret_cast<__nv_bfloat162*>(rk + nt * 8 + 2 * t) = __floats2bfloat162_rn(dk_acc[nt][0] * p.scale, dk_acc[nt][1] * p.scale);
-      *reinterpret_cast<__nv_bfloat162*>(rv + nt * 8 + 2 * t) = __floats2bfloat162_rn(dv_acc[nt][0], dv_acc[nt][1]);
+      *reinterpret_cast<__nv_bfloat162*>(rk + nt * 8 + 2 * t) =
+          __floats2bfloat162_rn(dk_acc[nt][2 * half] * p.scale, dk_acc[nt][2 * half + 1] * p.scale);
+      *reinterpret_cast<__nv_bfloat162*>(rv + nt * 8 + 2 * t) = __floats2bfloat162_rn(dv_acc[nt][2 * half], dv_acc[nt][2 * half + 1]);
     }
   }
-  if (kb < p.Tc) {
-    __nv_bfloat16* rk = p.dk + ((int64_t)kb * p.nkv + kvh) * HD;
-    __nv_bfloat16* rv = p.dv + ((int64_t)kb * p.nkv + kvh) * HD;
+}
+
+// Sum the per-query-head partials of a group in head order and round to bf16.
+// part: [group, 2, n] fp32 with n = Tc * nkv * HD (n % 8 == 0); dk, dv: [n] bf16.
+__global__ void __launch_bounds__(256)
+dkv_reduce_kernel(const float* __restrict__ part, int group, int64_t n, __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv) {
+  const int64_t nvec = n >> 3;
+  for (int64_t vi = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; vi < 2 * nvec; vi += (int64_t)gridDim.x * blockDim.x) {
+    const int which = vi >= nvec;
+    const int64_t off = (vi - which * nvec) << 3;
+    float acc[8];
 #pragma unroll
-    for (int nt = 0; nt < HD / 8; ++nt) {
-      *reinterpret_cast<__nv_bfloat162*>(rk + nt * 8 + 2 * t) = __floats2bfloat162_rn(dk_acc[nt][2] * p.scale, dk_acc[nt][3] * p.scale);
-      *reinterpret_cast<__nv_bfloat162*>(rv + nt * 8 + 2 * t) = __floats2bfloat162_rn(dv_acc[nt][2], dv_acc[nt][3]);
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int s = 0; s < group; ++s) {
+      const float4* src = reinterpret_cast<const float4*>(part + ((int64_t)s * 2 + which) * n + off);
+      const float4 a = src[0], b = src[1];
+      acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+      acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
     }
+    st8((which ? dv : dk) + off, pack8(acc));
   }
 }
 
@@ -728,8 +765,14 @@ static int launch_bwd_t(const AttnParams& p, int* tile_qmin, int* tile_qmax, cud
   dim3 grid_q((p.Tq + kBM - 1) / kBM, p.nh);
   attn_bwd_dq_kernel<HD><<<grid_q, kAttnThreads, bwd_smem<HD>(), stream>>>(p);
   kv_tile_range_kernel<<<(p.Tq + 255) / 256, 256, 0, stream>>>(p.lo, p.hi, p.Tq, p.Tc, tile_qmin, tile_qmax);
-  dim3 grid_kv(n_kv_tiles, p.nkv);
+  dim3 grid_kv(p.nh, n_kv_tiles);  // x = head: all heads of the heaviest tile are dispatched first
   attn_bwd_dkv_kernel<HD><<<grid_kv, kAttnThreads, bwd_smem<HD>(), stream>>>(p);
+  if (p.dkv_part != nullptr) {
+    const int64_t n = (int64_t)p.Tc * p.nkv * HD;
+    const int64_t blocks = (2 * (n >> 3) + 255) / 256;
+    count_launch(1);
+    dkv_reduce_kernel<<<(int)(blocks < 8 * kNumSM ? blocks : 8 * kNumSM), 256, 0, stream>>>(p.dkv_part, p.nh / p.nkv, n, p.dk, p.dv);
+  }
   return 0;
 }
 

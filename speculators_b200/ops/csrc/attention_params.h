@@ -31,6 +31,7 @@ struct AttnParams {
   float* dve;
   __nv_bfloat16* dk;     // [Tc, nkv, HD] contiguous
   __nv_bfloat16* dv;
+  float* dkv_part;       // [group, 2, Tc, nkv, HD] fp32 per-query-head partials of dK / dV (grouped-query attention only)
   const int* tile_qmin;  // [ceil(Tc / kBN)] first / one-past-last query row that can see the kv tile
   const int* tile_qmax;
 };

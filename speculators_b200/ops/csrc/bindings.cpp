@@ -423,6 +423,11 @@ std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> attn_bwd(
     dke = at::empty({0}, lse2.options());
     dve = at::empty({0}, lse2.options());
   }
+  Tensor dkv_part;
+  if (p.nh > p.nkv) {  // grouped queries: per-head fp32 partials, summed in head order afterwards
+    dkv_part = at::empty({p.nh / p.nkv, 2, k.size(0), k.size(1), hd}, lse2.options());
+    p.dkv_part = dkv_part.data_ptr<float>();
+  }
   const int n_tiles = (p.Tc + sb200::kAttnKeyTile - 1) / sb200::kAttnKeyTile;
   Tensor qmin = at::full({n_tiles}, 0x7fffffff, lo.options());
   Tensor qmax = at::zeros({n_tiles}, lo.options());

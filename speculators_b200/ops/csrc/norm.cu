@@ -61,6 +61,9 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 }
 
 // One CTA walks rows blockIdx.x, +gridDim.x, ... and keeps its dw partial in registers.
+// A row's x and dy stay in registers (packed bf16) between the reduction and the dx pass,
+// and the next row is fetched before the block-wide reduction of the current one, so the
+// loads of one row overlap the synchronisation of the previous row.
 template <int NV>
 __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
@@ -70,24 +73,49 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   __shared__ float scratch[33];
   const int nvec = H >> 3;
   float dwacc[NV][8];
+  bf16x8 wreg[NV];
 #pragma unroll
-  for (int i = 0; i < NV; ++i)
+  for (int i = 0; i < NV; ++i) {
+    const int v = threadIdx.x + i * kNormThreads;
+    if (v < nvec) wreg[i] = ld8(w + (v << 3));
 #pragma unroll
     for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
+  }
 
-  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
-    const float rstd = rstd_in[r];
+  constexpr bool kPrefetch = NV <= 4;  // wider rows would spill: fetch each row when it is due
+  constexpr int NB = kPrefetch ? NV : 1;
+  bf16x8 xa[NV], da[NV], xb[NB], db[NB];
+  auto fetch = [&](int r, bf16x8* xr_, bf16x8* dr_) {
     const __nv_bfloat16* xr = x + (int64_t)r * x_stride;
     const __nv_bfloat16* dyr = dy + (int64_t)r * dy_stride;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
+        xr_[i] = ld8(xr + (v << 3));
+        dr_[i] = ld8(dyr + (v << 3));
+      }
+    }
+  };
+  int r = blockIdx.x;
+  if (kPrefetch && r < rows) fetch(r, xa, da);
+  for (; r < rows; r += gridDim.x) {
+    if constexpr (kPrefetch) {
+      const int rn = r + gridDim.x;
+      if (rn < rows) fetch(rn, xb, db);
+    } else {
+      fetch(r, xa, da);
+    }
+    const float rstd = rstd_in[r];
     float dot = 0.f;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int v = threadIdx.x + i * kNormThreads;
       if (v < nvec) {
         float xv[8], dv[8], wv[8];
-        unpack8(ld8(xr + (v << 3)), xv);
-        unpack8(ld8(dyr + (v << 3)), dv);
-        unpack8(ld8(w + (v << 3)), wv);
+        unpack8(xa[i], xv);
+        unpack8(da[i], dv);
+        unpack8(wreg[i], wv);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const float xh = xv[j] * rstd;
@@ -98,15 +126,14 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
     }
     dot = block_sum(dot, scratch) / (float)H;
     __nv_bfloat16* dxr = dx + (int64_t)r * dx_stride;
-    // second pass re-reads the row (L1/L2 resident) instead of holding it in registers
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int v = threadIdx.x + i * kNormThreads;
       if (v < nvec) {
         float xv[8], dv[8], wv[8], o[8];
-        unpack8(ld8(xr + (v << 3)), xv);
-        unpack8(ld8(dyr + (v << 3)), dv);
-        unpack8(ld8(w + (v << 3)), wv);
+        unpack8(xa[i], xv);
+        unpack8(da[i], dv);
+        unpack8(wreg[i], wv);
         if (accumulate_dx) unpack8(ld8(dxr + (v << 3)), o);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -116,6 +143,13 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
         st8(dxr + (v << 3), pack8(o));
       }
     }
+    if constexpr (kPrefetch) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        xa[i] = xb[i];
+        da[i] = db[i];
+      }
+    }
   }
   if (dw_partial) {
     float* out = dw_partial + (int64_t)blockIdx.x * H;
@@ -123,29 +157,33 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
     for (int i = 0; i < NV; ++i) {
       const int v = threadIdx.x + i * kNormThreads;
       if (v < nvec) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) out[(v << 3) + j] = dwacc[i][j];
+        float4* o4 = reinterpret_cast<float4*>(out + (v << 3));
+        o4[0] = make_float4(dwacc[i][0], dwacc[i][1], dwacc[i][2], dwacc[i][3]);
+        o4[1] = make_float4(dwacc[i][4], dwacc[i][5], dwacc[i][6], dwacc[i][7]);
       }
     }
   }
 }
 
-// dw[c] (+)= sum_p partial[p, c].  Block = 32 columns x 8 row-groups; the row-groups
-// split P and meet in shared memory, so each column is summed by 8 threads in a
-// fixed order (deterministic) and a launch has H/32 CTAs instead of H/256.
-__global__ void colsum_kernel(const float* __restrict__ partial, float* __restrict__ dw, int P,
-                              int H, int accumulate) {
-  __shared__ float tile[8][33];
+// dw[c] (+)= sum_p partial[p, c].  Block = 32 columns x 32 row-groups; the row-groups
+// split P (a handful of independent loads per thread) and meet in shared memory, so
+// each column is summed in a fixed order (deterministic) by H/32 CTAs.
+constexpr int kColsumGroups = 32;
+__global__ void __launch_bounds__(32 * kColsumGroups)
+colsum_kernel(const float* __restrict__ partial, float* __restrict__ dw, int P, int H, int accumulate) {
+  __shared__ float tile[kColsumGroups][33];
   const int c = blockIdx.x * 32 + threadIdx.x;
   float s = 0.f;
-  if (c < H)
-    for (int p = threadIdx.y; p < P; p += 8) s += partial[(int64_t)p * H + c];
+  if (c < H) {
+#pragma unroll 4
+    for (int p = threadIdx.y; p < P; p += kColsumGroups) s += partial[(int64_t)p * H + c];
+  }
   tile[threadIdx.y][threadIdx.x] = s;
   __syncthreads();
   if (threadIdx.y == 0 && c < H) {
     float t = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) t += tile[i][threadIdx.x];
+    for (int i = 0; i < kColsumGroups; ++i) t += tile[i][threadIdx.x];
     dw[c] = accumulate ? dw[c] + t : t;
   }
 }
@@ -188,7 +226,7 @@ void launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const floa
 #undef SB200_BWD
   if (dw_partial && dw) count_launch(1);
   if (dw_partial && dw)
-    colsum_kernel<<<(H + 31) / 32, dim3(32, 8), 0, stream>>>(dw_partial, dw, grid, H, accumulate_dw);
+    colsum_kernel<<<(H + 31) / 32, dim3(32, kColsumGroups), 0, stream>>>(dw_partial, dw, grid, H, accumulate_dw);
 }
 
 }  // namespace sb200

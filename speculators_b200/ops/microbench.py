@@ -111,6 +111,17 @@ def op_rmsnorm(a):
     return _no_grad(lambda: ops.rms_norm(x, w, 1e-5)), 0.0, 2.0 * 2 * T * H, dict
 
 
+def op_rmsnorm_bwd(a):
+    from speculators_b200 import ops
+
+    T, H = a.t, a.hidden
+    x = _bf16(T, H).requires_grad_()
+    w = torch.ones(H, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y = ops.rms_norm(x, w, 1e-5)
+    gy = torch.randn_like(y)
+    return (lambda: y.backward(gy, retain_graph=True)), 0.0, 2.0 * 3 * T * H, dict
+
+
 def op_adamw(a):
     from speculators_b200 import ops
 
@@ -125,7 +136,7 @@ def op_adamw(a):
 
 
 OPS = {"gemm": op_gemm, "gemm_cublas": op_gemm_cublas, "attn_fwd": op_attn_fwd, "attn_bwd": op_attn_bwd, "loss": op_loss,
-       "rmsnorm": op_rmsnorm, "adamw": op_adamw}
+       "rmsnorm": op_rmsnorm, "rmsnorm_bwd": op_rmsnorm_bwd, "adamw": op_adamw}
 
 
 def main(argv: list[str] | None = None) -> int:
