@@ -153,8 +153,12 @@ class Eagle3DraftModel(DraftVocabMixin, SpeculatorModel):
         ttt_steps: int = 3,
         ttt_step_loss_decay: float = 1.0,
         loss_config: LossConfig | None = None,
+        return_draft_tokens: bool = True,
         **_,
     ):
+        """``return_draft_tokens=False`` (what the trainer passes) skips the per-pass
+        argmax over the full ``[T, V]`` logits; the first element of the result is
+        then an empty list."""
         device = hidden_states.device
         T = hidden_states.shape[1]
         dtype = self.fc.weight.dtype
@@ -210,7 +214,8 @@ class Eagle3DraftModel(DraftVocabMixin, SpeculatorModel):
                 loss = loss + s_loss
                 metrics.update(s_metrics)
 
-            draft_tokens.append(torch.argmax(logits.detach(), dim=-1).unsqueeze(0))
+            if return_draft_tokens:
+                draft_tokens.append(torch.argmax(logits.detach(), dim=-1).unsqueeze(0))
             # teacher forcing: ground-truth ids shifted left by 1 + step, zero padded
             ids = torch.cat([original_ids[1 + step :], original_ids.new_zeros(min(1 + step, T))])[:T]
             positions = positions + 1
@@ -255,5 +260,6 @@ class Eagle3DraftModel(DraftVocabMixin, SpeculatorModel):
             "ttt_steps": kwargs["ttt_steps"],
             "ttt_step_loss_decay": kwargs["ttt_step_loss_decay"],
             "loss_config": loss_config,
+            "return_draft_tokens": False,  # the trainer only consumes loss and metrics
         }
         return dict(call), dict(call)

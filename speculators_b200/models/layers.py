@@ -239,8 +239,7 @@ class Attention(nn.Module):
             q, k = qk[:, :nq], qk[:, nq:]
             v = qkv[:, nq + nk :]
         else:
-            qkv = ops.rope_(qkv, positions, rotary.cos, rotary.sin, self.nh + self.nkv, self.hd, self.rot)
-            q, k, v = qkv[:, :nq], qkv[:, nq : nq + nk], qkv[:, nq + nk :]
+            q, k, v = ops.rope_split(qkv, positions, rotary.cos, rotary.sin, self.nh + self.nkv, self.hd, self.rot, nq, nk)
         return q.view(T, self.nh, self.hd), k.view(T, self.nkv, self.hd), v.view(T, self.nkv, self.hd)
 
     def forward(self, x, positions, rotary, spec: AttnSpec, past: list | None = None, ctx_len: int | None = None,

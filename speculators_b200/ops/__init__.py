@@ -33,6 +33,7 @@ __all__ = [
     "native",
     "rms_norm",
     "rope_",
+    "rope_split",
     "sum_of_squares",
     "swiglu",
     "token_cross_entropy",
@@ -265,7 +266,7 @@ class _RopeFn(torch.autograd.Function):
     def backward(ctx, dx):
         positions, cos_t, sin_t = ctx.saved_tensors
         heads, hd, rot = ctx.cfg
-        dx = dx.clone() if not dx.is_contiguous() else dx.clone()
+        dx = dx.clone()  # the incoming gradient may be shared with other consumers
         native().rope_(dx, positions, cos_t, sin_t, heads, hd, rot, -1.0)
         return dx, None, None, None, None, None, None
 
@@ -277,6 +278,41 @@ def rope_(x, positions, cos_t, sin_t, heads: int, hd: int, rot: int):
     if _use_native(x):
         return _RopeFn.apply(x, positions, cos_t, sin_t, heads, hd, rot)
     return _rope_ref(x, positions, cos_t, sin_t, heads, hd, rot, 1.0)
+
+
+class _RopeSplitFn(torch.autograd.Function):
+    """Rotate the q|k heads of a fused projection buffer in place and hand out the
+    q / k / v column blocks as views.  Backward gathers the three gradients into one
+    fresh buffer (a single concatenation instead of three zero-filled slice
+    gradients and their sums) and un-rotates it in place."""
+
+    @staticmethod
+    def forward(ctx, qkv, positions, cos_t, sin_t, heads, hd, rot, nq, nk):
+        ctx.save_for_backward(positions, cos_t, sin_t)
+        ctx.cfg = (heads, hd, rot)
+        qkv = qkv.detach()
+        native().rope_(qkv, positions, cos_t, sin_t, heads, hd, rot, 1.0)
+        q, k, v = qkv[:, :nq], qkv[:, nq : nq + nk], qkv[:, nq + nk :]
+        return q, k, v
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        positions, cos_t, sin_t = ctx.saved_tensors
+        heads, hd, rot = ctx.cfg
+        d = torch.cat([dq, dk, dv], dim=-1)
+        native().rope_(d, positions, cos_t, sin_t, heads, hd, rot, -1.0)
+        return d, None, None, None, None, None, None, None, None
+
+
+def rope_split(qkv, positions, cos_t, sin_t, heads: int, hd: int, rot: int, nq: int, nk: int):
+    """``rope_`` on the first ``heads`` heads of ``qkv`` ([T, nq + nk + nv]) followed by
+    the split into ``(q [T, nq], k [T, nk], v [T, rest])``.  On CUDA the buffer is
+    rotated in place and the results are views of it: the caller must own ``qkv``
+    (a fresh projection output) and must not modify the views in place."""
+    if _use_native(qkv) and qkv.requires_grad and torch.is_grad_enabled():
+        return _RopeSplitFn.apply(qkv, positions, cos_t, sin_t, heads, hd, rot, nq, nk)
+    out = rope_(qkv, positions, cos_t, sin_t, heads, hd, rot)
+    return out[:, :nq], out[:, nq : nq + nk], out[:, nq + nk :]
 
 
 # --------------------------------------------------------------------------- losses

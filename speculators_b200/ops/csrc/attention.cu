@@ -506,16 +506,38 @@ attn_bwd_dq_kernel(const AttnParams p) {
   }
 }
 
-// For every kv tile: the range of query rows whose interval touches it.
-__global__ void kv_tile_range_kernel(const int* __restrict__ lo, const int* __restrict__ hi, int Tq,
-                                     int Tc, int* __restrict__ qmin, int* __restrict__ qmax) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= Tq) return;
-  const int l = lo[i], hgh = min(hi[i], Tc);
-  if (hgh <= l || l < 0) return;
-  for (int j = l / kBN; j <= (hgh - 1) / kBN; ++j) {
-    atomicMin(qmin + j, i);
-    atomicMax(qmax + j, i + 1);
+// For every kv tile: the range of query rows whose interval touches it.  One CTA per
+// tile scans all query rows (coalesced) and reduces min / max in the block.
+__global__ void __launch_bounds__(256)
+kv_tile_range_kernel(const int* __restrict__ lo, const int* __restrict__ hi, int Tq,
+                     int Tc, int* __restrict__ qmin, int* __restrict__ qmax) {
+  __shared__ int smin[8], smax[8];
+  const int k0 = blockIdx.x * kBN, k1 = k0 + kBN;
+  int mn = 0x7fffffff, mx = 0;
+  for (int i = threadIdx.x; i < Tq; i += blockDim.x) {
+    const int l = lo[i], h = min(hi[i], Tc);
+    if (l >= 0 && h > l && l < k1 && h > k0) {
+      mn = min(mn, i);
+      mx = max(mx, i + 1);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    mn = min(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+  if ((threadIdx.x & 31) == 0) {
+    smin[threadIdx.x >> 5] = mn;
+    smax[threadIdx.x >> 5] = mx;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) {
+      mn = min(mn, smin[w]);
+      mx = max(mx, smax[w]);
+    }
+    qmin[blockIdx.x] = mn;
+    qmax[blockIdx.x] = mx;
   }
 }
 
@@ -764,7 +786,7 @@ static int launch_bwd_t(const AttnParams& p, int* tile_qmin, int* tile_qmax, cud
   count_launch(3);
   dim3 grid_q((p.Tq + kBM - 1) / kBM, p.nh);
   attn_bwd_dq_kernel<HD><<<grid_q, kAttnThreads, bwd_smem<HD>(), stream>>>(p);
-  kv_tile_range_kernel<<<(p.Tq + 255) / 256, 256, 0, stream>>>(p.lo, p.hi, p.Tq, p.Tc, tile_qmin, tile_qmax);
+  kv_tile_range_kernel<<<n_kv_tiles, 256, 0, stream>>>(p.lo, p.hi, p.Tq, p.Tc, tile_qmin, tile_qmax);
   dim3 grid_kv(p.nh, n_kv_tiles);  // x = head: all heads of the heaviest tile are dispatched first
   attn_bwd_dkv_kernel<HD><<<grid_kv, kAttnThreads, bwd_smem<HD>(), stream>>>(p);
   if (p.dkv_part != nullptr) {
@@ -783,7 +805,7 @@ int launch_attn_fwd(const AttnParams& p, int hd, cudaStream_t stream) {
   return -1;
 }
 
-// tile_qmin must be pre-filled with INT_MAX and tile_qmax with 0 by the caller.
+// tile_qmin / tile_qmax: scratch, one int per 64-key tile (fully written here).
 int launch_attn_bwd(const AttnParams& p, int hd, int* tile_qmin, int* tile_qmax, cudaStream_t stream) {
   if (p.Tq <= 0) return 0;
   if (hd == 64) return launch_bwd_t<64>(p, tile_qmin, tile_qmax, stream);

@@ -37,7 +37,7 @@ struct AttnParams {
 };
 
 int launch_attn_fwd(const AttnParams& p, int hd, cudaStream_t stream);
-// tile_qmin must hold INT_MAX and tile_qmax 0 in every entry (one per 64-key tile).
+// tile_qmin / tile_qmax: scratch of one int per 64-key tile, fully written by the launch.
 int launch_attn_bwd(const AttnParams& p, int hd, int* tile_qmin, int* tile_qmax, cudaStream_t stream);
 constexpr int kAttnKeyTile = 64;
 

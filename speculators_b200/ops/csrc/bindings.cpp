@@ -429,8 +429,8 @@ std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> attn_bwd(
     p.dkv_part = dkv_part.data_ptr<float>();
   }
   const int n_tiles = (p.Tc + sb200::kAttnKeyTile - 1) / sb200::kAttnKeyTile;
-  Tensor qmin = at::full({n_tiles}, 0x7fffffff, lo.options());
-  Tensor qmax = at::zeros({n_tiles}, lo.options());
+  Tensor qmin = at::empty({n_tiles}, lo.options());
+  Tensor qmax = at::empty({n_tiles}, lo.options());
   p.out = (__nv_bfloat16*)out.data_ptr();
   p.o_rs = out.stride(0);
   p.lse2 = lse2.data_ptr<float>();

@@ -84,6 +84,43 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const int64_t* __rest
   }
 }
 
+// Same rotation, eight channel pairs per thread (16-byte accesses); needs rot/2 % 8 == 0
+// and 16-byte aligned rows/heads (row_stride % 8 == 0, hd % 8 == 0, aligned base).
+__global__ void rope_vec8_kernel(__nv_bfloat16* __restrict__ x, const int64_t* __restrict__ positions,
+                                 const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                 int64_t tokens, int heads, int hd, int rot, int64_t row_stride,
+                                 int64_t max_pos, float sign) {
+  const int half = rot >> 1;
+  const int hv = half >> 3;
+  const int64_t total = tokens * heads * hv;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int i = (int)(idx % hv) << 3;
+    const int64_t th = idx / hv;
+    const int h = (int)(th % heads);
+    const int64_t t = th / heads;
+    int64_t pos = positions[t];
+    pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+    const float4* c4 = reinterpret_cast<const float4*>(cos_t + pos * half + i);
+    const float4* s4 = reinterpret_cast<const float4*>(sin_t + pos * half + i);
+    const float4 ca = c4[0], cb = c4[1], sa = s4[0], sb = s4[1];
+    const float c[8] = {ca.x, ca.y, ca.z, ca.w, cb.x, cb.y, cb.z, cb.w};
+    const float sn[8] = {sa.x, sa.y, sa.z, sa.w, sb.x, sb.y, sb.z, sb.w};
+    __nv_bfloat16* p = x + t * row_stride + (int64_t)h * hd + i;
+    float x1[8], x2[8], y1[8], y2[8];
+    unpack8(ld8(p), x1);
+    unpack8(ld8(p + half), x2);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float sj = sign * sn[j];
+      y1[j] = x1[j] * c[j] - x2[j] * sj;
+      y2[j] = x2[j] * c[j] + x1[j] * sj;
+    }
+    st8(p, pack8(y1));
+    st8(p + half, pack8(y2));
+  }
+}
+
 static inline int grid_for(int64_t total, int threads) {
   int64_t g = (total + threads - 1) / threads;
   const int64_t cap = (int64_t)kNumSM * 16;
@@ -108,7 +145,15 @@ void launch_rope(void* x, const int64_t* positions, const float* cos_t, const fl
                  float sign, cudaStream_t stream) {
   if (tokens <= 0) return;
   count_launch(1);
-  rope_kernel<<<grid_for(tokens * heads * (rot >> 1), 256), 256, 0, stream>>>(
+  const int half = rot >> 1;
+  const bool vec = (half % 8 == 0) && (hd % 8 == 0) && (row_stride % 8 == 0) && ((uintptr_t)x % 16 == 0) &&
+                   ((uintptr_t)cos_t % 16 == 0) && ((uintptr_t)sin_t % 16 == 0);
+  if (vec) {
+    rope_vec8_kernel<<<grid_for(tokens * heads * (half >> 3), 256), 256, 0, stream>>>(
+        (__nv_bfloat16*)x, positions, cos_t, sin_t, tokens, heads, hd, rot, row_stride, max_pos, sign);
+    return;
+  }
+  rope_kernel<<<grid_for(tokens * heads * half, 256), 256, 0, stream>>>(
       (__nv_bfloat16*)x, positions, cos_t, sin_t, tokens, heads, hd, rot, row_stride, max_pos, sign);
 }
 

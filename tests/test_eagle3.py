@@ -56,8 +56,10 @@ def test_shift_batch():
 def test_forward_backward_metrics_and_frozen_params(tiny_verifier_dir, tiny_vocab_maps):
     model = make_tiny_eagle3(tiny_verifier_dir, tiny_vocab_maps, num_layers=2)
     kwargs, _ = sb.Eagle3DraftModel.get_trainer_kwargs(loss_fn="kl_div", ttt_steps=3, ttt_step_loss_decay=0.8)
-    toks, loss, metrics = model(**make_tiny_batch(), **kwargs)
+    assert kwargs["return_draft_tokens"] is False  # the trainer path skips the argmax over [T, V]
+    toks, loss, metrics = model(**make_tiny_batch(), **{**kwargs, "return_draft_tokens": True})
     assert len(toks) == 3 and toks[0].shape == (1, 40)
+    assert model(**make_tiny_batch(), **kwargs)[0] == []
     for s in range(3):
         for key in ("loss", "full_acc", "cond_acc"):
             assert f"{key}_{s}_sum" in metrics and f"{key}_{s}_total" in metrics

@@ -86,6 +86,33 @@ def test_rope_matches_reference_and_inverts(rot):
     _close(y, x, atol=3e-2)
 
 
+@pytest.mark.parametrize("hd,rot", [(128, 128), (64, 64), (64, 24)])
+def test_rope_split_matches_separate_ops(hd, rot):
+    """The fused rotate+split (vectorised kernel when rot/2 % 8 == 0, one concatenated
+    gradient) against the fp32 rotation followed by plain slicing, values and grads."""
+    torch.manual_seed(1)
+    T, nh, nkv = 50, 4, 2
+    nq, nk = nh * hd, nkv * hd
+    base = torch.randn(T, nq + 2 * nk, device=DEV)
+    pos = torch.randint(0, 300, (T,), device=DEV)
+    ang = torch.outer(torch.arange(512, dtype=torch.float64), 1.0 / (10000.0 ** (torch.arange(0, rot, 2, dtype=torch.float64) / rot)))
+    cos, sin = ang.cos().float().to(DEV), ang.sin().float().to(DEV)
+    wq, wk, wv = (torch.randn(T, n, device=DEV) for n in (nq, nk, nk))
+
+    x = base.to(torch.bfloat16).requires_grad_()
+    q, k, v = ops.rope_split(x * 1.0, pos, cos, sin, nh + nkv, hd, rot, nq, nk)
+    ((q.float() * wq).sum() + (k.float() * wk).sum() + 2 * (k.float() * wk).sum() + (v.float() * wv).sum()).backward()
+
+    xr = base.to(torch.bfloat16).float().requires_grad_()
+    yr = ops._rope_ref(xr, pos, cos, sin, nh + nkv, hd, rot, 1.0)
+    qr, kr, vr = yr[:, :nq], yr[:, nq:nq + nk], yr[:, nq + nk:]
+    ((qr * wq).sum() + 3 * (kr * wk).sum() + (vr * wv).sum()).backward()
+    _close(q, qr, atol=3e-2)
+    _close(k, kr, atol=3e-2)
+    assert torch.equal(v.float(), vr)
+    _close(x.grad, xr.grad, atol=5e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("op", ["kl_div", "rkl", "jsd", "ce", "tv"])
 @pytest.mark.parametrize("T,V,shift", [(33, 1000, 0), (64, 32000, 2), (5, 151936, 1), (17, 1003, 0)])
 def test_row_loss_fwd_bwd(op, T, V, shift):
