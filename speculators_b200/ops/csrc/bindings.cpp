@@ -23,7 +23,7 @@ int launch_loss_bwd(int, const void*, const void*, const float*, const float*, v
                     int64_t, int64_t, int64_t, int, cudaStream_t);
 int64_t launch_count();
 int launch_gemm_tn_tcgen05(const void*, const void*, void*, const void*, int, int, int, int64_t, int64_t, int64_t, int64_t, int,
-                           int*, cudaStream_t);
+                           int*, int, cudaStream_t);
 int sumsq_num_partials();
 int peer_malloc(int64_t, void**);
 int peer_free(void*);
@@ -312,7 +312,9 @@ void fused_sharded_adamw(int64_t world, int64_t rank, int64_t shard, const Tenso
 // ---- tcgen05 GEMM ------------------------------------------------------------------------
 // out[M,N] = a[M,K] @ b[N,K]^T; epilogue 0 = store, 1 = out += result, 2 = result + residual.
 // `status` (int32[1], device) receives a non-zero code if a bounded wait in the kernel ran out.
-void gemm_tn(const Tensor& a, const Tensor& b, Tensor out, const c10::optional<Tensor>& residual, int64_t epilogue, Tensor status) {
+// variant: 0 = choose, 1 = one CTA per 128x256 tile, 2 = CTA pairs on 256x256 tiles.
+void gemm_tn_variant(const Tensor& a, const Tensor& b, Tensor out, const c10::optional<Tensor>& residual, int64_t epilogue, Tensor status,
+                     int64_t variant) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && out.is_cuda() && status.is_cuda());
   TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16);
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && out.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && out.stride(1) == 1);
@@ -330,8 +332,12 @@ void gemm_tn(const Tensor& a, const Tensor& b, Tensor out, const c10::optional<T
   c10::cuda::CUDAGuard guard(a.device());
   const int rc = sb200::launch_gemm_tn_tcgen05(a.data_ptr(), b.data_ptr(), out.data_ptr(), res, (int)a.size(0), (int)b.size(0),
                                                (int)a.size(1), a.stride(0), b.stride(0), out.stride(0), ldr, (int)epilogue,
-                                               status.data_ptr<int>(), cur_stream());
+                                               status.data_ptr<int>(), (int)variant, cur_stream());
   TORCH_CHECK(rc == 0, "gemm_tn launch failed (", rc, ")");
+}
+
+void gemm_tn(const Tensor& a, const Tensor& b, Tensor out, const c10::optional<Tensor>& residual, int64_t epilogue, Tensor status) {
+  gemm_tn_variant(a, b, out, residual, epilogue, status, 0);
 }
 
 // ---- masked attention ------------------------------------------------------------------
@@ -472,6 +478,7 @@ TORCH_LIBRARY(sb200, m) {
   m.def("fused_optim_ctl_words", &fused_optim_ctl_words);
   m.def("fused_sharded_adamw", &fused_sharded_adamw);
   m.def("gemm_tn", &gemm_tn);
+  m.def("gemm_tn_variant", &gemm_tn_variant);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);
 }

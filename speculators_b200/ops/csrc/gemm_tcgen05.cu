@@ -15,6 +15,14 @@
 // Tiles are walked n-major so that CTAs running at the same time share B (weight) tiles in
 // L2.  Ragged M / N / K are handled by TMA zero fill and masked stores.
 //
+// Two kernels share this structure.  gemm_tn_kernel works on 128x256 tiles, one CTA per
+// tile.  gemm_tn_2cta_kernel pairs two SMs (a cluster of two CTAs, tcgen05 cta_group::2)
+// on a 256x256 tile: each CTA stages its own 128 rows of A and 128 of the tile's 256 rows
+// of B (32 KB per stage instead of 48 KB, six stages instead of four), the even CTA's
+// elected thread issues M=256 MMAs that read both CTAs' shared memory and write both
+// CTAs' TMEM, and completion is multicast to the barriers of both CTAs.  Halving the B
+// traffic per SM is what the L2-to-SM path needs to keep the tensor pipe fed.
+//
 // Every wait is bounded: a thread that exhausts its poll budget records a code in the
 // caller's status word and leaves its loop; the other roles then run out of budget (or
 // see the status word) too, the CTA meets at the final barrier, frees its TMEM and
@@ -115,6 +123,48 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+// ---- cluster / cta_group::2 helpers ------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of the same shared variable in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load whose completion bytes are counted on a barrier that may live in the peer CTA
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrive on the barrier at the same shared-memory offset in both CTAs of the pair once all
+// MMAs issued so far have retired
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(mask) : "memory");
+}
+
 struct Params {
   __nv_bfloat16* c;
   const __nv_bfloat16* residual;
@@ -123,6 +173,53 @@ struct Params {
   int epilogue;
   int* status;
 };
+
+// Epilogue of one thread: TMEM lane `taddr` (its 256 fp32 columns) -> row `row`, columns
+// n0 .. n0+255 of C, with the configured epilogue.
+__device__ __forceinline__ void store_accumulator(const Params& p, uint32_t taddr, int row, int n0) {
+  __nv_bfloat16* crow = p.c + (int64_t)row * p.ldc + n0;
+  const __nv_bfloat16* rrow = p.residual ? p.residual + (int64_t)row * p.ldr + n0 : nullptr;
+  const bool vec_ok = ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0) &&
+                      (p.epilogue != kAddResidual || (((p.ldr & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0)));
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld32(taddr + c * 32, r);
+    tmem_ld_wait();
+    if (row < p.M) {
+      const int col0 = n0 + c * 32;
+      if (vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          float f[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]);
+          if (p.epilogue == kAccumulate) {
+            float o[8];
+            unpack8(ld8(crow + c * 32 + v * 8), o);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] += o[j];
+          } else if (p.epilogue == kAddResidual) {
+            float o[8];
+            unpack8(ld8(rrow + c * 32 + v * 8), o);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] += o[j];
+          }
+          st8(crow + c * 32 + v * 8, pack8(f));
+        }
+      } else {
+        for (int j = 0; j < 32; ++j) {
+          if (col0 + j < p.N) {
+            float f = __uint_as_float(r[j]);
+            if (p.epilogue == kAccumulate) f += __bfloat162float(crow[c * 32 + j]);
+            else if (p.epilogue == kAddResidual) f += __bfloat162float(rrow[c * 32 + j]);
+            crow[c * 32 + j] = __float2bfloat16(f);
+          }
+        }
+      }
+    }
+  }
+}
 
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
@@ -215,50 +312,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       fence_after_sync();
-      const int row = m0 + quarter * 32 + lane;
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
-      __nv_bfloat16* crow = p.c + (int64_t)row * p.ldc + n0;
-      const __nv_bfloat16* rrow = p.residual ? p.residual + (int64_t)row * p.ldr + n0 : nullptr;
-      const bool vec_ok = ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0) &&
-                          (p.epilogue != kAddResidual || (((p.ldr & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0)));
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(taddr + c * 32, r);
-        tmem_ld_wait();
-        if (row < p.M) {
-          const int col0 = n0 + c * 32;
-          if (vec_ok && col0 + 32 <= p.N) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              float f[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]);
-              if (p.epilogue == kAccumulate) {
-                float o[8];
-                unpack8(ld8(crow + c * 32 + v * 8), o);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) f[j] += o[j];
-              } else if (p.epilogue == kAddResidual) {
-                float o[8];
-                unpack8(ld8(rrow + c * 32 + v * 8), o);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) f[j] += o[j];
-              }
-              st8(crow + c * 32 + v * 8, pack8(f));
-            }
-          } else {
-            for (int j = 0; j < 32; ++j) {
-              if (col0 + j < p.N) {
-                float f = __uint_as_float(r[j]);
-                if (p.epilogue == kAccumulate) f += __bfloat162float(crow[c * 32 + j]);
-                else if (p.epilogue == kAddResidual) f += __bfloat162float(rrow[c * 32 + j]);
-                crow[c * 32 + j] = __float2bfloat16(f);
-              }
-            }
-          }
-        }
-      }
+      store_accumulator(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, m0 + quarter * 32 + lane, n0);
       fence_before_sync();
       mbar_arrive(smem_addr(&bar_acc_empty[acc]));
     }
@@ -272,6 +326,128 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncwarp();
     fence_after_sync();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ---- 256x256 tiles on CTA pairs ----------------------------------------------------------
+constexpr int P_STAGES = 6;
+constexpr int P_HALF = 128;                                    // rows of A and of B staged per CTA
+constexpr int P_A_BYTES = P_HALF * BK * 2, P_B_BYTES = P_HALF * BK * 2, P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
+constexpr int P_TILE_M = 2 * P_HALF, P_TILE_N = 2 * P_HALF;
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ __align__(8) uint64_t bar_full[P_STAGES], bar_empty[P_STAGES], bar_acc_full[2], bar_acc_empty[2];
+  __shared__ uint32_t tmem_base_slot;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int tiles_m = (p.M + P_TILE_M - 1) / P_TILE_M, tiles_n = (p.N + P_TILE_N - 1) / P_TILE_N;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; ++s) {
+      mbar_init(smem_addr(&bar_full[s]), 1);   // the leader's expect_tx arrival; bytes come from both CTAs' copies
+      mbar_init(smem_addr(&bar_empty[s]), 1);  // one multicast commit per use
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_addr(&bar_acc_full[a]), 1);
+      mbar_init(smem_addr(&bar_acc_empty[a]), 256);  // the epilogue threads of both CTAs (used in the leader only)
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {  // collective over the pair: the same warp of both CTAs
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  fence_before_sync();
+  cluster_sync_all();  // barriers of both CTAs are initialised before any remote signal
+  fence_after_sync();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const int m0 = (tile % tiles_m) * P_TILE_M + (int)rank * P_HALF;
+        const int nb0 = (tile / tiles_m) * P_TILE_N + (int)rank * P_HALF;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!(ok = mbar_wait(smem_addr(&bar_empty[stage]), phase ^ 1, p.status, kTimeoutProducer))) break;
+          const uint32_t full_local = smem_addr(&bar_full[stage]);
+          if (leader) mbar_expect_tx(full_local, 2 * P_STAGE_BYTES);
+          const uint32_t full_leader = map_to_cta(full_local, 0);
+          const uint32_t sa = smem_addr(smem + stage * P_STAGE_BYTES);
+          tma_load_2d_pair(sa, &map_a, full_leader, kb * BK, m0);
+          tma_load_2d_pair(sa + P_A_BYTES, &map_b, full_leader, kb * BK, nb0);
+          if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      // tail: stay until the MMAs that read this CTA's last slots have retired (their
+      // completion is signalled into this CTA's shared memory)
+      for (int s = 0; s < P_STAGES && ok; ++s) {
+        ok = mbar_wait(smem_addr(&bar_empty[stage]), phase ^ 1, p.status, kTimeoutProducer);
+        if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = instr_desc_bf16(P_TILE_M, P_TILE_N);
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      int local = 0;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
+        const int acc = local & 1;
+        if (!(ok = mbar_wait(smem_addr(&bar_acc_empty[acc]), ((local >> 1) & 1) ^ 1, p.status, kTimeoutMma))) break;
+        fence_after_sync();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!(ok = mbar_wait(smem_addr(&bar_full[stage]), phase, p.status, kTimeoutMma))) break;
+          fence_after_sync();
+          const uint32_t sa = smem_addr(smem + stage * P_STAGE_BYTES);
+          const uint64_t adesc = smem_desc_kmajor_sw128(sa), bdesc = smem_desc_kmajor_sw128(sa + P_A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) umma_bf16_pair(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+          umma_commit_pair(smem_addr(&bar_empty[stage]));  // frees the slot in both CTAs
+          if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit_pair(smem_addr(&bar_acc_full[acc]));  // wakes the epilogues of both CTAs
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int quarter = warp & 3;
+    const uint32_t acc_empty_leader[2] = {map_to_cta(smem_addr(&bar_acc_empty[0]), 0), map_to_cta(smem_addr(&bar_acc_empty[1]), 0)};
+    bool ok = true;
+    int local = 0;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
+      const int acc = local & 1;
+      const int m0 = (tile % tiles_m) * P_TILE_M + (int)rank * P_HALF, n0 = (tile / tiles_m) * P_TILE_N;
+      ok = mbar_wait(smem_addr(&bar_acc_full[acc]), (local >> 1) & 1, p.status, kTimeoutEpilogue);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      fence_after_sync();
+      store_accumulator(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, m0 + quarter * 32 + lane, n0);
+      fence_before_sync();
+      mbar_arrive_cluster(acc_empty_leader[acc]);
+    }
+  }
+
+  // Both CTAs stay until the pair is done: the peer's copies signal the leader's barriers,
+  // the leader's MMAs read the peer's shared memory and write its TMEM.
+  fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    fence_after_sync();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -312,16 +488,33 @@ static int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t co
 // C[M,N] = A[M,K] * B[N,K]^T with epilogue (0 store, 1 C += result, 2 result + residual).
 // lda / ldb / ldc / ldr in elements; A, B rows must be 16-byte aligned (ld multiple of 8).
 // `status` is a device int the kernel writes a non-zero code to if a bounded wait ran out.
+// variant: 0 = choose (CTA pairs when M > 128), 1 = one CTA per 128x256 tile, 2 = CTA pairs.
 int launch_gemm_tn_tcgen05(const void* a, const void* b, void* c, const void* residual, int M, int N, int K, int64_t lda,
-                           int64_t ldb, int64_t ldc, int64_t ldr, int epilogue, int* status, cudaStream_t stream) {
+                           int64_t ldb, int64_t ldc, int64_t ldr, int epilogue, int* status, int variant, cudaStream_t stream) {
   using namespace tc;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda & 7) || (ldb & 7) || (reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15)) return -1;
+  const bool pairs = variant == 2 || (variant == 0 && M > BM);
   CUtensorMap map_a, map_b;
   int rc = make_map(&map_a, a, M, K, lda, BM);
   if (rc) return rc;
-  rc = make_map(&map_b, b, N, K, ldb, BN);
+  rc = make_map(&map_b, b, N, K, ldb, pairs ? P_HALF : BN);
   if (rc) return rc;
+  Params p{(__nv_bfloat16*)c, (const __nv_bfloat16*)residual, M, N, K, ldc, ldr, epilogue, status};
+  count_launch(1);
+  if (pairs) {
+    static bool configured2 = false;
+    constexpr int smem2 = P_STAGES * P_STAGE_BYTES + 1024;
+    if (!configured2) {
+      if (cudaFuncSetAttribute(gemm_tn_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) != cudaSuccess) return -2;
+      configured2 = true;
+    }
+    const int tiles = ((M + P_TILE_M - 1) / P_TILE_M) * ((N + P_TILE_N - 1) / P_TILE_N);
+    const int max_pairs = kNumSM / 2;
+    const int grid = 2 * (tiles < max_pairs ? tiles : max_pairs);
+    gemm_tn_2cta_kernel<<<grid, THREADS, smem2, stream>>>(map_a, map_b, p);
+    return cudaGetLastError() == cudaSuccess ? 0 : -3;
+  }
   static bool configured = false;
   constexpr int smem_bytes = STAGES * STAGE_BYTES + 1024;
   if (!configured) {
@@ -330,8 +523,6 @@ int launch_gemm_tn_tcgen05(const void* a, const void* b, void* c, const void* re
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < kNumSM ? tiles : kNumSM;
-  Params p{(__nv_bfloat16*)c, (const __nv_bfloat16*)residual, M, N, K, ldc, ldr, epilogue, status};
-  count_launch(1);
   gemm_tn_kernel<<<grid, THREADS, smem_bytes, stream>>>(map_a, map_b, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

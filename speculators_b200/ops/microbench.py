@@ -54,7 +54,7 @@ def op_gemm(a):
     M, N, K = a.m, a.n, a.k
     x, w, out = _bf16(M, K), _bf16(N, K, scale=0.05), torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    fn = lambda: nat.gemm_tn(x, w, out, None, 0, status)  # noqa: E731
+    fn = lambda: nat.gemm_tn_variant(x, w, out, None, 0, status, a.variant)  # noqa: E731
     return fn, 2.0 * M * N * K, 2.0 * (M * K + N * K + M * N), lambda: {"status": int(status.item())}
 
 
@@ -146,6 +146,7 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true", help="do not rewrite an L2-sized buffer between iterations")
     ap.add_argument("--peaks", default=None, help="JSON file with measured hbm_gbs and bf16_tflops")
+    ap.add_argument("--variant", type=int, default=0, help="gemm: 0 choose, 1 one CTA per tile, 2 CTA pairs")
     ap.add_argument("-m", type=int, default=2048)
     ap.add_argument("-n", type=int, default=6144)
     ap.add_argument("-k", type=int, default=8192)

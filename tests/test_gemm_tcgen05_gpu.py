@@ -8,7 +8,7 @@ from speculators_b200 import ops
 pytestmark = pytest.mark.gpu
 
 
-def _run(M, N, K, epilogue=0, lda_pad=0, seed=0):
+def _run(M, N, K, epilogue=0, lda_pad=0, seed=0, variant=0):
     torch.manual_seed(seed)
     a_full = (torch.randn(M, K + lda_pad, device="cuda") * 0.5).to(torch.bfloat16)
     a = a_full[:, :K]
@@ -21,7 +21,7 @@ def _run(M, N, K, epilogue=0, lda_pad=0, seed=0):
         ref = ref + out.float()
     elif epilogue == 2:
         ref = ref + res.float()
-    ops.native().gemm_tn(a, b, out, res if epilogue == 2 else None, epilogue, status)
+    ops.native().gemm_tn_variant(a, b, out, res if epilogue == 2 else None, epilogue, status, variant)
     torch.cuda.synchronize()
     assert int(status.item()) == 0, f"kernel reported wait timeout code {int(status.item())}"
     err = (out.float() - ref).abs().max().item()
@@ -30,16 +30,30 @@ def _run(M, N, K, epilogue=0, lda_pad=0, seed=0):
 
 
 def test_single_tile():
-    _run(128, 256, 64)
+    _run(128, 256, 64, variant=1)
+
+
+def test_single_pair_tile():
+    """One 256x256 tile on one CTA pair (tcgen05 cta_group::2), one k-block."""
+    _run(256, 256, 64, variant=2)
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 512), (256, 512, 256), (200, 300, 136), (2048, 4096, 1024), (77, 1000, 72), (1000, 520, 4096)])
-def test_shapes_including_ragged_edges(M, N, K):
-    _run(M, N, K)
+@pytest.mark.parametrize("variant", [1, 2])
+def test_shapes_including_ragged_edges(M, N, K, variant):
+    _run(M, N, K, variant=variant)
 
 
-def test_strided_a_and_epilogues():
-    _run(256, 512, 192, lda_pad=64)
-    _run(384, 768, 320, epilogue=1)
-    _run(384, 768, 320, epilogue=2)
-    _run(130, 260, 72, epilogue=1)
+@pytest.mark.parametrize("variant", [1, 2])
+def test_strided_a_and_epilogues(variant):
+    _run(256, 512, 192, lda_pad=64, variant=variant)
+    _run(384, 768, 320, epilogue=1, variant=variant)
+    _run(384, 768, 320, epilogue=2, variant=variant)
+    _run(130, 260, 72, epilogue=1, variant=variant)
+
+
+def test_many_tiles_per_pair_wraps_the_ring():
+    """More tiles than CTA pairs and more k-blocks than pipeline stages: exercises the
+    phase wrap of every barrier and both accumulator buffers."""
+    _run(2048, 6144, 1024, variant=2)
+    _run(4096, 5120, 640, epilogue=2, variant=2)
