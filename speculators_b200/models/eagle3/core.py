@@ -61,10 +61,11 @@ class Eagle3FirstLayer(nn.Module):
 
     def forward(self, embeds, hidden, positions, rotary, spec, past=None, ctx_len=None):
         H = self.hidden_size
-        x = ops.eagle3_input_concat(
-            embeds, hidden, self.input_layernorm.weight, self.hidden_norm.weight, self.hidden_norm.variance_epsilon
+        x, normed_hidden = ops.eagle3_input_concat(
+            embeds, hidden, self.input_layernorm.weight, self.hidden_norm.weight, self.hidden_norm.variance_epsilon,
+            return_hidden_half=True,
         )
-        residual = x[:, H:] if self.norm_before_residual else hidden
+        residual = normed_hidden if self.norm_before_residual else hidden
         h = self.self_attn(x, positions, rotary, spec, past, ctx_len, residual=residual)
         return self.mlp(self.post_attention_layernorm(h), residual=h)
 

@@ -88,8 +88,18 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             flat = getattr(weight, "_flat_grad", None)
             if flat is not None:
-                target = flat if r0 is None else flat[r0:r1]
-                target.addmm_(dy2.t(), x2)
+                if getattr(weight, "_grad_fresh", False):
+                    # first gradient of this weight since the engine's zero_grad, which left
+                    # the buffer uncleared: store instead of accumulate
+                    weight._grad_fresh = False
+                    if r0 is None:
+                        torch.mm(dy2.t(), x2, out=flat)
+                    else:
+                        flat.zero_()
+                        flat[r0:r1].addmm_(dy2.t(), x2)
+                else:
+                    target = flat if r0 is None else flat[r0:r1]
+                    target.addmm_(dy2.t(), x2)
             elif r0 is None:
                 dw = dy2.t() @ x2
             else:
@@ -179,12 +189,18 @@ class _Eagle3InputFn(torch.autograd.Function):
         nat.rmsnorm_fwd(embeds, w_e, None, out[:, :H], rs_e, eps)
         nat.rmsnorm_fwd(hidden, w_h, None, out[:, H:], rs_h, eps)
         ctx.save_for_backward(embeds, hidden, w_e, w_h, rs_e, rs_h)
-        return out
+        ctx.set_materialize_grads(False)
+        # second result: the normalised-hidden half on its own, so that a consumer of just
+        # that half (the residual branch) hands its gradient back as [T, H] instead of
+        # autograd padding it to [T, 2H] (zero fill + copy + add)
+        return out, out[:, H:]
 
     @staticmethod
-    def backward(ctx, dout):
+    def backward(ctx, dout, dhalf):
         embeds, hidden, w_e, w_h, rs_e, rs_h = ctx.saved_tensors
         T, H = hidden.shape
+        if dout is None:
+            dout = torch.zeros((T, 2 * H), dtype=hidden.dtype, device=hidden.device)
         if dout.stride(1) != 1 or dout.stride(0) % 8:
             dout = dout.contiguous()
         nat = native()
@@ -197,7 +213,8 @@ class _Eagle3InputFn(torch.autograd.Function):
         if need_h or need_wh:
             d_h = torch.empty_like(hidden)
             dw_h = torch.empty(H, dtype=torch.float32, device=hidden.device) if need_wh else None
-            nat.rmsnorm_bwd(dout[:, H:], hidden, w_h, rs_h, d_h, dw_h, False, False)
+            dy_h = dout[:, H:] if dhalf is None else dout[:, H:] + dhalf
+            nat.rmsnorm_bwd(dy_h, hidden, w_h, rs_h, d_h, dw_h, False, False)
         return (
             d_e if need_e else None,
             d_h if need_h else None,
@@ -207,13 +224,16 @@ class _Eagle3InputFn(torch.autograd.Function):
         )
 
 
-def eagle3_input_concat(embeds, hidden, w_embed_norm, w_hidden_norm, eps):
-    """First-layer input of an EAGLE-3 draft: both halves normalised, concatenated."""
+def eagle3_input_concat(embeds, hidden, w_embed_norm, w_hidden_norm, eps, return_hidden_half: bool = False):
+    """First-layer input of an EAGLE-3 draft: both halves normalised, concatenated
+    (``[T, 2H]``).  With ``return_hidden_half`` also returns the normalised-hidden half
+    ``[T, H]`` as a result of its own (a view of the first on CUDA)."""
     if _use_native(hidden):
-        return _Eagle3InputFn.apply(embeds.contiguous(), hidden.contiguous(), w_embed_norm, w_hidden_norm, eps)
-    return torch.cat(
-        [_rms_norm_ref(embeds, w_embed_norm, eps), _rms_norm_ref(hidden, w_hidden_norm, eps)], dim=-1
-    )
+        out, half = _Eagle3InputFn.apply(embeds.contiguous(), hidden.contiguous(), w_embed_norm, w_hidden_norm, eps)
+    else:
+        out = torch.cat([_rms_norm_ref(embeds, w_embed_norm, eps), _rms_norm_ref(hidden, w_hidden_norm, eps)], dim=-1)
+        half = out[:, hidden.shape[-1]:]
+    return (out, half) if return_hidden_half else out
 
 
 # --------------------------------------------------------------------------- swiglu

@@ -34,6 +34,9 @@ int fused_optim_ctl_words();
 int fused_optim_num_partials();
 int launch_fused_sharded_adamw(int, int, int64_t, const void* const*, void* const*, void* const*, float*, float*, float*, float*,
                                float*, const float*, int*, cudaStream_t);
+int hs_ring_ctl_words_per_slot();
+int launch_hs_push(const void*, int64_t, void*, uint32_t*, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t*, int*, cudaStream_t);
+int launch_hs_pop(void*, int64_t, const void*, uint32_t*, uint32_t, uint32_t, uint32_t*, int*, cudaStream_t);
 void launch_sumsq(const void*, int, int64_t, float*, float*, int, cudaStream_t);
 void launch_set_hyper(float*, const float*, cudaStream_t);
 void launch_adamw(float*, float*, float*, const void*, int, void*, int64_t, const float*,
@@ -283,6 +286,33 @@ Tensor peer_tensor(int64_t ptr, int64_t numel, at::ScalarType dtype, int64_t dev
 }
 int64_t fused_optim_ctl_words() { return sb200::fused_optim_ctl_words(); }
 
+// ---- hidden-state ring (device-to-device hand-off) -----------------------------------------
+int64_t hs_ring_ctl_words() { return sb200::hs_ring_ctl_words_per_slot(); }
+
+// src: contiguous CUDA tensor (payload, size a multiple of 16 bytes); slot_data / slot_ctl: device addresses
+// of the slot in the consumer's memory as mapped into this process; scratch: int32[2] zeros on this device.
+void hs_push(const Tensor& src, int64_t slot_data, int64_t slot_ctl, int64_t seq, int64_t n_slots, int64_t rows, int64_t width,
+             int64_t spin_limit, Tensor scratch, Tensor status) {
+  TORCH_CHECK(src.is_cuda() && src.is_contiguous() && scratch.is_cuda() && status.is_cuda());
+  TORCH_CHECK(scratch.scalar_type() == at::kInt && scratch.numel() >= 2 && status.scalar_type() == at::kInt && status.numel() >= 1);
+  c10::cuda::CUDAGuard guard(src.device());
+  const int rc = sb200::launch_hs_push(src.data_ptr(), (int64_t)src.nbytes(), reinterpret_cast<void*>(slot_data),
+                                       reinterpret_cast<uint32_t*>(slot_ctl), (uint32_t)seq, (uint32_t)n_slots, (uint32_t)rows, (uint32_t)width,
+                                       (uint32_t)spin_limit, reinterpret_cast<uint32_t*>(scratch.data_ptr<int>()), status.data_ptr<int>(),
+                                       cur_stream());
+  TORCH_CHECK(rc == 0, "hs_push: bad arguments or launch failure (", rc, ")");
+}
+
+void hs_pop(Tensor dst, int64_t slot_data, int64_t slot_ctl, int64_t seq, int64_t spin_limit, Tensor scratch, Tensor status) {
+  TORCH_CHECK(dst.is_cuda() && dst.is_contiguous() && scratch.is_cuda() && status.is_cuda());
+  TORCH_CHECK(scratch.scalar_type() == at::kInt && scratch.numel() >= 2 && status.scalar_type() == at::kInt && status.numel() >= 1);
+  c10::cuda::CUDAGuard guard(dst.device());
+  const int rc = sb200::launch_hs_pop(dst.data_ptr(), (int64_t)dst.nbytes(), reinterpret_cast<const void*>(slot_data),
+                                      reinterpret_cast<uint32_t*>(slot_ctl), (uint32_t)seq, (uint32_t)spin_limit,
+                                      reinterpret_cast<uint32_t*>(scratch.data_ptr<int>()), status.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(rc == 0, "hs_pop: bad arguments or launch failure (", rc, ")");
+}
+
 // g_ptrs / w_ptrs / ctl_ptrs: int64 CPU tensors [world] of device addresses valid on this rank.
 void fused_sharded_adamw(int64_t world, int64_t rank, int64_t shard, const Tensor& g_ptrs, const Tensor& w_ptrs, const Tensor& ctl_ptrs,
                          Tensor master, Tensor m, Tensor v, Tensor gred, const Tensor& hyper, Tensor status) {
@@ -477,6 +507,9 @@ TORCH_LIBRARY(sb200, m) {
   m.def("peer_tensor", &peer_tensor);
   m.def("fused_optim_ctl_words", &fused_optim_ctl_words);
   m.def("fused_sharded_adamw", &fused_sharded_adamw);
+  m.def("hs_ring_ctl_words", &hs_ring_ctl_words);
+  m.def("hs_push", &hs_push);
+  m.def("hs_pop", &hs_pop);
   m.def("gemm_tn", &gemm_tn);
   m.def("gemm_tn_variant", &gemm_tn_variant);
   m.def("attn_fwd", &attn_fwd);

@@ -93,6 +93,11 @@ class TrainEngine:
         self.step_count = 0
         self._flatten()
         self._init_state()
+        import os
+
+        self._lazy_zero = self.device.type == "cuda" and os.environ.get("SB200_EAGER_ZERO_GRAD") != "1"
+        if self._lazy_zero:
+            self._install_lazy_zero_hooks()
 
     def _want_p2p(self) -> bool:
         import os
@@ -221,12 +226,52 @@ class TrainEngine:
 
     # ------------------------------------------------------------------ step
     def zero_grad(self) -> None:
-        self.flat_g.zero_()
+        """Clear the gradient buffer.  On CUDA the matrices (almost all of the buffer) are
+        not written: they are flagged ``_grad_fresh`` and whoever produces their first
+        gradient of the step stores it instead of accumulating (``ops.linear``'s weight
+        gradient GEMM, or the hook below for gradients that arrive through autograd's own
+        accumulation); ``apply`` clears the ones nothing touched."""
+        lazy = self._lazy_zero
+        if not lazy:
+            self.flat_g.zero_()
         for p, o in zip(self.params, self.offsets):  # re-attach if something replaced .grad
             if p.grad is None or p.grad.data_ptr() != self.flat_g.data_ptr() + o * self.flat_g.element_size():
                 p.grad = self.flat_g[o : o + p.numel()].view(p.shape)
                 if p.ndim == 2:
                     p._flat_grad = p.grad
+            if lazy:
+                if p.ndim == 2:
+                    p._grad_fresh = True
+                else:
+                    p.grad.zero_()
+
+    def _install_lazy_zero_hooks(self) -> None:
+        def make(p):
+            def on_grad(g):
+                if getattr(p, "_grad_fresh", False):
+                    p._grad_fresh = False
+                    p._flat_grad.zero_()
+                return g
+
+            return on_grad
+
+        for p in self.params:
+            if p.ndim == 2:
+                p._grad_fresh = False
+                p.register_hook(make(p))
+
+    def mark_grads_written(self) -> None:
+        """Call after writing gradients into ``flat_g`` / ``p.grad`` directly (not through
+        backward): tells ``apply`` that the matrices' regions hold this step's gradients."""
+        for p in self.params:
+            if p.ndim == 2:
+                p._grad_fresh = False
+
+    def _settle_untouched_grads(self) -> None:
+        for p in self.params:
+            if p.ndim == 2 and getattr(p, "_grad_fresh", False):
+                p._grad_fresh = False
+                p._flat_grad.zero_()
 
     def prepare_hyper(self, lr: float | None = None) -> None:
         """Host side of a step: bump the step counter and stage lr / bias corrections
@@ -250,6 +295,8 @@ class TrainEngine:
 
     def apply(self) -> None:
         """Device side of a step (capturable): reduce, norm, update, gather."""
+        if self._lazy_zero:
+            self._settle_untouched_grads()
         if self.p2p:
             ops.native().fused_sharded_adamw(
                 self.world, self.rank, self.hi - self.lo, self._g_ptrs, self._w_ptrs, self._ctl_ptrs, self.master, self.exp_avg,

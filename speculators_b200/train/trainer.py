@@ -160,7 +160,7 @@ class _GraphedStep:
         graph = torch.cuda.CUDAGraph()
         count_capture = ops.native().launch_count()
         with torch.cuda.graph(graph):
-            tr.engine.flat_g.zero_()
+            tr.engine.zero_grad()
             _, loss, metrics = tr.model(**static_in, **kwargs)
             loss.backward()
             if self.capture_optimizer:

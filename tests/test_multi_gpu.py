@@ -44,6 +44,7 @@ def _engine_worker(rank, world, port, out_path):
                 g = torch.Generator(device="cuda").manual_seed(1000 * step + r)
                 grads.append((torch.randn(eng.total, generator=g, device="cuda") * 0.1 * (step + 1)).bfloat16())
             eng.flat_g.copy_(grads[rank])
+            eng.mark_grads_written()
             eng.step()
             if mode == "nccl":
                 gavg = sum(x.float() for x in grads) / world
@@ -80,3 +81,43 @@ def test_fused_peer_optimizer_matches_nccl_path(tmp_path):
     mp.spawn(_engine_worker, args=(2, 29641, str(out)), nprocs=2, join=True)
     for r in json.loads(out.read_text()):
         assert r["same"] and r["p2p_err"] <= 5e-6 and r["nccl_err"] <= 5e-4 and r["w_err"] <= 8e-3, r
+
+
+def _sample(seq, rows, width, device):
+    g = torch.Generator(device="cpu").manual_seed(seq)
+    hs = torch.randn(rows, width, generator=g).to(torch.bfloat16).to(device)
+    ids = torch.randint(0, 32000, (rows,), generator=g, dtype=torch.int32).to(device)
+    return hs, ids
+
+
+def _ring_worker(rank, world, path, out_path):
+    from speculators_b200.hs_connectors import HiddenStateRingWriter, NvlinkTransfer
+
+    torch.cuda.set_device(rank)
+    width, n = 3 * 256, 6
+    if rank == 1:  # consumer: the trainer side of the transport
+        transfer = NvlinkTransfer(path, n_slots=2, max_rows=512, width=width, rank=0, device="cuda:1", timeout_s=20.0)
+        transfer.setup()
+        ok = True
+        for seq in range(1, n + 1):
+            got = transfer.get_generated(str(seq))
+            hs, ids = _sample(seq, 100 + 50 * seq, width, "cuda:1")
+            ok = ok and torch.equal(got["hidden_states"], hs) and torch.equal(got["token_ids"], ids.long())
+        with open(out_path, "w") as fh:
+            json.dump({"ok": bool(ok)}, fh)
+        transfer.ring.close()
+    else:  # producer: the verifier side
+        writer = HiddenStateRingWriter(NvlinkTransfer.wait_for_ring(path, rank=0, timeout_s=60.0), device="cuda:0")
+        for seq in range(1, n + 1):  # queued back to back: pushes 3.. wait on the device for the consumer's acknowledgements
+            hs, ids = _sample(seq, 100 + 50 * seq, width, "cuda:0")
+            writer.push(seq, hs, ids, timeout_s=20.0, check=False)
+        torch.cuda.synchronize()
+        writer.check_status()
+        writer.close()
+
+
+def test_hidden_state_ring_across_two_gpus(tmp_path):
+    _need_two()
+    out = tmp_path / "ring.json"
+    mp.spawn(_ring_worker, args=(2, str(tmp_path / "rdv"), str(out)), nprocs=2, join=True)
+    assert json.loads(out.read_text())["ok"] is True

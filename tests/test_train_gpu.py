@@ -68,3 +68,18 @@ def test_engine_flat_gradients_match_plain_autograd(tiny_verifier_dir, tiny_voca
             continue
         a, b = p.grad.float(), ref[name].grad.float()
         assert float((a - b).abs().max()) <= 0.03 * float(b.abs().max()) + 1e-3, name
+    # zero_grad leaves the matrices uncleared and flags them: a second backward without it
+    # accumulates, one after it starts over, and a weight no backward touched is cleared
+    # by the optimizer step
+    first = engine.flat_g.float().clone()
+    flat_model(**batch, **kwargs)[1].backward()
+    twice = engine.flat_g.float()
+    assert float((twice - 2 * first).abs().max()) <= 0.03 * float(first.abs().max()) + 1e-3
+    engine.zero_grad()
+    flat_model(**batch, **kwargs)[1].backward()
+    assert float((engine.flat_g.float() - first).abs().max()) <= 0.03 * float(first.abs().max()) + 1e-3
+    engine.zero_grad()
+    before = engine.flat_w.float().clone()
+    engine.step(lr=0.0)  # nothing was back-propagated: every gradient must read as zero
+    assert float(engine.flat_g.float().abs().max()) == 0.0
+    assert float(engine.grad_norm()) == 0.0 and torch.equal(engine.flat_w.float(), before)
