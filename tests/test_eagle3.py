@@ -140,3 +140,29 @@ def test_numerical_parity_with_reference_sdpa_path(tiny_verifier_dir, tiny_vocab
     assert torch.allclose(mine.fc.weight.grad, ref.fc.weight.grad, atol=1e-5)
     nq = ref.layers[0].self_attn.q_proj.weight.shape[0]
     assert torch.allclose(mine.layers[0].self_attn.qkv_proj.weight.grad[:nq], ref.layers[0].self_attn.q_proj.weight.grad, atol=1e-6)
+
+
+def test_component_table_and_partial_rotary_oracle():
+    from speculators_b200 import ops
+    from speculators_b200.models.base_components import model_classes, override_components
+    from speculators_b200.models.eagle3.core import Eagle3FirstLayer
+    from speculators_b200.models.eagle3.rotary_partial import install_partial_neox_rotary, partial_neox_apply_rotary_pos_emb
+
+    comps = override_components("llama", first_layer_class=Eagle3FirstLayer)
+    assert comps.first_layer_class is Eagle3FirstLayer and comps.decoder_layer_class is model_classes["llama"].decoder_layer_class
+    assert {"llama", "qwen3", "qwen3_next", "qwen3_5_moe_text"} <= set(model_classes)
+    with pytest.raises(KeyError):
+        override_components("gpt2")
+    install_partial_neox_rotary()
+    # the package's rotary op in partial mode equals the reference-signature function
+    torch.manual_seed(0)
+    T, heads, hd, rot = 9, 3, 16, 8
+    x = torch.randn(T, heads * hd)
+    pos = torch.arange(T)
+    ang = torch.outer(torch.arange(32, dtype=torch.float32), 1.0 / (10000.0 ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot)))
+    cos_t, sin_t = ang.cos(), ang.sin()
+    ours = ops.rope_(x.clone(), pos, cos_t, sin_t, heads, hd, rot).view(T, heads, hd)
+    cos_full, sin_full = torch.cat([cos_t, cos_t], -1)[pos], torch.cat([sin_t, sin_t], -1)[pos]
+    q = x.view(T, heads, hd).transpose(0, 1).unsqueeze(0)  # [1, heads, T, hd]
+    ref, _ = partial_neox_apply_rotary_pos_emb(q, q, cos_full.unsqueeze(0), sin_full.unsqueeze(0))
+    torch.testing.assert_close(ours, ref[0].transpose(0, 1), atol=1e-5, rtol=1e-5)
