@@ -238,3 +238,54 @@ def test_vocab_mapping_offsets_and_ties():
     kept = torch.nonzero(t2d).squeeze(1)
     assert kept.tolist() == [0, 2, 5, 9]  # top-3 by count, then the lowest unseen id
     assert (torch.arange(4) + d2t).tolist() == kept.tolist()  # d2t stores offsets
+
+
+def test_vllm_connector_halves_with_dict_store():
+    """Scheduler/worker halves of the server-side plugin against an in-memory store:
+    paged-cache gather, key naming, delayed completion, error marker on non-finite data."""
+    import time as _time
+
+    from speculators_b200.hs_connectors import DictStoreClient, HiddenStatesStore
+    from speculators_b200.hs_connectors.vllm_connector import (
+        SchedulerSide, WorkerSide, extract_from_kv_cache, sanitize_key, slot_mapping_for_blocks,
+    )
+
+    assert sanitize_key("cmpl-12/ab") == "cmpl-12_ab" and sanitize_key("9x") == "k9x"
+    block_size, width = 4, 6
+    cache = torch.arange(8 * block_size * width, dtype=torch.float32).reshape(8, block_size, width)
+    slots = slot_mapping_for_blocks([5, 2], block_size)
+    assert slots.tolist() == [20, 21, 22, 23, 8, 9, 10, 11]
+    got = extract_from_kv_cache(cache, slots, 6)
+    assert torch.equal(got, torch.cat([cache[5], cache[2][:2]]))
+
+    store = HiddenStatesStore(client=DictStoreClient())
+    sched, worker = SchedulerSide(), WorkerSide(store, block_size, num_writer_threads=2)
+    worker.register(cache)
+    sched.on_new_request("req/1")
+    delay_free, params = sched.request_finished("req/1", [7, 8, 9, 10, 11, 12], [7, 8, 9, 10, 11, 12, 13], [5, 2])
+    assert delay_free is True and params == {"handle": "req_1"}
+    # with include_output_tokens the sampled last token is dropped
+    _, p2 = sched.request_finished("r2", None, [1, 2, 3], [0], {"include_output_tokens": True})
+    pending = sched.drain()
+    assert [p.key for p in pending] == ["req_1", "r2"] and pending[1].token_ids.tolist() == [1, 2] and sched.drain() == []
+    worker.submit(pending)
+    done: set = set()
+    for _ in range(200):
+        done |= worker.poll({"req/1", "r2", "other-rank-only"})
+        if {"req/1", "r2"} <= done:
+            break
+        _time.sleep(0.01)
+    assert done == {"req/1", "r2", "other-rank-only"}
+    sample = store.get_sample("req_1", timeout=1.0)
+    assert torch.equal(sample["hidden_states"], got) and sample["token_ids"].tolist() == [7, 8, 9, 10, 11, 12]
+    # non-finite hidden states: the write fails and leaves an error marker the consumer sees
+    cache[1, 0, 0] = float("nan")
+    _, _ = sched.request_finished("bad", [1, 2], [1, 2], [1])
+    worker.submit(sched.drain())
+    for _ in range(200):
+        if worker.poll({"bad"}):
+            break
+        _time.sleep(0.01)
+    with pytest.raises(Exception, match="(?i)non-finite|nan|error"):
+        store.get_sample("bad", timeout=0.5)
+    worker.shutdown()
