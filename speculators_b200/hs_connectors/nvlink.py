@@ -61,7 +61,7 @@ class _RingBase:
         self.ids_off, self.used_bytes, self.slot_bytes = _layout(self.max_rows, self.width)
         self.ctl_words = int(_native().hs_ring_ctl_words())
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self.scratch = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self.scratch = torch.zeros(4, dtype=torch.int32, device=self.device)  # go flag, block ticket, popped rows, popped width
         self._data = self._ctl = 0
 
     def _slot(self, seq: int) -> tuple[int, int]:
@@ -86,8 +86,6 @@ class HiddenStateRing(_RingBase):
             self._data = int(nat.peer_alloc(self.n_slots * self.slot_bytes))
             self._ctl = int(nat.peer_alloc(self.n_slots * self.ctl_words * 4))
         self._staging = torch.empty(self.used_bytes, dtype=torch.uint8, device=self.device)
-        index = self.device.index if self.device.index is not None else torch.cuda.current_device()
-        self._ctl_view = nat.peer_tensor(self._ctl, self.n_slots * self.ctl_words, torch.int32, index)
 
     def describe(self) -> dict[str, Any]:
         """What a producer needs to map the ring (JSON-serialisable)."""
@@ -102,8 +100,7 @@ class HiddenStateRing(_RingBase):
         (fresh tensors).  ``TimeoutError`` if it does not arrive within ``timeout_s``."""
         data, ctl = self._slot(seq)
         _native().hs_pop(self._staging, data, ctl, seq, _spin_limit(timeout_s), self.scratch, self.status)
-        i = (seq - 1) % self.n_slots
-        rows = int(self._ctl_view[i * self.ctl_words + 2].item())  # synchronises with the copy
+        rows = int(self.scratch[2].item())  # taken out by the pop kernel before it freed the slot; synchronises with the copy
         self._check(f"pop of sample {seq}")
         hs = self._staging[: self.max_rows * self.width * 2].view(torch.bfloat16).view(self.max_rows, self.width)[:rows].clone()
         ids = self._staging[self.ids_off : self.ids_off + self.max_rows * 4].view(torch.int32)[:rows].long()

@@ -305,7 +305,7 @@ void hs_push(const Tensor& src, int64_t slot_data, int64_t slot_ctl, int64_t seq
 
 void hs_pop(Tensor dst, int64_t slot_data, int64_t slot_ctl, int64_t seq, int64_t spin_limit, Tensor scratch, Tensor status) {
   TORCH_CHECK(dst.is_cuda() && dst.is_contiguous() && scratch.is_cuda() && status.is_cuda());
-  TORCH_CHECK(scratch.scalar_type() == at::kInt && scratch.numel() >= 2 && status.scalar_type() == at::kInt && status.numel() >= 1);
+  TORCH_CHECK(scratch.scalar_type() == at::kInt && scratch.numel() >= 4 && status.scalar_type() == at::kInt && status.numel() >= 1);
   c10::cuda::CUDAGuard guard(dst.device());
   const int rc = sb200::launch_hs_pop(dst.data_ptr(), (int64_t)dst.nbytes(), reinterpret_cast<const void*>(slot_data),
                                       reinterpret_cast<uint32_t*>(slot_ctl), (uint32_t)seq, (uint32_t)spin_limit,

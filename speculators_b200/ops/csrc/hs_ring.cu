@@ -11,8 +11,9 @@
 //
 // push:  (bounded) wait until ack == seq - n_slots (the previous occupant was consumed),
 //        copy the payload into the peer slot with 16-byte stores, fence, release-store seq.
-// pop:   (bounded) wait until seq shows the wanted sample, copy the payload out of the own
-//        slot, release-store ack.
+// pop:   (bounded) wait until seq shows the wanted sample, copy the payload and its shape
+//        out of the own slot, release-store ack (from then on the producer may overwrite
+//        payload and shape).
 //
 // Both waits are bounded; when one runs out the kernel writes a code to the caller's
 // status word and the copy part is skipped, so the context stays usable and the host
@@ -51,7 +52,8 @@ __global__ void wait_word_kernel(const uint32_t* word, uint32_t want, uint32_t s
 // `flag` (release, system scope) after optionally recording the payload shape.
 __global__ void __launch_bounds__(256)
 copy_publish_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, int64_t nvec, const uint32_t* go, uint32_t* ticket,
-                    uint32_t* flag, uint32_t flag_value, uint32_t* shape_words, uint32_t rows, uint32_t width) {
+                    uint32_t* flag, uint32_t flag_value, uint32_t* shape_words, uint32_t rows, uint32_t width,
+                    const uint32_t* shape_src, uint32_t* shape_dst) {
   if (*reinterpret_cast<const volatile uint32_t*>(go) == 0) return;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) dst[i] = src[i];
   __threadfence_system();
@@ -60,9 +62,13 @@ copy_publish_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, int6
     const uint32_t t = atomicAdd(ticket, 1u);
     if (t == gridDim.x - 1) {
       *ticket = 0;
-      if (shape_words != nullptr) {
+      if (shape_words != nullptr) {  // push: record the payload shape before the sample becomes visible
         reinterpret_cast<volatile uint32_t*>(shape_words)[0] = rows;
         reinterpret_cast<volatile uint32_t*>(shape_words)[1] = width;
+      }
+      if (shape_dst != nullptr) {  // pop: take the shape out before the slot is handed back
+        shape_dst[0] = reinterpret_cast<const volatile uint32_t*>(shape_src)[0];
+        shape_dst[1] = reinterpret_cast<const volatile uint32_t*>(shape_src)[1];
       }
       __threadfence_system();
       st_release_sys(flag, flag_value);
@@ -90,11 +96,12 @@ int launch_hs_push(const void* src, int64_t nbytes, void* slot_data, uint32_t* s
   hs::wait_word_kernel<<<1, 1, 0, stream>>>(slot_ctl + 1, free_when, spin_limit, hs::kTimeoutSlotBusy, status, scratch);
   const int64_t nvec = nbytes >> 4;
   hs::copy_publish_kernel<<<copy_grid(nvec), 256, 0, stream>>>(static_cast<const uint4*>(src), static_cast<uint4*>(slot_data), nvec, scratch,
-                                                              scratch + 1, slot_ctl + 0, seq, slot_ctl + 2, rows, width);
+                                                              scratch + 1, slot_ctl + 0, seq, slot_ctl + 2, rows, width, nullptr, nullptr);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
-// Consumer side.  dst receives the payload; afterwards ack := seq frees the slot.
+// Consumer side.  dst receives the payload and scratch[2..3] its shape (rows, width);
+// afterwards ack := seq frees the slot.  scratch: four uint32 in local memory.
 int launch_hs_pop(void* dst, int64_t nbytes, const void* slot_data, uint32_t* slot_ctl, uint32_t seq, uint32_t spin_limit, uint32_t* scratch,
                   int* status, cudaStream_t stream) {
   if (nbytes <= 0 || (nbytes & 15) || (reinterpret_cast<uintptr_t>(dst) & 15) || (reinterpret_cast<uintptr_t>(slot_data) & 15)) return -1;
@@ -102,7 +109,7 @@ int launch_hs_pop(void* dst, int64_t nbytes, const void* slot_data, uint32_t* sl
   hs::wait_word_kernel<<<1, 1, 0, stream>>>(slot_ctl + 0, seq, spin_limit, hs::kTimeoutNoSample, status, scratch);
   const int64_t nvec = nbytes >> 4;
   hs::copy_publish_kernel<<<copy_grid(nvec), 256, 0, stream>>>(static_cast<const uint4*>(slot_data), static_cast<uint4*>(dst), nvec, scratch,
-                                                              scratch + 1, slot_ctl + 1, seq, nullptr, 0, 0);
+                                                              scratch + 1, slot_ctl + 1, seq, nullptr, 0, 0, slot_ctl + 2, scratch + 2);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

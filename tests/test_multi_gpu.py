@@ -98,13 +98,21 @@ def _ring_worker(rank, world, path, out_path):
     if rank == 1:  # consumer: the trainer side of the transport
         transfer = NvlinkTransfer(path, n_slots=2, max_rows=512, width=width, rank=0, device="cuda:1", timeout_s=20.0)
         transfer.setup()
-        ok = True
+        ok, notes = True, []
         for seq in range(1, n + 1):
             got = transfer.get_generated(str(seq))
             hs, ids = _sample(seq, 100 + 50 * seq, width, "cuda:1")
-            ok = ok and torch.equal(got["hidden_states"], hs) and torch.equal(got["token_ids"], ids.long())
+            same_shape = got["hidden_states"].shape == hs.shape
+            hs_ok = same_shape and torch.equal(got["hidden_states"], hs)
+            ids_ok = same_shape and torch.equal(got["token_ids"], ids.long())
+            if not (hs_ok and ids_ok):
+                bad = (got["hidden_states"] != hs).flatten().nonzero().flatten() if same_shape else torch.zeros(0)
+                notes.append({"seq": seq, "shape": list(got["hidden_states"].shape), "want": list(hs.shape), "hs_ok": bool(hs_ok),
+                              "ids_ok": bool(ids_ok), "n_bad": int(bad.numel()), "first_bad": int(bad[0]) if bad.numel() else -1,
+                              "last_bad": int(bad[-1]) if bad.numel() else -1})
+            ok = ok and hs_ok and ids_ok
         with open(out_path, "w") as fh:
-            json.dump({"ok": bool(ok)}, fh)
+            json.dump({"ok": bool(ok), "notes": notes}, fh)
         transfer.ring.close()
     else:  # producer: the verifier side
         writer = HiddenStateRingWriter(NvlinkTransfer.wait_for_ring(path, rank=0, timeout_s=60.0), device="cuda:0")
@@ -120,4 +128,5 @@ def test_hidden_state_ring_across_two_gpus(tmp_path):
     _need_two()
     out = tmp_path / "ring.json"
     mp.spawn(_ring_worker, args=(2, str(tmp_path / "rdv"), str(out)), nprocs=2, join=True)
-    assert json.loads(out.read_text())["ok"] is True
+    result = json.loads(out.read_text())
+    assert result["ok"] is True, result["notes"]
