@@ -155,8 +155,11 @@ def make_batches(torch, args, cfg, rank: int, device, n_batches: int = 2):
     return out
 
 
-def timed_region(torch, dist, world, device, fn_step, batches, steps, warmup):
-    """W untimed + K timed steps; returns per-rank milliseconds for the K steps."""
+def timed_region(torch, dist, world, device, fn_step, batches, steps, warmup, lookahead=False):
+    """W untimed + K timed steps; returns per-rank milliseconds for the K steps.  With
+    ``lookahead`` the step function also receives the batch of the following step (None for
+    the last warm-up step and the last timed step, so that every timed step's input copy
+    starts and ends inside the timed region)."""
     cuda = device.type == "cuda"
 
     def barrier():
@@ -165,15 +168,22 @@ def timed_region(torch, dist, world, device, fn_step, batches, steps, warmup):
         if cuda:
             torch.cuda.synchronize()
 
+    def call(i, last):
+        b = batches[i % len(batches)]
+        if lookahead:
+            fn_step(b, None if last else batches[(i + 1) % len(batches)])
+        else:
+            fn_step(b)
+
     for i in range(warmup):
-        fn_step(batches[i % len(batches)])
+        call(i, i == warmup - 1)
     barrier()
     if cuda:
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
     t0 = time.perf_counter()
     for i in range(steps):
-        fn_step(batches[(warmup + i) % len(batches)])
+        call(warmup + i, i == steps - 1)
     if cuda:
         end.record()
     barrier()
@@ -245,11 +255,13 @@ def run_ours(args):
     # (2) end to end: pinned host batch -> H2D every step, loss read back every step
     last = {}
 
-    def step_e2e(b):
-        loss, _ = trainer.train_step(b)
+    def step_e2e(b, upcoming):
+        # the public training call: this step's batch plus the one that follows, whose
+        # host-to-device copy the trainer overlaps with this step's compute
+        loss, _ = trainer.train_step(b, upcoming)
         last["loss"] = float(loss.item())
 
-    ms_e2e = timed_region(torch, dist, world, device, step_e2e, batches, args.steps, min(args.warmup, 3))
+    ms_e2e = timed_region(torch, dist, world, device, step_e2e, batches, args.steps, min(args.warmup, 3), lookahead=True)
     h2d = sum(v.numel() * v.element_size() for v in batches[0].values())
 
     value = world * tokens_per_step * args.steps / (ms / 1000.0)

@@ -125,6 +125,20 @@ class _StepTimer:
         }
 
 
+def _with_lookahead(iterable):
+    """``(item, next_item_or_None)`` pairs: lets the trainer start the next batch's
+    host-to-device copy while the current step runs."""
+    it = iter(iterable)
+    try:
+        cur = next(it)
+    except StopIteration:
+        return
+    for nxt in it:
+        yield cur, nxt
+        cur = nxt
+    yield cur, None
+
+
 class _GraphedStep:
     """CUDA-graph capture of forward + backward (+ optimizer) per input signature."""
 
@@ -134,6 +148,12 @@ class _GraphedStep:
         self.cache: dict[tuple, tuple] = {}
         self.launches_per_capture: dict[tuple, int] = {}  # own-kernel launches recorded per graph
         self.capture_launch_total = 0  # launches issued while warming up / capturing
+        # input prefetch: host->device copy of the next batch on a side stream while the
+        # current step computes; [host batch object, staged device tensors, event]
+        self._copy_stream: torch.cuda.Stream | None = None
+        self._staged: tuple | None = None
+        self._staging: dict[tuple, dict] = {}
+        self._consumed: torch.cuda.Event | None = None
 
     @staticmethod
     def signature(batch: dict) -> tuple:
@@ -170,7 +190,29 @@ class _GraphedStep:
         self.capture_launch_total += count_after - count_before
         return graph, static_in, loss, metrics
 
-    def run(self, batch: dict, lr: float | None):
+    def prefetch(self, batch: dict) -> None:
+        """Start copying ``batch`` (host tensors, ideally pinned) to the device on a side
+        stream.  The next ``run`` given this same dict object picks the staged copy up
+        instead of copying on the training stream."""
+        sig = self.signature(batch)
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream()
+        stage = self._staging.get(sig)
+        if stage is None:
+            stage = {k: torch.empty(v.shape, dtype=v.dtype, device=self.trainer.device) for k, v in batch.items() if isinstance(v, torch.Tensor)}
+            self._staging[sig] = stage
+        # the staging buffers may still be read by the device-to-device copy of the step
+        # that consumed the previous prefetch (only that copy: not the step's compute)
+        if self._consumed is not None:
+            self._copy_stream.wait_event(self._consumed)
+        with torch.cuda.stream(self._copy_stream):
+            for k, v in stage.items():
+                v.copy_(batch[k], non_blocking=True)
+            done = torch.cuda.Event()
+            done.record()
+        self._staged = (batch, stage, done)
+
+    def run(self, batch: dict, lr: float | None, next_batch: dict | None = None):
         sig = self.signature(batch)
         entry = self.cache.get(sig)
         tr = self.trainer
@@ -178,8 +220,16 @@ class _GraphedStep:
             entry = self._capture(batch)
             self.cache[sig] = entry
         graph, static_in, loss, metrics = entry
+        source = batch
+        if self._staged is not None and self._staged[0] is batch:
+            _, source, done = self._staged
+            torch.cuda.current_stream().wait_event(done)
+        self._staged = None
         for k, v in static_in.items():
-            v.copy_(batch[k], non_blocking=True)
+            v.copy_(source[k], non_blocking=True)
+        if source is not batch:
+            self._consumed = torch.cuda.Event()
+            self._consumed.record()
         tr.timer.mark("fetch")
         tr.engine.prepare_hyper(lr)
         graph.replay()
@@ -187,6 +237,8 @@ class _GraphedStep:
         tr.timer.mark("bwd")
         if not self.capture_optimizer:
             tr.engine.apply()
+        if next_batch is not None:
+            self.prefetch(next_batch)
         return loss, metrics
 
 
@@ -319,12 +371,14 @@ class Trainer:
     def _current_lr(self) -> float:
         return self.schedulers[0].current_lr() if self.schedulers else self.config.lr
 
-    def train_step(self, batch: dict) -> tuple[torch.Tensor, dict[str, torch.Tensor]]:
+    def train_step(self, batch: dict, next_batch: dict | None = None) -> tuple[torch.Tensor, dict[str, torch.Tensor]]:
         """One optimizer step on ``batch`` (host or device tensors).  Returns the
-        loss and metric tensors on the training device."""
+        loss and metric tensors on the training device.  ``next_batch`` (optional, the
+        dict that the following call will receive) has its host-to-device copy started
+        on a side stream so that it overlaps this step's compute."""
         lr = self._current_lr()
         if self._graphed is not None:
-            loss, metrics = self._graphed.run(batch, lr)
+            loss, metrics = self._graphed.run(batch, lr, next_batch)
         else:
             dev_batch = {k: v.to(self.device, non_blocking=True) if isinstance(v, torch.Tensor) else v for k, v in batch.items()}
             self.timer.mark("fetch")
@@ -374,9 +428,9 @@ class Trainer:
                 pass
         self.timer.reset(self.global_step % cfg.log_freq == 0)
         self.timer.mark("start")
-        for rel, batch in enumerate(loader, 1):
+        for rel, (batch, upcoming) in enumerate(_with_lookahead(loader), 1):
             local_step = rel + skip_steps
-            loss, metrics = self.train_step(batch)
+            loss, metrics = self.train_step(batch, upcoming)
             lr_now = self._current_lr()
             if self.timer.enabled:
                 doc = batch.get("document_ids") if isinstance(batch, dict) else None

@@ -48,6 +48,25 @@ def test_graph_and_eager_trainers_agree_and_learn(tiny_verifier_dir, tiny_vocab_
     assert t_graph._graphed is not None and len(t_graph._graphed.cache) == 1
 
 
+def test_prefetched_inputs_give_the_same_steps(tiny_verifier_dir, tiny_vocab_maps):
+    """``train_step(batch, next_batch)`` stages the next batch on a side stream; the
+    losses must equal those of the plain call sequence, also when the announced batch is
+    not the one that arrives."""
+    base = make_tiny_eagle3(tiny_verifier_dir, tiny_vocab_maps)
+    seq = [{k: v.pin_memory() for k, v in make_tiny_batch(T=64, docs=(20, 30, 10), pad=4, seed=s).items()} for s in (0, 1, 2)]
+    order = [0, 1, 2, 1, 0, 2]
+    plain = _trainer(copy.deepcopy(base), seq[0], graph=True)
+    ahead = _trainer(copy.deepcopy(base), seq[0], graph=True)
+    want = [float(plain.train_step(seq[i])[0].item()) for i in order]
+    got = []
+    for n, i in enumerate(order):
+        nxt = seq[order[n + 1]] if n + 1 < len(order) else None
+        if n == 2:
+            nxt = seq[0]  # a wrong announcement: the staged copy must be ignored at the next call
+        got.append(float(ahead.train_step(seq[i], nxt)[0].item()))
+    assert got == want
+
+
 def test_engine_flat_gradients_match_plain_autograd(tiny_verifier_dir, tiny_vocab_maps):
     """Weight gradients accumulated in place into the flat buffer by ``ops.linear``
     equal the gradients plain autograd produces for the same bf16 model."""
