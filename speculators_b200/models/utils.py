@@ -8,10 +8,21 @@ import warnings
 from speculators_b200.layer_config import TransformerLayerConfig, read_config_json, unwrap_text_config
 
 __all__ = [
+    "conditional_torch_compile",
     "get_verifier_config",
     "resolve_draft_intermediate_size",
     "resolve_target_layer_ids",
 ]
+
+
+def conditional_torch_compile(fn=None, **_compile_kwargs):
+    """Kept for API parity with the reference (src/speculators/models/utils.py:12-17),
+    which compiles hot functions when CUDA is present.  This package has no tracing
+    compiler in its hot path (CUDA kernels + CUDA graphs), so the function comes back
+    unchanged; usable bare or with arguments."""
+    if fn is None:
+        return lambda f: f
+    return fn
 
 
 def get_verifier_config(verifier_name_or_path: str, trust_remote_code: bool = False) -> TransformerLayerConfig:

@@ -83,3 +83,32 @@ def test_from_dict_requires_discriminator():
         SpeculatorModelConfig.from_dict({"draft_vocab_size": 3})
     with pytest.raises(ValueError):
         SpeculatorModelConfig.from_dict({"speculators_model_type": "nope"})
+
+
+def test_optimizer_and_attention_compat_modules(tmp_path):
+    import torch
+
+    from speculators_b200.models.attention import AttnSpec, create_float_mask
+    from speculators_b200.models.utils import conditional_torch_compile
+    from speculators_b200.train import TrainerConfig
+    from speculators_b200.train.optimizers import build_optimizers, split_named_params_for_muon
+
+    model = torch.nn.Sequential(torch.nn.Linear(8, 16, bias=False), torch.nn.LayerNorm(16))
+    (engine,) = build_optimizers(model, TrainerConfig(lr=1e-2, num_epochs=1, save_path=str(tmp_path), optimizer="adamw"), device="cpu")
+    before = engine.flat_w.clone()
+    model(torch.randn(4, 8)).pow(2).sum().backward()
+    engine.step()
+    assert not torch.equal(engine.flat_w, before)
+    muon, adamw = split_named_params_for_muon(model)
+    assert [n for n, _ in muon] == ["0.weight"] and len(adamw) == 2
+    with pytest.raises(ValueError, match="Unsupported optimizer"):
+        build_optimizers(model, TrainerConfig(lr=1e-2, num_epochs=1, save_path=str(tmp_path), optimizer="sgd"), device="cpu")
+    spec = AttnSpec(lo=torch.tensor([0, 0, 2], dtype=torch.int32), hi=torch.tensor([1, 2, 2], dtype=torch.int32))
+    m = create_float_mask(spec, 3)
+    assert m[1].tolist() == [0.0, 0.0, float("-inf")] and torch.isinf(m[2]).all()
+
+    @conditional_torch_compile
+    def f(x):
+        return x + 1
+
+    assert f(1) == 2 and conditional_torch_compile(dynamic=True)(f)(2) == 3
