@@ -68,7 +68,8 @@ attn_fwd_kernel(const AttnParams p) {
   __nv_bfloat16* Vs = Ks + 2 * kTile;  // 2 buffers
   __shared__ int s_range[2];
 
-  const int tile_m = blockIdx.x, h = blockIdx.y;
+  // late query tiles see the most keys under a causal mask: hand them out first
+  const int tile_m = gridDim.x - 1 - blockIdx.x, h = blockIdx.y;
   const int kvh = h / (p.nh / p.nkv);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -291,7 +292,8 @@ attn_bwd_dq_kernel(const AttnParams p) {
   __nv_bfloat16* Vs = Ks + 2 * kTile;  // 2 buffers
   __shared__ int s_range[2];
 
-  const int tile_m = blockIdx.x, h = blockIdx.y;
+  // late query tiles see the most keys under a causal mask: hand them out first
+  const int tile_m = gridDim.x - 1 - blockIdx.x, h = blockIdx.y;
   const int kvh = h / (p.nh / p.nkv);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;

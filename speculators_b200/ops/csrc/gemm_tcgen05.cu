@@ -40,6 +40,7 @@ constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTE
 constexpr int THREADS = 192;
 constexpr int TMEM_COLS = 512;
 constexpr uint32_t POLL_LIMIT = 1u << 22;
+constexpr int kDefaultPairVariant = 2;
 
 enum Epilogue : int { kStore = 0, kAccumulate = 1, kAddResidual = 2 };
 enum Status : int { kOk = 0, kTimeoutProducer = 1, kTimeoutMma = 2, kTimeoutEpilogue = 3 };
@@ -174,6 +175,14 @@ struct Params {
   int* status;
 };
 
+// 32-byte store (one full sector) of sixteen bf16; ptr must be 32-byte aligned.
+__device__ __forceinline__ void st32(__nv_bfloat16* ptr, const bf16x8& a, const bf16x8& b) {
+  const uint4 x = *reinterpret_cast<const uint4*>(&a), y = *reinterpret_cast<const uint4*>(&b);
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"l"(ptr), "r"(x.x), "r"(x.y), "r"(x.z), "r"(x.w), "r"(y.x), "r"(y.y), "r"(y.z), "r"(y.w)
+               : "memory");
+}
+
 // Epilogue of one thread: TMEM lane `taddr` (its 256 fp32 columns) -> row `row`, columns
 // n0 .. n0+255 of C, with the configured epilogue.
 __device__ __forceinline__ void store_accumulator(const Params& p, uint32_t taddr, int row, int n0) {
@@ -181,6 +190,7 @@ __device__ __forceinline__ void store_accumulator(const Params& p, uint32_t tadd
   const __nv_bfloat16* rrow = p.residual ? p.residual + (int64_t)row * p.ldr + n0 : nullptr;
   const bool vec_ok = ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0) &&
                       (p.epilogue != kAddResidual || (((p.ldr & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0)));
+  const bool wide_ok = vec_ok && ((p.ldc & 15) == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 31) == 0);
 #pragma unroll 1
   for (int c = 0; c < BN / 32; ++c) {
     uint32_t r[32];
@@ -189,6 +199,7 @@ __device__ __forceinline__ void store_accumulator(const Params& p, uint32_t tadd
     if (row < p.M) {
       const int col0 = n0 + c * 32;
       if (vec_ok && col0 + 32 <= p.N) {
+        bf16x8 packed[4];
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
           float f[8];
@@ -205,7 +216,14 @@ __device__ __forceinline__ void store_accumulator(const Params& p, uint32_t tadd
 #pragma unroll
             for (int j = 0; j < 8; ++j) f[j] += o[j];
           }
-          st8(crow + c * 32 + v * 8, pack8(f));
+          packed[v] = pack8(f);
+        }
+        if (wide_ok) {  // full 32-byte sectors per store
+          st32(crow + c * 32, packed[0], packed[1]);
+          st32(crow + c * 32 + 16, packed[2], packed[3]);
+        } else {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) st8(crow + c * 32 + v * 8, packed[v]);
         }
       } else {
         for (int j = 0; j < 32; ++j) {
@@ -330,15 +348,23 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ---- 256x256 tiles on CTA pairs ----------------------------------------------------------
-constexpr int P_STAGES = 6;
+// A pipeline stage holds KSUB sub-tiles of 64 K-elements (KSUB x 32 KB per CTA); the ring
+// always spans 192 KB.  KSUB = 2 halves the number of barrier waits / commits the MMA
+// thread executes per unit of tensor work (its instruction stream, not the tensor pipe,
+// is what paces the loop at KSUB = 1).
 constexpr int P_HALF = 128;                                    // rows of A and of B staged per CTA
-constexpr int P_A_BYTES = P_HALF * BK * 2, P_B_BYTES = P_HALF * BK * 2, P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
+constexpr int P_A_BYTES = P_HALF * BK * 2, P_B_BYTES = P_HALF * BK * 2, P_SUB_BYTES = P_A_BYTES + P_B_BYTES;
 constexpr int P_TILE_M = 2 * P_HALF, P_TILE_N = 2 * P_HALF;
+constexpr int P_RING_BYTES = 6 * P_SUB_BYTES;
 
+template <int KSUB>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int P_STAGES = 6 / KSUB;
+  constexpr int P_STAGE_BYTES = KSUB * P_SUB_BYTES;
+  constexpr int STAGE_K = KSUB * BK;
   __shared__ __align__(8) uint64_t bar_full[P_STAGES], bar_empty[P_STAGES], bar_acc_full[2], bar_acc_empty[2];
   __shared__ uint32_t tmem_base_slot;
 
@@ -348,7 +374,7 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
   const int tiles_m = (p.M + P_TILE_M - 1) / P_TILE_M, tiles_n = (p.N + P_TILE_N - 1) / P_TILE_N;
   const int num_tiles = tiles_m * tiles_n;
-  const int num_kb = (p.K + BK - 1) / BK;
+  const int num_kb = (p.K + STAGE_K - 1) / STAGE_K;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < P_STAGES; ++s) {
@@ -384,8 +410,11 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           if (leader) mbar_expect_tx(full_local, 2 * P_STAGE_BYTES);
           const uint32_t full_leader = map_to_cta(full_local, 0);
           const uint32_t sa = smem_addr(smem + stage * P_STAGE_BYTES);
-          tma_load_2d_pair(sa, &map_a, full_leader, kb * BK, m0);
-          tma_load_2d_pair(sa + P_A_BYTES, &map_b, full_leader, kb * BK, nb0);
+#pragma unroll
+          for (int u = 0; u < KSUB; ++u) {  // columns past K read as zeros (TMA fill)
+            tma_load_2d_pair(sa + u * P_SUB_BYTES, &map_a, full_leader, kb * STAGE_K + u * BK, m0);
+            tma_load_2d_pair(sa + u * P_SUB_BYTES + P_A_BYTES, &map_b, full_leader, kb * STAGE_K + u * BK, nb0);
+          }
           if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -414,7 +443,14 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           const uint32_t sa = smem_addr(smem + stage * P_STAGE_BYTES);
           const uint64_t adesc = smem_desc_kmajor_sw128(sa), bdesc = smem_desc_kmajor_sw128(sa + P_A_BYTES);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) umma_bf16_pair(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+          for (int u = 0; u < KSUB; ++u) {
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k) {
+              // next sub-tile: + P_SUB_BYTES; next 16 K-elements inside a 128-byte swizzled row: + 32 bytes (16-byte units)
+              const uint32_t off = u * (P_SUB_BYTES >> 4) + 2 * k;
+              umma_bf16_pair(tmem_d, adesc + off, bdesc + off, idesc, (kb | u | k) != 0);
+            }
+          }
           umma_commit_pair(smem_addr(&bar_empty[stage]));  // frees the slot in both CTAs
           if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
         }
@@ -488,13 +524,15 @@ static int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t co
 // C[M,N] = A[M,K] * B[N,K]^T with epilogue (0 store, 1 C += result, 2 result + residual).
 // lda / ldb / ldc / ldr in elements; A, B rows must be 16-byte aligned (ld multiple of 8).
 // `status` is a device int the kernel writes a non-zero code to if a bounded wait ran out.
-// variant: 0 = choose (CTA pairs when M > 128), 1 = one CTA per 128x256 tile, 2 = CTA pairs.
+// variant: 0 = choose (CTA pairs when M > 128), 1 = one CTA per 128x256 tile, 2 = CTA pairs with
+// 64-wide K stages, 3 = CTA pairs with 128-wide K stages.
 int launch_gemm_tn_tcgen05(const void* a, const void* b, void* c, const void* residual, int M, int N, int K, int64_t lda,
                            int64_t ldb, int64_t ldc, int64_t ldr, int epilogue, int* status, int variant, cudaStream_t stream) {
   using namespace tc;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda & 7) || (ldb & 7) || (reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15)) return -1;
-  const bool pairs = variant == 2 || (variant == 0 && M > BM);
+  if (variant == 0) variant = M > BM ? kDefaultPairVariant : 1;
+  const bool pairs = variant >= 2;
   CUtensorMap map_a, map_b;
   int rc = make_map(&map_a, a, M, K, lda, BM);
   if (rc) return rc;
@@ -504,15 +542,17 @@ int launch_gemm_tn_tcgen05(const void* a, const void* b, void* c, const void* re
   count_launch(1);
   if (pairs) {
     static bool configured2 = false;
-    constexpr int smem2 = P_STAGES * P_STAGE_BYTES + 1024;
+    constexpr int smem2 = P_RING_BYTES + 1024;
     if (!configured2) {
-      if (cudaFuncSetAttribute(gemm_tn_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) != cudaSuccess) return -2;
+      if (cudaFuncSetAttribute(gemm_tn_2cta_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) != cudaSuccess) return -2;
+      if (cudaFuncSetAttribute(gemm_tn_2cta_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) != cudaSuccess) return -2;
       configured2 = true;
     }
     const int tiles = ((M + P_TILE_M - 1) / P_TILE_M) * ((N + P_TILE_N - 1) / P_TILE_N);
     const int max_pairs = kNumSM / 2;
     const int grid = 2 * (tiles < max_pairs ? tiles : max_pairs);
-    gemm_tn_2cta_kernel<<<grid, THREADS, smem2, stream>>>(map_a, map_b, p);
+    if (variant == 3) gemm_tn_2cta_kernel<2><<<grid, THREADS, smem2, stream>>>(map_a, map_b, p);
+    else gemm_tn_2cta_kernel<1><<<grid, THREADS, smem2, stream>>>(map_a, map_b, p);
     return cudaGetLastError() == cudaSuccess ? 0 : -3;
   }
   static bool configured = false;

@@ -36,15 +36,16 @@ def test_single_tile():
 def test_single_pair_tile():
     """One 256x256 tile on one CTA pair (tcgen05 cta_group::2), one k-block."""
     _run(256, 256, 64, variant=2)
+    _run(256, 256, 64, variant=3)
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 512), (256, 512, 256), (200, 300, 136), (2048, 4096, 1024), (77, 1000, 72), (1000, 520, 4096)])
-@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("variant", [1, 2, 3])
 def test_shapes_including_ragged_edges(M, N, K, variant):
     _run(M, N, K, variant=variant)
 
 
-@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("variant", [1, 2, 3])
 def test_strided_a_and_epilogues(variant):
     _run(256, 512, 192, lda_pad=64, variant=variant)
     _run(384, 768, 320, epilogue=1, variant=variant)
@@ -55,5 +56,7 @@ def test_strided_a_and_epilogues(variant):
 def test_many_tiles_per_pair_wraps_the_ring():
     """More tiles than CTA pairs and more k-blocks than pipeline stages: exercises the
     phase wrap of every barrier and both accumulator buffers."""
-    _run(2048, 6144, 1024, variant=2)
-    _run(4096, 5120, 640, epilogue=2, variant=2)
+    for variant in (2, 3):
+        _run(2048, 6144, 1024, variant=variant)
+        _run(4096, 5120, 640, epilogue=2, variant=variant)
+        _run(512, 768, 192, variant=variant)  # K not a multiple of the 128-wide stage: zero-filled tail
