@@ -25,7 +25,10 @@ from speculators_b200.ops import AttnSpec
 __all__ = ["dense_peagle_mask", "peagle_attn_spec"]
 
 
-def peagle_attn_spec(anchor_pos, depth, document_ids, num_depths: int, sliding_window: int | None = None) -> AttnSpec:
+def peagle_attn_spec(anchor_pos, depth, document_ids, num_depths: int, sliding_window: int | None = None,
+                     row_valid: torch.Tensor | None = None) -> AttnSpec:
+    """``row_valid`` (bool ``[n]``, optional): rows marked False (padding of the
+    fixed-shape sampler) see nothing and are nobody's key."""
     doc = document_ids.reshape(-1)
     T = doc.shape[0]
     n = anchor_pos.shape[0]
@@ -36,6 +39,8 @@ def peagle_attn_spec(anchor_pos, depth, document_ids, num_depths: int, sliding_w
         lo = torch.maximum(lo, anchor_pos + depth - int(sliding_window) + 1)
     hi = anchor_pos + 1
     pad = doc[anchor_pos] == -1
+    if row_valid is not None:
+        pad = pad | ~row_valid
     hi = torch.where(pad, torch.zeros_like(hi), hi)
     lo = torch.where(pad, torch.zeros_like(lo), lo)
     extra = None
@@ -44,7 +49,13 @@ def peagle_attn_spec(anchor_pos, depth, document_ids, num_depths: int, sliding_w
         table = torch.full((num_depths, T), -1, dtype=torch.int32, device=device)
         rows = torch.arange(n, device=device)
         deep = depth >= 1
-        table[depth[deep], anchor_pos[deep]] = (rows[deep] - T).to(torch.int32)
+        if row_valid is None:
+            table[depth[deep], anchor_pos[deep]] = (rows[deep] - T).to(torch.int32)
+        else:  # fixed shapes: scatter every row, invalid ones into a spare column
+            col = torch.where(deep & row_valid, anchor_pos, torch.full_like(anchor_pos, T))
+            wide = torch.full((num_depths, T + 1), -1, dtype=torch.int32, device=device)
+            wide[depth, col] = (rows - T).to(torch.int32)
+            table = wide[:, :T]
         cols = []
         for d in range(1, num_depths):
             cand = table[d][anchor_pos]

@@ -22,12 +22,19 @@ from speculators_b200.model import SpeculatorModel
 from speculators_b200.models.eagle3.core import Eagle3DraftModel
 from speculators_b200.models.peagle.attention import peagle_attn_spec
 from speculators_b200.models.peagle.config import PEagleSpeculatorConfig
-from speculators_b200.models.peagle.data import generate_cod_sample_indices
+from speculators_b200.models.peagle.data import generate_cod_sample_indices, generate_cod_sample_indices_fixed
 from speculators_b200.models.peagle.metrics import compute_metrics
 from speculators_b200.models.utils import resolve_target_layer_ids
 from speculators_b200.proposals.greedy import GreedyTokenProposalConfig
 
 __all__ = ["PEagleDraftModel"]
+
+
+def _fixed_shape_default(explicit: bool | None) -> bool:
+    """COD sampling with argument-only shapes: explicit choice, else ``SB200_PEAGLE_FIXED_SHAPE=1``."""
+    import os
+
+    return bool(explicit) if explicit is not None else os.environ.get("SB200_PEAGLE_FIXED_SHAPE") == "1"
 
 
 @SpeculatorModel.register("peagle")
@@ -39,14 +46,20 @@ class PEagleDraftModel(Eagle3DraftModel):
 
     def __init__(self, config: PEagleSpeculatorConfig):
         super().__init__(config)
+        # with the fixed-shape sampler every tensor shape of the step is static
+        self.cuda_graph_safe = _fixed_shape_default(None)
         self.mask_token_id = config.mask_token_id
         self.mask_hidden = nn.Parameter(torch.randn(1, 1, self.num_aux * self.hidden_size))
 
     def forward(
         self, hidden_states, input_ids, document_ids, position_ids=None, loss_mask=None, verifier_last_hidden_states=None,
         loss_config: LossConfig | None = None, max_anchors: int | None = None, num_depths: int = 8,
-        down_sample_ratio: float = 0.7, down_sample_ratio_min: float = 0.2, **_,
+        down_sample_ratio: float = 0.7, down_sample_ratio_min: float = 0.2, fixed_shape: bool = False, cod_sample=None, **_,
     ):
+        """``fixed_shape``: draw the COD sample with shapes that depend only on the
+        arguments (rows the mask rules out are carried as inert padding), which makes the
+        step capturable in a CUDA graph.  ``cod_sample``: a ready
+        ``(anchor_pos, depth[, row_valid])`` to use instead of drawing one."""
         if verifier_last_hidden_states is None:
             raise ValueError("verifier_last_hidden_states required for training")
         if self.mask_token_id is None:
@@ -56,10 +69,20 @@ class PEagleDraftModel(Eagle3DraftModel):
         dtype = self.fc.weight.dtype
         if loss_mask is None:
             loss_mask = torch.ones_like(input_ids, dtype=torch.float32)
-        anchor_pos, depth = generate_cod_sample_indices(
-            T, loss_mask, num_depths=num_depths, down_sample_ratio=down_sample_ratio,
-            down_sample_ratio_min=down_sample_ratio_min, max_anchors=max_anchors,
-        )
+        row_valid = None
+        if cod_sample is not None:
+            anchor_pos, depth, *rest = cod_sample
+            row_valid = rest[0] if rest else None
+        elif fixed_shape:
+            anchor_pos, depth, row_valid = generate_cod_sample_indices_fixed(
+                T, loss_mask, num_depths=num_depths, down_sample_ratio=down_sample_ratio,
+                down_sample_ratio_min=down_sample_ratio_min, max_anchors=max_anchors,
+            )
+        else:
+            anchor_pos, depth = generate_cod_sample_indices(
+                T, loss_mask, num_depths=num_depths, down_sample_ratio=down_sample_ratio,
+                down_sample_ratio_min=down_sample_ratio_min, max_anchors=max_anchors,
+            )
         orig = anchor_pos + depth
         depth0 = depth == 0
         ids = torch.where(depth0, input_ids.reshape(-1)[orig], torch.full_like(orig, self.mask_token_id))
@@ -69,8 +92,9 @@ class PEagleDraftModel(Eagle3DraftModel):
         hidden = self._project_aux(sampled)
 
         doc = document_ids.reshape(-1).to(device)
-        full_spec = peagle_attn_spec(anchor_pos, depth, doc, num_depths, None) if self.uses_full_attn else None
-        win_spec = peagle_attn_spec(anchor_pos, depth, doc, num_depths, self.sliding_window) if self.uses_sliding_window_attn else None
+        full_spec = peagle_attn_spec(anchor_pos, depth, doc, num_depths, None, row_valid) if self.uses_full_attn else None
+        win_spec = (peagle_attn_spec(anchor_pos, depth, doc, num_depths, self.sliding_window, row_valid)
+                    if self.uses_sliding_window_attn else None)
         self.rotary_emb.ensure(int(T) + num_depths + 1)
         for li, layer in enumerate(self.layers):
             spec = win_spec if li in self.sliding_window_indices else full_spec
@@ -83,7 +107,8 @@ class PEagleDraftModel(Eagle3DraftModel):
             vl = verifier_last_hidden_states.reshape(T, -1).to(dtype)[orig]
             targets = ops.linear(self.verifier_norm(vl), self.verifier_lm_head.weight)
         loss, metrics = compute_metrics(
-            logits.unsqueeze(0), targets.unsqueeze(0), loss_mask, anchor_pos, depth, num_depths, loss_config=loss_config
+            logits.unsqueeze(0), targets.unsqueeze(0), loss_mask, anchor_pos, depth, num_depths, loss_config=loss_config,
+            row_valid=row_valid,
         )
         return None, loss, metrics
 
@@ -121,5 +146,6 @@ class PEagleDraftModel(Eagle3DraftModel):
             "num_depths": kwargs.get("num_depths", 8),
             "down_sample_ratio": kwargs.get("down_sample_ratio", 0.7),
             "down_sample_ratio_min": kwargs.get("down_sample_ratio_min", 0.2),
+            "fixed_shape": _fixed_shape_default(kwargs.get("cod_fixed_shape")),
         }
         return dict(shared), dict(shared)

@@ -13,7 +13,7 @@ from __future__ import annotations
 
 import torch
 
-__all__ = ["generate_cod_sample_indices"]
+__all__ = ["cod_capacities", "generate_cod_sample_indices", "generate_cod_sample_indices_fixed"]
 
 
 def generate_cod_sample_indices(
@@ -47,3 +47,75 @@ def generate_cod_sample_indices(
         anchors.append(picked - d)
         depths.append(torch.full((picked.numel(),), d, dtype=torch.long, device=device))
     return torch.cat(anchors), torch.cat(depths)
+
+
+def cod_capacities(seq_length: int, num_depths: int, down_sample_ratio: float, down_sample_ratio_min: float,
+                   max_anchors: int | None = None) -> list[int]:
+    """Upper bound of the number of rows per depth (depth 0 first): what the sampler
+    would keep if every position were inside the loss mask."""
+    seeds = seq_length if max_anchors is None else min(seq_length, max_anchors)
+    caps = [seq_length]
+    for d in range(1, num_depths):
+        want = int(max(0, seeds - d) * max(down_sample_ratio**d, down_sample_ratio_min))
+        if want <= 0:
+            break
+        caps.append(want)
+    return caps
+
+
+def _random_subset(member: torch.Tensor, count: torch.Tensor, capacity: int, generator=None) -> tuple[torch.Tensor, torch.Tensor]:
+    """``min(count, member.sum())`` positions drawn uniformly without replacement from the
+    set ``member`` (bool ``[T]``), ascending, in a ``[capacity]`` array padded with ``T``;
+    second result: which entries are real.  Fixed shapes, no host synchronisation."""
+    T = member.shape[0]
+    keys = torch.rand(T, device=member.device, generator=generator)
+    keys = torch.where(member, keys, torch.full_like(keys, 2.0))
+    order = torch.argsort(keys)[:capacity]  # members first, in random order
+    take = torch.minimum(count, member.sum())
+    real = torch.arange(capacity, device=member.device) < take
+    picked = torch.where(real, order, torch.full_like(order, T)).sort().values
+    return picked, picked < T
+
+
+def generate_cod_sample_indices_fixed(
+    seq_length: int, loss_mask: torch.Tensor, num_depths: int = 8, down_sample_ratio: float = 0.7,
+    down_sample_ratio_min: float = 0.2, filter_position_zero: bool = True, max_anchors: int | None = None, generator=None,
+):
+    """Same sampling law as ``generate_cod_sample_indices`` with shapes that depend only
+    on the arguments (``sum(cod_capacities(...))`` rows), so the step can be captured in a
+    CUDA graph: -> ``(anchor_pos, depth, row_valid)``.  Rows that the variable-shape
+    sampler would not have produced carry ``row_valid = False`` (``anchor_pos = 0``); every
+    count that depends on the mask (valid positions, pool sizes, ``want``) stays on the
+    device."""
+    T = seq_length
+    mask = loss_mask.reshape(-1)
+    device = mask.device
+    is_valid = mask == 1
+    caps = cod_capacities(T, num_depths, down_sample_ratio, down_sample_ratio_min, max_anchors)
+    n_valid = is_valid.sum()
+    if max_anchors is not None and max_anchors < T:
+        seed_pos, seed_real = _random_subset(is_valid, torch.full_like(n_valid, max_anchors), max_anchors, generator)
+        pool = torch.zeros(T + 1, dtype=torch.bool, device=device)
+        pool[seed_pos] = seed_real
+        pool = pool[:T]
+        n_seeds = torch.clamp(n_valid, max=max_anchors)
+    else:
+        pool, n_seeds = is_valid, n_valid
+    anchors = [torch.arange(T, device=device)]
+    depths = [torch.zeros(T, dtype=torch.long, device=device)]
+    valids = [torch.ones(T, dtype=torch.bool, device=device)]
+    for d, cap in enumerate(caps[1:], start=1):
+        factor = max(down_sample_ratio**d, down_sample_ratio_min)
+        want = (torch.clamp(n_seeds - d, min=0).double() * factor).floor().long()
+        picked, real = _random_subset(pool, want, cap, generator)
+        nxt = torch.where(real, (picked + 1) % T, torch.full_like(picked, T))
+        ok = real & is_valid[nxt.clamp(max=T - 1)]
+        if filter_position_zero:
+            ok = ok & (nxt != 0)
+        nxt_pool = torch.zeros(T + 1, dtype=torch.bool, device=device)
+        nxt_pool[torch.where(ok, nxt, torch.full_like(nxt, T))] = True
+        pool = nxt_pool[:T]
+        anchors.append(torch.where(real, picked - d, torch.zeros_like(picked)))
+        depths.append(torch.full((cap,), d, dtype=torch.long, device=device))
+        valids.append(real)
+    return torch.cat(anchors), torch.cat(depths), torch.cat(valids)

@@ -12,12 +12,15 @@ from speculators_b200.models.metrics import compute_accuracy_multi_step
 __all__ = ["compute_metrics"]
 
 
-def compute_metrics(logits, targets, loss_mask, anchor_pos, depth, num_depths: int, loss_config: LossConfig | None = None):
+def compute_metrics(logits, targets, loss_mask, anchor_pos, depth, num_depths: int, loss_config: LossConfig | None = None,
+                    row_valid: torch.Tensor | None = None):
     if loss_config is None:
         loss_config = {"kl_div": (kl_div_loss, 1.0)}
     device = logits.device
     n = logits.shape[1]
     sampled_mask = loss_mask.reshape(-1)[anchor_pos + depth].unsqueeze(0)
+    if row_valid is not None:  # padding rows of the fixed-shape sampler take no part
+        sampled_mask = sampled_mask * row_valid.to(sampled_mask.dtype).unsqueeze(0)
     pos = depth.unsqueeze(0)
     per_term, pred_ids, target_ids = rowwise_terms(
         loss_config, logits.reshape(n, -1), targets.reshape(n, -1), shift=0, rows=n, active=sampled_mask.reshape(-1).bool()

@@ -27,6 +27,8 @@ __all__ = [
     "adamw_step_",
     "eagle3_input_concat",
     "fused_row_loss",
+    "check_gemm_status",
+    "gemm_status",
     "linear",
     "masked_attention",
     "masked_attention_reference",
@@ -52,6 +54,53 @@ def _use_native(t: torch.Tensor) -> bool:
 
 
 # --------------------------------------------------------------------------- linear
+_GEMM_STATUS: dict[int, torch.Tensor] = {}
+
+
+def _own_gemm_enabled() -> bool:
+    import os
+
+    return os.environ.get("SB200_LINEAR_GEMM", "tcgen05") != "cublas"
+
+
+def _gemm_operand_ok(t: torch.Tensor) -> bool:
+    return (t.is_cuda and t.dtype == torch.bfloat16 and t.dim() == 2 and t.stride(1) == 1 and t.stride(0) % 8 == 0
+            and t.data_ptr() % 16 == 0)
+
+
+def gemm_status(device: torch.device) -> torch.Tensor:
+    """The device word the tcgen05 GEMM writes a non-zero code to if one of its bounded
+    waits ever runs out (it should stay 0; read it where a host sync is acceptable)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _GEMM_STATUS:
+        _GEMM_STATUS[idx] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+    return _GEMM_STATUS[idx]
+
+
+def check_gemm_status() -> None:
+    """Raise if a tcgen05 GEMM launched by this process reported a wait that ran out."""
+    for idx, word in _GEMM_STATUS.items():
+        code = int(word.item())
+        if code:
+            word.zero_()
+            raise RuntimeError(f"tcgen05 GEMM on cuda:{idx} gave up waiting (code {code}: 1 producer, 2 MMA issuer, 3 epilogue)")
+
+
+def _forward_gemm(x2: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None) -> torch.Tensor:
+    """``x2 @ w.T (+ residual)`` for 2-D operands.  bf16 CUDA operands with 16-byte aligned
+    rows run on the package's tcgen05 kernel (the residual is read in its epilogue, no
+    copy of it is made); everything else goes to the library."""
+    if _gemm_operand_ok(x2) and _gemm_operand_ok(w) and _own_gemm_enabled() and (
+        residual is None or (_gemm_operand_ok(residual) and residual.shape == (x2.shape[0], w.shape[0]))
+    ):
+        out = torch.empty((x2.shape[0], w.shape[0]), dtype=x2.dtype, device=x2.device)
+        native().gemm_tn(x2, w, out, residual, 2 if residual is not None else 0, gemm_status(x2.device))
+        return out
+    if residual is not None:
+        return torch.addmm(residual, x2, w.t())
+    return x2 @ w.t()
+
+
 class _LinearFn(torch.autograd.Function):
     """``y = x @ W[rows].T (+ residual)`` with the weight gradient accumulated in place.
 
@@ -67,10 +116,7 @@ class _LinearFn(torch.autograd.Function):
         # x is [rows, in]; the result is a fresh tensor (never a view), so callers may
         # rotate / normalise it in place
         w = weight if r0 is None else weight[r0:r1]
-        if residual is not None:
-            y = torch.addmm(residual, x, w.t())
-        else:
-            y = x @ w.t()
+        y = _forward_gemm(x, w, residual)
         ctx.save_for_backward(x, weight)
         ctx.rows = (r0, r1)
         ctx.has_residual = residual is not None
@@ -111,9 +157,11 @@ class _LinearFn(torch.autograd.Function):
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None, residual: torch.Tensor | None = None,
            rows: tuple[int, int] | None = None) -> torch.Tensor:
-    """``x @ weight[rows].T (+ bias) (+ residual)``.  The matrix products are plain
-    library GEMMs (cuBLASLt through ATen); what this wrapper adds is epilogue
-    fusion of the residual and in-place weight-gradient accumulation."""
+    """``x @ weight[rows].T (+ bias) (+ residual)``.  On CUDA in bf16 the forward product
+    runs on the package's tcgen05 GEMM with the residual read in its epilogue
+    (``SB200_LINEAR_GEMM=cublas`` sends it to the library instead); the two backward
+    products are library GEMMs, the weight gradient accumulating in place into the
+    engine's flat gradient buffer."""
     if x.is_cuda and (weight.requires_grad or x.requires_grad) and torch.is_grad_enabled():
         r0, r1 = rows if rows is not None else (None, None)
         lead = x.shape[:-1]
@@ -127,6 +175,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
         return y
     w = weight if rows is None else weight[rows[0] : rows[1]]
     b = bias if (bias is None or rows is None) else bias[rows[0] : rows[1]]
+    if x.is_cuda and x.dtype == torch.bfloat16 and b is None and not torch.is_grad_enabled() and _own_gemm_enabled():
+        x2 = x.reshape(-1, x.shape[-1])
+        res2 = residual.reshape(-1, residual.shape[-1]) if residual is not None else None
+        return _forward_gemm(x2, w, res2).view(*x.shape[:-1], w.shape[0])
     y = F.linear(x, w, b)
     return y if residual is None else y + residual
 

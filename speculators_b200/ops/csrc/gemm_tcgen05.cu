@@ -40,7 +40,7 @@ constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTE
 constexpr int THREADS = 192;
 constexpr int TMEM_COLS = 512;
 constexpr uint32_t POLL_LIMIT = 1u << 22;
-constexpr int kDefaultPairVariant = 2;
+constexpr int kDefaultPairVariant = 3;
 
 enum Epilogue : int { kStore = 0, kAccumulate = 1, kAddResidual = 2 };
 enum Status : int { kOk = 0, kTimeoutProducer = 1, kTimeoutMma = 2, kTimeoutEpilogue = 3 };

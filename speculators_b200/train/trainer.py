@@ -353,7 +353,7 @@ class Trainer:
                 self.checkpointer.load_scheduler_state_dict(self.schedulers)
         use_graph = cfg.use_cuda_graph if cfg.use_cuda_graph is not None else self.device_type == "cuda"
         # only models whose forward has fixed shapes and no host synchronisation can be replayed
-        use_graph = use_graph and bool(getattr(type(self.model), "cuda_graph_safe", False))
+        use_graph = use_graph and bool(getattr(self.model, "cuda_graph_safe", False))
         if os.environ.get("SB200_DISABLE_CUDA_GRAPH") == "1":
             use_graph = False
         self._graphed = None
@@ -436,6 +436,10 @@ class Trainer:
                 doc = batch.get("document_ids") if isinstance(batch, dict) else None
                 num_tokens = int((doc != -1).sum().item()) if doc is not None else 0
                 profile = self.timer.profile(num_tokens)
+                if self.device_type == "cuda":
+                    from speculators_b200.ops import check_gemm_status
+
+                    check_gemm_status()  # the profile read above already synchronised
                 if self.is_distributed and metrics:
                     keys = list(metrics)
                     stacked = torch.stack([metrics[k].float().reshape(()) for k in keys])

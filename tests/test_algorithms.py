@@ -82,6 +82,60 @@ def test_peagle_forward_backward(tiny_verifier_dir, tiny_vocab_maps):
     assert {"position_0_acc_sum", "position_3_acc_total", "full_acc_sum"} <= set(metrics)
 
 
+def test_cod_fixed_shape_sampler_and_inert_padding(tiny_verifier_dir, tiny_vocab_maps):
+    from speculators_b200.models.peagle.data import cod_capacities, generate_cod_sample_indices_fixed
+
+    torch.manual_seed(0)
+    T, D = 64, 4
+    mask = (torch.rand(1, T) > 0.3).float()
+    caps = cod_capacities(T, D, 0.7, 0.2)
+    assert caps == [64, int(63 * 0.7), int(62 * 0.49), int(61 * 0.343)]
+    a, d, ok = generate_cod_sample_indices_fixed(T, mask, num_depths=D)
+    assert a.shape == d.shape == ok.shape == (sum(caps),) and ok[:T].all() and torch.equal(a[:T], torch.arange(T))
+    # the shape depends on the arguments only, not on the mask
+    assert generate_cod_sample_indices_fixed(T, torch.zeros(1, T), num_depths=D)[0].shape == a.shape
+    assert not generate_cod_sample_indices_fixed(T, torch.zeros(1, T), num_depths=D)[2][T:].any()
+    va, vd = a[ok], d[ok]
+    pairs = set(zip(va.tolist(), vd.tolist()))
+    for ai, di in pairs:  # every rollout member has its predecessor, and stands on a supervised token
+        assert di == 0 or ai < 0 or (ai, di - 1) in pairs
+    deep = vd >= 1
+    assert (mask[0, (va + vd)[deep]] == 1).all()
+    # same law as the variable-shape sampler: depth 1 keeps int((n_valid - 1) * 0.7) rows (the pool is large enough)
+    n_valid = int(mask.sum())
+    assert int((ok & (d == 1)).sum()) == int((n_valid - 1) * 0.7)
+    ref_a, ref_d = generate_cod_sample_indices(T, mask, num_depths=D)
+    assert int((ref_d == 1).sum()) == int((n_valid - 1) * 0.7)
+    # max_anchors caps the seeds
+    a2, d2, ok2 = generate_cod_sample_indices_fixed(T, mask, num_depths=D, max_anchors=10)
+    assert a2.numel() == sum(cod_capacities(T, D, 0.7, 0.2, 10)) and int((ok2 & (d2 == 1)).sum()) == int(9 * 0.7)
+
+    # padding rows are inert: a variable-shape sample and the same sample padded to the
+    # fixed shape (in depth-major order) give the same loss and metrics
+    model = _peagle(tiny_verifier_dir, tiny_vocab_maps, layers=2)
+    batch = make_tiny_batch()
+    T = batch["input_ids"].shape[1]
+    kw, _ = PEagleDraftModel.get_trainer_kwargs(loss_fn="kl_div", num_depths=D)
+    torch.manual_seed(3)
+    va, vd = generate_cod_sample_indices(T, batch["loss_mask"], num_depths=D)
+    caps = cod_capacities(T, D, 0.7, 0.2)
+    pa, pd, pv = [], [], []
+    for depth_i, cap in enumerate(caps):
+        rows = va[vd == depth_i]
+        pad = cap - rows.numel()
+        pa.append(torch.cat([rows, torch.zeros(pad, dtype=torch.long)]))
+        pd.append(torch.full((cap,), depth_i, dtype=torch.long))
+        pv.append(torch.cat([torch.ones(rows.numel(), dtype=torch.bool), torch.zeros(pad, dtype=torch.bool)]))
+    _, loss_var, m_var = model(**batch, **kw, cod_sample=(va, vd))
+    _, loss_fix, m_fix = model(**batch, **kw, cod_sample=(torch.cat(pa), torch.cat(pd), torch.cat(pv)))
+    torch.testing.assert_close(loss_fix, loss_var, rtol=1e-5, atol=1e-6)
+    for key in m_var:
+        torch.testing.assert_close(m_fix[key].float(), m_var[key].float(), rtol=1e-5, atol=1e-6)
+    _, loss_drawn, _ = model(**batch, **kw, fixed_shape=True)
+    loss_drawn.backward()
+    assert torch.isfinite(loss_drawn) and model.mask_hidden.grad is not None
+
+
 @pytest.mark.skipif(not HAVE_REF, reason="reference not installed")
 def test_peagle_parity_with_reference(tiny_verifier_dir, tiny_vocab_maps):
     ref_core = _import_ref("speculators.models.peagle.core")
