@@ -273,7 +273,10 @@ def run_ours(args):
             "data": "synthetic (seeded uniform tokens; random-init verifier forward for hidden states; random-init draft)",
             "impl": "ours",
             "config": {"model": "eagle3 1-layer draft for llama-3.1-8b-arch verifier" if args.model == "llama31_8b" else "tiny", "global_batch": world,
-                       "seq_len": args.seq_len, "parallelism": f"dp{world}" + ("-sharded" if world > 1 else ""), "draft_vocab": draft_vocab,
+                       "seq_len": args.seq_len, "parallelism": f"dp{world}" + ("-sharded" if world > 1 else ""),
+                       "optimizer_comm": ("nvls multimem" if getattr(trainer.engine, "nvls", False) else "nvlink p2p" if getattr(trainer.engine, "p2p", False)
+                                          else "nccl" if world > 1 else "none"),
+                       "draft_vocab": draft_vocab,
                        "ttt_steps": args.ttt_steps, "optimizer": "adamw lr 1e-4",
                        "cuda_graph": trainer._graphed is not None,
                        "l2": "per-step working set (1.9 GB of weights + activations) exceeds the 126 MB L2; 2 distinct input batches alternate"},

@@ -17,6 +17,13 @@
 //             sure nobody runs ahead while a peer still writes its weights or reads its
 //             gradients.
 //
+// When the gradient and weight buffers are also mapped through an NVLink multicast object
+// (NVSwitch), the two bulk transfers go through the switch instead of through per-peer
+// loads and stores: kernel A reads its shard with multimem.ld_reduce (the switch adds the
+// ranks' copies, fp32 accumulation, one bf16 rounding) and kernel B writes it with
+// multimem.st (the switch replicates the store to every rank), so a rank moves 1/world of
+// the buffer per direction instead of (world-1)/world.
+//
 // Barriers are generation counters in peer memory (release store / acquire load at
 // system scope).  The generation is a device-side step counter, so a captured CUDA
 // graph can be replayed.  Every wait is bounded; on expiry a status word is set, the
@@ -47,6 +54,8 @@ struct Params {
   int64_t shard;  // elements per rank (multiple of 8)
   const __nv_bfloat16* g[kMaxRanks];
   __nv_bfloat16* w[kMaxRanks];
+  const __nv_bfloat16* g_mc;  // multicast mapping of the gradient buffers (nullptr: per-peer loads)
+  __nv_bfloat16* w_mc;        // multicast mapping of the weight buffers (nullptr: per-peer stores)
   uint32_t* ctl[kMaxRanks];
   float* master;
   float* m;
@@ -72,6 +81,23 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
   uint32_t v;
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
+}
+
+// Sum of the eight bf16 at the same offset of every rank's buffer, added in the switch.
+__device__ __forceinline__ bf16x8 multimem_ld_reduce8(const __nv_bfloat16* mc_ptr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc_ptr)
+               : "memory");
+  return *reinterpret_cast<bf16x8*>(&v);
+}
+// Store sixteen bytes to the same offset of every rank's buffer.
+__device__ __forceinline__ void multimem_st8(__nv_bfloat16* mc_ptr, const bf16x8& val) {
+  const uint4 v = *reinterpret_cast<const uint4*>(&val);
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+               ::"l"(mc_ptr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
 }
 
 // Bounded wait until *p == want (acquire at the given scope).
@@ -133,13 +159,17 @@ reduce_scatter_norm_kernel(const Params p) {
     const int64_t nvec = p.shard >> 3;
     for (int64_t vi = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; vi < nvec; vi += (int64_t)gridDim.x * blockDim.x) {
       float sum[8];
+      if (p.g_mc != nullptr) {
+        unpack8(multimem_ld_reduce8(p.g_mc + base + (vi << 3)), sum);
+      } else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) sum[j] = 0.f;
-      for (int q = 0; q < p.world; ++q) {  // fixed order: deterministic sum
-        float f[8];
-        unpack8(ld8(p.g[q] + base + (vi << 3)), f);
+        for (int j = 0; j < 8; ++j) sum[j] = 0.f;
+        for (int q = 0; q < p.world; ++q) {  // fixed order: deterministic sum
+          float f[8];
+          unpack8(ld8(p.g[q] + base + (vi << 3)), f);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) sum[j] += f[j];
+          for (int j = 0; j < 8; ++j) sum[j] += f[j];
+        }
       }
       float4* dst = reinterpret_cast<float4*>(p.gred + (vi << 3));
       dst[0] = make_float4(sum[0], sum[1], sum[2], sum[3]);
@@ -218,7 +248,11 @@ adamw_all_gather_kernel(const Params p) {
         reinterpret_cast<float4*>(p.v + i0)[h] = make_float4(vv[0], vv[1], vv[2], vv[3]);
       }
       const bf16x8 packed = pack8(out);
-      for (int q = 0; q < p.world; ++q) st8(p.w[q] + base + i0, packed);  // all-gather by push
+      if (p.w_mc != nullptr) {
+        multimem_st8(p.w_mc + base + i0, packed);  // all-gather by one store, replicated in the switch
+      } else {
+        for (int q = 0; q < p.world; ++q) st8(p.w[q] + base + i0, packed);  // all-gather by push
+      }
     }
   }
   // closing barrier: the last block of this rank signals every peer and waits for all of them
@@ -245,9 +279,10 @@ int fused_optim_ctl_words() { return fo::kCtlWords; }
 int fused_optim_num_partials() { return fo::kBlocks; }
 
 // Pointers are device addresses valid on the calling rank (peer-mapped for q != rank).
+// g_mc / w_mc: multicast addresses of the gradient / weight buffers, or nullptr for per-peer access.
 int launch_fused_sharded_adamw(int world, int rank, int64_t shard, const void* const* g_peers, void* const* w_peers,
-                               void* const* ctl_peers, float* master, float* m, float* v, float* gred, float* partial,
-                               const float* hyper, int* status, cudaStream_t stream) {
+                               void* const* ctl_peers, const void* g_mc, void* w_mc, float* master, float* m, float* v, float* gred,
+                               float* partial, const float* hyper, int* status, cudaStream_t stream) {
   if (world < 1 || world > fo::kMaxRanks || rank < 0 || rank >= world || shard <= 0 || (shard & 7)) return -1;
   fo::Params p{};
   p.world = world;
@@ -258,6 +293,8 @@ int launch_fused_sharded_adamw(int world, int rank, int64_t shard, const void* c
     p.w[q] = static_cast<__nv_bfloat16*>(w_peers[q]);
     p.ctl[q] = static_cast<uint32_t*>(ctl_peers[q]);
   }
+  p.g_mc = static_cast<const __nv_bfloat16*>(g_mc);
+  p.w_mc = static_cast<__nv_bfloat16*>(w_mc);
   p.master = master;
   p.m = m;
   p.v = v;

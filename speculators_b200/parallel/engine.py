@@ -26,7 +26,9 @@ replicated mode through a Newton-Schulz update on the matrix views.
 
 from __future__ import annotations
 
+import logging
 import math
+import os
 from dataclasses import dataclass, field
 
 import torch
@@ -34,6 +36,8 @@ import torch.distributed as dist
 from torch import nn
 
 from speculators_b200 import ops
+
+log = logging.getLogger(__name__)
 
 __all__ = ["EngineConfig", "TrainEngine", "split_named_params_for_muon"]
 
@@ -71,8 +75,10 @@ class EngineConfig:
     shard: bool = False
     # "nccl": reduce-scatter / all-gather through torch.distributed.  "p2p": the sharded
     # step runs as two fused kernels that read peers' gradients and write peers' weights
-    # through NVLink peer mappings (single node, AdamW, bf16 compute).  "auto": p2p when
-    # it applies, else nccl.
+    # through NVLink peer mappings (single node, AdamW, bf16 compute).  "nvls": the same two
+    # kernels, with the bulk transfers going through an NVLink multicast mapping of the
+    # buffers (multimem.ld_reduce / multimem.st: the switch adds and replicates).  "auto":
+    # nvls when the system offers multicast, else p2p when it applies, else nccl.
     comm: str = "auto"
     group: object | None = None
     broadcast_from_rank0: bool = True
@@ -89,6 +95,7 @@ class TrainEngine:
         self.world = dist.get_world_size(self.group) if self.distributed else 1
         self.rank = dist.get_rank(self.group) if self.distributed else 0
         self.sharded = bool(config.shard) and self.world > 1
+        self.nvls = False
         self.p2p = self._want_p2p()
         self.step_count = 0
         self._flatten()
@@ -103,21 +110,37 @@ class TrainEngine:
         import os
 
         mode = os.environ.get("SB200_COMM", self.cfg.comm)
-        if mode not in ("auto", "p2p", "nccl"):
-            raise ValueError(f"comm must be auto, p2p or nccl, got {mode!r}")
+        if mode not in ("auto", "nvls", "p2p", "nccl"):
+            raise ValueError(f"comm must be auto, nvls, p2p or nccl, got {mode!r}")
+        self._comm_mode = mode
         applicable = (
             self.sharded and self.device.type == "cuda" and self.cfg.optimizer == "adamw"
             and self.cfg.compute_dtype == torch.bfloat16 and self.world <= 8
         )
-        if mode == "p2p" and not applicable:
-            raise ValueError("comm='p2p' needs sharded multi-rank CUDA training with AdamW in bf16 on one node (<= 8 ranks)")
-        return applicable and mode in ("auto", "p2p")
+        if mode in ("p2p", "nvls") and not applicable:
+            raise ValueError(f"comm={mode!r} needs sharded multi-rank CUDA training with AdamW in bf16 on one node (<= 8 ranks)")
+        return applicable and mode in ("auto", "nvls", "p2p")
 
     def _alloc_flat(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
         """Flat buffer in ordinary allocator memory, or (p2p) in cudaMalloc'ed memory
         that is exported to the peers."""
         if not self.p2p:
             return torch.zeros(numel, dtype=dtype, device=self.device)
+        if self._symm is not False and self._comm_mode in ("auto", "nvls"):
+            # symmetric memory (torch): the same buffer mapped on every rank, plus, where the
+            # NVSwitch supports it, one multicast address that reaches all copies
+            try:
+                import torch.distributed._symmetric_memory as symm
+
+                t = symm.empty(numel, dtype=dtype, device=self.device)
+                t.zero_()
+                self._symm = True
+                return t
+            except Exception as err:  # noqa: BLE001
+                if self._comm_mode == "nvls" or self._symm is True:
+                    raise
+                log.info("symmetric memory not available (%s); using CUDA IPC peer mappings", err)
+                self._symm = False
         nat = ops.native()
         ptr = nat.peer_alloc(numel * torch.empty((), dtype=dtype).element_size())
         self._peer_local.append(ptr)
@@ -174,6 +197,7 @@ class TrainEngine:
         self.total = (off + unit - 1) // unit * unit
         self._peer_local: list[int] = []
         self._peer_mapped: list[int] = []
+        self._symm: bool | None = None  # None: not tried yet, True / False: symmetric memory in use / not available
         self.flat_w = self._alloc_flat(self.total, cfg.compute_dtype)
         self.flat_g = self._alloc_flat(self.total, cfg.compute_dtype)
         init32 = torch.zeros(self.total, dtype=torch.float32, device=dev)
@@ -218,9 +242,31 @@ class TrainEngine:
             nat = ops.native()
             ctl = nat.peer_alloc(int(nat.fused_optim_ctl_words()) * 4)
             self._peer_local.append(ctl)
-            self._g_ptrs = torch.tensor(self._exchange(self.flat_g.data_ptr()), dtype=torch.int64)
-            self._w_ptrs = torch.tensor(self._exchange(self.flat_w.data_ptr()), dtype=torch.int64)
+            self._g_mc = self._w_mc = 0
+            if self._symm:
+                import torch.distributed._symmetric_memory as symm
+
+                grp = self.group if self.group is not None else dist.group.WORLD
+                handles = []
+                for buf in (self.flat_g, self.flat_w):
+                    h = symm.rendezvous(buf, grp)
+                    ptrs = [int(x) for x in h.buffer_ptrs]
+                    off = buf.data_ptr() - ptrs[self.rank]  # the tensor may sit at an offset inside the mapped allocation
+                    if off < 0:
+                        raise RuntimeError("symmetric memory: tensor lies outside its own mapped buffer")
+                    handles.append((h, [x + off for x in ptrs], int(h.multicast_ptr) + off if int(h.multicast_ptr) else 0))
+                self._symm_handles = handles  # keeps the mappings alive
+                self._g_ptrs = torch.tensor(handles[0][1], dtype=torch.int64)
+                self._w_ptrs = torch.tensor(handles[1][1], dtype=torch.int64)
+                if handles[0][2] and handles[1][2] and os.environ.get("SB200_MULTIMEM", "1") != "0":
+                    self._g_mc, self._w_mc = handles[0][2], handles[1][2]
+                elif self._comm_mode == "nvls":
+                    raise RuntimeError("comm='nvls': no NVLink multicast address for the flat buffers on this system")
+            else:
+                self._g_ptrs = torch.tensor(self._exchange(self.flat_g.data_ptr()), dtype=torch.int64)
+                self._w_ptrs = torch.tensor(self._exchange(self.flat_w.data_ptr()), dtype=torch.int64)
             self._ctl_ptrs = torch.tensor(self._exchange(ctl), dtype=torch.int64)
+            self.nvls = bool(self._g_mc)
             self.grad_reduced = torch.zeros(n, dtype=torch.float32, device=dev)
             dist.barrier(group=self.group)
 
@@ -299,7 +345,8 @@ class TrainEngine:
             self._settle_untouched_grads()
         if self.p2p:
             ops.native().fused_sharded_adamw(
-                self.world, self.rank, self.hi - self.lo, self._g_ptrs, self._w_ptrs, self._ctl_ptrs, self.master, self.exp_avg,
+                self.world, self.rank, self.hi - self.lo, self._g_ptrs, self._w_ptrs, self._ctl_ptrs, self._g_mc, self._w_mc,
+                self.master, self.exp_avg,
                 self.exp_avg_sq, self.grad_reduced, self.hyper, self.status,
             )
             return
