@@ -126,25 +126,46 @@ class TrainEngine:
         that is exported to the peers."""
         if not self.p2p:
             return torch.zeros(numel, dtype=dtype, device=self.device)
-        if self._symm is not False and self._comm_mode in ("auto", "nvls"):
-            # symmetric memory (torch): the same buffer mapped on every rank, plus, where the
-            # NVSwitch supports it, one multicast address that reaches all copies
-            try:
-                import torch.distributed._symmetric_memory as symm
-
-                t = symm.empty(numel, dtype=dtype, device=self.device)
-                t.zero_()
-                self._symm = True
-                return t
-            except Exception as err:  # noqa: BLE001
-                if self._comm_mode == "nvls" or self._symm is True:
-                    raise
-                log.info("symmetric memory not available (%s); using CUDA IPC peer mappings", err)
-                self._symm = False
         nat = ops.native()
         ptr = nat.peer_alloc(numel * torch.empty((), dtype=dtype).element_size())
         self._peer_local.append(ptr)
         return nat.peer_tensor(ptr, numel, dtype, self.device.index or 0)
+
+    def _alloc_symmetric_pair(self, numel: int, dtype: torch.dtype):
+        """(flat_w, flat_g) in torch symmetric memory, mapped on every rank and, where the
+        NVSwitch offers it, reachable through one multicast address; ``None`` when that
+        is not available.  All ranks take the same branch: the outcome is agreed with an
+        all-reduce before anything depends on it."""
+        if not self.p2p or self._comm_mode not in ("auto", "nvls") or os.environ.get("SB200_MULTIMEM", "1") == "0":
+            return None
+        bufs, handles, err = [], [], None
+        try:
+            import torch.distributed._symmetric_memory as symm
+
+            grp = self.group if self.group is not None else dist.group.WORLD
+            for _ in range(2):
+                t = symm.empty(numel, dtype=dtype, device=self.device)
+                t.zero_()
+                bufs.append(t)
+            for t in bufs:
+                h = symm.rendezvous(t, grp)
+                ptrs = [int(x) for x in h.buffer_ptrs]
+                off = t.data_ptr() - ptrs[self.rank]  # the tensor may sit at an offset inside the mapped allocation
+                mc = int(h.multicast_ptr)
+                if off < 0 or not mc:
+                    raise RuntimeError("no NVLink multicast mapping for the buffer")
+                handles.append((h, [x + off for x in ptrs], mc + off))
+        except Exception as exc:  # noqa: BLE001 - any failure means "use the peer-mapping path"
+            err = exc
+        agreed = torch.tensor([0 if err is not None else 1], device=self.device)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=self.group)
+        if int(agreed.item()) == 0:
+            if self._comm_mode == "nvls":
+                raise RuntimeError(f"comm='nvls' is not available on this system: {err or 'another rank failed'}")
+            log.info("NVLink multicast not used (%s); falling back to CUDA IPC peer mappings", err or "another rank failed")
+            return None
+        self._symm_handles = handles  # keeps the mappings alive
+        return bufs[0], bufs[1]
 
     def _exchange(self, local_ptr: int) -> list[int]:
         """All ranks publish the IPC handle of ``local_ptr``; returns the address of
@@ -197,9 +218,13 @@ class TrainEngine:
         self.total = (off + unit - 1) // unit * unit
         self._peer_local: list[int] = []
         self._peer_mapped: list[int] = []
-        self._symm: bool | None = None  # None: not tried yet, True / False: symmetric memory in use / not available
-        self.flat_w = self._alloc_flat(self.total, cfg.compute_dtype)
-        self.flat_g = self._alloc_flat(self.total, cfg.compute_dtype)
+        self._symm_handles = None
+        pair = self._alloc_symmetric_pair(self.total, cfg.compute_dtype)
+        if pair is not None:
+            self.flat_w, self.flat_g = pair
+        else:
+            self.flat_w = self._alloc_flat(self.total, cfg.compute_dtype)
+            self.flat_g = self._alloc_flat(self.total, cfg.compute_dtype)
         init32 = torch.zeros(self.total, dtype=torch.float32, device=dev)
         for p, o in zip(self.params, self.offsets):
             init32[o : o + p.numel()].copy_(p.data.detach().reshape(-1).to(device=dev, dtype=torch.float32))
@@ -243,25 +268,11 @@ class TrainEngine:
             ctl = nat.peer_alloc(int(nat.fused_optim_ctl_words()) * 4)
             self._peer_local.append(ctl)
             self._g_mc = self._w_mc = 0
-            if self._symm:
-                import torch.distributed._symmetric_memory as symm
-
-                grp = self.group if self.group is not None else dist.group.WORLD
-                handles = []
-                for buf in (self.flat_g, self.flat_w):
-                    h = symm.rendezvous(buf, grp)
-                    ptrs = [int(x) for x in h.buffer_ptrs]
-                    off = buf.data_ptr() - ptrs[self.rank]  # the tensor may sit at an offset inside the mapped allocation
-                    if off < 0:
-                        raise RuntimeError("symmetric memory: tensor lies outside its own mapped buffer")
-                    handles.append((h, [x + off for x in ptrs], int(h.multicast_ptr) + off if int(h.multicast_ptr) else 0))
-                self._symm_handles = handles  # keeps the mappings alive
-                self._g_ptrs = torch.tensor(handles[0][1], dtype=torch.int64)
-                self._w_ptrs = torch.tensor(handles[1][1], dtype=torch.int64)
-                if handles[0][2] and handles[1][2] and os.environ.get("SB200_MULTIMEM", "1") != "0":
-                    self._g_mc, self._w_mc = handles[0][2], handles[1][2]
-                elif self._comm_mode == "nvls":
-                    raise RuntimeError("comm='nvls': no NVLink multicast address for the flat buffers on this system")
+            if self._symm_handles is not None:
+                (_, w_ptrs, w_mc), (_, g_ptrs, g_mc) = self._symm_handles
+                self._g_ptrs = torch.tensor(g_ptrs, dtype=torch.int64)
+                self._w_ptrs = torch.tensor(w_ptrs, dtype=torch.int64)
+                self._g_mc, self._w_mc = g_mc, w_mc
             else:
                 self._g_ptrs = torch.tensor(self._exchange(self.flat_g.data_ptr()), dtype=torch.int64)
                 self._w_ptrs = torch.tensor(self._exchange(self.flat_w.data_ptr()), dtype=torch.int64)
