@@ -136,7 +136,11 @@ class TrainEngine:
         NVSwitch offers it, reachable through one multicast address; ``None`` when that
         is not available.  All ranks take the same branch: the outcome is agreed with an
         all-reduce before anything depends on it."""
-        if not self.p2p or self._comm_mode not in ("auto", "nvls") or os.environ.get("SB200_MULTIMEM", "1") == "0":
+        # reduce-scatter and all-gather each move (world-1)/world of the buffer over every
+        # GPU's links in one direction whichever way they are issued, so the switch's
+        # reduction / replication saves no link time here; measured at 2 GPUs it was 1.5 %
+        # slower than the per-peer path, hence opt-in
+        if not self.p2p or self._comm_mode != "nvls":
             return None
         bufs, handles, err = [], [], None
         try:
