@@ -14,6 +14,13 @@ CLI parity: scripts/data_generation_offline.py:58 (parse_args), :437 (main) of t
 
 from __future__ import annotations
 
+import os as _os
+import sys as _sys
+
+_REPO_ROOT = _os.path.dirname(_os.path.dirname(_os.path.abspath(__file__)))
+if _REPO_ROOT not in _sys.path:  # run from a checkout without installing the package
+    _sys.path.insert(0, _REPO_ROOT)
+
 import argparse
 import asyncio
 import logging

@@ -17,6 +17,13 @@ CLI parity: scripts/prepare_data.py:83 (parse_args), :206 (main) of the referenc
 
 from __future__ import annotations
 
+import os as _os
+import sys as _sys
+
+_REPO_ROOT = _os.path.dirname(_os.path.dirname(_os.path.abspath(__file__)))
+if _REPO_ROOT not in _sys.path:  # run from a checkout without installing the package
+    _sys.path.insert(0, _REPO_ROOT)
+
 import argparse
 import logging
 import shutil

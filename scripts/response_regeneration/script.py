@@ -11,6 +11,13 @@ in the output file.  CLI parity: scripts/response_regeneration/script.py:62 of t
 
 from __future__ import annotations
 
+import os as _os
+import sys as _sys
+
+_REPO_ROOT = _os.path.dirname(_os.path.dirname(_os.path.dirname(_os.path.abspath(__file__))))
+if _REPO_ROOT not in _sys.path:  # run from a checkout without installing the package
+    _sys.path.insert(0, _REPO_ROOT)
+
 import argparse
 import asyncio
 import json

@@ -279,7 +279,7 @@ def test_benchmark_run_and_compare(tiny_verifier_dir, tmp_path, capsys):
     torch.save({i: 100 - i for i in range(64)}, tmp_path / "token_freq.pt")
     train_argv = ["--verifier-name-or-path", tiny_verifier_dir, "--total-seq-len", "48", "--draft-vocab-size", "32",
                   "--target-layer-ids", "1", "2", "3", "--token-freq-path", str(tmp_path / "token_freq.pt"), "--ttt-steps", "2",
-                  "--save-path", str(tmp_path / "unused")]
+                  "--save-path", str(tmp_path / "unused"), "--data-path", str(tmp_path / "data")]
     results = {}
     for name, steps in (("a", 3), ("b", 4)):
         bench_args = argparse.Namespace(synthetic=True, warmup_steps=1, measured_steps=steps, output=str(tmp_path / f"{name}.json"), no_per_step=False)
