@@ -190,6 +190,9 @@ class Eagle3DraftModel(DraftVocabMixin, SpeculatorModel):
 
         past = [[] for _ in self.layers]
         draft_tokens = []
+        # teacher forcing: pass k reads the ground-truth ids shifted left by k (zero padded);
+        # one padded copy, every pass takes a view of it
+        padded_ids = torch.cat([original_ids, original_ids.new_zeros(ttt_steps)])
         for step in range(ttt_steps):
             with torch.no_grad():
                 embeds = self.embed_tokens(ids).to(dtype)
@@ -217,8 +220,7 @@ class Eagle3DraftModel(DraftVocabMixin, SpeculatorModel):
 
             if return_draft_tokens:
                 draft_tokens.append(torch.argmax(logits.detach(), dim=-1).unsqueeze(0))
-            # teacher forcing: ground-truth ids shifted left by 1 + step, zero padded
-            ids = torch.cat([original_ids[1 + step :], original_ids.new_zeros(min(1 + step, T))])[:T]
+            ids = padded_ids[1 + step : 1 + step + T]
             positions = positions + 1
 
         if return_loss:

@@ -30,10 +30,55 @@ def align_for_step(logits, targets, loss_mask, prev_correct, ttt_step: int):
     return logits, targets, loss_mask, prev_correct
 
 
+USE_FUSED_TAIL = True  # tests flip this to compare against the op-by-op formulation
+
+
+def _single_fused_primitive(loss_config: LossConfig) -> tuple[str, float] | None:
+    """``(kernel op, weight)`` when the configuration is one fused primitive term."""
+    from speculators_b200.losses.rowwise import _PRIMITIVES, _is_fused
+    from speculators_b200.losses.utils import loss_name_of
+
+    if len(loss_config) != 1:
+        return None
+    (fn, weight), = loss_config.values()
+    name = loss_name_of(fn)
+    return (name, float(weight)) if name in _PRIMITIVES and _is_fused(fn) else None
+
+
+def _compute_metrics_fused(logits, targets, loss_mask, prev_correct, ttt_step: int, decay: float, op: str, weight: float):
+    """CUDA fast path for one fused loss term: row-loss kernel + one tail kernel (masked
+    mean, decay, accuracy counters, ``prev_correct`` update) instead of ~30 small ops."""
+    from speculators_b200 import ops
+    from speculators_b200.losses.utils import _REDUCTION_EPS
+
+    T = logits.shape[1]
+    rows = T - ttt_step
+    mask_u8 = loss_mask.reshape(-1)[ttt_step:]
+    if mask_u8.dtype not in (torch.bool, torch.uint8):
+        mask_u8 = mask_u8 != 0
+    prev_flat = prev_correct.reshape(-1)
+    active = mask_u8.bool() | prev_flat[:rows]
+    row_loss, pred, tgt = ops.fused_row_loss_raw(op, logits.reshape(T, -1), targets.reshape(targets.shape[1], -1), ttt_step, rows, active)
+    out = ops.ttt_step_tail(row_loss, pred, tgt, mask_u8.contiguous(), prev_flat, decay, _REDUCTION_EPS)
+    loss = out[0] * weight if weight != 1.0 else out[0]
+    stats = out.detach()
+    one = torch.ones((), device=logits.device)
+    metrics = {
+        f"loss_{ttt_step}_sum": stats[0] * weight if weight != 1.0 else stats[0], f"loss_{ttt_step}_total": one,
+        f"full_acc_{ttt_step}_sum": stats[1], f"full_acc_{ttt_step}_total": stats[2],
+        f"cond_acc_{ttt_step}_sum": stats[1], f"cond_acc_{ttt_step}_total": stats[3],
+    }
+    return loss, metrics
+
+
 def compute_metrics(logits, targets, loss_mask, prev_correct, ttt_step: int, ttt_step_loss_decay: float, loss_config: LossConfig | None = None):
     """Returns ``(step_loss, metrics)``; updates ``prev_correct`` in place."""
     if loss_config is None:
         loss_config = {"kl_div": (kl_div_loss, 1.0)}
+    if USE_FUSED_TAIL and logits.is_cuda and logits.dtype == torch.bfloat16 and loss_mask is not None and prev_correct is not None and prev_correct.dtype == torch.bool:
+        single = _single_fused_primitive(loss_config)
+        if single is not None and prev_correct.is_contiguous():
+            return _compute_metrics_fused(logits, targets, loss_mask, prev_correct, ttt_step, float(ttt_step_loss_decay) ** ttt_step, *single)
     T = logits.shape[1]
     rows = T - ttt_step
     device = logits.device

@@ -39,6 +39,7 @@ __all__ = [
     "sum_of_squares",
     "swiglu",
     "token_cross_entropy",
+    "ttt_step_tail",
 ]
 
 LOSS_OPS = {"kl_div": 0, "rkl": 1, "jsd": 2, "ce": 3, "tv": 4}
@@ -426,6 +427,53 @@ class _RowLossFn(torch.autograd.Function):
         op, shift, rows = ctx.cfg
         d = native().loss_bwd(op, logits, targets, dloss.contiguous().float(), stats, shift, rows)
         return d, None, None, None, None, None
+
+
+class _StepTailFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, row_loss, pred, target, mask, prev, decay, eps):
+        out, weight = native().step_tail(row_loss, pred, target, mask, prev, decay, eps)
+        ctx.save_for_backward(weight)
+        ctx.mark_dirty(prev)
+        ctx.mark_non_differentiable(prev)
+        return out, prev
+
+    @staticmethod
+    def backward(ctx, dout, _dprev):
+        (weight,) = ctx.saved_tensors
+        return weight * dout[0], None, None, None, None, None, None
+
+
+def ttt_step_tail(row_loss, pred_ids, target_ids, mask, prev_correct, decay: float, eps: float):
+    """Masked-mean loss of one training-time-test pass and its accuracy counters.
+
+    ``row_loss`` fp32 ``[rows]`` (differentiable), ``pred_ids`` / ``target_ids`` integer
+    ``[rows]``, ``mask`` bool / uint8 ``[rows]``, ``prev_correct`` bool / uint8 ``[>= rows]``
+    (AND-ed in place with this pass's hits).  Returns fp32 ``[4]``: ``loss =
+    decay * sum(row_loss * mask) / (sum(mask) + eps)``, ``correct = sum(prev & hit & mask)``,
+    ``total = sum(mask)``, ``cond_total = sum(prev before the update)``.  One launch on
+    CUDA; the same arithmetic with torch ops elsewhere."""
+    rows = row_loss.shape[0]
+    if _use_native(row_loss) and pred_ids.dtype == torch.int32 and target_ids.dtype == torch.int32:
+        out, _ = _StepTailFn.apply(row_loss.contiguous(), pred_ids, target_ids, mask, prev_correct, float(decay), float(eps))
+        return out
+    m = mask[:rows].bool()
+    was = prev_correct[:rows].bool()
+    cond_total = was.sum().float()
+    now = was & (pred_ids[:rows] == target_ids[:rows])
+    prev_correct[:rows] = now.to(prev_correct.dtype)
+    mf = m.to(row_loss.dtype)
+    loss = decay * (row_loss * mf).sum() / (mf.sum() + eps)
+    return torch.stack([loss, (now & m).sum().float(), mf.sum().float(), cond_total])
+
+
+def fused_row_loss_raw(op: str, logits, targets, shift: int, rows: int, active):
+    """``fused_row_loss`` on CUDA without the widening of the argmax by-products (int32)."""
+    if logits.stride(-1) != 1:
+        logits = logits.contiguous()
+    if targets.stride(-1) != 1:
+        targets = targets.contiguous()
+    return _RowLossFn.apply(logits, targets, LOSS_OPS[op], shift, rows, active)
 
 
 def fused_row_loss(op: str, logits, targets, shift: int = 0, rows: int | None = None, active=None):

@@ -37,6 +37,7 @@ int launch_fused_sharded_adamw(int, int, int64_t, const void* const*, void* cons
 int hs_ring_ctl_words_per_slot();
 int launch_hs_push(const void*, int64_t, void*, uint32_t*, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t*, int*, cudaStream_t);
 int launch_hs_pop(void*, int64_t, const void*, uint32_t*, uint32_t, uint32_t, uint32_t*, int*, cudaStream_t);
+void launch_step_tail(const float*, const int*, const int*, const uint8_t*, uint8_t*, int, float, float, float*, float*, cudaStream_t);
 void launch_sumsq(const void*, int, int64_t, float*, float*, int, cudaStream_t);
 void launch_set_hyper(float*, const float*, cudaStream_t);
 void launch_adamw(float*, float*, float*, const void*, int, void*, int64_t, const float*,
@@ -286,6 +287,26 @@ Tensor peer_tensor(int64_t ptr, int64_t numel, at::ScalarType dtype, int64_t dev
 }
 int64_t fused_optim_ctl_words() { return sb200::fused_optim_ctl_words(); }
 
+// ---- tail of a training-time-test pass --------------------------------------------------------
+// row_loss fp32[rows], pred / target int32[rows], mask uint8[rows] (0 / non-0), prev uint8 or bool [rows] (updated in place).
+// Returns (out fp32[4] = loss, correct, total, cond_total; weight fp32[rows] = d loss / d row_loss).
+std::tuple<Tensor, Tensor> step_tail(const Tensor& row_loss, const Tensor& pred, const Tensor& target, const Tensor& mask, Tensor prev,
+                                     double decay, double eps) {
+  const int64_t rows = row_loss.numel();
+  TORCH_CHECK(row_loss.is_cuda() && row_loss.scalar_type() == at::kFloat && row_loss.is_contiguous());
+  TORCH_CHECK(pred.scalar_type() == at::kInt && target.scalar_type() == at::kInt && pred.is_contiguous() && target.is_contiguous());
+  TORCH_CHECK(pred.numel() >= rows && target.numel() >= rows && mask.numel() >= rows && prev.numel() >= rows);
+  TORCH_CHECK((mask.scalar_type() == at::kByte || mask.scalar_type() == at::kBool) && mask.is_contiguous());
+  TORCH_CHECK((prev.scalar_type() == at::kByte || prev.scalar_type() == at::kBool) && prev.is_contiguous());
+  c10::cuda::CUDAGuard guard(row_loss.device());
+  Tensor out = at::empty({4}, row_loss.options());
+  Tensor weight = at::empty({rows}, row_loss.options());
+  sb200::launch_step_tail(row_loss.data_ptr<float>(), pred.data_ptr<int>(), target.data_ptr<int>(),
+                          static_cast<const uint8_t*>(mask.data_ptr()), static_cast<uint8_t*>(prev.data_ptr()), (int)rows, (float)decay,
+                          (float)eps, out.data_ptr<float>(), weight.data_ptr<float>(), cur_stream());
+  return {out, weight};
+}
+
 // ---- hidden-state ring (device-to-device hand-off) -----------------------------------------
 int64_t hs_ring_ctl_words() { return sb200::hs_ring_ctl_words_per_slot(); }
 
@@ -509,6 +530,7 @@ TORCH_LIBRARY(sb200, m) {
   m.def("peer_tensor", &peer_tensor);
   m.def("fused_optim_ctl_words", &fused_optim_ctl_words);
   m.def("fused_sharded_adamw", &fused_sharded_adamw);
+  m.def("step_tail", &step_tail);
   m.def("hs_ring_ctl_words", &hs_ring_ctl_words);
   m.def("hs_push", &hs_push);
   m.def("hs_pop", &hs_pop);

@@ -48,6 +48,43 @@ def test_graph_and_eager_trainers_agree_and_learn(tiny_verifier_dir, tiny_vocab_
     assert t_graph._graphed is not None and len(t_graph._graphed.cache) == 1
 
 
+def test_fused_step_tail_matches_op_by_op_metrics():
+    """One-launch tail (masked mean, decay, accuracy counters, prev_correct update) against
+    the same quantities computed with separate torch ops, forward and backward."""
+    from speculators_b200.models.eagle3 import metrics as em
+
+    torch.manual_seed(0)
+    T, V = 300, 512
+    targets = (torch.randn(1, T, V, device="cuda") * 2).to(torch.bfloat16)
+    mask = torch.rand(1, T, device="cuda") > 0.4
+    results = {}
+    for fused in (True, False):
+        em.USE_FUSED_TAIL = fused
+        logits = (torch.randn(1, T, V, device="cuda", generator=torch.Generator(device="cuda").manual_seed(1)) * 2).to(torch.bfloat16).requires_grad_()
+        prev = mask.clone()
+        total, log = torch.zeros((), device="cuda"), {}
+        for step in range(3):
+            # make some predictions right so that the conditional counters are not trivial
+            with torch.no_grad():
+                lg = logits.detach().clone()
+                hit_rows = torch.arange(0, T - step, 3, device="cuda")
+                lg[0, hit_rows, targets[0, hit_rows + step].argmax(-1)] = 50.0
+            lg.requires_grad_()
+            loss, m = em.compute_metrics(lg, targets, mask, prev, step, 0.8)
+            loss.backward()
+            total = total + loss.detach()
+            log.update({k: float(v) for k, v in m.items()})
+            log[f"grad_{step}"] = lg.grad.float().abs().sum().item()
+        results[fused] = (float(total), log, prev.clone())
+    em.USE_FUSED_TAIL = True
+    (lf, mf, pf), (lo, mo, po) = results[True], results[False]
+    assert abs(lf - lo) <= 1e-4 * abs(lo) + 1e-6 and torch.equal(pf, po)
+    assert set(mf) == set(mo)
+    for key in mo:
+        assert abs(mf[key] - mo[key]) <= 1e-4 * abs(mo[key]) + 1e-5, (key, mf[key], mo[key])
+    assert mo["cond_acc_1_total"] < mo["cond_acc_0_total"] and mo["full_acc_0_sum"] > 0
+
+
 def test_prefetched_inputs_give_the_same_steps(tiny_verifier_dir, tiny_vocab_maps):
     """``train_step(batch, next_batch)`` stages the next batch on a side stream; the
     losses must equal those of the plain call sequence, also when the announced batch is
