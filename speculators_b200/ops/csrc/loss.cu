@@ -49,6 +49,45 @@ __device__ __forceinline__ void online_update(RowStats& s, const float (&x)[8], 
   }
 }
 
+// KL(target || draft) in one pass: next to the target row's online softmax statistics keep
+// A = sum_v e^{t_v - m}(t_v - x_v) relative to the same running max m, so that
+// sum_v p_v (t_v - x_v) = A / Z needs no second read of the rows.
+__device__ __forceinline__ void online_update_kl(RowStats& s, float& A, const float (&t)[8], const float (&x)[8], int col0) {
+  float vmax = t[0];
+#pragma unroll
+  for (int j = 1; j < 8; ++j) vmax = fmaxf(vmax, t[j]);
+  const float m_new = fmaxf(s.m, vmax);
+  float add = 0.f, add_a = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float e = __expf(t[j] - m_new);
+    add += e;
+    if (e > 0.f) add_a += e * (t[j] - x[j]);  // zero-probability targets contribute nothing
+  }
+  const float resc = __expf(s.m - m_new);
+  s.z = s.z * resc + add;
+  A = A * resc + add_a;
+  s.m = m_new;
+  if (vmax > s.best) {
+    s.best = vmax;
+#pragma unroll
+    for (int j = 7; j >= 0; --j)
+      if (t[j] == vmax) s.best_idx = col0 + j;
+  }
+}
+
+__device__ __forceinline__ void online_update_kl_scalar(RowStats& s, float& A, float t, float x, int col) {
+  const float m_new = fmaxf(s.m, t);
+  const float e = __expf(t - m_new), resc = __expf(s.m - m_new);
+  s.z = s.z * resc + e;
+  A = A * resc + (e > 0.f ? e * (t - x) : 0.f);
+  s.m = m_new;
+  if (t > s.best) {
+    s.best = t;
+    s.best_idx = col;
+  }
+}
+
 __device__ __forceinline__ void online_update_scalar(RowStats& s, float x, int col) {
   const float m_new = fmaxf(s.m, x);
   s.z = s.z * __expf(s.m - m_new) + __expf(x - m_new);
@@ -138,19 +177,26 @@ loss_fwd_kernel(const __nv_bfloat16* __restrict__ logits, const __nv_bfloat16* _
   const int nvec = vec_ok ? (V >> 3) : 0;
 
   RowStats sd{-INFINITY, 0.f, -INFINITY, 0x7fffffff}, stt{-INFINITY, 0.f, -INFINITY, 0x7fffffff};
+  float kl_a = 0.f;  // OP == kOpKL: the cross term, accumulated in the same pass
   for (int v = threadIdx.x; v < nvec; v += kLossThreads) {
     float a[8], b[8];
     unpack8(ld8(x + (v << 3)), a);
     online_update(sd, a, v << 3);
     if (has_t) {
       unpack8(ld8(t + (v << 3)), b);
-      online_update(stt, b, v << 3);
+      if (OP == kOpKL) online_update_kl(stt, kl_a, b, a, v << 3);
+      else online_update(stt, b, v << 3);
     }
   }
   for (int c = (nvec << 3) + threadIdx.x; c < V; c += kLossThreads) {
-    online_update_scalar(sd, __bfloat162float(x[c]), c);
-    if (has_t) online_update_scalar(stt, __bfloat162float(t[c]), c);
+    const float xc = __bfloat162float(x[c]);
+    online_update_scalar(sd, xc, c);
+    if (has_t) {
+      if (OP == kOpKL) online_update_kl_scalar(stt, kl_a, __bfloat162float(t[c]), xc, c);
+      else online_update_scalar(stt, __bfloat162float(t[c]), c);
+    }
   }
+  const float my_mt = stt.m;  // this thread's running max of the target row, before the block-wide combine
   block_combine(sd, scratch, iscratch);
   if (has_t) {
     block_combine(stt, scratch, iscratch);
@@ -166,6 +212,11 @@ loss_fwd_kernel(const __nv_bfloat16* __restrict__ logits, const __nv_bfloat16* _
   float acc0 = 0.f, acc1 = 0.f;
   if (OP == kOpCE) {
     if (threadIdx.x == 0) acc0 = lse_d - __bfloat162float(x[stt.best_idx]);
+  } else if (OP == kOpKL) {
+    // sum_v p_v (t_v - x_v) = (sum over threads of A rescaled to the row max) / Z_t; thread 0 adds
+    // the normaliser terms once so that the block sum below yields the row's KL directly
+    acc0 = (my_mt == -INFINITY) ? 0.f : kl_a * __expf(my_mt - stt.m) / stt.z;
+    if (threadIdx.x == 0) acc0 += lse_d - lse_t;
   } else {
     auto body = [&](float xv, float tv) {
       const float ldp = xv - lse_d, ltp = tv - lse_t;
