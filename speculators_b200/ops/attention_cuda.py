@@ -1,8 +1,14 @@
 """CUDA path of ``masked_attention``: autograd wrapper around the sm_100a kernels
-in ``csrc/attention.cu`` (head dims 64 and 128).  Other head dims use the dense
-formulation."""
+(head dims 64 and 128).  Other head dims use the dense formulation.
+
+Forward at head dim 128 runs on the tcgen05 tensor cores (``csrc/attention_tc.cu``: TMA
+tiles, TMEM score / output accumulators); ``FWD_IMPL = "mma"`` (or ``SB200_ATTN_FWD=mma``)
+selects the ``mma.sync`` kernel of ``csrc/attention.cu``, which also serves head dim 64 and
+the backward pass."""
 
 from __future__ import annotations
+
+import os
 
 import torch
 
@@ -10,6 +16,7 @@ from speculators_b200.ops import _ext
 from speculators_b200.ops.attention import AttnSpec, masked_attention_reference
 
 _SUPPORTED_HEAD_DIMS = (64, 128)
+FWD_IMPL = os.environ.get("SB200_ATTN_FWD", "tc")
 
 
 def _rows_ok(t: torch.Tensor) -> torch.Tensor:
@@ -27,7 +34,12 @@ class _MaskedAttentionFn(torch.autograd.Function):
         q, k, v = _rows_ok(q), _rows_ok(k), _rows_ok(v)
         if ext_idx is not None:
             k_ext, v_ext = _rows_ok(k_ext), _rows_ok(v_ext)
-        out, lse2 = _ext.lib().attn_fwd(q, k, v, lo, hi, k_ext, v_ext, ext_idx, scale)
+        if FWD_IMPL == "tc" and q.shape[2] == 128:
+            from speculators_b200.ops import gemm_status
+
+            out, lse2 = _ext.lib().attn_fwd_tc(q, k, v, lo, hi, k_ext, v_ext, ext_idx, scale, gemm_status(q.device))
+        else:
+            out, lse2 = _ext.lib().attn_fwd(q, k, v, lo, hi, k_ext, v_ext, ext_idx, scale)
         ctx.save_for_backward(q, k, v, out, lse2, lo, hi, k_ext, v_ext, ext_idx)
         ctx.scale = scale
         return out

@@ -37,6 +37,8 @@ struct AttnParams {
 };
 
 int launch_attn_fwd(const AttnParams& p, int hd, cudaStream_t stream);
+// tcgen05 forward, head_dim 128; `status`: device int that receives a code when a bounded wait expires.
+int launch_attn_fwd_tc(const AttnParams& p, int* status, cudaStream_t stream);
 // tile_qmin / tile_qmax: scratch of one int per 64-key tile, fully written by the launch.
 int launch_attn_bwd(const AttnParams& p, int hd, int* tile_qmin, int* tile_qmax, cudaStream_t stream);
 constexpr int kAttnKeyTile = 64;

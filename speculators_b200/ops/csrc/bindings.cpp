@@ -457,6 +457,25 @@ std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tens
   return {out, lse2};
 }
 
+// Forward on the tcgen05 tensor cores (head_dim 128).  `status` (int32[1], device) receives a
+// non-zero code if a bounded wait in the kernel ran out.
+std::tuple<Tensor, Tensor> attn_fwd_tc(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& lo, const Tensor& hi,
+                                       const c10::optional<Tensor>& ke, const c10::optional<Tensor>& ve,
+                                       const c10::optional<Tensor>& ext_idx, double scale, Tensor status) {
+  sb200::AttnParams p = make_params(q, k, v, lo, hi, ke, ve, ext_idx, scale);
+  TORCH_CHECK(q.size(2) == 128, "attn_fwd_tc: head_dim must be 128");
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == at::kInt && status.numel() >= 1);
+  c10::cuda::CUDAGuard guard(q.device());
+  Tensor out = at::empty({q.size(0), q.size(1), q.size(2)}, q.options());
+  Tensor lse2 = at::empty({q.size(1), q.size(0)}, q.options().dtype(at::kFloat));
+  p.out = (__nv_bfloat16*)out.data_ptr();
+  p.o_rs = out.stride(0);
+  p.lse2 = lse2.data_ptr<float>();
+  const int rc = sb200::launch_attn_fwd_tc(p, status.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(rc == 0, "attn_fwd_tc launch failed (", rc, ")");
+  return {out, lse2};
+}
+
 std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> attn_bwd(
     const Tensor& dout, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out, const Tensor& lse2,
     const Tensor& lo, const Tensor& hi, const c10::optional<Tensor>& ke, const c10::optional<Tensor>& ve,
@@ -537,5 +556,6 @@ TORCH_LIBRARY(sb200, m) {
   m.def("gemm_tn", &gemm_tn);
   m.def("gemm_tn_variant", &gemm_tn_variant);
   m.def("attn_fwd", &attn_fwd);
+  m.def("attn_fwd_tc", &attn_fwd_tc);
   m.def("attn_bwd", &attn_bwd);
 }

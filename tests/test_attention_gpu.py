@@ -83,3 +83,34 @@ def test_rows_without_any_key_return_zero():
     assert (out[10:20] == 0).all() and torch.isfinite(out).all()
     out.sum().backward()
     assert torch.isfinite(q.grad).all() and (q.grad[10:20] == 0).all()
+
+
+@pytest.mark.parametrize("impl", ["tc", "mma"])
+def test_forward_implementations_head_dim_128(impl, monkeypatch):
+    """tcgen05 forward (TMA tiles, TMEM accumulators) and the mma.sync forward against the
+    fp32 oracle on a multi-tile, multi-document sequence read from a fused q|k|v buffer."""
+    from speculators_b200.ops import attention_cuda, check_gemm_status
+
+    monkeypatch.setattr(attention_cuda, "FWD_IMPL", impl)
+    _run(1100, 8, 2, 128, step=2, window=None, pattern="multi_pad", fused_buffer=True, seed=3)
+    _run(700, 4, 4, 128, step=0, window=150, pattern="single", seed=4)
+    check_gemm_status()
+
+
+def test_tc_forward_rows_without_any_key():
+    from speculators_b200.ops import check_gemm_status
+
+    T, nh, hd = 300, 2, 128
+    q = torch.randn(T, nh, hd, device=DEV).to(torch.bfloat16)
+    k = torch.randn(T, nh, hd, device=DEV).to(torch.bfloat16)
+    v = torch.randn(T, nh, hd, device=DEV).to(torch.bfloat16)
+    lo = torch.zeros(T, dtype=torch.int32, device=DEV)
+    hi = torch.arange(1, T + 1, dtype=torch.int32, device=DEV)
+    hi[120:140] = 0
+    hi[256:] = 0  # a whole query tile without keys
+    spec = AttnSpec(lo=lo, hi=hi)
+    out = masked_attention(q, k, v, spec)
+    ref = masked_attention_reference(q.float(), k.float(), v.float(), spec)
+    assert (out[120:140] == 0).all() and (out[256:] == 0).all()
+    torch.testing.assert_close(out.float(), ref, atol=2e-2, rtol=2e-2)
+    check_gemm_status()
