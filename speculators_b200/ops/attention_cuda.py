@@ -1,10 +1,11 @@
 """CUDA path of ``masked_attention``: autograd wrapper around the sm_100a kernels
 (head dims 64 and 128).  Other head dims use the dense formulation.
 
-Forward at head dim 128 runs on the tcgen05 tensor cores (``csrc/attention_tc.cu``: TMA
-tiles, TMEM score / output accumulators); ``FWD_IMPL = "mma"`` (or ``SB200_ATTN_FWD=mma``)
-selects the ``mma.sync`` kernel of ``csrc/attention.cu``, which also serves head dim 64 and
-the backward pass."""
+Forward and backward at head dim 128 run on the tcgen05 tensor cores
+(``csrc/attention_tc.cu``, ``csrc/attention_bwd_tc.cu``: TMA tiles, TMEM accumulators,
+probability tiles handed to the next product through TMEM); ``FWD_IMPL`` / ``BWD_IMPL`` =
+``"mma"`` (or ``SB200_ATTN_FWD=mma`` / ``SB200_ATTN_BWD=mma``) select the ``mma.sync``
+kernels of ``csrc/attention.cu``, which also serve head dim 64."""
 
 from __future__ import annotations
 
@@ -17,6 +18,7 @@ from speculators_b200.ops.attention import AttnSpec, masked_attention_reference
 
 _SUPPORTED_HEAD_DIMS = (64, 128)
 FWD_IMPL = os.environ.get("SB200_ATTN_FWD", "tc")
+BWD_IMPL = os.environ.get("SB200_ATTN_BWD", "tc")
 
 
 def _rows_ok(t: torch.Tensor) -> torch.Tensor:
@@ -47,7 +49,14 @@ class _MaskedAttentionFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dout):
         q, k, v, out, lse2, lo, hi, k_ext, v_ext, ext_idx = ctx.saved_tensors
-        dq, dk, dv, dke, dve = _ext.lib().attn_bwd(_rows_ok(dout), q, k, v, out, lse2, lo, hi, k_ext, v_ext, ext_idx, ctx.scale)
+        if BWD_IMPL == "tc" and q.shape[2] == 128:
+            from speculators_b200.ops import gemm_status
+
+            impl, status = 1, gemm_status(q.device)
+        else:
+            impl, status = 0, None
+        dq, dk, dv, dke, dve = _ext.lib().attn_bwd(
+            _rows_ok(dout), q, k, v, out, lse2, lo, hi, k_ext, v_ext, ext_idx, ctx.scale, impl, status)
         if ext_idx is not None:
             return dq, dk, dv, None, None, dke.to(q.dtype), dve.to(q.dtype), None, None
         return dq, dk, dv, None, None, None, None, None, None

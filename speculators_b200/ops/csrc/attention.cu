@@ -800,6 +800,21 @@ static int launch_bwd_t(const AttnParams& p, int* tile_qmin, int* tile_qmax, cud
   return 0;
 }
 
+int launch_kv_tile_range(const AttnParams& p, int* tile_qmin, int* tile_qmax, cudaStream_t stream) {
+  const int n_kv_tiles = (p.Tc + kBN - 1) / kBN;
+  count_launch(1);
+  kv_tile_range_kernel<<<n_kv_tiles, 256, 0, stream>>>(p.lo, p.hi, p.Tq, p.Tc, tile_qmin, tile_qmax);
+  return 0;
+}
+
+int launch_dkv_reduce(const AttnParams& p, cudaStream_t stream) {
+  const int64_t n = (int64_t)p.Tc * p.nkv * 128;
+  const int64_t blocks = (2 * (n >> 3) + 255) / 256;
+  count_launch(1);
+  dkv_reduce_kernel<<<(int)(blocks < 8 * kNumSM ? blocks : 8 * kNumSM), 256, 0, stream>>>(p.dkv_part, p.nh / p.nkv, n, p.dk, p.dv);
+  return 0;
+}
+
 int launch_attn_fwd(const AttnParams& p, int hd, cudaStream_t stream) {
   if (p.Tq <= 0) return 0;
   if (hd == 64) return launch_fwd_t<64>(p, stream);

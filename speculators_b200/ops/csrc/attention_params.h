@@ -42,5 +42,11 @@ int launch_attn_fwd_tc(const AttnParams& p, int* status, cudaStream_t stream);
 // tile_qmin / tile_qmax: scratch of one int per 64-key tile, fully written by the launch.
 int launch_attn_bwd(const AttnParams& p, int hd, int* tile_qmin, int* tile_qmax, cudaStream_t stream);
 constexpr int kAttnKeyTile = 64;
+// tcgen05 backward (dQ kernel, dK/dV kernel), head_dim 128; same scratch and status conventions.
+int launch_attn_bwd_tc(const AttnParams& p, int* tile_qmin, int* tile_qmax, int* status, cudaStream_t stream);
+// Pieces of the backward shared by both implementations: per-64-key-tile query row ranges,
+// and the head-ordered sum of the fp32 dK / dV partials of grouped queries (head_dim 128).
+int launch_kv_tile_range(const AttnParams& p, int* tile_qmin, int* tile_qmax, cudaStream_t stream);
+int launch_dkv_reduce(const AttnParams& p, cudaStream_t stream);
 
 }  // namespace sb200

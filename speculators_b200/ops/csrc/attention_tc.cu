@@ -41,30 +41,6 @@ constexpr float kLog2e = 1.4426950408889634f;
 
 enum Status : int { kTimeoutProducer = 31, kTimeoutMma = 32, kTimeoutSoftmax = 33 };
 
-// kind::f16 instruction descriptor: D fp32, A / B bf16, A K-major, B K-major or MN-major.
-__host__ __device__ constexpr uint32_t instr_desc(int m, int n, bool b_mn_major) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
-// MN-major operand, 128-byte swizzle: shared-memory rows are the contraction index (128 B =
-// 64 MN-elements each, 8-row groups 1024 B apart), the next 64 MN-elements start `lbo` bytes on.
-__device__ __forceinline__ uint64_t smem_desc_mnmajor_sw128(uint32_t addr, uint32_t lbo) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr & 0x3ffff) >> 4);
-  d |= (uint64_t)(lbo >> 4) << 16;
-  d |= (uint64_t)(1024 >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
-
-// 2^x on the special-function unit; -inf gives 0, results below the normal range flush to 0
-__device__ __forceinline__ float ex2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
 __global__ void __launch_bounds__(THREADS, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const AttnParams p, int* status) {

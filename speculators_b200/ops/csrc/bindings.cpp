@@ -479,9 +479,14 @@ std::tuple<Tensor, Tensor> attn_fwd_tc(const Tensor& q, const Tensor& k, const T
 std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> attn_bwd(
     const Tensor& dout, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out, const Tensor& lse2,
     const Tensor& lo, const Tensor& hi, const c10::optional<Tensor>& ke, const c10::optional<Tensor>& ve,
-    const c10::optional<Tensor>& ext_idx, double scale) {
+    const c10::optional<Tensor>& ext_idx, double scale, int64_t impl, const c10::optional<Tensor>& status) {
+  // impl 0: mma.sync kernels; 1: tcgen05 kernels (head_dim 128; `status` receives a code if a bounded wait ran out)
   sb200::AttnParams p = make_params(q, k, v, lo, hi, ke, ve, ext_idx, scale);
   const int64_t hd = q.size(2);
+  if (impl == 1) {
+    TORCH_CHECK(hd == 128, "attn_bwd: the tcgen05 kernels need head_dim 128");
+    TORCH_CHECK(status.has_value() && status->is_cuda() && status->scalar_type() == at::kInt && status->numel() >= 1);
+  }
   check_heads(dout, "dout", hd);
   check_heads(out, "out", hd);
   TORCH_CHECK(dout.size(0) == q.size(0) && dout.size(1) == q.size(1) && out.sizes() == dout.sizes());
@@ -521,7 +526,8 @@ std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> attn_bwd(
   p.dv = (__nv_bfloat16*)dv.data_ptr();
   p.tile_qmin = qmin.data_ptr<int>();
   p.tile_qmax = qmax.data_ptr<int>();
-  const int rc = sb200::launch_attn_bwd(p, (int)hd, qmin.data_ptr<int>(), qmax.data_ptr<int>(), cur_stream());
+  const int rc = impl == 1 ? sb200::launch_attn_bwd_tc(p, qmin.data_ptr<int>(), qmax.data_ptr<int>(), status->data_ptr<int>(), cur_stream())
+                           : sb200::launch_attn_bwd(p, (int)hd, qmin.data_ptr<int>(), qmax.data_ptr<int>(), cur_stream());
   TORCH_CHECK(rc == 0, "attn_bwd launch failed (", rc, ")");
   return {dq, dk, dv, dke, dve};
 }

@@ -86,12 +86,14 @@ def test_rows_without_any_key_return_zero():
 
 
 @pytest.mark.parametrize("impl", ["tc", "mma"])
-def test_forward_implementations_head_dim_128(impl, monkeypatch):
-    """tcgen05 forward (TMA tiles, TMEM accumulators) and the mma.sync forward against the
-    fp32 oracle on a multi-tile, multi-document sequence read from a fused q|k|v buffer."""
+def test_implementations_head_dim_128(impl, monkeypatch):
+    """tcgen05 kernels (TMA tiles, TMEM accumulators) and the mma.sync kernels, forward and
+    backward, against the fp32 oracle on multi-tile, multi-document sequences read from a
+    fused q|k|v buffer."""
     from speculators_b200.ops import attention_cuda, check_gemm_status
 
     monkeypatch.setattr(attention_cuda, "FWD_IMPL", impl)
+    monkeypatch.setattr(attention_cuda, "BWD_IMPL", impl)
     _run(1100, 8, 2, 128, step=2, window=None, pattern="multi_pad", fused_buffer=True, seed=3)
     _run(700, 4, 4, 128, step=0, window=150, pattern="single", seed=4)
     check_gemm_status()
