@@ -96,8 +96,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       mbar_init(smem_addr(&bar_kv_empty[s]), 1);
     }
     mbar_init(smem_addr(&bar_sdp_full), 1);
-    mbar_init(smem_addr(&bar_sdp_free), 256);
-    mbar_init(smem_addr(&bar_ds_ready), 256);
+    mbar_init(smem_addr(&bar_sdp_free), 8);  // one arrival per element-wise warp
+    mbar_init(smem_addr(&bar_ds_ready), 8);  // one arrival per element-wise warp
     mbar_init(smem_addr(&bar_dq_done), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     s_range[0] = 0x7fffffff;
@@ -251,7 +251,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         tmem_ld_wait();
         if (c == 1) {  // S and dP of the tile are in registers: the next tile's products may overwrite them
           fence_before_sync();
-          mbar_arrive(smem_addr(&bar_sdp_free));
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_addr(&bar_sdp_free));
         }
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
@@ -276,7 +277,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       tmem_st32(lane_base + COL_DS + (t & 1) * 64 + half * 32, pk);
       tmem_st_wait();
       fence_before_sync();
-      mbar_arrive(smem_addr(&bar_ds_ready));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_addr(&bar_ds_ready));
     }
 
     float dq[64];
@@ -297,51 +299,80 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       fence_before_sync();
     }
 
-    // individually addressed extra keys: each thread of the pair takes 64 of the 128
-    // dimensions of q.k and dO.v, the halves meet through the exchange slots
-    for (int e = 0; e < p.E; ++e) {
-      const int idx = row_ok ? p.ext_idx[(int64_t)row * p.E + e] : -1;
-      const bool valid = idx >= 0 && idx < p.Te;
-      const int64_t idc = valid ? idx : 0;
-      const __nv_bfloat16* kr = p.ke + idc * p.ke_rs + kvh * HD + colh;
-      const __nv_bfloat16* vr = p.ve + idc * p.ve_rs + kvh * HD + colh;
-      bf16x8 kreg[8], vreg[8];
+    // Individually addressed extra keys: each thread of the pair takes 64 of the 128
+    // dimensions of q.k and dO.v, the halves meet through the exchange slots.  Rows of the
+    // extra K / V tensors and the dK / dV contributions travel through a per-warp staging
+    // area (the K / V stages, idle once the tile loop has drained) so that global loads and
+    // atomics are issued warp-wide over whole rows instead of one row per lane.
+    if (p.E > 0) {
+      unsigned char* stage = k_s + (warp - 2) * 16384;  // 16 KB per warp
+      for (int e = 0; e < p.E; ++e) {
+        const int idx = row_ok ? p.ext_idx[(int64_t)row * p.E + e] : -1;
+        const bool valid = idx >= 0 && idx < p.Te;
+        const int idc = valid ? idx : 0;
+        // stage in: 8 lanes fetch the 128 bytes of one row's half, 4 rows per instruction
+        __syncwarp();
 #pragma unroll
-      for (int c = 0; c < 8; ++c) kreg[c] = ld8(kr + c * 8);
-#pragma unroll
-      for (int c = 0; c < 8; ++c) vreg[c] = ld8(vr + c * 8);
-      float dot = 0.f, dpe = 0.f;
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        float a[8], b[8], g[8], w[8];
-        unpack8(*reinterpret_cast<const bf16x8*>(q_row + ((c ^ sw) << 4)), a);
-        unpack8(kreg[c], b);
-        unpack8(*reinterpret_cast<const bf16x8*>(do_row + ((c ^ sw) << 4)), g);
-        unpack8(vreg[c], w);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          dot = fmaf(a[i], b[i], dot);
-          dpe = fmaf(g[i], w[i], dpe);
+        for (int it = 0; it < 8; ++it) {
+          const int r = it * 4 + (lane >> 3), pc = lane & 7;
+          const int64_t ir = __shfl_sync(0xffffffffu, idc, r);
+          const bf16x8 kx = ld8(p.ke + ir * p.ke_rs + kvh * HD + colh + pc * 8);
+          const bf16x8 vx = ld8(p.ve + ir * p.ve_rs + kvh * HD + colh + pc * 8);
+          *reinterpret_cast<bf16x8*>(stage + r * 128 + ((pc ^ (r & 7)) << 4)) = kx;
+          *reinterpret_cast<bf16x8*>(stage + 4096 + r * 128 + ((pc ^ (r & 7)) << 4)) = vx;
         }
-      }
-      const float2 other = exchange(make_float2(dot, dpe));
-      const float pe = valid ? ex2(fmaf(dot + other.x, sc, -lse)) : 0.f;
-      const float dse = pe * (dpe + other.y - delta);
-      if (valid && ok) {
-        float* dkr = p.dke + ((int64_t)idx * p.nkv + kvh) * HD + colh;
-        float* dvr = p.dve + ((int64_t)idx * p.nkv + kvh) * HD + colh;
+        __syncwarp();
+        const unsigned char* k_row = stage + lane * 128;
+        const unsigned char* v_row = stage + 4096 + lane * 128;
+        const int lsw = lane & 7;
+        float dot = 0.f, dpe = 0.f;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          float a[8], b[8], g[8], w[8];
+          unpack8(*reinterpret_cast<const bf16x8*>(q_row + ((c ^ sw) << 4)), a);
+          unpack8(*reinterpret_cast<const bf16x8*>(k_row + ((c ^ lsw) << 4)), b);
+          unpack8(*reinterpret_cast<const bf16x8*>(do_row + ((c ^ sw) << 4)), g);
+          unpack8(*reinterpret_cast<const bf16x8*>(v_row + ((c ^ lsw) << 4)), w);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            dot = fmaf(a[i], b[i], dot);
+            dpe = fmaf(g[i], w[i], dpe);
+          }
+        }
+        const float2 other = exchange(make_float2(dot, dpe));
+        const float pe = valid ? ex2(fmaf(dot + other.x, sc, -lse)) : 0.f;
+        const float dse = pe * (dpe + other.y - delta);
         const float dss = dse * p.scale;
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
-          float a[8], b[8], g[8];
-          unpack8(*reinterpret_cast<const bf16x8*>(q_row + ((c ^ sw) << 4)), a);
-          unpack8(ld8(kr + c * 8), b);  // second read of the row: served by L1
-          unpack8(*reinterpret_cast<const bf16x8*>(do_row + ((c ^ sw) << 4)), g);
+          float b[8];
+          unpack8(*reinterpret_cast<const bf16x8*>(k_row + ((c ^ lsw) << 4)), b);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            dq[c * 8 + i] = fmaf(dse, b[i], dq[c * 8 + i]);
-            atomicAdd(dkr + c * 8 + i, dss * a[i]);
-            atomicAdd(dvr + c * 8 + i, pe * g[i]);
+          for (int i = 0; i < 8; ++i) dq[c * 8 + i] = fmaf(dse, b[i], dq[c * 8 + i]);
+        }
+        // contributions to the extra keys' dK (dss * q) then dV (pe * dO): each lane lays its
+        // row's 64 floats into the staging area, then 16 lanes add one row's 256 bytes
+#pragma unroll 1
+        for (int which = 0; which < 2; ++which) {
+          const unsigned char* src_row = which ? do_row : q_row;
+          const float mul = which ? pe : dss;
+          float* dst_base = (which ? p.dve : p.dke) + kvh * HD + colh;
+          __syncwarp();
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            float a[8];
+            unpack8(*reinterpret_cast<const bf16x8*>(src_row + ((c ^ sw) << 4)), a);
+            float4* out4 = reinterpret_cast<float4*>(stage + 8192 + lane * 256);
+            out4[(2 * c) ^ lsw] = make_float4(mul * a[0], mul * a[1], mul * a[2], mul * a[3]);
+            out4[(2 * c + 1) ^ lsw] = make_float4(mul * a[4], mul * a[5], mul * a[6], mul * a[7]);
+          }
+          __syncwarp();
+#pragma unroll
+          for (int it = 0; it < 16; ++it) {
+            const int r = it * 2 + (lane >> 4), pc = lane & 15;
+            const int ir = __shfl_sync(0xffffffffu, valid && ok ? idx : -1, r);
+            const float4 val = reinterpret_cast<const float4*>(stage + 8192 + r * 256)[pc ^ (r & 7)];
+            if (ir >= 0) atomicAdd(reinterpret_cast<float4*>(dst_base + (int64_t)ir * p.nkv * HD + pc * 4), val);
           }
         }
       }
@@ -402,8 +433,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
     mbar_init(smem_addr(&bar_s_full), 1);
     mbar_init(smem_addr(&bar_dp_full), 1);
-    mbar_init(smem_addr(&bar_p_ready), 256);
-    mbar_init(smem_addr(&bar_ds_ready), 256);
+    mbar_init(smem_addr(&bar_p_ready), 8);  // one arrival per element-wise warp
+    mbar_init(smem_addr(&bar_ds_ready), 8);  // one arrival per element-wise warp
     mbar_init(smem_addr(&bar_dv_done), 1);
     mbar_init(smem_addr(&bar_dk_done), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -590,7 +621,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       tmem_st32(lane_base + COL_ST + colh, pk);  // P^T over the first half of this thread's own S^T columns
       tmem_st_wait();
       fence_before_sync();
-      mbar_arrive(smem_addr(&bar_p_ready));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_addr(&bar_p_ready));
 
       if (ok) ok = mbar_wait(smem_addr(&bar_dp_full), t & 1, status, kTimeoutDkvCompute);
       ok = __all_sync(0xffffffffu, ok);
@@ -614,7 +646,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       tmem_st32(lane_base + COL_DPT + colh, pk);  // dS^T over the first half of this thread's own dP^T columns
       tmem_st_wait();
       fence_before_sync();
-      mbar_arrive(smem_addr(&bar_ds_ready));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_addr(&bar_ds_ready));
       if (t + 1 < n_tiles) stash_stats(t + 1);
     }
 

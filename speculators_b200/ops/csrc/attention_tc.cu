@@ -70,7 +70,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       mbar_init(smem_addr(&bar_v_empty[s]), 1);
       mbar_init(smem_addr(&bar_s_full[s]), 1);
     }
-    mbar_init(smem_addr(&bar_p_ready), 256);
+    mbar_init(smem_addr(&bar_p_ready), 8);  // one arrival per softmax warp
     mbar_init(smem_addr(&bar_o_full), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     s_range[0] = 0x7fffffff;
@@ -301,7 +301,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         tmem_st_wait();
       }
       fence_before_sync();
-      mbar_arrive(smem_addr(&bar_p_ready));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_addr(&bar_p_ready));
     }
 
     // this thread's 64 columns of the finished output row come back into registers
@@ -330,17 +331,31 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       if (ok) ok = mbar_wait(smem_addr(&bar_q), 0, status, kTimeoutSoftmax);
       ok = __all_sync(0xffffffffu, ok);
       const unsigned char* q_row = q_s + half * SUB_BYTES + prow * 128;
+      // rows of the extra K / V tensors come in through a per-warp staging area (the K / V
+      // stages, idle once the tile loop has drained): 8 lanes fetch the 128 bytes of one row's
+      // half, 4 rows per instruction, instead of every lane walking its own row
+      unsigned char* stage = k_s + (warp - 2) * 8192;
+      const int lsw = lane & 7;
       for (int e = 0; e < p.E; ++e) {
         const int idx = row_ok ? p.ext_idx[(int64_t)row * p.E + e] : -1;
         const bool valid = idx >= 0 && idx < p.Te;
-        const int64_t idc = valid ? idx : 0;
-        const __nv_bfloat16* kr = p.ke + idc * p.ke_rs + kvh * HD + colh;
-        const __nv_bfloat16* vr = p.ve + idc * p.ve_rs + kvh * HD + colh;
+        const int idc = valid ? idx : 0;
+        __syncwarp();
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int r = it * 4 + (lane >> 3), pc = lane & 7;
+          const int64_t ir = __shfl_sync(0xffffffffu, idc, r);
+          const bf16x8 kx = ld8(p.ke + ir * p.ke_rs + kvh * HD + colh + pc * 8);
+          const bf16x8 vx = ld8(p.ve + ir * p.ve_rs + kvh * HD + colh + pc * 8);
+          *reinterpret_cast<bf16x8*>(stage + r * 128 + ((pc ^ (r & 7)) << 4)) = kx;
+          *reinterpret_cast<bf16x8*>(stage + 4096 + r * 128 + ((pc ^ (r & 7)) << 4)) = vx;
+        }
+        __syncwarp();
         bf16x8 kreg[8], vreg[8];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) kreg[c] = ld8(kr + c * 8);
+        for (int c = 0; c < 8; ++c) kreg[c] = *reinterpret_cast<const bf16x8*>(stage + lane * 128 + ((c ^ lsw) << 4));
 #pragma unroll
-        for (int c = 0; c < 8; ++c) vreg[c] = ld8(vr + c * 8);
+        for (int c = 0; c < 8; ++c) vreg[c] = *reinterpret_cast<const bf16x8*>(stage + 4096 + lane * 128 + ((c ^ lsw) << 4));
         float d4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
