@@ -27,6 +27,8 @@ numerical oracle for both paths.
 
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 import torch.nn.functional as F
@@ -141,6 +143,7 @@ class SparseMoeBlock(nn.Module):
         shared = int(config.get("shared_expert_intermediate_size", 0) or 0)
         self.shared_expert = _SharedExpert(H, shared) if shared > 0 else None
         self.shared_expert_gate = Linear(H, 1, bias=False) if shared > 0 else None
+        self._comm = None  # peer-memory exchange buffers, created at the first expert-parallel CUDA call
 
     def route(self, x: torch.Tensor):
         probs = torch.softmax(self.gate(x).float(), dim=-1)
@@ -152,6 +155,11 @@ class SparseMoeBlock(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         T, H = x.shape
         top_p, top_e = self.route(x)
+        if self.ep_size > 1 and self._peer_exchange_ok(x):
+            out = self._expert_parallel_peer(x, top_p, top_e)
+            if self.shared_expert is not None:
+                out = out + torch.sigmoid(self.shared_expert_gate(x)) * self.shared_expert(x)
+            return out
         flat_e = top_e.reshape(-1)  # [T*k]
         token_of = torch.arange(T, device=x.device).repeat_interleave(self.top_k)
         order = torch.argsort(flat_e, stable=True)
@@ -167,6 +175,44 @@ class SparseMoeBlock(nn.Module):
         if self.shared_expert is not None:
             out = out + torch.sigmoid(self.shared_expert_gate(x)) * self.shared_expert(x)
         return out
+
+    # ------------------------------------------------------------------ peer-memory exchange
+    def _peer_exchange_ok(self, x: torch.Tensor) -> bool:
+        """bf16 CUDA activations go through the NVLink peer-memory kernels
+        (``parallel/ep_comm.py``); ``SB200_EP_COMM=nccl`` keeps the library all-to-all."""
+        return x.is_cuda and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and os.environ.get("SB200_EP_COMM", "p2p") != "nccl"
+
+    def _ep_comm(self, x: torch.Tensor):
+        """Exchange buffers of the group, created (collectively) at the first call.  Capacity:
+        ``SB200_EP_CAPACITY_ROWS`` or the worst case of this first call (every slot of every
+        rank routed to one rank)."""
+        if self._comm is None:
+            from speculators_b200.parallel.ep_comm import EpComm
+
+            t_max = torch.tensor([x.shape[0]], device=x.device)
+            dist.all_reduce(t_max, op=dist.ReduceOp.MAX, group=self.ep_group)
+            rows = int(os.environ.get("SB200_EP_CAPACITY_ROWS", 0)) or self.ep_size * int(t_max.item()) * self.top_k
+            self._comm = EpComm(self.ep_group, x.shape[1], rows, x.device)
+            self._comm.connect()
+        return self._comm
+
+    def _expert_parallel_peer(self, x: torch.Tensor, top_p: torch.Tensor, top_e: torch.Tensor) -> torch.Tensor:
+        """Dispatch, local experts, weighted combine with the rows moved by peer-memory
+        kernels; only the token counts go through the process group."""
+        from speculators_b200.parallel.ep_comm import build_plan, ep_combine, ep_dispatch
+
+        comm = self._ep_comm(x)
+        counts = torch.bincount(top_e.reshape(-1), minlength=self.num_experts)
+        counts_all = torch.empty(self.ep_size, self.num_experts, dtype=counts.dtype, device=x.device)
+        dist.all_gather_into_tensor(counts_all, counts, group=self.ep_group)
+        plan = build_plan(top_e, counts_all, self.ep_rank, self.num_local)
+        if plan.max_recv > comm.capacity:
+            raise RuntimeError(f"expert-parallel receive buffer too small: a rank receives {plan.max_recv} rows, capacity is "
+                               f"{comm.capacity}; set SB200_EP_CAPACITY_ROWS")
+        plan.parity = comm.next_parity()
+        recv_x = ep_dispatch(x, comm, plan)
+        ys = _grouped_expert_forward(recv_x, plan.local_counts, self.experts.gate_up_proj, self.experts.down_proj)
+        return ep_combine(ys, top_p, comm, plan)
 
     def _expert_parallel(self, xs: torch.Tensor, sorted_e: torch.Tensor) -> torch.Tensor:
         """Dispatch (all-to-all), local experts, combine (all-to-all).  Rows arrive

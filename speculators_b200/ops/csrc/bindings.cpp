@@ -5,6 +5,7 @@
 #include <torch/library.h>
 
 #include "attention_params.h"
+#include "ep_a2a.h"
 #include <ATen/ATen.h>
 
 namespace sb200 {
@@ -362,6 +363,71 @@ void fused_sharded_adamw(int64_t world, int64_t rank, int64_t shard, const Tenso
   TORCH_CHECK(rc == 0, "fused_sharded_adamw launch failed (", rc, ")");
 }
 
+// ---- expert-parallel token exchange --------------------------------------------------------
+// *_ptrs: int64 CPU tensors [world] with the address of one buffer on every rank as mapped here.
+sb200::EpPeers ep_peers(const Tensor& ptrs, int64_t world) {
+  TORCH_CHECK(ptrs.device().is_cpu() && ptrs.scalar_type() == at::kLong && ptrs.numel() == world && world >= 1 && world <= 16);
+  sb200::EpPeers out{};
+  for (int q = 0; q < world; ++q) out.ptr[q] = (unsigned long long)ptrs.data_ptr<int64_t>()[q];
+  return out;
+}
+void check_slots(const Tensor& t, int64_t n, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kInt && t.is_contiguous() && t.numel() == n, name, ": int32 CUDA [", n, "] expected");
+}
+
+void ep_push(const Tensor& src, const Tensor& src_row, const Tensor& dst_rank, const Tensor& dst_pos, const c10::optional<Tensor>& scale,
+             const Tensor& dst_ptrs, Tensor counter, const Tensor& flag_ptrs, int64_t rank, int64_t world, int64_t seq) {
+  check_rows(src, "src");
+  TORCH_CHECK(src.is_contiguous() && src.size(1) % 8 == 0, "src rows must be contiguous with a multiple of 8 columns");
+  const int64_t n = src_row.numel();
+  check_slots(src_row, n, "src_row");
+  check_slots(dst_rank, n, "dst_rank");
+  check_slots(dst_pos, n, "dst_pos");
+  if (scale.has_value()) TORCH_CHECK(scale->is_cuda() && scale->scalar_type() == at::kFloat && scale->is_contiguous() && scale->numel() == n);
+  TORCH_CHECK(counter.is_cuda() && counter.scalar_type() == at::kInt && counter.numel() >= 1);
+  c10::cuda::CUDAGuard guard(src.device());
+  const sb200::EpPeers dstp = ep_peers(dst_ptrs, world), flg = ep_peers(flag_ptrs, world);
+  const int rc = sb200::launch_ep_push((const __nv_bfloat16*)src.data_ptr(), src_row.data_ptr<int>(), dst_rank.data_ptr<int>(),
+                                       dst_pos.data_ptr<int>(), scale.has_value() ? scale->data_ptr<float>() : nullptr, (int)n,
+                                       (int)src.size(1), dstp, reinterpret_cast<unsigned int*>(counter.data_ptr<int>()), flg, (int)rank,
+                                       (int)world, (uint32_t)seq, cur_stream());
+  TORCH_CHECK(rc == 0, "ep_push launch failed (", rc, ")");
+}
+
+void ep_signal(const Tensor& flag_ptrs, int64_t rank, int64_t world, int64_t seq, const Tensor& on_device_of) {
+  c10::cuda::CUDAGuard guard(on_device_of.device());
+  const int rc = sb200::launch_ep_signal(ep_peers(flag_ptrs, world), (int)rank, (int)world, (uint32_t)seq, cur_stream());
+  TORCH_CHECK(rc == 0, "ep_signal launch failed (", rc, ")");
+}
+
+void ep_wait(const Tensor& flags_local, int64_t world, int64_t seq, int64_t spin_limit, Tensor status) {
+  TORCH_CHECK(flags_local.is_cuda() && flags_local.scalar_type() == at::kInt && flags_local.is_contiguous() && flags_local.numel() >= world);
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == at::kInt && status.numel() >= 1);
+  c10::cuda::CUDAGuard guard(flags_local.device());
+  const int rc = sb200::launch_ep_wait(reinterpret_cast<const uint32_t*>(flags_local.data_ptr<int>()), (int)world, (uint32_t)seq,
+                                       (uint32_t)spin_limit, status.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(rc == 0, "ep_wait launch failed (", rc, ")");
+}
+
+void ep_pull(const Tensor& src_ptrs, const Tensor& src_rank, const Tensor& src_pos, const c10::optional<Tensor>& weight, int64_t world,
+             Tensor out, int64_t k, c10::optional<Tensor> rows_out) {
+  check_rows(out, "out");
+  TORCH_CHECK(out.is_contiguous() && out.size(1) % 8 == 0);
+  const int64_t n = out.size(0) * k;
+  check_slots(src_rank, n, "src_rank");
+  check_slots(src_pos, n, "src_pos");
+  if (weight.has_value()) TORCH_CHECK(weight->is_cuda() && weight->scalar_type() == at::kFloat && weight->is_contiguous() && weight->numel() == n);
+  if (rows_out.has_value())
+    TORCH_CHECK(rows_out->is_cuda() && rows_out->scalar_type() == at::kBFloat16 && rows_out->is_contiguous() &&
+                rows_out->numel() == n * out.size(1), "rows_out: bf16 [T*k, H] expected");
+  c10::cuda::CUDAGuard guard(out.device());
+  const int rc = sb200::launch_ep_pull(ep_peers(src_ptrs, world), src_rank.data_ptr<int>(), src_pos.data_ptr<int>(),
+                                       weight.has_value() ? weight->data_ptr<float>() : nullptr, (int)out.size(0), (int)k, (int)out.size(1),
+                                       (int)world, (__nv_bfloat16*)out.data_ptr(),
+                                       rows_out.has_value() ? (__nv_bfloat16*)rows_out->data_ptr() : nullptr, cur_stream());
+  TORCH_CHECK(rc == 0, "ep_pull launch failed (", rc, ")");
+}
+
 // ---- tcgen05 GEMM ------------------------------------------------------------------------
 // out[M,N] = a[M,K] @ b[N,K]^T; epilogue 0 = store, 1 = out += result, 2 = result + residual.
 // `status` (int32[1], device) receives a non-zero code if a bounded wait in the kernel ran out.
@@ -556,6 +622,10 @@ TORCH_LIBRARY(sb200, m) {
   m.def("fused_optim_ctl_words", &fused_optim_ctl_words);
   m.def("fused_sharded_adamw", &fused_sharded_adamw);
   m.def("step_tail", &step_tail);
+  m.def("ep_push", &ep_push);
+  m.def("ep_signal", &ep_signal);
+  m.def("ep_wait", &ep_wait);
+  m.def("ep_pull", &ep_pull);
   m.def("hs_ring_ctl_words", &hs_ring_ctl_words);
   m.def("hs_push", &hs_push);
   m.def("hs_pop", &hs_pop);

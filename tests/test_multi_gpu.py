@@ -149,3 +149,60 @@ def test_hidden_state_ring_across_two_gpus(tmp_path):
     mp.spawn(_ring_worker, args=(2, str(tmp_path / "rdv"), str(out)), nprocs=2, join=True)
     result = json.loads(out.read_text())
     assert result["ok"] is True, result["notes"]
+
+
+def _moe_ep_worker(rank, world, port, out_path):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from speculators_b200.layer_config import TransformerLayerConfig
+    from speculators_b200.models.moe import SparseMoeBlock
+
+    cfg = TransformerLayerConfig(model_type="qwen3_next", hidden_size=256, intermediate_size=512, num_attention_heads=4,
+                                 num_key_value_heads=2, head_dim=64, vocab_size=128, num_experts=8, num_experts_per_tok=2,
+                                 moe_intermediate_size=128, shared_expert_intermediate_size=128)
+    torch.manual_seed(0)
+    block = SparseMoeBlock(cfg, ep_group=dist.group.WORLD).to(dev).to(torch.bfloat16)  # router / shared expert identical on both ranks
+    with torch.no_grad():
+        torch.manual_seed(10 + rank)
+        block.experts.gate_up_proj.copy_(torch.randn_like(block.experts.gate_up_proj) * 0.05)
+        block.experts.down_proj.copy_(torch.randn_like(block.experts.down_proj) * 0.05)
+    torch.manual_seed(100 + rank)
+    x0 = torch.randn(300 + 41 * rank, 256, device=dev).to(torch.bfloat16)
+    dout = torch.randn_like(x0)
+    results = {}
+    for mode in ("nccl", "p2p"):
+        os.environ["SB200_EP_COMM"] = mode
+        for p in block.parameters():
+            p.grad = None
+        x = x0.clone().requires_grad_()
+        for _ in range(3):  # several calls per step, then the backward passes in reverse order (as the MTP steps do)
+            y = block(x)
+        y2 = block(y)
+        (y2 * dout).sum().backward()
+        results[mode] = (y2.detach().float(), x.grad.float(), block.experts.down_proj.grad.float(), block.gate.weight.grad.float())
+    if block._comm is not None:
+        block._comm.check_status()
+    errs = [float((a - b).abs().max() / (b.abs().max() + 1e-6)) for a, b in zip(results["p2p"], results["nccl"])]
+    used_peer = block._comm is not None
+    gathered = [None] * world
+    dist.all_gather_object(gathered, {"errs": errs, "peer": used_peer})
+    if rank == 0:
+        with open(out_path, "w") as fh:
+            json.dump(gathered, fh)
+    if block._comm is not None:
+        block._comm.close()
+    dist.destroy_process_group()
+
+
+def test_moe_expert_parallel_peer_exchange_matches_nccl(tmp_path):
+    """Dispatch / combine through the NVLink peer-memory kernels against the all-to-all path:
+    outputs, input gradients, expert and router gradients on two GPUs."""
+    _need_two()
+    out = tmp_path / "moe.json"
+    mp.spawn(_moe_ep_worker, args=(2, 29651, str(out)), nprocs=2, join=True)
+    res = json.loads(out.read_text())
+    for r in res:
+        assert r["peer"], res
+        assert max(r["errs"]) < 3e-2, res
