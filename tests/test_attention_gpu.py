@@ -116,3 +116,35 @@ def test_tc_forward_rows_without_any_key():
     assert (out[120:140] == 0).all() and (out[256:] == 0).all()
     torch.testing.assert_close(out.float(), ref, atol=2e-2, rtol=2e-2)
     check_gemm_status()
+
+
+def test_tc_kernels_with_separate_query_and_context_lengths_and_many_extras():
+    """Block drafting shape: Tq != Tc, every query sees a prefix of the context plus up to
+    eight individually addressed extra keys (some slots unused, rows shared between queries)."""
+    from speculators_b200.ops import check_gemm_status
+
+    torch.manual_seed(7)
+    Tq, Tc, Te, nh, nkv, hd, E = 389, 530, 389, 8, 2, 128, 8
+    q = torch.randn(Tq, nh, hd, device=DEV).to(torch.bfloat16)
+    k = torch.randn(Tc, nkv, hd, device=DEV).to(torch.bfloat16)
+    v = torch.randn(Tc, nkv, hd, device=DEV).to(torch.bfloat16)
+    ke = torch.randn(Te, nkv, hd, device=DEV).to(torch.bfloat16)
+    ve = torch.randn(Te, nkv, hd, device=DEV).to(torch.bfloat16)
+    hi = torch.randint(0, Tc + 1, (Tq,), device=DEV, dtype=torch.int32)
+    lo = (hi.float() * torch.rand(Tq, device=DEV)).to(torch.int32)
+    block = torch.arange(Tq, device=DEV) // E * E
+    ext = block[:, None] + torch.arange(E, device=DEV)[None, :]  # the query's own block of extra rows
+    ext = torch.where((ext <= torch.arange(Tq, device=DEV)[:, None]) & (ext < Te), ext, torch.full_like(ext, -1)).to(torch.int32)
+    spec = AttnSpec(lo=lo, hi=hi, extra_idx=ext)
+    leaves = [t.detach().clone().requires_grad_() for t in (q, k, v, ke, ve)]
+    out = masked_attention(leaves[0], leaves[1], leaves[2], spec, leaves[3], leaves[4])
+    dout = torch.randn_like(out)
+    out.backward(dout)
+    refs = [t.detach().float().requires_grad_() for t in (q, k, v, ke, ve)]
+    ref = masked_attention_reference(refs[0], refs[1], refs[2], spec, refs[3], refs[4])
+    ref.backward(dout.float())
+    torch.testing.assert_close(out.float(), ref, atol=2e-2, rtol=2e-2)
+    for name, a, b in zip(["dq", "dk", "dv", "dk_ext", "dv_ext"], leaves, refs):
+        tol = 3e-2 * float(b.grad.abs().max()) + 2e-2
+        assert float((a.grad.float() - b.grad).abs().max()) < tol, name
+    check_gemm_status()
