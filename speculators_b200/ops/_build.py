@@ -20,7 +20,13 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 BUILD = HERE / "build"
+BUILD_CHECKED = HERE / "build_checked"
 LIB = HERE / "_sb200.so"
+# Debug flavour: same sources with -DSB200_CHECK_BOUNDS (data-dependent row indices are
+# validated in the kernels, violations recorded and skipped); selected with
+# SB200_CHECKED_BUILD=1, built on demand with build(checked=True).
+LIB_CHECKED = HERE / "_sb200_checked.so"
+CHECKED = os.environ.get("SB200_CHECKED_BUILD", "0") == "1"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -58,20 +64,32 @@ def _run(cmd: list[str]) -> None:
         raise RuntimeError(f"command failed: {' '.join(cmd)}\n{proc.stdout}\n{proc.stderr}")
 
 
-def is_current() -> bool:
+def active_lib() -> Path:
+    return LIB_CHECKED if CHECKED else LIB
+
+
+def is_current(checked: bool | None = None) -> bool:
     import torch
 
-    stamp = BUILD / "stamp"
-    return LIB.exists() and stamp.exists() and stamp.read_text() == _digest(torch.__version__)
+    checked = CHECKED if checked is None else checked
+    lib = LIB_CHECKED if checked else LIB
+    stamp = (BUILD_CHECKED if checked else BUILD) / "stamp"
+    return lib.exists() and stamp.exists() and stamp.read_text() == _digest(torch.__version__ + ("+checked" if checked else ""))
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
+def build(force: bool = False, verbose: bool = False, checked: bool | None = None) -> Path:
     """Compile every kernel for sm_100a and link the extension; returns the .so path."""
     import torch
     from torch.utils import cpp_extension
 
-    if not force and is_current():
-        return LIB
+    checked = CHECKED if checked is None else checked
+    if not force and is_current(checked):
+        return LIB_CHECKED if checked else LIB
+    return _build_into(BUILD_CHECKED if checked else BUILD, LIB_CHECKED if checked else LIB,
+                       ["-DSB200_CHECK_BOUNDS"] if checked else [], "+checked" if checked else "", verbose, torch, cpp_extension)
+
+
+def _build_into(BUILD: Path, LIB: Path, defines: list[str], tag: str, verbose: bool, torch, cpp_extension) -> Path:  # noqa: N803
     BUILD.mkdir(exist_ok=True)
     cu, cpp = _sources()
     nvcc = _nvcc()
@@ -84,11 +102,11 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     for src in cu:
         obj = BUILD / (src.stem + ".o")
         objs.append(obj)
-        jobs.append([nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)])
+        jobs.append([nvcc, *NVCC_FLAGS, *defines, "-I", str(CSRC), "-c", str(src), "-o", str(obj)])
     for src in cpp:
         obj = BUILD / (src.stem + ".cpp.o")
         objs.append(obj)
-        cmd = ["g++", "-O2", "-std=c++17", "-fPIC", f"-D_GLIBCXX_USE_CXX11_ABI={abi}",
+        cmd = ["g++", "-O2", "-std=c++17", "-fPIC", *defines, f"-D_GLIBCXX_USE_CXX11_ABI={abi}",
                "-I", str(CSRC), "-I", str(cuda_home / "include")]
         for inc in torch_inc:
             cmd += ["-isystem", inc]
@@ -105,9 +123,9 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             f"-L{cuda_home / 'lib64'}", "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch",
             "-lcudart", f"-Wl,-rpath,{torch_lib}", f"-Wl,-rpath,{cuda_home / 'lib64'}"]
     _run(link)
-    (BUILD / "stamp").write_text(_digest(torch.__version__))
+    (BUILD / "stamp").write_text(_digest(torch.__version__ + tag))
     return LIB
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose=True))
+    print(build(force="--force" in sys.argv, verbose=True, checked=True if "--checked" in sys.argv else None))

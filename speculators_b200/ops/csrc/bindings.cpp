@@ -11,7 +11,14 @@
 namespace sb200 {
 int rmsnorm_bwd_partial_rows(int rows);
 void launch_rmsnorm_fwd(const void*, const void*, const int64_t*, void*, float*, int, int, int64_t,
-                        int64_t, float, cudaStream_t);
+                        int64_t, float, int64_t, cudaStream_t);
+struct BoundsRecord {
+  int site;
+  long long index;
+  long long limit;
+};
+int read_bounds_norm(BoundsRecord*);
+int read_bounds_ep(BoundsRecord*);
 void launch_rmsnorm_bwd(const void*, const void*, const void*, const float*, void*, float*, float*,
                         int, int, int64_t, int64_t, int64_t, int, int, cudaStream_t);
 void launch_swiglu_fwd(const void*, void*, int64_t, int, cudaStream_t);
@@ -85,7 +92,7 @@ void rmsnorm_fwd(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& 
   }
   c10::cuda::CUDAGuard guard(x.device());
   sb200::launch_rmsnorm_fwd(x.data_ptr(), w.data_ptr(), idx, y.data_ptr(), rs, rows, H, x.stride(0),
-                            y.stride(0), (float)eps, cur_stream());
+                            y.stride(0), (float)eps, x.size(0), cur_stream());
 }
 
 void rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd, Tensor dx,
@@ -363,6 +370,28 @@ void fused_sharded_adamw(int64_t world, int64_t rank, int64_t shard, const Tenso
   TORCH_CHECK(rc == 0, "fused_sharded_adamw launch failed (", rc, ")");
 }
 
+// ---- debug build: index checks -------------------------------------------------------------
+bool checked_build() {
+#ifdef SB200_CHECK_BOUNDS
+  return true;
+#else
+  return false;
+#endif
+}
+// One row (site, index, limit) per module with index checks; site 0 = nothing recorded since
+// the last call.  Reading clears the records.  Always zeros in the normal build.
+Tensor bounds_report() {
+  Tensor out = at::zeros({2, 3}, at::TensorOptions().dtype(at::kLong));
+  sb200::BoundsRecord rec[2];
+  TORCH_CHECK(sb200::read_bounds_norm(&rec[0]) == 0 && sb200::read_bounds_ep(&rec[1]) == 0, "bounds_report: reading the device records failed");
+  for (int i = 0; i < 2; ++i) {
+    out[i][0] = (int64_t)rec[i].site;
+    out[i][1] = (int64_t)rec[i].index;
+    out[i][2] = (int64_t)rec[i].limit;
+  }
+  return out;
+}
+
 // ---- expert-parallel token exchange --------------------------------------------------------
 // *_ptrs: int64 CPU tensors [world] with the address of one buffer on every rank as mapped here.
 sb200::EpPeers ep_peers(const Tensor& ptrs, int64_t world) {
@@ -376,7 +405,8 @@ void check_slots(const Tensor& t, int64_t n, const char* name) {
 }
 
 void ep_push(const Tensor& src, const Tensor& src_row, const Tensor& dst_rank, const Tensor& dst_pos, const c10::optional<Tensor>& scale,
-             const Tensor& dst_ptrs, Tensor counter, const Tensor& flag_ptrs, int64_t rank, int64_t world, int64_t seq) {
+             const Tensor& dst_ptrs, int64_t capacity, Tensor counter, const Tensor& flag_ptrs, int64_t rank, int64_t world,
+             int64_t seq) {
   check_rows(src, "src");
   TORCH_CHECK(src.is_contiguous() && src.size(1) % 8 == 0, "src rows must be contiguous with a multiple of 8 columns");
   const int64_t n = src_row.numel();
@@ -389,8 +419,9 @@ void ep_push(const Tensor& src, const Tensor& src_row, const Tensor& dst_rank, c
   const sb200::EpPeers dstp = ep_peers(dst_ptrs, world), flg = ep_peers(flag_ptrs, world);
   const int rc = sb200::launch_ep_push((const __nv_bfloat16*)src.data_ptr(), src_row.data_ptr<int>(), dst_rank.data_ptr<int>(),
                                        dst_pos.data_ptr<int>(), scale.has_value() ? scale->data_ptr<float>() : nullptr, (int)n,
-                                       (int)src.size(1), dstp, reinterpret_cast<unsigned int*>(counter.data_ptr<int>()), flg, (int)rank,
-                                       (int)world, (uint32_t)seq, cur_stream());
+                                       (int)src.size(1), (int)src.size(0), (int)capacity, dstp,
+                                       reinterpret_cast<unsigned int*>(counter.data_ptr<int>()), flg, (int)rank, (int)world, (uint32_t)seq,
+                                       cur_stream());
   TORCH_CHECK(rc == 0, "ep_push launch failed (", rc, ")");
 }
 
@@ -409,8 +440,8 @@ void ep_wait(const Tensor& flags_local, int64_t world, int64_t seq, int64_t spin
   TORCH_CHECK(rc == 0, "ep_wait launch failed (", rc, ")");
 }
 
-void ep_pull(const Tensor& src_ptrs, const Tensor& src_rank, const Tensor& src_pos, const c10::optional<Tensor>& weight, int64_t world,
-             Tensor out, int64_t k, c10::optional<Tensor> rows_out) {
+void ep_pull(const Tensor& src_ptrs, int64_t capacity, const Tensor& src_rank, const Tensor& src_pos, const c10::optional<Tensor>& weight,
+             int64_t world, Tensor out, int64_t k, c10::optional<Tensor> rows_out) {
   check_rows(out, "out");
   TORCH_CHECK(out.is_contiguous() && out.size(1) % 8 == 0);
   const int64_t n = out.size(0) * k;
@@ -423,7 +454,7 @@ void ep_pull(const Tensor& src_ptrs, const Tensor& src_rank, const Tensor& src_p
   c10::cuda::CUDAGuard guard(out.device());
   const int rc = sb200::launch_ep_pull(ep_peers(src_ptrs, world), src_rank.data_ptr<int>(), src_pos.data_ptr<int>(),
                                        weight.has_value() ? weight->data_ptr<float>() : nullptr, (int)out.size(0), (int)k, (int)out.size(1),
-                                       (int)world, (__nv_bfloat16*)out.data_ptr(),
+                                       (int)world, (int)capacity, (__nv_bfloat16*)out.data_ptr(),
                                        rows_out.has_value() ? (__nv_bfloat16*)rows_out->data_ptr() : nullptr, cur_stream());
   TORCH_CHECK(rc == 0, "ep_pull launch failed (", rc, ")");
 }
@@ -622,6 +653,8 @@ TORCH_LIBRARY(sb200, m) {
   m.def("fused_optim_ctl_words", &fused_optim_ctl_words);
   m.def("fused_sharded_adamw", &fused_sharded_adamw);
   m.def("step_tail", &step_tail);
+  m.def("checked_build", &checked_build);
+  m.def("bounds_report", &bounds_report);
   m.def("ep_push", &ep_push);
   m.def("ep_signal", &ep_signal);
   m.def("ep_wait", &ep_wait);

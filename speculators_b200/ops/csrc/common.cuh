@@ -8,6 +8,45 @@ namespace sb200 {
 
 void count_launch(int n);
 
+// Debug build (-DSB200_CHECK_BOUNDS): kernels validate data-dependent row indices before
+// using them.  The first violation is recorded (site, index, limit) in a per-module device
+// record that the host reads back; the access is skipped, so a bad index never becomes a
+// fault.  In the normal build the check compiles to `true`.
+//   sites: 1 rmsnorm gather row, 2 exchange push source row, 3 exchange push destination
+//          row, 4 exchange pull source row
+struct BoundsRecord {
+  int site;
+  long long index;
+  long long limit;
+};
+#ifdef SB200_CHECK_BOUNDS
+__device__ __forceinline__ bool bounds_ok(BoundsRecord* rec, long long idx, long long n, int site) {
+  if (idx >= 0 && idx < n) return true;
+  if (atomicCAS(&rec->site, 0, site) == 0) {
+    rec->index = idx;
+    rec->limit = n;
+  }
+  return false;
+}
+#define SB200_BOUNDS_RECORD static __device__ sb200::BoundsRecord g_bounds = {0, 0, 0};
+#define SB200_IN_RANGE(idx, n, site) sb200::bounds_ok(&g_bounds, (long long)(idx), (long long)(n), site)
+// host side: copy the module's record out and clear it
+#define SB200_BOUNDS_READER(name)                                                       \
+  int name(BoundsRecord* out) {                                                         \
+    if (cudaMemcpyFromSymbol(out, g_bounds, sizeof(BoundsRecord)) != cudaSuccess) return -1; \
+    const BoundsRecord zero = {0, 0, 0};                                                \
+    return cudaMemcpyToSymbol(g_bounds, &zero, sizeof(BoundsRecord)) == cudaSuccess ? 0 : -1; \
+  }
+#else
+#define SB200_BOUNDS_RECORD
+#define SB200_IN_RANGE(idx, n, site) true
+#define SB200_BOUNDS_READER(name)  \
+  int name(BoundsRecord* out) {    \
+    *out = BoundsRecord{0, 0, 0};  \
+    return 0;                      \
+  }
+#endif
+
 constexpr int kWarp = 32;
 // B200: 148 SMs.  Persistent / grid-stride kernels size their grids from this.
 constexpr int kNumSM = 148;

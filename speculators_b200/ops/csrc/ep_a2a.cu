@@ -36,15 +36,18 @@ __device__ __forceinline__ uint32_t ep_ld_acquire_sys(const uint32_t* p) {
 
 constexpr int kWarpsPerBlock = 8;
 
+SB200_BOUNDS_RECORD
+
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 ep_push_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ src_row, const int* __restrict__ dst_rank,
-               const int* __restrict__ dst_pos, const float* __restrict__ scale, int n_slots, int H, EpPeers dst, unsigned int* done_counter, EpPeers flags, int my_rank, int world, uint32_t seq) {
+               const int* __restrict__ dst_pos, const float* __restrict__ scale, int n_slots, int H, int src_rows, int capacity, EpPeers dst, unsigned int* done_counter, EpPeers flags, int my_rank, int world, uint32_t seq) {
   const int lane = threadIdx.x & 31;
   const int nvec = H >> 3;
   for (int s = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5); s < n_slots; s += gridDim.x * kWarpsPerBlock) {
     const int r = dst_rank[s];
     if (r < 0 || r >= world) continue;
     const int64_t pos = dst_pos[s];
+    if (!SB200_IN_RANGE(src_row[s], src_rows, 2) || !SB200_IN_RANGE(pos, capacity, 3)) continue;  // debug build only
     const __nv_bfloat16* in = src + (int64_t)src_row[s] * H;
     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(dst.ptr[r]) + pos * H;
     const float w = scale != nullptr ? scale[s] : 1.f;
@@ -91,7 +94,7 @@ __global__ void ep_wait_kernel(const uint32_t* __restrict__ flags_local, int wor
 
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 ep_pull_kernel(EpPeers src, const int* __restrict__ src_rank, const int* __restrict__ src_pos, const float* __restrict__ weight,
-               int T, int k, int H, int world, __nv_bfloat16* __restrict__ out, __nv_bfloat16* __restrict__ rows_out) {
+               int T, int k, int H, int world, int capacity, __nv_bfloat16* __restrict__ out, __nv_bfloat16* __restrict__ rows_out) {
   const int lane = threadIdx.x & 31;
   const int nvec = H >> 3;
   for (int t = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5); t < T; t += gridDim.x * kWarpsPerBlock) {
@@ -103,6 +106,7 @@ ep_pull_kernel(EpPeers src, const int* __restrict__ src_rank, const int* __restr
         const int s = t * k + j;
         const int r = src_rank[s];
         if (r < 0 || r >= world) continue;
+        if (!SB200_IN_RANGE(src_pos[s], capacity, 4)) continue;  // debug build only
         const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(src.ptr[r]) + (int64_t)src_pos[s] * H;
         const float w = weight != nullptr ? weight[s] : 1.f;
         const bf16x8 raw = ld8(row + v * 8);
@@ -124,12 +128,14 @@ int grid_for(int64_t units) {
 
 }  // namespace
 
+SB200_BOUNDS_READER(read_bounds_ep)
+
 int launch_ep_push(const __nv_bfloat16* src, const int* src_row, const int* dst_rank, const int* dst_pos, const float* scale,
-                   int n_slots, int H, const EpPeers& dst, unsigned int* done_counter,
+                   int n_slots, int H, int src_rows, int capacity, const EpPeers& dst, unsigned int* done_counter,
                    const EpPeers& flags, int my_rank, int world, uint32_t seq, cudaStream_t stream) {
   if (H % 8 != 0 || world < 1 || world > 16) return -1;
   count_launch(1);
-  ep_push_kernel<<<grid_for(n_slots), kWarpsPerBlock * 32, 0, stream>>>(src, src_row, dst_rank, dst_pos, scale, n_slots, H, dst, done_counter, flags,
+  ep_push_kernel<<<grid_for(n_slots), kWarpsPerBlock * 32, 0, stream>>>(src, src_row, dst_rank, dst_pos, scale, n_slots, H, src_rows, capacity, dst, done_counter, flags,
                                                                        my_rank, world, seq);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
@@ -149,10 +155,10 @@ int launch_ep_wait(const uint32_t* flags_local, int world, uint32_t seq, uint32_
 }
 
 int launch_ep_pull(const EpPeers& src, const int* src_rank, const int* src_pos, const float* weight, int T, int k, int H, int world,
-                   __nv_bfloat16* out, __nv_bfloat16* rows_out, cudaStream_t stream) {
+                   int capacity, __nv_bfloat16* out, __nv_bfloat16* rows_out, cudaStream_t stream) {
   if (H % 8 != 0 || world < 1 || world > 16) return -1;
   count_launch(1);
-  ep_pull_kernel<<<grid_for(T), kWarpsPerBlock * 32, 0, stream>>>(src, src_rank, src_pos, weight, T, k, H, world, out, rows_out);
+  ep_pull_kernel<<<grid_for(T), kWarpsPerBlock * 32, 0, stream>>>(src, src_rank, src_pos, weight, T, k, H, world, capacity, out, rows_out);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

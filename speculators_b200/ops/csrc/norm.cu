@@ -17,16 +17,19 @@ constexpr int kNormThreads = 256;
 // Vectors (8 x bf16) handled per thread are a template parameter NV in {2, 4, 8}:
 // H <= 256 * 8 * NV, i.e. 4096 / 8192 / 16384 columns.
 
+SB200_BOUNDS_RECORD
+
 template <int NV>
 __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                    const int64_t* __restrict__ row_index, __nv_bfloat16* __restrict__ y,
                    float* __restrict__ rstd_out, int rows, int H, int64_t x_stride,
-                   int64_t y_stride, float eps) {
+                   int64_t y_stride, float eps, int64_t src_rows) {
   __shared__ float scratch[33];
   const int nvec = H >> 3;
   for (int r = blockIdx.x; r < rows; r += gridDim.x) {
     const int64_t src = row_index ? row_index[r] : (int64_t)r;
+    if (!SB200_IN_RANGE(src, src_rows, 1)) continue;  // debug build only
     const __nv_bfloat16* xr = x + src * x_stride;
     float cache[NV][8];
     float ss = 0.f;
@@ -193,15 +196,18 @@ int rmsnorm_bwd_partial_rows(int rows) {
   return rows < g ? rows : g;
 }
 
+SB200_BOUNDS_READER(read_bounds_norm)
+
+// src_rows: number of rows of `x` (what `row_index` may address).
 void launch_rmsnorm_fwd(const void* x, const void* w, const int64_t* row_index, void* y,
                         float* rstd, int rows, int H, int64_t x_stride, int64_t y_stride, float eps,
-                        cudaStream_t stream) {
+                        int64_t src_rows, cudaStream_t stream) {
   if (rows <= 0) return;
   int grid = rows < 8 * kNumSM ? rows : 8 * kNumSM;
 #define SB200_FWD(NVV)                                                                         \
   rmsnorm_fwd_kernel<NVV><<<grid, kNormThreads, 0, stream>>>(                                    \
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, row_index, (__nv_bfloat16*)y, rstd, rows, \
-      H, x_stride, y_stride, eps)
+      H, x_stride, y_stride, eps, src_rows)
   count_launch(1);
   if (H <= 4096) SB200_FWD(2);
   else if (H <= 8192) SB200_FWD(4);

@@ -171,8 +171,8 @@ class EpComm:
         """Rows of ``src`` to their slots' places in the ranks' ``kind`` buffers, then publish.
         Returns the sequence number to wait for."""
         seq = self._next_seq()
-        self._nat.ep_push(src, plan.src_row, plan.dst_rank, plan.dst_pos, scale, self.ptrs[(kind, parity)], self.counter,
-                          self.flag_ptrs, self.rank, self.world, seq)
+        self._nat.ep_push(src, plan.src_row, plan.dst_rank, plan.dst_pos, scale, self.ptrs[(kind, parity)], self.capacity,
+                          self.counter, self.flag_ptrs, self.rank, self.world, seq)
         return seq
 
     def signal(self) -> int:
@@ -188,7 +188,7 @@ class EpComm:
         ``keep_rows`` also the gathered rows [T*k, H]."""
         out = torch.empty(n_tokens, self.hidden, dtype=torch.bfloat16, device=self.device)
         rows = torch.empty(n_tokens * plan.top_k, self.hidden, dtype=torch.bfloat16, device=self.device) if keep_rows else None
-        self._nat.ep_pull(self.ptrs[(kind, parity)], plan.dst_rank, plan.dst_pos, weight, self.world, out, plan.top_k, rows)
+        self._nat.ep_pull(self.ptrs[(kind, parity)], self.capacity, plan.dst_rank, plan.dst_pos, weight, self.world, out, plan.top_k, rows)
         return (out, rows) if keep_rows else out
 
     def check_status(self) -> None:
