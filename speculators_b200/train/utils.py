@@ -30,17 +30,20 @@ def normalize_counted_metrics(metrics: dict[str, float], world_size: int = 1) ->
 
 
 def save_train_command(save_dir: str | os.PathLike, argv: list[str] | None = None) -> str:
-    """Write ``train_command.txt``: timestamp, git revision, world size, package
-    versions and the exact command line."""
-    argv = list(sys.argv if argv is None else argv)
+    """Write ``train_command.txt``: a provenance header (``# Timestamp:``, ``# Git SHA:``,
+    ``# World size:``, one ``# <package>: <version>`` line per tracked package) followed by
+    the shell-quoted command line.  ``argv`` is the command the run was resolved from;
+    without it the live ``sys.argv`` is recorded.  The file is replaced atomically
+    (src/speculators/train/utils.py:103-150)."""
+    argv = list(argv or sys.argv)
     os.makedirs(save_dir, exist_ok=True)
     lines = [
-        f"# {datetime.datetime.now(datetime.timezone.utc).isoformat()}",
-        f"# git: {provenance.git_sha() or 'unknown'}",
-        f"# world_size: {os.environ.get('WORLD_SIZE', '1')}",
+        f"# Timestamp: {datetime.datetime.now(datetime.timezone.utc).isoformat()}",
+        f"# Git SHA: {provenance.git_sha() or 'unknown'}",
+        f"# World size: {os.environ.get('WORLD_SIZE', '1')}",
     ]
-    lines += [f"# {pkg}=={ver}" for pkg, ver in provenance.package_versions().items()]
-    lines.append(" ".join(shlex.quote(a) for a in [sys.executable, *argv]))
+    lines += [f"# {pkg}: {ver}" for pkg, ver in provenance.package_versions().items()]
+    lines.append(shlex.join(argv))
     path = os.path.join(save_dir, "train_command.txt")
     provenance.atomic_write(path, "\n".join(lines) + "\n")
     return path
