@@ -6,14 +6,16 @@ schema every time the registry changes (src/speculators/utils/pydantic_utils.py:
 41-194, ``reload_schema``).  Here the dispatch happens at validation time in a
 ``wrap`` validator on the base class, so a subclass registered after import is
 picked up without any schema rebuild; ``reload_schema`` is kept as a cheap
-``model_rebuild`` for API parity.
+``model_rebuild`` for API parity.  In the other direction a ``wrap`` serializer makes a
+field declared with the family's base type dump the fields of the concrete subclass it
+holds (pydantic alone would serialize by the declared type and drop them).
 """
 
 from __future__ import annotations
 
 from typing import Any, ClassVar
 
-from pydantic import BaseModel, model_validator
+from pydantic import BaseModel, model_serializer, model_validator
 
 from speculators_b200.utils.registry import ClassRegistryMixin
 
@@ -64,3 +66,25 @@ class PydanticClassRegistryMixin(ReloadableBaseModel, ClassRegistryMixin):
                 )
             return handler(value)
         return target.model_validate(value)
+
+    @model_serializer(mode="wrap")
+    def _serialize_as_own_class(self, handler, info):  # noqa: ANN001
+        data = handler(self)
+        own = type(self)
+        if not isinstance(data, dict) or id(self) in _RESERIALIZING or info.include or info.exclude:
+            return data
+        if all(name in data for name in own.model_fields):
+            return data
+        # fields are missing: dropped by the caller's exclude_* flags, or because this instance
+        # was reached through a field typed as a base class; dumping with the instance's own
+        # schema and the same flags is right in both cases
+        _RESERIALIZING.add(id(self))
+        try:
+            return own.__pydantic_serializer__.to_python(
+                self, mode=info.mode, by_alias=info.by_alias, exclude_unset=info.exclude_unset, exclude_defaults=info.exclude_defaults,
+                exclude_none=info.exclude_none, round_trip=info.round_trip, warnings=False)
+        finally:
+            _RESERIALIZING.discard(id(self))
+
+
+_RESERIALIZING: set[int] = set()

@@ -1,0 +1,120 @@
+"""Small utilities: rank filter of the logger, pydantic class registry, checkpoint loading helpers."""
+
+import json
+import logging
+
+import pytest
+import torch
+from pydantic import BaseModel
+from safetensors.torch import save_file
+
+from speculators_b200.train.logger import IsRank0Filter
+from speculators_b200.utils import loading
+from speculators_b200.utils.pydantic_utils import PydanticClassRegistryMixin, ReloadableBaseModel
+
+
+def _record(**extra):
+    record = logging.LogRecord("speculators", logging.INFO, __file__, 0, "msg", None, None)
+    for k, v in extra.items():
+        setattr(record, k, v)
+    return record
+
+
+def test_rank0_filter_uses_the_global_rank(monkeypatch):
+    monkeypatch.setenv("RANK", "1")
+    monkeypatch.setenv("LOCAL_RANK", "0")  # first process of a second node: not global rank 0
+    assert IsRank0Filter().filter(_record()) is False
+    monkeypatch.setenv("RANK", "0")
+    assert IsRank0Filter().filter(_record()) is True
+    monkeypatch.setenv("RANK", "3")
+    assert IsRank0Filter().filter(_record(override_rank0_filter=True)) is True
+
+
+# ---------------------------------------------------------------- pydantic registry
+def test_reloadable_model_and_registry_marshalling():
+    class Plain(ReloadableBaseModel):
+        x: int = 1
+
+    assert Plain().x == 1
+    Plain.reload_schema()  # must not raise
+    assert Plain(x=3).model_dump() == {"x": 3}
+
+    class Shape(PydanticClassRegistryMixin):
+        schema_discriminator = "kind"
+        kind: str
+
+        @classmethod
+        def __pydantic_schema_base_type__(cls):
+            return Shape if cls.__name__ == "Shape" else cls
+
+    @Shape.register("circle")
+    class Circle(Shape):
+        kind: str = "circle"
+        r: float = 1.0
+
+    @Shape.register()
+    class Square(Shape):
+        kind: str = "Square"
+        side: float = 2.0
+
+    assert Shape.registry["circle"] is Circle and "Square" in Shape.registry
+    with pytest.raises(TypeError):
+        Shape.register_decorator(object)  # not a pydantic model
+
+    class Holder(BaseModel):
+        shape: Shape
+
+    Shape.reload_schema()
+    Holder.model_rebuild(force=True)
+    held = Holder.model_validate({"shape": {"kind": "circle", "r": 2.5}})
+    assert isinstance(held.shape, Circle) and held.shape.r == 2.5
+    assert isinstance(Shape.model_validate({"kind": "Square"}), Square)
+    assert Holder.model_validate(held.model_dump()).shape == held.shape
+
+
+# ---------------------------------------------------------------- loading helpers
+def test_config_only_dir_detection(tmp_path):
+    assert not loading.is_config_only_dir(tmp_path)  # no config.json
+    (tmp_path / "config.json").write_text("{}")
+    assert loading.is_config_only_dir(tmp_path)
+    for name in ("pytorch_model.bin", "model.safetensors.index.json", "pytorch_model.bin.index.json", "model-00001-of-00002.safetensors"):
+        marker = tmp_path / name
+        marker.write_text("x")
+        assert not loading.is_config_only_dir(tmp_path), name
+        marker.unlink()
+    assert not loading.is_config_only_dir(tmp_path / "config.json")  # a file, not a directory
+
+
+def test_key_resolution_exact_suffix_and_aliases():
+    keys = ["model.embed_tokens.weight", "model.layers.0.mlp.up_proj.weight", "output.weight", "norm.weight"]
+    assert loading._match("model.embed_tokens.weight", keys) == "model.embed_tokens.weight"
+    assert loading._match("embed_tokens.weight", keys) == "model.embed_tokens.weight"  # suffix
+    assert loading._match("lm_head.weight", keys) == "output.weight"  # alias, exact
+    assert loading._match("model.norm.weight", keys) == "norm.weight"
+    assert loading._match("llm.embed.weight", ["prefix.llm.embed.weight"]) == "prefix.llm.embed.weight"
+    assert loading._match("missing.weight", keys) is None
+    assert loading._match("lm_head.weight", ["lm_head.weight", "output.weight"]) == "lm_head.weight"  # exact beats alias
+
+
+def test_load_layers_from_single_file_and_sharded_checkpoints(tmp_path):
+    tensors = {"model.embed_tokens.weight": torch.randn(8, 4), "model.norm.weight": torch.randn(4), "lm_head.weight": torch.randn(8, 4)}
+    single = tmp_path / "single"
+    single.mkdir()
+    save_file(tensors, str(single / "model.safetensors"))
+    got = loading.load_model_layers(["embed_tokens.weight", "lm_head.weight", "nope.weight"], single)
+    assert set(got) == {"embed_tokens.weight", "lm_head.weight"}
+    assert torch.equal(got["embed_tokens.weight"], tensors["model.embed_tokens.weight"])
+    assert sorted(loading.list_checkpoint_keys(single)) == sorted(tensors)
+
+    sharded = tmp_path / "sharded"
+    sharded.mkdir()
+    save_file({"model.embed_tokens.weight": tensors["model.embed_tokens.weight"]}, str(sharded / "a.safetensors"))
+    save_file({k: v for k, v in tensors.items() if k != "model.embed_tokens.weight"}, str(sharded / "b.safetensors"))
+    wmap = {"model.embed_tokens.weight": "a.safetensors", "model.norm.weight": "b.safetensors", "lm_head.weight": "b.safetensors"}
+    (sharded / "model.safetensors.index.json").write_text(json.dumps({"weight_map": wmap}))
+    got = loading.load_model_layers(["model.norm.weight", "embed_tokens.weight"], sharded)
+    assert torch.equal(got["model.norm.weight"], tensors["model.norm.weight"]) and torch.equal(got["embed_tokens.weight"], tensors["model.embed_tokens.weight"])
+    with pytest.raises(ValueError, match="None of the requested"):
+        loading.load_model_layers(["nope.weight"], sharded)
+    with pytest.raises(FileNotFoundError):
+        loading.list_checkpoint_keys(tmp_path)
