@@ -136,7 +136,7 @@ class TrainerArgs(_Group):
     log_freq: int = Field(default=1, description="Log metrics every N steps.")
     save_path: str = Field(default="./output/checkpoints")
     fsdp_shard: bool = Field(default=False, description="Shard optimizer state and master weights across ranks.")
-    max_steps: int | None = Field(default=None)
+    max_steps: int | None = Field(default=None, gt=0, description="Stop after this many optimizer steps (a positive integer); default: run all epochs.")
 
 
 class LoggingArgs(_Group):
