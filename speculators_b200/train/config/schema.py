@@ -86,6 +86,18 @@ class DataArgs(_Group):
     prefetch_factor: int = Field(default=4, description="Batches prefetched per worker.")
     max_anchors: int = Field(default=512, description="Anchors per batch (DFlash / DSpark / P-EAGLE).")
 
+    @field_validator("hidden_states_dtype")
+    @classmethod
+    def _names_a_supported_dtype(cls, v: str) -> str:
+        import torch  # only needed to check the name; keeps the schema importable without it otherwise
+
+        resolved = getattr(torch, v, None)
+        if not isinstance(resolved, torch.dtype):  # torch.nn, torch.cuda, ... exist but are not dtypes
+            raise ValueError("hidden_states_dtype must name a torch dtype, e.g. `bfloat16`.")
+        if resolved is torch.float16:
+            raise ValueError("hidden_states_dtype float16 is not supported (it needs gradient scaling); use bfloat16.")
+        return v
+
 
 class GenerationArgs(_Group):
     vllm_endpoint: str = Field(default="http://localhost:8000/v1", description="OpenAI-compatible endpoint of the verifier server.")
@@ -137,6 +149,15 @@ class TrainerArgs(_Group):
     save_path: str = Field(default="./output/checkpoints")
     fsdp_shard: bool = Field(default=False, description="Shard optimizer state and master weights across ranks.")
     max_steps: int | None = Field(default=None, gt=0, description="Stop after this many optimizer steps (a positive integer); default: run all epochs.")
+
+    @field_validator("checkpoint_freq")
+    @classmethod
+    def _whole_epochs_or_a_fraction(cls, v: float) -> float:
+        if v <= 0:
+            raise ValueError("--checkpoint-freq must be > 0")
+        if v > 1 and not float(v).is_integer():
+            raise ValueError(f"--checkpoint-freq={v} is not an integer. Values > 1 are epoch counts and must be whole numbers.")
+        return v
 
 
 class LoggingArgs(_Group):
