@@ -90,6 +90,7 @@ class SpeculatorModelConfig(PydanticClassRegistryMixin):
 
     model_config = ConfigDict(arbitrary_types_allowed=True, extra="allow", validate_assignment=False)
     schema_discriminator: ClassVar[str] = "speculators_model_type"
+    dispatch_on_construct: ClassVar[bool] = False  # only from_dict / from_pretrained / model_validate pick the algorithm's class
     model_type: ClassVar[str] = "speculator_model"
 
     speculators_model_type: str = ""
@@ -120,13 +121,17 @@ class SpeculatorModelConfig(PydanticClassRegistryMixin):
     def to_json_string(self) -> str:
         return json.dumps(self.to_dict(), indent=2, sort_keys=True) + "\n"
 
+    def to_json_file(self, json_file_path: str | os.PathLike, **_: Any) -> None:
+        with open(json_file_path, "w", encoding="utf-8") as fh:
+            fh.write(self.to_json_string())
+
     @classmethod
     def from_dict(cls, config_dict: dict[str, Any], **kwargs: Any) -> "SpeculatorModelConfig":
         merged = {**config_dict, **kwargs}
         if "speculators_model_type" not in merged:
             raise ValueError(
-                "config dict has no 'speculators_model_type'; it is not a speculators "
-                "checkpoint (external checkpoints go through speculators_b200.convert)"
+                "The config dictionary must contain the 'speculators_model_type' field; without it "
+                "this is not a speculators checkpoint (external checkpoints go through speculators_b200.convert)"
             )
         merged.pop("model_type", None)
         merged.pop("transformers_version", None)
@@ -139,8 +144,8 @@ class SpeculatorModelConfig(PydanticClassRegistryMixin):
         data = read_config_json(pretrained_model_name_or_path)
         if "speculators_model_type" not in data:
             raise NotImplementedError(
-                "config.json has no 'speculators_model_type': loading a non-speculators "
-                "config directly is not supported; convert the checkpoint first"
+                "config.json has no 'speculators_model_type'. Loading a non-speculator model config "
+                "is not supported yet; convert the checkpoint first"
             )
         kwargs = {k: v for k, v in kwargs.items() if k in cls.model_fields}
         return cls.from_dict(data, **kwargs)

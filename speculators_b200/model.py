@@ -121,6 +121,10 @@ class DraftVocabMixin(nn.Module):
 class SpeculatorModel(ClassRegistryMixin, nn.Module):
     config_class: ClassVar[type[SpeculatorModelConfig]] = SpeculatorModelConfig
     main_input_name: ClassVar[str] = "input_ids"
+    base_model_prefix: ClassVar[str] = "model"
+    # algorithms register themselves when this package's ``models`` sub-packages are imported
+    auto_package: ClassVar[str] = "speculators_b200.models"
+    registry_auto_discovery: ClassVar[bool] = True
     _keys_to_ignore_on_load_missing: ClassVar[list[str]] = []
     _keys_to_ignore_on_save: ClassVar[list[str]] = []
 
@@ -132,6 +136,14 @@ class SpeculatorModel(ClassRegistryMixin, nn.Module):
         nn.Module.__init__(self)
         config.tie_word_embeddings = False
         self.config = config
+
+    def post_init(self) -> None:
+        """End-of-constructor hook (the convention of ``transformers`` models, which
+        subclasses written against the reference follow): applies ``_init_weights`` to every
+        sub-module when the subclass defines it."""
+        init = getattr(self, "_init_weights", None)
+        if callable(init):
+            self.apply(init)
 
     # ------------------------------------------------------------------ abstract API
     def forward(self, *args, **kwargs):

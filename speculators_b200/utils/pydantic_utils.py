@@ -30,6 +30,9 @@ class ReloadableBaseModel(BaseModel):
 
 class PydanticClassRegistryMixin(ReloadableBaseModel, ClassRegistryMixin):
     schema_discriminator: ClassVar[str] = "model_type"
+    # Base(tag=...) builds the registered subclass; families whose base must stay constructible
+    # as itself switch this off
+    dispatch_on_construct: ClassVar[bool] = True
 
     @classmethod
     def __pydantic_schema_base_type__(cls) -> type[Any]:
@@ -41,10 +44,21 @@ class PydanticClassRegistryMixin(ReloadableBaseModel, ClassRegistryMixin):
                 root = klass
         return root
 
+    def __new__(cls, *args: Any, **kwargs: Any):
+        """Constructing the family's base class with the tag of a registered subclass builds
+        that subclass: ``Base(kind="x", ...)`` is ``X(kind="x", ...)``."""
+        target = cls
+        if kwargs and cls.dispatch_on_construct and cls is cls.__pydantic_schema_base_type__():
+            tag = kwargs.get(cls.schema_discriminator)
+            found = (cls.registry or {}).get(tag) if isinstance(tag, str) else None
+            if found is not None and issubclass(found, cls):
+                target = found
+        return super().__new__(target)
+
     @classmethod
     def register_decorator(cls, clazz: type[Any], name: str | None = None) -> type[Any]:
         if not (isinstance(clazz, type) and issubclass(clazz, BaseModel)):
-            raise TypeError(f"{clazz!r} is not a pydantic BaseModel subclass")
+            raise TypeError(f"{clazz!r} is not a subclass of Pydantic BaseModel")
         return super().register_decorator(clazz, name=name)
 
     @model_validator(mode="wrap")

@@ -36,7 +36,7 @@ class ClassRegistryMixin:
     @classmethod
     def register(cls, name: str | None = None) -> Callable[[type[Any]], type[Any]]:
         if name is not None and not isinstance(name, str):
-            raise ValueError(f"registry names must be str or None, got {name!r}")
+            raise ValueError(f"name must be a string or None, got {name!r}")
 
         def _apply(klass: type[Any]) -> type[Any]:
             return cls.register_decorator(klass, name=name)
@@ -47,17 +47,17 @@ class ClassRegistryMixin:
     def register_decorator(cls, clazz: type[Any], name: str | None = None) -> type[Any]:
         if not isinstance(clazz, type):
             raise TypeError(
-                f"register_decorator decorates classes; got {clazz!r}. "
+                f"register_decorator must be used as a class decorator; got {clazz!r}. "
                 "Use @Base.register('name') or @Base.register_decorator."
             )
         if name is not None and not isinstance(name, str):
-            raise ValueError(f"registry names must be str, got {name!r}")
+            raise ValueError(f"name must be a string or None, got {name!r}")
         key = name or clazz.__name__
         table = cls._table(create=True)
         assert table is not None
         if key in table:
             raise ValueError(
-                f"{cls.__name__} registry already holds {key!r} -> {table[key]!r}; "
+                f"{key!r} is already registered in the {cls.__name__} registry as {table[key]!r}; "
                 f"refusing to replace it with {clazz!r}"
             )
         table[key] = clazz
@@ -68,8 +68,8 @@ class ClassRegistryMixin:
         table = cls._table(create=False)
         if table is None:
             raise ValueError(
-                f"{cls.__name__}.registered_classes() called before any class was "
-                "registered"
+                f"{cls.__name__}.registered_classes() must be called after registering classes "
+                "(nothing is registered yet)"
             )
         return tuple(table.values())
 
