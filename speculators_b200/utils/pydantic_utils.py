@@ -13,6 +13,7 @@ holds (pydantic alone would serialize by the declared type and drop them).
 
 from __future__ import annotations
 
+import threading
 from typing import Any, ClassVar
 
 from pydantic import BaseModel, model_serializer, model_validator
@@ -55,6 +56,15 @@ class PydanticClassRegistryMixin(ReloadableBaseModel, ClassRegistryMixin):
                 target = found
         return super().__new__(target)
 
+    def __init__(self, **data: Any) -> None:
+        # tell the validator below that this object already has its final class (``__new__`` chose
+        # it): it must fill *this* instance instead of building another one
+        _CONSTRUCTION.stack.append(True)
+        try:
+            super().__init__(**data)
+        finally:
+            _CONSTRUCTION.stack.pop()
+
     @classmethod
     def register_decorator(cls, clazz: type[Any], name: str | None = None) -> type[Any]:
         if not (isinstance(clazz, type) and issubclass(clazz, BaseModel)):
@@ -65,6 +75,9 @@ class PydanticClassRegistryMixin(ReloadableBaseModel, ClassRegistryMixin):
     @classmethod
     def _dispatch_on_discriminator(cls, value: Any, handler):  # noqa: ANN001
         if isinstance(value, cls) or not isinstance(value, dict):
+            return handler(value)
+        if _CONSTRUCTION.stack and _CONSTRUCTION.stack[-1]:
+            _CONSTRUCTION.stack[-1] = False  # only the object under construction; its nested fields dispatch normally
             return handler(value)
         root = cls.__pydantic_schema_base_type__()
         if cls is not root:
@@ -102,3 +115,9 @@ class PydanticClassRegistryMixin(ReloadableBaseModel, ClassRegistryMixin):
 
 
 _RESERIALIZING: set[int] = set()
+class _ConstructionStack(threading.local):
+    def __init__(self) -> None:
+        self.stack: list[bool] = []
+
+
+_CONSTRUCTION = _ConstructionStack()
