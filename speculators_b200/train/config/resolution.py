@@ -112,27 +112,38 @@ def _annotation_spec(annotation: Any) -> tuple[Any, bool, list[Any] | None]:
     return annotation, False, None
 
 
-def add_config_cli_arguments(parser: argparse.ArgumentParser) -> None:
-    for dest, field in _all_fields().items():
-        base, is_list, choices = _annotation_spec(field.annotation)
-        extra = field.json_schema_extra if isinstance(field.json_schema_extra, dict) else {}
-        registry_key = extra.get("cli_choices")
-        if registry_key:
-            choices = sorted(_CHOICE_REGISTRIES[registry_key])
-        kwargs: dict[str, Any] = {"dest": dest, "default": argparse.SUPPRESS, "help": field.description}
-        if base is bool:
-            default = field.default
-            if default is True or default is None or extra.get("cli_bool") == "optional":
-                kwargs["action"] = argparse.BooleanOptionalAction
-            else:
-                kwargs["action"] = "store_true"
+def _add_field_argument(target, dest: str, field) -> None:  # noqa: ANN001
+    base, is_list, choices = _annotation_spec(field.annotation)
+    extra = field.json_schema_extra if isinstance(field.json_schema_extra, dict) else {}
+    registry_key = extra.get("cli_choices")
+    if registry_key:
+        choices = sorted(_CHOICE_REGISTRIES[registry_key])
+    kwargs: dict[str, Any] = {"dest": dest, "default": argparse.SUPPRESS, "help": field.description}
+    if base is bool:
+        default = field.default
+        if default is True or default is None or extra.get("cli_bool") == "optional":
+            kwargs["action"] = argparse.BooleanOptionalAction
         else:
-            kwargs["type"] = base if base in (int, float, str) else str
-            if is_list:
-                kwargs["nargs"] = "+"
-            if choices:
-                kwargs["choices"] = choices
-        parser.add_argument(_flag(dest), **kwargs)
+            kwargs["action"] = "store_true"
+    else:
+        kwargs["type"] = base if base in (int, float, str) else str
+        if is_list:
+            kwargs["nargs"] = "+"
+        if choices:
+            kwargs["choices"] = choices
+    target.add_argument(_flag(dest), **kwargs)
+
+
+def add_config_cli_arguments(parser: argparse.ArgumentParser) -> None:
+    """One flag per schema field; ``--help`` lists them grouped by concern (``general`` for
+    the root fields, then one argparse group per config group)."""
+    general = parser.add_argument_group("general")
+    for name in ROOT_FIELDS:
+        _add_field_argument(general, name, TrainConfig.model_fields[name])
+    for gname, gmodel in GROUPS.items():
+        group = parser.add_argument_group(gname)
+        for dest, field in gmodel.model_fields.items():
+            _add_field_argument(group, dest, field)
     for actions in _BACKEND_ACTIONS.values():
         for action in actions:
             kwargs = {"dest": action.dest, "default": argparse.SUPPRESS, "help": action.help}

@@ -228,3 +228,10 @@ def test_flatten_resolves_algorithm_dependent_defaults():
     assert (x["num_layers"], x["loss_fn"]) == (2, "kl_div")
     with pytest.raises(ValidationError, match="requires --loss-fn=ce"):  # the dflash default weighting needs cross-entropy
         TrainConfig.from_flat({"verifier_name_or_path": "m", "speculator_type": "dflash", "loss_fn": "kl_div"})
+
+
+def test_help_lists_flags_grouped_by_concern():
+    from speculators_b200.train.config.resolution import build_parser
+
+    titles = {group.title for group in build_parser()._action_groups}
+    assert {"general", "verifier", "draft", "data", "optimizer", "mtp"} <= titles
