@@ -117,6 +117,8 @@ class TransformerLayerConfig:
             if isinstance(data.get("text_config"), dict):
                 data = data["text_config"]
             return cls(**data)
+        if hasattr(value, "__dict__"):  # any plain attribute holder (argparse / SimpleNamespace stand-ins)
+            return cls(**{k: v for k, v in vars(value).items() if not k.startswith("_")})
         raise TypeError(f"cannot build a TransformerLayerConfig from {type(value)!r}")
 
     # ---- attribute protocol ---------------------------------------------------

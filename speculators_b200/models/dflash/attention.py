@@ -15,7 +15,7 @@ import torch
 from speculators_b200.models.eagle3.attention import causal_document_interval
 from speculators_b200.ops import AttnSpec
 
-__all__ = ["anchor_block_attn_spec", "dense_anchor_block_mask"]
+__all__ = ["anchor_block_attn_spec", "create_anchor_block_mask_mod", "dense_anchor_block_mask"]
 
 
 def anchor_block_attn_spec(document_ids, anchor_positions, block_size: int, sliding_window: int | None = None,
@@ -61,3 +61,37 @@ def dense_anchor_block_mask(document_ids, total_seq_len: int, anchor_positions, 
     if sliding_window is not None and not sliding_window_non_causal:
         same_block = same_block & (kv <= q + total_seq_len)
     return prefix | same_block
+
+
+def create_anchor_block_mask_mod(document_ids: torch.Tensor, total_seq_len: int, anchor_positions: torch.Tensor, block_size: int,
+                                 sliding_window: int | None = None, sliding_window_non_causal: bool = False):
+    """Element-level form of the anchored-block mask in the ``mask_mod(b, h, q_idx, kv_idx)``
+    convention of ``torch.nn.attention.flex_attention``; returns ``(mask_mod, q_len, kv_len)``
+    with ``q_len = n_anchors * block_size`` and ``kv_len = total_seq_len + q_len`` (the packed
+    sequence followed by the synthetic blocks).  Same rule as ``dense_anchor_block_mask`` /
+    ``anchor_block_attn_spec``: block ``j`` sees the keys of its anchor's document before the
+    anchor (inside the window, if any) and its own block - all of it, or only earlier slots
+    when a window is set and ``sliding_window_non_causal`` is off
+    (src/speculators/models/dflash/attention.py:7-107)."""
+    if anchor_positions.ndim != 1:
+        raise ValueError(f"anchor_positions must be 1D, got shape {tuple(anchor_positions.shape)}")
+    anchors = anchor_positions.to(device=document_ids.device, dtype=torch.long)
+    q_len = anchors.numel() * block_size
+    anchor_of_query = anchors.repeat_interleave(block_size)
+    causal_in_block = sliding_window is not None and not sliding_window_non_causal
+
+    def mask_mod(_b, _h, q_idx, kv_idx):
+        anchor = anchor_of_query[q_idx]
+        position = kv_idx % total_seq_len
+        in_sequence = kv_idx < total_seq_len
+        same_doc = (document_ids[anchor] == document_ids[position]) & (document_ids[anchor] != -1)
+        prefix = in_sequence & same_doc & (position < anchor)
+        if sliding_window is not None:
+            prefix = prefix & (position >= anchor - sliding_window)
+        own_block = (~in_sequence if isinstance(in_sequence, torch.Tensor) else not in_sequence) & (
+            q_idx // block_size == (kv_idx - total_seq_len) // block_size)
+        if causal_in_block:
+            own_block = own_block & (kv_idx <= q_idx + total_seq_len)
+        return prefix | own_block
+
+    return mask_mod, q_len, total_seq_len + q_len

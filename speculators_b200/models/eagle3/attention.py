@@ -20,7 +20,7 @@ import torch
 
 from speculators_b200.ops import AttnSpec
 
-__all__ = ["causal_document_interval", "dense_ttt_mask", "ttt_attn_spec"]
+__all__ = ["causal_document_interval", "create_combined_mask_mod", "dense_ttt_mask", "extend_dense_mask_for_draft_tokens", "ttt_attn_spec"]
 
 
 def causal_document_interval(document_ids: torch.Tensor, sliding_window: int | None = None):
@@ -61,3 +61,39 @@ def dense_ttt_mask(document_ids: torch.Tensor, ttt_step: int, sliding_window: in
         causal = causal & (kv > q - sliding_window)
     same_doc = (doc[q] != -1) & (doc[q] == doc[kv % T])
     return (causal & same_doc) | (kv % T == q)
+
+
+def create_combined_mask_mod(document_ids: torch.Tensor, total_seq_len: int, sliding_window: int | None = None):
+    """Element-level form of the training-time-test mask, in the ``mask_mod(b, h, q_idx,
+    kv_idx)`` convention of ``torch.nn.attention.flex_attention`` (usable with its
+    ``create_mask`` / ``create_block_mask``, or as an oracle for ``ttt_attn_spec``).  Keys
+    ``kv_idx >= total_seq_len`` are the appended draft passes: pass ``p`` holds position
+    ``kv_idx - p * total_seq_len``.  A query sees the causal (optionally windowed) keys of
+    its own document - padding rows (document -1) see none - plus, in every pass, the key
+    at its own position (src/speculators/models/eagle3/attention.py:11-34)."""
+
+    def mask_mod(_b, _h, q_idx, kv_idx):
+        position = kv_idx % total_seq_len
+        in_document = (document_ids[q_idx] != -1) & (document_ids[q_idx] == document_ids[position])
+        causal = q_idx >= kv_idx
+        if sliding_window is not None:
+            causal = causal & (kv_idx > q_idx - sliding_window)
+        return (causal & in_document) | (position == q_idx)
+
+    return mask_mod
+
+
+def extend_dense_mask_for_draft_tokens(mask: torch.Tensor, total_seq_len: int) -> torch.Tensor:
+    """Append the key columns of one more training-time-test pass to a dense mask
+    ``[..., total_seq_len, kv_len]``: query ``q`` sees exactly the new key ``q``.  Boolean
+    masks get an identity block; additive float masks get 0 on the diagonal and ``-inf``
+    elsewhere, so that the new block means the same in both conventions
+    (src/speculators/models/eagle3/attention.py:115-132 appends the 0/1 identity in the
+    mask's dtype, which for an additive mask admits every new key)."""
+    eye = torch.eye(total_seq_len, dtype=torch.bool, device=mask.device)
+    if mask.dtype == torch.bool:
+        block = eye
+    else:
+        block = torch.zeros(total_seq_len, total_seq_len, dtype=mask.dtype, device=mask.device).masked_fill(~eye, float("-inf"))
+    block = block.reshape((1,) * (mask.dim() - 2) + block.shape).expand(*mask.shape[:-2], total_seq_len, total_seq_len)
+    return torch.cat([mask, block], dim=-1)

@@ -16,7 +16,7 @@ from torch import nn
 from speculators_b200.layer_config import TransformerLayerConfig
 from speculators_b200.models.layers import DecoderLayer, Linear, RMSNorm
 
-__all__ = ["MTPLayer", "build_mtp_layer", "resolve_model_type"]
+__all__ = ["MTPLayer", "MTPLayerMixin", "build_mtp_layer", "mtp_model_classes", "resolve_model_type"]
 
 _DENSE_TYPES = ("qwen3", "llama", "qwen2")
 _MOE_TYPES = ("qwen3_next", "qwen3_5_moe_text", "qwen3_5_text")
@@ -50,6 +50,57 @@ class MTPLayer(_MTPMixin, DecoderLayer):
     def forward(self, hidden_states, token_embeddings, positions, rotary, spec):
         x = self.combine(hidden_states, token_embeddings)
         return self.final_layernorm(DecoderLayer.forward(self, x, positions, rotary, spec))
+
+
+MTPLayerMixin = _MTPMixin  # public name (src/speculators/models/mtp/model_definitions.py:73)
+
+
+class _LazyMTPClasses(dict):
+    """``model_type -> ModelComponents`` with the MTP layer as ``first_layer_class``
+    (src/speculators/models/mtp/model_definitions.py:152-190).  Filled on first use: the
+    MoE layer module imports this one."""
+
+    def _fill(self) -> None:
+        if dict.__len__(self):
+            return
+        from speculators_b200.models import base_components
+        from speculators_b200.models.moe import MoEMTPLayer
+
+        for kind in _DENSE_TYPES:
+            dict.__setitem__(self, kind, base_components.override_components(kind, first_layer_class=MTPLayer))
+        for kind in _MOE_TYPES:
+            dict.__setitem__(self, kind, base_components.override_components(kind, first_layer_class=MoEMTPLayer))
+
+    def __getitem__(self, key):
+        self._fill()
+        return dict.__getitem__(self, key)
+
+    def __contains__(self, key) -> bool:
+        self._fill()
+        return dict.__contains__(self, key)
+
+    def __iter__(self):
+        self._fill()
+        return dict.__iter__(self)
+
+    def __len__(self) -> int:
+        self._fill()
+        return dict.__len__(self)
+
+    def keys(self):
+        self._fill()
+        return dict.keys(self)
+
+    def items(self):
+        self._fill()
+        return dict.items(self)
+
+    def values(self):
+        self._fill()
+        return dict.values(self)
+
+
+mtp_model_classes = _LazyMTPClasses()
 
 
 def build_mtp_layer(config: TransformerLayerConfig, layer_idx: int = 0) -> nn.Module:

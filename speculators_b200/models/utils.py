@@ -8,6 +8,7 @@ import warnings
 from speculators_b200.layer_config import TransformerLayerConfig, read_config_json, unwrap_text_config
 
 __all__ = [
+    "flatten_rope_parameters",
     "conditional_torch_compile",
     "get_verifier_config",
     "resolve_draft_intermediate_size",
@@ -43,6 +44,21 @@ def resolve_target_layer_ids(target_layer_ids: list[int] | None, verifier_name_o
         stacklevel=3,
     )
     return ids
+
+
+def flatten_rope_parameters(config):
+    """Configs that keep one rotary setting per layer type (``rope_parameters`` keyed by
+    ``sliding_attention`` / ``full_attention``) become a deep copy whose ``rope_parameters``
+    is the ``sliding_attention`` entry, which is what a rotary table is built from; any other
+    config is returned as it is (src/speculators/models/utils.py:60-74)."""
+    import copy
+
+    rope = getattr(config, "rope_parameters", None)
+    if not rope or "sliding_attention" not in rope:
+        return config
+    out = copy.deepcopy(config)
+    out.rope_parameters = rope["sliding_attention"]
+    return out
 
 
 def resolve_draft_intermediate_size(verifier_config) -> int:
