@@ -112,3 +112,30 @@ def test_optimizer_and_attention_compat_modules(tmp_path):
         return x + 1
 
     assert f(1) == 2 and conditional_torch_compile(dynamic=True)(f)(2) == 3
+
+
+def test_eagle_converter_helpers_and_legacy_model_name(tiny_verifier_dir, tiny_vocab_maps, tmp_path):
+    import torch
+
+    from speculators_b200.convert.eagle.eagle3_legacy_model import Eagle3Speculator
+    from speculators_b200.convert.eagle.utils import (
+        build_llama_config_dtype_kwarg, build_llama_config_rope_kwargs, detect_fusion_bias_and_layernorms, find_vocab_size,
+    )
+    from tests.conftest import make_tiny_eagle3
+
+    assert detect_fusion_bias_and_layernorms({"fc.bias": torch.zeros(1), "post_embedding_layernorm.weight": torch.zeros(1)}) == (True, True)
+    assert detect_fusion_bias_and_layernorms({"fc.weight": torch.zeros(1)}) == (False, False)
+    assert find_vocab_size({"a": {"b": {"vocab_size": 7}}}) == 7 and find_vocab_size({"a": 1}) is None
+    assert build_llama_config_dtype_kwarg(None) == {} and build_llama_config_dtype_kwarg("bfloat16") == {"torch_dtype": "bfloat16"}
+    rope = build_llama_config_rope_kwargs(5e5, {"type": "llama3", "factor": 8.0})
+    assert rope["rope_parameters"] == {"rope_theta": 5e5, "rope_type": "llama3", "factor": 8.0} and rope["rope_scaling"]["factor"] == 8.0
+    assert build_llama_config_rope_kwargs()["rope_parameters"] == {"rope_theta": 10000.0, "rope_type": "default"}
+
+    model = make_tiny_eagle3(tiny_verifier_dir, tiny_vocab_maps)
+    model.save_pretrained(tmp_path / "ckpt")
+    legacy = Eagle3Speculator.from_pretrained(str(tmp_path / "ckpt"), verifier=tiny_verifier_dir, verifier_attachment_mode="detached")
+    assert torch.equal(legacy.fc.weight, model.fc.weight)
+    built = Eagle3Speculator(model.config, verifier=None, verifier_attachment_mode="detached", reduce_vocab_size=False, has_drafter_embedding=False)
+    assert built.d2t is None and not built.embed_tokens.weight.requires_grad
+    with pytest.raises(ValueError, match="detached"):
+        Eagle3Speculator(model.config, verifier_attachment_mode="full")
