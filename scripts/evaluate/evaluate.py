@@ -77,7 +77,7 @@ def save_eval_provenance(output_dir: Path) -> None:
         from speculators_b200.provenance import atomic_write, git_sha, package_versions
 
         head = [f"# Timestamp: {datetime.now(timezone.utc).isoformat()}", f"# Git SHA: {git_sha()}"]
-        head += [f"# {k}: {v}" for k, v in package_versions().items()]
+        head += package_versions()
         atomic_write(output_dir / "eval_command.txt", "\n".join(head) + f"\n{shlex.join(sys.argv)}\n")
     except Exception:  # noqa: BLE001
         logger.warning("Failed to save eval_command.txt", exc_info=True)

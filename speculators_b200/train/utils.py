@@ -39,10 +39,10 @@ def save_train_command(save_dir: str | os.PathLike, argv: list[str] | None = Non
     os.makedirs(save_dir, exist_ok=True)
     lines = [
         f"# Timestamp: {datetime.datetime.now(datetime.timezone.utc).isoformat()}",
-        f"# Git SHA: {provenance.git_sha() or 'unknown'}",
+        f"# Git SHA: {provenance.git_sha()}",
         f"# World size: {os.environ.get('WORLD_SIZE', '1')}",
     ]
-    lines += [f"# {pkg}: {ver}" for pkg, ver in provenance.package_versions().items()]
+    lines += provenance.package_versions()
     lines.append(shlex.join(argv))
     path = os.path.join(save_dir, "train_command.txt")
     provenance.atomic_write(path, "\n".join(lines) + "\n")

@@ -31,7 +31,7 @@ def test_train_command_file_has_header_and_quoted_command(tmp_path):
 def test_train_command_defaults_and_overwrite(tmp_path):
     (tmp_path / "train_command.txt").write_text("old content")
     env = {k: v for k, v in os.environ.items() if k != "WORLD_SIZE"}
-    with patch.dict(os.environ, env, clear=True), patch("speculators_b200.provenance.git_sha", return_value=None):
+    with patch.dict(os.environ, env, clear=True), patch("speculators_b200.provenance.find_repo_root", return_value=None):
         save_train_command(str(tmp_path), argv=["train.py", "--epochs", "3"])
     text = (tmp_path / "train_command.txt").read_text()
     assert "old content" not in text and "# World size: 1" in text and "# Git SHA: unknown" in text

@@ -118,3 +118,30 @@ def test_load_layers_from_single_file_and_sharded_checkpoints(tmp_path):
         loading.load_model_layers(["nope.weight"], sharded)
     with pytest.raises(FileNotFoundError):
         loading.list_checkpoint_keys(tmp_path)
+
+
+def test_provenance_helpers(tmp_path):
+    import subprocess
+
+    from speculators_b200 import provenance
+
+    lines = provenance.package_versions()
+    assert all(line.startswith("# ") and ": " in line for line in lines)
+    assert provenance.package_versions(("definitely-not-a-package",)) == ["# definitely-not-a-package: not installed"]
+    assert provenance.git_sha(None) == "unknown" and provenance.git_diff(None) == ""
+    assert provenance.run_git(["git", "rev-parse", "HEAD"], tmp_path) == ""  # not a repository
+    assert provenance.find_package_repo("no_such_package_anywhere") is None
+    repo = tmp_path / "repo"
+    repo.mkdir()
+    env = {"GIT_AUTHOR_NAME": "t", "GIT_AUTHOR_EMAIL": "t@t", "GIT_COMMITTER_NAME": "t", "GIT_COMMITTER_EMAIL": "t@t", "PATH": __import__("os").environ["PATH"]}
+    subprocess.run(["git", "init", "-q"], cwd=repo, check=True, env=env)
+    (repo / "a.txt").write_text("one\n")
+    subprocess.run(["git", "add", "a.txt"], cwd=repo, check=True, env=env)
+    subprocess.run(["git", "commit", "-q", "-m", "first"], cwd=repo, check=True, env=env)
+    sha = provenance.git_sha(repo)
+    assert len(sha) == 40 and provenance.git_diff(repo) == ""
+    (repo / "a.txt").write_text("two\n")
+    assert "+two" in provenance.git_diff(repo)
+    assert provenance.find_repo_root(repo / "a.txt") == repo
+    provenance.atomic_write(repo / "sub" / "f.txt", "hello")
+    assert (repo / "sub" / "f.txt").read_text() == "hello" and [p.name for p in (repo / "sub").iterdir()] == ["f.txt"]
