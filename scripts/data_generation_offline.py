@@ -97,6 +97,11 @@ async def generate(args: argparse.Namespace, dataset) -> int:
     return 0
 
 
+def parse_args(argv: list[str] | None = None) -> argparse.Namespace:
+    """Parsed command line (``sys.argv`` when ``argv`` is None)."""
+    return build_parser().parse_args(argv)
+
+
 def main(argv: list[str] | None = None) -> int:
     args = build_parser().parse_args(argv)
     if not 0 <= args.rank < args.world_size:

@@ -81,6 +81,11 @@ def _num_hidden_layers(model: str, trust_remote_code: bool) -> int:
     return getattr(cfg, "text_config", cfg).num_hidden_layers
 
 
+def parse_args(argv: list[str] | None = None) -> argparse.Namespace:
+    """Parsed command line (``sys.argv`` when ``argv`` is None)."""
+    return build_parser().parse_args(argv)
+
+
 def main(argv: list[str] | None = None) -> int:
     args, vllm_args = build_parser().parse_known_args(argv)
     if "--" in vllm_args:
