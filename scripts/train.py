@@ -15,7 +15,9 @@ import sys
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 from speculators_b200.train.config import TrainConfig  # noqa: E402
-from speculators_b200.train.entrypoint import main  # noqa: E402
+from speculators_b200.train.entrypoint import (  # noqa: E402,F401 - the building blocks stay importable from the script
+    _build_from_config_only, build_draft_model, create_transformer_layer_config, load_draft_transformer_layer_config, main,
+)
 
 if __name__ == "__main__":
     main(TrainConfig.resolve())

@@ -13,18 +13,29 @@ from safetensors.torch import load_file
 
 log = logging.getLogger("speculators")
 
-__all__ = ["ensure_checkpoint_is_local", "find_vocab_size", "load_checkpoint_config", "load_checkpoint_weights"]
+__all__ = ["download_checkpoint_from_hub", "ensure_checkpoint_is_local", "find_vocab_size", "load_checkpoint_config", "load_checkpoint_weights"]
 
 
-def ensure_checkpoint_is_local(path: str | Path, cache_dir: str | Path | None = None) -> Path:
-    p = Path(path)
-    if p.exists():
-        return p
+def download_checkpoint_from_hub(model_id: str, cache_dir: str | None = None) -> Path:
+    """Fetch the config / weight files of a hub checkpoint; ``FileNotFoundError`` when that
+    is not possible (no ``huggingface_hub``, no network, unknown id)."""
     try:
         from huggingface_hub import snapshot_download
     except ImportError as err:
-        raise FileNotFoundError(f"Checkpoint '{path}' is not a local path and huggingface_hub is unavailable") from err
-    return Path(snapshot_download(repo_id=str(path), cache_dir=cache_dir, allow_patterns=["*.json", "*.safetensors", "*.bin"]))
+        raise FileNotFoundError(f"Checkpoint '{model_id}' is not a local path and huggingface_hub is unavailable") from err
+    try:
+        local = snapshot_download(repo_id=model_id, cache_dir=cache_dir, allow_patterns=["*.json", "*.safetensors", "*.bin", "*.index.json"])
+    except Exception as err:  # noqa: BLE001 - the hub raises several unrelated exception types
+        raise FileNotFoundError(f"Checkpoint not found: {model_id}") from err
+    return Path(local)
+
+
+def ensure_checkpoint_is_local(path: str | Path, cache_dir: str | Path | None = None) -> Path:
+    """An existing local path as it is; anything else is taken for a hub id and downloaded."""
+    p = Path(path)
+    if p.exists():
+        return p
+    return download_checkpoint_from_hub(str(path), cache_dir=str(cache_dir) if cache_dir else None)
 
 
 def load_checkpoint_config(path: str | Path) -> dict:

@@ -108,23 +108,28 @@ def _leave_final_turn_open(model: str) -> bool:
     return "mistral" in model.rsplit("/", 1)[-1].lower()
 
 
-def _request(model: str, item: ClientItem, timeout: float | None) -> tuple[str, dict]:
+def _request(model: str, item: ClientItem, timeout: float | None, kv_transfer_params: dict | None = None) -> tuple[str, dict]:
+    extra: dict[str, Any] = {"return_token_ids": True}
+    if kv_transfer_params:
+        extra["kv_transfer_params"] = dict(kv_transfer_params)
     if item.get("messages") is None:
-        return "completions", dict(model=model, prompt=item["input_ids"], max_tokens=1, extra_body={"return_token_ids": True}, timeout=timeout)
-    extra = {"add_generation_prompt": False, "continue_final_message": _leave_final_turn_open(model), "return_token_ids": True}
+        return "completions", dict(model=model, prompt=item["input_ids"], max_tokens=1, extra_body=extra, timeout=timeout)
+    extra.update({"add_generation_prompt": False, "continue_final_message": _leave_final_turn_open(model)})
     return "chat", dict(model=model, messages=item["messages"], max_tokens=1, extra_body=extra, timeout=timeout)
 
 
 @with_retries
-def generate_hidden_states(client, model: str, client_item: ClientItem, *, timeout: float | None = DEFAULT_REQUEST_TIMEOUT) -> str:
-    kind, kwargs = _request(model, client_item, timeout)
+def generate_hidden_states(client, model: str, client_item: ClientItem, *, timeout: float | None = DEFAULT_REQUEST_TIMEOUT,
+                           kv_transfer_params: dict | None = None) -> str:
+    kind, kwargs = _request(model, client_item, timeout, kv_transfer_params)
     res = client.completions.create(**kwargs) if kind == "completions" else client.chat.completions.create(**kwargs)
     return extract_output(res, client_item["input_ids"])
 
 
 @with_retries
-async def generate_hidden_states_async(client, model: str, client_item: ClientItem, *, timeout: float | None = DEFAULT_REQUEST_TIMEOUT) -> str:
-    kind, kwargs = _request(model, client_item, timeout)
+async def generate_hidden_states_async(client, model: str, client_item: ClientItem, *, timeout: float | None = DEFAULT_REQUEST_TIMEOUT,
+                                       kv_transfer_params: dict | None = None) -> str:
+    kind, kwargs = _request(model, client_item, timeout, kv_transfer_params)
     coro = client.completions.create(**kwargs) if kind == "completions" else client.chat.completions.create(**kwargs)
     res = await (asyncio.wait_for(coro, timeout=timeout) if timeout is not None else coro)
     return extract_output(res, client_item["input_ids"])

@@ -84,6 +84,6 @@ class MooncakeBackend(HiddenStatesBackend):
         return {
             "kv_connector": "MooncakeHiddenStatesConnector",
             "kv_role": "kv_producer",
-            "kv_connector_module_path": "speculators_b200.hs_connectors.mooncake_hidden_states_connector",
+            "kv_connector_module_path": "speculators_b200.hs_connectors.vllm_connector",
             "kv_connector_extra_config": {"mooncake": dataclasses.asdict(cfg)},
         }

@@ -24,6 +24,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import threading
 import time
 from pathlib import Path
 from typing import Any
@@ -195,6 +196,12 @@ class NvlinkTransfer(HiddenStatesTransfer):
         self.setup()
         return self.ring.pop(int(handle), self.timeout_s)
 
+    def request_params(self) -> dict:
+        """Tells the server-side connector which trainer rank's ring the sample goes to; the
+        connector answers with the sample's sequence number in that ring as the handle."""
+        self.setup()  # the ring must be announced before the server looks for it
+        return {"ring_rank": self.rank}
+
     @staticmethod
     def wait_for_ring(rendezvous_path: str | Path, rank: int = 0, timeout_s: float = 60.0) -> dict[str, Any]:
         """Producer side: block until trainer ``rank`` has announced its ring."""
@@ -205,6 +212,73 @@ class NvlinkTransfer(HiddenStatesTransfer):
                 raise TimeoutError(f"no ring announced at {path} after {timeout_s}s")
             time.sleep(0.05)
         return json.loads(path.read_text())
+
+
+def ring_key(rank: int, seq: int) -> str:
+    return f"ring{rank}-{seq}"
+
+
+def parse_ring_key(key: str) -> tuple[int, int]:
+    rank, _, seq = key.removeprefix("ring").partition("-")
+    if not key.startswith("ring") or not rank.isdigit() or not seq.isdigit():
+        raise ValueError(f"not a ring key: {key!r}")
+    return int(rank), int(seq)
+
+
+class NvlinkRingSink:
+    """Store-shaped end of the server-side connector (``put_sample`` / ``put_error``): samples
+    keyed ``ring<rank>-<seq>`` are pushed into trainer ``rank``'s ring straight from device
+    memory.  A ring takes its samples in sequence order, requests finish in any order, so a
+    sample that arrives early is held until its predecessors have been pushed."""
+
+    accepts_device_tensors = True
+    is_setup = True
+
+    def __init__(self, rendezvous_path: str | Path, device: torch.device | str | None = None, timeout_s: float = 60.0, writer_factory=None):
+        self.rendezvous_path, self.device, self.timeout_s = Path(rendezvous_path), device, timeout_s
+        self._writer_factory = writer_factory or self._open_writer
+        self._writers: dict[int, Any] = {}
+        self._next: dict[int, int] = {}
+        self._held: dict[int, dict[int, tuple[torch.Tensor, torch.Tensor | None]]] = {}
+        self._lock = threading.Lock()
+
+    def setup(self) -> None:
+        """Rings are opened per trainer rank when its first sample arrives."""
+
+    def _open_writer(self, rank: int):
+        description = NvlinkTransfer.wait_for_ring(self.rendezvous_path, rank, self.timeout_s)
+        return HiddenStateRingWriter(description, self.device or f"cuda:{torch.cuda.current_device()}")
+
+    def _offer(self, rank: int, seq: int, hidden_states: torch.Tensor, token_ids: torch.Tensor | None) -> None:
+        with self._lock:
+            self._held.setdefault(rank, {})[seq] = (hidden_states, token_ids)
+            writer = self._writers.get(rank)
+            if writer is None:
+                writer = self._writers[rank] = self._writer_factory(rank)
+            nxt = self._next.get(rank, 1)
+            while nxt in self._held[rank]:
+                hs, ids = self._held[rank].pop(nxt)
+                writer.push(nxt, hs, ids, timeout_s=self.timeout_s)
+                nxt += 1
+            self._next[rank] = nxt
+
+    def put_sample(self, key: str, sample: dict[str, torch.Tensor]) -> None:
+        rank, seq = parse_ring_key(key)
+        self._offer(rank, seq, sample["hidden_states"], sample.get("token_ids"))
+
+    def put_error(self, key: str, message: str) -> None:
+        """A failed request still takes its place in the sequence: an empty sample (zero rows)
+        reaches the consumer, whose length check rejects it."""
+        rank, seq = parse_ring_key(key)
+        writer = self._writers.get(rank) or self._writer_factory(rank)
+        self._writers[rank] = writer
+        empty = torch.zeros(0, writer.width, dtype=torch.bfloat16, device=getattr(writer, "device", "cpu"))
+        self._offer(rank, seq, empty, None)
+
+    def close(self) -> None:
+        for writer in self._writers.values():
+            writer.close()
+        self._writers = {}
 
 
 @HiddenStatesBackend.register("nvlink")
@@ -230,5 +304,6 @@ class NvlinkBackend(HiddenStatesBackend):
     def build_kv_transfer_config(args: argparse.Namespace) -> dict[str, Any]:
         return {
             "kv_connector": "NvlinkHiddenStatesConnector", "kv_role": "kv_producer",
+            "kv_connector_module_path": "speculators_b200.hs_connectors.vllm_connector",
             "kv_connector_extra_config": {"rendezvous_path": args.nvlink_rendezvous_path},
         }

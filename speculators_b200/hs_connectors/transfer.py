@@ -67,6 +67,11 @@ class HiddenStatesTransfer(ABC):
     def delete(self, handle: str) -> None:  # noqa: B027
         """Drop a generated sample."""
 
+    def request_params(self) -> dict | None:
+        """``kv_transfer_params`` to send with a generation request (what the server-side
+        connector needs to know about this consumer); ``None``: nothing to send."""
+        return None
+
 
 class HiddenStatesBackend(ABC):
     registry: ClassVar[dict[str, type["HiddenStatesBackend"]]] = {}

@@ -63,9 +63,15 @@ class SchedulerSide:
     """Runs in the scheduler process: names requests, and when one finishes keeps its
     blocks alive (returns ``True``) until the worker has copied the hidden states out."""
 
-    def __init__(self) -> None:
+    def __init__(self, ring_mode: bool = False) -> None:
+        """``ring_mode``: samples go to per-trainer-rank rings (NVLink transport).  A finished
+        request is then named by the ring of the rank that asked (``ring_rank`` in its
+        ``kv_transfer_params``) and the next sequence number of that ring, which is also the
+        handle the client gets back."""
         self._keys: dict[str, str] = {}
         self._pending: dict[str, PendingSave] = {}
+        self._ring_mode = ring_mode
+        self._ring_seq: dict[int, int] = {}
 
     def on_new_request(self, req_id: str) -> None:
         self._keys[req_id] = sanitize_key(req_id)
@@ -73,6 +79,14 @@ class SchedulerSide:
     def request_finished(self, req_id: str, prompt_token_ids: list[int] | None, all_token_ids: list[int], block_ids: list[int],
                          kv_params: dict | None = None) -> tuple[bool, dict[str, Any]]:
         key = self._keys.pop(req_id, sanitize_key(req_id))
+        handle = key
+        if self._ring_mode:
+            from speculators_b200.hs_connectors.nvlink import ring_key
+
+            rank = int((kv_params or {}).get("ring_rank", 0))
+            seq = self._ring_seq.get(rank, 0) + 1
+            self._ring_seq[rank] = seq
+            key, handle = ring_key(rank, seq), str(seq)
         if (kv_params or {}).get("include_output_tokens", False):
             # the last token was sampled but never fed through the model: no hidden state for it
             ids = torch.tensor(list(all_token_ids)[:-1])
@@ -81,7 +95,7 @@ class SchedulerSide:
         else:
             ids = torch.tensor([], dtype=torch.long)
         self._pending[req_id] = PendingSave(req_id, key, ids, list(block_ids))
-        return True, {"handle": key}
+        return True, {"handle": handle}
 
     def drain(self) -> list[PendingSave]:
         out = list(self._pending.values())
@@ -117,6 +131,11 @@ class WorkerSide:
                 with torch.cuda.stream(stream):
                     hs = extract_from_kv_cache(cache, slots.to(cache.device, non_blocking=True), n)
                     assert_finite("hidden_states", hs)
+                    if getattr(self.store, "accepts_device_tensors", False):
+                        # device-to-device transports take the rows where they are
+                        self.store.put_sample(pending.key, {"hidden_states": hs, "token_ids": pending.token_ids.to(cache.device)})
+                        stream.synchronize()
+                        return
                     host = torch.empty_like(hs, device="cpu", pin_memory=True)
                     host.copy_(hs, non_blocking=True)
                 stream.synchronize()
@@ -196,9 +215,11 @@ if KVConnectorBase_V1 is not None:
             self._group = self._hidden_state_group(kv_cache_config)
             block_size = (kv_cache_config.kv_cache_groups[self._group].kv_cache_spec.block_size
                           if kv_cache_config is not None else vllm_config.cache_config.block_size)
+            self._scheduler, self._worker = self._build_sides(block_size)
+
+        def _build_sides(self, block_size: int):
             cfg = MooncakeStoreConfig.from_dict(self._kv_transfer_config.get_from_extra_config("mooncake", {}))
-            self._scheduler = SchedulerSide()
-            self._worker = WorkerSide(HiddenStatesStore(cfg), block_size, getattr(cfg, "num_writer_threads", 4))
+            return SchedulerSide(), WorkerSide(HiddenStatesStore(cfg), block_size, getattr(cfg, "num_writer_threads", 4))
 
         @staticmethod
         def _hidden_state_group(kv_cache_config) -> int:
@@ -263,4 +284,19 @@ if KVConnectorBase_V1 is not None:
         def get_required_kvcache_layout(cls, vllm_config):
             return "NHD"  # keeps one token's hidden states contiguous
 
-    __all__ += ["MooncakeConnectorMetadata", "MooncakeHiddenStatesConnector"]
+    class NvlinkHiddenStatesConnector(MooncakeHiddenStatesConnector):
+        """Same capture path, different sink: finished requests' hidden states are pushed from
+        the verifier GPU into the asking trainer rank's NVLink ring
+        (``hs_connectors/nvlink.py``).  Load with ``--kv_transfer_config '{"kv_connector":
+        "NvlinkHiddenStatesConnector", "kv_connector_module_path":
+        "speculators_b200.hs_connectors.vllm_connector", "kv_connector_extra_config":
+        {"rendezvous_path": ...}}'``."""
+
+        def _build_sides(self, block_size: int):
+            from speculators_b200.hs_connectors.nvlink import NvlinkRingSink
+
+            where = self._kv_transfer_config.get_from_extra_config("rendezvous_path", "/tmp/hidden_states_nvlink")  # noqa: S108
+            # one writer thread: pushes into a ring are ordered anyway
+            return SchedulerSide(ring_mode=True), WorkerSide(NvlinkRingSink(where), block_size, num_writer_threads=1)
+
+    __all__ += ["MooncakeConnectorMetadata", "MooncakeHiddenStatesConnector", "NvlinkHiddenStatesConnector"]

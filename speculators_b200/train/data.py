@@ -147,7 +147,8 @@ class ArrowDataset(BaseDataset):
             self._setup_client()
         row = self._row(index)
         try:
-            handle = generate_hidden_states(self.client, self.model, build_client_item(row), timeout=self.request_timeout, max_retries=self.max_retries)
+            handle = generate_hidden_states(self.client, self.model, build_client_item(row), timeout=self.request_timeout,
+                                            max_retries=self.max_retries, kv_transfer_params=self.transfer.request_params())
             loaded = self.transfer.get_generated(handle)
             if loaded is None:
                 raise ValueError(f"Failed to load hidden states for handle {handle}")

@@ -289,3 +289,72 @@ def test_vllm_connector_halves_with_dict_store():
     with pytest.raises(Exception, match="(?i)non-finite|nan|error"):
         store.get_sample("bad", timeout=0.5)
     worker.shutdown()
+
+
+def test_ring_mode_names_requests_by_rank_and_sequence_and_sink_pushes_in_order():
+    """NVLink transport, server side: the scheduler half numbers finished requests per trainer
+    rank and hands the number back as the handle; the sink holds samples that finish early
+    until their predecessors are in the ring; a failed request still takes its place."""
+    import time as _time
+
+    from speculators_b200.hs_connectors.nvlink import NvlinkRingSink, parse_ring_key, ring_key
+    from speculators_b200.hs_connectors.vllm_connector import SchedulerSide, WorkerSide
+
+    assert parse_ring_key(ring_key(3, 17)) == (3, 17)
+    with pytest.raises(ValueError):
+        parse_ring_key("req_1")
+
+    sched = SchedulerSide(ring_mode=True)
+    handles = [sched.request_finished(f"r{i}", [1, 2, 3], [1, 2, 3], [i], {"ring_rank": rank})[1]["handle"]
+               for i, rank in enumerate([0, 1, 0, 0, 1])]
+    assert handles == ["1", "1", "2", "3", "2"]
+    pending = sched.drain()
+    assert [p.key for p in pending] == ["ring0-1", "ring1-1", "ring0-2", "ring0-3", "ring1-2"]
+
+    pushed: dict[int, list] = {}
+
+    class _Writer:
+        width = 6
+
+        def __init__(self, rank):
+            self.rank = rank
+
+        def push(self, seq, hs, ids, timeout_s=1.0):
+            pushed.setdefault(self.rank, []).append((seq, hs.shape[0]))
+
+        def close(self):
+            pass
+
+    sink = NvlinkRingSink("/nonexistent", writer_factory=_Writer)
+    rows = lambda n: {"hidden_states": torch.zeros(n, 6), "token_ids": torch.arange(n)}  # noqa: E731
+    sink.put_sample("ring0-3", rows(3))  # early: held
+    sink.put_sample("ring0-2", rows(2))  # still waiting for 1
+    assert pushed == {}
+    sink.put_sample("ring0-1", rows(1))
+    assert pushed[0] == [(1, 1), (2, 2), (3, 3)]
+    sink.put_error("ring1-1", "boom")  # empty sample keeps ring 1's sequence going
+    sink.put_sample("ring1-2", rows(5))
+    assert pushed[1] == [(1, 0), (2, 5)]
+
+    # through the worker half (CPU cache): device-capable sinks are only used on CUDA caches,
+    # a CPU cache goes through the same put_sample with host rows
+    cache = torch.arange(4 * 2 * 6, dtype=torch.float32).reshape(4, 2, 6)
+    worker = WorkerSide(NvlinkRingSink("/nonexistent", writer_factory=_Writer), block_size=2, num_writer_threads=1)
+    worker.register(cache)
+    sched2 = SchedulerSide(ring_mode=True)
+    sched2.request_finished("a", [5, 6, 7], [5, 6, 7], [2, 0], {"ring_rank": 2})
+    worker.submit(sched2.drain())
+    for _ in range(200):
+        if worker.poll({"a"}):
+            break
+        _time.sleep(0.01)
+    assert pushed[2] == [(1, 3)]
+
+
+def test_generation_request_carries_the_transfer_parameters():
+    from speculators_b200.data_generation.vllm_client import _request
+
+    kind, kwargs = _request("m", {"input_ids": [1, 2]}, 5.0, {"ring_rank": 3})
+    assert kind == "completions" and kwargs["extra_body"]["kv_transfer_params"] == {"ring_rank": 3}
+    kind, kwargs = _request("m", {"input_ids": [1], "messages": [{"role": "user", "content": "hi"}]}, None)
+    assert kind == "chat" and "kv_transfer_params" not in kwargs["extra_body"] and kwargs["extra_body"]["return_token_ids"] is True
