@@ -11,9 +11,10 @@ over N GPUs.  Synthetic seeded tokens, random-init weights.
 For N > 1 launch under ``python -m torch.distributed.run --nproc-per-node N``.
 Rank 0 prints one JSON line.  ``value`` is whole-job tokens/s from K steps timed
 with CUDA events between barriers (max over ranks) with the batch already on the
-device; ``e2e`` repeats the measurement through ``Trainer.train_step`` with the
-batch in pinned host memory (H2D copy every step) and a device-to-host read of the
-loss every step.
+device; ``e2e`` repeats the measurement through ``Trainer.train_step_async`` with the
+batch in pinned host memory (H2D copy every step, started one step ahead on a side
+stream) and a device-to-host read of every step's loss (the host reads step n's loss once
+step n + 1 is enqueued; the last one at once).
 """
 
 from __future__ import annotations
@@ -257,9 +258,16 @@ def run_ours(args):
 
     def step_e2e(b, upcoming):
         # the public training call: this step's batch plus the one that follows, whose
-        # host-to-device copy the trainer overlaps with this step's compute
-        loss, _ = trainer.train_step(b, upcoming)
-        last["loss"] = float(loss.item())
+        # host-to-device copy the trainer overlaps with this step's compute.  Every step's loss
+        # is read back on the host; the read of step n happens once step n + 1 is enqueued, so
+        # the device does not idle while the host reads (the last step is read at once).
+        handle = trainer.train_step_async(b, upcoming)
+        if last.get("pending") is not None:
+            last["loss"] = last["pending"].value()
+        last["pending"] = handle
+        if upcoming is None:
+            last["loss"] = handle.value()
+            last["pending"] = None
 
     ms_e2e = timed_region(torch, dist, world, device, step_e2e, batches, args.steps, min(args.warmup, 3), lookahead=True)
     h2d = sum(v.numel() * v.element_size() for v in batches[0].values())

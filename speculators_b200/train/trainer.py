@@ -40,7 +40,7 @@ from speculators_b200.train.utils import normalize_counted_metrics
 root_logger = logging.getLogger("speculators")
 metric_logger = logging.getLogger("speculators.metrics")
 
-__all__ = ["Trainer", "TrainerConfig"]
+__all__ = ["LossHandle", "Trainer", "TrainerConfig"]
 
 MIN_STEP_PCT = 0.25
 _VAL_SYNC_INTERVAL = 50  # barrier every N validation batches to bound rank skew
@@ -123,6 +123,20 @@ class _StepTimer:
             "tokens_per_s": num_tokens / (step / 1000.0) if step > 0 else 0.0,
             "fetch_frac": fetch / step if step > 0 else 0.0,
         }
+
+
+class LossHandle:
+    """Loss of one ``train_step_async`` call on its way to the host."""
+
+    RING = 4
+
+    def __init__(self, host: torch.Tensor, event) -> None:  # noqa: ANN001
+        self._host, self._event = host, event
+
+    def value(self) -> float:
+        if self._event is not None:
+            self._event.synchronize()
+        return float(self._host[0])
 
 
 def _with_lookahead(iterable):
@@ -392,6 +406,26 @@ class Trainer:
             sched.step()
         self.timer.mark("opt")
         return loss, metrics
+
+    def train_step_async(self, batch: dict, next_batch: dict | None = None) -> "LossHandle":
+        """``train_step`` that does not make the host wait for the step: the loss is copied to
+        pinned host memory behind the step on the training stream and returned as a handle
+        whose ``value()`` waits for just that copy.  Reading the handle of step ``n`` after
+        step ``n + 1`` has been enqueued keeps the device busy while the host reads.  At most
+        ``LossHandle.RING`` handles may be outstanding."""
+        loss, _ = self.train_step(batch, next_batch)
+        if not hasattr(self, "_loss_ring"):
+            pin = self.device.type == "cuda"
+            self._loss_ring = [torch.zeros(1, dtype=torch.float32, pin_memory=pin) for _ in range(LossHandle.RING)]
+            self._loss_ring_pos = 0
+        slot = self._loss_ring[self._loss_ring_pos % LossHandle.RING]
+        self._loss_ring_pos += 1
+        slot.copy_(loss.detach().reshape(1), non_blocking=True)
+        event = None
+        if self.device.type == "cuda":
+            event = torch.cuda.Event()
+            event.record()
+        return LossHandle(slot, event)
 
     # ------------------------------------------------------------------ epochs
     def _prepare_resume_skip(self, epoch: int) -> int:

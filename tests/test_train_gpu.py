@@ -48,6 +48,23 @@ def test_graph_and_eager_trainers_agree_and_learn(tiny_verifier_dir, tiny_vocab_
     assert t_graph._graphed is not None and len(t_graph._graphed.cache) == 1
 
 
+def test_async_step_returns_every_loss_through_pinned_handles(tiny_verifier_dir, tiny_vocab_maps):
+    """``train_step_async``: the loss of step n is read after step n + 1 was enqueued and is
+    the value a synchronous ``train_step`` on an identical trainer reports for step n."""
+    base = make_tiny_eagle3(tiny_verifier_dir, tiny_vocab_maps)
+    batch = make_tiny_batch(T=64, docs=(20, 30, 10), pad=4)
+    sync, lagged = _trainer(copy.deepcopy(base), batch, graph=True), _trainer(copy.deepcopy(base), batch, graph=True)
+    want = [float(sync.train_step(batch)[0].item()) for _ in range(6)]
+    got, pending = [], None
+    for _ in range(6):
+        handle = lagged.train_step_async(batch, batch)
+        if pending is not None:
+            got.append(pending.value())
+        pending = handle
+    got.append(pending.value())
+    assert got == pytest.approx(want, rel=1e-5, abs=1e-6)
+
+
 def test_fused_step_tail_matches_op_by_op_metrics():
     """One-launch tail (masked mean, decay, accuracy counters, prev_correct update) against
     the same quantities computed with separate torch ops, forward and backward."""

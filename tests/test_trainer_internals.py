@@ -181,3 +181,27 @@ def test_mid_epoch_checkpoint_and_resume(tiny_verifier_dir, tiny_vocab_maps, tmp
     assert final["global_step"] == 4
     val = second.val_epoch(0)
     assert val is not None and all(k.endswith("_epoch") for k in val) and "loss_epoch" in val and 0.0 <= val["full_acc_0_epoch"] <= 1.0
+
+
+def test_async_step_handles_on_cpu(tiny_verifier_dir, tiny_vocab_maps, tmp_path):
+    """The handle API also works without a GPU (no event, plain host tensor)."""
+    import copy
+
+    import speculators_b200 as sb
+    from speculators_b200.train import Trainer, TrainerConfig
+    from speculators_b200.train.synthetic import SyntheticLoader
+    from tests.conftest import make_tiny_batch, make_tiny_eagle3
+
+    base = make_tiny_eagle3(tiny_verifier_dir, tiny_vocab_maps)
+    batch = make_tiny_batch(T=32)
+    kwargs, _ = sb.Eagle3DraftModel.get_trainer_kwargs(loss_fn="kl_div", ttt_steps=2, ttt_step_loss_decay=1.0)
+
+    def make(model):
+        return Trainer(model, TrainerConfig(lr=1e-3, num_epochs=1, save_path=str(tmp_path / str(id(model))), train_call_kwargs=kwargs,
+                                            scheduler_type="none", log_freq=10**9, device="cpu"), SyntheticLoader([batch], 3))
+
+    a, b = make(copy.deepcopy(base)), make(copy.deepcopy(base))
+    want = [float(a.train_step(batch)[0].item()) for _ in range(3)]
+    handles = [b.train_step_async(batch) for _ in range(3)]
+    # on the CPU every handle holds its own value only until the ring wraps; three fit
+    assert [h.value() for h in handles] == pytest.approx(want, rel=1e-6)
