@@ -9,8 +9,8 @@
 //       S = Q K^T, dP = dO V^T                 (queries on the TMEM lanes)
 //       P = 2^(S * scale * log2e - lse),  dS = P * (dP - delta)      -> TMEM (bf16)
 //       dQ += dS K                             (A from TMEM, K tile as MN-major B operand)
-//     It also computes delta = rowsum(dO * O) for the second kernel and handles the
-//     individually addressed extra keys (their dK / dV through fp32 atomics).
+//     It also handles the individually addressed extra keys (their dK / dV through fp32
+//     atomics).  delta = rowsum(dO * O) comes from a small streaming kernel in front.
 //
 //   dK/dV kernel, one CTA per (query head, key tile), loop over the query tiles that see it:
 //       S^T = K Q^T, dP^T = V dO^T             (keys on the TMEM lanes)
@@ -68,6 +68,26 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   return *reinterpret_cast<const uint32_t*>(&h2);
 }
 
+// ---------------------------------------------------------------------------------- delta
+// delta[h, row] = sum_c dO[row, h, c] * O[row, h, c]: one warp per (row, head), 8 bytes per lane.
+__global__ void __launch_bounds__(256)
+attn_delta_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ out, float* __restrict__ delta, int Tq, int nh,
+                  int64_t do_rs, int64_t o_rs) {
+  const int lane = threadIdx.x & 31;
+  const int64_t n = (int64_t)Tq * nh;
+  for (int64_t idx = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); idx < n; idx += (int64_t)gridDim.x * 8) {
+    const int row = (int)(idx / nh), h = (int)(idx % nh);
+    const uint2 a = *reinterpret_cast<const uint2*>(dout + (int64_t)row * do_rs + h * HD + lane * 4);
+    const uint2 b = *reinterpret_cast<const uint2*>(out + (int64_t)row * o_rs + h * HD + lane * 4);
+    const float2 a0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.x)), a1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.y));
+    const float2 b0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&b.x)), b1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&b.y));
+    float acc = a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) delta[(int64_t)h * Tq + row] = acc;
+  }
+}
+
 // ------------------------------------------------------------------------------------- dQ
 __global__ void __launch_bounds__(THREADS, 1)
 attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
@@ -77,9 +97,15 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* q_s = smem;
   unsigned char* do_s = q_s + TILE_BYTES;
-  unsigned char* k_s = do_s + TILE_BYTES;     // 2 stages
-  unsigned char* v_s = k_s + 2 * TILE_BYTES;  // 2 stages
-  __shared__ __align__(8) uint64_t bar_qdo, bar_kv_full[2], bar_kv_empty[2], bar_sdp_full, bar_sdp_free, bar_ds_ready, bar_dq_done;
+  // A K tile is read twice, at the start of its tile (S = Q K^T) and at the very end (dQ += dS K),
+  // so a stage is only released a whole tile after the next one is needed: three stages keep
+  // the refill out of the critical path.  A V tile is done with as soon as dP = dO V^T has
+  // been multiplied, before the tile's element-wise work even starts: one buffer, refilled
+  // during that work, is enough.
+  unsigned char* k_s = do_s + TILE_BYTES;     // 3 stages
+  unsigned char* v_s = k_s + 3 * TILE_BYTES;  // 1 buffer
+  __shared__ __align__(8) uint64_t bar_qdo, bar_k_full[3], bar_k_empty[3], bar_v_full, bar_v_empty, bar_sdp_full, bar_sdp_free, bar_ds_ready,
+      bar_dq_done;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int s_range[2];
   __shared__ float2 s_xchg[2][2][BM];
@@ -91,10 +117,12 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 
   if (threadIdx.x == 0) {
     mbar_init(smem_addr(&bar_qdo), 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(smem_addr(&bar_kv_full[s]), 1);
-      mbar_init(smem_addr(&bar_kv_empty[s]), 1);
+    for (int s = 0; s < 3; ++s) {
+      mbar_init(smem_addr(&bar_k_full[s]), 1);
+      mbar_init(smem_addr(&bar_k_empty[s]), 1);
     }
+    mbar_init(smem_addr(&bar_v_full), 1);
+    mbar_init(smem_addr(&bar_v_empty), 1);
     mbar_init(smem_addr(&bar_sdp_full), 1);
     mbar_init(smem_addr(&bar_sdp_free), 8);  // one arrival per element-wise warp
     mbar_init(smem_addr(&bar_ds_ready), 8);  // one arrival per element-wise warp
@@ -148,16 +176,19 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       tma_load_2d(smem_addr(do_s), &map_do, qb, h * HD, q0);
       tma_load_2d(smem_addr(do_s) + SUB_BYTES, &map_do, qb, h * HD + 64, q0);
       for (int t = 0; t < n_tiles; ++t) {
-        const int st = t & 1;
-        if (!mbar_wait(smem_addr(&bar_kv_empty[st]), ((t >> 1) & 1) ^ 1, status, kTimeoutDqProducer)) break;
-        const uint32_t full = smem_addr(&bar_kv_full[st]);
-        mbar_expect_tx(full, 2 * TILE_BYTES);
+        const int st = t % 3;
         const int key0 = (j0 + t) * BN;
-        const uint32_t ka = smem_addr(k_s + st * TILE_BYTES), va = smem_addr(v_s + st * TILE_BYTES);
-        tma_load_2d(ka, &map_k, full, kvh * HD, key0);
-        tma_load_2d(ka + SUB_BYTES, &map_k, full, kvh * HD + 64, key0);
-        tma_load_2d(va, &map_v, full, kvh * HD, key0);
-        tma_load_2d(va + SUB_BYTES, &map_v, full, kvh * HD + 64, key0);
+        if (!mbar_wait(smem_addr(&bar_k_empty[st]), ((t / 3) & 1) ^ 1, status, kTimeoutDqProducer)) break;
+        const uint32_t kfull = smem_addr(&bar_k_full[st]);
+        mbar_expect_tx(kfull, TILE_BYTES);
+        const uint32_t ka = smem_addr(k_s + st * TILE_BYTES), va = smem_addr(v_s);
+        tma_load_2d(ka, &map_k, kfull, kvh * HD, key0);
+        tma_load_2d(ka + SUB_BYTES, &map_k, kfull, kvh * HD + 64, key0);
+        if (!mbar_wait(smem_addr(&bar_v_empty), (t & 1) ^ 1, status, kTimeoutDqProducer)) break;
+        const uint32_t vfull = smem_addr(&bar_v_full);
+        mbar_expect_tx(vfull, TILE_BYTES);
+        tma_load_2d(va, &map_v, vfull, kvh * HD, key0);
+        tma_load_2d(va + SUB_BYTES, &map_v, vfull, kvh * HD + 64, key0);
       }
     }
   } else if (warp == 1) {
@@ -166,18 +197,21 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       constexpr uint32_t idesc_mn = instr_desc(BM, HD, true);
       const uint32_t qa = smem_addr(q_s), da = smem_addr(do_s);
       auto issue_scores = [&](int t) {  // S = Q K_t^T and dP = dO V_t^T
-        mma_ss(tmem_base + COL_S, qa, smem_addr(k_s + (t & 1) * TILE_BYTES), idesc_kk);
-        mma_ss(tmem_base + COL_DP, da, smem_addr(v_s + (t & 1) * TILE_BYTES), idesc_kk);
+        mma_ss(tmem_base + COL_S, qa, smem_addr(k_s + (t % 3) * TILE_BYTES), idesc_kk);
+        mma_ss(tmem_base + COL_DP, da, smem_addr(v_s), idesc_kk);
         umma_commit(smem_addr(&bar_sdp_full));
+        umma_commit(smem_addr(&bar_v_empty));  // the V buffer may be refilled
       };
-      bool ok = mbar_wait(smem_addr(&bar_qdo), 0, status, kTimeoutDqMma) && mbar_wait(smem_addr(&bar_kv_full[0]), 0, status, kTimeoutDqMma);
+      bool ok = mbar_wait(smem_addr(&bar_qdo), 0, status, kTimeoutDqMma) && mbar_wait(smem_addr(&bar_k_full[0]), 0, status, kTimeoutDqMma) &&
+                mbar_wait(smem_addr(&bar_v_full), 0, status, kTimeoutDqMma);
       if (ok) {
         fence_after_sync();
         issue_scores(0);
       }
       for (int t = 0; t < n_tiles && ok; ++t) {
         if (t + 1 < n_tiles) {
-          if (!(ok = mbar_wait(smem_addr(&bar_kv_full[(t + 1) & 1]), ((t + 1) >> 1) & 1, status, kTimeoutDqMma))) break;
+          if (!(ok = mbar_wait(smem_addr(&bar_k_full[(t + 1) % 3]), ((t + 1) / 3) & 1, status, kTimeoutDqMma))) break;
+          if (!(ok = mbar_wait(smem_addr(&bar_v_full), (t + 1) & 1, status, kTimeoutDqMma))) break;
           // the element-wise threads hold tile t's S / dP in registers from here on
           if (!(ok = mbar_wait(smem_addr(&bar_sdp_free), t & 1, status, kTimeoutDqMma))) break;
           fence_after_sync();
@@ -186,9 +220,9 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         if (!(ok = mbar_wait(smem_addr(&bar_ds_ready), t & 1, status, kTimeoutDqMma))) break;
         fence_after_sync();
         const uint32_t ds = tmem_base + COL_DS + (t & 1) * 64;
-        mma_ts(tmem_base + COL_DQ, ds, ds + 32, smem_addr(k_s + (t & 1) * TILE_BYTES), idesc_mn, t > 0);
+        mma_ts(tmem_base + COL_DQ, ds, ds + 32, smem_addr(k_s + (t % 3) * TILE_BYTES), idesc_mn, t > 0);
         umma_commit(smem_addr(&bar_dq_done));
-        umma_commit(smem_addr(&bar_kv_empty[t & 1]));
+        umma_commit(smem_addr(&bar_k_empty[t % 3]));
       }
     }
   } else {
@@ -217,24 +251,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     ok = __all_sync(0xffffffffu, ok);
     const unsigned char* q_row = q_s + half * SUB_BYTES + prow * 128;    // this thread's 64 head-dim columns of q
     const unsigned char* do_row = do_s + half * SUB_BYTES + prow * 128;  // ... and of dO
-    // delta = rowsum(dO * O)
-    float delta;
-    {
-      float part = 0.f;
-      if (row_ok) {
-        const __nv_bfloat16* orow = p.out + (int64_t)row * p.o_rs + h * HD + colh;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          float a[8], b[8];
-          unpack8(*reinterpret_cast<const bf16x8*>(do_row + ((c ^ sw) << 4)), a);
-          unpack8(ld8(orow + c * 8), b);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) part = fmaf(a[i], b[i], part);
-        }
-      }
-      delta = part + exchange(make_float2(part, 0.f)).x;
-      if (row_ok && half == 0) p.delta[(int64_t)h * p.Tq + row] = delta;
-    }
+    const float delta = row_ok ? p.delta[(int64_t)h * p.Tq + row] : 0.f;  // rowsum(dO * O), from attn_delta_kernel
 
     for (int t = 0; t < n_tiles; ++t) {
       if (ok) ok = mbar_wait(smem_addr(&bar_sdp_full), t & 1, status, kTimeoutDqCompute);
@@ -378,15 +395,10 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       }
     }
 
-    if (ok && row_ok) {
-      __nv_bfloat16* drow = p.dq + (int64_t)row * p.dq_rs + h * HD + colh;
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        float f[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] = dq[c * 8 + i] * p.scale;
-        st8(drow + c * 8, pack8(f));
-      }
+    if (__all_sync(0xffffffffu, ok)) {
+      // whole rows through the warp's staging area (the K / V stages are idle by now)
+      const int warp_row0 = q0 + quarter * 32;
+      store_rows64_bf16(k_s + (warp - 2) * 16384, dq, p.scale, p.dq + (int64_t)warp_row0 * p.dq_rs + h * HD + colh, p.dq_rs, p.Tq - warp_row0, lane);
     }
   }
 
@@ -653,9 +665,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
     // results: this thread's key row, 64 head-dim columns of dV and of dK
     float acc[64];
-    const bool key_ok = key < p.Tc;
     const int64_t plane = (int64_t)p.Tc * p.nkv * HD;
-    const int64_t off = ((int64_t)key * p.nkv + kvh) * HD + colh;
 #pragma unroll 1
     for (int which = 0; which < 2; ++which) {  // 0: dK, 1: dV
 #pragma unroll
@@ -675,21 +685,16 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         fence_before_sync();
       }
-      if (ok && key_ok) {
-        if (p.dkv_part != nullptr) {
-          float* dst = p.dkv_part + (int64_t)(h - kvh * group) * 2 * plane + which * plane + off;
-#pragma unroll
-          for (int c = 0; c < 16; ++c) *reinterpret_cast<float4*>(dst + c * 4) = make_float4(acc[c * 4], acc[c * 4 + 1], acc[c * 4 + 2], acc[c * 4 + 3]);
-        } else {
-          __nv_bfloat16* dst = (which ? p.dv : p.dk) + off;
-#pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            float f[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) f[i] = acc[c * 8 + i];
-            st8(dst + c * 8, pack8(f));
-          }
-        }
+      if (__all_sync(0xffffffffu, ok)) {
+        // whole rows through the warp's staging area (the Q / dO stages are idle by now)
+        unsigned char* stage = q_s + (warp - 2) * 16384;
+        const int warp_key0 = key_base + quarter * 32;
+        const int64_t off0 = ((int64_t)warp_key0 * p.nkv + kvh) * HD + colh;
+        if (p.dkv_part != nullptr)
+          store_rows64_f32(stage, acc, p.dkv_part + (int64_t)(h - kvh * group) * 2 * plane + which * plane + off0, (int64_t)p.nkv * HD,
+                           p.Tc - warp_key0, lane);
+        else
+          store_rows64_bf16(stage, acc, 1.f, (which ? p.dv : p.dk) + off0, (int64_t)p.nkv * HD, p.Tc - warp_key0, lane);
       }
     }
   }
@@ -724,7 +729,12 @@ int launch_attn_bwd_tc(const AttnParams& p, int* tile_qmin, int* tile_qmax, int*
     if (cudaFuncSetAttribute(attn_bwd_dkv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -2;
     configured = true;
   }
-  count_launch(2);
+  count_launch(3);
+  {
+    const int64_t pairs = (int64_t)p.Tq * p.nh;
+    const int64_t blocks = (pairs + 7) / 8;
+    attn_delta_kernel<<<(int)(blocks < 16 * kNumSM ? blocks : 16 * kNumSM), 256, 0, stream>>>(p.dout, p.out, p.delta, p.Tq, p.nh, p.do_rs, p.o_rs);
+  }
   dim3 grid_q(p.nh, (p.Tq + BM - 1) / BM);
   attn_bwd_dq_tc_kernel<<<grid_q, THREADS, SMEM_BYTES, stream>>>(map_q, map_do, map_k, map_v, p, status);
   rc = launch_kv_tile_range(p, tile_qmin, tile_qmax, stream);

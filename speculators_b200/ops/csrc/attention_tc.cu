@@ -384,17 +384,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     }
 
     const float l_all = l + exchange(l);
-    if (ok && row_ok) {
-      const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
-      __nv_bfloat16* orow = p.out + (int64_t)row * p.o_rs + h * HD + colh;
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        float f[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] = o[c * 8 + i] * inv;
-        st8(orow + c * 8, pack8(f));
-      }
-      if (half == 0) p.lse2[(int64_t)h * p.Tq + row] = l_all > 0.f ? m + log2f(l_all) : INFINITY;
+    const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+    if (ok && row_ok && half == 0) p.lse2[(int64_t)h * p.Tq + row] = l_all > 0.f ? m + log2f(l_all) : INFINITY;
+    if (__all_sync(0xffffffffu, ok)) {
+      // whole rows through the warp's staging area (the K / V stages are idle by now)
+      const int warp_row0 = q0 + quarter * 32;
+      store_rows64_bf16(k_s + (warp - 2) * 8192, o, inv, p.out + (int64_t)warp_row0 * p.o_rs + h * HD + colh, p.o_rs, p.Tq - warp_row0, lane);
     }
   }
 

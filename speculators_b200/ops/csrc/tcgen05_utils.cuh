@@ -136,6 +136,48 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+// ---- row-per-lane results to global memory through a per-warp staging area ----------------
+// A lane that holds one output row would store it as 16-byte pieces scattered over 32 rows
+// (partial sectors, one line per lane).  Instead the warp lays its 32 rows into shared memory
+// (16-byte chunks XOR-swizzled by the row so that neither side has bank conflicts) and then
+// writes whole rows: 8 lanes per 128-byte bf16 row, 16 lanes per 256-byte fp32 row.
+// `stage`: 4 KB (bf16) / 8 KB (fp32) private to the warp; `rows_valid`: rows of the warp's 32
+// that exist; `gbase`: element 0 of the warp's row 0; vals[i] is column i of the lane's row.
+__device__ __forceinline__ void store_rows64_bf16(unsigned char* stage, const float (&vals)[64], float mul, __nv_bfloat16* gbase,
+                                                  int64_t row_stride, int rows_valid, int lane) {
+  __syncwarp();
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    float f[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = vals[c * 8 + i] * mul;
+    *reinterpret_cast<bf16x8*>(stage + lane * 128 + ((c ^ (lane & 7)) << 4)) = pack8(f);
+  }
+  __syncwarp();
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int r = it * 4 + (lane >> 3), pc = lane & 7;
+    const bf16x8 v = *reinterpret_cast<const bf16x8*>(stage + r * 128 + ((pc ^ (r & 7)) << 4));
+    if (r < rows_valid) st8(gbase + (int64_t)r * row_stride + pc * 8, v);
+  }
+  __syncwarp();
+}
+__device__ __forceinline__ void store_rows64_f32(unsigned char* stage, const float (&vals)[64], float* gbase, int64_t row_stride,
+                                                 int rows_valid, int lane) {
+  __syncwarp();
+  float4* mine = reinterpret_cast<float4*>(stage + lane * 256);
+#pragma unroll
+  for (int c = 0; c < 16; ++c) mine[c ^ (lane & 7)] = make_float4(vals[c * 4], vals[c * 4 + 1], vals[c * 4 + 2], vals[c * 4 + 3]);
+  __syncwarp();
+#pragma unroll
+  for (int it = 0; it < 16; ++it) {
+    const int r = it * 2 + (lane >> 4), pc = lane & 15;
+    const float4 v = reinterpret_cast<const float4*>(stage + r * 256)[pc ^ (r & 7)];
+    if (r < rows_valid) *reinterpret_cast<float4*>(gbase + (int64_t)r * row_stride + pc * 4) = v;
+  }
+  __syncwarp();
+}
+
 // ---- cluster / cta_group::2 helpers ------------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
