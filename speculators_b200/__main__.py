@@ -43,5 +43,11 @@ def main(argv: list[str] | None = None) -> int:
     return 0
 
 
+
+def app(argv: list[str] | None = None) -> None:
+    """Console entry point (the reference exposes its command line under this name)."""
+    raise SystemExit(main(argv))
+
+
 if __name__ == "__main__":
     sys.exit(main())

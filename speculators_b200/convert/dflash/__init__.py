@@ -1,0 +1,3 @@
+from speculators_b200.convert.dflash.converter import DFlashConverter
+
+__all__ = ["DFlashConverter"]

@@ -35,6 +35,7 @@ class InvalidResponseError(Exception):
 class ClientItem(TypedDict, total=False):
     input_ids: list[int]
     messages: list[dict]  # only for multimodal conversations (chat completions re-tokenises)
+from speculators_b200.hs_connectors.transfer import wait_for_lock, wait_for_lock_async  # noqa: E402,F401 - reference exposes them here too
 
 
 def _backoff_or_raise(err: Exception, attempt: int, total: int) -> float | None:

@@ -25,7 +25,7 @@ from typing import Any, ClassVar
 import torch
 from safetensors.torch import load_file
 
-__all__ = ["FileBackend", "FileTransfer", "HiddenStatesBackend", "HiddenStatesTransfer", "wait_for_lock"]
+__all__ = ["FileBackend", "FileTransfer", "HiddenStatesBackend", "HiddenStatesTransfer", "wait_for_lock", "wait_for_lock_async"]
 
 
 def wait_for_lock(lock_path: str, timeout: float = 10.0, poll_interval: float = 0.1) -> None:
@@ -43,6 +43,31 @@ def wait_for_lock(lock_path: str, timeout: float = 10.0, poll_interval: float = 
                 if time.monotonic() >= deadline:
                     raise TimeoutError(f"Timed out waiting for lock: {lock_path}") from None
                 time.sleep(poll_interval)
+    finally:
+        os.close(fd)
+    try:
+        os.remove(lock_path)
+    except FileNotFoundError:
+        pass
+
+
+async def wait_for_lock_async(lock_path: str, timeout: float = 10.0, poll_interval: float = 0.1) -> None:
+    """``wait_for_lock`` for event-loop callers: polls the producer's ``flock`` without
+    blocking the loop; ``TimeoutError`` (``asyncio.TimeoutError``) after ``timeout`` seconds."""
+    import asyncio
+
+    fd = os.open(lock_path, os.O_RDWR)
+
+    async def poll() -> None:
+        while True:
+            try:
+                fcntl.flock(fd, fcntl.LOCK_EX | fcntl.LOCK_NB)
+                return
+            except BlockingIOError:
+                await asyncio.sleep(poll_interval)
+
+    try:
+        await asyncio.wait_for(poll(), timeout=timeout)
     finally:
         os.close(fd)
     try:

@@ -14,7 +14,7 @@ from speculators_b200.layer_config import TransformerLayerConfig
 from speculators_b200.models.layers import MLP, FusedLinear, Linear, RMSNorm, RotaryTable
 from speculators_b200.ops import AttnSpec
 
-__all__ = ["DFlashAttention", "DFlashDecoderLayer"]
+__all__ = ["DFlashAttention", "DFlashDecoderLayer", "Qwen3DFlashAttention", "Qwen3DFlashDecoderLayer", "apply_rotary_pos_emb"]
 
 
 class DFlashAttention(nn.Module):
@@ -58,3 +58,24 @@ class DFlashDecoderLayer(nn.Module):
     def forward(self, noise, target_hidden, noise_positions, all_positions, rotary, spec):
         noise = self.self_attn(self.input_layernorm(noise), target_hidden, noise_positions, all_positions, rotary, spec, residual=noise)
         return self.mlp(self.post_attention_layernorm(noise), residual=noise)
+
+
+# names of the reference's Hugging-Face-based classes (src/speculators/models/dflash/model_definitions.py:47,158)
+Qwen3DFlashAttention = DFlashAttention
+Qwen3DFlashDecoderLayer = DFlashDecoderLayer
+
+
+def apply_rotary_pos_emb(q, k, cos, sin, position_ids=None, unsqueeze_dim: int = 1):  # noqa: ARG001
+    """Rotate-half rotary embedding of ``q`` and ``k`` ([..., heads, T, hd] with ``cos`` / ``sin``
+    [..., T, hd]); when ``q`` is shorter than ``k`` (block queries appended to the context) it
+    takes the last ``q_len`` positions (src/speculators/models/dflash/model_definitions.py:29-44).
+    The training path applies the same rotation inside ``ops.rope_split``."""
+    import torch
+
+    def rotate_half(x):
+        a, b = x[..., : x.shape[-1] // 2], x[..., x.shape[-1] // 2:]
+        return torch.cat((-b, a), dim=-1)
+
+    cos, sin = cos.unsqueeze(unsqueeze_dim), sin.unsqueeze(unsqueeze_dim)
+    q_len = q.size(-2)
+    return q * cos[..., -q_len:, :] + rotate_half(q) * sin[..., -q_len:, :], k * cos + rotate_half(k) * sin

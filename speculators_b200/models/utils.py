@@ -8,6 +8,7 @@ import warnings
 from speculators_b200.layer_config import TransformerLayerConfig, read_config_json, unwrap_text_config
 
 __all__ = [
+    "DEFAULT_TARGET_LAYER_IDS_WARNING",
     "flatten_rope_parameters",
     "conditional_torch_compile",
     "get_verifier_config",
@@ -26,6 +27,12 @@ def conditional_torch_compile(fn=None, **_compile_kwargs):
     return fn
 
 
+DEFAULT_TARGET_LAYER_IDS_WARNING = (
+    "--target-layer-ids is not explicitly set. Setting target layers to {ids}. If custom target "
+    "layers were used when launching vllm datagen, please set them explicitly."
+)
+
+
 def get_verifier_config(verifier_name_or_path: str, trust_remote_code: bool = False) -> TransformerLayerConfig:
     """Language-model part of the verifier's config.json (``text_config`` unwrapped)."""
     del trust_remote_code  # nothing is executed from the checkpoint directory
@@ -38,11 +45,7 @@ def resolve_target_layer_ids(target_layer_ids: list[int] | None, verifier_name_o
         return list(target_layer_ids)
     n = int(get_verifier_config(verifier_name_or_path, trust_remote_code).num_hidden_layers)
     ids = [2, n // 2, n - 3]
-    warnings.warn(
-        f"--target-layer-ids is not explicitly set. Setting target layers to {ids}. If custom target "
-        "layers were used when launching vllm datagen, please set them explicitly.",
-        stacklevel=3,
-    )
+    warnings.warn(DEFAULT_TARGET_LAYER_IDS_WARNING.format(ids=ids), stacklevel=3)
     return ids
 
 

@@ -18,15 +18,19 @@ import threading
 
 log = logging.getLogger("speculators")
 
-__all__ = ["GracefulShutdownHandler", "TrainingInterrupted", "with_graceful_shutdown"]
+__all__ = ["DEFAULT_SHUTDOWN_TIMEOUT", "TrainingInterruptedError", "GracefulShutdownHandler", "TrainingInterrupted", "with_graceful_shutdown"]
 
 DEFAULT_TIMEOUT_S = 120.0
+DEFAULT_SHUTDOWN_TIMEOUT = int(DEFAULT_TIMEOUT_S)  # the reference's name for the same budget
 
 
 class TrainingInterrupted(BaseException):
     def __init__(self, signum: int):
         super().__init__(f"received signal {signum}")
         self.signum = signum
+
+
+TrainingInterruptedError = TrainingInterrupted  # the reference's name
 
 
 class GracefulShutdownHandler:

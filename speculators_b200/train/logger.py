@@ -16,6 +16,7 @@ Run names accept the placeholders ``{time}``, ``{utc_time}``, ``{rank}``,
 
 from __future__ import annotations
 
+import json
 import logging
 import numbers
 import os
@@ -23,6 +24,8 @@ from collections.abc import Mapping
 from datetime import datetime, timezone
 from pathlib import Path
 from typing import Any
+
+import torch
 
 __all__ = [
     "FormatDictFilter", "IsMappingFilter", "IsRank0Filter", "MLFlowHandler", "TensorBoardHandler", "TrackioHandler",
@@ -121,6 +124,11 @@ class _LazyHandler(logging.Handler):
             self._ready = True
 
 
+# hyper-parameter values TensorBoard's hparams plugin takes as they are; anything else (lists,
+# nested dicts) is JSON-encoded before it is handed over
+TB_SUPPORTED_TYPES = (int, float, str, bool, torch.Tensor, type(None))
+
+
 class TensorBoardHandler(_LazyHandler):
     def _setup(self) -> None:
         from torch.utils.tensorboard import SummaryWriter
@@ -132,12 +140,17 @@ class TensorBoardHandler(_LazyHandler):
             return
         self._ensure()
         if getattr(record, "hparams", False):
-            text = "\n".join(f"    {k}: {v}" for k, v in _flatten_dict(record.msg).items())
-            self.writer.add_text("hparams", text)
+            flat = _flatten_dict(record.msg)
+            self.writer.add_text("hparams", "\n".join(f"    {k}: {v}" for k, v in flat.items()))
+            self.writer.add_hparams(self._scalarise(flat), {}, run_name=".")  # the hparams tab of the same run
             return
         step = getattr(record, "step", None)
         for key, value in _scalars(record.msg).items():
             self.writer.add_scalar(key, value, global_step=step)
+
+    @staticmethod
+    def _scalarise(d: Mapping) -> dict:
+        return {k: (v if isinstance(v, TB_SUPPORTED_TYPES) else json.dumps(v, default=str)) for k, v in d.items()}
 
     def flush(self) -> None:
         if self._ready:

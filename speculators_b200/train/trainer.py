@@ -351,7 +351,7 @@ class Trainer:
                 lr=cfg.lr, weight_decay=cfg.weight_decay, max_grad_norm=cfg.max_grad_norm, optimizer=cfg.optimizer,
                 muon_lr=cfg.muon_lr, muon_momentum=cfg.muon_momentum, muon_weight_decay=cfg.muon_weight_decay,
                 muon_ns_steps=cfg.muon_ns_steps, muon_adjust_lr_fn=cfg.muon_adjust_lr_fn,
-                compute_dtype=compute_dtype, shard=cfg.fsdp_shard, broadcast_from_rank0=True,
+                compute_dtype=compute_dtype, shard=cfg.fsdp_shard or hasattr(self.model, "_sb200_shard_request"), broadcast_from_rank0=True,
             ),
             device=self.device,
         )

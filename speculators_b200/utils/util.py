@@ -8,6 +8,12 @@ import torch
 __all__ = ["empty_cache", "get_current_device", "get_device_name", "mem_get_info"]
 
 
+def is_npu_available() -> bool:
+    """Ascend NPUs are not a target of this package (sm_100a only): always False.  Kept so that
+    code written against the reference's helper keeps importing."""
+    return False
+
+
 def get_device_name() -> str:
     return "cuda" if torch.cuda.is_available() else "cpu"
 

@@ -139,3 +139,45 @@ def test_eagle_converter_helpers_and_legacy_model_name(tiny_verifier_dir, tiny_v
     assert built.d2t is None and not built.embed_tokens.weight.requires_grad
     with pytest.raises(ValueError, match="detached"):
         Eagle3Speculator(model.config, verifier_attachment_mode="full")
+
+
+def test_reference_module_paths_and_names_resolve():
+    """Names a user of the reference imports from its module paths exist here under the same
+    paths (aliases over this package's own implementations where the design differs)."""
+    import importlib
+
+    expected = {
+        "speculators_b200.models": ["Eagle3DraftModel", "DFlashSpeculatorConfig", "MTPDraftModel", "PEagleDraftModel", "DSparkDraftModel"],
+        "speculators_b200.models.eagle3": ["shift_batch"],
+        "speculators_b200.models.mtp": ["shift_batch_mtp"],
+        "speculators_b200.models.eagle3.model_definitions": ["Eagle3FirstLayerMixin", "LlamaDecoderEagle3FirstLayer", "Qwen3DecoderEagle3FirstLayer", "model_classes"],
+        "speculators_b200.models.dflash.model_definitions": ["Qwen3DFlashAttention", "Qwen3DFlashDecoderLayer", "apply_rotary_pos_emb"],
+        "speculators_b200.models.mtp.model_definitions": ["MTPLayerMixin", "mtp_model_classes", "resolve_model_type"],
+        "speculators_b200.models.attention": ["ALL_ATTENTION_FUNCTIONS"],
+        "speculators_b200.models.utils": ["DEFAULT_TARGET_LAYER_IDS_WARNING", "flatten_rope_parameters", "resolve_draft_intermediate_size"],
+        "speculators_b200.train.distributed": ["apply_fully_sharded", "get_dp_group", "get_sp_rank", "maybe_setup_distributed"],
+        "speculators_b200.train.graceful_shutdown": ["DEFAULT_SHUTDOWN_TIMEOUT", "TrainingInterruptedError"],
+        "speculators_b200.train.logger": ["TB_SUPPORTED_TYPES", "IsRank0Filter"],
+        "speculators_b200.convert": ["convert_model"],
+        "speculators_b200.convert.eagle": ["Eagle3Converter"],
+        "speculators_b200.convert.dflash": ["DFlashConverter"],
+        "speculators_b200.convert.mtp": ["MTPConverter", "MTP_EXACT_REMAP", "MTP_PREFIX_REMAP"],
+        "speculators_b200.convert.utils": ["download_checkpoint_from_hub", "ensure_checkpoint_is_local"],
+        "speculators_b200.data_generation.vllm_client": ["wait_for_lock", "wait_for_lock_async"],
+        "speculators_b200.utils.util": ["is_npu_available"],
+        "speculators_b200.__main__": ["app", "main"],
+    }
+    for module, names in expected.items():
+        mod = importlib.import_module(module)
+        for name in names:
+            assert hasattr(mod, name), f"{module}.{name}"
+    from speculators_b200.models.mtp.model_definitions import mtp_model_classes
+
+    assert {"qwen3", "qwen3_next"} <= set(mtp_model_classes) and mtp_model_classes["qwen3"].first_layer_class.__name__ == "MTPLayer"
+    from speculators_b200.models.dflash.model_definitions import apply_rotary_pos_emb
+    import torch
+
+    q, k = torch.randn(1, 2, 3, 8), torch.randn(1, 2, 5, 8)
+    cos, sin = torch.ones(1, 5, 8), torch.zeros(1, 5, 8)
+    rq, rk = apply_rotary_pos_emb(q, k, cos, sin)
+    assert torch.equal(rq, q) and torch.equal(rk, k)  # identity rotation
