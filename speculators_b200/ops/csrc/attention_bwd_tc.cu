@@ -69,22 +69,26 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 }
 
 // ---------------------------------------------------------------------------------- delta
-// delta[h, row] = sum_c dO[row, h, c] * O[row, h, c]: one warp per (row, head), 8 bytes per lane.
+// delta[h, row] = sum_c dO[row, h, c] * O[row, h, c]: 16 lanes per (row, head), 16 bytes per lane.
 __global__ void __launch_bounds__(256)
 attn_delta_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ out, float* __restrict__ delta, int Tq, int nh,
                   int64_t do_rs, int64_t o_rs) {
-  const int lane = threadIdx.x & 31;
+  const int lane = threadIdx.x & 31, sub = lane >> 4, l16 = lane & 15;
   const int64_t n = (int64_t)Tq * nh;
-  for (int64_t idx = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); idx < n; idx += (int64_t)gridDim.x * 8) {
-    const int row = (int)(idx / nh), h = (int)(idx % nh);
-    const uint2 a = *reinterpret_cast<const uint2*>(dout + (int64_t)row * do_rs + h * HD + lane * 4);
-    const uint2 b = *reinterpret_cast<const uint2*>(out + (int64_t)row * o_rs + h * HD + lane * 4);
-    const float2 a0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.x)), a1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.y));
-    const float2 b0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&b.x)), b1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&b.y));
-    float acc = a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y;
+  for (int64_t base = ((int64_t)blockIdx.x * 8 + (threadIdx.x >> 5)) * 2; base < n; base += (int64_t)gridDim.x * 16) {
+    const int64_t idx = base + sub;
+    float acc = 0.f;
+    if (idx < n) {
+      const int row = (int)(idx / nh), h = (int)(idx % nh);
+      float a[8], b[8];
+      unpack8(ld8(dout + (int64_t)row * do_rs + h * HD + l16 * 8), a);
+      unpack8(ld8(out + (int64_t)row * o_rs + h * HD + l16 * 8), b);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0) delta[(int64_t)h * Tq + row] = acc;
+      for (int i = 0; i < 8; ++i) acc = fmaf(a[i], b[i], acc);
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (l16 == 0 && idx < n) delta[(int64_t)(idx % nh) * Tq + idx / nh] = acc;
   }
 }
 
@@ -732,7 +736,7 @@ int launch_attn_bwd_tc(const AttnParams& p, int* tile_qmin, int* tile_qmax, int*
   count_launch(3);
   {
     const int64_t pairs = (int64_t)p.Tq * p.nh;
-    const int64_t blocks = (pairs + 7) / 8;
+    const int64_t blocks = (pairs + 15) / 16;
     attn_delta_kernel<<<(int)(blocks < 16 * kNumSM ? blocks : 16 * kNumSM), 256, 0, stream>>>(p.dout, p.out, p.delta, p.Tq, p.nh, p.do_rs, p.o_rs);
   }
   dim3 grid_q(p.nh, (p.Tq + BM - 1) / BM);
