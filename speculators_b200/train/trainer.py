@@ -100,6 +100,13 @@ class _StepTimer:
         else:
             self._marks[name] = time.perf_counter()
 
+    def snapshot(self) -> "_StepTimer":
+        """Frozen copy of this step's marks: its ``profile`` can be read after the timer has
+        been reset for the next step."""
+        frozen = _StepTimer(self.enabled, "cuda" if self.cuda else "cpu")
+        frozen._marks = dict(self._marks)
+        return frozen
+
     def _between(self, a: str, b: str) -> float:
         ma, mb = self._marks.get(a), self._marks.get(b)
         if ma is None or mb is None:
@@ -108,10 +115,11 @@ class _StepTimer:
             return float(ma.elapsed_time(mb))
         return (mb - ma) * 1000.0
 
-    def profile(self, num_tokens: int) -> dict[str, float] | None:
+    def profile(self, num_tokens: int, synchronize: bool = True) -> dict[str, float] | None:
+        """``synchronize=False``: the caller knows that every mark's event has completed."""
         if not self.enabled:
             return None
-        if self.cuda:
+        if self.cuda and synchronize:
             torch.cuda.current_stream().synchronize()
         fetch = self._between("start", "fetch")
         fwd = self._between("fetch", "fwd")
@@ -467,26 +475,10 @@ class Trainer:
             loss, metrics = self.train_step(batch, upcoming)
             lr_now = self._current_lr()
             if self.timer.enabled:
-                doc = batch.get("document_ids") if isinstance(batch, dict) else None
-                num_tokens = int((doc != -1).sum().item()) if doc is not None else 0
-                profile = self.timer.profile(num_tokens)
-                if self.device_type == "cuda":
-                    from speculators_b200.ops import check_gemm_status
-
-                    check_gemm_status()  # the profile read above already synchronised
-                if self.is_distributed and metrics:
-                    keys = list(metrics)
-                    stacked = torch.stack([metrics[k].float().reshape(()) for k in keys])
-                    dist.reduce(stacked, dst=0, op=dist.ReduceOp.SUM)
-                    values = dict(zip(keys, stacked.tolist()))
-                else:
-                    values = {k: float(v) for k, v in metrics.items()}
-                world = dist.get_world_size() if self.is_distributed else 1
-                metric_logger.info(
-                    {"train": normalize_counted_metrics(values, world), "profile": profile, "epoch": epoch,
-                     "lr": lr_now, "global_step": self.global_step},
-                    extra={"step": self.global_step},
-                )
+                # the record of the previous logged step is complete by now: emit it, then queue
+                # this step's (its values are copied to pinned memory behind the step)
+                self._flush_step_log()
+                self._queue_step_log(epoch, lr_now, metrics, batch)
             self.global_step += 1
             self.timer.reset(self.global_step % cfg.log_freq == 0)
             self.timer.mark("start")
@@ -496,7 +488,76 @@ class Trainer:
                 step_interval is not None and not cfg.save_best and local_step % step_interval == 0
                 and num_steps - local_step >= step_interval * MIN_STEP_PCT
             ):
+                self._flush_step_log()
                 self.maybe_save_checkpoint(epoch, local_step=local_step)
+        self._flush_step_log()
+
+    # ------------------------------------------------------------------ step logging
+    def _queue_step_log(self, epoch: int, lr_now: float, metrics: dict, batch) -> None:  # noqa: ANN001
+        """Start moving a step's metrics to the host without waiting for the step: one stacked
+        device tensor (summed over ranks when distributed), copied to pinned memory behind the
+        step on the training stream.  ``_flush_step_log`` reads it when the next logged step
+        comes around (or at the end of the epoch), so logging every step does not put a host
+        synchronisation between consecutive steps."""
+        keys = list(metrics)
+        entries = [metrics[k].detach().float().reshape(()) for k in keys]
+        doc = batch.get("document_ids") if isinstance(batch, dict) else None
+        num_tokens = 0
+        if doc is not None and doc.device.type == "cpu":
+            num_tokens = int((doc != -1).sum())
+        elif doc is not None:
+            entries.append((doc != -1).sum().float())  # counted on the device, read with the rest
+        has_count = doc is not None and doc.device.type != "cpu"
+        status = None
+        if self.device_type == "cuda":
+            from speculators_b200.ops import gemm_status
+
+            status = gemm_status(self.device).float().reshape(())
+        host = event = None
+        n_metrics = len(keys)
+        if entries or status is not None:
+            stacked = torch.stack(entries) if entries else torch.zeros(0, device=self.device)
+            if self.is_distributed and n_metrics:
+                head = stacked[:n_metrics].clone()
+                dist.reduce(head, dst=0, op=dist.ReduceOp.SUM)
+                stacked = torch.cat([head, stacked[n_metrics:]])
+            if status is not None:
+                stacked = torch.cat([stacked, status.reshape(1)])
+            host = torch.empty(stacked.shape, dtype=torch.float32, pin_memory=self.device_type == "cuda")
+            host.copy_(stacked, non_blocking=True)
+            if self.device_type == "cuda":
+                event = torch.cuda.Event()
+                event.record()
+        self._pending_step_log = {
+            "keys": keys, "host": host, "event": event, "timer": self.timer.snapshot(), "epoch": epoch, "lr": lr_now,
+            "global_step": self.global_step, "num_tokens": num_tokens, "has_count": has_count, "has_status": status is not None,
+        }
+
+    def _flush_step_log(self) -> None:
+        pending = getattr(self, "_pending_step_log", None)
+        if pending is None:
+            return
+        self._pending_step_log = None
+        if pending["event"] is not None:
+            pending["event"].synchronize()
+        raw = pending["host"].tolist() if pending["host"] is not None else []
+        keys = pending["keys"]
+        values = dict(zip(keys, raw[: len(keys)]))
+        rest = raw[len(keys):]
+        num_tokens = pending["num_tokens"]
+        if pending["has_count"]:
+            num_tokens = int(rest.pop(0))
+        if pending["has_status"] and rest and rest[-1] != 0:
+            from speculators_b200.ops import check_gemm_status
+
+            check_gemm_status()  # raises with the code of the wait that ran out
+        profile = pending["timer"].profile(num_tokens, synchronize=pending["event"] is None)  # the marks precede the copy's event
+        world = dist.get_world_size() if self.is_distributed else 1
+        metric_logger.info(
+            {"train": normalize_counted_metrics(values, world), "profile": profile, "epoch": pending["epoch"], "lr": pending["lr"],
+             "global_step": pending["global_step"]},
+            extra={"step": pending["global_step"]},
+        )
 
     def _maybe_val_sync(self, batch_index: int) -> None:
         if not self.is_distributed or _VAL_SYNC_INTERVAL <= 0:

@@ -205,3 +205,45 @@ def test_async_step_handles_on_cpu(tiny_verifier_dir, tiny_vocab_maps, tmp_path)
     handles = [b.train_step_async(batch) for _ in range(3)]
     # on the CPU every handle holds its own value only until the ring wraps; three fit
     assert [h.value() for h in handles] == pytest.approx(want, rel=1e-6)
+
+
+def test_step_records_are_emitted_in_order_one_step_late_and_flushed(tiny_verifier_dir, tiny_vocab_maps, tmp_path):
+    """Per-step logging does not wait for the step: the record of step n is emitted when step
+    n + 1 is queued, and the last one when the epoch ends; nothing is lost or reordered."""
+    import logging
+
+    import speculators_b200 as sb
+    from speculators_b200.train import Trainer, TrainerConfig
+    from speculators_b200.train import trainer as trainer_mod
+    from speculators_b200.train.synthetic import SyntheticLoader
+    from tests.conftest import make_tiny_batch, make_tiny_eagle3
+
+    records = []
+
+    class Capture(logging.Handler):
+        def emit(self, record):
+            if isinstance(record.msg, dict) and "train" in record.msg:
+                records.append(record.msg)
+
+    handler = Capture()
+    trainer_mod.metric_logger.addHandler(handler)
+    old_level = trainer_mod.metric_logger.level
+    trainer_mod.metric_logger.setLevel(logging.INFO)
+    try:
+        model = make_tiny_eagle3(tiny_verifier_dir, tiny_vocab_maps)
+        batch = make_tiny_batch(T=32)
+        kwargs, _ = sb.Eagle3DraftModel.get_trainer_kwargs(loss_fn="kl_div", ttt_steps=2, ttt_step_loss_decay=1.0)
+        trainer = Trainer(model, TrainerConfig(lr=1e-3, num_epochs=1, save_path=str(tmp_path), train_call_kwargs=kwargs, scheduler_type="none",
+                                               log_freq=1, device="cpu"), SyntheticLoader([batch], 4))
+        import os
+
+        os.environ["SB200_NO_TQDM"] = "1"
+        trainer.train_epoch(0)
+    finally:
+        trainer_mod.metric_logger.removeHandler(handler)
+        trainer_mod.metric_logger.setLevel(old_level)
+    assert [r["global_step"] for r in records] == [0, 1, 2, 3]
+    assert all("loss" in r["train"] and r["profile"] is not None and r["profile"]["step_ms"] >= 0 for r in records)
+    losses = [r["train"]["loss"] for r in records]
+    assert losses[-1] < losses[0]
+    assert getattr(trainer, "_pending_step_log", None) is None
