@@ -26,6 +26,7 @@ replicated mode through a Newton-Schulz update on the matrix views.
 
 from __future__ import annotations
 
+import contextlib
 import logging
 import math
 import os
@@ -33,7 +34,10 @@ from dataclasses import dataclass, field
 
 import torch
 import torch.distributed as dist
+
 from torch import nn
+
+from speculators_b200.utils.util import nvtx_range
 
 from speculators_b200 import ops
 
@@ -367,10 +371,11 @@ class TrainEngine:
             )
             return
         if self.distributed and self.world > 1:
-            if self.sharded:
-                dist.reduce_scatter_tensor(self.grad_shard, self.flat_g, op=dist.ReduceOp.SUM, group=self.group)
-            else:
-                dist.all_reduce(self.flat_g, op=dist.ReduceOp.SUM, group=self.group)
+            with nvtx_range("grad reduce"), self._comm_timed():
+                if self.sharded:
+                    dist.reduce_scatter_tensor(self.grad_shard, self.flat_g, op=dist.ReduceOp.SUM, group=self.group)
+                else:
+                    dist.all_reduce(self.flat_g, op=dist.ReduceOp.SUM, group=self.group)
         g = self.grad_shard if self.sharded else self.flat_g
         ops.sum_of_squares(g, self.norm_sq, accumulate=False)
         if self.sharded:
@@ -385,7 +390,41 @@ class TrainEngine:
         else:
             ops.adamw_step_(self.master, self.exp_avg, self.exp_avg_sq, g, w16, self.hyper, self.norm_sq)
         if self.sharded:
-            dist.all_gather_into_tensor(self.flat_w, self.flat_w[self.lo : self.hi], group=self.group)
+            with nvtx_range("weight all-gather"), self._comm_timed():
+                dist.all_gather_into_tensor(self.flat_w, self.flat_w[self.lo : self.hi], group=self.group)
+
+    # ------------------------------------------------------------------ exposed communication
+    def account_comm(self, enabled: bool) -> None:
+        """Time the collectives of the next ``apply`` calls with CUDA events (library-collective
+        path; they run on the training stream, so all of their time is exposed).  In the fused
+        peer-memory modes the transfers happen inside the optimizer kernel and are part of its
+        time.  Not usable while the step is being captured into a CUDA graph."""
+        self._comm_events = [] if enabled else None
+
+    @contextlib.contextmanager
+    def _comm_timed(self):
+        events = getattr(self, "_comm_events", None)
+        if events is None or not self.flat_g.is_cuda or torch.cuda.is_current_stream_capturing():
+            yield
+            return
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        yield
+        stop.record()
+        events.append((start, stop))
+
+    def exposed_comm_ms(self) -> float | None:
+        """Milliseconds the collectives timed since ``account_comm(True)`` took (synchronises on
+        their events) and clears the list; ``None`` when nothing was timed."""
+        events = getattr(self, "_comm_events", None)
+        if not events:
+            return None
+        total = 0.0
+        for start, stop in events:
+            stop.synchronize()
+            total += start.elapsed_time(stop)
+        self._comm_events = []
+        return total
 
     def step(self, lr: float | None = None) -> None:
         self.prepare_hyper(lr)

@@ -35,6 +35,7 @@ from speculators_b200.parallel.engine import EngineConfig, TrainEngine
 from speculators_b200.train.checkpointer import Checkpointer
 from speculators_b200.train.graceful_shutdown import with_graceful_shutdown
 from speculators_b200.train.schedule import LRSchedule, resolve_scheduler_steps
+from speculators_b200.utils.util import nvtx_range
 from speculators_b200.train.utils import normalize_counted_metrics
 
 root_logger = logging.getLogger("speculators")
@@ -400,16 +401,22 @@ class Trainer:
         on a side stream so that it overlaps this step's compute."""
         lr = self._current_lr()
         if self._graphed is not None:
-            loss, metrics = self._graphed.run(batch, lr, next_batch)
+            with nvtx_range("step (graph replay)"):
+                loss, metrics = self._graphed.run(batch, lr, next_batch)
         else:
-            dev_batch = {k: v.to(self.device, non_blocking=True) if isinstance(v, torch.Tensor) else v for k, v in batch.items()}
+            with nvtx_range("fetch"):
+                dev_batch = {k: v.to(self.device, non_blocking=True) if isinstance(v, torch.Tensor) else v for k, v in batch.items()}
             self.timer.mark("fetch")
-            self.engine.zero_grad()
-            _, loss, metrics = self.model(**dev_batch, **(self.config.train_call_kwargs or {}))
+            with nvtx_range("forward"):
+                self.engine.zero_grad()
+                _, loss, metrics = self.model(**dev_batch, **(self.config.train_call_kwargs or {}))
             self.timer.mark("fwd")
-            loss.backward()
+            with nvtx_range("backward"):
+                loss.backward()
             self.timer.mark("bwd")
-            self.engine.step(lr)
+            with nvtx_range("optimizer"):
+                self.engine.account_comm(self.timer.enabled)  # collectives of a logged step are timed
+                self.engine.step(lr)
         for sched in self.schedulers:
             sched.step()
         self.timer.mark("opt")
@@ -530,6 +537,7 @@ class Trainer:
                 event.record()
         self._pending_step_log = {
             "keys": keys, "host": host, "event": event, "timer": self.timer.snapshot(), "epoch": epoch, "lr": lr_now,
+            "engine": self.engine if self._graphed is None else None,
             "global_step": self.global_step, "num_tokens": num_tokens, "has_count": has_count, "has_status": status is not None,
         }
 
@@ -552,6 +560,11 @@ class Trainer:
 
             check_gemm_status()  # raises with the code of the wait that ran out
         profile = pending["timer"].profile(num_tokens, synchronize=pending["event"] is None)  # the marks precede the copy's event
+        if profile is not None and pending.get("engine") is not None:
+            comm = pending["engine"].exposed_comm_ms()  # library collectives of that step; None: none timed
+            if comm is not None:
+                profile["comm_ms"] = comm
+                profile["comm_frac"] = comm / profile["step_ms"] if profile["step_ms"] > 0 else 0.0
         world = dist.get_world_size() if self.is_distributed else 1
         metric_logger.info(
             {"train": normalize_counted_metrics(values, world), "profile": profile, "epoch": pending["epoch"], "lr": pending["lr"],

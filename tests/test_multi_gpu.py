@@ -51,6 +51,7 @@ def _engine_worker(rank, world, port, out_path):
                 grads.append((torch.randn(eng.total, generator=g, device="cuda") * 0.1 * (step + 1)).bfloat16())
             eng.flat_g.copy_(grads[rank])
             eng.mark_grads_written()
+            eng.account_comm(step == steps - 1)  # time the last step's collectives
             eng.step()
             if mode == "nccl":
                 gavg = sum(x.float() for x in grads) / world
@@ -62,6 +63,9 @@ def _engine_worker(rank, world, port, out_path):
                 ref_w.sub_(lr / (1 - 0.9**t) * ref_m / ((ref_v / (1 - 0.999**t)).sqrt() + 1e-8))
         torch.cuda.synchronize()
         eng.check_status()
+        comm_ms = eng.exposed_comm_ms()
+        # library collectives are timed; in the fused modes the transfers are inside the kernel
+        assert (comm_ms is not None and comm_ms > 0) if mode == "nccl" else comm_ms is None, (mode, comm_ms)
         results[mode] = (eng.flat_w.float().clone(), eng.master.clone(), eng.lo, eng.hi)
         eng.close()
     lo, hi = results["p2p"][2:]
