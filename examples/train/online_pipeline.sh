@@ -19,6 +19,7 @@ VLLM_GPUS="${VLLM_GPUS:-0,1}"             # the server and the trainer need sepa
 TRAIN_GPUS="${TRAIN_GPUS:-2,3}"
 NUM_TRAIN_GPUS="${NUM_TRAIN_GPUS:-2}"
 VLLM_ARGS="${VLLM_ARGS:---data-parallel-size 2 --gpu-memory-utilization 0.85}"
+LAUNCH_ARGS="${LAUNCH_ARGS:-}"            # flags of scripts/launch_vllm.py itself, e.g. --target-layer-ids 2 18 33
 DRAFT_VOCAB_SIZE="${DRAFT_VOCAB_SIZE:-32000}"
 MAX_SAMPLES="${MAX_SAMPLES:-5000}"
 SEQ_LENGTH="${SEQ_LENGTH:-8192}"
@@ -28,7 +29,7 @@ EXTRA_TRAIN_ARGS="${EXTRA_TRAIN_ARGS:-}"  # algorithm-specific flags
 
 echo "=== 1/4 starting the verifier server ($MODEL on GPUs $VLLM_GPUS) ==="
 # shellcheck disable=SC2086
-CUDA_VISIBLE_DEVICES="$VLLM_GPUS" python scripts/launch_vllm.py "$MODEL" -- --port "$VLLM_PORT" $VLLM_ARGS &
+CUDA_VISIBLE_DEVICES="$VLLM_GPUS" python scripts/launch_vllm.py "$MODEL" $LAUNCH_ARGS -- --port "$VLLM_PORT" $VLLM_ARGS &
 server=$!
 trap 'kill "$server" 2>/dev/null || true; wait "$server" 2>/dev/null || true' EXIT
 until curl -sf "http://localhost:${VLLM_PORT}/health" > /dev/null 2>&1; do
