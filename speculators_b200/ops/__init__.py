@@ -78,13 +78,22 @@ def gemm_status(device: torch.device) -> torch.Tensor:
     return _GEMM_STATUS[idx]
 
 
+_WAIT_CODES = {
+    1: "GEMM producer", 2: "GEMM MMA issuer", 3: "GEMM epilogue",
+    31: "attention forward producer", 32: "attention forward MMA issuer", 33: "attention forward softmax",
+    41: "attention dQ producer", 42: "attention dQ MMA issuer", 43: "attention dQ element-wise warps",
+    44: "attention dK/dV producer", 45: "attention dK/dV MMA issuer", 46: "attention dK/dV element-wise warps",
+}
+
+
 def check_gemm_status() -> None:
-    """Raise if a tcgen05 GEMM launched by this process reported a wait that ran out."""
+    """Raise if a tcgen05 kernel (GEMM or attention) launched by this process reported a wait
+    that ran out; the kernels share one status word per device."""
     for idx, word in _GEMM_STATUS.items():
         code = int(word.item())
         if code:
             word.zero_()
-            raise RuntimeError(f"tcgen05 GEMM on cuda:{idx} gave up waiting (code {code}: 1 producer, 2 MMA issuer, 3 epilogue)")
+            raise RuntimeError(f"a tcgen05 kernel on cuda:{idx} gave up waiting (code {code}: {_WAIT_CODES.get(code, 'unknown wait')})")
 
 
 def _forward_gemm(x2: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None) -> torch.Tensor:

@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import hashlib
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -127,5 +128,66 @@ def _build_into(BUILD: Path, LIB: Path, defines: list[str], tag: str, verbose: b
     return LIB
 
 
+_ENTRY = re.compile(r"Compiling entry function '([^']+)'")
+_SPILL = re.compile(r"(\d+) bytes stack frame, (\d+) bytes spill stores, (\d+) bytes spill loads")
+_USED = re.compile(r"Used (\d+) registers")
+_SMEM = re.compile(r"(\d+) bytes smem")
+
+
+def parse_ptxas_info(text: str) -> list[dict]:
+    """Rows ``{kernel, registers, smem, stack, spill_stores, spill_loads}`` from the text
+    ``nvcc -Xptxas -v`` writes to stderr (one row per entry function)."""
+    rows: list[dict] = []
+    current: dict | None = None
+    for line in text.splitlines():
+        if m := _ENTRY.search(line):
+            current = {"kernel": m.group(1), "registers": 0, "smem": 0, "stack": 0, "spill_stores": 0, "spill_loads": 0}
+            rows.append(current)
+        elif current is not None and (m := _SPILL.search(line)):
+            current["stack"], current["spill_stores"], current["spill_loads"] = (int(g) for g in m.groups())
+        elif current is not None and (m := _USED.search(line)):
+            current["registers"] = int(m.group(1))
+            if sm := _SMEM.search(line):
+                current["smem"] = int(sm.group(1))
+    return rows
+
+
+def _demangle(names: list[str]) -> list[str]:
+    try:
+        proc = subprocess.run(["c++filt", "-p"], input="\n".join(names), capture_output=True, text=True, check=True)
+        out = proc.stdout.splitlines()
+        return out if len(out) == len(names) else names
+    except (OSError, subprocess.CalledProcessError):
+        return names
+
+
+def resource_usage(only: list[str] | None = None) -> list[dict]:
+    """Compile the CUDA sources with ``-Xptxas -v`` into a scratch folder and return registers,
+    static shared memory and spills of every kernel (``only``: file stems to restrict to)."""
+    scratch = BUILD / "resources"
+    scratch.mkdir(parents=True, exist_ok=True)
+    cu, _ = _sources()
+    nvcc = _nvcc()
+    rows: list[dict] = []
+    for src in cu:
+        if only and src.stem not in only:
+            continue
+        proc = subprocess.run([nvcc, *NVCC_FLAGS, "-Xptxas", "-v", "-I", str(CSRC), "-c", str(src), "-o", str(scratch / (src.stem + ".o"))],
+                              capture_output=True, text=True)
+        if proc.returncode != 0:
+            raise RuntimeError(f"nvcc failed on {src.name}\n{proc.stderr}")
+        found = parse_ptxas_info(proc.stderr)
+        for row, name in zip(found, _demangle([r["kernel"] for r in found])):
+            row["kernel"], row["file"] = name, src.name
+        rows.extend(found)
+    return rows
+
+
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose=True, checked=True if "--checked" in sys.argv else None))
+    if "--resources" in sys.argv:
+        stems = [a for a in sys.argv[1:] if not a.startswith("--")]
+        print(f"{'file':<22} {'regs':>4} {'smem':>6} {'stack':>5} {'spill st/ld':>11}  kernel")
+        for r in resource_usage(stems or None):
+            print(f"{r['file']:<22} {r['registers']:>4} {r['smem']:>6} {r['stack']:>5} {r['spill_stores']:>5}/{r['spill_loads']:<5}  {r['kernel'][:110]}")
+    else:
+        print(build(force="--force" in sys.argv, verbose=True, checked=True if "--checked" in sys.argv else None))

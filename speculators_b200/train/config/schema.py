@@ -126,27 +126,27 @@ class OptimizerArgs(_Group):
     lr: float = Field(default=1e-4, description="AdamW learning rate.")
     weight_decay: float = Field(default=0.01, description="AdamW weight decay.")
     muon_lr: float | None = Field(default=None, description="Muon learning rate (default: 10 * lr).")
-    muon_momentum: float = Field(default=0.95)
-    muon_weight_decay: float = Field(default=0.1)
+    muon_momentum: float = Field(default=0.95, description="Muon momentum (Nesterov).")
+    muon_weight_decay: float = Field(default=0.1, description="Decoupled weight decay of the Muon group.")
     muon_ns_steps: int = Field(default=5, description="Newton-Schulz iterations.")
-    muon_adjust_lr_fn: Literal["original", "match_rms_adamw"] = Field(default="match_rms_adamw")
+    muon_adjust_lr_fn: Literal["original", "match_rms_adamw"] = Field(default="match_rms_adamw", description="How the Muon step is scaled with the matrix shape.")
 
 
 class SchedulerArgs(_Group):
-    scheduler_type: Literal["linear", "cosine", "none"] = Field(default="linear")
-    scheduler_warmup_steps: int | None = Field(default=None)
-    scheduler_warmup_ratio: float | None = Field(default=None)
-    scheduler_total_steps: int | None = Field(default=None)
-    scheduler_num_cosine_cycles: float = Field(default=0.5)
+    scheduler_type: Literal["linear", "cosine", "none"] = Field(default="linear", description="Learning-rate schedule after warm-up.")
+    scheduler_warmup_steps: int | None = Field(default=None, description="Linear warm-up steps (wins over the ratio).")
+    scheduler_warmup_ratio: float | None = Field(default=None, description="Warm-up as a fraction of the total steps, in [0, 1].")
+    scheduler_total_steps: int | None = Field(default=None, description="Steps the schedule spans (default: epochs * batches per epoch).")
+    scheduler_num_cosine_cycles: float = Field(default=0.5, description="Cosine periods over the schedule (0.5: one descent to zero).")
 
 
 class TrainerArgs(_Group):
-    epochs: int = Field(default=20)
+    epochs: int = Field(default=20, description="Passes over the training split.")
     checkpoint_freq: float = Field(default=1.0, description=">= 1: every N epochs; < 1: fraction of an epoch.")
     save_best: bool = Field(default=False, description="Keep only the best validation epoch.")
     no_resume_from_checkpoint: bool = Field(default=False, description="Ignore existing checkpoints in --save-path.")
     log_freq: int = Field(default=1, description="Log metrics every N steps.")
-    save_path: str = Field(default="./output/checkpoints")
+    save_path: str = Field(default="./output/checkpoints", description="Checkpoint directory (also where a run resumes from).")
     fsdp_shard: bool = Field(default=False, description="Shard optimizer state and master weights across ranks.")
     max_steps: int | None = Field(default=None, gt=0, description="Stop after this many optimizer steps (a positive integer); default: run all epochs.")
 
@@ -162,8 +162,8 @@ class TrainerArgs(_Group):
 
 class LoggingArgs(_Group):
     logger: str = Field(default="", description="Comma-separated metric backends: tensorboard, wandb, trackio, mlflow.")
-    log_dir: str = Field(default="./logs")
-    run_name: str | None = Field(default=None)
+    log_dir: str = Field(default="./logs", description="Directory of the metric backends' files.")
+    run_name: str | None = Field(default=None, description="Run name; {time}, {utc_time}, {rank}, {local_rank} are substituted.")
 
 
 class DFlashArgs(_Group):
@@ -209,8 +209,8 @@ class TrainConfig(BaseModel):
 
     speculator_type: str = Field(default="eagle3", description="eagle3, dflash, dspark, peagle or mtp.")
     dry_run: bool = Field(default=False, description="Build the draft, save it to --save-path and exit before training.")
-    seed: int = Field(default=42)
-    deterministic_cuda: bool = Field(default=False)
+    seed: int = Field(default=42, description="Seed of Python, NumPy and torch generators.")
+    deterministic_cuda: bool = Field(default=False, description="Ask torch for deterministic algorithms (slower).")
 
     verifier: VerifierArgs = Field(default_factory=VerifierArgs)
     draft: DraftArgs = Field(default_factory=DraftArgs)

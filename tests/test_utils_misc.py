@@ -145,3 +145,23 @@ def test_provenance_helpers(tmp_path):
     assert provenance.find_repo_root(repo / "a.txt") == repo
     provenance.atomic_write(repo / "sub" / "f.txt", "hello")
     assert (repo / "sub" / "f.txt").read_text() == "hello" and [p.name for p in (repo / "sub").iterdir()] == ["f.txt"]
+
+
+def test_ptxas_info_parser():
+    from speculators_b200.ops._build import parse_ptxas_info
+
+    text = """ptxas info    : 0 bytes gmem
+ptxas info    : Compiling entry function '_ZN5sb2001aEv' for 'sm_100a'
+ptxas info    : Function properties for _ZN5sb2001aEv
+    48 bytes stack frame, 44 bytes spill stores, 40 bytes spill loads
+ptxas info    : Used 168 registers, used 10 barriers, 48 bytes cumulative stack size, 1024 bytes smem
+ptxas info    : Compile time = 10.0 ms
+ptxas info    : Compiling entry function '_ZN5sb2001bEv' for 'sm_100a'
+ptxas info    : Function properties for _ZN5sb2001bEv
+    0 bytes stack frame, 0 bytes spill stores, 0 bytes spill loads
+ptxas info    : Used 40 registers, used 1 barriers, 264 bytes smem
+"""
+    rows = parse_ptxas_info(text)
+    assert [r["kernel"] for r in rows] == ["_ZN5sb2001aEv", "_ZN5sb2001bEv"]
+    assert (rows[0]["registers"], rows[0]["stack"], rows[0]["spill_stores"], rows[0]["spill_loads"], rows[0]["smem"]) == (168, 48, 44, 40, 1024)
+    assert (rows[1]["registers"], rows[1]["smem"], rows[1]["spill_stores"]) == (40, 264, 0)
