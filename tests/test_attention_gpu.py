@@ -52,7 +52,7 @@ def _run(T, nh, nkv, hd, step, window, pattern, fused_buffer=False, seed=0):
 
 
 @pytest.mark.parametrize("hd", [64, 128])
-@pytest.mark.parametrize("T", [64, 200, 257])
+@pytest.mark.parametrize("T", [64, 127, 128, 129, 200, 257])
 def test_causal_single_document(T, hd):
     _run(T, 4, 2, hd, step=0, window=None, pattern="single")
 
