@@ -26,8 +26,14 @@ import argparse
 import sys
 from datetime import datetime
 
-from speculators_b200.train.benchmark import compare_benchmarks, run_benchmark
+from speculators_b200.train.benchmark import (  # noqa: F401  (re-exported: the harness is importable as this script)
+    ProfileCapture, collect_provenance, compare_benchmarks, compute_statistics, create_synthetic_batch, run_benchmark,
+)
+from speculators_b200.train.synthetic import SyntheticLoader
 from speculators_b200.train.config import TrainConfig
+
+_MetricCapture = ProfileCapture  # the reference script's private names for the same two helpers
+_SyntheticLoader = SyntheticLoader
 
 
 def build_parser() -> argparse.ArgumentParser:

@@ -29,6 +29,12 @@ from speculators_b200.data_generation import regeneration as rg
 from speculators_b200.data_generation.configs import DATASET_CONFIGS
 from speculators_b200.data_generation.vllm_client import DEFAULT_MAX_RETRIES, InvalidResponseError, with_retries
 
+# the helpers live in the package; they are reachable from the script module too, under the
+# names the reference script gives them
+extract_conversation, extract_tools, load_seen = rg.extract_conversation, rg.extract_tools, rg.load_seen
+regenerate_conversation, build_boundary_sample = rg.regenerate_conversation, rg.boundary_sample
+_primary_identifier, prepare_row = rg.primary_identifier, rg.prepare_row
+
 logger = logging.getLogger(__name__)
 RETRYABLE_HTTP_STATUSES = frozenset({408, 409, 425, 429})
 
@@ -36,7 +42,7 @@ RETRYABLE_HTTP_STATUSES = frozenset({408, 409, 425, 429})
 def _dataset_choice(name: str) -> str:
     if name in rg.MULTIMODAL_DATASETS:
         raise argparse.ArgumentTypeError(
-            f"{name} is multimodal: regeneration is text-only. Generate its responses elsewhere and convert them with prepare_data.py."
+            f"{name} is multimodal and regeneration does not support images (it is text-only). Generate its responses elsewhere and convert them with prepare_data.py."
         )
     return name
 

@@ -289,6 +289,14 @@ def preprocess_batch(
     return sink.out
 
 
+def _preprocess_batch(examples: dict, is_multimodal: bool, render_endpoint: str | None, max_length: int,
+                      minimum_valid_tokens: int | None = None) -> dict[str, list]:
+    """``preprocess_batch`` with the renderer given as a server URL
+    (src/speculators/data_generation/preprocessing.py:441-447 takes the endpoint)."""
+    render = EndpointRenderer(render_endpoint) if render_endpoint is not None else None
+    return preprocess_batch(examples, is_multimodal, render, max_length, minimum_valid_tokens)
+
+
 # ----------------------------------------------------------------------------- datasets
 def _is_multimodal_processor(processor) -> bool:
     try:

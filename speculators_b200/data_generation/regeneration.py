@@ -30,7 +30,7 @@ from typing import Any
 from speculators_b200.data_generation.configs import DATASET_CONFIGS, DatasetConfig
 
 __all__ = [
-    "MULTIMODAL_DATASETS", "REGEN_DATASETS", "RegenStats", "boundary_sample", "extract_conversation", "extract_tools",
+    "MULTIMODAL_DATASETS", "REGEN_DATASETS", "RegenStats", "boundary_sample", "extract_conversation", "extract_tools", "prepare_row",
     "load_seen", "prepare_item", "primary_identifier", "regenerate_conversation", "run_regeneration", "sanitize_filename",
     "tool_result_names",
 ]
@@ -113,14 +113,23 @@ def primary_identifier(row: dict) -> str:
     return "hash_" + hashlib.sha256(blob.encode("utf-8")).hexdigest()
 
 
-def prepare_item(row: dict, config: DatasetConfig, idx: int) -> dict | None:
-    """Work item for one dataset row, or ``None`` to skip it (filtered / nothing to ask)."""
+def prepare_row(row: dict, config: DatasetConfig) -> tuple[dict, list[dict], list] | None:
+    """``(normalised row, turns to replay, cached tool results)`` of one dataset row, or ``None``
+    when the preset's filter drops it.  The preset's ``normalize_fn`` output is laid over the
+    raw row (as ``datasets.map`` merges columns), so raw fall-back fields stay readable."""
     if config.filter_fn is not None and not config.filter_fn(row):
         return None
     norm = {**row, **config.normalize_fn(row)} if config.normalize_fn else row
     turns, results = extract_conversation(norm, config.prompt_field)
-    if not turns:
+    return norm, turns, results
+
+
+def prepare_item(row: dict, config: DatasetConfig, idx: int) -> dict | None:
+    """Work item for one dataset row, or ``None`` to skip it (filtered / nothing to ask)."""
+    prepared = prepare_row(row, config)
+    if prepared is None or not prepared[1]:
         return None
+    norm, turns, results = prepared
     return {"idx": idx, "primary_id": primary_identifier(row), "turns": turns, "tools": extract_tools(norm), "tool_results": results}
 
 

@@ -20,7 +20,10 @@ import torch
 
 from speculators_b200.ops import AttnSpec
 
-__all__ = ["causal_document_interval", "create_combined_mask_mod", "dense_ttt_mask", "extend_dense_mask_for_draft_tokens", "ttt_attn_spec"]
+__all__ = [
+    "block_mask_to_dense_attention_mask", "causal_document_interval", "create_combined_mask_mod", "dense_ttt_mask",
+    "extend_dense_mask_for_draft_tokens", "extend_mask_for_draft_tokens", "ttt_attn_spec",
+]
 
 
 def causal_document_interval(document_ids: torch.Tensor, sliding_window: int | None = None):
@@ -97,3 +100,51 @@ def extend_dense_mask_for_draft_tokens(mask: torch.Tensor, total_seq_len: int) -
         block = torch.zeros(total_seq_len, total_seq_len, dtype=mask.dtype, device=mask.device).masked_fill(~eye, float("-inf"))
     block = block.reshape((1,) * (mask.dim() - 2) + block.shape).expand(*mask.shape[:-2], total_seq_len, total_seq_len)
     return torch.cat([mask, block], dim=-1)
+
+
+# ---- interoperability with torch's flex-attention block masks ---------------------------------
+# The package's own attention does not use block masks; these two helpers exist for code that
+# drives ``torch.nn.attention.flex_attention`` with the same training-time-test pattern
+# (src/speculators/models/eagle3/attention.py:37-112, :135-148).
+def extend_mask_for_draft_tokens(block_mask):
+    """A ``BlockMask`` whose key axis is one training-time-test pass longer: query block ``i``
+    additionally sees the new key block ``i`` (the ``mask_mod`` decides which elements inside;
+    with ``create_combined_mask_mod`` only the diagonal).  Requires square blocks and a query
+    axis of the original sequence length; the ``mask_mod`` is kept."""
+    from torch.nn.attention.flex_attention import BlockMask
+
+    q_block, kv_block = block_mask.BLOCK_SIZE
+    if q_block != kv_block:
+        raise ValueError(f"square blocks expected, got {block_mask.BLOCK_SIZE}")
+    q_len, kv_len = block_mask.seq_lengths
+    counts, indices = block_mask.kv_num_blocks, block_mask.kv_indices
+    n_q_blocks = counts.shape[-1]
+    n_kv_blocks = -(-kv_len // kv_block)
+    width = n_kv_blocks + n_q_blocks
+
+    def widen(table):
+        grown = table.new_full((*table.shape[:-1], width), -1)
+        grown[..., : table.shape[-1]] = table
+        return grown
+
+    new_indices = widen(indices)
+    appended = torch.arange(n_kv_blocks, width, device=indices.device, dtype=indices.dtype).expand(counts.shape)
+    new_indices.scatter_(-1, counts.long().unsqueeze(-1), appended.unsqueeze(-1))  # first free column of each row
+    full_counts, full_indices = block_mask.full_kv_num_blocks, block_mask.full_kv_indices
+    return BlockMask.from_kv_blocks(
+        kv_num_blocks=counts + 1, kv_indices=new_indices,
+        full_kv_num_blocks=full_counts, full_kv_indices=None if full_indices is None else widen(full_indices),
+        BLOCK_SIZE=block_mask.BLOCK_SIZE, mask_mod=block_mask.mask_mod, seq_lengths=(q_len, kv_len + n_q_blocks * kv_block),
+    )
+
+
+def block_mask_to_dense_attention_mask(block_mask, device: torch.device, dtype: torch.dtype) -> torch.Tensor:
+    """Element mask ``[B, H, q_len, kv_len]`` of a ``BlockMask`` (1 = attend) from its
+    ``mask_mod``, evaluated for all pairs at once."""
+    batch, heads, q_len, kv_len = block_mask.shape
+    b = torch.arange(batch, device=device).view(-1, 1, 1, 1)
+    h = torch.arange(heads, device=device).view(1, -1, 1, 1)
+    q = torch.arange(q_len, device=device).view(1, 1, -1, 1)
+    kv = torch.arange(kv_len, device=device).view(1, 1, 1, -1)
+    allowed = block_mask.mask_mod(b, h, q, kv)
+    return torch.as_tensor(allowed, device=device).expand(batch, heads, q_len, kv_len).to(dtype)

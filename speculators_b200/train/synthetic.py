@@ -65,7 +65,9 @@ class SyntheticLoader:
         def set_epoch(self, _epoch: int) -> None:
             pass
 
-    def __init__(self, batches: list[dict], num_steps: int):
+    def __init__(self, batches: list[dict] | dict, num_steps: int):
+        if isinstance(batches, dict):  # one batch, repeated
+            batches = [batches]
         self.batches, self.num_steps = batches, num_steps
         self.batch_sampler = self._Sampler()
 

@@ -35,6 +35,7 @@ from speculators_b200.parallel.engine import EngineConfig, TrainEngine
 from speculators_b200.train.checkpointer import Checkpointer
 from speculators_b200.train.graceful_shutdown import with_graceful_shutdown
 from speculators_b200.train.schedule import LRSchedule, resolve_scheduler_steps
+from speculators_b200.train.schedule import resolve_scheduler_steps as _resolve_scheduler_steps  # noqa: F401  (the reference's name)
 from speculators_b200.utils.util import nvtx_range
 from speculators_b200.train.utils import normalize_counted_metrics
 

@@ -103,3 +103,8 @@ def load_model_layers(layer_names: list[str], model_path: str | Path) -> dict[st
             for name, key in pairs:
                 out[name] = fh.get_tensor(key)
     return out
+
+
+# the reference's private names for the two lookups above (its tests and some downstream code use them)
+_resolve_key = _match
+_resolve_file = resolve_checkpoint_file

@@ -166,3 +166,32 @@ def test_component_table_and_partial_rotary_oracle():
     q = x.view(T, heads, hd).transpose(0, 1).unsqueeze(0)  # [1, heads, T, hd]
     ref, _ = partial_neox_apply_rotary_pos_emb(q, q, cos_full.unsqueeze(0), sin_full.unsqueeze(0))
     torch.testing.assert_close(ours, ref[0].transpose(0, 1), atol=1e-5, rtol=1e-5)
+
+
+def test_block_mask_interop_helpers():
+    """Extending a flex-attention block mask by one pass adds the diagonal key block per
+    query block, twice in a row, and the dense conversion equals the element mask."""
+    from torch.nn.attention.flex_attention import create_block_mask, create_mask
+
+    from speculators_b200.models.eagle3.attention import (
+        block_mask_to_dense_attention_mask, create_combined_mask_mod, extend_mask_for_draft_tokens,
+    )
+
+    T, B = 16, 4
+    doc = torch.tensor([0] * 6 + [1] * 7 + [-1] * 3)
+    mod = create_combined_mask_mod(doc, T)
+    bm = create_block_mask(mod, None, None, T, T, device="cpu", BLOCK_SIZE=B)
+    base = bm.to_dense()[0, 0].bool()
+    grown = bm
+    for step in (1, 2):
+        grown = extend_mask_for_draft_tokens(grown)
+        assert grown.seq_lengths == (T, T * (step + 1))
+        blocks = grown.to_dense()[0, 0].bool()
+        assert blocks.shape == (T // B, (T // B) * (step + 1))
+        assert torch.equal(blocks[:, : T // B], base)
+        for p in range(1, step + 1):
+            assert torch.equal(blocks[:, p * (T // B): (p + 1) * (T // B)], torch.eye(T // B, dtype=torch.bool))
+        dense = block_mask_to_dense_attention_mask(grown, torch.device("cpu"), torch.bool)
+        want = create_mask(mod, None, None, T, T * (step + 1), device="cpu")
+        assert torch.equal(dense, want)
+    assert grown.mask_mod is bm.mask_mod
