@@ -130,7 +130,7 @@ class SpeculatorModelConfig(PydanticClassRegistryMixin):
         merged = {**config_dict, **kwargs}
         if "speculators_model_type" not in merged:
             raise ValueError(
-                "The config dictionary must contain the 'speculators_model_type' field; without it "
+                "The config dictionary must contain the 'speculators_model_type' field - without it "
                 "this is not a speculators checkpoint (external checkpoints go through speculators_b200.convert)"
             )
         merged.pop("model_type", None)

@@ -86,6 +86,7 @@ def _collect_backend_args():
 
 
 _BACKEND_ACTIONS, BACKEND_DESTS = _collect_backend_args()
+_BACKEND_DESTS = BACKEND_DESTS  # the reference's name
 
 
 def _backfill_backend_defaults(backend: str, merged: dict[str, Any]) -> None:

@@ -358,3 +358,19 @@ def test_generation_request_carries_the_transfer_parameters():
     assert kind == "completions" and kwargs["extra_body"]["kv_transfer_params"] == {"ring_rank": 3}
     kind, kwargs = _request("m", {"input_ids": [1], "messages": [{"role": "user", "content": "hi"}]}, None)
     assert kind == "chat" and "kv_transfer_params" not in kwargs["extra_body"] and kwargs["extra_body"]["return_token_ids"] is True
+
+
+def test_top_level_hs_connectors_import_paths():
+    """The stand-alone package name of the transports resolves to the same objects."""
+    import hs_connectors
+    from hs_connectors import FileTransfer, HiddenStatesBackend
+    from hs_connectors.mooncake_store import MooncakeHiddenStatesStore
+
+    import speculators_b200.hs_connectors as own
+
+    assert HiddenStatesBackend is own.HiddenStatesBackend and FileTransfer is own.FileTransfer
+    assert MooncakeHiddenStatesStore is own.store.MooncakeHiddenStatesStore
+    import hs_connectors.mooncake_hidden_states_connector as connector
+
+    assert connector is own.mooncake_hidden_states_connector
+    assert {"file", "mooncake", "nvlink"} <= set(hs_connectors.HiddenStatesBackend.registry)
