@@ -361,16 +361,21 @@ def test_generation_request_carries_the_transfer_parameters():
 
 
 def test_top_level_hs_connectors_import_paths():
-    """The stand-alone package name of the transports resolves to the same objects."""
-    import hs_connectors
-    from hs_connectors import FileTransfer, HiddenStatesBackend
-    from hs_connectors.mooncake_store import MooncakeHiddenStatesStore
+    """The stand-alone package name of the transports resolves to the same objects (checked in a
+    fresh interpreter: other tests import the reference's own ``hs_connectors`` for comparisons)."""
+    import subprocess
 
-    import speculators_b200.hs_connectors as own
-
-    assert HiddenStatesBackend is own.HiddenStatesBackend and FileTransfer is own.FileTransfer
-    assert MooncakeHiddenStatesStore is own.store.MooncakeHiddenStatesStore
-    import hs_connectors.mooncake_hidden_states_connector as connector
-
-    assert connector is own.mooncake_hidden_states_connector
-    assert {"file", "mooncake", "nvlink"} <= set(hs_connectors.HiddenStatesBackend.registry)
+    code = """
+import hs_connectors
+from hs_connectors import FileTransfer, HiddenStatesBackend
+from hs_connectors.mooncake_store import MooncakeHiddenStatesStore
+import hs_connectors.mooncake_hidden_states_connector as connector
+import speculators_b200.hs_connectors as own
+assert HiddenStatesBackend is own.HiddenStatesBackend and FileTransfer is own.FileTransfer
+assert MooncakeHiddenStatesStore is own.store.MooncakeHiddenStatesStore
+assert connector is own.mooncake_hidden_states_connector
+assert {"file", "mooncake", "nvlink"} <= set(hs_connectors.HiddenStatesBackend.registry)
+print("ok")
+"""
+    proc = subprocess.run([sys.executable, "-c", code], cwd=ROOT, capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0 and proc.stdout.strip().endswith("ok"), proc.stderr[-2000:]
