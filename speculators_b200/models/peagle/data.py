@@ -113,7 +113,9 @@ def generate_cod_sample_indices_fixed(
         if filter_position_zero:
             ok = ok & (nxt != 0)
         nxt_pool = torch.zeros(T + 1, dtype=torch.bool, device=device)
-        nxt_pool[torch.where(ok, nxt, torch.full_like(nxt, T))] = True
+        # index_fill_ takes the value as a kernel argument; ``pool[idx] = True`` would copy a host scalar,
+        # which a CUDA graph capture refuses
+        nxt_pool.index_fill_(0, torch.where(ok, nxt, torch.full_like(nxt, T)), True)
         pool = nxt_pool[:T]
         anchors.append(torch.where(real, picked - d, torch.zeros_like(picked)))
         depths.append(torch.full((cap,), d, dtype=torch.long, device=device))

@@ -208,12 +208,14 @@ class _RMSNormFn(torch.autograd.Function):
         x2 = x.reshape(-1, H)
         if x2.stride(-1) != 1:
             x2 = x2.contiguous()
-        y = torch.empty((x2.shape[0], H), dtype=x.dtype, device=x.device)
+        # allocated in the caller's shape and returned as it is: a view made in here could not be
+        # modified in place afterwards (the rotary kernel does that to normalised q / k heads)
+        y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
         rstd = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device)
-        native().rmsnorm_fwd(x2, weight, None, y, rstd, eps)
+        native().rmsnorm_fwd(x2, weight, None, y.view(-1, H), rstd, eps)
         ctx.save_for_backward(x2, weight, rstd)
         ctx.shape = x.shape
-        return y.view(x.shape)
+        return y
 
     @staticmethod
     def backward(ctx, dy):
@@ -358,6 +360,10 @@ def rope_(x, positions, cos_t, sin_t, heads: int, hd: int, rot: int):
     (``[T, >= heads*hd]``), rotating the first ``rot`` channels of each head.
     In place on CUDA; returns the rotated tensor."""
     if _use_native(x):
+        if x._is_view() or x.stride(-1) != 1:  # noqa: SLF001
+            # rotating a view in place would rewrite its base's history (and is refused outright for
+            # views that custom functions hand out): work on a private copy instead
+            x = x.clone(memory_format=torch.contiguous_format)
         return _RopeFn.apply(x, positions, cos_t, sin_t, heads, hd, rot)
     return _rope_ref(x, positions, cos_t, sin_t, heads, hd, rot, 1.0)
 
