@@ -50,6 +50,9 @@ class MTPDraftModel(DraftVocabMixin, SpeculatorModel):
             raise NotImplementedError("Vocab reduction is not supported for MTP speculators")
         tc = config.transformer_layer_config
         self.mtp_layers = nn.ModuleList([build_mtp_layer(tc, 0)])
+        # expert routing sizes its buffers from counts read on the host (bincount, exchange plans):
+        # a layer with experts runs eagerly, a dense one as a CUDA graph
+        self.cuda_graph_safe = type(self.mtp_layers[0]).__name__ != "MoEMTPLayer"
         self.rotary_emb = RotaryTable(tc)
 
     @property

@@ -288,7 +288,10 @@ loss_bwd_kernel(const __nv_bfloat16* __restrict__ logits, const __nv_bfloat16* _
       ((V & 7) == 0) && ((ld_logits & 7) == 0) && ((ld_targets & 7) == 0) && ((ld_dlogits & 7) == 0);
   const int nvec = vec_ok ? (V >> 3) : 0;
   const float go = r < rows ? grad_out[r] : 0.f;
-  if (go == 0.f) {
+  // a row the forward skipped (inactive) has all-zero statistics; its sum-exp would be >= 1
+  // otherwise.  Such a row gets no gradient whatever the upstream value is.
+  const bool skipped = r < rows && stats[(int64_t)rows + r] == 0.f;
+  if (go == 0.f || skipped) {
     bf16x8 z;
 #pragma unroll
     for (int i = 0; i < 4; ++i) z.v[i] = __floats2bfloat162_rn(0.f, 0.f);

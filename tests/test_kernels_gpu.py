@@ -178,3 +178,23 @@ def test_sum_of_squares_and_adamw_match_torch():
         opt.step()
     _close(p, ref.detach(), atol=1e-5, rtol=1e-4)
     _close(w16, p, atol=2e-2)
+
+
+@pytest.mark.parametrize("T,V", [(33, 1000), (20, 32000), (7, 1003)])
+def test_token_cross_entropy_fwd_bwd(T, V):
+    """Cross-entropy against integer labels (the MTP loss), with rows switched off by ``keep``."""
+    torch.manual_seed(0)
+    x = (torch.randn(T, V, device=DEV) * 3.0).to(torch.bfloat16).requires_grad_()
+    labels = torch.randint(0, V, (T,), device=DEV)
+    keep = torch.rand(T, device=DEV) > 0.3
+    w = torch.rand(T, device=DEV)
+    loss = ops.token_cross_entropy(x, labels, keep)
+    (loss * w).sum().backward()
+    xf = x.detach().float().requires_grad_()
+    ref = torch.nn.functional.cross_entropy(xf, labels, reduction="none")
+    ref = torch.where(keep, ref, torch.zeros_like(ref))
+    (ref * w).sum().backward()
+    _close(loss, ref, atol=2e-3, rtol=2e-3)
+    assert (loss[~keep] == 0).all()
+    _close(x.grad, xf.grad, atol=2e-3, rtol=5e-2)
+    assert (x.grad[~keep] == 0).all()
