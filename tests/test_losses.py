@@ -79,3 +79,28 @@ def test_masked_reduction_and_compound():
     assert torch.allclose(total, 0.25 * parts["ce_loss"] + 0.75 * parts["tv_loss"])
     _, parts1 = losses.compound_loss(x, t, mask, pos, losses.resolve_loss_config("kl_div", "eager"))
     assert parts1 == {}
+
+
+def test_skipped_rows_get_no_gradient_whatever_the_upstream_weight():
+    """Rows switched off (``keep`` / ``active`` false) cost 0 and receive a zero gradient even when
+    the upstream gradient of those rows is not zero (the MTP loss divides a plain sum by the count)."""
+    import torch
+
+    from speculators_b200 import ops
+
+    torch.manual_seed(0)
+    T, V = 12, 50
+    keep = torch.tensor([True, False] * (T // 2))
+    labels = torch.randint(0, V, (T,))
+    x = torch.randn(T, V, requires_grad=True)
+    loss = ops.token_cross_entropy(x, labels, keep)
+    (loss.sum() / keep.sum()).backward()
+    assert (loss[~keep] == 0).all() and (x.grad[~keep] == 0).all() and (x.grad[keep].abs().sum(-1) > 0).all()
+
+    y = torch.randn(T, V, requires_grad=True)
+    t = torch.randn(T, V)
+    for op in ("kl_div", "ce", "tv"):
+        y.grad = None
+        row, _, _ = ops.fused_row_loss(op, y, t, active=keep)
+        row.sum().backward()
+        assert (row[~keep] == 0).all() and (y.grad[~keep] == 0).all()
