@@ -42,6 +42,8 @@ TINY = dict(LLAMA31_8B, hidden_size=256, num_hidden_layers=4, num_attention_head
             head_dim=64, intermediate_size=688, vocab_size=1024, rope_theta=10000.0, max_position_embeddings=4096)
 AUX_LAYERS = {"llama31_8b": [2, 16, 29], "tiny": [1, 2, 3]}
 METRIC = "EAGLE3-8B draft-train tokens/s at 1/2/4/8 B200 (device max over ranks)"
+PARITY_STEPS = 6  # optimizer steps from the common initial weights whose losses both arms record
+PARITY_RTOL = 0.03
 
 
 def parse_args():
@@ -50,6 +52,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--regions", type=int, default=5, help="timed regions of --steps steps each; the median is reported")
     ap.add_argument("--model", choices=["llama31_8b", "tiny"], default="llama31_8b")
     ap.add_argument("--seq-len", type=int, default=2048)
     ap.add_argument("--draft-vocab", type=int, default=None)
@@ -114,53 +117,32 @@ def dist_env():
     return int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
 
 
-def build_vocab_maps(torch, vocab_size: int, draft_vocab: int, seq_len: int, seed: int = 0):
-    """Top-``draft_vocab`` ids by frequency in a seeded uniform token stream."""
-    from speculators_b200.train.vocab_mapping import build_vocab_mappings_from_distribution, token_frequency_from_ids
-
-    gen = torch.Generator().manual_seed(seed + 17)
-    stream = torch.randint(0, vocab_size, (64 * seq_len,), generator=gen)
-    return build_vocab_mappings_from_distribution(token_frequency_from_ids(stream), draft_vocab, vocab_size)
+def model_config(args):
+    cfg = dict(LLAMA31_8B if args.model == "llama31_8b" else TINY)
+    draft_vocab = args.draft_vocab or (32000 if args.model == "llama31_8b" else 512)
+    return cfg, draft_vocab
 
 
-def verifier_dir(torch, cfg: dict, tag: str, local_rank: int, barrier) -> str:
-    """config.json + embed / lm_head / norm safetensors of the random verifier,
-    written once per node by local rank 0."""
-    from speculators_b200.verifier import write_random_verifier_stub
-
-    path = os.path.join(tempfile.gettempdir(), f"sb200_bench_verifier_{tag}")
-    done = os.path.join(path, ".done")
-    if local_rank == 0 and not os.path.exists(done):
-        dev = "cuda" if torch.cuda.is_available() else "cpu"
-        write_random_verifier_stub(path, cfg, seed=0, dtype=torch.bfloat16, device=dev)
-        open(done, "w").close()
-    barrier()
-    return path
+def inputs_tag(args, device_type: str) -> str:
+    return f"{args.model}_s{args.seq_len}_v{args.draft_vocab or 0}_{'rand' if args.no_verifier_forward else 'vf'}_{device_type}"
 
 
-def make_batches(torch, args, cfg, rank: int, device, n_batches: int = 2):
-    from speculators_b200.train.synthetic import make_eagle3_batch
-    from speculators_b200.verifier import RandomVerifier
-
-    aux = AUX_LAYERS[args.model]
-    verifier = None
-    if not args.no_verifier_forward:
-        verifier = RandomVerifier(cfg, seed=0, device=device, dtype=torch.bfloat16 if device.type == "cuda" else torch.float32)
-    out = []
-    for i in range(n_batches):
-        out.append(make_eagle3_batch(
-            args.seq_len, cfg["hidden_size"], len(aux), cfg["vocab_size"], seed=1000 * rank + i, mask_p=0.6,
-            mask_span=max(1, min(64, args.seq_len // 32)), dtype=torch.bfloat16, verifier=verifier, layer_ids=aux, pin=device.type == "cuda",
-        ))
-    del verifier
-    return out
+def config_record(args, world: int, draft_vocab: int) -> dict:
+    """What is being measured: identical in both arms (how each arm runs it goes under ``impl_detail``)."""
+    return {
+        "model": "eagle3 1-layer draft for llama-3.1-8b-arch verifier" if args.model == "llama31_8b" else "tiny",
+        "global_batch": world, "seq_len": args.seq_len, "parallelism": f"dp{world}" + ("-sharded" if world > 1 else ""),
+        "draft_vocab": draft_vocab, "ttt_steps": args.ttt_steps, "optimizer": "adamw lr 1e-4", "loss": "kl_div",
+        "regions": args.regions, "parity_steps": PARITY_STEPS,
+        "l2": "per-step working set (1.9 GB of weights + activations) exceeds the 126 MB L2; 2 distinct input batches alternate",
+    }
 
 
-def timed_region(torch, dist, world, device, fn_step, batches, steps, warmup, lookahead=False):
-    """W untimed + K timed steps; returns per-rank milliseconds for the K steps.  With
-    ``lookahead`` the step function also receives the batch of the following step (None for
-    the last warm-up step and the last timed step, so that every timed step's input copy
-    starts and ends inside the timed region)."""
+def timed_region(torch, dist, world, device, fn_step, batches, steps, offset=0, lookahead=False):
+    """K timed steps between barrier + synchronize on both sides; returns the K steps' device
+    milliseconds (max over ranks).  With ``lookahead`` the step function also receives the
+    batch of the following step (None for the last timed step, so that every timed step's
+    input copy starts and ends inside the timed region)."""
     cuda = device.type == "cuda"
 
     def barrier():
@@ -169,22 +151,17 @@ def timed_region(torch, dist, world, device, fn_step, batches, steps, warmup, lo
         if cuda:
             torch.cuda.synchronize()
 
-    def call(i, last):
-        b = batches[i % len(batches)]
-        if lookahead:
-            fn_step(b, None if last else batches[(i + 1) % len(batches)])
-        else:
-            fn_step(b)
-
-    for i in range(warmup):
-        call(i, i == warmup - 1)
     barrier()
     if cuda:
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
     t0 = time.perf_counter()
     for i in range(steps):
-        call(warmup + i, i == steps - 1)
+        b = batches[(offset + i) % len(batches)]
+        if lookahead:
+            fn_step(b, None if i == steps - 1 else batches[(offset + i + 1) % len(batches)])
+        else:
+            fn_step(b)
     if cuda:
         end.record()
     barrier()
@@ -196,12 +173,28 @@ def timed_region(torch, dist, world, device, fn_step, batches, steps, warmup, lo
     return ms
 
 
+def spread(values: list[float]) -> dict:
+    return {"median": statistics.median(values), "min": min(values), "max": max(values), "n": len(values)}
+
+
+def loss_parity(mine: list[float] | None, other: list[float] | None) -> dict:
+    """Both arms start from the same draft weights and see the same batches; their losses over
+    the first steps must agree within ``PARITY_RTOL`` (bf16 compute on different kernels)."""
+    if not mine or not other:
+        return {"loss_parity": None, "loss_parity_note": "the other arm's record is not on this machine"}
+    n = min(len(mine), len(other))
+    gaps = [abs(a - b) / max(abs(b), 1e-6) for a, b in zip(mine[:n], other[:n])]
+    return {"loss_parity": bool(max(gaps) <= PARITY_RTOL), "loss_parity_max_rel_gap": max(gaps), "loss_parity_rtol": PARITY_RTOL,
+            "loss_trace_other_arm": other[:n]}
+
+
 # ----------------------------------------------------------------------------- this framework
 def run_ours(args):
     import torch
     import torch.distributed as dist
 
     sys.path.insert(0, REPO)
+    import bench_inputs
     import speculators_b200 as sb
     from speculators_b200 import ops
     from speculators_b200.layer_config import TransformerLayerConfig
@@ -212,23 +205,32 @@ def run_ours(args):
     rank, local_rank, world = dist_env()
     maybe_setup_distributed()
     device = torch.device(args.device) if args.device else (torch.device("cuda", local_rank) if torch.cuda.is_available() else torch.device("cpu"))
-    cfg = dict(LLAMA31_8B if args.model == "llama31_8b" else TINY)
-    draft_vocab = args.draft_vocab or (32000 if args.model == "llama31_8b" else 512)
+    cuda = device.type == "cuda"
+    if cuda:
+        torch.cuda.set_device(device)
+    cfg, draft_vocab = model_config(args)
     torch.manual_seed(0)
 
     def barrier():
         if world > 1:
             dist.barrier()
 
-    vdir = verifier_dir(torch, cfg, args.model, local_rank, barrier)
-    d2t, t2d = build_vocab_maps(torch, cfg["vocab_size"], draft_vocab, args.seq_len)
+    tag = inputs_tag(args, device.type)
+    root = bench_inputs.ensure_inputs(
+        cfg, tag, seq_len=args.seq_len, draft_vocab=draft_vocab, layer_ids=AUX_LAYERS[args.model], rank=rank, local_rank=local_rank,
+        n_batches=2, device=device, verifier_forward=not args.no_verifier_forward, barrier=barrier,
+    )
+    d2t, t2d = bench_inputs.load_vocab_maps(root)
+    batches = bench_inputs.load_batches(root, rank, pin=cuda)
     draft_cfg = TransformerLayerConfig(**dict(cfg, num_hidden_layers=1, sliding_window=2048, layer_types=["sliding_attention"]))
     model = sb.Eagle3DraftModel.from_training_args(
         draft_cfg, t2d=t2d, d2t=d2t, draft_vocab_size=draft_vocab, norm_before_residual=True, norm_before_fc=True,
-        norm_output=True, ttt_steps=args.ttt_steps, verifier_name_or_path=vdir, target_layer_ids=AUX_LAYERS[args.model],
+        norm_output=True, ttt_steps=args.ttt_steps, verifier_name_or_path=os.path.join(root, "verifier"), target_layer_ids=AUX_LAYERS[args.model],
     )
+    init = bench_inputs.seeded_draft_init({k: tuple(v.shape) for k, v in model.state_dict().items()})
+    missing = model.load_state_dict(init, strict=False)
+    assert not missing.unexpected_keys, missing.unexpected_keys
     train_kwargs, _ = sb.Eagle3DraftModel.get_trainer_kwargs(loss_fn="kl_div", ttt_steps=args.ttt_steps, ttt_step_loss_decay=1.0)
-    batches = make_batches(torch, args, cfg, rank, device)
     loader = SyntheticLoader(batches, args.steps + args.warmup)
     trainer = Trainer(model, TrainerConfig(
         lr=1e-4, num_epochs=1, save_path=os.path.join(tempfile.gettempdir(), "sb200_bench_unused"), train_call_kwargs=train_kwargs,
@@ -237,21 +239,35 @@ def run_ours(args):
     ), loader)
     trainer.model.train()
     tokens_per_step = sum(int((b["document_ids"] != -1).sum()) for b in batches) / len(batches)
-
-    # (1) device-resident inputs
     dev_batches = [{k: v.to(device) for k, v in b.items()} for b in batches]
-    sampler = ClockSampler(local_rank)
-    cuda = device.type == "cuda"
     count0 = ops.native().launch_count() if cuda else 0
 
+    # (0) the first optimizer steps from the common initial weights: their losses are compared
+    # with the other arm's (they also serve as warm-up)
+    trace = []
+    for i in range(PARITY_STEPS):
+        loss, _ = trainer.train_step(dev_batches[i % len(dev_batches)])
+        trace.append(loss.detach().float().reshape(1).clone())
+    trace_t = torch.cat(trace)
+    if world > 1:
+        dist.all_reduce(trace_t, op=dist.ReduceOp.SUM)
+        trace_t /= world
+    loss_trace = [float(x) for x in trace_t.cpu()]
+
+    # (1) device-resident inputs
     def step_dev(b):
         trainer.train_step(b)
 
+    for i in range(max(0, args.warmup - PARITY_STEPS)):
+        step_dev(dev_batches[i % 2])
+    sampler = ClockSampler(local_rank)
     if rank == 0 and cuda:
         sampler.start()
-    ms = timed_region(torch, dist, world, device, step_dev, dev_batches, args.steps, args.warmup)
+    region_ms = [timed_region(torch, dist, world, device, step_dev, dev_batches, args.steps, offset=r) for r in range(args.regions)]
     clocks = sampler.stop() if (rank == 0 and cuda) else {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
-    launches = _count_launches(trainer, ops, count0, args.steps, args.warmup, cuda)
+    timed_steps = args.steps * args.regions
+    launches = _count_launches(trainer, ops, count0, args.steps, timed_steps + max(args.warmup, PARITY_STEPS), cuda)
+    ms = statistics.median(region_ms)
 
     # (2) end to end: pinned host batch -> H2D every step, loss read back every step
     last = {}
@@ -269,33 +285,97 @@ def run_ours(args):
             last["loss"] = handle.value()
             last["pending"] = None
 
-    ms_e2e = timed_region(torch, dist, world, device, step_e2e, batches, args.steps, min(args.warmup, 3), lookahead=True)
+    for i in range(min(args.warmup, 3)):
+        step_e2e(batches[i % 2], None)
+    e2e_ms = [timed_region(torch, dist, world, device, step_e2e, batches, args.steps, offset=r, lookahead=True) for r in range(args.regions)]
+    ms_e2e = statistics.median(e2e_ms)
     h2d = sum(v.numel() * v.element_size() for v in batches[0].values())
+    comm = _exposed_comm(torch, dist, trainer, ops, world, cuda)
+    if cuda:
+        ops.check_gemm_status()
+        trainer.engine.check_status()
 
     value = world * tokens_per_step * args.steps / (ms / 1000.0)
     e2e = world * tokens_per_step * args.steps / (ms_e2e / 1000.0)
     if rank == 0:
-        print(json.dumps({
+        record = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if cuda else "fp32",
-            "data": "synthetic (seeded uniform tokens; random-init verifier forward for hidden states; random-init draft)",
+            "data": "synthetic (seeded uniform tokens; hidden states from a plain-PyTorch forward of the random-init verifier; seeded draft init; "
+                    "both arms read the same files)",
             "impl": "ours",
-            "config": {"model": "eagle3 1-layer draft for llama-3.1-8b-arch verifier" if args.model == "llama31_8b" else "tiny", "global_batch": world,
-                       "seq_len": args.seq_len, "parallelism": f"dp{world}" + ("-sharded" if world > 1 else ""),
-                       "optimizer_comm": ("nvls multimem" if getattr(trainer.engine, "nvls", False) else "nvlink p2p" if getattr(trainer.engine, "p2p", False)
-                                          else "nccl" if world > 1 else "none"),
-                       "draft_vocab": draft_vocab,
-                       "ttt_steps": args.ttt_steps, "optimizer": "adamw lr 1e-4",
-                       "cuda_graph": trainer._graphed is not None,
-                       "l2": "per-step working set (1.9 GB of weights + activations) exceeds the 126 MB L2; 2 distinct input batches alternate"},
+            "config": config_record(args, world, draft_vocab),
+            "impl_detail": {
+                "optimizer_comm": ("nvls multimem" if getattr(trainer.engine, "nvls", False) else "nvlink p2p" if getattr(trainer.engine, "p2p", False)
+                                   else ("nccl" if cuda else "gloo") if world > 1 else "none"),
+                "cuda_graph": trainer._graphed is not None,
+                "path": "speculators_b200.train.Trainer.train_step / train_step_async",
+            },
+            "regions_ms_per_step": spread([m / args.steps for m in region_ms]),
             "clocks": clocks,
-            "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4, "last_loss": last.get("loss")},
+            "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+                    "regions_ms_per_step": spread([m / args.steps for m in e2e_ms]), "last_loss": last.get("loss")},
+            "exposed_comm_ms_per_step": comm,
+            "loss_trace": loss_trace, "last_loss": last.get("loss"),
             "gpu_launches": launches,
-        }))
+        }
+        record.update(loss_parity(loss_trace, (bench_inputs.read_result(tag, "reference", world) or {}).get("loss_trace")))
+        bench_inputs.write_result(tag, "ours", world, {"loss_trace": loss_trace})
+        print(json.dumps(record))
     maybe_destroy_distributed()
 
 
-def _count_launches(trainer, ops, count0, steps, warmup, cuda):
+def _exposed_comm(torch, dist, trainer, ops, world, cuda):
+    """Milliseconds per step that the training stream spends in communication.  One GPU: none.
+    Library collectives: their own CUDA-event time over a few optimizer steps (they run on the
+    training stream, nothing overlaps them).  Fused peer-memory step: the two kernels hold the
+    transfers and the AdamW arithmetic together, so the figure is their time minus that of the
+    local AdamW kernel over a buffer of the shard's size."""
+    if world == 1 or not cuda:
+        return 0.0 if world == 1 else None
+    eng = trainer.engine
+    reps = 5
+
+    def timed(fn):
+        dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / reps], dtype=torch.float64, device=eng.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    if getattr(eng, "p2p", False):
+        eng.mark_grads_written()
+        fused = timed(eng.step)
+        n = eng.hi - eng.lo
+        g = torch.zeros(n, dtype=torch.bfloat16, device=eng.device)
+        w = torch.zeros(n, dtype=torch.bfloat16, device=eng.device)
+        m, v, master = (torch.zeros(n, dtype=torch.float32, device=eng.device) for _ in range(3))
+        nsq = torch.zeros(1, dtype=torch.float32, device=eng.device)
+
+        def local():
+            ops.sum_of_squares(g, nsq, accumulate=False)
+            ops.adamw_step_(master, m, v, g, w, eng.hyper, nsq)
+
+        return max(0.0, fused - timed(local))
+    eng.account_comm(True)
+    eng.mark_grads_written()
+    for _ in range(reps):
+        eng.step()
+    total = eng.exposed_comm_ms()
+    eng.account_comm(False)
+    t = torch.tensor([(total or 0.0) / reps], dtype=torch.float64, device=eng.device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def _count_launches(trainer, ops, count0, steps, total_steps, cuda):
+    """Own-kernel launches inside one timed region of ``steps`` steps."""
     if not cuda:
         return 0
     g = trainer._graphed
@@ -304,21 +384,32 @@ def _count_launches(trainer, ops, count0, steps, warmup, cuda):
         extra = ops.native().launch_count() - count0 - getattr(g, "capture_launch_total", 0)
         # launches recorded at capture time are replayed once per step; launches made
         # eagerly (outside the graph) are counted directly and scaled to the timed steps
-        return int(per_step * steps + max(0, extra) * steps / max(1, steps + warmup))
-    return int((ops.native().launch_count() - count0) * steps / max(1, steps + warmup))
+        return int(per_step * steps + max(0, extra) * steps / max(1, total_steps))
+    return int((ops.native().launch_count() - count0) * steps / max(1, total_steps))
 
 
 # ----------------------------------------------------------------------------- reference arm
 def run_reference(args):
+    """The unmodified reference from ``baseline/_ref`` through its own ``Trainer.train_epoch``.
+    Nothing of this framework is imported here: the inputs come from ``bench_inputs`` (plain
+    PyTorch) as files that the other arm reads too."""
     ref_root = os.path.join(REPO, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref_root, "speculators")):
         print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed (pip --target install of the reference missing)"}))
         return
+    sys.path[:] = [p for p in sys.path if os.path.abspath(p or ".") != REPO]  # the repo root must not shadow or leak packages
     sys.path.insert(0, ref_root)
     try:
+        import importlib.util
+        import logging
+
         import torch
         import torch.distributed as dist
         from transformers import LlamaConfig
+
+        spec = importlib.util.spec_from_file_location("bench_inputs", os.path.join(REPO, "bench_inputs.py"))
+        bench_inputs = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(bench_inputs)
 
         from speculators.models.eagle3.core import Eagle3DraftModel
         from speculators.train.distributed import maybe_destroy_distributed, maybe_setup_distributed
@@ -334,20 +425,20 @@ def run_reference(args):
     maybe_setup_distributed()
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
-    cfg = dict(LLAMA31_8B if args.model == "llama31_8b" else TINY)
-    draft_vocab = args.draft_vocab or (32000 if args.model == "llama31_8b" else 512)
+    cfg, draft_vocab = model_config(args)
     torch.manual_seed(0)
 
     def barrier():
         if world > 1:
             dist.barrier()
 
-    # data and the verifier stub directory are plain tensors / files; building them
-    # with this repo's helpers keeps both arms on identical inputs
-    sys.path.insert(1, REPO)
-    vdir = verifier_dir(torch, cfg, args.model, local_rank, barrier)
-    d2t, t2d = build_vocab_maps(torch, cfg["vocab_size"], draft_vocab, args.seq_len)
-    batches = make_batches(torch, args, cfg, rank, device)
+    tag = inputs_tag(args, "cuda")
+    root = bench_inputs.ensure_inputs(
+        cfg, tag, seq_len=args.seq_len, draft_vocab=draft_vocab, layer_ids=AUX_LAYERS[args.model], rank=rank, local_rank=local_rank,
+        n_batches=2, device=device, verifier_forward=not args.no_verifier_forward, barrier=barrier,
+    )
+    d2t, t2d = bench_inputs.load_vocab_maps(root)
+    batches = bench_inputs.load_batches(root, rank, pin=True)
 
     hf_cfg = LlamaConfig(**{k: v for k, v in cfg.items() if k not in ("architectures", "model_type", "rope_theta")})
     hf_cfg.num_hidden_layers = 1
@@ -359,10 +450,32 @@ def run_reference(args):
         hf_cfg.rope_theta = cfg["rope_theta"]
     model = Eagle3DraftModel.from_training_args(
         hf_cfg, t2d=t2d, d2t=d2t, draft_vocab_size=draft_vocab, norm_before_residual=True, norm_before_fc=True,
-        norm_output=True, ttt_steps=args.ttt_steps, verifier_name_or_path=vdir, target_layer_ids=AUX_LAYERS[args.model],
+        norm_output=True, ttt_steps=args.ttt_steps, verifier_name_or_path=os.path.join(root, "verifier"), target_layer_ids=AUX_LAYERS[args.model],
     )
+    init = bench_inputs.seeded_draft_init({k: tuple(v.shape) for k, v in model.state_dict().items()})
+    with torch.no_grad():
+        own = model.state_dict()
+        for k, v in init.items():
+            own[k].copy_(v)
     train_kwargs, _ = Eagle3DraftModel.get_trainer_kwargs(loss_fn="kl_div", loss_implementation="fused", ttt_steps=args.ttt_steps, ttt_step_loss_decay=1.0)
     tokens_per_step = sum(int((b["document_ids"] != -1).sum()) for b in batches) / len(batches)
+
+    class Capture(logging.Handler):
+        """Records what the stock trainer logs on its logging steps (its own loss read-back)."""
+
+        def __init__(self):
+            super().__init__()
+            self.losses, self.n_metrics = [], 0
+
+        def emit(self, record):
+            msg = record.msg
+            if isinstance(msg, dict) and isinstance(msg.get("train"), dict) and "loss" in msg["train"]:
+                self.losses.append(float(msg["train"]["loss"]))
+
+    capture = Capture()
+    mlog = logging.getLogger("speculators.metrics")
+    mlog.addHandler(capture)
+    mlog.setLevel(logging.INFO)
 
     class TimedLoader:
         """Feeds W + K batches to the stock ``Trainer.train_epoch`` loop and brackets the
@@ -372,8 +485,8 @@ def run_reference(args):
             def set_epoch(self, _e):
                 pass
 
-        def __init__(self, items, warmup, steps):
-            self.items, self.warmup, self.steps = items, warmup, steps
+        def __init__(self, items, warmup, steps, offset=0):
+            self.items, self.warmup, self.steps, self.offset = items, warmup, steps, offset
             self.batch_sampler = self._Sampler()
             self.ms = None
 
@@ -385,22 +498,26 @@ def run_reference(args):
             for i in range(self.warmup + self.steps):
                 if i == self.warmup:
                     barrier(); torch.cuda.synchronize(); start.record()
-                yield self.items[i % len(self.items)]
+                yield self.items[(self.offset + i) % len(self.items)]
             end.record()
             barrier(); torch.cuda.synchronize()
             self.ms = start.elapsed_time(end)
 
-    def run(items, warmup):
-        loader = TimedLoader(items, warmup, args.steps)
-        if run.trainer is None:
-            run.trainer = Trainer(model, TrainerConfig(
+    state = {"trainer": None}
+
+    def run(items, warmup, steps, log_freq, offset=0):
+        loader = TimedLoader(items, warmup, steps, offset)
+        if state["trainer"] is None:
+            state["trainer"] = Trainer(model, TrainerConfig(
                 lr=1e-4, num_epochs=1, save_path=os.path.join(tempfile.gettempdir(), "sb200_ref_unused"), resume_from_checkpoint=False,
-                train_call_kwargs=train_kwargs, optimizer="adamw", scheduler_type="none", log_freq=10**9, fsdp_shard=world > 1,
+                train_call_kwargs=train_kwargs, optimizer="adamw", scheduler_type="none", log_freq=log_freq, fsdp_shard=world > 1,
             ), loader)
-        else:
-            run.trainer.train_loader = loader
-            run.trainer.global_step = 1  # keep the once-per-log_freq profiling sync out of the timed steps
-        run.trainer.train_epoch(0)
+        tr = state["trainer"]
+        tr.train_loader = loader
+        tr.config = tr.config._replace(log_freq=log_freq)
+        if log_freq > 1:
+            tr.global_step = 1  # keeps the once-per-log_freq logging step (synchronize + .item()) out of these steps
+        tr.train_epoch(0)
         ms = loader.ms
         if world > 1:
             t = torch.tensor([ms], dtype=torch.float64, device=device)
@@ -408,37 +525,67 @@ def run_reference(args):
             ms = float(t.item())
         return ms
 
-    run.trainer = None
     sampler = ClockSampler(local_rank)
     dev_batches = [{k: v.to(device) for k, v in b.items()} for b in batches]
+    quiet = 10**9
     try:
-        run(dev_batches, max(args.warmup, 3))  # first call pays torch.compile; discard
+        # first optimizer steps from the common initial weights, logged every step through the
+        # trainer's own logging path: the loss trace that the other arm is compared with
+        # (this call also pays torch.compile)
+        run(dev_batches, 0, PARITY_STEPS, 1)
+        loss_trace = list(capture.losses[:PARITY_STEPS])
+        run(dev_batches, max(args.warmup, 3), 1, quiet)
         if rank == 0:
             sampler.start()
-        ms = run(dev_batches, args.warmup)
+        region_ms = [run(dev_batches, 0, args.steps, quiet, offset=r) for r in range(args.regions)]
         clocks = sampler.stop() if rank == 0 else {}
-        ms_e2e = run(batches, min(args.warmup, 3))
+        # end to end, stock logging path on every step (log_freq=1: synchronize, metric reduce,
+        # .item() of every metric = the reference's own loss read-back) ...
+        run(batches, min(args.warmup, 3), 1, 1)
+        n_before = len(capture.losses)
+        e2e_ms = [run(batches, 0, args.steps, 1, offset=r) for r in range(args.regions)]
+        logged = len(capture.losses) - n_before
+        # ... and without it (no device-to-host read inside the timed steps)
+        e2e_nolog_ms = [run(batches, 0, args.steps, quiet, offset=r) for r in range(args.regions)]
     except Exception as err:  # noqa: BLE001
         if rank == 0:
             print(json.dumps({"impl": "reference", "unavailable": f"reference run failed: {type(err).__name__}: {err}"[:400]}))
         maybe_destroy_distributed()
         return
+    ms, ms_e2e, ms_nolog = statistics.median(region_ms), statistics.median(e2e_ms), statistics.median(e2e_nolog_ms)
     value = world * tokens_per_step * args.steps / (ms / 1000.0)
-    e2e = world * tokens_per_step * args.steps / (ms_e2e / 1000.0)
     h2d = sum(v.numel() * v.element_size() for v in batches[0].values())
+    # the logging step reads the token count (int64) and one fp32 scalar per metric
+    with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+        n_metrics = len(model(**dev_batches[0], **train_kwargs)[2]) if world == 1 else None
+    d2h = 8 + 4 * n_metrics if n_metrics is not None else 12
     if rank == 0:
-        print(json.dumps({
+        record = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic (same generator as the `ours` arm)", "impl": "reference",
-            "config": {"model": "eagle3 1-layer draft for llama-3.1-8b-arch verifier" if args.model == "llama31_8b" else "tiny", "global_batch": world,
-                       "seq_len": args.seq_len, "parallelism": f"dp{world}" + ("-fsdp2" if world > 1 else ""), "draft_vocab": draft_vocab,
-                       "ttt_steps": args.ttt_steps, "optimizer": "adamw lr 1e-4",
-                       "path": "speculators.train.trainer.Trainer.train_epoch, torch.compile + flex attention + fused Triton loss (stock)"},
+            "data": "synthetic (seeded uniform tokens; hidden states from a plain-PyTorch forward of the random-init verifier; seeded draft init; "
+                    "both arms read the same files)",
+            "impl": "reference",
+            "config": config_record(args, world, draft_vocab),
+            "impl_detail": {
+                "optimizer_comm": "fsdp2 (nccl)" if world > 1 else "none", "cuda_graph": False,
+                "path": "speculators.train.trainer.Trainer.train_epoch, torch.compile + flex attention + fused Triton loss (stock)",
+            },
+            "regions_ms_per_step": spread([m / args.steps for m in region_ms]),
             "clocks": clocks,
-            "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 0},
+            "e2e": {"value": world * tokens_per_step * args.steps / (ms_e2e / 1000.0), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "logged_steps": logged,
+                    "how": "log_freq=1: the stock trainer's logging step (synchronize, metric reduce, .item() per metric) on every step",
+                    "regions_ms_per_step": spread([m / args.steps for m in e2e_ms])},
+            "e2e_nolog": {"value": world * tokens_per_step * args.steps / (ms_nolog / 1000.0), "unit": "tokens/s", "ms_per_step": ms_nolog / args.steps,
+                          "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 0, "how": "no logging step inside the timed steps"},
+            "exposed_comm_ms_per_step": None,
+            "loss_trace": loss_trace, "last_loss": capture.losses[-1] if capture.losses else None,
             "gpu_launches": 0,
-        }))
+        }
+        record.update(loss_parity(loss_trace, (bench_inputs.read_result(tag, "ours", world) or {}).get("loss_trace")))
+        bench_inputs.write_result(tag, "reference", world, {"loss_trace": loss_trace})
+        print(json.dumps(record))
     maybe_destroy_distributed()
 
 
