@@ -41,7 +41,7 @@ int peer_close(void*);
 int fused_optim_ctl_words();
 int fused_optim_num_partials();
 int launch_fused_sharded_adamw(int, int, int64_t, const void* const*, void* const*, void* const*, const void*, void*, float*, float*,
-                               float*, float*, float*, const float*, int*, cudaStream_t);
+                               float*, float*, float*, const float*, int*, uint32_t, cudaStream_t);
 int hs_ring_ctl_words_per_slot();
 int launch_hs_push(const void*, int64_t, void*, uint32_t*, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t*, int*, cudaStream_t);
 int launch_hs_pop(void*, int64_t, const void*, uint32_t*, uint32_t, uint32_t, uint32_t*, int*, cudaStream_t);
@@ -345,7 +345,11 @@ void hs_pop(Tensor dst, int64_t slot_data, int64_t slot_ctl, int64_t seq, int64_
 // g_ptrs / w_ptrs / ctl_ptrs: int64 CPU tensors [world] of device addresses valid on this rank.
 // g_mc / w_mc: multicast (NVSwitch) addresses of the gradient / weight buffers, 0 = use the per-peer addresses.
 void fused_sharded_adamw(int64_t world, int64_t rank, int64_t shard, const Tensor& g_ptrs, const Tensor& w_ptrs, const Tensor& ctl_ptrs,
-                         int64_t g_mc, int64_t w_mc, Tensor master, Tensor m, Tensor v, Tensor gred, const Tensor& hyper, Tensor status) {
+                         int64_t g_mc, int64_t w_mc, Tensor master, Tensor m, Tensor v, Tensor gred, const Tensor& hyper, Tensor status, int64_t spin_limit) {
+  // validated before the fixed-size pointer arrays below are filled
+  TORCH_CHECK(world >= 1 && world <= 8 && rank >= 0 && rank < world && shard > 0 && shard % 8 == 0,
+              "fused_sharded_adamw: need 1 <= world <= 8, 0 <= rank < world and a positive shard that is a multiple of 8");
+  TORCH_CHECK(spin_limit > 0 && spin_limit <= 0xFFFFFFF0LL, "fused_sharded_adamw: spin_limit out of range");
   TORCH_CHECK(g_ptrs.device().is_cpu() && g_ptrs.scalar_type() == at::kLong && g_ptrs.numel() == world);
   TORCH_CHECK(w_ptrs.device().is_cpu() && w_ptrs.scalar_type() == at::kLong && w_ptrs.numel() == world);
   TORCH_CHECK(ctl_ptrs.device().is_cpu() && ctl_ptrs.scalar_type() == at::kLong && ctl_ptrs.numel() == world);
@@ -366,7 +370,7 @@ void fused_sharded_adamw(int64_t world, int64_t rank, int64_t shard, const Tenso
   const int rc = sb200::launch_fused_sharded_adamw((int)world, (int)rank, shard, g, w, c, reinterpret_cast<const void*>(g_mc),
                                                    reinterpret_cast<void*>(w_mc), master.data_ptr<float>(), m.data_ptr<float>(),
                                                    v.data_ptr<float>(), gred.data_ptr<float>(), partial.data_ptr<float>(),
-                                                   hyper.data_ptr<float>(), status.data_ptr<int>(), cur_stream());
+                                                   hyper.data_ptr<float>(), status.data_ptr<int>(), (uint32_t)spin_limit, cur_stream());
   TORCH_CHECK(rc == 0, "fused_sharded_adamw launch failed (", rc, ")");
 }
 

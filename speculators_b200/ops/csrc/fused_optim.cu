@@ -36,7 +36,9 @@ namespace fo {
 constexpr int kMaxRanks = 8;
 constexpr int kThreads = 256;
 constexpr int kBlocks = 2 * kNumSM;
-constexpr uint32_t kSpinLimit = 1u << 24;  // x ~64 ns backoff: about a second
+constexpr uint32_t kSpinsPerSecond = 1u << 24;  // one poll + 64 ns back-off: about 60 ns
+// The wait budget (poll iterations) is a kernel argument: the host passes tens of seconds by
+// default, since the collectives this replaces tolerate long rank skew; it stays bounded.
 
 enum Status : int { kOk = 0, kTimeoutGradBarrier = 11, kTimeoutNormBarrier = 12, kTimeoutEndBarrier = 13, kTimeoutLocal = 14 };
 
@@ -64,6 +66,7 @@ struct Params {
   float* partial;  // [kBlocks] local scratch
   const float* hyper;
   int* status;
+  uint32_t spin_limit;  // poll iterations every wait may use
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
@@ -102,8 +105,8 @@ __device__ __forceinline__ void multimem_st8(__nv_bfloat16* mc_ptr, const bf16x8
 
 // Bounded wait until *p == want (acquire at the given scope).
 template <bool SYS>
-__device__ __forceinline__ bool wait_eq(const uint32_t* p, uint32_t want, int* status, int code) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+__device__ __forceinline__ bool wait_eq(const uint32_t* p, uint32_t want, int* status, int code, uint32_t spin_limit) {
+  for (uint32_t i = 0; i < spin_limit; ++i) {
     const uint32_t v = SYS ? ld_acquire_sys(p) : ld_acquire_gpu(p);
     if (v == want) return true;
     if ((i & 0x3ff) == 0x3ff && *reinterpret_cast<volatile int*>(status) != kOk) return false;
@@ -116,7 +119,7 @@ __device__ __forceinline__ bool wait_eq(const uint32_t* p, uint32_t want, int* s
 // Block 0 runs `leader` (cross-rank part) and publishes `gen` in the local release word;
 // every other block waits for that word.  Returns false if anything timed out.
 template <typename F>
-__device__ __forceinline__ bool leader_then_release(uint32_t* release_word, uint32_t gen, int* status, F leader) {
+__device__ __forceinline__ bool leader_then_release(uint32_t* release_word, uint32_t gen, int* status, uint32_t spin_limit, F leader) {
   __shared__ int ok_s;
   if (threadIdx.x == 0) {
     bool ok = true;
@@ -125,11 +128,13 @@ __device__ __forceinline__ bool leader_then_release(uint32_t* release_word, uint
       // publish even on failure (with a poisoned value) so the other blocks do not wait out their budget
       st_release_gpu(release_word, ok ? gen : 0xffffffffu);
     } else {
-      for (uint32_t i = 0; i < kSpinLimit; ++i) {
+      // the leader's own waits use the same budget one after another (up to `world` of them)
+      const uint64_t local_limit = (uint64_t)spin_limit * (kMaxRanks + 1);
+      for (uint64_t i = 0; i < local_limit; ++i) {
         const uint32_t v = ld_acquire_gpu(release_word);
         if (v == gen) break;
         if (v == 0xffffffffu || (((i & 0x3ff) == 0x3ff) && *reinterpret_cast<volatile int*>(status) != kOk)) { ok = false; break; }
-        if (i + 1 == kSpinLimit) { atomicCAS(status, kOk, kTimeoutLocal); ok = false; }
+        if (i + 1 == local_limit) { atomicCAS(status, kOk, kTimeoutLocal); ok = false; }
         __nanosleep(64);
       }
     }
@@ -145,11 +150,11 @@ reduce_scatter_norm_kernel(const Params p) {
   uint32_t* ctl = p.ctl[p.rank];
   const uint32_t gen = ctl[34] + 1;  // step counter is advanced at the end of kernel B
 
-  const bool ok = leader_then_release(ctl + 32, gen, p.status, [&]() {
+  const bool ok = leader_then_release(ctl + 32, gen, p.status, p.spin_limit, [&]() {
     __threadfence_system();
     for (int q = 0; q < p.world; ++q) st_release_sys(p.ctl[q] + 0 + p.rank, gen);
     for (int q = 0; q < p.world; ++q)
-      if (!wait_eq<true>(ctl + 0 + q, gen, p.status, kTimeoutGradBarrier)) return false;
+      if (!wait_eq<true>(ctl + 0 + q, gen, p.status, kTimeoutGradBarrier, p.spin_limit)) return false;
     return true;
   });
 
@@ -202,9 +207,9 @@ adamw_all_gather_kernel(const Params p) {
   uint32_t* ctl = p.ctl[p.rank];
   const uint32_t gen = ctl[34] + 1;
 
-  const bool ok = leader_then_release(ctl + 33, gen, p.status, [&]() {
+  const bool ok = leader_then_release(ctl + 33, gen, p.status, p.spin_limit, [&]() {
     for (int q = 0; q < p.world; ++q)
-      if (!wait_eq<true>(ctl + 8 + q, gen, p.status, kTimeoutNormBarrier)) return false;
+      if (!wait_eq<true>(ctl + 8 + q, gen, p.status, kTimeoutNormBarrier, p.spin_limit)) return false;
     float total = 0.f;
     for (int q = 0; q < p.world; ++q) total += __uint_as_float(reinterpret_cast<volatile uint32_t*>(ctl + 24)[q]);
     reinterpret_cast<volatile uint32_t*>(ctl)[37] = __float_as_uint(total);
@@ -265,7 +270,7 @@ adamw_all_gather_kernel(const Params p) {
       if (ok) {
         for (int q = 0; q < p.world; ++q) st_release_sys(p.ctl[q] + 16 + p.rank, gen);
         for (int q = 0; q < p.world; ++q)
-          if (!wait_eq<true>(ctl + 16 + q, gen, p.status, kTimeoutEndBarrier)) break;
+          if (!wait_eq<true>(ctl + 16 + q, gen, p.status, kTimeoutEndBarrier, p.spin_limit)) break;
       }
       ctl[34] = gen;  // advance the step counter (also after a failure, so a retry starts a fresh generation)
       __threadfence();
@@ -282,7 +287,7 @@ int fused_optim_num_partials() { return fo::kBlocks; }
 // g_mc / w_mc: multicast addresses of the gradient / weight buffers, or nullptr for per-peer access.
 int launch_fused_sharded_adamw(int world, int rank, int64_t shard, const void* const* g_peers, void* const* w_peers,
                                void* const* ctl_peers, const void* g_mc, void* w_mc, float* master, float* m, float* v, float* gred,
-                               float* partial, const float* hyper, int* status, cudaStream_t stream) {
+                               float* partial, const float* hyper, int* status, uint32_t spin_limit, cudaStream_t stream) {
   if (world < 1 || world > fo::kMaxRanks || rank < 0 || rank >= world || shard <= 0 || (shard & 7)) return -1;
   fo::Params p{};
   p.world = world;
@@ -302,6 +307,7 @@ int launch_fused_sharded_adamw(int world, int rank, int64_t shard, const void* c
   p.partial = partial;
   p.hyper = hyper;
   p.status = status;
+  p.spin_limit = spin_limit ? spin_limit : fo::kSpinsPerSecond;
   count_launch(2);
   fo::reduce_scatter_norm_kernel<<<fo::kBlocks, fo::kThreads, 0, stream>>>(p);
   fo::adamw_all_gather_kernel<<<fo::kBlocks, fo::kThreads, 0, stream>>>(p);

@@ -88,6 +88,8 @@ extern "C" int sb200_sumsq_bf16_noalloc(const void* x, long long n, float* out, 
     const int grid = n_chunks < 8 * sb200::kNumSM ? n_chunks : 8 * sb200::kNumSM;
     sb200::count_launch(1);
     noalloc_partial_kernel<<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), n, scratch, n_chunks);
+    err = cudaGetLastError();  // a refused first launch leaves the partials unwritten: do not reduce them
+    if (err != cudaSuccess) return fail(SB200_NOALLOC_ERR_CUDA, "kernel launch (partials)", err);
   }
   sb200::count_launch(1);
   noalloc_final_kernel<<<1, 256, 0, s>>>(scratch, n_chunks, out, accumulate);

@@ -43,7 +43,7 @@ from speculators_b200 import ops
 
 log = logging.getLogger(__name__)
 
-__all__ = ["EngineConfig", "TrainEngine", "split_named_params_for_muon"]
+__all__ = ["EngineConfig", "TrainEngine", "peer_wait_seconds", "peer_wait_spins", "split_named_params_for_muon"]
 
 _ALIGN = 128  # elements; keeps every parameter and every shard 16-byte aligned
 _ADAMW_NAME_HINTS = ("embed_tokens", "lm_head")
@@ -124,7 +124,36 @@ class TrainEngine:
         )
         if mode in ("p2p", "nvls") and not applicable:
             raise ValueError(f"comm={mode!r} needs sharded multi-rank CUDA training with AdamW in bf16 on one node (<= 8 ranks)")
-        return applicable and mode in ("auto", "nvls", "p2p")
+        if not applicable or mode == "nccl":
+            return False
+        reason = self._peer_memory_unavailable()
+        if reason is not None:
+            if mode in ("p2p", "nvls"):
+                raise RuntimeError(f"comm={mode!r} is not available: {reason}")
+            log.info("peer-memory optimizer step not used (%s); using the library collectives", reason)
+            self._comm_mode = "nccl"
+            return False
+        return True
+
+    def _peer_memory_unavailable(self) -> str | None:
+        """Why the ranks of this group cannot map one another's memory (None: they can).  Every
+        rank publishes its host name and device index; the verdict is formed from the gathered
+        lists, so all ranks take the same branch."""
+        import socket
+
+        mine = (socket.gethostname(), self.device.index if self.device.index is not None else torch.cuda.current_device())
+        everyone: list = [None] * self.world
+        dist.all_gather_object(everyone, mine, group=self.group)
+        if len({h for h, _ in everyone}) > 1:
+            return "the ranks are on more than one node"
+        ok = all(q == self.rank or d == mine[1] or _can_access_peer(mine[1], d) for q, (_, d) in enumerate(everyone))
+        if len({d for _, d in everyone}) < self.world:
+            ok = False  # two ranks on one device: kernels that wait on one another must not share a GPU
+        verdicts: list = [None] * self.world
+        dist.all_gather_object(verdicts, bool(ok), group=self.group)
+        if not all(verdicts):
+            return "a rank has no peer access to another rank's GPU (or two ranks share one GPU)"
+        return None
 
     def _alloc_flat(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
         """Flat buffer in ordinary allocator memory, or (p2p) in cudaMalloc'ed memory
@@ -171,7 +200,8 @@ class TrainEngine:
         if int(agreed.item()) == 0:
             if self._comm_mode == "nvls":
                 raise RuntimeError(f"comm='nvls' is not available on this system: {err or 'another rank failed'}")
-            log.info("NVLink multicast not used (%s); falling back to CUDA IPC peer mappings", err or "another rank failed")
+            log.info("NVLink multicast not used (%s)", err or "another rank failed")
+            self._multicast_refused = self.world > 2 and self._comm_mode == "auto"
             return None
         self._symm_handles = handles  # keeps the mappings alive
         return bufs[0], bufs[1]
@@ -229,6 +259,11 @@ class TrainEngine:
         self._peer_mapped: list[int] = []
         self._symm_handles = None
         pair = self._alloc_symmetric_pair(self.total, cfg.compute_dtype)
+        if pair is None and getattr(self, "_multicast_refused", False):
+            # measured at 8 ranks: per-peer loads / stores 2.78 ms, library collectives 2.01 ms
+            log.info("NVLink multicast is not available on more than two ranks; using the library collectives")
+            self.p2p = False
+            self._comm_mode = "nccl"
         if pair is not None:
             self.flat_w, self.flat_g = pair
         else:
@@ -367,7 +402,7 @@ class TrainEngine:
             ops.native().fused_sharded_adamw(
                 self.world, self.rank, self.hi - self.lo, self._g_ptrs, self._w_ptrs, self._ctl_ptrs, self._g_mc, self._w_mc,
                 self.master, self.exp_avg,
-                self.exp_avg_sq, self.grad_reduced, self.hyper, self.status,
+                self.exp_avg_sq, self.grad_reduced, self.hyper, self.status, peer_wait_spins(),
             )
             return
         if self.distributed and self.world > 1:
@@ -464,14 +499,20 @@ class TrainEngine:
             if self.cfg.compute_dtype != torch.float32:
                 self.flat_w[o : o + n].view(p.shape).copy_(master)
 
-    def check_status(self) -> None:
+    def check_status(self, code: int | None = None) -> None:
         """Raise if a bounded device-side wait of the fused step ran out (a peer did
-        not arrive).  Reads one int from the device, so call it where a host sync is
-        acceptable (logging steps, checkpoints)."""
-        code = int(self.status.item())
+        not arrive).  A step whose wait ran out applied no update on this rank and the ranks'
+        barrier generations no longer pair up, so training must stop here, not continue.
+        Without ``code`` this reads one int from the device, so call it where a host sync is
+        acceptable; the trainer passes the value it copied out with its step record."""
+        if code is None:
+            code = int(self.status.item())
         if code != 0:
             names = {11: "gradient barrier", 12: "norm barrier", 13: "closing barrier", 14: "local release"}
-            raise RuntimeError(f"fused optimizer step timed out waiting at the {names.get(code, code)}: a peer rank did not arrive")
+            raise RuntimeError(
+                f"fused optimizer step timed out waiting at the {names.get(code, code)}: a peer rank did not arrive within "
+                f"{peer_wait_seconds():.0f} s (SB200_PEER_WAIT_S); the step was not applied on rank {self.rank}"
+            )
 
     def close(self) -> None:
         """Unmap peers' buffers and free exported memory (p2p mode)."""
@@ -496,10 +537,27 @@ class TrainEngine:
         dist.all_gather_into_tensor(full, shard.contiguous(), group=self.group)
         return full
 
-    def optimizer_state_dict(self) -> dict:
-        """Full (unsharded) optimizer state keyed by parameter name; every rank
-        participates in the gathers, all ranks receive the result."""
-        master, m, v = (self._gather_full(t) for t in (self.master, self.exp_avg, self.exp_avg_sq))
+    def _gather_to_first(self, shard: torch.Tensor) -> torch.Tensor | None:
+        """The full tensor on the group's first rank (``None`` elsewhere): only the writer of a
+        checkpoint pays the memory and the device-to-host copy."""
+        if not self.sharded:
+            return shard
+        dst = dist.get_global_rank(self.group, 0) if self.group is not None else 0
+        if self.rank == 0:
+            full = torch.empty(self.total, dtype=shard.dtype, device=shard.device)
+            dist.gather(shard.contiguous(), list(full.chunk(self.world)), dst=dst, group=self.group)
+            return full
+        dist.gather(shard.contiguous(), None, dst=dst, group=self.group)
+        return None
+
+    def optimizer_state_dict(self, first_rank_only: bool = False) -> dict:
+        """Full (unsharded) optimizer state keyed by parameter name; every rank participates in
+        the gathers.  With ``first_rank_only`` the tensors are assembled on the group's first
+        rank alone and the other ranks get a dict without ``state`` entries."""
+        gather = self._gather_to_first if first_rank_only else self._gather_full
+        master, m, v = (gather(t) for t in (self.master, self.exp_avg, self.exp_avg_sq))
+        if master is None:
+            return {"step": self.step_count, "optimizer": self.cfg.optimizer, "state": {}}
         state = {}
         for name, p, o in zip(self.names, self.params, self.offsets):
             n = p.numel()
@@ -511,7 +569,18 @@ class TrainEngine:
         return {"step": self.step_count, "optimizer": self.cfg.optimizer, "state": state}
 
     def load_optimizer_state_dict(self, sd: dict) -> None:
+        """Restore ``optimizer_state_dict`` output.  A ``torch.optim`` state dict (integer keys
+        plus ``param_groups``: what the reference's checkpoints hold) is a different format: it is
+        not mapped, the optimizer starts fresh and a warning says so."""
+        if "param_groups" in sd or any(isinstance(k, int) for k in sd.get("state", {})):
+            log.warning(
+                "optimizer state is in torch.optim format (integer parameter indices + param_groups), not this engine's "
+                "name-keyed format: moments and step count are NOT restored; the optimizer starts fresh from the loaded weights."
+            )
+            return
         self.step_count = int(sd.get("step", 0))
+        if not any(name in sd.get("state", {}) for name in self.names):
+            log.warning("optimizer state matches none of the %d trainable parameter names: nothing restored.", len(self.names))
         for name, p, o in zip(self.names, self.params, self.offsets):
             entry = sd["state"].get(name)
             if entry is None:
@@ -545,6 +614,29 @@ class TrainEngine:
             name: master[o : o + p.numel()].view(p.shape).clone()
             for name, p, o in zip(self.names, self.params, self.offsets)
         }
+
+
+def peer_wait_seconds() -> float:
+    """Budget of every cross-rank wait inside the peer-memory kernels (optimizer barriers,
+    expert-parallel exchange).  The library collectives they replace tolerate minutes of rank
+    skew (a stalled hidden-state fetch, a one-sided graph capture, logging on rank 0), so the
+    default is tens of seconds; it stays bounded so that a lost peer ends in an error."""
+    try:
+        return min(240.0, max(0.001, float(os.environ.get("SB200_PEER_WAIT_S", "30"))))
+    except ValueError:
+        return 30.0
+
+
+def peer_wait_spins(per_second: int = 1 << 24) -> int:
+    """The budget as poll iterations (one poll plus a 64 ns back-off is about 60 ns)."""
+    return int(min(0xFFFFFFF0, max(1, peer_wait_seconds() * per_second)))
+
+
+def _can_access_peer(a: int, b: int) -> bool:
+    try:
+        return bool(torch.cuda.can_device_access_peer(a, b))
+    except Exception:  # noqa: BLE001 - an unknown device index counts as "no"
+        return False
 
 
 def _newton_schulz(g: torch.Tensor, steps: int) -> torch.Tensor:

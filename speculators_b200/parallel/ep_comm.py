@@ -90,7 +90,7 @@ class EpComm:
     of one process to each other (tests)."""
 
     def __init__(self, group, hidden: int, capacity_rows: int, device: torch.device, *, rank: int | None = None,
-                 world: int | None = None, spin_limit: int = 1 << 24):
+                 world: int | None = None, spin_limit: int | None = None):
         if hidden % 8:
             raise ValueError("hidden size must be a multiple of 8")
         self.group = group
@@ -99,7 +99,11 @@ class EpComm:
         if not 1 <= self.world <= 16:
             raise ValueError("expert-parallel groups of 1..16 ranks are supported")
         self.hidden, self.capacity, self.device = hidden, int(capacity_rows), torch.device(device)
-        self.spin_limit = spin_limit
+        if spin_limit is None:  # tens of seconds by default (SB200_PEER_WAIT_S), like the optimizer's barriers
+            from speculators_b200.parallel.engine import peer_wait_spins
+
+            spin_limit = peer_wait_spins()
+        self.spin_limit = int(spin_limit)
         self._nat = ops.native()
         self._seq = 0
         self._calls = 0
@@ -191,8 +195,11 @@ class EpComm:
         self._nat.ep_pull(self.ptrs[(kind, parity)], self.capacity, plan.dst_rank, plan.dst_pos, weight, self.world, out, plan.top_k, rows)
         return (out, rows) if keep_rows else out
 
-    def check_status(self) -> None:
-        code = int(self.status.item())
+    def check_status(self, code: int | None = None) -> None:
+        """Raise if a wait of the exchange ran out: the rows read after such a wait are stale, so
+        training must stop.  ``code``: a value of the status word already copied to the host."""
+        if code is None:
+            code = int(self.status.item())
         if code:
             raise RuntimeError(f"expert-parallel exchange: a rank did not arrive within the wait budget (status {code})")
 

@@ -1,8 +1,11 @@
 """Checkpoint layout, save / load, best-epoch bookkeeping.
 
-On disk (identical to src/speculators/train/checkpointer.py:54-68 so runs can
-be resumed across implementations and every epoch directory is directly
-``vllm serve``-able)::
+On disk (same directory layout as src/speculators/train/checkpointer.py:54-68; every epoch
+directory is directly ``vllm serve``-able).  ``config.json`` and ``model.safetensors`` are
+interchangeable with the reference.  ``optimizer_state_dict.pt`` and
+``scheduler_state_dict.pt`` are not: they hold this engine's name-keyed fp32 master / moment
+tensors and an ``LRSchedule`` state, where the reference stores ``torch.optim`` state dicts
+keyed by parameter index; loading the other format restarts the optimizer with a warning::
 
     <save_path>/<epoch>/config.json, model.safetensors (bf16),
                         optimizer_state_dict.pt, scheduler_state_dict.pt,
@@ -12,8 +15,8 @@ be resumed across implementations and every epoch directory is directly
     <save_path>/interrupted/                       written on graceful shutdown
 
 One class serves single-process, replicated and sharded training: the engine
-returns full (gathered) tensors from ``optimizer_state_dict`` /
-``master_state_dict`` on every rank, rank 0 writes, everyone meets at a barrier.
+gathers ``master_state_dict`` on every rank (every rank's model copy stays complete) and the
+optimizer state on rank 0 only, rank 0 writes, everyone meets at a barrier.
 The reference needs two classes because FSDP2 state lives in DTensors
 (``DistributedCheckpointer``, :359-438); both names are kept as aliases.
 """
@@ -125,7 +128,7 @@ class Checkpointer:
         if engine is not None:
             for name, tensor in engine.master_state_dict().items():  # collective in sharded mode
                 _assign_master(state, name, tensor)
-            opt_state = engine.optimizer_state_dict()  # collective in sharded mode
+            opt_state = engine.optimizer_state_dict(first_rank_only=True)  # collective in sharded mode
         if _is_rank0():
             target.mkdir(parents=True, exist_ok=True)
             inner = _unwrap(model)

@@ -499,6 +499,7 @@ class Trainer:
                 self._flush_step_log()
                 self.maybe_save_checkpoint(epoch, local_step=local_step)
         self._flush_step_log()
+        self.check_device_status()
 
     # ------------------------------------------------------------------ step logging
     def _queue_step_log(self, epoch: int, lr_now: float, metrics: dict, batch) -> None:  # noqa: ANN001
@@ -516,11 +517,8 @@ class Trainer:
         elif doc is not None:
             entries.append((doc != -1).sum().float())  # counted on the device, read with the rest
         has_count = doc is not None and doc.device.type != "cpu"
-        status = None
-        if self.device_type == "cuda":
-            from speculators_b200.ops import gemm_status
-
-            status = gemm_status(self.device).float().reshape(())
+        words = self._status_words()
+        status = torch.cat([w.reshape(1) for _, w, _ in words]).float() if words else None
         host = event = None
         n_metrics = len(keys)
         if entries or status is not None:
@@ -530,7 +528,7 @@ class Trainer:
                 dist.reduce(head, dst=0, op=dist.ReduceOp.SUM)
                 stacked = torch.cat([head, stacked[n_metrics:]])
             if status is not None:
-                stacked = torch.cat([stacked, status.reshape(1)])
+                stacked = torch.cat([stacked, status])
             host = torch.empty(stacked.shape, dtype=torch.float32, pin_memory=self.device_type == "cuda")
             host.copy_(stacked, non_blocking=True)
             if self.device_type == "cuda":
@@ -539,8 +537,38 @@ class Trainer:
         self._pending_step_log = {
             "keys": keys, "host": host, "event": event, "timer": self.timer.snapshot(), "epoch": epoch, "lr": lr_now,
             "engine": self.engine if self._graphed is None else None,
-            "global_step": self.global_step, "num_tokens": num_tokens, "has_count": has_count, "has_status": status is not None,
+            "global_step": self.global_step, "num_tokens": num_tokens, "has_count": has_count, "status_checks": [(label, check) for label, _, check in words],
         }
+
+    def _status_words(self) -> list:
+        """``(label, device int32 word, check(code))`` of everything on this rank that reports
+        a bounded wait running out: the tcgen05 kernels, the peer-memory optimizer step, every
+        expert-parallel exchange.  Their values ride along with the logged step's record; a
+        non-zero value stops training (the step that set it did no update, or read stale rows)."""
+        if self.device_type != "cuda":
+            return []
+        from speculators_b200.ops import check_gemm_status, gemm_status
+
+        words = [("tcgen05", gemm_status(self.device), lambda _code: check_gemm_status())]
+        words.append(("optimizer", self.engine.status, self.engine.check_status))
+        for name, mod in self.model.named_modules():
+            comm = getattr(mod, "_comm", None)
+            if comm is not None and hasattr(comm, "status") and hasattr(comm, "check_status"):
+                words.append((f"expert exchange {name}", comm.status, comm.check_status))
+        return words
+
+    def check_device_status(self) -> None:
+        """Read every status word now (one host synchronisation) and raise on the first that is
+        set.  Called before a checkpoint is written and at the end of an epoch, so that weights
+        produced after a failed wait are never saved as if they were good."""
+        words = self._status_words()
+        if not words:
+            return
+        codes = torch.cat([w.reshape(1) for _, w, _ in words]).tolist()
+        for (label, _, check), code in zip(words, codes):
+            if code != 0:
+                root_logger.error("device status word '%s' = %d: stopping", label, int(code))
+                check(int(code))
 
     def _flush_step_log(self) -> None:
         pending = getattr(self, "_pending_step_log", None)
@@ -556,10 +584,11 @@ class Trainer:
         num_tokens = pending["num_tokens"]
         if pending["has_count"]:
             num_tokens = int(rest.pop(0))
-        if pending["has_status"] and rest and rest[-1] != 0:
-            from speculators_b200.ops import check_gemm_status
-
-            check_gemm_status()  # raises with the code of the wait that ran out
+        checks = pending["status_checks"]
+        for (label, check), code in zip(checks, rest[len(rest) - len(checks):] if checks else []):
+            if code != 0:
+                root_logger.error("device status word '%s' = %d at global step %d: stopping", label, int(code), pending["global_step"])
+                check(int(code))  # raises with the meaning of the code
         profile = pending["timer"].profile(num_tokens, synchronize=pending["event"] is None)  # the marks precede the copy's event
         if profile is not None and pending.get("engine") is not None:
             comm = pending["engine"].exposed_comm_ms()  # library collectives of that step; None: none timed
@@ -615,6 +644,8 @@ class Trainer:
             or (cfg.checkpoint_freq >= 1 and isinstance(epoch, int) and epoch != 0 and (epoch + 1) % cfg.checkpoint_freq != 0)
         ):
             return
+        if epoch != "interrupted":
+            self.check_device_status()
         root_logger.info("Saving checkpoint to %s", self.checkpointer.path / str(epoch))
         self.checkpointer.save_checkpoint(self.model, self.engine, epoch)
         if self.schedulers:

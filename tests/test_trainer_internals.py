@@ -247,3 +247,46 @@ def test_step_records_are_emitted_in_order_one_step_late_and_flushed(tiny_verifi
     losses = [r["train"]["loss"] for r in records]
     assert losses[-1] < losses[0]
     assert getattr(trainer, "_pending_step_log", None) is None
+
+
+@pytest.mark.parametrize("log_freq", [1, 10**9])
+def test_device_status_word_stops_training(tiny_verifier_dir, tiny_vocab_maps, tmp_path, log_freq):
+    """A status word that a bounded device wait set (here: injected on the host) must end the
+    run with an error: on the next logged step when steps are logged, else at the end of the
+    epoch, and before any checkpoint is written."""
+    kwargs, _ = sb.Eagle3DraftModel.get_trainer_kwargs(loss_fn="kl_div", ttt_steps=2, ttt_step_loss_decay=1.0)
+    batches = [make_tiny_batch(T=32, seed=s) for s in range(3)]
+    model = make_tiny_eagle3(tiny_verifier_dir, tiny_vocab_maps)
+    tr = Trainer(model, TrainerConfig(lr=1e-3, num_epochs=1, save_path=str(tmp_path), train_call_kwargs=kwargs, scheduler_type="none",
+                                      log_freq=log_freq, device="cpu"), SyntheticLoader(batches, 3))
+    word = torch.zeros(1, dtype=torch.int32)
+    tr._status_words = lambda: [("optimizer", word, tr.engine.check_status)]
+    tr.train_epoch(0)  # all clear: runs through
+    word.fill_(11)
+    with pytest.raises(RuntimeError, match="fused optimizer step timed out waiting at the gradient barrier"):
+        tr.train_epoch(0)
+    with pytest.raises(RuntimeError, match="timed out"):
+        tr.maybe_save_checkpoint(0)
+    assert not (tmp_path / "0").exists()
+
+
+def test_optimizer_state_formats(tiny_verifier_dir, tiny_vocab_maps, tmp_path, caplog):
+    """A torch.optim-format state dict (what the reference's checkpoints hold) is recognised
+    and refused with a warning instead of being skipped silently."""
+    import logging
+
+    from speculators_b200.parallel.engine import EngineConfig, TrainEngine
+
+    eng = TrainEngine(make_tiny_eagle3(tiny_verifier_dir, tiny_vocab_maps), EngineConfig(compute_dtype=torch.float32), device="cpu")
+    eng.step_count = 5
+    own = eng.optimizer_state_dict(first_rank_only=True)
+    assert own["step"] == 5 and set(own["state"]) == set(eng.names)
+    with caplog.at_level(logging.WARNING):
+        eng.load_optimizer_state_dict({"state": {0: {"step": torch.tensor(3.0)}}, "param_groups": [{"lr": 1e-4, "params": [0]}]})
+    assert "torch.optim format" in caplog.text and eng.step_count == 5
+    caplog.clear()
+    with caplog.at_level(logging.WARNING):
+        eng.load_optimizer_state_dict({"step": 2, "state": {"no.such.weight": {}}})
+    assert "matches none" in caplog.text and eng.step_count == 2
+    eng.load_optimizer_state_dict(own)
+    assert eng.step_count == 5
