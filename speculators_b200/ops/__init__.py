@@ -31,6 +31,9 @@ __all__ = [
     "gemm_status",
     "linear",
     "masked_attention",
+    "matmul_nn",
+    "matmul_nt",
+    "matmul_tn",
     "masked_attention_reference",
     "native",
     "rms_norm",
@@ -111,6 +114,49 @@ def _forward_gemm(x2: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | No
     return x2 @ w.t()
 
 
+def _dgrad_gemm(dy2: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
+    """``dy2 @ w`` (input gradient of a linear layer) on the tcgen05 kernel: the weight is read
+    as stored, ``[out, in]`` with ``in`` contiguous, as an MN-major B operand."""
+    dx = out if out is not None else torch.empty((dy2.shape[0], w.shape[1]), dtype=dy2.dtype, device=dy2.device)
+    native().gemm(dy2, w, dx, 1 if accumulate else 0, False, True, gemm_status(dy2.device))
+    return dx
+
+
+def _wgrad_gemm(dy2: torch.Tensor, x2: torch.Tensor, out: torch.Tensor | None, accumulate: bool) -> torch.Tensor:
+    """``dy2.T @ x2`` (weight gradient) on the tcgen05 kernel, both operands read in place as
+    MN-major tiles, stored into or added to ``out`` in the epilogue."""
+    if out is None:
+        out = torch.empty((dy2.shape[1], x2.shape[1]), dtype=dy2.dtype, device=dy2.device)
+    native().gemm(dy2, x2, out, 1 if accumulate else 0, True, True, gemm_status(dy2.device))
+    return out
+
+
+def matmul_nt(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """``a @ b.T`` for 2-D tensors; bf16 CUDA operands with aligned rows use the tcgen05 kernel."""
+    if _gemm_operand_ok(a) and _gemm_operand_ok(b) and _own_gemm_enabled():
+        return _forward_gemm(a, b, None)
+    return a @ b.t()
+
+
+def matmul_nn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
+    """``a @ b`` for 2-D tensors (``b`` read as stored, no transpose copy), optionally stored
+    into / added to ``out``."""
+    if _gemm_operand_ok(a) and _gemm_operand_ok(b) and _own_gemm_enabled() and (out is None or _gemm_operand_ok(out)):
+        return _dgrad_gemm(a, b, out, accumulate)
+    if out is None:
+        return a @ b
+    return out.addmm_(a, b) if accumulate else torch.mm(a, b, out=out)
+
+
+def matmul_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
+    """``a.T @ b`` for 2-D tensors, optionally stored into / added to ``out``."""
+    if _gemm_operand_ok(a) and _gemm_operand_ok(b) and _own_gemm_enabled() and (out is None or _gemm_operand_ok(out)):
+        return _wgrad_gemm(a, b, out, accumulate)
+    if out is None:
+        return a.t() @ b
+    return out.addmm_(a.t(), b) if accumulate else torch.mm(a.t(), b, out=out)
+
+
 class _LinearFn(torch.autograd.Function):
     """``y = x @ W[rows].T (+ residual)`` with the weight gradient accumulated in place.
 
@@ -137,30 +183,36 @@ class _LinearFn(torch.autograd.Function):
         x2, weight = ctx.saved_tensors
         r0, r1 = ctx.rows
         w = weight if r0 is None else weight[r0:r1]
-        dy2 = dy if dy.is_contiguous() else dy.contiguous()
+        dy2 = dy if (dy.stride(-1) == 1 and dy.stride(0) % 8 == 0 and dy.data_ptr() % 16 == 0) else dy.contiguous()
         dx = dw = None
+        own = _own_gemm_enabled() and _gemm_operand_ok(dy2) and _gemm_operand_ok(w) and _gemm_operand_ok(x2)
         if ctx.needs_input_grad[0]:
-            dx = dy2 @ w
+            dx = _dgrad_gemm(dy2, w) if own else dy2 @ w
         if ctx.needs_input_grad[1]:
             flat = getattr(weight, "_flat_grad", None)
             if flat is not None:
-                if getattr(weight, "_grad_fresh", False):
+                target = flat if r0 is None else flat[r0:r1]
+                fresh = getattr(weight, "_grad_fresh", False)
+                if fresh:
                     # first gradient of this weight since the engine's zero_grad, which left
                     # the buffer uncleared: store instead of accumulate
                     weight._grad_fresh = False
-                    if r0 is None:
-                        torch.mm(dy2.t(), x2, out=flat)
-                    else:
+                    if r0 is not None:
                         flat.zero_()
-                        flat[r0:r1].addmm_(dy2.t(), x2)
+                if own and _gemm_operand_ok(target):
+                    _wgrad_gemm(dy2, x2, target, accumulate=not fresh or r0 is not None)
+                elif fresh and r0 is None:
+                    torch.mm(dy2.t(), x2, out=flat)
                 else:
-                    target = flat if r0 is None else flat[r0:r1]
                     target.addmm_(dy2.t(), x2)
             elif r0 is None:
-                dw = dy2.t() @ x2
+                dw = _wgrad_gemm(dy2, x2, None, accumulate=False) if own else dy2.t() @ x2
             else:
                 dw = torch.zeros_like(weight)
-                dw[r0:r1] = dy2.t() @ x2
+                if own and _gemm_operand_ok(dw[r0:r1]):
+                    _wgrad_gemm(dy2, x2, dw[r0:r1], accumulate=False)
+                else:
+                    dw[r0:r1] = dy2.t() @ x2
         dres = dy if ctx.has_residual and ctx.needs_input_grad[2] else None
         return dx, dw, dres, None, None
 
@@ -170,8 +222,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
     """``x @ weight[rows].T (+ bias) (+ residual)``.  On CUDA in bf16 the forward product
     runs on the package's tcgen05 GEMM with the residual read in its epilogue
     (``SB200_LINEAR_GEMM=cublas`` sends it to the library instead); the two backward
-    products are library GEMMs, the weight gradient accumulating in place into the
-    engine's flat gradient buffer."""
+    products run on the same kernel with the transposed operands read in place (MN-major
+    tiles), the weight gradient accumulating in the epilogue into the engine's flat
+    gradient buffer."""
     if x.is_cuda and (weight.requires_grad or x.requires_grad) and torch.is_grad_enabled():
         r0, r1 = rows if rows is not None else (None, None)
         lead = x.shape[:-1]

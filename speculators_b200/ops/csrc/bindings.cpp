@@ -32,6 +32,8 @@ int launch_loss_bwd(int, const void*, const void*, const float*, const float*, v
 int64_t launch_count();
 int launch_gemm_tn_tcgen05(const void*, const void*, void*, const void*, int, int, int, int64_t, int64_t, int64_t, int64_t, int,
                            int*, int, cudaStream_t);
+int launch_gemm_tcgen05(const void*, const void*, void*, const void*, int, int, int, int64_t, int64_t, int64_t, int64_t, int, int, int,
+                        int*, int, cudaStream_t);
 int sumsq_num_partials();
 int peer_malloc(int64_t, void**);
 int peer_free(void*);
@@ -50,6 +52,8 @@ void launch_sumsq(const void*, int, int64_t, float*, float*, int, cudaStream_t);
 void launch_set_hyper(float*, const float*, cudaStream_t);
 void launch_adamw(float*, float*, float*, const void*, int, void*, int64_t, const float*,
                   const float*, cudaStream_t);
+void launch_muon_momentum(const void*, int, float*, void*, int64_t, const float*, const float*, float, int, float*, float*, cudaStream_t);
+void launch_muon_apply(float*, const void*, void*, int64_t, const float*, float, float, float, cudaStream_t);
 }  // namespace sb200
 
 namespace {
@@ -231,6 +235,44 @@ void sumsq(const Tensor& g, Tensor out, bool accumulate) {
   sb200::launch_sumsq(g.data_ptr(), g.scalar_type() == at::kBFloat16, g.numel(),
                       partial.data_ptr<float>(), out.data_ptr<float>(), accumulate, cur_stream());
 }
+
+// Muon, first half: buf <- momentum update of the clipped gradient, out <- bf16 (nesterov) update,
+// out_sumsq[0] <- squared Frobenius norm of out.  partial: fp32[sumsq_num_partials()] scratch.
+void muon_momentum(const Tensor& grad, Tensor buf, Tensor out, const Tensor& hyper, const Tensor& norm_sq, double momentum, bool nesterov,
+                   Tensor partial, Tensor out_sumsq) {
+  const int64_t n = buf.numel();
+  TORCH_CHECK(grad.is_cuda() && grad.is_contiguous() && grad.numel() == n &&
+              (grad.scalar_type() == at::kBFloat16 || grad.scalar_type() == at::kFloat));
+  TORCH_CHECK(buf.is_cuda() && buf.scalar_type() == at::kFloat && buf.is_contiguous());
+  TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kBFloat16 && out.is_contiguous() && out.numel() == n);
+  TORCH_CHECK(hyper.is_cuda() && hyper.scalar_type() == at::kFloat && hyper.numel() >= 9);
+  TORCH_CHECK(norm_sq.is_cuda() && norm_sq.scalar_type() == at::kFloat && norm_sq.numel() >= 1);
+  TORCH_CHECK(partial.is_cuda() && partial.scalar_type() == at::kFloat && partial.numel() >= sb200::sumsq_num_partials());
+  TORCH_CHECK(out_sumsq.is_cuda() && out_sumsq.scalar_type() == at::kFloat && out_sumsq.numel() >= 1);
+  c10::cuda::CUDAGuard guard(buf.device());
+  sb200::launch_muon_momentum(grad.data_ptr(), grad.scalar_type() == at::kBFloat16, buf.data_ptr<float>(), out.data_ptr(), n,
+                              hyper.data_ptr<float>(), norm_sq.data_ptr<float>(), (float)momentum, nesterov ? 1 : 0,
+                              partial.data_ptr<float>(), out_sumsq.data_ptr<float>(), cur_stream());
+}
+
+// Muon, second half: master <- master * (1 - lr * wd) - lr * adjust * update, w16 <- bf16(master); lr = hyper[0] * lr_ratio.
+void muon_apply(Tensor master, const Tensor& update, c10::optional<Tensor> w16, const Tensor& hyper, double lr_ratio, double weight_decay,
+                double adjust) {
+  const int64_t n = master.numel();
+  TORCH_CHECK(master.is_cuda() && master.scalar_type() == at::kFloat && master.is_contiguous());
+  TORCH_CHECK(update.is_cuda() && update.scalar_type() == at::kBFloat16 && update.is_contiguous() && update.numel() == n);
+  TORCH_CHECK(hyper.is_cuda() && hyper.scalar_type() == at::kFloat && hyper.numel() >= 9);
+  void* w = nullptr;
+  if (w16.has_value()) {
+    TORCH_CHECK(w16->is_cuda() && w16->scalar_type() == at::kBFloat16 && w16->numel() == n && w16->is_contiguous());
+    w = w16->data_ptr();
+  }
+  c10::cuda::CUDAGuard guard(master.device());
+  sb200::launch_muon_apply(master.data_ptr<float>(), update.data_ptr(), w, n, hyper.data_ptr<float>(), (float)lr_ratio,
+                           (float)weight_decay, (float)adjust, cur_stream());
+}
+
+int64_t sumsq_num_partials_binding() { return sb200::sumsq_num_partials(); }
 
 // hyper (fp32[16], CUDA) <- vals (<= 16 host doubles), passed as kernel arguments.
 void set_hyper(Tensor hyper, std::vector<double> vals) {
@@ -494,6 +536,27 @@ void gemm_tn(const Tensor& a, const Tensor& b, Tensor out, const c10::optional<T
   gemm_tn_variant(a, b, out, residual, epilogue, status, 0);
 }
 
+// out[M,N] (=, +=) op(a) @ op(b)^T with either operand stored transposed:
+//   a_mn false: a is [M, K];  true: a is [K, M] (the product uses a^T, read in place)
+//   b_mn false: b is [N, K];  true: b is [K, N]
+// dgrad of a linear layer: gemm(dy[T,out], w[out,in], dx, b_mn = true);
+// wgrad: gemm(dy[T,out], x[T,in], dw[out,in], a_mn = b_mn = true, epilogue 1 to accumulate).
+void gemm(const Tensor& a, const Tensor& b, Tensor out, int64_t epilogue, bool a_mn, bool b_mn, Tensor status) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && out.is_cuda() && status.is_cuda());
+  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16);
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && out.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && out.stride(1) == 1);
+  TORCH_CHECK(epilogue == 0 || epilogue == 1, "gemm: epilogue 0 (store) or 1 (accumulate)");
+  const int64_t M = a_mn ? a.size(1) : a.size(0), K = a_mn ? a.size(0) : a.size(1);
+  const int64_t N = b_mn ? b.size(1) : b.size(0), Kb = b_mn ? b.size(0) : b.size(1);
+  TORCH_CHECK(K == Kb && out.size(0) == M && out.size(1) == N, "gemm: shape mismatch");
+  TORCH_CHECK(status.scalar_type() == at::kInt && status.numel() >= 1);
+  c10::cuda::CUDAGuard guard(a.device());
+  const int rc = sb200::launch_gemm_tcgen05(a.data_ptr(), b.data_ptr(), out.data_ptr(), nullptr, (int)M, (int)N, (int)K, a.stride(0),
+                                            b.stride(0), out.stride(0), 0, (int)epilogue, a_mn ? 1 : 0, b_mn ? 1 : 0,
+                                            status.data_ptr<int>(), 0, cur_stream());
+  TORCH_CHECK(rc == 0, "gemm launch failed (", rc, ")");
+}
+
 // ---- masked attention ------------------------------------------------------------------
 void check_heads(const Tensor& t, const char* name, int64_t hd) {
   TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.dim() == 3, name, ": bf16 CUDA [T, heads, hd] expected");
@@ -646,6 +709,9 @@ TORCH_LIBRARY(sb200, m) {
   m.def("ce_label_fwd", &ce_label_fwd);
   m.def("sumsq", &sumsq);
   m.def("adamw", &adamw);
+  m.def("muon_momentum", &muon_momentum);
+  m.def("muon_apply", &muon_apply);
+  m.def("sumsq_num_partials", &sumsq_num_partials_binding);
   m.def("set_hyper", &set_hyper);
   m.def("launch_count", &launch_count);
   m.def("peer_alloc", &peer_alloc);
@@ -667,6 +733,7 @@ TORCH_LIBRARY(sb200, m) {
   m.def("hs_push", &hs_push);
   m.def("hs_pop", &hs_pop);
   m.def("gemm_tn", &gemm_tn);
+  m.def("gemm", &gemm);
   m.def("gemm_tn_variant", &gemm_tn_variant);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_fwd_tc", &attn_fwd_tc);

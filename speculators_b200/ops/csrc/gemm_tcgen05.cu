@@ -23,6 +23,16 @@
 // CTAs' TMEM, and completion is multicast to the barriers of both CTAs.  Halving the B
 // traffic per SM is what the L2-to-SM path needs to keep the tensor pipe fed.
 //
+// Operand layouts.  The forward product has both operands K-major (rows of A and of B run
+// along the contraction).  The backward products of a linear layer do not:
+//   dgrad  dX[T,in]  = dY[T,out] * W[out,in]        B is read as stored, [K, N] with N contiguous
+//   wgrad  dW[out,in] (+)= dY[T,out]^T * X[T,in]    A is [K, M] with M contiguous, B is [K, N]
+// The CTA-pair kernel therefore takes each operand either K-major or MN-major (template flags):
+// an MN-major operand is staged by TMA as boxes of 64 MN-elements x 128 contraction rows (the
+// same 16 KB, 128-byte swizzle) and described to the tensor core with an MN-major shared-memory
+// descriptor plus the transpose bit of the instruction descriptor, so no operand is ever
+// transposed in memory.
+//
 // Every wait is bounded: a thread that exhausts its poll budget records a code in the
 // caller's status word and leaves its loop; the other roles then run out of budget (or
 // see the status word) too, the CTA meets at the final barrier, frees its TMEM and
@@ -115,6 +125,59 @@ __device__ __forceinline__ void store_accumulator(const Params& p, uint32_t tadd
   }
 }
 
+// ---- epilogues that read memory (C += result, result + residual) ---------------------------
+// The addend row (256 bf16 = 512 bytes per thread) is fetched into registers *before* the
+// thread waits for the accumulator, so the loads' latency is spent while the tensor core still
+// works on the tile.  With a short contraction (weight gradients: K = tokens of one step) the
+// time per tile is otherwise set by eight dependent load round trips per thread.
+struct RowPrefetch {
+  uint4 v[BN / 8];
+  bool valid;
+};
+
+__device__ __forceinline__ bool tile_reads_vectorised(const Params& p, int n0) {
+  if (p.epilogue == kStore || n0 + BN > p.N || (p.ldc & 7) || (reinterpret_cast<uintptr_t>(p.c) & 15)) return false;
+  if (p.epilogue == kAddResidual && ((p.ldr & 7) || (reinterpret_cast<uintptr_t>(p.residual) & 15))) return false;
+  return true;
+}
+
+__device__ __forceinline__ void prefetch_addend(const Params& p, int row, int n0, RowPrefetch& pre) {
+  pre.valid = tile_reads_vectorised(p, n0) && row < p.M;
+  if (pre.valid) {
+    const __nv_bfloat16* src = p.epilogue == kAccumulate ? p.c + (int64_t)row * p.ldc + n0 : p.residual + (int64_t)row * p.ldr + n0;
+#pragma unroll
+    for (int i = 0; i < BN / 8; ++i) pre.v[i] = __ldg(reinterpret_cast<const uint4*>(src) + i);
+  }
+}
+
+// Same result as store_accumulator for a row whose addend is already in registers.
+__device__ __forceinline__ void store_accumulator_prefetched(const Params& p, uint32_t taddr, int row, int n0, const RowPrefetch& pre) {
+  __nv_bfloat16* crow = p.c + (int64_t)row * p.ldc + n0;
+  const bool wide_ok = ((p.ldc & 15) == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 31) == 0);
+#pragma unroll
+  for (int c = 0; c < BN / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld32(taddr + c * 32, r);
+    tmem_ld_wait();
+    bf16x8 packed[4];
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      float f[8], o[8];
+      unpack8(*reinterpret_cast<const bf16x8*>(&pre.v[c * 4 + v]), o);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]) + o[j];
+      packed[v] = pack8(f);
+    }
+    if (wide_ok) {
+      st32(crow + c * 32, packed[0], packed[1]);
+      st32(crow + c * 32 + 16, packed[2], packed[3]);
+    } else {
+#pragma unroll
+      for (int v = 0; v < 4; ++v) st8(crow + c * 32 + v * 8, packed[v]);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
   extern __shared__ unsigned char smem_raw[];
@@ -202,11 +265,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
       const int acc = local & 1;
       const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+      RowPrefetch pre;
+      prefetch_addend(p, m0 + quarter * 32 + lane, n0, pre);
       ok = mbar_wait(smem_addr(&bar_acc_full[acc]), (local >> 1) & 1, p.status, kTimeoutEpilogue);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       fence_after_sync();
-      store_accumulator(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, m0 + quarter * 32 + lane, n0);
+      if (pre.valid) store_accumulator_prefetched(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, m0 + quarter * 32 + lane, n0, pre);
+      else store_accumulator(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, m0 + quarter * 32 + lane, n0);
       fence_before_sync();
       mbar_arrive(smem_addr(&bar_acc_empty[acc]));
     }
@@ -233,11 +299,12 @@ constexpr int P_A_BYTES = P_HALF * BK * 2, P_B_BYTES = P_HALF * BK * 2, P_SUB_BY
 constexpr int P_TILE_M = 2 * P_HALF, P_TILE_N = 2 * P_HALF;
 constexpr int P_RING_BYTES = 6 * P_SUB_BYTES;
 
-template <int KSUB>
+template <int KSUB, bool A_MN = false, bool B_MN = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  static_assert(KSUB == 2 || (!A_MN && !B_MN), "MN-major operands are staged as 128-row boxes: KSUB must be 2");
   constexpr int P_STAGES = 6 / KSUB;
   constexpr int P_STAGE_BYTES = KSUB * P_SUB_BYTES;
   constexpr int STAGE_K = KSUB * BK;
@@ -286,10 +353,15 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           if (leader) mbar_expect_tx(full_local, 2 * P_STAGE_BYTES);
           const uint32_t full_leader = map_to_cta(full_local, 0);
           const uint32_t sa = smem_addr(smem + stage * P_STAGE_BYTES);
+          // Elements outside the matrices read as zeros (TMA fill).  K-major operand: sub-tile u =
+          // 128 rows x 64 contraction columns.  MN-major operand: sub-tile u = 128 contraction rows x
+          // 64 MN-columns (MN-elements 64u .. 64u+63 of this CTA's 128).  Either way 16 KB at the same place.
 #pragma unroll
-          for (int u = 0; u < KSUB; ++u) {  // columns past K read as zeros (TMA fill)
-            tma_load_2d_pair(sa + u * P_SUB_BYTES, &map_a, full_leader, kb * STAGE_K + u * BK, m0);
-            tma_load_2d_pair(sa + u * P_SUB_BYTES + P_A_BYTES, &map_b, full_leader, kb * STAGE_K + u * BK, nb0);
+          for (int u = 0; u < KSUB; ++u) {
+            if (A_MN) tma_load_2d_pair(sa + u * P_SUB_BYTES, &map_a, full_leader, m0 + u * 64, kb * STAGE_K);
+            else tma_load_2d_pair(sa + u * P_SUB_BYTES, &map_a, full_leader, kb * STAGE_K + u * BK, m0);
+            if (B_MN) tma_load_2d_pair(sa + u * P_SUB_BYTES + P_A_BYTES, &map_b, full_leader, nb0 + u * 64, kb * STAGE_K);
+            else tma_load_2d_pair(sa + u * P_SUB_BYTES + P_A_BYTES, &map_b, full_leader, kb * STAGE_K + u * BK, nb0);
           }
           if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
         }
@@ -304,7 +376,7 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
     if (leader && lane == 0) {
-      constexpr uint32_t idesc = instr_desc_bf16(P_TILE_M, P_TILE_N);
+      constexpr uint32_t idesc = instr_desc_ab(P_TILE_M, P_TILE_N, A_MN, B_MN);
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       int local = 0;
@@ -317,14 +389,17 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           if (!(ok = mbar_wait(smem_addr(&bar_full[stage]), phase, p.status, kTimeoutMma))) break;
           fence_after_sync();
           const uint32_t sa = smem_addr(smem + stage * P_STAGE_BYTES);
-          const uint64_t adesc = smem_desc_kmajor_sw128(sa), bdesc = smem_desc_kmajor_sw128(sa + P_A_BYTES);
+          // MN-major: the two 64-element column blocks are P_SUB_BYTES apart (leading byte offset)
+          const uint64_t adesc = A_MN ? smem_desc_mnmajor_sw128(sa, P_SUB_BYTES) : smem_desc_kmajor_sw128(sa);
+          const uint64_t bdesc = B_MN ? smem_desc_mnmajor_sw128(sa + P_A_BYTES, P_SUB_BYTES) : smem_desc_kmajor_sw128(sa + P_A_BYTES);
 #pragma unroll
           for (int u = 0; u < KSUB; ++u) {
 #pragma unroll
             for (int k = 0; k < BK / 16; ++k) {
-              // next sub-tile: + P_SUB_BYTES; next 16 K-elements inside a 128-byte swizzled row: + 32 bytes (16-byte units)
-              const uint32_t off = u * (P_SUB_BYTES >> 4) + 2 * k;
-              umma_bf16_pair(tmem_d, adesc + off, bdesc + off, idesc, (kb | u | k) != 0);
+              // K-major: next sub-tile + P_SUB_BYTES, next 16 K-elements inside a 128-byte swizzled row + 32 bytes;
+              // MN-major: 16 contraction rows of 128 bytes = 2048 bytes per step (all in 16-byte units)
+              const uint32_t off_k = u * (P_SUB_BYTES >> 4) + 2 * k, off_mn = (u * (BK / 16) + k) * (2048 >> 4);
+              umma_bf16_pair(tmem_d, adesc + (A_MN ? off_mn : off_k), bdesc + (B_MN ? off_mn : off_k), idesc, (kb | u | k) != 0);
             }
           }
           umma_commit_pair(smem_addr(&bar_empty[stage]));  // frees the slot in both CTAs
@@ -342,11 +417,14 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
       const int acc = local & 1;
       const int m0 = (tile % tiles_m) * P_TILE_M + (int)rank * P_HALF, n0 = (tile / tiles_m) * P_TILE_N;
+      RowPrefetch pre;
+      prefetch_addend(p, m0 + quarter * 32 + lane, n0, pre);
       ok = mbar_wait(smem_addr(&bar_acc_full[acc]), (local >> 1) & 1, p.status, kTimeoutEpilogue);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       fence_after_sync();
-      store_accumulator(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, m0 + quarter * 32 + lane, n0);
+      if (pre.valid) store_accumulator_prefetched(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, m0 + quarter * 32 + lane, n0, pre);
+      else store_accumulator(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, m0 + quarter * 32 + lane, n0);
       fence_before_sync();
       mbar_arrive_cluster(acc_empty_leader[acc]);
     }
@@ -366,22 +444,27 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // ---- host side ---------------------------------------------------------------------------
 }  // namespace tc
 
-// C[M,N] = A[M,K] * B[N,K]^T with epilogue (0 store, 1 C += result, 2 result + residual).
-// lda / ldb / ldc / ldr in elements; A, B rows must be 16-byte aligned (ld multiple of 8).
+// C[M,N] = op(A) * op(B)^T with epilogue (0 store, 1 C += result, 2 result + residual).
+//   a_mn == 0: A is [M, K] row-major (K-major), lda = row stride;  a_mn == 1: A is [K, M] row-major (M contiguous)
+//   b_mn == 0: B is [N, K] row-major (K-major), ldb = row stride;  b_mn == 1: B is [K, N] row-major (N contiguous)
+// lda / ldb / ldc / ldr in elements; operand rows must be 16-byte aligned (ld multiple of 8).
 // `status` is a device int the kernel writes a non-zero code to if a bounded wait ran out.
-// variant: 0 = choose (CTA pairs when M > 128), 1 = one CTA per 128x256 tile, 2 = CTA pairs with
-// 64-wide K stages, 3 = CTA pairs with 128-wide K stages.
-int launch_gemm_tn_tcgen05(const void* a, const void* b, void* c, const void* residual, int M, int N, int K, int64_t lda,
-                           int64_t ldb, int64_t ldc, int64_t ldr, int epilogue, int* status, int variant, cudaStream_t stream) {
+// variant: 0 = choose (CTA pairs when M > 128 or an operand is MN-major), 1 = one CTA per 128x256 tile (K-major
+// only), 2 = CTA pairs with 64-wide K stages (K-major only), 3 = CTA pairs with 128-wide K stages.
+int launch_gemm_tcgen05(const void* a, const void* b, void* c, const void* residual, int M, int N, int K, int64_t lda,
+                        int64_t ldb, int64_t ldc, int64_t ldr, int epilogue, int a_mn, int b_mn, int* status, int variant,
+                        cudaStream_t stream) {
   using namespace tc;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda & 7) || (ldb & 7) || (reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15)) return -1;
-  if (variant == 0) variant = M > BM ? kDefaultPairVariant : 1;
+  const bool mn = a_mn || b_mn;
+  if (variant == 0) variant = (M > BM || mn) ? kDefaultPairVariant : 1;
+  if (mn && variant != 3) return -4;
   const bool pairs = variant >= 2;
   CUtensorMap map_a, map_b;
-  int rc = make_map_bf16(&map_a, a, M, K, lda, BM);
+  int rc = a_mn ? make_map_bf16(&map_a, a, K, M, lda, 2 * BK) : make_map_bf16(&map_a, a, M, K, lda, BM);
   if (rc) return rc;
-  rc = make_map_bf16(&map_b, b, N, K, ldb, pairs ? P_HALF : BN);
+  rc = b_mn ? make_map_bf16(&map_b, b, K, N, ldb, 2 * BK) : make_map_bf16(&map_b, b, N, K, ldb, pairs ? P_HALF : BN);
   if (rc) return rc;
   Params p{(__nv_bfloat16*)c, (const __nv_bfloat16*)residual, M, N, K, ldc, ldr, epilogue, status};
   count_launch(1);
@@ -389,14 +472,21 @@ int launch_gemm_tn_tcgen05(const void* a, const void* b, void* c, const void* re
     static bool configured2 = false;
     constexpr int smem2 = P_RING_BYTES + 1024;
     if (!configured2) {
-      if (cudaFuncSetAttribute(gemm_tn_2cta_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) != cudaSuccess) return -2;
-      if (cudaFuncSetAttribute(gemm_tn_2cta_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) != cudaSuccess) return -2;
+      bool ok = cudaFuncSetAttribute(gemm_tn_2cta_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) == cudaSuccess;
+      ok = ok && cudaFuncSetAttribute(gemm_tn_2cta_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) == cudaSuccess;
+      ok = ok && cudaFuncSetAttribute(gemm_tn_2cta_kernel<2, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) == cudaSuccess;
+      ok = ok && cudaFuncSetAttribute(gemm_tn_2cta_kernel<2, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) == cudaSuccess;
+      ok = ok && cudaFuncSetAttribute(gemm_tn_2cta_kernel<2, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) == cudaSuccess;
+      if (!ok) return -2;
       configured2 = true;
     }
     const int tiles = ((M + P_TILE_M - 1) / P_TILE_M) * ((N + P_TILE_N - 1) / P_TILE_N);
     const int max_pairs = kNumSM / 2;
     const int grid = 2 * (tiles < max_pairs ? tiles : max_pairs);
-    if (variant == 3) gemm_tn_2cta_kernel<2><<<grid, THREADS, smem2, stream>>>(map_a, map_b, p);
+    if (a_mn && b_mn) gemm_tn_2cta_kernel<2, true, true><<<grid, THREADS, smem2, stream>>>(map_a, map_b, p);
+    else if (a_mn) gemm_tn_2cta_kernel<2, true, false><<<grid, THREADS, smem2, stream>>>(map_a, map_b, p);
+    else if (b_mn) gemm_tn_2cta_kernel<2, false, true><<<grid, THREADS, smem2, stream>>>(map_a, map_b, p);
+    else if (variant == 3) gemm_tn_2cta_kernel<2><<<grid, THREADS, smem2, stream>>>(map_a, map_b, p);
     else gemm_tn_2cta_kernel<1><<<grid, THREADS, smem2, stream>>>(map_a, map_b, p);
     return cudaGetLastError() == cudaSuccess ? 0 : -3;
   }
@@ -410,6 +500,11 @@ int launch_gemm_tn_tcgen05(const void* a, const void* b, void* c, const void* re
   const int grid = tiles < kNumSM ? tiles : kNumSM;
   gemm_tn_kernel<<<grid, THREADS, smem_bytes, stream>>>(map_a, map_b, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+int launch_gemm_tn_tcgen05(const void* a, const void* b, void* c, const void* residual, int M, int N, int K, int64_t lda,
+                           int64_t ldb, int64_t ldc, int64_t ldr, int epilogue, int* status, int variant, cudaStream_t stream) {
+  return launch_gemm_tcgen05(a, b, c, residual, M, N, K, lda, ldb, ldc, ldr, epilogue, 0, 0, status, variant, stream);
 }
 
 }  // namespace sb200

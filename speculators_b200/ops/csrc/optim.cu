@@ -108,6 +108,81 @@ adamw_kernel(float* __restrict__ master, float* __restrict__ m, float* __restric
   }
 }
 
+// ---- Muon ------------------------------------------------------------------------------
+// Matrix update of Muon around its Newton-Schulz iteration (which runs as GEMMs):
+//   muon_momentum: g' = g * grad_scale * clip;  buf = lerp(buf, g', 1 - momentum);
+//                  u = nesterov ? lerp(g', buf, momentum) : buf;  out = bf16(u)
+//                  plus the per-CTA sums of u^2 (for the Frobenius normalisation that
+//                  opens the iteration), one launch for both;
+//   muon_apply:    w = w * (1 - lr * wd) - lr * adjust * o;  w16 = bf16(w)
+// with lr = hyper[0] * lr_ratio (the matrix group follows the schedule of the AdamW group),
+// read from device memory so that the launches can be captured.
+template <typename G>
+__global__ void __launch_bounds__(kOptThreads)
+muon_momentum_kernel(const G* __restrict__ grad, float* __restrict__ buf, __nv_bfloat16* __restrict__ out, int64_t n,
+                     const float* __restrict__ hyper, const float* __restrict__ norm_sq, float momentum, int nesterov,
+                     float* __restrict__ partial) {
+  __shared__ float scratch[33];
+  const float max_norm = hyper[7];
+  float gscale = hyper[8];
+  if (max_norm > 0.f && norm_sq) {
+    const float coef = max_norm / (gscale * sqrtf(norm_sq[0]) + 1e-6f);
+    if (coef < 1.f) gscale *= coef;
+  }
+  float acc = 0.f;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const float g = to_f<G>(grad[i]) * gscale;
+    float b = buf[i];
+    b += (g - b) * (1.f - momentum);
+    buf[i] = b;
+    const float u = nesterov ? g + (b - g) * momentum : b;
+    const __nv_bfloat16 r = __float2bfloat16(u);
+    out[i] = r;
+    const float ur = __bfloat162float(r);
+    acc += ur * ur;
+  }
+  acc = block_sum(acc, scratch);
+  if (threadIdx.x == 0) partial[blockIdx.x] = acc;
+}
+
+__global__ void __launch_bounds__(kOptThreads)
+muon_apply_kernel(float* __restrict__ master, const __nv_bfloat16* __restrict__ update, __nv_bfloat16* __restrict__ w16, int64_t n,
+                  const float* __restrict__ hyper, float lr_ratio, float weight_decay, float adjust) {
+  const float lr = hyper[0] * lr_ratio;
+  const float keep = 1.f - lr * weight_decay, step = lr * adjust;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const float w = master[i] * keep - step * __bfloat162float(update[i]);
+    master[i] = w;
+    if (w16) w16[i] = __float2bfloat16(w);
+  }
+}
+
+// partial: [sumsq_num_partials()] scratch; out_sumsq[0] = sum of squares of the bf16 update
+void launch_muon_momentum(const void* grad, int grad_is_bf16, float* buf, void* out, int64_t n, const float* hyper,
+                          const float* norm_sq, float momentum, int nesterov, float* partial, float* out_sumsq,
+                          cudaStream_t stream) {
+  if (n <= 0) return;
+  const int P = 4 * kNumSM;
+  count_launch(2);
+  if (grad_is_bf16)
+    muon_momentum_kernel<__nv_bfloat16><<<P, kOptThreads, 0, stream>>>((const __nv_bfloat16*)grad, buf, (__nv_bfloat16*)out, n, hyper,
+                                                                       norm_sq, momentum, nesterov, partial);
+  else
+    muon_momentum_kernel<float><<<P, kOptThreads, 0, stream>>>((const float*)grad, buf, (__nv_bfloat16*)out, n, hyper, norm_sq,
+                                                               momentum, nesterov, partial);
+  sumsq_final_kernel<<<1, 256, 0, stream>>>(partial, P, out_sumsq, 0);
+}
+
+void launch_muon_apply(float* master, const void* update, void* w16, int64_t n, const float* hyper, float lr_ratio,
+                       float weight_decay, float adjust, cudaStream_t stream) {
+  if (n <= 0) return;
+  int64_t blocks = (n + kOptThreads - 1) / kOptThreads;
+  const int64_t cap = (int64_t)kNumSM * 16;
+  count_launch(1);
+  muon_apply_kernel<<<(int)(blocks < cap ? blocks : cap), kOptThreads, 0, stream>>>(
+      master, (const __nv_bfloat16*)update, (__nv_bfloat16*)w16, n, hyper, lr_ratio, weight_decay, adjust);
+}
+
 // Hyper-parameters travel as kernel arguments (copied at launch), so the host can
 // prepare step k+1 while step k is still queued: no staging buffer to overwrite.
 struct HyperVals {

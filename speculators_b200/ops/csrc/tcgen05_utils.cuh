@@ -69,6 +69,12 @@ __host__ __device__ constexpr uint32_t instr_desc(int m, int n, bool b_mn_major)
   return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// kind::f16 instruction descriptor with either operand K-major or MN-major (bit 15: A, bit 16: B).
+__host__ __device__ constexpr uint32_t instr_desc_ab(int m, int n, bool a_mn_major, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
 // MN-major operand, 128-byte swizzle: shared-memory rows are the contraction index (128 B =
 // 64 MN-elements each, 8-row groups 1024 B apart), the next 64 MN-elements start `lbo` bytes on.
 __device__ __forceinline__ uint64_t smem_desc_mnmajor_sw128(uint32_t addr, uint32_t lbo) {

@@ -64,6 +64,43 @@ def op_gemm_cublas(a):
     return (lambda: torch.matmul(x, w.t(), out=out)), 2.0 * M * N * K, 2.0 * (M * K + N * K + M * N), dict
 
 
+def _layout_operands(a, a_mn: bool, b_mn: bool):
+    M, N, K = a.m, a.n, a.k
+    x = _bf16(K, M) if a_mn else _bf16(M, K)
+    w = _bf16(K, N, scale=0.05) if b_mn else _bf16(N, K, scale=0.05)
+    return x, w, torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+
+
+def op_gemm_dgrad(a):
+    """out[M,N] = x[M,K] @ w[K,N] (input gradient of a linear layer: M tokens, K out features, N in features)."""
+    from speculators_b200 import ops
+
+    x, w, out = _layout_operands(a, False, True)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    fn = lambda: ops.native().gemm(x, w, out, 0, False, True, status)  # noqa: E731
+    return fn, 2.0 * a.m * a.n * a.k, 2.0 * (a.m * a.k + a.n * a.k + a.m * a.n), lambda: {"status": int(status.item())}
+
+
+def op_gemm_dgrad_cublas(a):
+    x, w, out = _layout_operands(a, False, True)
+    return (lambda: torch.mm(x, w, out=out)), 2.0 * a.m * a.n * a.k, 2.0 * (a.m * a.k + a.n * a.k + a.m * a.n), dict
+
+
+def op_gemm_wgrad(a):
+    """out[M,N] += dy[K,M]^T @ x[K,N] (weight gradient: M out features, N in features, K tokens)."""
+    from speculators_b200 import ops
+
+    x, w, out = _layout_operands(a, True, True)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    fn = lambda: ops.native().gemm(x, w, out, 1, True, True, status)  # noqa: E731
+    return fn, 2.0 * a.m * a.n * a.k, 2.0 * (a.m * a.k + a.n * a.k + 2 * a.m * a.n), lambda: {"status": int(status.item())}
+
+
+def op_gemm_wgrad_cublas(a):
+    x, w, out = _layout_operands(a, True, True)
+    return (lambda: out.addmm_(x.t(), w)), 2.0 * a.m * a.n * a.k, 2.0 * (a.m * a.k + a.n * a.k + 2 * a.m * a.n), dict
+
+
 def _attn_inputs(a):
     from speculators_b200.models.eagle3.attention import ttt_attn_spec
 
@@ -135,7 +172,8 @@ def op_adamw(a):
     return fn, 0.0, n * (3 * 4 * 2 + 2 + 2.0), dict
 
 
-OPS = {"gemm": op_gemm, "gemm_cublas": op_gemm_cublas, "attn_fwd": op_attn_fwd, "attn_bwd": op_attn_bwd, "loss": op_loss,
+OPS = {"gemm": op_gemm, "gemm_cublas": op_gemm_cublas, "gemm_dgrad": op_gemm_dgrad, "gemm_dgrad_cublas": op_gemm_dgrad_cublas,
+       "gemm_wgrad": op_gemm_wgrad, "gemm_wgrad_cublas": op_gemm_wgrad_cublas, "attn_fwd": op_attn_fwd, "attn_bwd": op_attn_bwd, "loss": op_loss,
        "rmsnorm": op_rmsnorm, "rmsnorm_bwd": op_rmsnorm_bwd, "adamw": op_adamw}
 
 

@@ -20,8 +20,11 @@ AdamW moments for the slice ``[lo, hi)`` of that buffer owned by this rank:
 A step is: (sum of squares of the owned gradient slice -> all-reduce of one
 scalar) -> fused AdamW with the clip coefficient applied in-kernel -> all-gather.
 No value is read back to the host, so the whole step can be captured in a CUDA
-graph.  Muon (the reference's default optimizer for 2-D weights) is supported in
-replicated mode through a Newton-Schulz update on the matrix views.
+graph.  Muon (the reference's default optimizer for 2-D weights,
+src/speculators/train/optimizers.py:61-110) assigns whole matrices to ranks: the owner keeps
+the fp32 master copy and the momentum, runs the Newton-Schulz update on the package's GEMM and
+broadcasts the refreshed bf16 weights; the AdamW tail (norm weights, embeddings) is sharded or
+replicated like the plain AdamW mode.
 """
 
 from __future__ import annotations
@@ -246,15 +249,21 @@ class TrainEngine:
         self.offsets: list[int] = []
         off = 0
         self.muon_end = 0
+        unit = _ALIGN * self.world
         for name, p in named:
+            if name not in muon_names and self.muon_end == 0 and off > 0:
+                # first tensor of the AdamW tail: the matrix region ends on a shard-unit boundary,
+                # so the tail divides evenly among the ranks
+                off = self.muon_end = (off + unit - 1) // unit * unit
             self.names.append(name)
             self.params.append(p)
             self.offsets.append(off)
             off += (p.numel() + _ALIGN - 1) // _ALIGN * _ALIGN
-            if name in muon_names:
-                self.muon_end = off
-        unit = _ALIGN * self.world
+        if muon_names and self.muon_end == 0:
+            off = self.muon_end = (off + unit - 1) // unit * unit  # matrices only
         self.total = (off + unit - 1) // unit * unit
+        if self.total == self.muon_end:
+            self.total += unit  # keeps the tail slice non-empty
         self._peer_local: list[int] = []
         self._peer_mapped: list[int] = []
         self._symm_handles = None
@@ -286,14 +295,19 @@ class TrainEngine:
         self._init32 = init32
 
     def _init_state(self) -> None:
+        # [lo, hi): the slice of the flat buffer whose AdamW state this rank holds.  With Muon the
+        # matrix region [0, muon_end) is not part of it: whole matrices are owned by ranks instead
+        # (``_init_muon``) and the AdamW slice covers the tail only.
+        first = self.muon_end
         if self.sharded:
-            per = self.total // self.world
-            self.lo, self.hi = self.rank * per, (self.rank + 1) * per
+            per = (self.total - first) // self.world
+            self.lo, self.hi = first + self.rank * per, first + (self.rank + 1) * per
         else:
-            self.lo, self.hi = 0, self.total
+            self.lo, self.hi = first, self.total
         n = self.hi - self.lo
         dev = self.device
         fp32_compute = self.cfg.compute_dtype == torch.float32
+        self._init_muon(fp32_compute)
         # with fp32 compute weights the flat buffer *is* the master copy
         self.master = self.flat_w[self.lo : self.hi] if fp32_compute else self._init32[self.lo : self.hi].clone()
         del self._init32
@@ -405,7 +419,24 @@ class TrainEngine:
                 self.exp_avg_sq, self.grad_reduced, self.hyper, self.status, peer_wait_spins(),
             )
             return
-        if self.distributed and self.world > 1:
+        multi = self.distributed and self.world > 1
+        w16 = None if self.cfg.compute_dtype == torch.float32 else self.flat_w[self.lo : self.hi]
+        if self.muon_items:
+            # Muon: every rank needs whole reduced matrices for the ones it owns, so the gradient
+            # buffer is all-reduced; the norm is then the same local reduction on every rank
+            if multi:
+                with nvtx_range("grad reduce"), self._comm_timed():
+                    dist.all_reduce(self.flat_g, op=dist.ReduceOp.SUM, group=self.group)
+            ops.sum_of_squares(self.flat_g, self.norm_sq, accumulate=False)
+            self._muon_update(self.flat_g)
+            ops.adamw_step_(self.master, self.exp_avg, self.exp_avg_sq, self.flat_g[self.lo : self.hi], w16, self.hyper, self.norm_sq)
+            if multi:
+                with nvtx_range("weight broadcast"), self._comm_timed():
+                    self._muon_broadcast(self.flat_w)
+                    if self.sharded:
+                        dist.all_gather_into_tensor(self.flat_w[self.muon_end :], self.flat_w[self.lo : self.hi], group=self.group)
+            return
+        if multi:
             with nvtx_range("grad reduce"), self._comm_timed():
                 if self.sharded:
                     dist.reduce_scatter_tensor(self.grad_shard, self.flat_g, op=dist.ReduceOp.SUM, group=self.group)
@@ -415,15 +446,7 @@ class TrainEngine:
         ops.sum_of_squares(g, self.norm_sq, accumulate=False)
         if self.sharded:
             dist.all_reduce(self.norm_sq, op=dist.ReduceOp.SUM, group=self.group)
-        w16 = None if self.cfg.compute_dtype == torch.float32 else self.flat_w[self.lo : self.hi]
-        if self.cfg.optimizer == "muon" and self.muon_end > 0:
-            self._muon_update(g)
-            a, b = self.muon_end - self.lo, self.hi - self.lo
-            if b > a >= 0:
-                ops.adamw_step_(self.master[a:b], self.exp_avg[a:b], self.exp_avg_sq[a:b], g[a:b],
-                                None if w16 is None else w16[a:b], self.hyper, self.norm_sq)
-        else:
-            ops.adamw_step_(self.master, self.exp_avg, self.exp_avg_sq, g, w16, self.hyper, self.norm_sq)
+        ops.adamw_step_(self.master, self.exp_avg, self.exp_avg_sq, g, w16, self.hyper, self.norm_sq)
         if self.sharded:
             with nvtx_range("weight all-gather"), self._comm_timed():
                 dist.all_gather_into_tensor(self.flat_w, self.flat_w[self.lo : self.hi], group=self.group)
@@ -466,38 +489,106 @@ class TrainEngine:
         self.apply()
 
     # ------------------------------------------------------------------ muon
-    def _muon_update(self, g: torch.Tensor) -> None:
-        """Momentum + Newton-Schulz orthogonalised update for the matrix region
-        (replicated mode).  Mirrors ``torch.optim.Muon`` semantics: nesterov
-        momentum, quintic NS iteration, decoupled weight decay and the
-        ``match_rms_adamw`` learning-rate adjustment ``0.2 * sqrt(max(m, n))``."""
-        if self.sharded:
-            raise NotImplementedError("Muon with --fsdp-shard: use --optimizer adamw or drop --fsdp-shard")
-        cfg = self.cfg
-        coef_scale = 1.0 / self.world
-        total_norm = coef_scale * self.norm_sq.sqrt()
-        clip = torch.clamp(cfg.max_grad_norm / (total_norm + 1e-6), max=1.0) if cfg.max_grad_norm else torch.ones_like(total_norm)
-        lr_scale = self.hyper[0] / max(self.base_lr, 1e-30)  # follow the schedule of the AdamW group
-        for p, o in zip(self.params, self.offsets):
-            if o >= self.muon_end:
-                break
+    def _init_muon(self, fp32_compute: bool) -> None:
+        """Ownership of the Muon matrices.  Newton-Schulz needs a whole matrix, so matrices are
+        not cut at shard boundaries: each is assigned to one rank (largest cost first onto the
+        least loaded rank, cost = the iteration's GEMM work), which keeps its fp32 master copy and
+        momentum, computes its update and broadcasts the refreshed weights.  The same assignment
+        is used with and without ``shard``: the result is identical to every rank updating every
+        matrix, at 1/world of the work and of the state."""
+        self.muon_items: list[tuple[int, str, nn.Parameter, int]] = [
+            (i, name, p, o) for i, (name, p, o) in enumerate(zip(self.names, self.params, self.offsets)) if o < self.muon_end
+        ]
+        self.muon_owner: dict[int, int] = {}
+        self.muon_state: dict[int, dict[str, torch.Tensor]] = {}
+        if not self.muon_items:
+            return
+        load = [0.0] * self.world
+
+        def cost(p):
+            m, n = min(p.shape), max(p.shape)
+            return 4.0 * m * m * n + 2.0 * m**3
+
+        for i, _name, p, _o in sorted(self.muon_items, key=lambda it: (-cost(it[2]), it[0])):
+            r = min(range(self.world), key=lambda q: (load[q], q))
+            self.muon_owner[i] = r
+            load[r] += cost(p)
+        for i, _name, p, o in self.muon_items:
+            if self.muon_owner[i] != self.rank:
+                continue
             n = p.numel()
-            grad = g[o : o + n].view(p.shape).float() * (coef_scale * clip)
-            buf = self.exp_avg[o : o + n].view(p.shape)
-            buf.lerp_(grad, 1 - cfg.muon_momentum)
-            update = grad.lerp(buf, cfg.muon_momentum)
-            update = _newton_schulz(update, cfg.muon_ns_steps)
+            master = self.flat_w[o : o + n].view(p.shape) if fp32_compute else self._init32[o : o + n].clone().view(p.shape)
+            self.muon_state[i] = {"master": master, "momentum": torch.zeros(p.shape, dtype=torch.float32, device=self.device)}
+        if self.device.type == "cuda":
+            self._muon_sumsq = torch.zeros(1, dtype=torch.float32, device=self.device)
+            self._muon_partial = torch.zeros(ops.native().sumsq_num_partials(), dtype=torch.float32, device=self.device)
+
+    def _muon_update(self, g: torch.Tensor) -> None:
+        """Momentum + Newton-Schulz orthogonalised update of the matrices this rank owns.
+        Same semantics as ``torch.optim.Muon``: nesterov momentum, quintic NS iteration,
+        decoupled weight decay and the ``match_rms_adamw`` learning-rate adjustment
+        ``0.2 * sqrt(max(m, n))``.  On CUDA the element-wise parts are two kernels (clip + momentum
+        + nesterov + bf16 cast + squared norm; decay + update + bf16 cast) and the iteration runs
+        on the package's GEMM with transposed operands read in place."""
+        cfg = self.cfg
+        cuda = self.device.type == "cuda" and cfg.compute_dtype == torch.bfloat16
+        lr_ratio = self.base_muon_lr / max(self.base_lr, 1e-30)  # the matrix group follows the AdamW group's schedule
+        if not cuda:
+            coef_scale = 1.0 / self.world
+            total_norm = coef_scale * self.norm_sq.sqrt()
+            clip = torch.clamp(cfg.max_grad_norm / (total_norm + 1e-6), max=1.0) if cfg.max_grad_norm else torch.ones_like(total_norm)
+        for i, _name, p, o in self.muon_items:
+            state = self.muon_state.get(i)
+            if state is None:
+                continue
+            n = p.numel()
             rows, cols = p.shape
-            if cfg.muon_adjust_lr_fn == "match_rms_adamw":
-                adj = 0.2 * math.sqrt(max(rows, cols))
-            else:
-                adj = math.sqrt(max(1.0, rows / cols))
-            lr = self.base_muon_lr * lr_scale
-            master = self.master[o : o + n].view(p.shape)
+            adj = 0.2 * math.sqrt(max(rows, cols)) if cfg.muon_adjust_lr_fn == "match_rms_adamw" else math.sqrt(max(1.0, rows / cols))
+            if cuda:
+                nat = ops.native()
+                upd = torch.empty(p.shape, dtype=torch.bfloat16, device=self.device)
+                nat.muon_momentum(g[o : o + n], state["momentum"].view(-1), upd.view(-1), self.hyper, self.norm_sq,
+                                  cfg.muon_momentum, True, self._muon_partial, self._muon_sumsq)
+                upd = _newton_schulz(upd * (1.0 / (self._muon_sumsq.sqrt() + 1e-7)).to(torch.bfloat16), cfg.muon_ns_steps, normalise=False)
+                nat.muon_apply(state["master"].view(-1), upd.reshape(-1), self.flat_w[o : o + n], self.hyper, lr_ratio,
+                               cfg.muon_weight_decay, adj)
+                continue
+            grad = g[o : o + n].view(p.shape).float() * (coef_scale * clip)
+            buf = state["momentum"]
+            buf.lerp_(grad, 1 - cfg.muon_momentum)
+            update = _newton_schulz(grad.lerp(buf, cfg.muon_momentum), cfg.muon_ns_steps)
+            lr = self.hyper[0] * lr_ratio
+            master = state["master"]
             master.mul_(1 - lr * cfg.muon_weight_decay)
             master.sub_(update * (lr * adj))
             if self.cfg.compute_dtype != torch.float32:
                 self.flat_w[o : o + n].view(p.shape).copy_(master)
+
+    def _muon_broadcast(self, flat: torch.Tensor) -> None:
+        """Every matrix region of ``flat`` from its owner to all ranks (asynchronous, waited
+        together)."""
+        work = []
+        for i, _name, p, o in self.muon_items:
+            src = self.muon_owner[i]
+            if self.group is not None:
+                src = dist.get_global_rank(self.group, src)
+            work.append(dist.broadcast(flat[o : o + p.numel()], src=src, group=self.group, async_op=True))
+        for w in work:
+            w.wait()
+
+    def _muon_full(self, key: str, first_rank_only: bool = False) -> dict[int, torch.Tensor | None]:
+        """``key`` ("master" / "momentum") of every Muon matrix as full fp32 tensors: on every
+        rank, or on the group's first rank only (``None`` elsewhere)."""
+        out: dict[int, torch.Tensor | None] = {}
+        multi = self.distributed and self.world > 1
+        for i, _name, p, _o in self.muon_items:
+            own = self.muon_state.get(i)
+            t = own[key].detach().clone().float() if own is not None else torch.empty(p.shape, dtype=torch.float32, device=self.device)
+            if multi:
+                src = self.muon_owner[i]
+                dist.broadcast(t, src=dist.get_global_rank(self.group, src) if self.group is not None else src, group=self.group)
+            out[i] = None if (first_rank_only and self.rank != 0) else t
+        return out
 
     def check_status(self, code: int | None = None) -> None:
         """Raise if a bounded device-side wait of the fused step ran out (a peer did
@@ -533,7 +624,7 @@ class TrainEngine:
     def _gather_full(self, shard: torch.Tensor) -> torch.Tensor:
         if not self.sharded:
             return shard
-        full = torch.empty(self.total, dtype=shard.dtype, device=shard.device)
+        full = torch.empty(self.total - self.muon_end, dtype=shard.dtype, device=shard.device)
         dist.all_gather_into_tensor(full, shard.contiguous(), group=self.group)
         return full
 
@@ -544,7 +635,7 @@ class TrainEngine:
             return shard
         dst = dist.get_global_rank(self.group, 0) if self.group is not None else 0
         if self.rank == 0:
-            full = torch.empty(self.total, dtype=shard.dtype, device=shard.device)
+            full = torch.empty(self.total - self.muon_end, dtype=shard.dtype, device=shard.device)
             dist.gather(shard.contiguous(), list(full.chunk(self.world)), dst=dst, group=self.group)
             return full
         dist.gather(shard.contiguous(), None, dst=dst, group=self.group)
@@ -556,15 +647,21 @@ class TrainEngine:
         rank alone and the other ranks get a dict without ``state`` entries."""
         gather = self._gather_to_first if first_rank_only else self._gather_full
         master, m, v = (gather(t) for t in (self.master, self.exp_avg, self.exp_avg_sq))
-        if master is None:
+        mu_master, mu_mom = self._muon_full("master", first_rank_only), self._muon_full("momentum", first_rank_only)
+        if master is None or (first_rank_only and self.rank != 0 and self.distributed and self.world > 1):
             return {"step": self.step_count, "optimizer": self.cfg.optimizer, "state": {}}
         state = {}
-        for name, p, o in zip(self.names, self.params, self.offsets):
+        base = self.muon_end  # the gathered AdamW tensors start at the end of the matrix region
+        for i, (name, p, o) in enumerate(zip(self.names, self.params, self.offsets)):
             n = p.numel()
+            if i in mu_master:  # a Muon matrix: the momentum sits in "exp_avg", there is no second moment
+                state[name] = {"master": mu_master[i].cpu(), "exp_avg": mu_mom[i].cpu(), "exp_avg_sq": torch.zeros(p.shape)}
+                continue
+            a = o - base
             state[name] = {
-                "master": master[o : o + n].view(p.shape).cpu().clone(),
-                "exp_avg": m[o : o + n].view(p.shape).cpu().clone(),
-                "exp_avg_sq": v[o : o + n].view(p.shape).cpu().clone(),
+                "master": master[a : a + n].view(p.shape).cpu().clone(),
+                "exp_avg": m[a : a + n].view(p.shape).cpu().clone(),
+                "exp_avg_sq": v[a : a + n].view(p.shape).cpu().clone(),
             }
         return {"step": self.step_count, "optimizer": self.cfg.optimizer, "state": state}
 
@@ -581,9 +678,15 @@ class TrainEngine:
         self.step_count = int(sd.get("step", 0))
         if not any(name in sd.get("state", {}) for name in self.names):
             log.warning("optimizer state matches none of the %d trainable parameter names: nothing restored.", len(self.names))
-        for name, p, o in zip(self.names, self.params, self.offsets):
+        for i, (name, p, o) in enumerate(zip(self.names, self.params, self.offsets)):
             entry = sd["state"].get(name)
             if entry is None:
+                continue
+            if o < self.muon_end:
+                own = self.muon_state.get(i)
+                if own is not None:
+                    own["master"].copy_(entry["master"].reshape(p.shape).float().to(self.device))
+                    own["momentum"].copy_(entry["exp_avg"].reshape(p.shape).float().to(self.device))
                 continue
             n = p.numel()
             a, b = max(o, self.lo), min(o + n, self.hi)
@@ -598,21 +701,31 @@ class TrainEngine:
         """Refresh the compute buffer from the master weights (after loading state)."""
         if self.cfg.compute_dtype != torch.float32:
             self.flat_w[self.lo : self.hi].copy_(self.master)
+            for i, _name, p, o in self.muon_items:
+                if i in self.muon_state:
+                    self.flat_w[o : o + p.numel()].view(p.shape).copy_(self.muon_state[i]["master"])
+        if self.muon_items and self.distributed and self.world > 1:
+            self._muon_broadcast(self.flat_w)
         if self.sharded:
-            dist.all_gather_into_tensor(self.flat_w, self.flat_w[self.lo : self.hi].clone(), group=self.group)
+            dist.all_gather_into_tensor(self.flat_w[self.muon_end :], self.flat_w[self.lo : self.hi].clone(), group=self.group)
 
     def load_model_weights_into_master(self) -> None:
         """After ``model.load_state_dict`` wrote new values through the parameter
         views, make them the master copy."""
         if self.cfg.compute_dtype != torch.float32:
             self.master.copy_(self.flat_w[self.lo : self.hi])
+            for i, _name, p, o in self.muon_items:
+                if i in self.muon_state:
+                    self.muon_state[i]["master"].copy_(self.flat_w[o : o + p.numel()].view(p.shape))
 
     def master_state_dict(self) -> dict[str, torch.Tensor]:
-        """fp32 master weights keyed by parameter name (full tensors)."""
+        """fp32 master weights keyed by parameter name (full tensors, on every rank)."""
         master = self._gather_full(self.master)
+        mu = self._muon_full("master")
+        base = self.muon_end
         return {
-            name: master[o : o + p.numel()].view(p.shape).clone()
-            for name, p, o in zip(self.names, self.params, self.offsets)
+            name: (mu[i] if i in mu else master[o - base : o - base + p.numel()].view(p.shape).clone())
+            for i, (name, p, o) in enumerate(zip(self.names, self.params, self.offsets))
         }
 
 
@@ -639,16 +752,18 @@ def _can_access_peer(a: int, b: int) -> bool:
         return False
 
 
-def _newton_schulz(g: torch.Tensor, steps: int) -> torch.Tensor:
+def _newton_schulz(g: torch.Tensor, steps: int, normalise: bool = True) -> torch.Tensor:
+    """Quintic Newton-Schulz iteration towards the orthogonal factor of ``g``.  The Gram matrix
+    is formed on the short side without materialising a transpose: ``X X^T`` for a wide matrix,
+    ``X^T X`` for a tall one (then ``X <- a X + X B`` instead of ``a X + B X``)."""
     a, b, c = 3.4445, -4.7750, 2.0315
     x = g.bfloat16() if g.is_cuda else g.clone()
-    transposed = x.shape[0] > x.shape[1]
-    if transposed:
-        x = x.t()
-    x = x / (x.norm() + 1e-7)
+    if normalise:
+        x = x / (x.norm() + 1e-7)
+    tall = x.shape[0] > x.shape[1]
     for _ in range(steps):
-        gram = x @ x.t()
-        x = a * x + (b * gram + c * gram @ gram) @ x
-    if transposed:
-        x = x.t()
+        gram = ops.matmul_tn(x, x) if tall else ops.matmul_nt(x, x)
+        poly = b * gram + c * ops.matmul_nn(gram, gram)
+        nxt = a * x
+        x = ops.matmul_nn(x, poly, out=nxt, accumulate=True) if tall else ops.matmul_nn(poly, x, out=nxt, accumulate=True)
     return x.to(g.dtype)

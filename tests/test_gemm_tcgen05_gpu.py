@@ -60,3 +60,82 @@ def test_many_tiles_per_pair_wraps_the_ring():
         _run(2048, 6144, 1024, variant=variant)
         _run(4096, 5120, 640, epilogue=2, variant=variant)
         _run(512, 768, 192, variant=variant)  # K not a multiple of the 128-wide stage: zero-filled tail
+
+
+# ---- transposed operands read in place (the backward products of a linear layer) -----------
+def _run_ex(M, N, K, a_mn, b_mn, epilogue=0, pad=0, seed=0):
+    """a stored [K, M] when a_mn else [M, K]; b stored [K, N] when b_mn else [N, K]; ``pad``
+    extra columns make the row strides larger than the row lengths (views into wider buffers)."""
+    torch.manual_seed(seed)
+
+    def operand(rows, cols):
+        full = (torch.randn(rows, cols + pad, device="cuda") * 0.5).to(torch.bfloat16)
+        return full[:, :cols]
+
+    a = operand(K, M) if a_mn else operand(M, K)
+    b = operand(K, N) if b_mn else operand(N, K)
+    out_full = torch.randn(M, N + pad, device="cuda").to(torch.bfloat16)
+    out = out_full[:, :N]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    af = a.float().t() if a_mn else a.float()
+    bf = b.float() if b_mn else b.float().t()
+    ref = af @ bf
+    if epilogue == 1:
+        ref = ref + out.float()
+    guard = out_full[:, N:].clone()
+    ops.native().gemm(a, b, out, epilogue, a_mn, b_mn, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, f"kernel reported wait timeout code {int(status.item())}"
+    err = (out.float() - ref).abs().max().item()
+    scale = ref.abs().max().item()
+    assert err <= 0.01 * scale + 0.05, (M, N, K, a_mn, b_mn, epilogue, err, scale)
+    assert torch.equal(out_full[:, N:], guard)  # nothing written past the matrix
+
+
+LAYOUTS = [(False, True), (True, True), (True, False), (False, False)]  # NN (dgrad), TN (wgrad), TT, NT
+
+
+@pytest.mark.parametrize("a_mn,b_mn", LAYOUTS)
+def test_layouts_single_tile_and_one_stage(a_mn, b_mn):
+    _run_ex(256, 256, 128, a_mn, b_mn)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", LAYOUTS)
+@pytest.mark.parametrize("M,N,K", [(256, 512, 256), (200, 304, 136), (2048, 4096, 1024), (80, 1000, 72), (1000, 520, 4096), (264, 8, 200)])
+def test_layouts_ragged_shapes(a_mn, b_mn, M, N, K):
+    _run_ex(M, N, K, a_mn, b_mn)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", LAYOUTS)
+def test_layouts_strided_views_and_accumulate(a_mn, b_mn):
+    _run_ex(384, 768, 320, a_mn, b_mn, pad=64)
+    _run_ex(384, 768, 320, a_mn, b_mn, epilogue=1)
+    _run_ex(136, 264, 72, a_mn, b_mn, epilogue=1, pad=8)
+
+
+def test_layouts_many_tiles_wrap_the_ring():
+    _run_ex(2048, 4096, 32000 // 8, False, True)   # dgrad through a tall weight
+    _run_ex(6144, 8192, 2048, True, True, epilogue=1)  # wgrad accumulate, more tiles than CTA pairs
+
+
+def test_linear_backward_runs_on_the_own_kernel():
+    """dX and dW of ``ops.linear`` against fp32 autograd, with the weight gradient accumulated
+    into an attached flat buffer over two passes (what the training engine sets up)."""
+    torch.manual_seed(0)
+    T, IN, OUT = 640, 512, 768
+    x = (torch.randn(T, IN, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+    w = torch.nn.Parameter((torch.randn(OUT, IN, device="cuda") * 0.05).to(torch.bfloat16))
+    w._flat_grad = torch.zeros_like(w)
+    w._grad_fresh = True
+    dy = (torch.randn(T, OUT, device="cuda") * 0.1).to(torch.bfloat16)
+    before = ops.native().launch_count()
+    for _ in range(2):
+        y = ops.linear(x, w)
+        (dx,) = torch.autograd.grad(y, x, dy, retain_graph=False)
+    torch.cuda.synchronize()
+    assert ops.native().launch_count() - before == 6  # forward, dgrad, wgrad per pass: no library GEMM
+    ops.check_gemm_status()
+    xf, wf, dyf = x.detach().float(), w.detach().float(), dy.float()
+    assert (dx.float() - dyf @ wf).abs().max() <= 0.01 * (dyf @ wf).abs().max() + 0.02
+    want = 2 * (dyf.t() @ xf)
+    assert (w._flat_grad.float() - want).abs().max() <= 0.01 * want.abs().max() + 0.05

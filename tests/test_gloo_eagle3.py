@@ -46,7 +46,7 @@ def _worker(rank, world, port, vdir, out_path, shard):
     state = eng.optimizer_state_dict(first_rank_only=True)
     if rank == 0:
         torch.save({"master": full, "moments": {k: v["exp_avg"] for k, v in state["state"].items()}}, out_path)
-    elif shard:
+    else:
         assert state["state"] == {}  # the full state is assembled on the writer only
     dist.destroy_process_group()
 

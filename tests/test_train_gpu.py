@@ -156,3 +156,77 @@ def test_engine_flat_gradients_match_plain_autograd(tiny_verifier_dir, tiny_voca
     engine.step(lr=0.0)  # nothing was back-propagated: every gradient must read as zero
     assert float(engine.flat_g.float().abs().max()) == 0.0
     assert float(engine.grad_norm()) == 0.0 and torch.equal(engine.flat_w.float(), before)
+
+
+def test_bf16_gradient_pipeline_tracks_an_fp32_run_for_200_steps(tiny_verifier_dir, tiny_vocab_maps):
+    """Gradients here are bf16 end to end (weight gradients accumulate in bf16 over the TTT
+    passes, the optimizer reads bf16), where the reference keeps fp32 ``.grad``.  Pin what that
+    costs: the GPU trainer (bf16 weights, activations and gradients, fp32 master weights) and
+    an all-fp32 CPU trainer start from the same weights and see the same eight batches for 200
+    steps; the loss curves must stay together and end at the same level."""
+    base = make_tiny_eagle3(tiny_verifier_dir, tiny_vocab_maps)
+    batches = [make_tiny_batch(T=64, docs=(20, 30, 10), pad=4, seed=s) for s in range(8)]
+    kwargs, _ = sb.Eagle3DraftModel.get_trainer_kwargs(loss_fn="kl_div", ttt_steps=3, ttt_step_loss_decay=1.0)
+
+    def make(device, graph):
+        return Trainer(copy.deepcopy(base), TrainerConfig(lr=2e-3, num_epochs=1, save_path=tempfile.mkdtemp(), train_call_kwargs=kwargs,
+                                                          scheduler_type="none", log_freq=10**9, use_cuda_graph=graph, device=device),
+                       SyntheticLoader(batches, 200))
+
+    gpu, cpu = make("cuda:0", True), make("cpu", False)
+    lg, lc = [], []
+    for step in range(200):
+        b = batches[step % len(batches)]
+        lg.append(gpu.train_step(b)[0].detach().float().reshape(1).clone())
+        lc.append(float(cpu.train_step(b)[0]))
+    lg = torch.cat(lg).cpu().tolist()
+    assert lc[-1] < 0.7 * lc[0] and lg[-1] < 0.7 * lg[0]  # both learn
+    gaps = [abs(a - b) / max(abs(b), 1e-3) for a, b in zip(lg, lc)]
+    assert max(gaps[:20]) < 0.03, max(gaps[:20])  # same trajectory at the start ...
+    tail_g, tail_c = sum(lg[-16:]) / 16, sum(lc[-16:]) / 16
+    assert abs(tail_g - tail_c) < 0.08 * tail_c + 0.01, (tail_g, tail_c)  # ... and the same level after 200 steps
+    assert sum(gaps) / len(gaps) < 0.05, sum(gaps) / len(gaps)
+
+
+def test_muon_on_gpu_tracks_the_fp32_engine():
+    """Muon with the iteration on the package's GEMM and the two element-wise kernels (bf16
+    weights on a GPU) against the same engine in fp32 on the CPU, from the same init."""
+    from torch import nn
+
+    from speculators_b200.models.layers import Linear
+    from speculators_b200.parallel.engine import EngineConfig, TrainEngine
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            torch.manual_seed(0)
+            self.a, self.b, self.c = Linear(256, 512), Linear(512, 128), Linear(128, 384)
+            self.gain = nn.Parameter(torch.ones(384))
+
+        def forward(self, x):
+            return self.c(torch.tanh(self.b(torch.tanh(self.a(x))))) * self.gain
+
+    cfg = dict(lr=1e-3, optimizer="muon", muon_lr=0.02, max_grad_norm=1.0)
+    cpu_net = Net()
+    gpu_net = copy.deepcopy(cpu_net)
+    e_cpu = TrainEngine(cpu_net, EngineConfig(**cfg, compute_dtype=torch.float32), device="cpu")
+    e_gpu = TrainEngine(gpu_net, EngineConfig(**cfg, compute_dtype=torch.bfloat16), device="cuda:0")
+    from speculators_b200 import ops
+
+    before = ops.native().launch_count()
+    for step in range(5):
+        g = torch.Generator().manual_seed(step)
+        x, y = torch.randn(96, 256, generator=g), torch.randn(96, 384, generator=g)
+        for net, eng, dev, dt in ((cpu_net, e_cpu, "cpu", torch.float32), (gpu_net, e_gpu, "cuda:0", torch.bfloat16)):
+            eng.zero_grad()
+            ((net(x.to(dev, dt)).float() - y.to(dev)) ** 2).mean().backward()
+            eng.step()
+    torch.cuda.synchronize()
+    ops.check_gemm_status()
+    assert ops.native().launch_count() - before > 5 * 3 * (2 + 3 * 5)  # momentum, apply and the iteration's GEMMs ran natively
+    want, got = e_cpu.master_state_dict(), e_gpu.master_state_dict()
+    for name in want:
+        w, g_ = want[name], got[name].cpu()
+        moved = (w - dict(Net().named_parameters())[name].detach()).abs().max()
+        assert moved > 0
+        assert (w - g_).abs().max() < 0.15 * moved + 1e-4, (name, float((w - g_).abs().max()), float(moved))
