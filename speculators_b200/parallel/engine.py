@@ -251,7 +251,7 @@ class TrainEngine:
         self.muon_end = 0
         unit = _ALIGN * self.world
         for name, p in named:
-            if name not in muon_names and self.muon_end == 0 and off > 0:
+            if muon_names and name not in muon_names and self.muon_end == 0 and off > 0:
                 # first tensor of the AdamW tail: the matrix region ends on a shard-unit boundary,
                 # so the tail divides evenly among the ranks
                 off = self.muon_end = (off + unit - 1) // unit * unit
