@@ -38,12 +38,87 @@ LLAMA31_8B = {
     "hidden_act": "silu", "attention_bias": False, "mlp_bias": False, "tie_word_embeddings": False,
     "initializer_range": 0.02,
 }
-TINY = dict(LLAMA31_8B, hidden_size=256, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
+TINY = dict(LLAMA31_8B, hidden_size=256, num_hidden_layers=6, num_attention_heads=4, num_key_value_heads=2,
             head_dim=64, intermediate_size=688, vocab_size=1024, rope_theta=10000.0, max_position_embeddings=4096)
-AUX_LAYERS = {"llama31_8b": [2, 16, 29], "tiny": [1, 2, 3]}
+QWEN3_8B = dict(LLAMA31_8B, architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=36, intermediate_size=12288,
+                vocab_size=151936, rms_norm_eps=1e-6, rope_theta=1000000.0, max_position_embeddings=40960)
+LLAMA33_70B = dict(LLAMA31_8B, hidden_size=8192, num_hidden_layers=80, num_attention_heads=64, intermediate_size=28672)
+VERIFIERS = {"llama31_8b": LLAMA31_8B, "tiny": TINY, "qwen3_8b": QWEN3_8B, "llama33_70b": LLAMA33_70B}
 METRIC = "EAGLE3-8B draft-train tokens/s at 1/2/4/8 B200 (device max over ranks)"
 PARITY_STEPS = 6  # optimizer steps from the common initial weights whose losses both arms record
 PARITY_RTOL = 0.03
+
+# One entry per measured configuration.  ``model`` / ``train``: keyword arguments that both
+# frameworks' ``from_training_args`` / ``get_trainer_kwargs`` take under the same names.
+CONFIGS = {
+    # EAGLE-3, 1 draft layer for a Llama-3.1-8B-shaped verifier (the headline; the default)
+    "eagle3": dict(
+        algo="eagle3", verifier="llama31_8b", seq_len=2048, draft_vocab=32000, aux=[2, 16, 29], draft_layers=1,
+        layer_types=["sliding_attention"], sliding_window=2048, verifier_forward=True,
+        model=dict(norm_before_residual=True, norm_before_fc=True, norm_output=True, ttt_steps=3),
+        train=dict(loss_fn="kl_div", ttt_steps=3, ttt_step_loss_decay=1.0),
+        label="eagle3 1-layer draft for llama-3.1-8b-arch verifier",
+    ),
+    # DFlash / DSpark for a Qwen3-8B-shaped verifier: 5 layers, blocks of 16, 512 anchors, window 2048 except layer 0
+    "dflash": dict(
+        algo="dflash", verifier="qwen3_8b", seq_len=4096, draft_vocab=32000, aux=[2, 10, 18, 26, 33], draft_layers=5,
+        layer_types=["full_attention"] + ["sliding_attention"] * 4, sliding_window=2048, verifier_forward=False,
+        model=dict(block_size=16, mask_token_id=151935),
+        train=dict(loss_fn="ce", per_position_loss_weight="dpace", dpace_alpha=0.5, dflash_decay_gamma=4.0, max_anchors=512),
+        label="dflash 5-layer draft (block 16, 512 anchors) for qwen3-8b-arch verifier",
+    ),
+    "dspark": dict(
+        algo="dspark", verifier="qwen3_8b", seq_len=4096, draft_vocab=32000, aux=[2, 10, 18, 26, 33], draft_layers=5,
+        layer_types=["full_attention"] + ["sliding_attention"] * 4, sliding_window=2048, verifier_forward=False,
+        model=dict(block_size=16, mask_token_id=151935, markov_rank=256, markov_head_type="vanilla", enable_confidence_head=True,
+                   confidence_head_with_markov=True),
+        train=dict(loss_fn="kl_div", per_position_loss_weight="fixed-exp-decay", dflash_decay_gamma=4.0, max_anchors=512,
+                   confidence_head_alpha=1.0),
+        label="dspark 5-layer draft (block 16, 512 anchors, markov + confidence heads) for qwen3-8b-arch verifier",
+    ),
+    # P-EAGLE, 1 draft layer at the width of a Llama-3.3-70B-shaped verifier, 4 parallel depths
+    "peagle": dict(
+        algo="peagle", verifier="llama33_70b", seq_len=2048, draft_vocab=32000, aux=[2, 40, 77], draft_layers=1,
+        layer_types=["sliding_attention"], sliding_window=2048, verifier_forward=False,
+        model=dict(norm_before_residual=True, norm_before_fc=True, norm_output=True, num_depths=4, mask_token_id=128255),
+        train=dict(loss_fn="kl_div", num_depths=4, down_sample_ratio=0.7, down_sample_ratio_min=0.2),
+        label="peagle 1-layer draft (4 depths) for llama-3.3-70b-arch verifier",
+    ),
+    # the CPU / gloo plumbing configuration (tiny Llama verifier run for the hidden states)
+    "tiny": dict(
+        algo="eagle3", verifier="tiny", seq_len=128, draft_vocab=512, aux=[1, 2, 3], draft_layers=1,
+        layer_types=["sliding_attention"], sliding_window=2048, verifier_forward=True,
+        model=dict(norm_before_residual=True, norm_before_fc=True, norm_output=True, ttt_steps=3),
+        train=dict(loss_fn="kl_div", ttt_steps=3, ttt_step_loss_decay=1.0),
+        label="tiny",
+    ),
+}
+
+
+def resolve_config(args) -> dict:
+    """The configuration entry with the command line's overrides applied."""
+    name = args.config or ("tiny" if args.model == "tiny" else "eagle3")
+    c = {k: (dict(v) if isinstance(v, dict) else v) for k, v in CONFIGS[name].items()}
+    c["name"] = name
+    if args.seq_len:
+        c["seq_len"] = args.seq_len
+    if args.draft_vocab:
+        c["draft_vocab"] = args.draft_vocab
+    if args.ttt_steps and c["algo"] == "eagle3":
+        c["model"]["ttt_steps"] = c["train"]["ttt_steps"] = args.ttt_steps
+    if args.no_verifier_forward:
+        c["verifier_forward"] = False
+    if args.scale == "tiny" and name != "tiny":
+        # the same algorithm and flags at plumbing size (CPU checks of this script)
+        c.update(verifier="tiny", seq_len=args.seq_len or 256, draft_vocab=args.draft_vocab or 512, aux=list(range(1, len(c["aux"]) + 1)))
+        if "mask_token_id" in c["model"]:
+            c["model"]["mask_token_id"] = TINY["vocab_size"] - 1
+        if "max_anchors" in c["train"]:
+            c["train"]["max_anchors"] = 16
+        c["label"] += " (tiny scale)"
+        c["name"] += "_tiny"
+    c["metric"] = METRIC if name in ("eagle3", "tiny") else f"{c['algo'].upper()} draft-train tokens/s at 1/2/4/8 B200 (device max over ranks)"
+    return c
 
 
 def parse_args():
@@ -53,10 +128,12 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--regions", type=int, default=5, help="timed regions of --steps steps each; the median is reported")
-    ap.add_argument("--model", choices=["llama31_8b", "tiny"], default="llama31_8b")
-    ap.add_argument("--seq-len", type=int, default=2048)
+    ap.add_argument("--config", choices=sorted(CONFIGS), default=None, help="measured configuration (default: eagle3, the headline)")
+    ap.add_argument("--model", choices=["llama31_8b", "tiny"], default="llama31_8b", help="'tiny' = --config tiny")
+    ap.add_argument("--scale", choices=["full", "tiny"], default="full", help="'tiny': the chosen configuration at plumbing size")
+    ap.add_argument("--seq-len", type=int, default=None)
     ap.add_argument("--draft-vocab", type=int, default=None)
-    ap.add_argument("--ttt-steps", type=int, default=3)
+    ap.add_argument("--ttt-steps", type=int, default=None)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-verifier-forward", action="store_true", help="draw hidden states from N(0,1) instead of running the random-init verifier")
     ap.add_argument("--device", default=None)
@@ -117,25 +194,29 @@ def dist_env():
     return int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
 
 
-def model_config(args):
-    cfg = dict(LLAMA31_8B if args.model == "llama31_8b" else TINY)
-    draft_vocab = args.draft_vocab or (32000 if args.model == "llama31_8b" else 512)
-    return cfg, draft_vocab
+def inputs_tag(c: dict, device_type: str) -> str:
+    return f"{c['name']}_s{c['seq_len']}_v{c['draft_vocab']}_{'vf' if c['verifier_forward'] else 'rand'}_{device_type}"
 
 
-def inputs_tag(args, device_type: str) -> str:
-    return f"{args.model}_s{args.seq_len}_v{args.draft_vocab or 0}_{'rand' if args.no_verifier_forward else 'vf'}_{device_type}"
-
-
-def config_record(args, world: int, draft_vocab: int) -> dict:
+def config_record(c: dict, world: int, regions: int) -> dict:
     """What is being measured: identical in both arms (how each arm runs it goes under ``impl_detail``)."""
     return {
-        "model": "eagle3 1-layer draft for llama-3.1-8b-arch verifier" if args.model == "llama31_8b" else "tiny",
-        "global_batch": world, "seq_len": args.seq_len, "parallelism": f"dp{world}" + ("-sharded" if world > 1 else ""),
-        "draft_vocab": draft_vocab, "ttt_steps": args.ttt_steps, "optimizer": "adamw lr 1e-4", "loss": "kl_div",
-        "regions": args.regions, "parity_steps": PARITY_STEPS,
-        "l2": "per-step working set (1.9 GB of weights + activations) exceeds the 126 MB L2; 2 distinct input batches alternate",
+        "model": c["label"], "global_batch": world, "seq_len": c["seq_len"], "parallelism": f"dp{world}" + ("-sharded" if world > 1 else ""),
+        "draft_vocab": c["draft_vocab"], "algorithm": c["algo"], "model_kwargs": c["model"], "train_kwargs": c["train"],
+        "optimizer": "adamw lr 1e-4", "regions": regions, "parity_steps": PARITY_STEPS,
+        "l2": "per-step working set (GBs of weights + activations) exceeds the 126 MB L2; 2 distinct input batches alternate",
     }
+
+
+def data_note(c: dict) -> str:
+    hs = "hidden states from a plain-PyTorch forward of the random-init verifier" if c["verifier_forward"] else "hidden states drawn N(0, 1)"
+    return f"synthetic (seeded uniform tokens; {hs}; seeded draft init; both arms read the same files)"
+
+
+def draft_layer_config(c: dict) -> dict:
+    """Decoder hyper-parameters of the draft: the verifier's widths, ``draft_layers`` layers."""
+    v = VERIFIERS[c["verifier"]]
+    return dict(v, num_hidden_layers=c["draft_layers"], sliding_window=c["sliding_window"], layer_types=list(c["layer_types"]))
 
 
 def timed_region(torch, dist, world, device, fn_step, batches, steps, offset=0, lookahead=False):
@@ -198,6 +279,7 @@ def run_ours(args):
     import speculators_b200 as sb
     from speculators_b200 import ops
     from speculators_b200.layer_config import TransformerLayerConfig
+    from speculators_b200.model import SpeculatorModel
     from speculators_b200.parallel import maybe_destroy_distributed, maybe_setup_distributed
     from speculators_b200.train import Trainer, TrainerConfig
     from speculators_b200.train.synthetic import SyntheticLoader
@@ -208,29 +290,30 @@ def run_ours(args):
     cuda = device.type == "cuda"
     if cuda:
         torch.cuda.set_device(device)
-    cfg, draft_vocab = model_config(args)
+    c = resolve_config(args)
+    cfg, draft_vocab = VERIFIERS[c["verifier"]], c["draft_vocab"]
     torch.manual_seed(0)
 
     def barrier():
         if world > 1:
             dist.barrier()
 
-    tag = inputs_tag(args, device.type)
+    tag = inputs_tag(c, device.type)
     root = bench_inputs.ensure_inputs(
-        cfg, tag, seq_len=args.seq_len, draft_vocab=draft_vocab, layer_ids=AUX_LAYERS[args.model], rank=rank, local_rank=local_rank,
-        n_batches=2, device=device, verifier_forward=not args.no_verifier_forward, barrier=barrier,
+        cfg, tag, seq_len=c["seq_len"], draft_vocab=draft_vocab, layer_ids=c["aux"], rank=rank, local_rank=local_rank,
+        n_batches=2, device=device, verifier_forward=c["verifier_forward"], barrier=barrier,
     )
     d2t, t2d = bench_inputs.load_vocab_maps(root)
     batches = bench_inputs.load_batches(root, rank, pin=cuda)
-    draft_cfg = TransformerLayerConfig(**dict(cfg, num_hidden_layers=1, sliding_window=2048, layer_types=["sliding_attention"]))
-    model = sb.Eagle3DraftModel.from_training_args(
-        draft_cfg, t2d=t2d, d2t=d2t, draft_vocab_size=draft_vocab, norm_before_residual=True, norm_before_fc=True,
-        norm_output=True, ttt_steps=args.ttt_steps, verifier_name_or_path=os.path.join(root, "verifier"), target_layer_ids=AUX_LAYERS[args.model],
+    model_class = SpeculatorModel.registry[c["algo"]]
+    model = model_class.from_training_args(
+        TransformerLayerConfig(**draft_layer_config(c)), t2d=t2d, d2t=d2t, draft_vocab_size=draft_vocab,
+        verifier_name_or_path=os.path.join(root, "verifier"), target_layer_ids=c["aux"], **c["model"],
     )
     init = bench_inputs.seeded_draft_init({k: tuple(v.shape) for k, v in model.state_dict().items()})
     missing = model.load_state_dict(init, strict=False)
     assert not missing.unexpected_keys, missing.unexpected_keys
-    train_kwargs, _ = sb.Eagle3DraftModel.get_trainer_kwargs(loss_fn="kl_div", ttt_steps=args.ttt_steps, ttt_step_loss_decay=1.0)
+    train_kwargs, _ = model_class.get_trainer_kwargs(**c["train"])
     loader = SyntheticLoader(batches, args.steps + args.warmup)
     trainer = Trainer(model, TrainerConfig(
         lr=1e-4, num_epochs=1, save_path=os.path.join(tempfile.gettempdir(), "sb200_bench_unused"), train_call_kwargs=train_kwargs,
@@ -299,12 +382,11 @@ def run_ours(args):
     e2e = world * tokens_per_step * args.steps / (ms_e2e / 1000.0)
     if rank == 0:
         record = {
-            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "metric": c["metric"], "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if cuda else "fp32",
-            "data": "synthetic (seeded uniform tokens; hidden states from a plain-PyTorch forward of the random-init verifier; seeded draft init; "
-                    "both arms read the same files)",
+            "data": data_note(c),
             "impl": "ours",
-            "config": config_record(args, world, draft_vocab),
+            "config": config_record(c, world, args.regions),
             "impl_detail": {
                 "optimizer_comm": ("nvls multimem" if getattr(trainer.engine, "nvls", False) else "nvlink p2p" if getattr(trainer.engine, "p2p", False)
                                    else ("nccl" if cuda else "gloo") if world > 1 else "none"),
@@ -405,13 +487,14 @@ def run_reference(args):
 
         import torch
         import torch.distributed as dist
-        from transformers import LlamaConfig
+        from transformers import LlamaConfig, Qwen3Config
 
         spec = importlib.util.spec_from_file_location("bench_inputs", os.path.join(REPO, "bench_inputs.py"))
         bench_inputs = importlib.util.module_from_spec(spec)
         spec.loader.exec_module(bench_inputs)
 
-        from speculators.models.eagle3.core import Eagle3DraftModel
+        import speculators.models  # noqa: F401  (registers the algorithms)
+        from speculators.model import SpeculatorModel
         from speculators.train.distributed import maybe_destroy_distributed, maybe_setup_distributed
         from speculators.train.trainer import Trainer, TrainerConfig
     except Exception as err:  # noqa: BLE001
@@ -425,39 +508,40 @@ def run_reference(args):
     maybe_setup_distributed()
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
-    cfg, draft_vocab = model_config(args)
+    c = resolve_config(args)
+    cfg, draft_vocab = VERIFIERS[c["verifier"]], c["draft_vocab"]
     torch.manual_seed(0)
 
     def barrier():
         if world > 1:
             dist.barrier()
 
-    tag = inputs_tag(args, "cuda")
+    tag = inputs_tag(c, "cuda")
     root = bench_inputs.ensure_inputs(
-        cfg, tag, seq_len=args.seq_len, draft_vocab=draft_vocab, layer_ids=AUX_LAYERS[args.model], rank=rank, local_rank=local_rank,
-        n_batches=2, device=device, verifier_forward=not args.no_verifier_forward, barrier=barrier,
+        cfg, tag, seq_len=c["seq_len"], draft_vocab=draft_vocab, layer_ids=c["aux"], rank=rank, local_rank=local_rank,
+        n_batches=2, device=device, verifier_forward=c["verifier_forward"], barrier=barrier,
     )
     d2t, t2d = bench_inputs.load_vocab_maps(root)
     batches = bench_inputs.load_batches(root, rank, pin=True)
 
-    hf_cfg = LlamaConfig(**{k: v for k, v in cfg.items() if k not in ("architectures", "model_type", "rope_theta")})
-    hf_cfg.num_hidden_layers = 1
-    hf_cfg.sliding_window = 2048
-    hf_cfg.layer_types = ["sliding_attention"]
+    draft = draft_layer_config(c)
+    hf_class = Qwen3Config if draft["model_type"] == "qwen3" else LlamaConfig
+    hf_cfg = hf_class(**{k: v for k, v in draft.items() if k not in ("architectures", "model_type", "rope_theta")})
     try:
         hf_cfg.rope_parameters = {"rope_type": "default", "rope_theta": cfg["rope_theta"]}
     except Exception:  # noqa: BLE001
         hf_cfg.rope_theta = cfg["rope_theta"]
-    model = Eagle3DraftModel.from_training_args(
-        hf_cfg, t2d=t2d, d2t=d2t, draft_vocab_size=draft_vocab, norm_before_residual=True, norm_before_fc=True,
-        norm_output=True, ttt_steps=args.ttt_steps, verifier_name_or_path=os.path.join(root, "verifier"), target_layer_ids=AUX_LAYERS[args.model],
+    model_class = SpeculatorModel.registry[c["algo"]]
+    model = model_class.from_training_args(
+        hf_cfg, t2d=t2d, d2t=d2t, draft_vocab_size=draft_vocab, verifier_name_or_path=os.path.join(root, "verifier"),
+        target_layer_ids=c["aux"], **c["model"],
     )
     init = bench_inputs.seeded_draft_init({k: tuple(v.shape) for k, v in model.state_dict().items()})
     with torch.no_grad():
         own = model.state_dict()
         for k, v in init.items():
             own[k].copy_(v)
-    train_kwargs, _ = Eagle3DraftModel.get_trainer_kwargs(loss_fn="kl_div", loss_implementation="fused", ttt_steps=args.ttt_steps, ttt_step_loss_decay=1.0)
+    train_kwargs, _ = model_class.get_trainer_kwargs(loss_implementation="fused", **c["train"])
     tokens_per_step = sum(int((b["document_ids"] != -1).sum()) for b in batches) / len(batches)
 
     class Capture(logging.Handler):
@@ -561,12 +645,11 @@ def run_reference(args):
     d2h = 8 + 4 * n_metrics if n_metrics is not None else 12
     if rank == 0:
         record = {
-            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "metric": c["metric"], "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic (seeded uniform tokens; hidden states from a plain-PyTorch forward of the random-init verifier; seeded draft init; "
-                    "both arms read the same files)",
+            "data": data_note(c),
             "impl": "reference",
-            "config": config_record(args, world, draft_vocab),
+            "config": config_record(c, world, args.regions),
             "impl_detail": {
                 "optimizer_comm": "fsdp2 (nccl)" if world > 1 else "none", "cuda_graph": False,
                 "path": "speculators.train.trainer.Trainer.train_epoch, torch.compile + flex attention + fused Triton loss (stock)",

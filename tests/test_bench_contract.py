@@ -41,12 +41,16 @@ def test_both_arms_print_the_same_config_record():
     sys.path.insert(0, REPO)
     import bench
 
-    args = argparse.Namespace(model="llama31_8b", seq_len=2048, ttt_steps=3, regions=5, draft_vocab=None)
-    a = bench.config_record(args, 8, 32000)
-    b = bench.config_record(args, 8, 32000)
-    assert a == b and a["parallelism"] == "dp8-sharded" and a["global_batch"] == 8
+    args = argparse.Namespace(model="llama31_8b", config=None, seq_len=None, ttt_steps=None, regions=5, draft_vocab=None, no_verifier_forward=False)
+    c = bench.resolve_config(args)
+    assert c["name"] == "eagle3" and c["seq_len"] == 2048 and c["draft_vocab"] == 32000 and c["metric"] == bench.METRIC
+    a = bench.config_record(c, 8, 5)
+    assert a["parallelism"] == "dp8-sharded" and a["global_batch"] == 8 and a["algorithm"] == "eagle3"
     src = open(os.path.join(REPO, "bench.py")).read()
-    assert src.count('"config": config_record(args, world, draft_vocab)') == 2
+    assert src.count('"config": config_record(c, world, args.regions)') == 2  # one expression, both arms
+    for name in ("dflash", "dspark", "peagle"):
+        args.config = name
+        assert bench.resolve_config(args)["algo"] == name
 
 
 def test_seeded_init_depends_on_names_only():
