@@ -41,7 +41,7 @@ def test_both_arms_print_the_same_config_record():
     sys.path.insert(0, REPO)
     import bench
 
-    args = argparse.Namespace(model="llama31_8b", config=None, seq_len=None, ttt_steps=None, regions=5, draft_vocab=None, no_verifier_forward=False)
+    args = argparse.Namespace(model="llama31_8b", config=None, seq_len=None, ttt_steps=None, regions=5, draft_vocab=None, no_verifier_forward=False, scale="full")
     c = bench.resolve_config(args)
     assert c["name"] == "eagle3" and c["seq_len"] == 2048 and c["draft_vocab"] == 32000 and c["metric"] == bench.METRIC
     a = bench.config_record(c, 8, 5)
