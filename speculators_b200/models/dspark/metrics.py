@@ -1,7 +1,12 @@
-"""DSpark loss and metrics (src/speculators/models/dspark/metrics.py:49-163):
-``loss = compound(logits, targets) + alpha * BCE(confidence, accept_rate)`` where
-``accept_rate = 1 - TV(logits, targets)`` is computed analytically and detached;
-plus calibration counters and the expected accepted length per block."""
+"""DSpark loss and metrics (values and key names of src/speculators/models/dspark/metrics.py:49-163).
+
+``loss = L(logits, targets) + alpha * BCE(confidence, a)`` with ``a = 1 - TV(logits, targets)`` the
+analytic per-slot acceptance rate (detached).  Reported next to it: calibration of the confidence
+head (mean absolute error, mean prediction, bias of the running product inside a block), the
+acceptance rate, the expected accepted length per block ``1 + sum_k prod_{j<=k} a_j`` and the
+per-slot accuracies.  All counters of a step are formed from one ``[rows, n]`` stack and a single
+reduction, so the metric tail is a handful of kernels whatever the number of counters.
+"""
 
 from __future__ import annotations
 
@@ -17,12 +22,14 @@ __all__ = ["compute_metrics"]
 _EPS = 1e-8
 
 
-def _masked_decayed_mean(elementwise, loss_mask, pos_idx, decay_fn):
-    mask = loss_mask.to(elementwise.dtype)
-    weighted = elementwise * mask
-    if decay_fn is not None:
-        weighted = weighted * decay_fn(pos_idx.to(weighted.dtype), elementwise_loss=elementwise)
-    return (weighted.sum(dim=1) / (mask.sum(dim=1) + _EPS)).mean()
+def _per_block(x: torch.Tensor, block_size: int, first_slot: int) -> torch.Tensor:
+    """``[1, N * B]`` -> ``[N, B - first_slot]`` (the slots that draft a token)."""
+    return x.reshape(-1, block_size)[:, first_slot:]
+
+
+def _confidence_loss(bce: torch.Tensor, mask_f: torch.Tensor, weights: torch.Tensor | None) -> torch.Tensor:
+    weighted = bce * mask_f if weights is None else bce * mask_f * weights
+    return (weighted.sum(dim=1) / (mask_f.sum(dim=1) + _EPS)).mean()
 
 
 def compute_metrics(logits, targets, confidence_logits, loss_mask, block_size: int, loss_config: LossConfig, tv_loss_fn=tv_loss,
@@ -30,54 +37,48 @@ def compute_metrics(logits, targets, confidence_logits, loss_mask, block_size: i
                     dpace_alpha: float = 0.5, sample_from_anchor: bool = True):
     device = logits.device
     n = logits.shape[1]
-    pos_idx = (torch.arange(n, device=device) % block_size).unsqueeze(0)
-    start = 0 if sample_from_anchor else 1
+    first = 0 if sample_from_anchor else 1
+    slot = (torch.arange(n, device=device) % block_size).unsqueeze(0)
     decay = block_decay_fn(per_position_loss_weight, loss_mask, block_size, gamma, dpace_alpha, sample_from_anchor)
-    loss, parts, pred_ids, target_ids = weighted_terms(loss_config, logits, targets, loss_mask, pos_idx, decay)
+    loss, parts, pred_ids, target_ids = weighted_terms(loss_config, logits, targets, loss_mask, slot, decay)
 
     with torch.no_grad():
-        accept_rate = 1.0 - tv_loss_fn(logits.detach(), targets)  # [1, n]
-        blocks = n // block_size
-        draft_mask = loss_mask.to(accept_rate.dtype).view(blocks, block_size)[:, start:]
-        accept_prefix = (accept_rate.view(blocks, block_size)[:, start:] * draft_mask).cumprod(dim=-1)
+        accept = 1.0 - tv_loss_fn(logits.detach(), targets)  # [1, n] analytic acceptance rate
+        mask_f = loss_mask.to(accept.dtype)
+        drafted = _per_block(mask_f, block_size, first)
+        accept_run = (_per_block(accept, block_size, first) * drafted).cumprod(dim=-1)
+        supervised = mask_f.sum().clamp_min(1.0)
 
-    metrics: dict[str, torch.Tensor] = {}
+    counters: dict[str, tuple[torch.Tensor, torch.Tensor]] = {}
+    one = torch.ones((), device=device)
     if confidence_logits is not None:
-        bce = binary_cross_entropy_with_logits(confidence_logits.float(), accept_rate.detach().float(), reduction="none")
-        conf_loss = _masked_decayed_mean(bce, loss_mask, pos_idx, decay)
+        conf = confidence_logits.float()
+        bce = binary_cross_entropy_with_logits(conf, accept.detach().float(), reduction="none")
+        weights = decay(slot.to(bce.dtype), elementwise_loss=bce) if decay is not None else None
+        conf_loss = _confidence_loss(bce, mask_f, weights)
         loss = loss + confidence_head_alpha * conf_loss
         with torch.no_grad():
-            mask_f = loss_mask.to(accept_rate.dtype)
-            total = mask_f.sum().clamp_min(1.0)
-            prob = confidence_logits.float().sigmoid()
-            metrics["confidence_loss_sum"] = conf_loss.detach().clone()
-            metrics["confidence_loss_total"] = torch.ones((), device=device)
-            metrics["confidence_abs_error_sum"] = ((prob - accept_rate).abs() * mask_f).sum()
-            metrics["confidence_abs_error_total"] = total
-            metrics["confidence_pred_mean_sum"] = (prob * mask_f).sum()
-            metrics["confidence_pred_mean_total"] = total.clone()
-            conf_prefix = (prob.view(blocks, block_size)[:, start:] * draft_mask).cumprod(dim=-1)
-            metrics["confidence_cumprod_bias_sum"] = ((conf_prefix - accept_prefix) * draft_mask).sum()
-            metrics["confidence_cumprod_bias_total"] = draft_mask.sum().clamp_min(1.0)
+            prob = conf.sigmoid()
+            conf_run = (_per_block(prob, block_size, first) * drafted).cumprod(dim=-1)
+            counters["confidence_loss"] = (conf_loss.detach().clone(), one)
+            counters["confidence_abs_error"] = (((prob - accept).abs() * mask_f).sum(), supervised)
+            counters["confidence_pred_mean"] = ((prob * mask_f).sum(), supervised.clone())
+            counters["confidence_cumprod_bias"] = (((conf_run - accept_run) * drafted).sum(), drafted.sum().clamp_min(1.0))
 
-    one = torch.ones((), device=device)
-    metrics["loss_sum"] = loss.detach().clone()
-    metrics["loss_total"] = one
+    counters["loss"] = (loss.detach().clone(), one)
     for name, value in parts.items():
-        metrics[f"{name}_sum"] = value
-        metrics[f"{name}_total"] = one.clone()
+        counters[name] = (value, one.clone())
     with torch.no_grad():
-        mask_f = loss_mask.to(accept_rate.dtype)
-        metrics["accept_rate_sum"] = (accept_rate * mask_f).sum()
-        metrics["accept_rate_total"] = mask_f.sum().clamp_min(1.0)
-        block_len = accept_prefix.sum(dim=-1) + 1.0
-        block_valid = (draft_mask.sum(dim=-1) > 0).to(accept_rate.dtype)
-        metrics["accept_len_sum"] = (block_len * block_valid).sum()
-        metrics["accept_len_total"] = block_valid.sum().clamp_min(1.0)
-    correct, total_pos = compute_accuracy_multi_step(pred_ids.unsqueeze(0), target_ids.unsqueeze(0), loss_mask, pos_idx, block_size)
-    metrics["full_acc_sum"] = correct[start:].sum()
-    metrics["full_acc_total"] = total_pos[start:].sum()
-    for pos in range(start, block_size):
-        metrics[f"position_{pos}_acc_sum"] = correct[pos]
-        metrics[f"position_{pos}_acc_total"] = total_pos[pos]
+        counters["accept_rate"] = ((accept * mask_f).sum(), supervised.clone())
+        live = (drafted.sum(dim=-1) > 0).to(accept.dtype)  # blocks with at least one supervised drafting slot
+        counters["accept_len"] = (((accept_run.sum(dim=-1) + 1.0) * live).sum(), live.sum().clamp_min(1.0))
+    hits, seen = compute_accuracy_multi_step(pred_ids.unsqueeze(0), target_ids.unsqueeze(0), loss_mask, slot, block_size)
+    counters["full_acc"] = (hits[first:].sum(), seen[first:].sum())
+    for k in range(first, block_size):
+        counters[f"position_{k}_acc"] = (hits[k], seen[k])
+
+    metrics: dict[str, torch.Tensor] = {}
+    for name, (total, count) in counters.items():
+        metrics[f"{name}_sum"] = total
+        metrics[f"{name}_total"] = count
     return loss, metrics

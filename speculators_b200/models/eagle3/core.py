@@ -34,7 +34,7 @@ from speculators_b200.losses import LossConfig, resolve_loss_config
 from speculators_b200.model import DraftVocabMixin, SpeculatorModel
 from speculators_b200.models.eagle3.attention import causal_document_interval, ttt_attn_spec
 from speculators_b200.models.eagle3.config import Eagle3SpeculatorConfig
-from speculators_b200.models.eagle3.metrics import compute_metrics
+from speculators_b200.models.eagle3.metrics import compute_metrics, compute_metrics_from_hidden
 from speculators_b200.models.layers import MLP, Attention, DecoderLayer, Linear, RMSNorm, RotaryTable
 from speculators_b200.models.utils import resolve_target_layer_ids
 from speculators_b200.proposals.greedy import GreedyTokenProposalConfig
@@ -205,18 +205,26 @@ class Eagle3DraftModel(DraftVocabMixin, SpeculatorModel):
                 else:
                     hidden = layer(hidden, positions, self.rotary_emb, spec, past[li])
             if self.config.norm_output:
-                hidden = self.norm(hidden)
-                logits = ops.linear(hidden, self.lm_head.weight)
+                hidden = head_in = self.norm(hidden)
             else:
-                logits = ops.linear(self.norm(hidden), self.lm_head.weight)
-
-            if return_loss:
-                s_loss, s_metrics = compute_metrics(
-                    logits.unsqueeze(0), targets.unsqueeze(0), loss_mask, prev_correct, step,
-                    ttt_step_loss_decay, loss_config=loss_config,
+                head_in = self.norm(hidden)
+            fused = None
+            if return_loss and not return_draft_tokens:
+                # lm_head GEMM with the loss's forward reduction in its epilogue (CUDA, bf16, KL / CE)
+                fused = compute_metrics_from_hidden(
+                    head_in, self.lm_head.weight, targets.unsqueeze(0), loss_mask, prev_correct, step, ttt_step_loss_decay,
+                    loss_config=loss_config,
                 )
-                loss = loss + s_loss
-                metrics.update(s_metrics)
+            if fused is None:
+                logits = ops.linear(head_in, self.lm_head.weight)
+                if return_loss:
+                    fused = compute_metrics(
+                        logits.unsqueeze(0), targets.unsqueeze(0), loss_mask, prev_correct, step,
+                        ttt_step_loss_decay, loss_config=loss_config,
+                    )
+            if return_loss:
+                loss = loss + fused[0]
+                metrics.update(fused[1])
 
             if return_draft_tokens:
                 draft_tokens.append(torch.argmax(logits.detach(), dim=-1).unsqueeze(0))

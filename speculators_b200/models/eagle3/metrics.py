@@ -17,7 +17,7 @@ from speculators_b200.losses import LossConfig, exp_loss_decay, kl_div_loss, red
 from speculators_b200.losses.rowwise import rowwise_terms
 from speculators_b200.models.metrics import compute_accuracy_single_step
 
-__all__ = ["align_for_step", "compute_metrics"]
+__all__ = ["align_for_step", "compute_metrics", "compute_metrics_from_hidden"]
 
 
 def align_for_step(logits, targets, loss_mask, prev_correct, ttt_step: int):
@@ -45,20 +45,28 @@ def _single_fused_primitive(loss_config: LossConfig) -> tuple[str, float] | None
     return (name, float(weight)) if name in _PRIMITIVES and _is_fused(fn) else None
 
 
-def _compute_metrics_fused(logits, targets, loss_mask, prev_correct, ttt_step: int, decay: float, op: str, weight: float):
+def _compute_metrics_fused(logits, targets, loss_mask, prev_correct, ttt_step: int, decay: float, op: str, weight: float, head=None):
     """CUDA fast path for one fused loss term: row-loss kernel + one tail kernel (masked
-    mean, decay, accuracy counters, ``prev_correct`` update) instead of ~30 small ops."""
+    mean, decay, accuracy counters, ``prev_correct`` update) instead of ~30 small ops.  With
+    ``head = (hidden [T, H], lm_head weight)`` instead of ``logits`` the head's GEMM and the
+    forward reduction of the loss run as one kernel (``None`` is returned if that does not apply)."""
     from speculators_b200 import ops
     from speculators_b200.losses.utils import _REDUCTION_EPS
 
-    T = logits.shape[1]
+    T = logits.shape[1] if head is None else head[0].shape[0]
     rows = T - ttt_step
     mask_u8 = loss_mask.reshape(-1)[ttt_step:]
     if mask_u8.dtype not in (torch.bool, torch.uint8):
         mask_u8 = mask_u8 != 0
     prev_flat = prev_correct.reshape(-1)
     active = mask_u8.bool() | prev_flat[:rows]
-    row_loss, pred, tgt = ops.fused_row_loss_raw(op, logits.reshape(T, -1), targets.reshape(targets.shape[1], -1), ttt_step, rows, active)
+    if head is None:
+        row_loss, pred, tgt = ops.fused_row_loss_raw(op, logits.reshape(T, -1), targets.reshape(targets.shape[1], -1), ttt_step, rows, active)
+    else:
+        fused = ops.lm_head_loss_raw(op, head[0], head[1], targets.reshape(targets.shape[1], -1), ttt_step, rows, active)
+        if fused is None:
+            return None
+        row_loss, pred, tgt = fused
     out = ops.ttt_step_tail(row_loss, pred, tgt, mask_u8.contiguous(), prev_flat, decay, _REDUCTION_EPS)
     loss = out[0] * weight if weight != 1.0 else out[0]
     stats = out.detach()
@@ -69,6 +77,24 @@ def _compute_metrics_fused(logits, targets, loss_mask, prev_correct, ttt_step: i
         f"cond_acc_{ttt_step}_sum": stats[1], f"cond_acc_{ttt_step}_total": stats[3],
     }
     return loss, metrics
+
+
+def compute_metrics_from_hidden(hidden, head_weight, targets, loss_mask, prev_correct, ttt_step: int, ttt_step_loss_decay: float,
+                                loss_config: LossConfig | None = None):
+    """``compute_metrics`` of ``hidden @ head_weight.T`` without a separate pass over the
+    logits: the lm_head GEMM's epilogue reduces each tile for the loss.  Returns ``None`` when
+    that path does not apply (not CUDA bf16, a loss other than one fused KL / CE term, ...);
+    the caller then forms the logits and calls ``compute_metrics``."""
+    if loss_config is None:
+        loss_config = {"kl_div": (kl_div_loss, 1.0)}
+    if not (USE_FUSED_TAIL and hidden.is_cuda and hidden.dtype == torch.bfloat16 and hidden.dim() == 2 and loss_mask is not None
+            and prev_correct is not None and prev_correct.dtype == torch.bool and prev_correct.is_contiguous()):
+        return None
+    single = _single_fused_primitive(loss_config)
+    if single is None:
+        return None
+    return _compute_metrics_fused(None, targets, loss_mask, prev_correct, ttt_step, float(ttt_step_loss_decay) ** ttt_step, *single,
+                                  head=(hidden, head_weight))
 
 
 def compute_metrics(logits, targets, loss_mask, prev_correct, ttt_step: int, ttt_step_loss_decay: float, loss_config: LossConfig | None = None):

@@ -30,6 +30,7 @@ __all__ = [
     "check_gemm_status",
     "gemm_status",
     "linear",
+    "lm_head_loss_raw",
     "masked_attention",
     "matmul_nn",
     "matmul_nt",
@@ -181,40 +182,47 @@ class _LinearFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         x2, weight = ctx.saved_tensors
-        r0, r1 = ctx.rows
-        w = weight if r0 is None else weight[r0:r1]
-        dy2 = dy if (dy.stride(-1) == 1 and dy.stride(0) % 8 == 0 and dy.data_ptr() % 16 == 0) else dy.contiguous()
-        dx = dw = None
-        own = _own_gemm_enabled() and _gemm_operand_ok(dy2) and _gemm_operand_ok(w) and _gemm_operand_ok(x2)
-        if ctx.needs_input_grad[0]:
-            dx = _dgrad_gemm(dy2, w) if own else dy2 @ w
-        if ctx.needs_input_grad[1]:
-            flat = getattr(weight, "_flat_grad", None)
-            if flat is not None:
-                target = flat if r0 is None else flat[r0:r1]
-                fresh = getattr(weight, "_grad_fresh", False)
-                if fresh:
-                    # first gradient of this weight since the engine's zero_grad, which left
-                    # the buffer uncleared: store instead of accumulate
-                    weight._grad_fresh = False
-                    if r0 is not None:
-                        flat.zero_()
-                if own and _gemm_operand_ok(target):
-                    _wgrad_gemm(dy2, x2, target, accumulate=not fresh or r0 is not None)
-                elif fresh and r0 is None:
-                    torch.mm(dy2.t(), x2, out=flat)
-                else:
-                    target.addmm_(dy2.t(), x2)
-            elif r0 is None:
-                dw = _wgrad_gemm(dy2, x2, None, accumulate=False) if own else dy2.t() @ x2
-            else:
-                dw = torch.zeros_like(weight)
-                if own and _gemm_operand_ok(dw[r0:r1]):
-                    _wgrad_gemm(dy2, x2, dw[r0:r1], accumulate=False)
-                else:
-                    dw[r0:r1] = dy2.t() @ x2
+        dx, dw = _linear_backward(x2, weight, ctx.rows, dy, ctx.needs_input_grad[0], ctx.needs_input_grad[1])
         dres = dy if ctx.has_residual and ctx.needs_input_grad[2] else None
         return dx, dw, dres, None, None
+
+
+def _linear_backward(x2, weight, rows, dy, need_dx: bool, need_dw: bool):
+    """``(dx, dw)`` of ``y = x2 @ weight[rows].T``; ``dw`` is ``None`` when the gradient went
+    straight into the flat buffer the training engine attached to the weight."""
+    r0, r1 = rows
+    w = weight if r0 is None else weight[r0:r1]
+    dy2 = dy if (dy.stride(-1) == 1 and dy.stride(0) % 8 == 0 and dy.data_ptr() % 16 == 0) else dy.contiguous()
+    dx = dw = None
+    own = _own_gemm_enabled() and _gemm_operand_ok(dy2) and _gemm_operand_ok(w) and _gemm_operand_ok(x2)
+    if need_dx:
+        dx = _dgrad_gemm(dy2, w) if own else dy2 @ w
+    if need_dw:
+        flat = getattr(weight, "_flat_grad", None)
+        if flat is not None:
+            target = flat if r0 is None else flat[r0:r1]
+            fresh = getattr(weight, "_grad_fresh", False)
+            if fresh:
+                # first gradient of this weight since the engine's zero_grad, which left
+                # the buffer uncleared: store instead of accumulate
+                weight._grad_fresh = False
+                if r0 is not None:
+                    flat.zero_()
+            if own and _gemm_operand_ok(target):
+                _wgrad_gemm(dy2, x2, target, accumulate=not fresh or r0 is not None)
+            elif fresh and r0 is None:
+                torch.mm(dy2.t(), x2, out=flat)
+            else:
+                target.addmm_(dy2.t(), x2)
+        elif r0 is None:
+            dw = _wgrad_gemm(dy2, x2, None, accumulate=False) if own else dy2.t() @ x2
+        else:
+            dw = torch.zeros_like(weight)
+            if own and _gemm_operand_ok(dw[r0:r1]):
+                _wgrad_gemm(dy2, x2, dw[r0:r1], accumulate=False)
+            else:
+                dw[r0:r1] = dy2.t() @ x2
+    return dx, dw
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None, residual: torch.Tensor | None = None,
@@ -495,6 +503,47 @@ class _RowLossFn(torch.autograd.Function):
         op, shift, rows = ctx.cfg
         d = native().loss_bwd(op, logits, targets, dloss.contiguous().float(), stats, shift, rows)
         return d, None, None, None, None, None
+
+
+class _LmHeadLossFn(torch.autograd.Function):
+    """``fused_row_loss(op, hidden @ weight.T, targets, shift, rows, active)`` with the head's GEMM
+    and the forward reduction of the loss in one kernel: the logits tile is reduced to
+    online-softmax records while it is still in tensor memory, so the forward never re-reads
+    ``[T, V]`` logits and targets.  The logits are stored (bf16) for the backward pass, which is
+    the row-loss backward kernel followed by the input-gradient GEMM."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, targets, op, shift, rows, active):
+        logits, loss, stats, am_d, am_t = native().lmhead_loss_fwd(op, hidden, weight, targets, active, shift, rows, gemm_status(hidden.device))
+        ctx.save_for_backward(hidden, weight, targets, logits, stats)
+        ctx.cfg = (op, shift, rows)
+        ctx.mark_non_differentiable(am_d, am_t)
+        return loss, am_d, am_t
+
+    @staticmethod
+    def backward(ctx, dloss, _a, _b):
+        hidden, weight, targets, logits, stats = ctx.saved_tensors
+        op, shift, rows = ctx.cfg
+        d = native().loss_bwd(op, logits, targets, dloss.contiguous().float(), stats, shift, rows)
+        dx, dw = _linear_backward(hidden, weight, (None, None), d, ctx.needs_input_grad[0], ctx.needs_input_grad[1])
+        return dx, dw, None, None, None, None, None
+
+
+FUSED_HEAD_OPS = ("kl_div", "ce")
+
+
+def lm_head_loss_raw(op: str, hidden: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor, shift: int, rows: int, active):
+    """Per-row loss between ``(hidden @ weight.T)[r]`` and ``targets[r + shift]`` for ``r < rows``
+    plus both argmaxes (int32), like ``fused_row_loss_raw`` on the product; ``None`` when the
+    fused head does not apply (other loss, other dtype / layout, switched off with
+    ``SB200_FUSED_HEAD=0``) and the caller should form the logits itself."""
+    import os
+
+    if (op not in FUSED_HEAD_OPS or not _own_gemm_enabled() or os.environ.get("SB200_FUSED_HEAD", "1") == "0"
+            or not (_gemm_operand_ok(hidden) and _gemm_operand_ok(weight) and _gemm_operand_ok(targets))
+            or weight.shape[0] % 8 or hidden.shape[0] <= 128):
+        return None
+    return _LmHeadLossFn.apply(hidden, weight, targets, LOSS_OPS[op], shift, rows, active)
 
 
 class _StepTailFn(torch.autograd.Function):

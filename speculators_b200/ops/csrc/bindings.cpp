@@ -34,6 +34,11 @@ int launch_gemm_tn_tcgen05(const void*, const void*, void*, const void*, int, in
                            int*, int, cudaStream_t);
 int launch_gemm_tcgen05(const void*, const void*, void*, const void*, int, int, int, int64_t, int64_t, int64_t, int64_t, int, int, int,
                         int*, int, cudaStream_t);
+int lmhead_stat_words();
+int lmhead_tiles_n(int);
+int launch_lmhead_logits_stats(const void*, const void*, void*, const void*, int, int, int, int64_t, int64_t, int64_t, int64_t, int, int, float*,
+                               int*, cudaStream_t);
+int launch_lmhead_combine(const float*, const void*, const uint8_t*, float*, float*, int*, int*, int, int, int64_t, int, cudaStream_t);
 int sumsq_num_partials();
 int peer_malloc(int64_t, void**);
 int peer_free(void*);
@@ -188,6 +193,45 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> loss_fwd(int64_t op, const Tensor& lo
                                         (int)shift, cur_stream());
   TORCH_CHECK(rc == 0, "loss_fwd: unknown op ", op);
   return {loss, stats, am_d, am_t};
+}
+
+// lm_head product fused with the row loss: logits = x @ w^T on the tcgen05 kernel whose epilogue also
+// reduces every (row, 256-column tile) of the logits and of targets[row + shift] to online-softmax
+// records; a second kernel merges them into the outputs of loss_fwd.  op 0 (KL) or 3 (CE on the argmax).
+std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> lmhead_loss_fwd(int64_t op, const Tensor& x, const Tensor& w, const Tensor& targets,
+                                                                   const c10::optional<Tensor>& active, int64_t shift, int64_t rows,
+                                                                   Tensor status) {
+  check_rows(x, "x");
+  check_rows(w, "w");
+  check_rows(targets, "targets");
+  TORCH_CHECK(op == 0 || op == 3, "lmhead_loss_fwd: op 0 (kl) or 3 (ce)");
+  const int64_t M = x.size(0), K = x.size(1), N = w.size(0);
+  TORCH_CHECK(w.size(1) == K && targets.size(1) == N && N % 8 == 0, "lmhead_loss_fwd: shape mismatch");
+  TORCH_CHECK(rows >= 0 && rows <= M && shift >= 0 && rows + shift <= targets.size(0));
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == at::kInt && status.numel() >= 1);
+  c10::cuda::CUDAGuard guard(x.device());
+  auto fopt = x.options().dtype(at::kFloat);
+  const int tiles_n = sb200::lmhead_tiles_n((int)N);
+  Tensor logits = at::empty({M, N}, x.options());
+  Tensor partial = at::empty({M, tiles_n, sb200::lmhead_stat_words()}, fopt);
+  Tensor loss = at::empty({rows}, fopt);
+  Tensor stats = at::empty({5, rows}, fopt);
+  Tensor am_d = at::empty({rows}, x.options().dtype(at::kInt));
+  Tensor am_t = at::empty({rows}, x.options().dtype(at::kInt));
+  const uint8_t* act = nullptr;
+  if (active.has_value()) {
+    TORCH_CHECK((active->scalar_type() == at::kBool || active->scalar_type() == at::kByte) && active->is_contiguous() &&
+                active->numel() == rows);
+    act = reinterpret_cast<const uint8_t*>(active->data_ptr());
+  }
+  int rc = sb200::launch_lmhead_logits_stats(x.data_ptr(), w.data_ptr(), logits.data_ptr(), targets.data_ptr(), (int)M, (int)N, (int)K,
+                                             x.stride(0), w.stride(0), logits.stride(0), targets.stride(0), (int)targets.size(0),
+                                             (int)shift, partial.data_ptr<float>(), status.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(rc == 0, "lmhead_loss_fwd: GEMM launch failed (", rc, ")");
+  rc = sb200::launch_lmhead_combine(partial.data_ptr<float>(), logits.data_ptr(), act, loss.data_ptr<float>(), stats.data_ptr<float>(),
+                                    am_d.data_ptr<int>(), am_t.data_ptr<int>(), (int)rows, tiles_n, logits.stride(0), (int)op, cur_stream());
+  TORCH_CHECK(rc == 0, "lmhead_loss_fwd: combine launch failed (", rc, ")");
+  return {logits, loss, stats, am_d, am_t};
 }
 
 // Token cross-entropy: labels int64[rows]; rows with keep == 0 cost nothing and get loss 0.
@@ -734,6 +778,7 @@ TORCH_LIBRARY(sb200, m) {
   m.def("hs_pop", &hs_pop);
   m.def("gemm_tn", &gemm_tn);
   m.def("gemm", &gemm);
+  m.def("lmhead_loss_fwd", &lmhead_loss_fwd);
   m.def("gemm_tn_variant", &gemm_tn_variant);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_fwd_tc", &attn_fwd_tc);

@@ -37,6 +37,7 @@
 // caller's status word and leaves its loop; the other roles then run out of budget (or
 // see the status word) too, the CTA meets at the final barrier, frees its TMEM and
 // returns.  Nothing traps and nothing spins forever.
+#include "loss_stats.cuh"
 #include "tcgen05_utils.cuh"
 
 namespace sb200 {
@@ -52,6 +53,22 @@ constexpr int kDefaultPairVariant = 3;
 enum Epilogue : int { kStore = 0, kAccumulate = 1, kAddResidual = 2 };
 enum Status : int { kOk = kStatusOk, kTimeoutProducer = 1, kTimeoutMma = 2, kTimeoutEpilogue = 3 };
 
+// Row statistics in the epilogue (the lm_head product fused with the row loss): next to
+// storing the logits tile, every thread reduces its row's 256 columns of the tile, together with
+// the same columns of the target logits row `row + shift`, to the online-softmax statistics of
+// both and the cross term of the KL divergence, and writes them as one record of kStatWords
+// floats at partial[(row * tiles_n + tile_n) * kStatWords].  A second kernel merges a row's
+// records.  The statistics are taken from the bf16-rounded logits, i.e. from the values the
+// backward pass reads back.
+constexpr int kStatWords = 12;  // m_d z_d best_d idx_d | m_t z_t A best_t | idx_t - - -
+struct RowStatsOut {
+  const __nv_bfloat16* targets;  // nullptr: plain GEMM
+  int64_t ldt;
+  int t_rows;   // rows of the target matrix
+  int shift;    // logits row r pairs with target row r + shift
+  float* partial;
+};
+
 struct Params {
   __nv_bfloat16* c;
   const __nv_bfloat16* residual;
@@ -59,6 +76,7 @@ struct Params {
   int64_t ldc, ldr;
   int epilogue;
   int* status;
+  RowStatsOut rs;
 };
 
 // 32-byte store (one full sector) of sixteen bf16; ptr must be 32-byte aligned.
@@ -175,6 +193,53 @@ __device__ __forceinline__ void store_accumulator_prefetched(const Params& p, ui
 #pragma unroll
       for (int v = 0; v < 4; ++v) st8(crow + c * 32 + v * 8, packed[v]);
     }
+  }
+}
+
+// ---- logits tile + row statistics ------------------------------------------------------------
+__device__ __forceinline__ void prefetch_targets(const Params& p, int row, int n0, RowPrefetch& pre) {
+  const int trow = row + p.rs.shift;
+  pre.valid = row < p.M && trow < p.rs.t_rows;
+  const __nv_bfloat16* src = p.rs.targets + (int64_t)trow * p.rs.ldt + n0;
+#pragma unroll
+  for (int i = 0; i < BN / 8; ++i) {
+    if (pre.valid && n0 + i * 8 + 8 <= p.N) pre.v[i] = __ldg(reinterpret_cast<const uint4*>(src) + i);
+    else pre.v[i] = make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
+// Requires N % 8 == 0, ldc % 8 == 0 and 16-byte aligned C / target rows (checked on the host).
+__device__ __forceinline__ void store_accumulator_with_stats(const Params& p, uint32_t taddr, int row, int n0, int tile_n, int tiles_n,
+                                                             const RowPrefetch& pre) {
+  __nv_bfloat16* crow = p.c + (int64_t)row * p.ldc + n0;
+  RowStats sd{-INFINITY, 0.f, -INFINITY, 0x7fffffff}, st{-INFINITY, 0.f, -INFINITY, 0x7fffffff};
+  float A = 0.f;
+#pragma unroll
+  for (int c = 0; c < BN / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld32(taddr + c * 32, r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const int col0 = n0 + c * 32 + v * 8;
+      float f[8], x[8], t[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]);
+      const bf16x8 packed = pack8(f);
+      if (col0 + 8 <= p.N) {
+        unpack8(packed, x);
+        unpack8(*reinterpret_cast<const bf16x8*>(&pre.v[c * 4 + v]), t);
+        online_update(sd, x, col0);
+        online_update_kl(st, A, t, x, col0);
+        if (row < p.M) st8(crow + c * 32 + v * 8, packed);
+      }
+    }
+  }
+  if (pre.valid) {
+    float4* out = reinterpret_cast<float4*>(p.rs.partial + ((int64_t)row * tiles_n + tile_n) * kStatWords);
+    out[0] = make_float4(sd.m, sd.z, sd.best, __int_as_float(sd.best_idx));
+    out[1] = make_float4(st.m, st.z, A, st.best);
+    out[2] = make_float4(__int_as_float(st.best_idx), 0.f, 0.f, 0.f);
   }
 }
 
@@ -418,13 +483,17 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int acc = local & 1;
       const int m0 = (tile % tiles_m) * P_TILE_M + (int)rank * P_HALF, n0 = (tile / tiles_m) * P_TILE_N;
       RowPrefetch pre;
-      prefetch_addend(p, m0 + quarter * 32 + lane, n0, pre);
+      const bool with_stats = p.rs.targets != nullptr;
+      if (with_stats) prefetch_targets(p, m0 + quarter * 32 + lane, n0, pre);
+      else prefetch_addend(p, m0 + quarter * 32 + lane, n0, pre);
       ok = mbar_wait(smem_addr(&bar_acc_full[acc]), (local >> 1) & 1, p.status, kTimeoutEpilogue);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       fence_after_sync();
-      if (pre.valid) store_accumulator_prefetched(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, m0 + quarter * 32 + lane, n0, pre);
-      else store_accumulator(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, m0 + quarter * 32 + lane, n0);
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+      if (with_stats) store_accumulator_with_stats(p, taddr, m0 + quarter * 32 + lane, n0, tile / tiles_m, tiles_n, pre);
+      else if (pre.valid) store_accumulator_prefetched(p, taddr, m0 + quarter * 32 + lane, n0, pre);
+      else store_accumulator(p, taddr, m0 + quarter * 32 + lane, n0);
       fence_before_sync();
       mbar_arrive_cluster(acc_empty_leader[acc]);
     }
@@ -451,9 +520,10 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // `status` is a device int the kernel writes a non-zero code to if a bounded wait ran out.
 // variant: 0 = choose (CTA pairs when M > 128 or an operand is MN-major), 1 = one CTA per 128x256 tile (K-major
 // only), 2 = CTA pairs with 64-wide K stages (K-major only), 3 = CTA pairs with 128-wide K stages.
-int launch_gemm_tcgen05(const void* a, const void* b, void* c, const void* residual, int M, int N, int K, int64_t lda,
-                        int64_t ldb, int64_t ldc, int64_t ldr, int epilogue, int a_mn, int b_mn, int* status, int variant,
-                        cudaStream_t stream) {
+static int launch_gemm_impl(const void* a, const void* b, void* c, const void* residual, int M, int N, int K, int64_t lda,
+                            int64_t ldb, int64_t ldc, int64_t ldr, int epilogue, int a_mn, int b_mn, int* status, int variant,
+                            const void* stats_targets, int64_t stats_ldt, int stats_t_rows, int stats_shift, float* stats_partial,
+                            cudaStream_t stream) {
   using namespace tc;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda & 7) || (ldb & 7) || (reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15)) return -1;
@@ -466,7 +536,13 @@ int launch_gemm_tcgen05(const void* a, const void* b, void* c, const void* resid
   if (rc) return rc;
   rc = b_mn ? make_map_bf16(&map_b, b, K, N, ldb, 2 * BK) : make_map_bf16(&map_b, b, N, K, ldb, pairs ? P_HALF : BN);
   if (rc) return rc;
-  Params p{(__nv_bfloat16*)c, (const __nv_bfloat16*)residual, M, N, K, ldc, ldr, epilogue, status};
+  Params p{(__nv_bfloat16*)c, (const __nv_bfloat16*)residual, M, N, K, ldc, ldr, epilogue, status, RowStatsOut{nullptr, 0, 0, 0, nullptr}};
+  if (stats_targets != nullptr) {
+    if (!pairs || a_mn || b_mn || epilogue != kStore || (N & 7) || (ldc & 7) || (stats_ldt & 7) || (reinterpret_cast<uintptr_t>(c) & 15) ||
+        (reinterpret_cast<uintptr_t>(stats_targets) & 15))
+      return -5;
+    p.rs = RowStatsOut{(const __nv_bfloat16*)stats_targets, stats_ldt, stats_t_rows, stats_shift, stats_partial};
+  }
   count_launch(1);
   if (pairs) {
     static bool configured2 = false;
@@ -502,9 +578,95 @@ int launch_gemm_tcgen05(const void* a, const void* b, void* c, const void* resid
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
+int launch_gemm_tcgen05(const void* a, const void* b, void* c, const void* residual, int M, int N, int K, int64_t lda,
+                        int64_t ldb, int64_t ldc, int64_t ldr, int epilogue, int a_mn, int b_mn, int* status, int variant,
+                        cudaStream_t stream) {
+  return launch_gemm_impl(a, b, c, residual, M, N, K, lda, ldb, ldc, ldr, epilogue, a_mn, b_mn, status, variant, nullptr, 0, 0, 0, nullptr, stream);
+}
+
 int launch_gemm_tn_tcgen05(const void* a, const void* b, void* c, const void* residual, int M, int N, int K, int64_t lda,
                            int64_t ldb, int64_t ldc, int64_t ldr, int epilogue, int* status, int variant, cudaStream_t stream) {
   return launch_gemm_tcgen05(a, b, c, residual, M, N, K, lda, ldb, ldc, ldr, epilogue, 0, 0, status, variant, stream);
+}
+
+// ---- lm_head product fused with the row loss (KL divergence / cross-entropy on the argmax) -----
+int lmhead_stat_words() { return tc::kStatWords; }
+int lmhead_tiles_n(int N) { return (N + tc::P_TILE_N - 1) / tc::P_TILE_N; }
+
+// logits[M,N] = x[M,K] * w[N,K]^T (stored, bf16) and, per (row, 256-column tile), the statistics of the logits
+// row and of targets[row + shift] over those columns into partial[M, tiles_n, kStatWords].
+int launch_lmhead_logits_stats(const void* x, const void* w, void* logits, const void* targets, int M, int N, int K, int64_t ldx,
+                               int64_t ldw, int64_t ldc, int64_t ldt, int t_rows, int shift, float* partial, int* status,
+                               cudaStream_t stream) {
+  return launch_gemm_impl(x, w, logits, nullptr, M, N, K, ldx, ldw, ldc, 0, tc::kStore, 0, 0, status, 3, targets, ldt, t_rows, shift, partial, stream);
+}
+
+// One warp per row: merge the row's tile records and write what the row-loss forward kernel writes
+// (loss, the five saved statistics, both argmaxes); rows with active[r] == 0 get the same sentinels.
+// op: 0 = KL(target || draft), 3 = cross-entropy against the target row's argmax.
+__global__ void __launch_bounds__(128)
+lmhead_combine_kernel(const float* __restrict__ partial, const __nv_bfloat16* __restrict__ logits, const uint8_t* __restrict__ active,
+                      float* __restrict__ loss, float* __restrict__ stats, int* __restrict__ argmax_d, int* __restrict__ argmax_t,
+                      int rows, int tiles_n, int64_t ld_logits, int op) {
+  const int r = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (r >= rows) return;
+  float* st = stats + r;
+  if (active && !active[r]) {
+    if (lane == 0) {
+      loss[r] = 0.f;
+      for (int k = 0; k < 5; ++k) st[(int64_t)k * rows] = 0.f;
+      if (argmax_d) argmax_d[r] = -1;
+      if (argmax_t) argmax_t[r] = -2;
+    }
+    return;
+  }
+  RowStats sd{-INFINITY, 0.f, -INFINITY, 0x7fffffff}, stt{-INFINITY, 0.f, -INFINITY, 0x7fffffff};
+  float A = 0.f;
+  for (int t = lane; t < tiles_n; t += 32) {
+    const float4* rec = reinterpret_cast<const float4*>(partial + ((int64_t)r * tiles_n + t) * tc::kStatWords);
+    const float4 a = rec[0], b = rec[1], c = rec[2];
+    merge_stats(sd, RowStats{a.x, a.y, a.z, __float_as_int(a.w)});
+    merge_stats_kl(stt, A, RowStats{b.x, b.y, b.w, __float_as_int(c.x)}, b.z);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    RowStats od{__shfl_xor_sync(0xffffffffu, sd.m, o), __shfl_xor_sync(0xffffffffu, sd.z, o), __shfl_xor_sync(0xffffffffu, sd.best, o),
+                __shfl_xor_sync(0xffffffffu, sd.best_idx, o)};
+    RowStats ot{__shfl_xor_sync(0xffffffffu, stt.m, o), __shfl_xor_sync(0xffffffffu, stt.z, o), __shfl_xor_sync(0xffffffffu, stt.best, o),
+                __shfl_xor_sync(0xffffffffu, stt.best_idx, o)};
+    const float oA = __shfl_xor_sync(0xffffffffu, A, o);
+    merge_stats(sd, od);
+    merge_stats_kl(stt, A, ot, oA);
+  }
+  if (lane == 0) {
+    const float lse_d = sd.m + __logf(sd.z), lse_t = stt.m + __logf(stt.z);
+    float L, extra;
+    if (op == 3) {
+      L = lse_d - __bfloat162float(logits[(int64_t)r * ld_logits + stt.best_idx]);
+      extra = (float)stt.best_idx;
+    } else {
+      L = A / stt.z + lse_d - lse_t;
+      extra = L;
+    }
+    loss[r] = L;
+    st[0] = sd.m;
+    st[(int64_t)rows] = sd.z;
+    st[(int64_t)2 * rows] = stt.m;
+    st[(int64_t)3 * rows] = stt.z;
+    st[(int64_t)4 * rows] = extra;
+    if (argmax_d) argmax_d[r] = sd.best_idx;
+    if (argmax_t) argmax_t[r] = stt.best_idx;
+  }
+}
+
+int launch_lmhead_combine(const float* partial, const void* logits, const uint8_t* active, float* loss, float* stats, int* argmax_d,
+                          int* argmax_t, int rows, int tiles_n, int64_t ld_logits, int op, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (op != 0 && op != 3) return -1;
+  count_launch(1);
+  lmhead_combine_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(partial, (const __nv_bfloat16*)logits, active, loss, stats, argmax_d, argmax_t, rows,
+                                                          tiles_n, ld_logits, op);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
 }  // namespace sb200

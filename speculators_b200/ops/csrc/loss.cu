@@ -18,85 +18,13 @@
 // steps of EAGLE-3 align their targets) and both argmaxes are by-products, so the
 // accuracy metrics need no extra pass over the vocabulary.
 #include "common.cuh"
+#include "loss_stats.cuh"
 
 namespace sb200 {
 
 enum LossOp : int { kOpKL = 0, kOpRKL = 1, kOpJSD = 2, kOpCE = 3, kOpTV = 4 };
 constexpr int kLossThreads = 512;
 constexpr int kNumStats = 5;  // m_d, z_d, m_t, z_t, per-op extra
-
-struct RowStats {
-  float m, z;
-  float best;
-  int best_idx;
-};
-
-__device__ __forceinline__ void online_update(RowStats& s, const float (&x)[8], int col0) {
-  float vmax = x[0];
-#pragma unroll
-  for (int j = 1; j < 8; ++j) vmax = fmaxf(vmax, x[j]);
-  const float m_new = fmaxf(s.m, vmax);
-  float add = 0.f;
-#pragma unroll
-  for (int j = 0; j < 8; ++j) add += __expf(x[j] - m_new);
-  s.z = s.z * __expf(s.m - m_new) + add;
-  s.m = m_new;
-  if (vmax > s.best) {
-    s.best = vmax;
-#pragma unroll
-    for (int j = 7; j >= 0; --j)
-      if (x[j] == vmax) s.best_idx = col0 + j;  // lowest index wins inside the vector
-  }
-}
-
-// KL(target || draft) in one pass: next to the target row's online softmax statistics keep
-// A = sum_v e^{t_v - m}(t_v - x_v) relative to the same running max m, so that
-// sum_v p_v (t_v - x_v) = A / Z needs no second read of the rows.
-__device__ __forceinline__ void online_update_kl(RowStats& s, float& A, const float (&t)[8], const float (&x)[8], int col0) {
-  float vmax = t[0];
-#pragma unroll
-  for (int j = 1; j < 8; ++j) vmax = fmaxf(vmax, t[j]);
-  const float m_new = fmaxf(s.m, vmax);
-  float add = 0.f, add_a = 0.f;
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const float e = __expf(t[j] - m_new);
-    add += e;
-    if (e > 0.f) add_a += e * (t[j] - x[j]);  // zero-probability targets contribute nothing
-  }
-  const float resc = __expf(s.m - m_new);
-  s.z = s.z * resc + add;
-  A = A * resc + add_a;
-  s.m = m_new;
-  if (vmax > s.best) {
-    s.best = vmax;
-#pragma unroll
-    for (int j = 7; j >= 0; --j)
-      if (t[j] == vmax) s.best_idx = col0 + j;
-  }
-}
-
-__device__ __forceinline__ void online_update_kl_scalar(RowStats& s, float& A, float t, float x, int col) {
-  const float m_new = fmaxf(s.m, t);
-  const float e = __expf(t - m_new), resc = __expf(s.m - m_new);
-  s.z = s.z * resc + e;
-  A = A * resc + (e > 0.f ? e * (t - x) : 0.f);
-  s.m = m_new;
-  if (t > s.best) {
-    s.best = t;
-    s.best_idx = col;
-  }
-}
-
-__device__ __forceinline__ void online_update_scalar(RowStats& s, float x, int col) {
-  const float m_new = fmaxf(s.m, x);
-  s.z = s.z * __expf(s.m - m_new) + __expf(x - m_new);
-  s.m = m_new;
-  if (x > s.best) {
-    s.best = x;
-    s.best_idx = col;
-  }
-}
 
 // Combine per-thread stats across the block.  Result valid in every thread.
 __device__ __forceinline__ void block_combine(RowStats& s, float* scratch, int* iscratch) {

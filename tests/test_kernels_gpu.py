@@ -198,3 +198,58 @@ def test_token_cross_entropy_fwd_bwd(T, V):
     assert (loss[~keep] == 0).all()
     _close(x.grad, xf.grad, atol=2e-3, rtol=5e-2)
     assert (x.grad[~keep] == 0).all()
+
+
+@pytest.mark.parametrize("op", ["kl_div", "ce"])
+@pytest.mark.parametrize("T,H,V,shift", [(300, 256, 1024, 0), (520, 192, 1000, 2), (2048, 512, 32000, 1), (257, 136, 264, 0)])
+def test_lm_head_fused_with_row_loss(op, T, H, V, shift):
+    """``lm_head_loss_raw`` (head GEMM whose epilogue reduces the tiles for the loss) against the
+    head GEMM followed by the row-loss kernel, and against the fp32 formula: row losses, both
+    argmaxes, the gradient of the hidden states; inactive rows and zero upstream rows included."""
+    torch.manual_seed(0)
+    hidden = (torch.randn(T, H, device=DEV) * 0.7).to(torch.bfloat16).requires_grad_()
+    weight = (torch.randn(V, H, device=DEV) * 0.2).to(torch.bfloat16)
+    targets = (torch.randn(T, V, device=DEV) * 3.0).to(torch.bfloat16)
+    rows = T - shift
+    active = torch.rand(rows, device=DEV) > 0.2
+    up = torch.rand(rows, device=DEV)
+    up[::3] = 0.0
+    fused = ops.lm_head_loss_raw(op, hidden, weight, targets, shift, rows, active)
+    assert fused is not None
+    loss, am_d, am_t = fused
+    (loss * up).sum().backward()
+    ops.check_gemm_status()
+    g_fused = hidden.grad.clone()
+    hidden.grad = None
+    logits = ops.linear(hidden, weight)
+    loss2, am_d2, am_t2 = ops.fused_row_loss_raw(op, logits, targets, shift, rows, active)
+    (loss2 * up).sum().backward()
+    _close(loss, loss2, atol=1e-4, rtol=1e-4)  # same bf16 logits, same statistics, another order of summation
+    assert torch.equal(am_t, am_t2)
+    lg = logits.detach().float()[:rows]
+    same = am_d == am_d2
+    picked = torch.gather(lg, 1, am_d.clamp_min(0).long().unsqueeze(1)).squeeze(1)
+    assert (same | (picked == lg.max(-1).values)).all()  # equal maxima may pick either index only on exact ties
+    _close(hidden.grad, g_fused, atol=1e-3, rtol=1e-2)
+    ref = _row_loss_ref(op, lg, targets.float()[shift: shift + rows])
+    ref = torch.where(active, ref, torch.zeros_like(ref))
+    _close(loss, ref, atol=3e-3, rtol=3e-3)
+    assert (loss[~active] == 0).all() and (am_d[~active] == -1).all() and (am_t[~active] == -2).all()
+
+
+def test_lm_head_fused_saturated_rows():
+    T, H, V = 256, 128, 512
+    hidden = torch.zeros(T, H, device=DEV, dtype=torch.bfloat16)
+    hidden[:, 0] = 1.0
+    weight = torch.zeros(V, H, device=DEV, dtype=torch.bfloat16)
+    weight[3, 0] = 30.0
+    weight[7, 0] = -30.0
+    targets = torch.zeros(T, V, device=DEV, dtype=torch.bfloat16)
+    targets[0::2, 3] = 30.0
+    targets[1::2, 9] = 30.0
+    for op in ("kl_div", "ce"):
+        loss, am_d, am_t = ops.lm_head_loss_raw(op, hidden, weight, targets, 0, T, None)
+        ref = _row_loss_ref(op, (hidden.float() @ weight.float().t()), targets.float())
+        assert torch.isfinite(loss).all()
+        _close(loss, ref, atol=2e-3, rtol=2e-3)
+        assert (am_d == 3).all() and (am_t[0::2] == 3).all() and (am_t[1::2] == 9).all()
