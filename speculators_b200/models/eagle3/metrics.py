@@ -70,7 +70,7 @@ def _compute_metrics_fused(logits, targets, loss_mask, prev_correct, ttt_step: i
     out = ops.ttt_step_tail(row_loss, pred, tgt, mask_u8.contiguous(), prev_flat, decay, _REDUCTION_EPS)
     loss = out[0] * weight if weight != 1.0 else out[0]
     stats = out.detach()
-    one = torch.ones((), device=logits.device)
+    one = torch.ones((), device=row_loss.device)
     metrics = {
         f"loss_{ttt_step}_sum": stats[0] * weight if weight != 1.0 else stats[0], f"loss_{ttt_step}_total": one,
         f"full_acc_{ttt_step}_sum": stats[1], f"full_acc_{ttt_step}_total": stats[2],

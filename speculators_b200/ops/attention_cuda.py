@@ -1,11 +1,12 @@
 """CUDA path of ``masked_attention``: autograd wrapper around the sm_100a kernels
-(head dims 64 and 128).  Other head dims use the dense formulation.
+(head dims 64, 128 and 256).  Other head dims use the dense formulation.
 
 Forward and backward at head dim 128 run on the tcgen05 tensor cores
 (``csrc/attention_tc.cu``, ``csrc/attention_bwd_tc.cu``: TMA tiles, TMEM accumulators,
 probability tiles handed to the next product through TMEM); ``FWD_IMPL`` / ``BWD_IMPL`` =
 ``"mma"`` (or ``SB200_ATTN_FWD=mma`` / ``SB200_ATTN_BWD=mma``) select the ``mma.sync``
-kernels of ``csrc/attention.cu``, which also serve head dim 64."""
+kernels of ``csrc/attention.cu``, which also serve head dims 64 and 256 (256: the gated
+full-attention heads of Qwen3-Next style MTP layers)."""
 
 from __future__ import annotations
 
@@ -16,7 +17,7 @@ import torch
 from speculators_b200.ops import _ext
 from speculators_b200.ops.attention import AttnSpec, masked_attention_reference
 
-_SUPPORTED_HEAD_DIMS = (64, 128)
+_SUPPORTED_HEAD_DIMS = (64, 128, 256)
 FWD_IMPL = os.environ.get("SB200_ATTN_FWD", "tc")
 BWD_IMPL = os.environ.get("SB200_ATTN_BWD", "tc")
 

@@ -819,6 +819,7 @@ int launch_attn_fwd(const AttnParams& p, int hd, cudaStream_t stream) {
   if (p.Tq <= 0) return 0;
   if (hd == 64) return launch_fwd_t<64>(p, stream);
   if (hd == 128) return launch_fwd_t<128>(p, stream);
+  if (hd == 256) return launch_fwd_t<256>(p, stream);
   return -1;
 }
 
@@ -827,6 +828,7 @@ int launch_attn_bwd(const AttnParams& p, int hd, int* tile_qmin, int* tile_qmax,
   if (p.Tq <= 0) return 0;
   if (hd == 64) return launch_bwd_t<64>(p, tile_qmin, tile_qmax, stream);
   if (hd == 128) return launch_bwd_t<128>(p, tile_qmin, tile_qmax, stream);
+  if (hd == 256) return launch_bwd_t<256>(p, tile_qmin, tile_qmax, stream);
   return -1;
 }
 

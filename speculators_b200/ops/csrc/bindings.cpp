@@ -615,7 +615,7 @@ sb200::AttnParams make_params(const Tensor& q, const Tensor& k, const Tensor& v,
   check_heads(q, "q", hd);
   check_heads(k, "k", hd);
   check_heads(v, "v", hd);
-  TORCH_CHECK(hd == 64 || hd == 128, "attention: head_dim must be 64 or 128");
+  TORCH_CHECK(hd == 64 || hd == 128 || hd == 256, "attention: head_dim must be 64, 128 or 256");
   TORCH_CHECK(k.size(0) == v.size(0) && k.size(1) == v.size(1) && q.size(1) % k.size(1) == 0);
   TORCH_CHECK(lo.scalar_type() == at::kInt && hi.scalar_type() == at::kInt && lo.is_contiguous() && hi.is_contiguous() &&
               lo.numel() == q.size(0) && hi.numel() == q.size(0), "lo/hi must be int32[Tq]");

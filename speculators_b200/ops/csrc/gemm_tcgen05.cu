@@ -150,7 +150,8 @@ __device__ __forceinline__ void store_accumulator(const Params& p, uint32_t tadd
 // time per tile is otherwise set by eight dependent load round trips per thread.
 struct RowPrefetch {
   uint4 v[BN / 8];
-  bool valid;
+  bool tile_ok;  // the same for every thread of the warp: selects the epilogue (its tcgen05.ld is warp-collective)
+  bool valid;    // this thread's row exists (its loads were issued, its stores may be)
 };
 
 __device__ __forceinline__ bool tile_reads_vectorised(const Params& p, int n0) {
@@ -160,7 +161,8 @@ __device__ __forceinline__ bool tile_reads_vectorised(const Params& p, int n0) {
 }
 
 __device__ __forceinline__ void prefetch_addend(const Params& p, int row, int n0, RowPrefetch& pre) {
-  pre.valid = tile_reads_vectorised(p, n0) && row < p.M;
+  pre.tile_ok = tile_reads_vectorised(p, n0);
+  pre.valid = pre.tile_ok && row < p.M;
   if (pre.valid) {
     const __nv_bfloat16* src = p.epilogue == kAccumulate ? p.c + (int64_t)row * p.ldc + n0 : p.residual + (int64_t)row * p.ldr + n0;
 #pragma unroll
@@ -168,7 +170,9 @@ __device__ __forceinline__ void prefetch_addend(const Params& p, int row, int n0
   }
 }
 
-// Same result as store_accumulator for a row whose addend is already in registers.
+// Same result as store_accumulator for a tile whose addend rows are already in registers.  Called
+// by whole warps (pre.tile_ok); a thread whose row does not exist takes part in the tensor-memory
+// loads and stores nothing.
 __device__ __forceinline__ void store_accumulator_prefetched(const Params& p, uint32_t taddr, int row, int n0, const RowPrefetch& pre) {
   __nv_bfloat16* crow = p.c + (int64_t)row * p.ldc + n0;
   const bool wide_ok = ((p.ldc & 15) == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 31) == 0);
@@ -186,6 +190,7 @@ __device__ __forceinline__ void store_accumulator_prefetched(const Params& p, ui
       for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]) + o[j];
       packed[v] = pack8(f);
     }
+    if (!pre.valid) continue;
     if (wide_ok) {
       st32(crow + c * 32, packed[0], packed[1]);
       st32(crow + c * 32 + 16, packed[2], packed[3]);
@@ -199,6 +204,7 @@ __device__ __forceinline__ void store_accumulator_prefetched(const Params& p, ui
 // ---- logits tile + row statistics ------------------------------------------------------------
 __device__ __forceinline__ void prefetch_targets(const Params& p, int row, int n0, RowPrefetch& pre) {
   const int trow = row + p.rs.shift;
+  pre.tile_ok = true;
   pre.valid = row < p.M && trow < p.rs.t_rows;
   const __nv_bfloat16* src = p.rs.targets + (int64_t)trow * p.rs.ldt + n0;
 #pragma unroll
@@ -336,7 +342,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       fence_after_sync();
-      if (pre.valid) store_accumulator_prefetched(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, m0 + quarter * 32 + lane, n0, pre);
+      if (pre.tile_ok) store_accumulator_prefetched(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, m0 + quarter * 32 + lane, n0, pre);
       else store_accumulator(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, m0 + quarter * 32 + lane, n0);
       fence_before_sync();
       mbar_arrive(smem_addr(&bar_acc_empty[acc]));
@@ -492,7 +498,7 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       fence_after_sync();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
       if (with_stats) store_accumulator_with_stats(p, taddr, m0 + quarter * 32 + lane, n0, tile / tiles_m, tiles_n, pre);
-      else if (pre.valid) store_accumulator_prefetched(p, taddr, m0 + quarter * 32 + lane, n0, pre);
+      else if (pre.tile_ok) store_accumulator_prefetched(p, taddr, m0 + quarter * 32 + lane, n0, pre);
       else store_accumulator(p, taddr, m0 + quarter * 32 + lane, n0);
       fence_before_sync();
       mbar_arrive_cluster(acc_empty_leader[acc]);

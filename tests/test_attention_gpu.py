@@ -51,7 +51,7 @@ def _run(T, nh, nkv, hd, step, window, pattern, fused_buffer=False, seed=0):
         assert float((a.grad.float() - b.grad).abs().max()) < tol, (name, float((a.grad.float() - b.grad).abs().max()), tol)
 
 
-@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("hd", [64, 128, 256])
 @pytest.mark.parametrize("T", [64, 127, 128, 129, 200, 257])
 def test_causal_single_document(T, hd):
     _run(T, 4, 2, hd, step=0, window=None, pattern="single")
@@ -61,6 +61,12 @@ def test_causal_single_document(T, hd):
 @pytest.mark.parametrize("window", [None, 48])
 def test_ttt_steps_multi_document_padding(step, window):
     _run(330, 8, 2, 128, step=step, window=window, pattern="multi_pad")
+
+
+@pytest.mark.parametrize("step,window,pattern", [(0, None, "multi_pad"), (1, 48, "multi_pad"), (2, None, "single")])
+def test_head_dim_256_gqa_documents_and_extra_keys(step, window, pattern):
+    """The gated full-attention heads of Qwen3-Next style MTP layers: 16 query heads on 2 KV heads of 256."""
+    _run(330, 16, 2, 256, step=step, window=window, pattern=pattern)
 
 
 def test_views_into_fused_projection_buffer():
