@@ -113,7 +113,17 @@ def expert_forward(x: torch.Tensor, expert_ids: torch.Tensor, gate_up: torch.Ten
 
 
 def _grouped_expert_forward(x_sorted: torch.Tensor, counts: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor) -> torch.Tensor:
-    """Rows already sorted by local expert; ``counts[e]`` rows belong to expert ``e``."""
+    """Rows already sorted by local expert; ``counts[e]`` rows belong to expert ``e``.  bf16 CUDA
+    rows with kernel-friendly widths run as grouped launches of the package's tcgen05 GEMM over a
+    128-row padded expert order (tile schedule driven by the device-side counts: no host read,
+    fixed shapes); ``SB200_MOE_GEMM=library`` or other shapes use the library / the dense loop."""
+    if (x_sorted.is_cuda and x_sorted.dtype == torch.bfloat16 and os.environ.get("SB200_MOE_GEMM", "tcgen05") != "library"
+            and gate_up.shape[1] % 256 == 0 and gate_up.shape[2] % 256 == 0 and down.shape[2] % 256 == 0 and x_sorted.shape[1] % 8 == 0):
+        plan = ops.GroupPlan(counts, x_sorted.shape[0])
+        x_pad = plan.pad(x_sorted)
+        if ops.grouped_linear_ok(x_pad, gate_up):
+            act = ops.swiglu(ops.grouped_linear(x_pad, gate_up, plan))
+            return plan.unpad(ops.grouped_linear(act, down, plan))
     grouped = getattr(torch, "_grouped_mm", None)
     if x_sorted.is_cuda and grouped is not None and x_sorted.dtype == torch.bfloat16:
         offs = counts.cumsum(0).to(torch.int32)

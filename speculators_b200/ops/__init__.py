@@ -29,6 +29,9 @@ __all__ = [
     "fused_row_loss",
     "check_gemm_status",
     "gemm_status",
+    "GroupPlan",
+    "grouped_linear",
+    "grouped_linear_ok",
     "linear",
     "lm_head_loss_raw",
     "masked_attention",
@@ -156,6 +159,67 @@ def matmul_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None,
     if out is None:
         return a.t() @ b
     return out.addmm_(a.t(), b) if accumulate else torch.mm(a.t(), b, out=out)
+
+
+# --------------------------------------------------------------------------- grouped (expert) linears
+class GroupPlan:
+    """Padded row order of a grouped product, all on the device: expert ``e`` owns the rows
+    ``seg[e] .. seg[e] + counts[e]`` of a ``[capacity, .]`` buffer, ``seg[e]`` a multiple of 128,
+    the rows up to ``seg[e + 1]`` are zero.  ``dest[i]`` is the padded row of the ``i``-th row of
+    the expert-sorted order.  Built without reading anything back to the host."""
+
+    def __init__(self, counts: torch.Tensor, num_rows: int):
+        counts32 = counts.to(torch.int32).contiguous()
+        E = counts32.numel()
+        self.seg, self.mtile_start = native().moe_group_plan(counts32)
+        self.capacity = (num_rows + 127 * E + 127) // 128 * 128  # worst case: every expert's tail padded by 127 rows
+        start = torch.cumsum(counts32, 0) - counts32  # unpadded offsets
+        expert_of = torch.repeat_interleave(torch.arange(E, device=counts.device), counts32.long(), output_size=num_rows)
+        self.dest = (torch.arange(num_rows, device=counts.device) - start[expert_of] + self.seg[expert_of]).long()
+
+    def pad(self, x_sorted: torch.Tensor) -> torch.Tensor:
+        out = x_sorted.new_zeros((self.capacity, x_sorted.shape[1]))
+        return out.index_copy(0, self.dest, x_sorted)
+
+    def unpad(self, y_padded: torch.Tensor) -> torch.Tensor:
+        return y_padded.index_select(0, self.dest)
+
+
+class _GroupedLinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x_pad, weight, seg, mts):
+        out = torch.empty((x_pad.shape[0], weight.shape[1]), dtype=x_pad.dtype, device=x_pad.device)
+        native().gemm_grouped_rows(x_pad, weight, out, False, seg, mts, gemm_status(x_pad.device))
+        ctx.save_for_backward(x_pad, weight, seg, mts)
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        x_pad, weight, seg, mts = ctx.saved_tensors
+        dy = dy if (dy.stride(-1) == 1 and dy.stride(0) % 8 == 0 and dy.data_ptr() % 16 == 0) else dy.contiguous()
+        status = gemm_status(dy.device)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty_like(x_pad)
+            native().gemm_grouped_rows(dy, weight, dx, True, seg, mts, status)
+        if ctx.needs_input_grad[1]:
+            dw = torch.empty_like(weight)
+            native().gemm_grouped_wgrad(dy, x_pad, dw, False, seg, mts, status)
+        return dx, dw, None, None
+
+
+def grouped_linear_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether ``grouped_linear`` can run on the tcgen05 kernel for these operands."""
+    return (_own_gemm_enabled() and _gemm_operand_ok(x) and weight.is_cuda and weight.dtype == torch.bfloat16 and weight.dim() == 3
+            and weight.is_contiguous() and weight.shape[1] % 256 == 0 and weight.shape[2] % 256 == 0 and x.shape[0] % 128 == 0)
+
+
+def grouped_linear(x_pad: torch.Tensor, weight: torch.Tensor, plan: GroupPlan) -> torch.Tensor:
+    """``y[r] = weight[e(r)] @ x_pad[r]`` for rows in the padded expert order of ``plan``
+    (``weight``: ``[E, out, in]``).  Forward, input gradient and per-expert weight gradient are
+    grouped launches of the tcgen05 GEMM whose tile schedule reads the experts' row counts from
+    device memory, so the call has fixed shapes and no host synchronisation."""
+    return _GroupedLinearFn.apply(x_pad, weight, plan.seg, plan.mtile_start)
 
 
 class _LinearFn(torch.autograd.Function):

@@ -34,6 +34,9 @@ int launch_gemm_tn_tcgen05(const void*, const void*, void*, const void*, int, in
                            int*, int, cudaStream_t);
 int launch_gemm_tcgen05(const void*, const void*, void*, const void*, int, int, int, int64_t, int64_t, int64_t, int64_t, int, int, int,
                         int*, int, cudaStream_t);
+void launch_moe_group_plan(const int*, int, int*, int*, cudaStream_t);
+int launch_gemm_grouped(const void*, const void*, void*, int, int, int, int64_t, int64_t, int64_t, int, int, int, const int*, const int*, int, int*,
+                        cudaStream_t);
 int lmhead_stat_words();
 int lmhead_tiles_n(int);
 int launch_lmhead_logits_stats(const void*, const void*, void*, const void*, int, int, int, int64_t, int64_t, int64_t, int64_t, int, int, float*,
@@ -193,6 +196,52 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> loss_fwd(int64_t op, const Tensor& lo
                                         (int)shift, cur_stream());
   TORCH_CHECK(rc == 0, "loss_fwd: unknown op ", op);
   return {loss, stats, am_d, am_t};
+}
+
+// ---- grouped (mixture-of-experts) products ----------------------------------------------------
+// counts int32[E] (device) -> (seg int32[E + 1], mtile_start int32[E + 1]): 128-row aligned segment offsets of the
+// padded row order and the prefix sum of 256-row tiles per expert.  Nothing is read back to the host.
+std::tuple<Tensor, Tensor> moe_group_plan(const Tensor& counts) {
+  TORCH_CHECK(counts.is_cuda() && counts.scalar_type() == at::kInt && counts.is_contiguous() && counts.dim() == 1);
+  c10::cuda::CUDAGuard guard(counts.device());
+  const int64_t E = counts.numel();
+  Tensor seg = at::empty({E + 1}, counts.options());
+  Tensor mts = at::empty({E + 1}, counts.options());
+  sb200::launch_moe_group_plan(counts.data_ptr<int>(), (int)E, seg.data_ptr<int>(), mts.data_ptr<int>(), cur_stream());
+  return {seg, mts};
+}
+
+// out[R, N] = x[R, K] . w_e^T for the rows of expert e (w: [E, N, K]); with `transposed` the weight is
+// [E, K, N] read in place (input gradient: out[R, N] = x[R, K] . w_e).  Rows follow the padded order of moe_group_plan.
+void gemm_grouped_rows(const Tensor& x, const Tensor& w, Tensor out, bool transposed, const Tensor& seg, const Tensor& mts, Tensor status) {
+  check_rows(x, "x");
+  check_rows(out, "out");
+  TORCH_CHECK(w.is_cuda() && w.scalar_type() == at::kBFloat16 && w.dim() == 3 && w.is_contiguous(), "w must be a contiguous bf16 [E, ., .] stack");
+  const int64_t E = w.size(0), R = x.size(0), K = x.size(1);
+  const int64_t N = transposed ? w.size(2) : w.size(1);
+  TORCH_CHECK((transposed ? w.size(1) : w.size(2)) == K && out.size(0) == R && out.size(1) == N, "gemm_grouped_rows: shape mismatch");
+  TORCH_CHECK(K % 128 == 0 && N % 256 == 0 && R % 128 == 0, "gemm_grouped_rows: K % 128, N % 256 and rows % 128 must be 0");
+  TORCH_CHECK(seg.is_cuda() && seg.scalar_type() == at::kInt && seg.numel() == E + 1 && mts.scalar_type() == at::kInt && mts.numel() == E + 1);
+  c10::cuda::CUDAGuard guard(x.device());
+  const int rc = sb200::launch_gemm_grouped(x.data_ptr(), w.data_ptr(), out.data_ptr(), (int)R, (int)N, (int)K, x.stride(0), w.stride(1),
+                                            out.stride(0), 0, 1, transposed ? 1 : 0, seg.data_ptr<int>(), mts.data_ptr<int>(), (int)E,
+                                            status.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(rc == 0, "gemm_grouped_rows launch failed (", rc, ")");
+}
+
+// dw[e] (=, +=) dy[seg_e, :]^T . x[seg_e, :]  (dw: [E, M, N], dy: [R, M], x: [R, N]); an expert without rows gets zeros (store) / is left alone (accumulate).
+void gemm_grouped_wgrad(const Tensor& dy, const Tensor& x, Tensor dw, bool accumulate, const Tensor& seg, const Tensor& mts, Tensor status) {
+  check_rows(dy, "dy");
+  check_rows(x, "x");
+  TORCH_CHECK(dw.is_cuda() && dw.scalar_type() == at::kBFloat16 && dw.dim() == 3 && dw.is_contiguous());
+  const int64_t E = dw.size(0), M = dw.size(1), N = dw.size(2), R = dy.size(0);
+  TORCH_CHECK(dy.size(1) == M && x.size(1) == N && x.size(0) == R && R % 128 == 0, "gemm_grouped_wgrad: shape mismatch");
+  TORCH_CHECK(seg.is_cuda() && seg.scalar_type() == at::kInt && seg.numel() == E + 1);
+  c10::cuda::CUDAGuard guard(x.device());
+  const int rc = sb200::launch_gemm_grouped(dy.data_ptr(), x.data_ptr(), dw.data_ptr(), (int)M, (int)N, (int)R, dy.stride(0), x.stride(0), N,
+                                            accumulate ? 1 : 0, 2, 1, seg.data_ptr<int>(), mts.data_ptr<int>(), (int)E, status.data_ptr<int>(),
+                                            cur_stream());
+  TORCH_CHECK(rc == 0, "gemm_grouped_wgrad launch failed (", rc, ")");
 }
 
 // lm_head product fused with the row loss: logits = x @ w^T on the tcgen05 kernel whose epilogue also
@@ -779,6 +828,9 @@ TORCH_LIBRARY(sb200, m) {
   m.def("gemm_tn", &gemm_tn);
   m.def("gemm", &gemm);
   m.def("lmhead_loss_fwd", &lmhead_loss_fwd);
+  m.def("moe_group_plan", &moe_group_plan);
+  m.def("gemm_grouped_rows", &gemm_grouped_rows);
+  m.def("gemm_grouped_wgrad", &gemm_grouped_wgrad);
   m.def("gemm_tn_variant", &gemm_tn_variant);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_fwd_tc", &attn_fwd_tc);

@@ -69,6 +69,23 @@ struct RowStatsOut {
   float* partial;
 };
 
+// Grouped products (mixture-of-experts): rows sorted by expert, expert e owning the rows
+// seg[e] .. seg[e+1] of the activation matrices, every seg[e] a multiple of 128 (the rows
+// between an expert's last token and the next boundary are zero).  All sizes that depend on the
+// routing are read from device memory, so the launch is fixed-shape and can be captured.
+//   kGroupRows  C[r, :] = A[r, :] . B_e^T for r in expert e (forward and input gradient): tiles are
+//               enumerated per expert through tile_start (prefix sum of ceil(rows_e / 256) * tiles_n);
+//               B is the stack of the experts' matrices ([E * N, K] K-major or [E * K, N] MN-major).
+//   kGroupK     C_e (+)= A[seg_e, :]^T . B[seg_e, :] (weight gradient): the contraction runs over
+//               expert e's rows, C is the stack [E * M, N]; an expert without rows yields zeros.
+enum GroupMode : int { kGroupNone = 0, kGroupRows = 1, kGroupK = 2 };
+struct Grouping {
+  int mode;
+  int num_groups;
+  const int* seg;         // [num_groups + 1] padded row offsets
+  const int* tile_start;  // [num_groups + 1] prefix sum of ceil(rows_e / 256) (kGroupRows); tiles of expert e: that x tiles_n
+};
+
 struct Params {
   __nv_bfloat16* c;
   const __nv_bfloat16* residual;
@@ -77,7 +94,52 @@ struct Params {
   int epilogue;
   int* status;
   RowStatsOut rs;
+  Grouping grp;
 };
+
+// Where one 256x256 tile (or this CTA's half of it) sits in the operands.
+struct TileInfo {
+  int a_m, a_k0;   // A: first MN index of this CTA's 128, first contraction index
+  int b_n, b_k0;   // B: the same
+  int num_kb;      // 128-wide contraction steps
+  int c_row0;      // C row of this CTA's first accumulator row
+  int row_end;     // C rows >= row_end do not exist (for this tile)
+  int n0;          // first C column
+  int tile_n;      // column-tile index (row statistics)
+};
+
+template <bool B_MN>
+__device__ __forceinline__ TileInfo decode_tile(const Params& p, int tile, int tiles_m, int tiles_n, int num_kb, int rank) {
+  TileInfo t;
+  if (p.grp.mode == kGroupNone) {
+    const int m0 = (tile % tiles_m) * 256 + rank * 128;
+    t.tile_n = tile / tiles_m;
+    t.n0 = t.tile_n * 256;
+    t.a_m = m0; t.a_k0 = 0; t.b_n = t.n0 + rank * 128; t.b_k0 = 0; t.num_kb = num_kb; t.c_row0 = m0; t.row_end = p.M;
+  } else if (p.grp.mode == kGroupRows) {
+    int lo = 0, hi = p.grp.num_groups - 1;  // last e with tile_start[e] <= tile
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (p.grp.tile_start[mid] * tiles_n <= tile) lo = mid; else hi = mid - 1;
+    }
+    const int e = lo, s0 = p.grp.seg[e], s1 = p.grp.seg[e + 1];
+    const int tm = (s1 - s0 + 255) >> 8, local = tile - p.grp.tile_start[e] * tiles_n;
+    const int m0 = s0 + (local % tm) * 256 + rank * 128;
+    t.tile_n = local / tm;
+    t.n0 = t.tile_n * 256;
+    t.a_m = m0; t.a_k0 = 0; t.num_kb = num_kb; t.c_row0 = m0; t.row_end = s1;
+    t.b_n = (B_MN ? 0 : e * p.N) + t.n0 + rank * 128;
+    t.b_k0 = B_MN ? e * p.K : 0;
+  } else {
+    const int per = tiles_m * tiles_n, e = tile / per, local = tile % per;
+    const int m0 = (local % tiles_m) * 256 + rank * 128, s0 = p.grp.seg[e];
+    t.tile_n = local / tiles_m;
+    t.n0 = t.tile_n * 256;
+    t.a_m = m0; t.a_k0 = s0; t.b_n = t.n0 + rank * 128; t.b_k0 = s0; t.num_kb = (p.grp.seg[e + 1] - s0) >> 7;
+    t.c_row0 = e * p.M + m0; t.row_end = e * p.M + p.M;
+  }
+  return t;
+}
 
 // 32-byte store (one full sector) of sixteen bf16; ptr must be 32-byte aligned.
 __device__ __forceinline__ void st32(__nv_bfloat16* ptr, const bf16x8& a, const bf16x8& b) {
@@ -89,7 +151,7 @@ __device__ __forceinline__ void st32(__nv_bfloat16* ptr, const bf16x8& a, const 
 
 // Epilogue of one thread: TMEM lane `taddr` (its 256 fp32 columns) -> row `row`, columns
 // n0 .. n0+255 of C, with the configured epilogue.
-__device__ __forceinline__ void store_accumulator(const Params& p, uint32_t taddr, int row, int n0) {
+__device__ __forceinline__ void store_accumulator(const Params& p, uint32_t taddr, int row, int n0, int row_end, bool zero) {
   __nv_bfloat16* crow = p.c + (int64_t)row * p.ldc + n0;
   const __nv_bfloat16* rrow = p.residual ? p.residual + (int64_t)row * p.ldr + n0 : nullptr;
   const bool vec_ok = ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0) &&
@@ -100,7 +162,11 @@ __device__ __forceinline__ void store_accumulator(const Params& p, uint32_t tadd
     uint32_t r[32];
     tmem_ld32(taddr + c * 32, r);
     tmem_ld_wait();
-    if (row < p.M) {
+    if (zero) {  // no contraction step ran (an expert without rows): the accumulator holds nothing
+#pragma unroll
+      for (int j = 0; j < 32; ++j) r[j] = 0u;
+    }
+    if (row < row_end) {
       const int col0 = n0 + c * 32;
       if (vec_ok && col0 + 32 <= p.N) {
         bf16x8 packed[4];
@@ -160,9 +226,9 @@ __device__ __forceinline__ bool tile_reads_vectorised(const Params& p, int n0) {
   return true;
 }
 
-__device__ __forceinline__ void prefetch_addend(const Params& p, int row, int n0, RowPrefetch& pre) {
+__device__ __forceinline__ void prefetch_addend(const Params& p, int row, int n0, int row_end, RowPrefetch& pre) {
   pre.tile_ok = tile_reads_vectorised(p, n0);
-  pre.valid = pre.tile_ok && row < p.M;
+  pre.valid = pre.tile_ok && row < row_end;
   if (pre.valid) {
     const __nv_bfloat16* src = p.epilogue == kAccumulate ? p.c + (int64_t)row * p.ldc + n0 : p.residual + (int64_t)row * p.ldr + n0;
 #pragma unroll
@@ -173,7 +239,7 @@ __device__ __forceinline__ void prefetch_addend(const Params& p, int row, int n0
 // Same result as store_accumulator for a tile whose addend rows are already in registers.  Called
 // by whole warps (pre.tile_ok); a thread whose row does not exist takes part in the tensor-memory
 // loads and stores nothing.
-__device__ __forceinline__ void store_accumulator_prefetched(const Params& p, uint32_t taddr, int row, int n0, const RowPrefetch& pre) {
+__device__ __forceinline__ void store_accumulator_prefetched(const Params& p, uint32_t taddr, int row, int n0, const RowPrefetch& pre, bool zero) {
   __nv_bfloat16* crow = p.c + (int64_t)row * p.ldc + n0;
   const bool wide_ok = ((p.ldc & 15) == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 31) == 0);
 #pragma unroll
@@ -187,7 +253,7 @@ __device__ __forceinline__ void store_accumulator_prefetched(const Params& p, ui
       float f[8], o[8];
       unpack8(*reinterpret_cast<const bf16x8*>(&pre.v[c * 4 + v]), o);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]) + o[j];
+      for (int j = 0; j < 8; ++j) f[j] = (zero ? 0.f : __uint_as_float(r[v * 8 + j])) + o[j];
       packed[v] = pack8(f);
     }
     if (!pre.valid) continue;
@@ -337,13 +403,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int acc = local & 1;
       const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
       RowPrefetch pre;
-      prefetch_addend(p, m0 + quarter * 32 + lane, n0, pre);
+      prefetch_addend(p, m0 + quarter * 32 + lane, n0, p.M, pre);
       ok = mbar_wait(smem_addr(&bar_acc_full[acc]), (local >> 1) & 1, p.status, kTimeoutEpilogue);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       fence_after_sync();
-      if (pre.tile_ok) store_accumulator_prefetched(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, m0 + quarter * 32 + lane, n0, pre);
-      else store_accumulator(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, m0 + quarter * 32 + lane, n0);
+      if (pre.tile_ok) store_accumulator_prefetched(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, m0 + quarter * 32 + lane, n0, pre, false);
+      else store_accumulator(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, m0 + quarter * 32 + lane, n0, p.M, false);
       fence_before_sync();
       mbar_arrive(smem_addr(&bar_acc_empty[acc]));
     }
@@ -387,7 +453,9 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const bool leader = rank == 0;
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
   const int tiles_m = (p.M + P_TILE_M - 1) / P_TILE_M, tiles_n = (p.N + P_TILE_N - 1) / P_TILE_N;
-  const int num_tiles = tiles_m * tiles_n;
+  const int num_tiles = p.grp.mode == kGroupRows ? p.grp.tile_start[p.grp.num_groups] * tiles_n
+                        : p.grp.mode == kGroupK  ? p.grp.num_groups * tiles_m * tiles_n
+                                                 : tiles_m * tiles_n;
   const int num_kb = (p.K + STAGE_K - 1) / STAGE_K;
 
   if (threadIdx.x == 0) {
@@ -416,9 +484,8 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-        const int m0 = (tile % tiles_m) * P_TILE_M + (int)rank * P_HALF;
-        const int nb0 = (tile / tiles_m) * P_TILE_N + (int)rank * P_HALF;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const TileInfo ti = decode_tile<B_MN>(p, tile, tiles_m, tiles_n, num_kb, (int)rank);
+        for (int kb = 0; kb < ti.num_kb; ++kb) {
           if (!(ok = mbar_wait(smem_addr(&bar_empty[stage]), phase ^ 1, p.status, kTimeoutProducer))) break;
           const uint32_t full_local = smem_addr(&bar_full[stage]);
           if (leader) mbar_expect_tx(full_local, 2 * P_STAGE_BYTES);
@@ -429,10 +496,10 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           // 64 MN-columns (MN-elements 64u .. 64u+63 of this CTA's 128).  Either way 16 KB at the same place.
 #pragma unroll
           for (int u = 0; u < KSUB; ++u) {
-            if (A_MN) tma_load_2d_pair(sa + u * P_SUB_BYTES, &map_a, full_leader, m0 + u * 64, kb * STAGE_K);
-            else tma_load_2d_pair(sa + u * P_SUB_BYTES, &map_a, full_leader, kb * STAGE_K + u * BK, m0);
-            if (B_MN) tma_load_2d_pair(sa + u * P_SUB_BYTES + P_A_BYTES, &map_b, full_leader, nb0 + u * 64, kb * STAGE_K);
-            else tma_load_2d_pair(sa + u * P_SUB_BYTES + P_A_BYTES, &map_b, full_leader, kb * STAGE_K + u * BK, nb0);
+            if (A_MN) tma_load_2d_pair(sa + u * P_SUB_BYTES, &map_a, full_leader, ti.a_m + u * 64, ti.a_k0 + kb * STAGE_K);
+            else tma_load_2d_pair(sa + u * P_SUB_BYTES, &map_a, full_leader, ti.a_k0 + kb * STAGE_K + u * BK, ti.a_m);
+            if (B_MN) tma_load_2d_pair(sa + u * P_SUB_BYTES + P_A_BYTES, &map_b, full_leader, ti.b_n + u * 64, ti.b_k0 + kb * STAGE_K);
+            else tma_load_2d_pair(sa + u * P_SUB_BYTES + P_A_BYTES, &map_b, full_leader, ti.b_k0 + kb * STAGE_K + u * BK, ti.b_n);
           }
           if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
         }
@@ -456,7 +523,8 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (!(ok = mbar_wait(smem_addr(&bar_acc_empty[acc]), ((local >> 1) & 1) ^ 1, p.status, kTimeoutMma))) break;
         fence_after_sync();
         const uint32_t tmem_d = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int tile_kb = decode_tile<B_MN>(p, tile, tiles_m, tiles_n, num_kb, 0).num_kb;
+        for (int kb = 0; kb < tile_kb; ++kb) {
           if (!(ok = mbar_wait(smem_addr(&bar_full[stage]), phase, p.status, kTimeoutMma))) break;
           fence_after_sync();
           const uint32_t sa = smem_addr(smem + stage * P_STAGE_BYTES);
@@ -487,19 +555,21 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     int local = 0;
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
       const int acc = local & 1;
-      const int m0 = (tile % tiles_m) * P_TILE_M + (int)rank * P_HALF, n0 = (tile / tiles_m) * P_TILE_N;
+      const TileInfo ti = decode_tile<B_MN>(p, tile, tiles_m, tiles_n, num_kb, (int)rank);
+      const int row = ti.c_row0 + quarter * 32 + lane, n0 = ti.n0;
+      const bool zero = ti.num_kb == 0;
       RowPrefetch pre;
       const bool with_stats = p.rs.targets != nullptr;
-      if (with_stats) prefetch_targets(p, m0 + quarter * 32 + lane, n0, pre);
-      else prefetch_addend(p, m0 + quarter * 32 + lane, n0, pre);
+      if (with_stats) prefetch_targets(p, row, n0, pre);
+      else prefetch_addend(p, row, n0, ti.row_end, pre);
       ok = mbar_wait(smem_addr(&bar_acc_full[acc]), (local >> 1) & 1, p.status, kTimeoutEpilogue);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       fence_after_sync();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
-      if (with_stats) store_accumulator_with_stats(p, taddr, m0 + quarter * 32 + lane, n0, tile / tiles_m, tiles_n, pre);
-      else if (pre.tile_ok) store_accumulator_prefetched(p, taddr, m0 + quarter * 32 + lane, n0, pre);
-      else store_accumulator(p, taddr, m0 + quarter * 32 + lane, n0);
+      if (with_stats) store_accumulator_with_stats(p, taddr, row, n0, ti.tile_n, tiles_n, pre);
+      else if (pre.tile_ok) store_accumulator_prefetched(p, taddr, row, n0, pre, zero);
+      else store_accumulator(p, taddr, row, n0, ti.row_end, zero);
       fence_before_sync();
       mbar_arrive_cluster(acc_empty_leader[acc]);
     }
@@ -529,7 +599,7 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 static int launch_gemm_impl(const void* a, const void* b, void* c, const void* residual, int M, int N, int K, int64_t lda,
                             int64_t ldb, int64_t ldc, int64_t ldr, int epilogue, int a_mn, int b_mn, int* status, int variant,
                             const void* stats_targets, int64_t stats_ldt, int stats_t_rows, int stats_shift, float* stats_partial,
-                            cudaStream_t stream) {
+                            const tc::Grouping* grp, cudaStream_t stream) {
   using namespace tc;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda & 7) || (ldb & 7) || (reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15)) return -1;
@@ -540,9 +610,18 @@ static int launch_gemm_impl(const void* a, const void* b, void* c, const void* r
   CUtensorMap map_a, map_b;
   int rc = a_mn ? make_map_bf16(&map_a, a, K, M, lda, 2 * BK) : make_map_bf16(&map_a, a, M, K, lda, BM);
   if (rc) return rc;
-  rc = b_mn ? make_map_bf16(&map_b, b, K, N, ldb, 2 * BK) : make_map_bf16(&map_b, b, N, K, ldb, pairs ? P_HALF : BN);
+  // grouped by rows: B is the stack of the experts' matrices
+  const int64_t b_stack = (grp != nullptr && grp->mode == kGroupRows) ? grp->num_groups : 1;
+  rc = b_mn ? make_map_bf16(&map_b, b, b_stack * K, N, ldb, 2 * BK) : make_map_bf16(&map_b, b, b_stack * N, K, ldb, pairs ? P_HALF : BN);
   if (rc) return rc;
-  Params p{(__nv_bfloat16*)c, (const __nv_bfloat16*)residual, M, N, K, ldc, ldr, epilogue, status, RowStatsOut{nullptr, 0, 0, 0, nullptr}};
+  Params p{(__nv_bfloat16*)c, (const __nv_bfloat16*)residual, M, N, K, ldc, ldr, epilogue, status, RowStatsOut{nullptr, 0, 0, 0, nullptr},
+           Grouping{kGroupNone, 0, nullptr, nullptr}};
+  if (grp != nullptr) {
+    if (!pairs || variant != 3 || stats_targets != nullptr || residual != nullptr) return -6;
+    if (grp->mode == kGroupRows && (a_mn || (K & 127) || (N & 255))) return -6;  // experts' matrices must not share a box
+    if (grp->mode == kGroupK && !(a_mn && b_mn)) return -6;
+    p.grp = *grp;
+  }
   if (stats_targets != nullptr) {
     if (!pairs || a_mn || b_mn || epilogue != kStore || (N & 7) || (ldc & 7) || (stats_ldt & 7) || (reinterpret_cast<uintptr_t>(c) & 15) ||
         (reinterpret_cast<uintptr_t>(stats_targets) & 15))
@@ -562,8 +641,9 @@ static int launch_gemm_impl(const void* a, const void* b, void* c, const void* r
       if (!ok) return -2;
       configured2 = true;
     }
-    const int tiles = ((M + P_TILE_M - 1) / P_TILE_M) * ((N + P_TILE_N - 1) / P_TILE_N);
     const int max_pairs = kNumSM / 2;
+    // grouped: the number of tiles is known on the device only; every pair looks for work
+    const int tiles = grp != nullptr ? max_pairs : ((M + P_TILE_M - 1) / P_TILE_M) * ((N + P_TILE_N - 1) / P_TILE_N);
     const int grid = 2 * (tiles < max_pairs ? tiles : max_pairs);
     if (a_mn && b_mn) gemm_tn_2cta_kernel<2, true, true><<<grid, THREADS, smem2, stream>>>(map_a, map_b, p);
     else if (a_mn) gemm_tn_2cta_kernel<2, true, false><<<grid, THREADS, smem2, stream>>>(map_a, map_b, p);
@@ -587,12 +667,46 @@ static int launch_gemm_impl(const void* a, const void* b, void* c, const void* r
 int launch_gemm_tcgen05(const void* a, const void* b, void* c, const void* residual, int M, int N, int K, int64_t lda,
                         int64_t ldb, int64_t ldc, int64_t ldr, int epilogue, int a_mn, int b_mn, int* status, int variant,
                         cudaStream_t stream) {
-  return launch_gemm_impl(a, b, c, residual, M, N, K, lda, ldb, ldc, ldr, epilogue, a_mn, b_mn, status, variant, nullptr, 0, 0, 0, nullptr, stream);
+  return launch_gemm_impl(a, b, c, residual, M, N, K, lda, ldb, ldc, ldr, epilogue, a_mn, b_mn, status, variant, nullptr, 0, 0, 0, nullptr, nullptr, stream);
 }
 
 int launch_gemm_tn_tcgen05(const void* a, const void* b, void* c, const void* residual, int M, int N, int K, int64_t lda,
                            int64_t ldb, int64_t ldc, int64_t ldr, int epilogue, int* status, int variant, cudaStream_t stream) {
   return launch_gemm_tcgen05(a, b, c, residual, M, N, K, lda, ldb, ldc, ldr, epilogue, 0, 0, status, variant, stream);
+}
+
+// ---- grouped products for mixture-of-experts layers -----------------------------------------
+// counts[e] rows belong to expert e.  seg[e] = offset of its (128-row aligned) segment in the padded
+// row order, mtile_start[e] = prefix sum of ceil(segment rows / 256).  One block; E <= 4096.
+__global__ void moe_group_plan_kernel(const int* __restrict__ counts, int num_groups, int* __restrict__ seg, int* __restrict__ mtile_start) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  int off = 0, tiles = 0;
+  for (int e = 0; e < num_groups; ++e) {
+    seg[e] = off;
+    mtile_start[e] = tiles;
+    const int padded = (counts[e] + 127) & ~127;
+    off += padded;
+    tiles += (padded + 255) >> 8;
+  }
+  seg[num_groups] = off;
+  mtile_start[num_groups] = tiles;
+}
+
+void launch_moe_group_plan(const int* counts, int num_groups, int* seg, int* mtile_start, cudaStream_t stream) {
+  count_launch(1);
+  moe_group_plan_kernel<<<1, 32, 0, stream>>>(counts, num_groups, seg, mtile_start);
+}
+
+// mode 1 (rows grouped): c[R, N] = a[R, K] . b_e^T, b the stack [E, N, K] (b_mn 0) or, for the input
+//   gradient, c[R, N] = a[R, K] . b_e with b = [E, K, N] (b_mn 1).  R = rows of the padded order.
+// mode 2 (contraction grouped): c_e[M, N] (=, +=) a[seg_e, M]^T . b[seg_e, N], c the stack [E, M, N]; K = R.
+int launch_gemm_grouped(const void* a, const void* b, void* c, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int epilogue,
+                        int mode, int b_mn, const int* seg, const int* mtile_start, int num_groups, int* status, cudaStream_t stream) {
+  if (mode != tc::kGroupRows && mode != tc::kGroupK) return -6;
+  const tc::Grouping grp{mode, num_groups, seg, mtile_start};
+  const int a_mn = mode == tc::kGroupK ? 1 : 0;
+  return launch_gemm_impl(a, b, c, nullptr, M, N, K, lda, ldb, ldc, 0, epilogue, a_mn, mode == tc::kGroupK ? 1 : b_mn, status, 3, nullptr, 0, 0, 0,
+                          nullptr, &grp, stream);
 }
 
 // ---- lm_head product fused with the row loss (KL divergence / cross-entropy on the argmax) -----
@@ -604,7 +718,7 @@ int lmhead_tiles_n(int N) { return (N + tc::P_TILE_N - 1) / tc::P_TILE_N; }
 int launch_lmhead_logits_stats(const void* x, const void* w, void* logits, const void* targets, int M, int N, int K, int64_t ldx,
                                int64_t ldw, int64_t ldc, int64_t ldt, int t_rows, int shift, float* partial, int* status,
                                cudaStream_t stream) {
-  return launch_gemm_impl(x, w, logits, nullptr, M, N, K, ldx, ldw, ldc, 0, tc::kStore, 0, 0, status, 3, targets, ldt, t_rows, shift, partial, stream);
+  return launch_gemm_impl(x, w, logits, nullptr, M, N, K, ldx, ldw, ldc, 0, tc::kStore, 0, 0, status, 3, targets, ldt, t_rows, shift, partial, nullptr, stream);
 }
 
 // One warp per row: merge the row's tile records and write what the row-loss forward kernel writes
