@@ -208,6 +208,10 @@ def config_record(c: dict, world: int, regions: int) -> dict:
     }
 
 
+def parity_steps_compared(c: dict) -> int:
+    return PARITY_STEPS if c["algo"] == "eagle3" else 1
+
+
 def data_note(c: dict) -> str:
     hs = "hidden states from a plain-PyTorch forward of the random-init verifier" if c["verifier_forward"] else "hidden states drawn N(0, 1)"
     return f"synthetic (seeded uniform tokens; {hs}; seeded draft init; both arms read the same files)"
@@ -258,15 +262,18 @@ def spread(values: list[float]) -> dict:
     return {"median": statistics.median(values), "min": min(values), "max": max(values), "n": len(values)}
 
 
-def loss_parity(mine: list[float] | None, other: list[float] | None) -> dict:
+def loss_parity(mine: list[float] | None, other: list[float] | None, compared: int = PARITY_STEPS) -> dict:
     """Both arms start from the same draft weights and see the same batches; their losses over
-    the first steps must agree within ``PARITY_RTOL`` (bf16 compute on different kernels)."""
+    the first ``compared`` steps must agree within ``PARITY_RTOL`` (bf16 compute on different
+    kernels).  Algorithms that draw anchors / depths at random in every step (each arm from its
+    own generator) are compared on the first step only: from the second step on the two arms
+    train on different samples of the same batch."""
     if not mine or not other:
         return {"loss_parity": None, "loss_parity_note": "the other arm's record is not on this machine"}
-    n = min(len(mine), len(other))
+    n = min(len(mine), len(other), compared)
     gaps = [abs(a - b) / max(abs(b), 1e-6) for a, b in zip(mine[:n], other[:n])]
     return {"loss_parity": bool(max(gaps) <= PARITY_RTOL), "loss_parity_max_rel_gap": max(gaps), "loss_parity_rtol": PARITY_RTOL,
-            "loss_trace_other_arm": other[:n]}
+            "loss_parity_steps_compared": n, "loss_trace_other_arm": other[:len(mine)]}
 
 
 # ----------------------------------------------------------------------------- this framework
@@ -401,7 +408,7 @@ def run_ours(args):
             "loss_trace": loss_trace, "last_loss": last.get("loss"),
             "gpu_launches": launches,
         }
-        record.update(loss_parity(loss_trace, (bench_inputs.read_result(tag, "reference", world) or {}).get("loss_trace")))
+        record.update(loss_parity(loss_trace, (bench_inputs.read_result(tag, "reference", world) or {}).get("loss_trace"), parity_steps_compared(c)))
         bench_inputs.write_result(tag, "ours", world, {"loss_trace": loss_trace})
         print(json.dumps(record))
     maybe_destroy_distributed()
@@ -666,7 +673,7 @@ def run_reference(args):
             "loss_trace": loss_trace, "last_loss": capture.losses[-1] if capture.losses else None,
             "gpu_launches": 0,
         }
-        record.update(loss_parity(loss_trace, (bench_inputs.read_result(tag, "ours", world) or {}).get("loss_trace")))
+        record.update(loss_parity(loss_trace, (bench_inputs.read_result(tag, "ours", world) or {}).get("loss_trace"), parity_steps_compared(c)))
         bench_inputs.write_result(tag, "reference", world, {"loss_trace": loss_trace})
         print(json.dumps(record))
     maybe_destroy_distributed()

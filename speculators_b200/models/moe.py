@@ -154,6 +154,20 @@ class SparseMoeBlock(nn.Module):
         self.shared_expert = _SharedExpert(H, shared) if shared > 0 else None
         self.shared_expert_gate = Linear(H, 1, bias=False) if shared > 0 else None
         self._comm = None  # peer-memory exchange buffers, created at the first expert-parallel CUDA call
+        if self.ep_size > 1:
+            # this rank's experts differ from every other rank's: the training engine keeps them out of
+            # its gradient collectives, and checkpoints hold the stack of all ranks' experts
+            for p in self.experts.parameters():
+                p._sb200_local = True
+            self._register_load_state_dict_pre_hook(self._take_own_experts)
+
+    def _take_own_experts(self, state_dict, prefix, *args) -> None:  # noqa: ANN001, ANN002
+        """Loading a checkpoint that holds all experts: keep the slice this rank owns."""
+        for name in ("gate_up_proj", "down_proj"):
+            key = f"{prefix}experts.{name}"
+            full = state_dict.get(key)
+            if full is not None and full.shape[0] == self.num_experts and self.num_local != self.num_experts:
+                state_dict[key] = full[self.ep_rank * self.num_local : (self.ep_rank + 1) * self.num_local]
 
     def route(self, x: torch.Tensor):
         probs = torch.softmax(self.gate(x).float(), dim=-1)
@@ -276,6 +290,9 @@ class MoEDecoderLayer(nn.Module):
 
 
 class MoEMTPLayer(_MTPMixin, MoEDecoderLayer):
+    """``ep_group``: process group over which the experts are split (expert parallelism); ``None``
+    keeps all experts on every rank."""
+
     def __init__(self, config: TransformerLayerConfig, layer_idx: int = 0, ep_group=None):
         MoEDecoderLayer.__init__(self, config, layer_idx, ep_group=ep_group)
         self._setup_mtp_modules(config, norm_cls=ZeroCenteredRMSNorm)

@@ -29,6 +29,18 @@ from speculators_b200.proposals.greedy import GreedyTokenProposalConfig
 __all__ = ["MTPDraftModel", "compute_step_weights"]
 
 
+def _expert_parallel_group(expert_parallel: bool | None):
+    import os
+
+    import torch.distributed as dist
+
+    if expert_parallel is None:
+        expert_parallel = os.environ.get("SB200_EXPERT_PARALLEL", "0") == "1"
+    if not expert_parallel or not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return None
+    return dist.group.WORLD
+
+
 def compute_step_weights(beta: float = 0.6, num_steps: int = 3) -> list[float]:
     """``beta**k`` normalised to sum to one (FastMTP, arXiv:2509.18362, eq. 2)."""
     raw = [beta**k for k in range(num_steps)]
@@ -43,13 +55,17 @@ class MTPDraftModel(DraftVocabMixin, SpeculatorModel):
     _keys_to_ignore_on_load_missing: ClassVar[list[str]] = ["embed_tokens.weight", "lm_head.weight", "verifier_lm_head.weight", "t2d", "d2t"]
     cuda_graph_safe: ClassVar[bool] = True
 
-    def __init__(self, config: MTPSpeculatorConfig):
+    def __init__(self, config: MTPSpeculatorConfig, ep_group=None):
+        """``ep_group`` (mixture-of-experts heads only): split the experts over this process group
+        instead of keeping all of them on every rank; tokens then travel to their experts' ranks
+        and back inside the layer (``models/moe.py``), and the training engine treats the expert
+        tensors as rank-local.  The reference only replicates or FSDP-shards the experts."""
         SpeculatorModel.__init__(self, config)
         self._init_vocab(config)
         if self.use_draft_vocab:
             raise NotImplementedError("Vocab reduction is not supported for MTP speculators")
         tc = config.transformer_layer_config
-        self.mtp_layers = nn.ModuleList([build_mtp_layer(tc, 0)])
+        self.mtp_layers = nn.ModuleList([build_mtp_layer(tc, 0, ep_group=ep_group)])
         # expert routing sizes its buffers from counts read on the host (bincount, exchange plans):
         # a layer with experts runs eagerly, a dense one as a CUDA graph
         self.cuda_graph_safe = type(self.mtp_layers[0]).__name__ != "MoEMTPLayer"
@@ -118,7 +134,10 @@ class MTPDraftModel(DraftVocabMixin, SpeculatorModel):
         return all_logits, total, metrics
 
     @classmethod
-    def from_training_args(cls, verifier_config, *, num_speculative_steps: int = 3, verifier_name_or_path: str | None = None, **_: Any) -> "MTPDraftModel":
+    def from_training_args(cls, verifier_config, *, num_speculative_steps: int = 3, verifier_name_or_path: str | None = None,
+                           expert_parallel: bool | None = None, **_: Any) -> "MTPDraftModel":
+        """``expert_parallel`` (default: the environment variable ``SB200_EXPERT_PARALLEL=1``): split a
+        mixture-of-experts head's experts over all ranks of the job."""
         if verifier_name_or_path is None:
             raise ValueError(
                 "verifier_name_or_path is required for MTP training. The verifier model must contain native MTP "
@@ -133,7 +152,7 @@ class MTPDraftModel(DraftVocabMixin, SpeculatorModel):
                 verifier=VerifierConfig.from_pretrained(verifier_name_or_path),
             ),
         )
-        model = cls(config=config)
+        model = cls(config=config, ep_group=_expert_parallel_group(expert_parallel))
         from speculators_b200.convert.mtp.converter import MTPConverter
 
         state = MTPConverter().convert_to_state_dict(verifier_name_or_path)

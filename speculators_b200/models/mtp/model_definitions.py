@@ -103,10 +103,10 @@ class _LazyMTPClasses(dict):
 mtp_model_classes = _LazyMTPClasses()
 
 
-def build_mtp_layer(config: TransformerLayerConfig, layer_idx: int = 0) -> nn.Module:
+def build_mtp_layer(config: TransformerLayerConfig, layer_idx: int = 0, ep_group=None) -> nn.Module:
     kind = resolve_model_type(config.model_type)
     if kind in _MOE_TYPES and int(config.get("num_experts", 0) or 0) > 0 or kind == "qwen3_next":
         from speculators_b200.models.moe import MoEMTPLayer
 
-        return MoEMTPLayer(config, layer_idx)
+        return MoEMTPLayer(config, layer_idx, ep_group=ep_group)
     return MTPLayer(config, layer_idx)

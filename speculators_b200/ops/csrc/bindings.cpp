@@ -9,7 +9,7 @@
 #include <ATen/ATen.h>
 
 namespace sb200 {
-int rmsnorm_bwd_partial_rows(int rows);
+int rmsnorm_bwd_partial_rows(int rows, int H);
 void launch_rmsnorm_fwd(const void*, const void*, const int64_t*, void*, float*, int, int, int64_t,
                         int64_t, float, int64_t, cudaStream_t);
 struct BoundsRecord {
@@ -121,7 +121,7 @@ void rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tenso
   Tensor partial;
   if (dw.has_value()) {
     TORCH_CHECK(dw->scalar_type() == at::kFloat && dw->numel() == H && dw->is_contiguous());
-    partial = at::empty({sb200::rmsnorm_bwd_partial_rows(rows), H}, dw->options());
+    partial = at::empty({sb200::rmsnorm_bwd_partial_rows(rows, H), H}, dw->options());
     dwp = partial.data_ptr<float>();
     dwo = dw->data_ptr<float>();
   }

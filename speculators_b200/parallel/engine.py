@@ -25,6 +25,12 @@ src/speculators/train/optimizers.py:61-110) assigns whole matrices to ranks: the
 the fp32 master copy and the momentum, runs the Newton-Schulz update on the package's GEMM and
 broadcasts the refreshed bf16 weights; the AdamW tail (norm weights, embeddings) is sharded or
 replicated like the plain AdamW mode.
+
+Expert-parallel parameters (tensors marked ``_sb200_local``: the experts a rank holds differ
+from rank to rank) live in a third region at the end of the flat buffers that no collective
+touches: their gradients are already complete on the owning rank (its experts saw every rank's
+tokens through the dispatch), only their squared norm joins the global gradient norm, and the
+owner keeps their full AdamW state.  State dicts present them as the stack of all ranks' experts.
 """
 
 from __future__ import annotations
@@ -127,6 +133,10 @@ class TrainEngine:
         )
         if mode in ("p2p", "nvls") and not applicable:
             raise ValueError(f"comm={mode!r} needs sharded multi-rank CUDA training with AdamW in bf16 on one node (<= 8 ranks)")
+        if applicable and any(getattr(p, "_sb200_local", False) for p in self.model.parameters()):
+            if mode in ("p2p", "nvls"):
+                raise ValueError(f"comm={mode!r} does not cover models with expert-parallel (rank-local) parameters")
+            applicable = False  # the fused step reduces the whole buffer; rank-local experts need the region-aware path
         if not applicable or mode == "nccl":
             return False
         reason = self._peer_memory_unavailable()
@@ -242,28 +252,43 @@ class TrainEngine:
             raise ValueError("No trainable parameters found to optimize.")
         use_muon = cfg.optimizer == "muon"
         muon_names = {n for n, _ in split_named_params_for_muon(model)[0]} if use_muon else set()
-        # Muon matrices first, then the AdamW tail: two contiguous regions
-        named.sort(key=lambda np_: 0 if np_[0] in muon_names else 1)
+        local_names = {n for n, p in named if getattr(p, "_sb200_local", False)} if self.world > 1 else set()
+        muon_names -= local_names
+        # Muon matrices first, then the AdamW tail, then the rank-local (expert-parallel) tensors
+        named.sort(key=lambda np_: 0 if np_[0] in muon_names else (2 if np_[0] in local_names else 1))
         self.names: list[str] = []
         self.params: list[nn.Parameter] = []
         self.offsets: list[int] = []
         off = 0
         self.muon_end = 0
         unit = _ALIGN * self.world
+        self.shared_end = -1
         for name, p in named:
             if muon_names and name not in muon_names and self.muon_end == 0 and off > 0:
                 # first tensor of the AdamW tail: the matrix region ends on a shard-unit boundary,
                 # so the tail divides evenly among the ranks
                 off = self.muon_end = (off + unit - 1) // unit * unit
+            if name in local_names and self.shared_end < 0:
+                if muon_names and self.muon_end == 0:
+                    off = self.muon_end = (off + unit - 1) // unit * unit
+                off = (off + unit - 1) // unit * unit
+                if off == self.muon_end:
+                    off += unit
+                self.shared_end = off  # everything before is replicated (or sharded) across the ranks
             self.names.append(name)
             self.params.append(p)
             self.offsets.append(off)
             off += (p.numel() + _ALIGN - 1) // _ALIGN * _ALIGN
-        if muon_names and self.muon_end == 0:
-            off = self.muon_end = (off + unit - 1) // unit * unit  # matrices only
-        self.total = (off + unit - 1) // unit * unit
-        if self.total == self.muon_end:
-            self.total += unit  # keeps the tail slice non-empty
+        if self.shared_end < 0:
+            if muon_names and self.muon_end == 0:
+                off = self.muon_end = (off + unit - 1) // unit * unit  # matrices only
+            self.total = (off + unit - 1) // unit * unit
+            if self.total == self.muon_end:
+                self.total += unit  # keeps the tail slice non-empty
+            self.shared_end = self.total
+        else:
+            self.total = (off + _ALIGN - 1) // _ALIGN * _ALIGN
+        self.local_names = local_names
         self._peer_local: list[int] = []
         self._peer_mapped: list[int] = []
         self._symm_handles = None
@@ -282,7 +307,7 @@ class TrainEngine:
         for p, o in zip(self.params, self.offsets):
             init32[o : o + p.numel()].copy_(p.data.detach().reshape(-1).to(device=dev, dtype=torch.float32))
         if self.distributed and cfg.broadcast_from_rank0:
-            dist.broadcast(init32, src=dist.get_global_rank(self.group, 0) if self.group is not None else 0, group=self.group)
+            dist.broadcast(init32[: self.shared_end], src=dist.get_global_rank(self.group, 0) if self.group is not None else 0, group=self.group)
             for p in model.parameters():  # frozen weights too: every rank trains the same model
                 if not p.requires_grad:
                     dist.broadcast(p.data, src=dist.get_global_rank(self.group, 0) if self.group is not None else 0, group=self.group)
@@ -300,16 +325,24 @@ class TrainEngine:
         # (``_init_muon``) and the AdamW slice covers the tail only.
         first = self.muon_end
         if self.sharded:
-            per = (self.total - first) // self.world
+            per = (self.shared_end - first) // self.world
             self.lo, self.hi = first + self.rank * per, first + (self.rank + 1) * per
         else:
-            self.lo, self.hi = first, self.total
+            self.lo, self.hi = first, self.shared_end
         n = self.hi - self.lo
         dev = self.device
         fp32_compute = self.cfg.compute_dtype == torch.float32
         self._init_muon(fp32_compute)
         # with fp32 compute weights the flat buffer *is* the master copy
         self.master = self.flat_w[self.lo : self.hi] if fp32_compute else self._init32[self.lo : self.hi].clone()
+        n_local = self.total - self.shared_end
+        self.local_master = self.local_exp_avg = self.local_exp_avg_sq = None
+        if n_local:
+            a, b = self.shared_end, self.total
+            self.local_master = self.flat_w[a:b] if fp32_compute else self._init32[a:b].clone()
+            self.local_exp_avg = torch.zeros(n_local, dtype=torch.float32, device=dev)
+            self.local_exp_avg_sq = torch.zeros(n_local, dtype=torch.float32, device=dev)
+            self.local_sq = torch.zeros(1, dtype=torch.float32, device=dev)
         del self._init32
         self.exp_avg = torch.zeros(n, dtype=torch.float32, device=dev)
         self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev)
@@ -421,35 +454,60 @@ class TrainEngine:
             return
         multi = self.distributed and self.world > 1
         w16 = None if self.cfg.compute_dtype == torch.float32 else self.flat_w[self.lo : self.hi]
+        shared_g, shared_w = self.flat_g[: self.shared_end], self.flat_w[: self.shared_end]  # the whole buffers unless experts are rank-local
         if self.muon_items:
             # Muon: every rank needs whole reduced matrices for the ones it owns, so the gradient
             # buffer is all-reduced; the norm is then the same local reduction on every rank
             if multi:
                 with nvtx_range("grad reduce"), self._comm_timed():
-                    dist.all_reduce(self.flat_g, op=dist.ReduceOp.SUM, group=self.group)
-            ops.sum_of_squares(self.flat_g, self.norm_sq, accumulate=False)
+                    dist.all_reduce(shared_g, op=dist.ReduceOp.SUM, group=self.group)
+            ops.sum_of_squares(shared_g, self.norm_sq, accumulate=False)
+            self._add_local_norm()
             self._muon_update(self.flat_g)
             ops.adamw_step_(self.master, self.exp_avg, self.exp_avg_sq, self.flat_g[self.lo : self.hi], w16, self.hyper, self.norm_sq)
+            self._local_update()
             if multi:
                 with nvtx_range("weight broadcast"), self._comm_timed():
                     self._muon_broadcast(self.flat_w)
                     if self.sharded:
-                        dist.all_gather_into_tensor(self.flat_w[self.muon_end :], self.flat_w[self.lo : self.hi], group=self.group)
+                        dist.all_gather_into_tensor(self.flat_w[self.muon_end : self.shared_end], self.flat_w[self.lo : self.hi], group=self.group)
             return
         if multi:
             with nvtx_range("grad reduce"), self._comm_timed():
                 if self.sharded:
-                    dist.reduce_scatter_tensor(self.grad_shard, self.flat_g, op=dist.ReduceOp.SUM, group=self.group)
+                    dist.reduce_scatter_tensor(self.grad_shard, shared_g, op=dist.ReduceOp.SUM, group=self.group)
                 else:
-                    dist.all_reduce(self.flat_g, op=dist.ReduceOp.SUM, group=self.group)
-        g = self.grad_shard if self.sharded else self.flat_g
+                    dist.all_reduce(shared_g, op=dist.ReduceOp.SUM, group=self.group)
+        g = self.grad_shard if self.sharded else shared_g
         ops.sum_of_squares(g, self.norm_sq, accumulate=False)
         if self.sharded:
+            if self.local_master is not None:  # one collective for both contributions
+                ops.sum_of_squares(self.flat_g[self.shared_end :], self.norm_sq, accumulate=True)
             dist.all_reduce(self.norm_sq, op=dist.ReduceOp.SUM, group=self.group)
+        else:
+            self._add_local_norm()
         ops.adamw_step_(self.master, self.exp_avg, self.exp_avg_sq, g, w16, self.hyper, self.norm_sq)
+        self._local_update()
         if self.sharded:
             with nvtx_range("weight all-gather"), self._comm_timed():
-                dist.all_gather_into_tensor(self.flat_w, self.flat_w[self.lo : self.hi], group=self.group)
+                dist.all_gather_into_tensor(shared_w, self.flat_w[self.lo : self.hi], group=self.group)
+
+    def _add_local_norm(self) -> None:
+        """Replicated-gradient modes: add the squared norm of every rank's local (expert) gradients
+        to the global figure (the shared part is already the same on every rank)."""
+        if self.local_master is None:
+            return
+        ops.sum_of_squares(self.flat_g[self.shared_end :], self.local_sq, accumulate=False)
+        if self.distributed and self.world > 1:
+            dist.all_reduce(self.local_sq, op=dist.ReduceOp.SUM, group=self.group)
+        self.norm_sq += self.local_sq
+
+    def _local_update(self) -> None:
+        """AdamW over the rank-local region (full state on the owner, no collective)."""
+        if self.local_master is None:
+            return
+        w16 = None if self.cfg.compute_dtype == torch.float32 else self.flat_w[self.shared_end :]
+        ops.adamw_step_(self.local_master, self.local_exp_avg, self.local_exp_avg_sq, self.flat_g[self.shared_end :], w16, self.hyper, self.norm_sq)
 
     # ------------------------------------------------------------------ exposed communication
     def account_comm(self, enabled: bool) -> None:
@@ -624,7 +682,7 @@ class TrainEngine:
     def _gather_full(self, shard: torch.Tensor) -> torch.Tensor:
         if not self.sharded:
             return shard
-        full = torch.empty(self.total - self.muon_end, dtype=shard.dtype, device=shard.device)
+        full = torch.empty(self.shared_end - self.muon_end, dtype=shard.dtype, device=shard.device)
         dist.all_gather_into_tensor(full, shard.contiguous(), group=self.group)
         return full
 
@@ -635,11 +693,26 @@ class TrainEngine:
             return shard
         dst = dist.get_global_rank(self.group, 0) if self.group is not None else 0
         if self.rank == 0:
-            full = torch.empty(self.total - self.muon_end, dtype=shard.dtype, device=shard.device)
+            full = torch.empty(self.shared_end - self.muon_end, dtype=shard.dtype, device=shard.device)
             dist.gather(shard.contiguous(), list(full.chunk(self.world)), dst=dst, group=self.group)
             return full
         dist.gather(shard.contiguous(), None, dst=dst, group=self.group)
         return None
+
+    def _local_stacks(self, region: torch.Tensor | None) -> dict[str, torch.Tensor]:
+        """Rank-local tensors of ``region`` (a ``[shared_end, total)`` sized buffer) as the stack of all
+        ranks' pieces along dim 0, keyed by parameter name (collective; every rank gets the result)."""
+        out: dict[str, torch.Tensor] = {}
+        if region is None:
+            return out
+        for name, p, o in zip(self.names, self.params, self.offsets):
+            if name not in self.local_names:
+                continue
+            mine = region[o - self.shared_end : o - self.shared_end + p.numel()].view(p.shape).float().contiguous()
+            full = torch.empty((self.world * p.shape[0], *p.shape[1:]), dtype=torch.float32, device=mine.device)
+            dist.all_gather_into_tensor(full, mine, group=self.group)
+            out[name] = full
+        return out
 
     def optimizer_state_dict(self, first_rank_only: bool = False) -> dict:
         """Full (unsharded) optimizer state keyed by parameter name; every rank participates in
@@ -648,6 +721,7 @@ class TrainEngine:
         gather = self._gather_to_first if first_rank_only else self._gather_full
         master, m, v = (gather(t) for t in (self.master, self.exp_avg, self.exp_avg_sq))
         mu_master, mu_mom = self._muon_full("master", first_rank_only), self._muon_full("momentum", first_rank_only)
+        stacks = {key: self._local_stacks(t) for key, t in (("master", self.local_master), ("exp_avg", self.local_exp_avg), ("exp_avg_sq", self.local_exp_avg_sq))}
         if master is None or (first_rank_only and self.rank != 0 and self.distributed and self.world > 1):
             return {"step": self.step_count, "optimizer": self.cfg.optimizer, "state": {}}
         state = {}
@@ -656,6 +730,9 @@ class TrainEngine:
             n = p.numel()
             if i in mu_master:  # a Muon matrix: the momentum sits in "exp_avg", there is no second moment
                 state[name] = {"master": mu_master[i].cpu(), "exp_avg": mu_mom[i].cpu(), "exp_avg_sq": torch.zeros(p.shape)}
+                continue
+            if name in self.local_names:  # the stack of every rank's experts
+                state[name] = {key: stacks[key][name].cpu() for key in stacks}
                 continue
             a = o - base
             state[name] = {
@@ -688,6 +765,12 @@ class TrainEngine:
                     own["master"].copy_(entry["master"].reshape(p.shape).float().to(self.device))
                     own["momentum"].copy_(entry["exp_avg"].reshape(p.shape).float().to(self.device))
                 continue
+            if name in self.local_names:  # this rank's slice of the stacked experts
+                a = o - self.shared_end
+                for key, dst in (("master", self.local_master), ("exp_avg", self.local_exp_avg), ("exp_avg_sq", self.local_exp_avg_sq)):
+                    piece = entry[key].float().chunk(self.world, dim=0)[self.rank] if entry[key].shape[0] == self.world * p.shape[0] else entry[key].float()
+                    dst[a : a + p.numel()].copy_(piece.reshape(-1).to(self.device))
+                continue
             n = p.numel()
             a, b = max(o, self.lo), min(o + n, self.hi)
             if a >= b:
@@ -701,19 +784,23 @@ class TrainEngine:
         """Refresh the compute buffer from the master weights (after loading state)."""
         if self.cfg.compute_dtype != torch.float32:
             self.flat_w[self.lo : self.hi].copy_(self.master)
+            if self.local_master is not None:
+                self.flat_w[self.shared_end :].copy_(self.local_master)
             for i, _name, p, o in self.muon_items:
                 if i in self.muon_state:
                     self.flat_w[o : o + p.numel()].view(p.shape).copy_(self.muon_state[i]["master"])
         if self.muon_items and self.distributed and self.world > 1:
             self._muon_broadcast(self.flat_w)
         if self.sharded:
-            dist.all_gather_into_tensor(self.flat_w[self.muon_end :], self.flat_w[self.lo : self.hi].clone(), group=self.group)
+            dist.all_gather_into_tensor(self.flat_w[self.muon_end : self.shared_end], self.flat_w[self.lo : self.hi].clone(), group=self.group)
 
     def load_model_weights_into_master(self) -> None:
         """After ``model.load_state_dict`` wrote new values through the parameter
         views, make them the master copy."""
         if self.cfg.compute_dtype != torch.float32:
             self.master.copy_(self.flat_w[self.lo : self.hi])
+            if self.local_master is not None:
+                self.local_master.copy_(self.flat_w[self.shared_end :])
             for i, _name, p, o in self.muon_items:
                 if i in self.muon_state:
                     self.muon_state[i]["master"].copy_(self.flat_w[o : o + p.numel()].view(p.shape))
@@ -722,9 +809,10 @@ class TrainEngine:
         """fp32 master weights keyed by parameter name (full tensors, on every rank)."""
         master = self._gather_full(self.master)
         mu = self._muon_full("master")
+        local = self._local_stacks(self.local_master)
         base = self.muon_end
         return {
-            name: (mu[i] if i in mu else master[o - base : o - base + p.numel()].view(p.shape).clone())
+            name: (mu[i] if i in mu else local[name] if name in local else master[o - base : o - base + p.numel()].view(p.shape).clone())
             for i, (name, p, o) in enumerate(zip(self.names, self.params, self.offsets))
         }
 

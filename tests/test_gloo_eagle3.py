@@ -48,6 +48,7 @@ def _worker(rank, world, port, vdir, out_path, shard):
         torch.save({"master": full, "moments": {k: v["exp_avg"] for k, v in state["state"].items()}}, out_path)
     else:
         assert state["state"] == {}  # the full state is assembled on the writer only
+    dist.barrier()  # nobody tears its connections down while a peer still talks
     dist.destroy_process_group()
 
 

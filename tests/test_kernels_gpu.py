@@ -20,7 +20,7 @@ def test_extension_is_loaded_from_tree():
     assert ops._ext.loaded_library_path().endswith("_sb200.so")
 
 
-@pytest.mark.parametrize("rows,H", [(1, 64), (127, 4096), (300, 8192), (65, 12288), (129, 256)])
+@pytest.mark.parametrize("rows,H", [(1, 64), (127, 4096), (300, 8192), (65, 12288), (129, 256), (70001, 128), (5000, 64), (333, 264)])
 def test_rmsnorm_fwd_bwd(rows, H):
     torch.manual_seed(0)
     x = torch.randn(rows, H, device=DEV, dtype=torch.bfloat16, requires_grad=True)

@@ -85,6 +85,7 @@ def _worker(rank, world, port, out_path, shard):
     if rank == 0:
         torch.save({"master": full, "momentum": {k: v["exp_avg"] for k, v in sd["state"].items()}, "owners": owners,
                     "weights": {k: v.detach().clone() for k, v in model.state_dict().items()}}, out_path)
+    dist.barrier()  # nobody tears its connections down while a peer still talks
     dist.destroy_process_group()
 
 

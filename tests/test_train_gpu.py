@@ -229,4 +229,6 @@ def test_muon_on_gpu_tracks_the_fp32_engine():
         w, g_ = want[name], got[name].cpu()
         moved = (w - dict(Net().named_parameters())[name].detach()).abs().max()
         assert moved > 0
-        assert (w - g_).abs().max() < 0.15 * moved + 1e-4, (name, float((w - g_).abs().max()), float(moved))
+        # matrices: Newton-Schulz in bf16 against fp32; vectors (AdamW): the first steps are sign-like, bf16 gradients flip a few
+        tol = 0.15 if w.ndim == 2 else 0.4
+        assert (w - g_).abs().max() < tol * moved + 1e-4, (name, float((w - g_).abs().max()), float(moved))
