@@ -43,7 +43,20 @@ TINY = dict(LLAMA31_8B, hidden_size=256, num_hidden_layers=6, num_attention_head
 QWEN3_8B = dict(LLAMA31_8B, architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=36, intermediate_size=12288,
                 vocab_size=151936, rms_norm_eps=1e-6, rope_theta=1000000.0, max_position_embeddings=40960)
 LLAMA33_70B = dict(LLAMA31_8B, hidden_size=8192, num_hidden_layers=80, num_attention_heads=64, intermediate_size=28672)
-VERIFIERS = {"llama31_8b": LLAMA31_8B, "tiny": TINY, "qwen3_8b": QWEN3_8B, "llama33_70b": LLAMA33_70B}
+# the MTP layer of a Qwen3-Next-80B-A3B-shaped verifier: gated full attention (head dim 256), 512 experts top-10 + shared expert
+QWEN3_NEXT_MTP = {
+    "architectures": ["Qwen3NextForCausalLM"], "model_type": "qwen3_next", "hidden_size": 2048, "num_hidden_layers": 48,
+    "num_attention_heads": 16, "num_key_value_heads": 2, "head_dim": 256, "intermediate_size": 5632, "vocab_size": 151936,
+    "rms_norm_eps": 1e-6, "rope_theta": 10000000.0, "partial_rotary_factor": 0.25, "max_position_embeddings": 262144,
+    "hidden_act": "silu", "attention_bias": False, "tie_word_embeddings": False, "initializer_range": 0.02,
+    "num_experts": 512, "num_experts_per_tok": 10, "moe_intermediate_size": 512, "shared_expert_intermediate_size": 512,
+    "norm_topk_prob": True, "decoder_sparse_step": 1, "mlp_only_layers": [],
+}
+TINY_MOE = dict(QWEN3_NEXT_MTP, hidden_size=256, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                vocab_size=1024, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=256, shared_expert_intermediate_size=256,
+                max_position_embeddings=4096)
+VERIFIERS = {"llama31_8b": LLAMA31_8B, "tiny": TINY, "qwen3_8b": QWEN3_8B, "llama33_70b": LLAMA33_70B, "qwen3_next_mtp": QWEN3_NEXT_MTP,
+             "tiny_moe": TINY_MOE}
 METRIC = "EAGLE3-8B draft-train tokens/s at 1/2/4/8 B200 (device max over ranks)"
 PARITY_STEPS = 6  # optimizer steps from the common initial weights whose losses both arms record
 PARITY_RTOL = 0.03
@@ -84,6 +97,13 @@ CONFIGS = {
         train=dict(loss_fn="kl_div", num_depths=4, down_sample_ratio=0.7, down_sample_ratio_min=0.2),
         label="peagle 1-layer draft (4 depths) for llama-3.3-70b-arch verifier",
     ),
+    # MTP-head fine-tuning for a Qwen3-Next-80B-A3B-shaped MTP layer, experts split over the ranks (expert parallel)
+    "mtp_moe": dict(
+        algo="mtp", verifier="qwen3_next_mtp", seq_len=4096, draft_vocab=None, aux=[48], draft_layers=1, layer_types=None,
+        sliding_window=None, verifier_forward=False, model=dict(num_speculative_steps=3),
+        train=dict(num_speculative_steps=3, step_weight_beta=0.6),
+        label="mtp head (gated attention hd 256, 512 experts top-10 + shared) for qwen3-next-80b-a3b-arch verifier",
+    ),
     # the CPU / gloo plumbing configuration (tiny Llama verifier run for the hidden states)
     "tiny": dict(
         algo="eagle3", verifier="tiny", seq_len=128, draft_vocab=512, aux=[1, 2, 3], draft_layers=1,
@@ -110,7 +130,8 @@ def resolve_config(args) -> dict:
         c["verifier_forward"] = False
     if args.scale == "tiny" and name != "tiny":
         # the same algorithm and flags at plumbing size (CPU checks of this script)
-        c.update(verifier="tiny", seq_len=args.seq_len or 256, draft_vocab=args.draft_vocab or 512, aux=list(range(1, len(c["aux"]) + 1)))
+        c.update(verifier="tiny_moe" if c["algo"] == "mtp" else "tiny", seq_len=args.seq_len or 256,
+                 draft_vocab=None if c["algo"] == "mtp" else (args.draft_vocab or 512), aux=list(range(1, len(c["aux"]) + 1)))
         if "mask_token_id" in c["model"]:
             c["model"]["mask_token_id"] = TINY["vocab_size"] - 1
         if "max_anchors" in c["train"]:
@@ -135,6 +156,7 @@ def parse_args():
     ap.add_argument("--draft-vocab", type=int, default=None)
     ap.add_argument("--ttt-steps", type=int, default=None)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-expert-parallel", action="store_true", help="mtp_moe on several GPUs: keep all experts on every rank")
     ap.add_argument("--no-verifier-forward", action="store_true", help="draw hidden states from N(0,1) instead of running the random-init verifier")
     ap.add_argument("--device", default=None)
     return ap.parse_args()
@@ -218,8 +240,11 @@ def data_note(c: dict) -> str:
 
 
 def draft_layer_config(c: dict) -> dict:
-    """Decoder hyper-parameters of the draft: the verifier's widths, ``draft_layers`` layers."""
+    """Decoder hyper-parameters of the draft: the verifier's widths, ``draft_layers`` layers (MTP: the
+    verifier's own configuration, whose MTP layer is what gets trained)."""
     v = VERIFIERS[c["verifier"]]
+    if c["algo"] == "mtp":
+        return dict(v)
     return dict(v, num_hidden_layers=c["draft_layers"], sliding_window=c["sliding_window"], layer_types=list(c["layer_types"]))
 
 
@@ -308,16 +333,36 @@ def run_ours(args):
     tag = inputs_tag(c, device.type)
     root = bench_inputs.ensure_inputs(
         cfg, tag, seq_len=c["seq_len"], draft_vocab=draft_vocab, layer_ids=c["aux"], rank=rank, local_rank=local_rank,
-        n_batches=2, device=device, verifier_forward=c["verifier_forward"], barrier=barrier,
+        n_batches=2, device=device, verifier_forward=c["verifier_forward"], barrier=barrier, kind=c["algo"],
     )
-    d2t, t2d = bench_inputs.load_vocab_maps(root)
     batches = bench_inputs.load_batches(root, rank, pin=cuda)
     model_class = SpeculatorModel.registry[c["algo"]]
-    model = model_class.from_training_args(
-        TransformerLayerConfig(**draft_layer_config(c)), t2d=t2d, d2t=d2t, draft_vocab_size=draft_vocab,
-        verifier_name_or_path=os.path.join(root, "verifier"), target_layer_ids=c["aux"], **c["model"],
-    )
-    init = bench_inputs.seeded_draft_init({k: tuple(v.shape) for k, v in model.state_dict().items()})
+    expert_parallel = False
+    if c["algo"] == "mtp":
+        from speculators_b200.config import SpeculatorsConfig, VerifierConfig
+        from speculators_b200.models.mtp.config import MTPSpeculatorConfig
+        from speculators_b200.proposals.greedy import GreedyTokenProposalConfig
+
+        expert_parallel = world > 1 and not args.no_expert_parallel
+        spec_cfg = MTPSpeculatorConfig(
+            transformer_layer_config=TransformerLayerConfig(**draft_layer_config(c)),
+            speculators_config=SpeculatorsConfig(
+                algorithm="mtp", proposal_methods=[GreedyTokenProposalConfig(speculative_tokens=c["model"]["num_speculative_steps"])],
+                default_proposal_method="greedy", verifier=VerifierConfig.from_pretrained(os.path.join(root, "verifier")),
+            ),
+        )
+        model = model_class(spec_cfg, ep_group=dist.group.WORLD if expert_parallel else None)
+        model.load_verifier_weights()
+    else:
+        d2t, t2d = bench_inputs.load_vocab_maps(root)
+        model = model_class.from_training_args(
+            TransformerLayerConfig(**draft_layer_config(c)), t2d=t2d, d2t=d2t, draft_vocab_size=draft_vocab,
+            verifier_name_or_path=os.path.join(root, "verifier"), target_layer_ids=c["aux"], **c["model"],
+        )
+    shapes = {k: tuple(v.shape) for k, v in model.state_dict().items()}
+    if expert_parallel:  # initial values are drawn for the stack of all experts; every rank loads its own slice
+        shapes = {k: ((v[0] * world, *v[1:]) if ".experts." in k else v) for k, v in shapes.items()}
+    init = bench_inputs.seeded_draft_init(shapes)
     missing = model.load_state_dict(init, strict=False)
     assert not missing.unexpected_keys, missing.unexpected_keys
     train_kwargs, _ = model_class.get_trainer_kwargs(**c["train"])
@@ -398,6 +443,7 @@ def run_ours(args):
                 "optimizer_comm": ("nvls multimem" if getattr(trainer.engine, "nvls", False) else "nvlink p2p" if getattr(trainer.engine, "p2p", False)
                                    else ("nccl" if cuda else "gloo") if world > 1 else "none"),
                 "cuda_graph": trainer._graphed is not None,
+                "expert_parallel": (os.environ.get("SB200_EP_COMM", "nvlink p2p") if cuda else "gloo all-to-all") if expert_parallel else False,
                 "path": "speculators_b200.train.Trainer.train_step / train_step_async",
             },
             "regions_ms_per_step": spread([m / args.steps for m in region_ms]),
@@ -526,29 +572,50 @@ def run_reference(args):
     tag = inputs_tag(c, "cuda")
     root = bench_inputs.ensure_inputs(
         cfg, tag, seq_len=c["seq_len"], draft_vocab=draft_vocab, layer_ids=c["aux"], rank=rank, local_rank=local_rank,
-        n_batches=2, device=device, verifier_forward=c["verifier_forward"], barrier=barrier,
+        n_batches=2, device=device, verifier_forward=c["verifier_forward"], barrier=barrier, kind=c["algo"],
     )
-    d2t, t2d = bench_inputs.load_vocab_maps(root)
     batches = bench_inputs.load_batches(root, rank, pin=True)
 
     draft = draft_layer_config(c)
-    hf_class = Qwen3Config if draft["model_type"] == "qwen3" else LlamaConfig
-    hf_cfg = hf_class(**{k: v for k, v in draft.items() if k not in ("architectures", "model_type", "rope_theta")})
-    try:
-        hf_cfg.rope_parameters = {"rope_type": "default", "rope_theta": cfg["rope_theta"]}
-    except Exception:  # noqa: BLE001
-        hf_cfg.rope_theta = cfg["rope_theta"]
     model_class = SpeculatorModel.registry[c["algo"]]
-    model = model_class.from_training_args(
-        hf_cfg, t2d=t2d, d2t=d2t, draft_vocab_size=draft_vocab, verifier_name_or_path=os.path.join(root, "verifier"),
-        target_layer_ids=c["aux"], **c["model"],
-    )
+    if c["algo"] == "mtp":
+        from transformers import Qwen3NextConfig
+
+        from speculators.config import SpeculatorsConfig, VerifierConfig
+        from speculators.models.mtp.config import MTPSpeculatorConfig
+        from speculators.proposals.greedy import GreedyTokenProposalConfig
+
+        hf_cfg = Qwen3NextConfig(**{k: v for k, v in draft.items() if k not in ("architectures", "model_type", "rope_theta")})
+        try:
+            hf_cfg.rope_parameters = {"rope_type": "default", "rope_theta": cfg["rope_theta"], "partial_rotary_factor": cfg["partial_rotary_factor"]}
+        except Exception:  # noqa: BLE001
+            hf_cfg.rope_theta = cfg["rope_theta"]
+        model = model_class(MTPSpeculatorConfig(
+            transformer_layer_config=hf_cfg,
+            speculators_config=SpeculatorsConfig(
+                algorithm="mtp", proposal_methods=[GreedyTokenProposalConfig(speculative_tokens=c["model"]["num_speculative_steps"])],
+                default_proposal_method="greedy", verifier=VerifierConfig.from_pretrained(os.path.join(root, "verifier")),
+            ),
+        ))
+        model.load_verifier_weights()
+    else:
+        d2t, t2d = bench_inputs.load_vocab_maps(root)
+        hf_class = Qwen3Config if draft["model_type"] == "qwen3" else LlamaConfig
+        hf_cfg = hf_class(**{k: v for k, v in draft.items() if k not in ("architectures", "model_type", "rope_theta")})
+        try:
+            hf_cfg.rope_parameters = {"rope_type": "default", "rope_theta": cfg["rope_theta"]}
+        except Exception:  # noqa: BLE001
+            hf_cfg.rope_theta = cfg["rope_theta"]
+        model = model_class.from_training_args(
+            hf_cfg, t2d=t2d, d2t=d2t, draft_vocab_size=draft_vocab, verifier_name_or_path=os.path.join(root, "verifier"),
+            target_layer_ids=c["aux"], **c["model"],
+        )
     init = bench_inputs.seeded_draft_init({k: tuple(v.shape) for k, v in model.state_dict().items()})
     with torch.no_grad():
         own = model.state_dict()
         for k, v in init.items():
             own[k].copy_(v)
-    train_kwargs, _ = model_class.get_trainer_kwargs(loss_implementation="fused", **c["train"])
+    train_kwargs, _ = model_class.get_trainer_kwargs(**({} if c["algo"] == "mtp" else {"loss_implementation": "fused"}), **c["train"])
     tokens_per_step = sum(int((b["document_ids"] != -1).sum()) for b in batches) / len(batches)
 
     class Capture(logging.Handler):

@@ -103,6 +103,20 @@ def _span_mask(T: int, p: float, span: int, gen: torch.Generator) -> torch.Tenso
     return on.repeat_interleave(span)[:T]
 
 
+def _make_batch_mtp(cfg: dict, seq_len: int, seed: int):
+    """MTP fine-tuning batch: token ids and the verifier's last hidden states (unit normal, RMS-normalised)."""
+    gen = torch.Generator().manual_seed(seed)
+    T, H = seq_len, cfg["hidden_size"]
+    ids = torch.randint(0, cfg["vocab_size"], (T,), generator=gen)
+    mask = _span_mask(T, 0.6, max(1, min(64, T // 32)), gen)
+    hs = torch.randn(T, H, generator=gen)
+    hs = (hs * torch.rsqrt(hs.pow(2).mean(-1, keepdim=True) + 1e-6)).to(torch.bfloat16)
+    return {
+        "input_ids": ids.unsqueeze(0), "hidden_states": hs.unsqueeze(0).contiguous(), "loss_mask": mask.unsqueeze(0),
+        "position_ids": torch.arange(T, dtype=torch.long).unsqueeze(0), "document_ids": torch.zeros(1, T, dtype=torch.long),
+    }
+
+
 def _make_batch(cfg: dict, seq_len: int, layer_ids: list[int], seed: int, device, dtype, verifier_forward: bool):
     gen = torch.Generator().manual_seed(seed)
     T, H = seq_len, cfg["hidden_size"]
@@ -136,8 +150,8 @@ def _vocab_maps(vocab_size: int, draft_vocab: int, seq_len: int, seed: int = 0):
     return d2t, t2d
 
 
-def ensure_inputs(cfg: dict, tag: str, *, seq_len: int, draft_vocab: int, layer_ids: list[int], rank: int, local_rank: int,
-                  n_batches: int, device, verifier_forward: bool, barrier) -> str:
+def ensure_inputs(cfg: dict, tag: str, *, seq_len: int, draft_vocab: int | None, layer_ids: list[int], rank: int, local_rank: int,
+                  n_batches: int, device, verifier_forward: bool, barrier, kind: str = "eagle3") -> str:
     """Write whatever is missing of the input files; ``barrier()`` separates the shared files
     (written by local rank 0) from their readers.  Returns the directory."""
     root = inputs_dir(tag)
@@ -158,12 +172,16 @@ def ensure_inputs(cfg: dict, tag: str, *, seq_len: int, draft_vocab: int, layer_
             },
             os.path.join(vdir, "model.safetensors"), metadata={"format": "pt"},
         )
-        d2t, t2d = _vocab_maps(V, draft_vocab, seq_len)
-        torch.save({"d2t": d2t, "t2d": t2d}, os.path.join(root, "vocab_maps.pt"))
+        if draft_vocab:
+            d2t, t2d = _vocab_maps(V, draft_vocab, seq_len)
+            torch.save({"d2t": d2t, "t2d": t2d}, os.path.join(root, "vocab_maps.pt"))
         open(os.path.join(vdir, ".done"), "w").close()
     mine = os.path.join(root, f"batches_rank{rank}.pt")
     if not os.path.exists(mine):
-        batches = [_make_batch(cfg, seq_len, layer_ids, 1000 * rank + i, device, dtype, verifier_forward) for i in range(n_batches)]
+        if kind == "mtp":
+            batches = [_make_batch_mtp(cfg, seq_len, 1000 * rank + i) for i in range(n_batches)]
+        else:
+            batches = [_make_batch(cfg, seq_len, layer_ids, 1000 * rank + i, device, dtype, verifier_forward) for i in range(n_batches)]
         torch.save(batches, mine + ".tmp")
         os.replace(mine + ".tmp", mine)
     if device.type == "cuda":
