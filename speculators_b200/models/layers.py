@@ -269,17 +269,36 @@ class Attention(nn.Module):
         return self.o_proj(out.reshape(T, self.nh * self.hd), residual=residual)
 
 
+_GATE_ACTIVATIONS = {
+    "gelu": lambda g: torch.nn.functional.gelu(g),
+    "gelu_new": lambda g: torch.nn.functional.gelu(g, approximate="tanh"),
+    "gelu_pytorch_tanh": lambda g: torch.nn.functional.gelu(g, approximate="tanh"),
+    "relu": torch.relu,
+}
+
+
 class MLP(nn.Module):
+    """Gated MLP ``down(act(gate(x)) * up(x))``.  SiLU (every supported verifier family's default)
+    runs on the fused SwiGLU kernel; the other activations the reference accepts through
+    ``--draft-hidden-act`` (GELU variants, ReLU) use the element-wise PyTorch formulation."""
+
     def __init__(self, config: TransformerLayerConfig, intermediate_size: int | None = None):
         super().__init__()
         inter = intermediate_size or config.intermediate_size
-        if config.hidden_act not in ("silu", "swish"):
-            raise NotImplementedError(f"hidden_act={config.hidden_act!r}: only SiLU-gated MLPs are built")
+        self.hidden_act = str(config.hidden_act)
+        if self.hidden_act not in ("silu", "swish") and self.hidden_act not in _GATE_ACTIVATIONS:
+            raise ValueError(f"hidden_act={config.hidden_act!r} is not supported; choose one of {['silu', *sorted(_GATE_ACTIVATIONS)]}")
         self.gate_up_proj = FusedLinear(config.hidden_size, ["gate_proj", "up_proj"], [inter, inter], bias=bool(config.mlp_bias)).attach(self, "gate_up_proj")
         self.down_proj = Linear(inter, config.hidden_size, bias=bool(config.mlp_bias))
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
-        return self.down_proj(ops.swiglu(self.gate_up_proj(x)), residual=residual)
+        gate_up = self.gate_up_proj(x)
+        if self.hidden_act in ("silu", "swish"):
+            hidden = ops.swiglu(gate_up)
+        else:
+            gate, up = gate_up.chunk(2, dim=-1)
+            hidden = _GATE_ACTIVATIONS[self.hidden_act](gate) * up
+        return self.down_proj(hidden, residual=residual)
 
 
 class DecoderLayer(nn.Module):

@@ -165,3 +165,23 @@ ptxas info    : Used 40 registers, used 1 barriers, 264 bytes smem
     assert [r["kernel"] for r in rows] == ["_ZN5sb2001aEv", "_ZN5sb2001bEv"]
     assert (rows[0]["registers"], rows[0]["stack"], rows[0]["spill_stores"], rows[0]["spill_loads"], rows[0]["smem"]) == (168, 48, 44, 40, 1024)
     assert (rows[1]["registers"], rows[1]["smem"], rows[1]["spill_stores"]) == (40, 264, 0)
+
+
+def test_gated_mlp_activations():
+    """``--draft-hidden-act``: SiLU on the fused kernel path, GELU variants and ReLU element-wise, anything else refused by name."""
+    import pytest
+    import torch
+
+    from speculators_b200.layer_config import TransformerLayerConfig
+    from speculators_b200.models.layers import MLP
+
+    base = dict(model_type="llama", hidden_size=16, intermediate_size=32, num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=1, vocab_size=10)
+    acts = {"silu": torch.nn.functional.silu, "gelu": torch.nn.functional.gelu, "relu": torch.relu,
+            "gelu_pytorch_tanh": lambda t: torch.nn.functional.gelu(t, approximate="tanh")}
+    x = torch.randn(5, 16)
+    for name, fn in acts.items():
+        mlp = MLP(TransformerLayerConfig(**base, hidden_act=name))
+        gate, up = (x @ mlp.gate_up_proj.weight.t()).chunk(2, dim=-1)
+        assert torch.allclose(mlp(x), (fn(gate) * up) @ mlp.down_proj.weight.t(), atol=1e-6)
+    with pytest.raises(ValueError, match="not supported"):
+        MLP(TransformerLayerConfig(**base, hidden_act="tanh"))
