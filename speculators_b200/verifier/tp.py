@@ -1,0 +1,107 @@
+"""Tensor-parallel verifier forward.
+
+The reference runs its verifier in a vLLM server with ``--tensor-parallel-size``
+(scripts/launch_vllm.py:104-163); a 70B-class verifier does not fit one GPU's worth of
+throughput next to the trainer.  This is the in-framework counterpart of that server for dense
+Llama / Qwen3 verifiers: the ranks of a process group split every layer Megatron-style
+
+* q | k | v and gate | up column-parallel (each rank holds ``heads / R`` query heads, ``kv_heads / R``
+  KV heads and ``intermediate / R`` MLP columns),
+* o and down row-parallel: every rank multiplies its slice and the partial sums are all-reduced,
+
+so a layer costs two all-reduces of ``[T, H]``.  All products run on the package's GEMM and
+attention kernels through the same ``DecoderLayer`` the draft models use (built for the local
+head / column counts).  Weights are the rank's slices of exactly the tensors ``RandomVerifier``
+generates for a seed, so the result equals the single-device forward (tested with two gloo ranks).
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from speculators_b200.layer_config import TransformerLayerConfig
+from speculators_b200.models.eagle3.attention import causal_document_interval
+from speculators_b200.models.layers import DecoderLayer, RotaryTable
+from speculators_b200.ops import AttnSpec
+from speculators_b200.verifier.model import _seeded
+
+__all__ = ["TensorParallelVerifier"]
+
+
+class TensorParallelVerifier:
+    def __init__(self, config: TransformerLayerConfig | dict, group=None, seed: int = 0, device="cpu", dtype=torch.float32):
+        self.cfg = TransformerLayerConfig.from_any(config)
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        c, R = self.cfg, self.world
+        if c.num_attention_heads % R or c.num_key_value_heads % R or c.intermediate_size % R:
+            raise ValueError(f"heads ({c.num_attention_heads} / {c.num_key_value_heads}) and intermediate size ({c.intermediate_size}) "
+                             f"must be divisible by the tensor-parallel size ({R})")
+        self.seed, self.device, self.dtype = seed, torch.device(device), dtype
+        self.rotary = RotaryTable(self.cfg).to(self.device)
+        self.local_cfg = TransformerLayerConfig(**{
+            **self.cfg.to_dict(), "num_attention_heads": c.num_attention_heads // R, "num_key_value_heads": c.num_key_value_heads // R,
+            "intermediate_size": c.intermediate_size // R, "head_dim": c.head_dim,
+        })
+        with torch.device("meta"):  # names, shapes and order of a full layer's tensors (what the seeds are tied to)
+            self._full_shapes = [(n, tuple(p.shape)) for n, p in DecoderLayer(self.cfg, 0).named_parameters()]
+
+    def embed_weight(self) -> torch.Tensor:
+        return _seeded((self.cfg.vocab_size, self.cfg.hidden_size), 0.02, self.seed * 1000 + 900, self.device, self.dtype)
+
+    def _slice(self, name: str, full: torch.Tensor) -> torch.Tensor:
+        """This rank's part of a full layer tensor."""
+        c, R, r = self.cfg, self.world, self.rank
+        hd = c.head_dim
+        if name.endswith("qkv_proj.weight"):
+            nq, nk = c.num_attention_heads * hd, c.num_key_value_heads * hd
+            q, k, v = full[:nq], full[nq : nq + nk], full[nq + nk :]
+            return torch.cat([t.chunk(R, dim=0)[r] for t in (q, k, v)], dim=0)
+        if name.endswith("gate_up_proj.weight"):
+            gate, up = full.chunk(2, dim=0)
+            return torch.cat([gate.chunk(R, dim=0)[r], up.chunk(R, dim=0)[r]], dim=0)
+        if name.endswith(("o_proj.weight", "down_proj.weight")):
+            return full.chunk(R, dim=1)[r]
+        return full  # norms: replicated
+
+    def _layer(self, idx: int) -> DecoderLayer:
+        layer = DecoderLayer(self.local_cfg, idx)
+        own = dict(layer.named_parameters())
+        with torch.no_grad():
+            for j, (name, shape) in enumerate(self._full_shapes):
+                p = own[name]
+                if len(shape) == 2:
+                    full = _seeded(shape, 0.02, (self.seed * 1000 + idx) * 64 + j, self.device, self.dtype)
+                    p.data = self._slice(name, full).contiguous()
+                    del full
+                else:
+                    p.data = p.data.to(device=self.device, dtype=self.dtype)
+        return layer
+
+    def _reduce(self, partial: torch.Tensor) -> torch.Tensor:
+        if self.world > 1:
+            dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
+        return partial
+
+    @torch.no_grad()
+    def forward(self, input_ids: torch.Tensor, layer_ids: list[int], document_ids: torch.Tensor | None = None, position_ids: torch.Tensor | None = None):
+        """Same contract as ``RandomVerifier.forward``; every rank of the group calls it with the
+        same inputs and gets the same (complete) hidden states."""
+        ids = input_ids.reshape(-1).to(self.device)
+        T = ids.shape[0]
+        doc = document_ids.reshape(-1).to(self.device) if document_ids is not None else torch.zeros(T, dtype=torch.long, device=self.device)
+        pos = position_ids.reshape(-1).to(self.device) if position_ids is not None else torch.arange(T, device=self.device)
+        lo, hi = causal_document_interval(doc)
+        spec = AttnSpec(lo=lo, hi=hi)
+        h = torch.nn.functional.embedding(ids, self.embed_weight())
+        taken: dict[int, torch.Tensor] = {}
+        for i in range(int(self.cfg.num_hidden_layers)):
+            layer = self._layer(i)
+            h = h + self._reduce(layer.self_attn(layer.input_layernorm(h), pos, self.rotary, spec))
+            h = h + self._reduce(layer.mlp(layer.post_attention_layernorm(h)))
+            if i in layer_ids:
+                taken[i] = h
+            del layer
+        return {"hidden_states": torch.cat([taken[i] for i in layer_ids], dim=-1), "verifier_last_hidden_states": h}
