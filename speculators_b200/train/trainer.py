@@ -76,6 +76,7 @@ class TrainerConfig(NamedTuple):
     max_grad_norm: float = 1.0
     use_cuda_graph: bool | None = None  # None: on when training on a GPU
     device: str | None = None  # None: cuda:<local_rank> when available, else cpu
+    process_group: object | None = None  # ranks that train together (None: all); e.g. the trainer half of a verifier / trainer split
 
 
 class _StepTimer:
@@ -362,6 +363,7 @@ class Trainer:
                 muon_lr=cfg.muon_lr, muon_momentum=cfg.muon_momentum, muon_weight_decay=cfg.muon_weight_decay,
                 muon_ns_steps=cfg.muon_ns_steps, muon_adjust_lr_fn=cfg.muon_adjust_lr_fn,
                 compute_dtype=compute_dtype, shard=cfg.fsdp_shard or hasattr(self.model, "_sb200_shard_request"), broadcast_from_rank0=True,
+                group=cfg.process_group,
             ),
             device=self.device,
         )
