@@ -97,6 +97,15 @@ CONFIGS = {
         train=dict(loss_fn="kl_div", num_depths=4, down_sample_ratio=0.7, down_sample_ratio_min=0.2),
         label="peagle 1-layer draft (4 depths) for llama-3.3-70b-arch verifier",
     ),
+    # the same draft trained online on one box: first half of the GPUs run the 70B-shaped verifier tensor-parallel and
+    # write hidden states into the trainer GPUs' rings over NVLink, second half train (needs >= 2 GPUs)
+    "peagle_online": dict(
+        algo="peagle", verifier="llama33_70b", seq_len=2048, draft_vocab=32000, aux=[2, 40, 77], draft_layers=1,
+        layer_types=["sliding_attention"], sliding_window=2048, verifier_forward=False, online=True,
+        model=dict(norm_before_residual=True, norm_before_fc=True, norm_output=True, num_depths=4, mask_token_id=128255),
+        train=dict(loss_fn="kl_div", num_depths=4, down_sample_ratio=0.7, down_sample_ratio_min=0.2),
+        label="peagle 1-layer draft (4 depths), online: llama-3.3-70b-arch verifier tensor-parallel on half of the GPUs",
+    ),
     # MTP-head fine-tuning for a Qwen3-Next-80B-A3B-shaped MTP layer, experts split over the ranks (expert parallel)
     "mtp_moe": dict(
         algo="mtp", verifier="qwen3_next_mtp", seq_len=4096, draft_vocab=None, aux=[48], draft_layers=1, layer_types=None,
@@ -302,7 +311,102 @@ def loss_parity(mine: list[float] | None, other: list[float] | None, compared: i
 
 
 # ----------------------------------------------------------------------------- this framework
+def run_ours_online(args, c):
+    """Verifier / trainer split on one box (``OnlineSplit``): tokens/s of the trainer half with the
+    verifier half producing its hidden states at the same time, everything device to device."""
+    import torch
+    import torch.distributed as dist
+
+    sys.path.insert(0, REPO)
+    import bench_inputs
+    from speculators_b200 import ops
+    from speculators_b200.layer_config import TransformerLayerConfig
+    from speculators_b200.model import SpeculatorModel
+    from speculators_b200.parallel import maybe_destroy_distributed, maybe_setup_distributed
+    from speculators_b200.train import Trainer, TrainerConfig
+    from speculators_b200.train.online import OnlineSplit
+    from speculators_b200.train.synthetic import SyntheticLoader
+
+    rank, local_rank, world = dist_env()
+    if world < 2:
+        print(json.dumps({"impl": "ours", "config": {"model": c["label"]}, "unavailable": "the online split needs at least 2 GPUs (one verifier, one trainer)"}))
+        return
+    os.environ.setdefault("SB200_COMM", "nccl")  # the trainer half is a sub-group: library collectives for its optimizer step
+    maybe_setup_distributed()
+    device = torch.device(args.device) if args.device else (torch.device("cuda", local_rank) if torch.cuda.is_available() else torch.device("cpu"))
+    cuda = device.type == "cuda"
+    if cuda:
+        torch.cuda.set_device(device)
+    cfg, draft_vocab = VERIFIERS[c["verifier"]], c["draft_vocab"]
+    torch.manual_seed(0)
+    root = bench_inputs.ensure_inputs(cfg, inputs_tag(c, device.type), seq_len=c["seq_len"], draft_vocab=draft_vocab, layer_ids=c["aux"], rank=rank,
+                                      local_rank=local_rank, n_batches=0, device=device, verifier_forward=False, barrier=dist.barrier)
+    split = OnlineSplit(cfg, c["aux"], c["seq_len"], device, n_slots=4, timeout_s=300.0)
+    topo = split.topo
+    trainer = None
+    last = {}
+    if not topo.is_verifier:
+        d2t, t2d = bench_inputs.load_vocab_maps(root)
+        model_class = SpeculatorModel.registry[c["algo"]]
+        model = model_class.from_training_args(
+            TransformerLayerConfig(**draft_layer_config(c)), t2d=t2d, d2t=d2t, draft_vocab_size=draft_vocab,
+            verifier_name_or_path=os.path.join(root, "verifier"), target_layer_ids=c["aux"], **c["model"],
+        )
+        model.load_state_dict(bench_inputs.seeded_draft_init({k: tuple(v.shape) for k, v in model.state_dict().items()}), strict=False)
+        train_kwargs, _ = model_class.get_trainer_kwargs(**c["train"])
+        trainer = Trainer(model, TrainerConfig(
+            lr=1e-4, num_epochs=1, save_path=os.path.join(tempfile.gettempdir(), "sb200_bench_unused"), train_call_kwargs=train_kwargs,
+            optimizer="adamw", scheduler_type="none", log_freq=10**9, fsdp_shard=topo.n_trainer > 1, use_cuda_graph=not args.no_graph,
+            device=str(device), process_group=split.trainer_group,
+        ), SyntheticLoader([], 0))
+        trainer.model.train()
+
+    def step(batch):
+        handle = trainer.train_step_async(batch)
+        if last.get("pending") is not None:
+            last["loss"] = last["pending"].value()  # every step's loss reaches the host (read one step late)
+        last["pending"] = handle
+
+    count0 = ops.native().launch_count() if cuda else 0
+    sampler = ClockSampler(local_rank)
+    if rank == 0 and cuda:
+        sampler.start()
+    region_ms = [split.run(step, args.warmup if r == 0 else 0, args.steps) for r in range(args.regions)]
+    clocks = sampler.stop() if (rank == 0 and cuda) else {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+    if trainer is not None and last.get("pending") is not None:
+        last["loss"] = last["pending"].value()
+    launches = int((ops.native().launch_count() - count0) * args.steps / max(1, args.steps * args.regions + args.warmup)) if cuda else 0
+    if cuda:
+        ops.check_gemm_status()
+    loss_t = torch.tensor([last.get("loss") or 0.0, 0.0 if topo.is_verifier else 1.0], dtype=torch.float64, device=device)
+    dist.all_reduce(loss_t)
+    ms = statistics.median(region_ms)
+    tokens = topo.n_trainer * c["seq_len"]
+    value = tokens * args.steps / (ms / 1000.0)
+    if rank == 0:
+        record = {
+            "metric": "PEAGLE online draft-train tokens/s on one box split between verifier and trainer GPUs (device max over ranks)",
+            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if cuda else "fp32",
+            "data": "synthetic (seeded uniform tokens; hidden states computed by the random-init verifier during the run; seeded draft init)",
+            "impl": "ours", "config": dict(config_record(c, world, args.regions), parallelism=f"tp{topo.n_verifier} verifier + dp{topo.n_trainer}-sharded trainer",
+                                            global_batch=topo.n_trainer),
+            "impl_detail": {"verifier": f"TensorParallelVerifier over {topo.n_verifier} GPUs, weights resident", "handoff": "NVLink peer-memory ring, batch built on the trainer GPU",
+                            "optimizer_comm": os.environ.get("SB200_COMM"), "path": "speculators_b200.train.online.OnlineSplit.run / Trainer.train_step_async"},
+            "regions_ms_per_step": spread([m / args.steps for m in region_ms]), "clocks": clocks,
+            "e2e": {"value": value, "unit": "tokens/s", "ms_per_step": ms / args.steps, "h2d_bytes_per_step": 8 * (c["seq_len"] + 1) * topo.n_trainer,
+                    "d2h_bytes_per_step": 4 * topo.n_trainer,
+                    "note": "the timed region is end to end already: token ids are the only host input, hidden states go GPU to GPU, every step's loss is read on the host"},
+            "last_loss": float(loss_t[0] / max(1.0, float(loss_t[1]))), "gpu_launches": launches,
+        }
+        print(json.dumps(record))
+    split.close()
+    maybe_destroy_distributed()
+
+
 def run_ours(args):
+    if resolve_config(args).get("online"):
+        return run_ours_online(args, resolve_config(args))
     import torch
     import torch.distributed as dist
 
@@ -558,6 +662,10 @@ def run_reference(args):
         return
 
     rank, local_rank, world = dist_env()
+    if resolve_config(args).get("online"):
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "the reference's online mode needs a running vLLM server with verifier weights (scripts/launch_vllm.py); none can be started here"}))
+        return
     maybe_setup_distributed()
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)

@@ -1,0 +1,157 @@
+"""Online training on one machine split between verifier GPUs and trainer GPUs.
+
+The reference's online mode is a vLLM server on some GPUs (tensor parallel), the trainer on the
+others, and hidden states travelling server -> store -> trainer dataloader -> CPU collate -> GPU
+(scripts/launch_vllm.py:104-163; src/speculators/train/data.py:220-255;
+docs/user_guide/tutorials/train.md:165-170).  ``OnlineSplit`` is the single-job counterpart: the
+first half of the ranks run the verifier tensor-parallel (``TensorParallelVerifier``), the second
+half train the draft (sharded optimizer among themselves); after every verifier forward one
+verifier rank pushes the auxiliary + last hidden states of a sequence straight into the ring of
+the trainer rank it is meant for (NVLink peer stores, ``hs_connectors/nvlink.py``), and the
+trainer builds its batch from the ring slot on its own device (``RingBatchLoader``).  No hidden
+state touches host memory.
+
+Flow control is the ring itself: the verifier runs at most ``n_slots`` samples ahead of a
+trainer; both sides wait with a bound (``timeout_s``) and raise on expiry.
+"""
+
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from speculators_b200.hs_connectors.nvlink import HiddenStateRing, HiddenStateRingWriter
+from speculators_b200.train.ring_loader import RingBatchLoader
+from speculators_b200.verifier.tp import TensorParallelVerifier
+
+__all__ = ["OnlineSplit", "SplitTopology"]
+
+
+@dataclass
+class SplitTopology:
+    world: int
+    rank: int
+    n_verifier: int
+
+    @property
+    def n_trainer(self) -> int:
+        return self.world - self.n_verifier
+
+    @property
+    def is_verifier(self) -> bool:
+        return self.rank < self.n_verifier
+
+    @property
+    def trainer_index(self) -> int:
+        return self.rank - self.n_verifier
+
+    def pusher_of(self, trainer_index: int) -> int:
+        """Verifier rank that pushes the samples of trainer ``trainer_index`` (every verifier rank holds
+        the complete hidden states after the tensor-parallel forward; the pushes are spread over them)."""
+        return trainer_index % self.n_verifier
+
+
+class OnlineSplit:
+    def __init__(self, verifier_config: dict, aux_layers: list[int], seq_len: int, device: torch.device, *, n_verifier: int | None = None,
+                 n_slots: int = 4, timeout_s: float = 120.0, seed: int = 0, resident: bool = True, sliced_init: bool = True):
+        if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() < 2:
+            raise RuntimeError("OnlineSplit needs at least two ranks (one verifier, one trainer)")
+        world, rank = dist.get_world_size(), dist.get_rank()
+        self.topo = SplitTopology(world, rank, n_verifier if n_verifier is not None else world // 2)
+        t = self.topo
+        self.device, self.seq_len, self.aux_layers, self.timeout_s, self.seed = device, int(seq_len), list(aux_layers), timeout_s, seed
+        self.hidden = int(verifier_config["hidden_size"])
+        self.vocab = int(verifier_config["vocab_size"])
+        # both groups are created by every rank (a collective of the whole job)
+        self.verifier_group = dist.new_group(list(range(t.n_verifier)))
+        self.trainer_group = dist.new_group(list(range(t.n_verifier, world)))
+        width = (len(self.aux_layers) + 1) * self.hidden
+        self.ring = HiddenStateRing(n_slots, self.seq_len + 1, width, device) if not t.is_verifier else None
+        described: list = [None] * world
+        dist.all_gather_object(described, self.ring.describe() if self.ring is not None else None)
+        self.writers: dict[int, HiddenStateRingWriter] = {}
+        self.verifier = None
+        if t.is_verifier:
+            for ti in range(t.n_trainer):
+                if t.pusher_of(ti) == rank:
+                    self.writers[ti] = HiddenStateRingWriter(described[t.n_verifier + ti], device)
+            self.verifier = TensorParallelVerifier(verifier_config, group=self.verifier_group, seed=seed, device=device,
+                                                   dtype=torch.bfloat16 if device.type == "cuda" else torch.float32,
+                                                   resident=resident, sliced_init=sliced_init)
+        self._seq = 0
+
+    # ------------------------------------------------------------------ data
+    def tokens(self, step: int, trainer_index: int) -> torch.Tensor:
+        """The sequence trainer ``trainer_index`` trains on at ``step`` (seeded; ``seq_len + 1`` tokens: the
+        pairing shift consumes one)."""
+        gen = torch.Generator().manual_seed(self.seed * 1_000_003 + step * 1009 + trainer_index)
+        return torch.randint(0, self.vocab, (self.seq_len + 1,), generator=gen)
+
+    # ------------------------------------------------------------------ verifier side
+    def verifier_step(self, step: int) -> None:
+        """Forward of one sequence per trainer rank; the responsible rank pushes each into its ring."""
+        t = self.topo
+        self._seq += 1
+        for ti in range(t.n_trainer):
+            ids = self.tokens(step, ti).to(self.device)
+            out = self.verifier.forward(ids, self.aux_layers)
+            if ti in self.writers:
+                payload = torch.cat([out["hidden_states"], out["verifier_last_hidden_states"]], dim=-1)
+                self.writers[ti].push(self._seq, payload, ids.to(torch.int32), timeout_s=self.timeout_s, check=False)
+
+    def check_verifier(self) -> None:
+        for w in self.writers.values():
+            w.check_status()
+
+    # ------------------------------------------------------------------ trainer side
+    def loader(self, num_steps: int) -> RingBatchLoader:
+        return RingBatchLoader(self.ring, num_steps, self.hidden, self.seq_len, first_seq=1, timeout_s=self.timeout_s)
+
+    # ------------------------------------------------------------------ a run of W + K steps
+    def run(self, trainer_step, warmup: int, steps: int) -> float:
+        """``trainer_step(batch)`` on trainer ranks; returns the K timed steps' milliseconds (max over all
+        ranks: verifier and trainer halves overlap, the slower one sets the pace)."""
+        cuda = self.device.type == "cuda"
+        loader = self.loader(warmup + steps) if not self.topo.is_verifier else None
+
+        def one(step):
+            if self.topo.is_verifier:
+                self.verifier_step(step)
+            else:
+                trainer_step(loader.next_batch())
+
+        for s in range(warmup):
+            one(s)
+        if cuda:
+            torch.cuda.synchronize()
+        dist.barrier()
+        t0 = time.perf_counter()
+        if cuda:
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+        for s in range(steps):
+            one(warmup + s)
+        if cuda:
+            end.record()
+            torch.cuda.synchronize()
+            ms = start.elapsed_time(end)
+        else:
+            ms = (time.perf_counter() - t0) * 1000.0
+        if self.topo.is_verifier:
+            self.check_verifier()
+        t = torch.tensor([ms], dtype=torch.float64, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def close(self) -> None:
+        if dist.is_initialized():
+            if self.device.type == "cuda":
+                torch.cuda.synchronize()
+            dist.barrier()
+        for w in self.writers.values():
+            w.close()
+        if self.ring is not None:
+            self.ring.close()

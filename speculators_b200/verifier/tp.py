@@ -30,7 +30,15 @@ __all__ = ["TensorParallelVerifier"]
 
 
 class TensorParallelVerifier:
-    def __init__(self, config: TransformerLayerConfig | dict, group=None, seed: int = 0, device="cpu", dtype=torch.float32):
+    def __init__(self, config: TransformerLayerConfig | dict, group=None, seed: int = 0, device="cpu", dtype=torch.float32,
+                 resident: bool = False, sliced_init: bool = False):
+        """``resident``: keep every layer's slices on the device after the first forward (a 70B-class
+        verifier over 4 GPUs holds 35 GB per GPU) instead of regenerating them per call.
+        ``sliced_init``: draw each rank's slices directly from a seed of their own instead of
+        slicing the full tensors (``world`` times less work at start-up; the weights then differ
+        from ``RandomVerifier``'s for the same seed, which only matters to tests)."""
+        self.resident, self.sliced_init = bool(resident), bool(sliced_init)
+        self._layers: dict[int, DecoderLayer] = {}
         self.cfg = TransformerLayerConfig.from_any(config)
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -67,17 +75,23 @@ class TensorParallelVerifier:
         return full  # norms: replicated
 
     def _layer(self, idx: int) -> DecoderLayer:
+        if idx in self._layers:
+            return self._layers[idx]
         layer = DecoderLayer(self.local_cfg, idx)
         own = dict(layer.named_parameters())
         with torch.no_grad():
             for j, (name, shape) in enumerate(self._full_shapes):
                 p = own[name]
-                if len(shape) == 2:
+                if len(shape) == 2 and self.sliced_init:
+                    p.data = _seeded(tuple(p.shape), 0.02, ((self.seed * 1000 + idx) * 64 + j) * 16 + self.rank, self.device, self.dtype)
+                elif len(shape) == 2:
                     full = _seeded(shape, 0.02, (self.seed * 1000 + idx) * 64 + j, self.device, self.dtype)
                     p.data = self._slice(name, full).contiguous()
                     del full
                 else:
                     p.data = p.data.to(device=self.device, dtype=self.dtype)
+        if self.resident:
+            self._layers[idx] = layer
         return layer
 
     def _reduce(self, partial: torch.Tensor) -> torch.Tensor:
@@ -95,7 +109,12 @@ class TensorParallelVerifier:
         pos = position_ids.reshape(-1).to(self.device) if position_ids is not None else torch.arange(T, device=self.device)
         lo, hi = causal_document_interval(doc)
         spec = AttnSpec(lo=lo, hi=hi)
-        h = torch.nn.functional.embedding(ids, self.embed_weight())
+        if self.resident:
+            if not hasattr(self, "_embed"):
+                self._embed = self.embed_weight()
+            h = torch.nn.functional.embedding(ids, self._embed)
+        else:
+            h = torch.nn.functional.embedding(ids, self.embed_weight())
         taken: dict[int, torch.Tensor] = {}
         for i in range(int(self.cfg.num_hidden_layers)):
             layer = self._layer(i)
