@@ -319,6 +319,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
 
 
 # --------------------------------------------------------------------------- rmsnorm
+_RMSNORM_MAX_WIDTH = 16384
+
+
 def _rms_norm_ref(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     dt = x.dtype
     xf = x.float()
@@ -358,8 +361,11 @@ class _RMSNormFn(torch.autograd.Function):
 
 
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
-    """RMSNorm over the last dim: ``weight * (x / rms(x))`` with fp32 statistics."""
-    if _use_native(x):
+    """RMSNorm over the last dim: ``weight * (x / rms(x))`` with fp32 statistics.  Rows of up to
+    16384 elements run on the package's kernels (one row per CTA with the row in registers; one row
+    per warp for rows of up to 256); wider rows (the concatenated auxiliary states of a 70B-class
+    verifier: 3 x 8192) use the element-wise formulation."""
+    if _use_native(x) and x.shape[-1] <= _RMSNORM_MAX_WIDTH and x.shape[-1] % 8 == 0:
         return _RMSNormFn.apply(x, weight, eps)
     return _rms_norm_ref(x, weight, eps)
 

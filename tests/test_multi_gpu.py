@@ -210,3 +210,121 @@ def test_moe_expert_parallel_peer_exchange_matches_nccl(tmp_path):
     for r in res:
         assert r["peer"], res
         assert max(r["errs"]) < 3e-2, res
+
+
+# ---- Muon with owned matrices over NCCL, against one GPU that sees both batches ---------------
+def _muon_worker(rank, world, port, out_path):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from speculators_b200.models.layers import Linear
+    from speculators_b200.parallel import EngineConfig, TrainEngine
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            torch.manual_seed(0)
+            self.a, self.b, self.c = Linear(256, 512), Linear(512, 256), Linear(256, 384)
+            self.gain = torch.nn.Parameter(torch.ones(384))
+
+        def forward(self, x):
+            return self.c(torch.tanh(self.b(torch.tanh(self.a(x))))) * self.gain
+
+    def data(step, r):
+        g = torch.Generator().manual_seed(17 * step + r)
+        return torch.randn(128, 256, generator=g).cuda().bfloat16(), torch.randn(128, 384, generator=g).cuda()
+
+    cfg = dict(lr=1e-3, optimizer="muon", muon_lr=0.02, max_grad_norm=1.0, compute_dtype=torch.bfloat16)
+    results = {}
+    for shard in (False, True):
+        net = Net()
+        eng = TrainEngine(net, EngineConfig(**cfg, shard=shard), device=f"cuda:{rank}")
+        for step in range(3):
+            x, y = data(step, rank)
+            eng.zero_grad()
+            ((net(x).float() - y) ** 2).mean().backward()
+            eng.step()
+        results[shard] = {k: v.float().cpu() for k, v in eng.master_state_dict().items()}
+        owners = sorted(set(eng.muon_owner.values()))
+    ok = None
+    if rank == 0:  # one GPU, both batches (mean of the two losses)
+        solo = Net()
+        e1 = TrainEngine(solo, EngineConfig(**cfg, group=dist.new_group([0])), device="cuda:0")
+    else:
+        dist.new_group([0])
+    if rank == 0:
+        for step in range(3):
+            e1.zero_grad()
+            total = 0
+            for r in range(world):
+                x, y = data(step, r)
+                total = total + ((solo(x).float() - y) ** 2).mean() / world
+            total.backward()
+            e1.step()
+        want = {k: v.float().cpu() for k, v in e1.master_state_dict().items()}
+        init = {k: v.detach().float().cpu() for k, v in Net().named_parameters()}
+        ok = {}
+        for shard, got in results.items():
+            worst = 0.0
+            for name, w in want.items():
+                moved = float((w - init[name]).abs().max())
+                worst = max(worst, float((got[name] - w).abs().max()) / max(moved, 1e-9))
+            ok[str(shard)] = worst
+        with open(out_path, "w") as fh:
+            json.dump({"rel_err": ok, "owners": owners}, fh)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_muon_with_owned_matrices_on_two_gpus(tmp_path):
+    _need_two()
+    out = tmp_path / "muon.json"
+    mp.spawn(_muon_worker, args=(2, 29671, str(out)), nprocs=2, join=True)
+    res = json.loads(out.read_text())
+    assert res["owners"] == [0, 1]
+    # bf16 Newton-Schulz on differently reduced gradients: the two-GPU runs stay within a fraction of the distance moved
+    assert res["rel_err"]["False"] < 0.35 and res["rel_err"]["True"] < 0.35, res
+
+
+# ---- online split: verifier on GPU 0 writes hidden states into the trainer's ring on GPU 1 -----
+def _online_worker(rank, world, port, out_path):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", SB200_COMM="nccl")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from speculators_b200.train.online import OnlineSplit
+    from speculators_b200.verifier import RandomVerifier
+
+    cfg = dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=256, intermediate_size=512, num_hidden_layers=4,
+               num_attention_heads=4, num_key_value_heads=2, head_dim=64, vocab_size=512, max_position_embeddings=1024, rms_norm_eps=1e-5,
+               rope_theta=10000.0, hidden_act="silu")
+    aux, T = [1, 2, 3], 96
+    split = OnlineSplit(cfg, aux, T, torch.device("cuda", rank), n_slots=2, timeout_s=60.0, sliced_init=False)
+    seen = []
+    ms = split.run(lambda batch: seen.append({k: v.clone() for k, v in batch.items()}), warmup=1, steps=3)
+    ok = True
+    if not split.topo.is_verifier:  # the same samples through the single-device verifier and the CPU-style pairing
+        ref = RandomVerifier(cfg, seed=0, device="cuda", dtype=torch.bfloat16)
+        for step, batch in enumerate(seen):
+            ids = split.tokens(step, 0).cuda()
+            out = ref.forward(ids, aux)
+            n = T
+            ok = ok and torch.equal(batch["input_ids"][0, :n], ids[1 : n + 1])
+            ok = ok and torch.allclose(batch["hidden_states"][0, :n].float(), out["hidden_states"][:n].float(), atol=3e-2, rtol=3e-2)
+            ok = ok and torch.allclose(batch["verifier_last_hidden_states"][0, :n].float(), out["verifier_last_hidden_states"][1 : n + 1].float(), atol=3e-2, rtol=3e-2)
+            ok = ok and bool((batch["position_ids"][0, :n] == torch.arange(1, n + 1, device="cuda")).all())
+        ok = bool(ok) and len(seen) == 4
+    flags = [None] * world
+    dist.all_gather_object(flags, bool(ok))
+    if rank == 0:
+        with open(out_path, "w") as fh:
+            json.dump({"ok": flags, "ms": ms}, fh)
+    split.close()
+    dist.destroy_process_group()
+
+
+def test_online_split_hands_hidden_states_gpu_to_gpu(tmp_path):
+    _need_two()
+    out = tmp_path / "online.json"
+    mp.spawn(_online_worker, args=(2, 29681, str(out)), nprocs=2, join=True)
+    res = json.loads(out.read_text())
+    assert res["ok"] == [True, True] and res["ms"] > 0
