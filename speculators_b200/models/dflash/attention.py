@@ -40,7 +40,8 @@ def anchor_block_attn_spec(document_ids, anchor_positions, block_size: int, slid
     if causal_in_block:
         q_slot = slot.repeat(n)
         extra = torch.where(slot[None, :] <= q_slot[:, None], extra, torch.full_like(extra, -1))
-    return AttnSpec(lo=lo.to(torch.int32), hi=hi.to(torch.int32), extra_idx=extra.contiguous())
+    return AttnSpec(lo=lo.to(torch.int32), hi=hi.to(torch.int32), extra_idx=extra.contiguous(), extra_block=int(block_size),
+                    extra_block_causal=bool(causal_in_block))
 
 
 def dense_anchor_block_mask(document_ids, total_seq_len: int, anchor_positions, block_size: int,

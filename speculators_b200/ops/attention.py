@@ -35,6 +35,12 @@ class AttnSpec:
     lo: torch.Tensor  # int32 [Tq]   first allowed context key
     hi: torch.Tensor  # int32 [Tq]   one past the last allowed context key
     extra_idx: torch.Tensor | None = None  # int32 [Tq, E] rows of the extra K/V, -1 = none
+    # When the extra keys have block structure - row r lists exactly the rows of its own block of `extra_block` rows
+    # of the extra K/V (with `extra_block_causal`: only those up to r) - the builder says so here: the tcgen05
+    # kernels then run a query tile's extras as one block-diagonal key tile on the tensor cores instead of
+    # gathering them row by row.  `extra_idx` stays authoritative for every other path.
+    extra_block: int = 0
+    extra_block_causal: bool = False
 
     def dense(self, n_ctx: int, n_extra: int = 0) -> torch.Tensor:
         """Boolean [Tq, n_ctx + n_extra] mask equivalent to this spec (tests/oracle)."""

@@ -20,6 +20,7 @@ from speculators_b200.ops.attention import AttnSpec, masked_attention_reference
 _SUPPORTED_HEAD_DIMS = (64, 128, 256)
 FWD_IMPL = os.environ.get("SB200_ATTN_FWD", "tc")
 BWD_IMPL = os.environ.get("SB200_ATTN_BWD", "tc")
+BLOCK_EXTRAS = os.environ.get("SB200_ATTN_BLOCK_EXTRAS", "1") != "0"  # 0: anchored blocks through the per-row extra-key path
 
 
 def _rows_ok(t: torch.Tensor) -> torch.Tensor:
@@ -33,18 +34,25 @@ def _rows_ok(t: torch.Tensor) -> torch.Tensor:
 
 class _MaskedAttentionFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, lo, hi, k_ext, v_ext, ext_idx, scale):
+    def forward(ctx, q, k, v, lo, hi, k_ext, v_ext, ext_idx, scale, ext_block, ext_causal):
         q, k, v = _rows_ok(q), _rows_ok(k), _rows_ok(v)
         if ext_idx is not None:
             k_ext, v_ext = _rows_ok(k_ext), _rows_ok(v_ext)
-        if FWD_IMPL == "tc" and q.shape[2] == 128:
+        tc_fwd = FWD_IMPL == "tc" and q.shape[2] == 128
+        tc_bwd = BWD_IMPL == "tc" and q.shape[2] == 128
+        # block-structured extras run as one more key tile on the tensor cores; both directions must take
+        # that route (or neither), since the forward's statistics feed the backward either way
+        block = int(ext_block) if (ext_idx is not None and tc_fwd and tc_bwd and BLOCK_EXTRAS and ext_block and 128 % int(ext_block) == 0
+                                   and k_ext.shape[0] >= q.shape[0]) else 0
+        if tc_fwd:
             from speculators_b200.ops import gemm_status
 
-            out, lse2 = _ext.lib().attn_fwd_tc(q, k, v, lo, hi, k_ext, v_ext, ext_idx, scale, gemm_status(q.device))
+            out, lse2 = _ext.lib().attn_fwd_tc(q, k, v, lo, hi, k_ext, v_ext, ext_idx, scale, gemm_status(q.device), block, bool(ext_causal))
         else:
             out, lse2 = _ext.lib().attn_fwd(q, k, v, lo, hi, k_ext, v_ext, ext_idx, scale)
         ctx.save_for_backward(q, k, v, out, lse2, lo, hi, k_ext, v_ext, ext_idx)
         ctx.scale = scale
+        ctx.block = (block, bool(ext_causal))
         return out
 
     @staticmethod
@@ -57,10 +65,10 @@ class _MaskedAttentionFn(torch.autograd.Function):
         else:
             impl, status = 0, None
         dq, dk, dv, dke, dve = _ext.lib().attn_bwd(
-            _rows_ok(dout), q, k, v, out, lse2, lo, hi, k_ext, v_ext, ext_idx, ctx.scale, impl, status)
+            _rows_ok(dout), q, k, v, out, lse2, lo, hi, k_ext, v_ext, ext_idx, ctx.scale, impl, status, ctx.block[0], ctx.block[1])
         if ext_idx is not None:
-            return dq, dk, dv, None, None, dke.to(q.dtype), dve.to(q.dtype), None, None
-        return dq, dk, dv, None, None, None, None, None, None
+            return dq, dk, dv, None, None, dke.to(q.dtype), dve.to(q.dtype), None, None, None, None
+        return dq, dk, dv, None, None, None, None, None, None, None, None
 
 
 def masked_attention_cuda(q, k_ctx, v_ctx, spec: AttnSpec, k_ext=None, v_ext=None, scale=None):
@@ -73,4 +81,5 @@ def masked_attention_cuda(q, k_ctx, v_ctx, spec: AttnSpec, k_ext=None, v_ext=Non
         ext_idx = k_ext = v_ext = None
     else:
         ext_idx = ext_idx.to(torch.int32).contiguous()
-    return _MaskedAttentionFn.apply(q, k_ctx, v_ctx, spec.lo, spec.hi, k_ext, v_ext, ext_idx, scale)
+    block = getattr(spec, "extra_block", 0) if ext_idx is not None else 0
+    return _MaskedAttentionFn.apply(q, k_ctx, v_ctx, spec.lo, spec.hi, k_ext, v_ext, ext_idx, scale, block, bool(getattr(spec, "extra_block_causal", False)))

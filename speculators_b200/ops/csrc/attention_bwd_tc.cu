@@ -61,6 +61,23 @@ __device__ __forceinline__ void mma_ts(uint32_t tmem_d, uint32_t a0, uint32_t a1
   }
 }
 
+// like tc::store_rows64_f32, adding into global memory (several query heads of a group meet on one KV head)
+__device__ __forceinline__ void atomic_rows64_f32(unsigned char* stage, const float (&vals)[64], float* gbase, int64_t row_stride, int rows_valid,
+                                                  int lane) {
+  __syncwarp();
+  float4* mine = reinterpret_cast<float4*>(stage + lane * 256);
+#pragma unroll
+  for (int c = 0; c < 16; ++c) mine[c ^ (lane & 7)] = make_float4(vals[c * 4], vals[c * 4 + 1], vals[c * 4 + 2], vals[c * 4 + 3]);
+  __syncwarp();
+#pragma unroll
+  for (int it = 0; it < 16; ++it) {
+    const int r = it * 2 + (lane >> 4), pc = lane & 15;
+    const float4 v = reinterpret_cast<const float4*>(stage + r * 256)[pc ^ (r & 7)];
+    if (r < rows_valid) atomicAdd(reinterpret_cast<float4*>(gbase + (int64_t)r * row_stride + pc * 4), v);
+  }
+  __syncwarp();
+}
+
 __device__ __forceinline__ void pair_barrier(int quarter) { asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory"); }
 
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
@@ -96,6 +113,7 @@ attn_delta_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* _
 __global__ void __launch_bounds__(THREADS, 1)
 attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                       const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                      const __grid_constant__ CUtensorMap map_ke, const __grid_constant__ CUtensorMap map_ve,
                       const AttnParams p, int* status) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -169,7 +187,10 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   __syncthreads();
   const int c_lo = s_range[0], c_hi = s_range[1];
   const int j0 = c_hi > c_lo ? c_lo / BN : 0;
-  const int n_tiles = c_hi > c_lo ? (c_hi + BN - 1) / BN - j0 : 0;
+  const int n_ctx = c_hi > c_lo ? (c_hi + BN - 1) / BN - j0 : 0;
+  // block-structured extras: the query tile's own 128 extra rows are one more key tile (the last); their dK / dV
+  // come from the dK/dV kernel's pass over the extra tensors, not from here
+  const int n_tiles = n_ctx + (p.ext_block > 0 ? 1 : 0);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -181,18 +202,21 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       tma_load_2d(smem_addr(do_s) + SUB_BYTES, &map_do, qb, h * HD + 64, q0);
       for (int t = 0; t < n_tiles; ++t) {
         const int st = t % 3;
-        const int key0 = (j0 + t) * BN;
+        const bool ext = t >= n_ctx;
+        const int key0 = ext ? q0 : (j0 + t) * BN;
+        const CUtensorMap* mk = ext ? &map_ke : &map_k;
+        const CUtensorMap* mv = ext ? &map_ve : &map_v;
         if (!mbar_wait(smem_addr(&bar_k_empty[st]), ((t / 3) & 1) ^ 1, status, kTimeoutDqProducer)) break;
         const uint32_t kfull = smem_addr(&bar_k_full[st]);
         mbar_expect_tx(kfull, TILE_BYTES);
         const uint32_t ka = smem_addr(k_s + st * TILE_BYTES), va = smem_addr(v_s);
-        tma_load_2d(ka, &map_k, kfull, kvh * HD, key0);
-        tma_load_2d(ka + SUB_BYTES, &map_k, kfull, kvh * HD + 64, key0);
+        tma_load_2d(ka, mk, kfull, kvh * HD, key0);
+        tma_load_2d(ka + SUB_BYTES, mk, kfull, kvh * HD + 64, key0);
         if (!mbar_wait(smem_addr(&bar_v_empty), (t & 1) ^ 1, status, kTimeoutDqProducer)) break;
         const uint32_t vfull = smem_addr(&bar_v_full);
         mbar_expect_tx(vfull, TILE_BYTES);
-        tma_load_2d(va, &map_v, vfull, kvh * HD, key0);
-        tma_load_2d(va + SUB_BYTES, &map_v, vfull, kvh * HD + 64, key0);
+        tma_load_2d(va, mv, vfull, kvh * HD, key0);
+        tma_load_2d(va + SUB_BYTES, mv, vfull, kvh * HD + 64, key0);
       }
     }
   } else if (warp == 1) {
@@ -238,6 +262,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const int lo = row_ok ? p.lo[row] : 0x7fffffff;
     const int hi = row_ok ? min(p.hi[row], p.Tc) : 0;
     const float lse = row_ok ? p.lse2[(int64_t)h * p.Tq + row] : INFINITY;
+    const int elo = (row_ok && p.ext_block > 0) ? (row / p.ext_block) * p.ext_block : 0x7fffffff;  // interval in rows of the extra tensors
+    const int ehi = (row_ok && p.ext_block > 0) ? min(p.ext_causal ? row + 1 : elo + p.ext_block, p.Te) : 0;
     const float sc = p.scale * kLog2e;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const int colh = half * 64;
@@ -261,8 +287,10 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       if (ok) ok = mbar_wait(smem_addr(&bar_sdp_full), t & 1, status, kTimeoutDqCompute);
       ok = __all_sync(0xffffffffu, ok);
       fence_after_sync();
-      const int key0 = (j0 + t) * BN + colh;
-      const bool full = __all_sync(0xffffffffu, lo <= key0 && hi >= key0 + 64);
+      const bool ext = t >= n_ctx;
+      const int key0 = (ext ? q0 : (j0 + t) * BN) + colh;
+      const int tlo = ext ? elo : lo, thi = ext ? ehi : hi;
+      const bool full = __all_sync(0xffffffffu, tlo <= key0 && thi >= key0 + 64);
       uint32_t pk[32];
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
@@ -281,8 +309,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
           float pr1 = ex2(fmaf(__uint_as_float(s[i + 1]), sc, -lse));
           if (!full) {
             const int key = key0 + c * 32 + i;
-            if (key < lo || key >= hi) pr0 = 0.f;
-            if (key + 1 < lo || key + 1 >= hi) pr1 = 0.f;
+            if (key < tlo || key >= thi) pr0 = 0.f;
+            if (key + 1 < tlo || key + 1 >= thi) pr1 = 0.f;
           }
           const float ds0 = pr0 * (__uint_as_float(d[i]) - delta);
           const float ds1 = pr1 * (__uint_as_float(d[i + 1]) - delta);
@@ -419,7 +447,10 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 __global__ void __launch_bounds__(THREADS, 1)
 attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                        const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                       const AttnParams p, int n_range_tiles, int* status) {
+                       const AttnParams p, int n_range_tiles, int ext_mode, int* status) {
+  // ext_mode (block-structured extras): the key tiles are tiles of the extra K / V tensors (the caller passes their
+  // tensor maps as map_k / map_v); key tile j is seen by query tile j alone, under the block mask, and the result is
+  // added (fp32 atomics over the query heads of a group) into dke / dve.
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* k_s = smem;
@@ -477,8 +508,9 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       qmax = max(qmax, p.tile_qmax[rt]);
     }
   }
-  const int i0 = qmax > qmin ? qmin / BM : 0;
-  const int n_tiles = qmax > qmin ? (qmax + BM - 1) / BM - i0 : 0;
+  const int i0 = ext_mode ? j : (qmax > qmin ? qmin / BM : 0);
+  const int n_tiles = ext_mode ? (j * BM < p.Tq ? 1 : 0) : (qmax > qmin ? (qmax + BM - 1) / BM - i0 : 0);
+  const int n_keys = ext_mode ? p.Te : p.Tc;
 
   if (warp == 0) {
     if (lane == 0 && n_tiles > 0) {
@@ -565,8 +597,12 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         ld_b = in ? p.delta[(int64_t)h * p.Tq + r] : 0.f;
         ld_full = 1;
       } else {
-        const int l = in ? p.lo[r] : 0x7fffffff;
-        const int hgh = in ? min(p.hi[r], p.Tc) : 0;
+        int l = in ? p.lo[r] : 0x7fffffff;
+        int hgh = in ? min(p.hi[r], p.Tc) : 0;
+        if (ext_mode) {  // the query's interval in rows of the extra tensors
+          l = in ? (r / p.ext_block) * p.ext_block : 0x7fffffff;
+          hgh = in ? min(p.ext_causal ? r + 1 : l + p.ext_block, p.Te) : 0;
+        }
         ld_a = __int_as_float(l);
         ld_b = __int_as_float(hgh);
         ld_full = (l <= key_base && hgh >= key_base + BN) ? 1u : 0u;
@@ -694,7 +730,9 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         unsigned char* stage = q_s + (warp - 2) * 16384;
         const int warp_key0 = key_base + quarter * 32;
         const int64_t off0 = ((int64_t)warp_key0 * p.nkv + kvh) * HD + colh;
-        if (p.dkv_part != nullptr)
+        if (ext_mode)
+          atomic_rows64_f32(stage, acc, (which ? p.dve : p.dke) + off0, (int64_t)p.nkv * HD, n_keys - warp_key0, lane);
+        else if (p.dkv_part != nullptr)
           store_rows64_f32(stage, acc, p.dkv_part + (int64_t)(h - kvh * group) * 2 * plane + which * plane + off0, (int64_t)p.nkv * HD,
                            p.Tc - warp_key0, lane);
         else
@@ -727,6 +765,14 @@ int launch_attn_bwd_tc(const AttnParams& p, int* tile_qmin, int* tile_qmax, int*
   if (rc) return rc;
   rc = tc::make_map_bf16(&map_v, p.v, p.Tc, (int64_t)p.nkv * HD, p.v_rs, BN);
   if (rc) return rc;
+  CUtensorMap map_ke = map_k, map_ve = map_v;
+  if (p.ext_block > 0) {
+    if (p.E != 0 || BM % p.ext_block != 0 || p.ke == nullptr || p.ve == nullptr || p.dke == nullptr || p.dve == nullptr) return -4;
+    rc = tc::make_map_bf16(&map_ke, p.ke, p.Te, (int64_t)p.nkv * HD, p.ke_rs, BN);
+    if (rc) return rc;
+    rc = tc::make_map_bf16(&map_ve, p.ve, p.Te, (int64_t)p.nkv * HD, p.ve_rs, BN);
+    if (rc) return rc;
+  }
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attn_bwd_dq_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -2;
@@ -740,11 +786,16 @@ int launch_attn_bwd_tc(const AttnParams& p, int* tile_qmin, int* tile_qmax, int*
     attn_delta_kernel<<<(int)(blocks < 16 * kNumSM ? blocks : 16 * kNumSM), 256, 0, stream>>>(p.dout, p.out, p.delta, p.Tq, p.nh, p.do_rs, p.o_rs);
   }
   dim3 grid_q(p.nh, (p.Tq + BM - 1) / BM);
-  attn_bwd_dq_tc_kernel<<<grid_q, THREADS, SMEM_BYTES, stream>>>(map_q, map_do, map_k, map_v, p, status);
+  attn_bwd_dq_tc_kernel<<<grid_q, THREADS, SMEM_BYTES, stream>>>(map_q, map_do, map_k, map_v, map_ke, map_ve, p, status);
   rc = launch_kv_tile_range(p, tile_qmin, tile_qmax, stream);
   if (rc) return rc;
   dim3 grid_kv(p.nh, (p.Tc + BN - 1) / BN);
-  attn_bwd_dkv_tc_kernel<<<grid_kv, THREADS, SMEM_BYTES, stream>>>(map_q, map_do, map_k, map_v, p, (p.Tc + kAttnKeyTile - 1) / kAttnKeyTile, status);
+  attn_bwd_dkv_tc_kernel<<<grid_kv, THREADS, SMEM_BYTES, stream>>>(map_q, map_do, map_k, map_v, p, (p.Tc + kAttnKeyTile - 1) / kAttnKeyTile, 0, status);
+  if (p.ext_block > 0) {  // gradients of the extra keys: one key tile per query tile, read from the extra tensors
+    count_launch(1);
+    dim3 grid_ext(p.nh, (p.Te + BN - 1) / BN);
+    attn_bwd_dkv_tc_kernel<<<grid_ext, THREADS, SMEM_BYTES, stream>>>(map_q, map_do, map_ke, map_ve, p, 0, 1, status);
+  }
   if (p.dkv_part != nullptr) {
     rc = launch_dkv_reduce(p, stream);
     if (rc) return rc;

@@ -19,6 +19,12 @@ struct AttnParams {
   __nv_bfloat16* out;
   float* lse2;  // [nh, Tq] log2-domain logsumexp of the scaled scores
   int Tq, Tc, Te, E, nh, nkv;
+  // Block-structured extra keys (tcgen05 kernels): when ext_block = B > 0 the extra keys of query row r are
+  // the rows [B * (r / B), B * (r / B) + B) of the extra K / V tensors (only up to r itself with ext_causal):
+  // the anchored blocks of DFlash / DSpark, whose 16 block keys are shared by the 16 rows of a block.  The 128
+  // extra rows that belong to a 128-row query tile then form one more key tile with a block-diagonal mask and
+  // go through the tensor-core path like any context tile; ext_idx is not read (E must be 0).
+  int ext_block, ext_causal;
   int64_t q_rs, k_rs, v_rs, ke_rs, ve_rs, o_rs;
   float scale;
   // backward only

@@ -43,7 +43,8 @@ enum Status : int { kTimeoutProducer = 31, kTimeoutMma = 32, kTimeoutSoftmax = 3
 
 __global__ void __launch_bounds__(THREADS, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                   const __grid_constant__ CUtensorMap map_v, const AttnParams p, int* status) {
+                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_ke,
+                   const __grid_constant__ CUtensorMap map_ve, const AttnParams p, int* status) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* q_s = smem;                       // 32 KB
@@ -109,7 +110,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   __syncthreads();
   const int c_lo = s_range[0], c_hi = s_range[1];
   const int j0 = c_hi > c_lo ? c_lo / BN : 0;
-  const int n_tiles = c_hi > c_lo ? (c_hi + BN - 1) / BN - j0 : 0;
+  const int n_ctx = c_hi > c_lo ? (c_hi + BN - 1) / BN - j0 : 0;
+  // block-structured extras: the tile's own 128 extra rows are one more key tile (the last one)
+  const int n_tiles = n_ctx + (p.ext_block > 0 ? 1 : 0);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -123,18 +126,21 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       for (int t = 0; t < n_tiles; ++t) {
         const int st = t & 1;
         const uint32_t par = ((t >> 1) & 1) ^ 1;
-        const int key0 = (j0 + t) * BN;
+        const bool ext = t >= n_ctx;
+        const int key0 = ext ? q0 : (j0 + t) * BN;
+        const CUtensorMap* mk = ext ? &map_ke : &map_k;
+        const CUtensorMap* mv = ext ? &map_ve : &map_v;
         if (!mbar_wait(smem_addr(&bar_k_empty[st]), par, status, kTimeoutProducer)) break;
         const uint32_t kfull = smem_addr(&bar_k_full[st]);
         mbar_expect_tx(kfull, TILE_BYTES);
         const uint32_t ka = smem_addr(k_s + st * TILE_BYTES), va = smem_addr(v_s + st * TILE_BYTES);
-        tma_load_2d(ka, &map_k, kfull, kvh * HD, key0);
-        tma_load_2d(ka + SUB_BYTES, &map_k, kfull, kvh * HD + 64, key0);
+        tma_load_2d(ka, mk, kfull, kvh * HD, key0);
+        tma_load_2d(ka + SUB_BYTES, mk, kfull, kvh * HD + 64, key0);
         if (!mbar_wait(smem_addr(&bar_v_empty[st]), par, status, kTimeoutProducer)) break;
         const uint32_t vfull = smem_addr(&bar_v_full[st]);
         mbar_expect_tx(vfull, TILE_BYTES);
-        tma_load_2d(va, &map_v, vfull, kvh * HD, key0);
-        tma_load_2d(va + SUB_BYTES, &map_v, vfull, kvh * HD + 64, key0);
+        tma_load_2d(va, mv, vfull, kvh * HD, key0);
+        tma_load_2d(va + SUB_BYTES, mv, vfull, kvh * HD + 64, key0);
       }
     }
   } else if (warp == 1) {
@@ -197,6 +203,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const bool row_ok = row < p.Tq;
     const int lo = row_ok ? p.lo[row] : 0x7fffffff;
     const int hi = row_ok ? min(p.hi[row], p.Tc) : 0;
+    // block-structured extras: the row's interval in rows of the extra tensors
+    const int elo = (row_ok && p.ext_block > 0) ? (row / p.ext_block) * p.ext_block : 0x7fffffff;
+    const int ehi = (row_ok && p.ext_block > 0) ? min(p.ext_causal ? row + 1 : elo + p.ext_block, p.Te) : 0;
     const float sc = p.scale * kLog2e;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const int colh = half * 64;
@@ -224,20 +233,22 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       ok = __all_sync(0xffffffffu, ok);
       fence_after_sync();
       const uint32_t tmem_s = lane_base + (t & 1) * BN + colh;
-      const int key0 = (j0 + t) * BN + colh;
+      const bool ext = t >= n_ctx;  // the tile of the query tile's own extra rows
+      const int key0 = (ext ? q0 : (j0 + t) * BN) + colh;
+      const int tlo = ext ? elo : lo, thi = ext ? ehi : hi;
       uint32_t r[2][32];
 #pragma unroll
       for (int c = 0; c < 2; ++c) tmem_ld32(tmem_s + c * 32, r[c]);
       tmem_ld_wait();
       // keys that every row of the warp sees need no per-element test
-      const bool full = __all_sync(0xffffffffu, lo <= key0 && hi >= key0 + 64);
+      const bool full = __all_sync(0xffffffffu, tlo <= key0 && thi >= key0 + 64);
       if (!full) {
 #pragma unroll
         for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int key = key0 + c * 32 + i;
-            if (key < lo || key >= hi) r[c][i] = 0xff800000u;  // -inf
+            if (key < tlo || key >= thi) r[c][i] = 0xff800000u;  // -inf
           }
       }
       float cmax[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // independent chains
@@ -415,6 +426,14 @@ int launch_attn_fwd_tc(const AttnParams& p, int* status, cudaStream_t stream) {
   if (rc) return rc;
   rc = tc::make_map_bf16(&map_v, p.v, p.Tc, (int64_t)p.nkv * HD, p.v_rs, BN);
   if (rc) return rc;
+  CUtensorMap map_ke = map_k, map_ve = map_v;
+  if (p.ext_block > 0) {
+    if (p.E != 0 || BM % p.ext_block != 0 || p.ke == nullptr || p.ve == nullptr) return -4;
+    rc = tc::make_map_bf16(&map_ke, p.ke, p.Te, (int64_t)p.nkv * HD, p.ke_rs, BN);
+    if (rc) return rc;
+    rc = tc::make_map_bf16(&map_ve, p.ve, p.Te, (int64_t)p.nkv * HD, p.ve_rs, BN);
+    if (rc) return rc;
+  }
   constexpr int smem_bytes = 5 * TILE_BYTES + 1024;
   static bool configured = false;
   if (!configured) {
@@ -423,7 +442,7 @@ int launch_attn_fwd_tc(const AttnParams& p, int* status, cudaStream_t stream) {
   }
   dim3 grid(p.nh, (p.Tq + BM - 1) / BM);
   count_launch(1);
-  attn_fwd_tc_kernel<<<grid, THREADS, smem_bytes, stream>>>(map_q, map_k, map_v, p, status);
+  attn_fwd_tc_kernel<<<grid, THREADS, smem_bytes, stream>>>(map_q, map_k, map_v, map_ke, map_ve, p, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

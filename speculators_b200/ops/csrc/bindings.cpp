@@ -699,6 +699,20 @@ sb200::AttnParams make_params(const Tensor& q, const Tensor& k, const Tensor& v,
   return p;
 }
 
+// Block-structured extras (tcgen05 kernels): the extra keys of row r are the rows of its block of `block` rows in
+// k_ext / v_ext (only up to r with `causal`); the per-row index list is then not used.
+void use_block_extras(sb200::AttnParams& p, const Tensor& q, int64_t block, bool causal) {
+  if (block <= 0) return;
+  TORCH_CHECK(p.ke != nullptr && p.ve != nullptr, "block-structured extras need k_ext and v_ext");
+  TORCH_CHECK(128 % block == 0, "block-structured extras: the block size must divide 128");
+  TORCH_CHECK(p.Te >= p.Tq, "block-structured extras: k_ext / v_ext hold one row per query row");
+  p.E = 0;
+  p.ext_idx = nullptr;
+  p.ext_block = (int)block;
+  p.ext_causal = causal ? 1 : 0;
+  (void)q;
+}
+
 std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& lo, const Tensor& hi,
                                     const c10::optional<Tensor>& ke, const c10::optional<Tensor>& ve,
                                     const c10::optional<Tensor>& ext_idx, double scale) {
@@ -718,8 +732,10 @@ std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tens
 // non-zero code if a bounded wait in the kernel ran out.
 std::tuple<Tensor, Tensor> attn_fwd_tc(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& lo, const Tensor& hi,
                                        const c10::optional<Tensor>& ke, const c10::optional<Tensor>& ve,
-                                       const c10::optional<Tensor>& ext_idx, double scale, Tensor status) {
+                                       const c10::optional<Tensor>& ext_idx, double scale, Tensor status, int64_t ext_block,
+                                       bool ext_causal) {
   sb200::AttnParams p = make_params(q, k, v, lo, hi, ke, ve, ext_idx, scale);
+  use_block_extras(p, q, ext_block, ext_causal);
   TORCH_CHECK(q.size(2) == 128, "attn_fwd_tc: head_dim must be 128");
   TORCH_CHECK(status.is_cuda() && status.scalar_type() == at::kInt && status.numel() >= 1);
   c10::cuda::CUDAGuard guard(q.device());
@@ -736,9 +752,12 @@ std::tuple<Tensor, Tensor> attn_fwd_tc(const Tensor& q, const Tensor& k, const T
 std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> attn_bwd(
     const Tensor& dout, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out, const Tensor& lse2,
     const Tensor& lo, const Tensor& hi, const c10::optional<Tensor>& ke, const c10::optional<Tensor>& ve,
-    const c10::optional<Tensor>& ext_idx, double scale, int64_t impl, const c10::optional<Tensor>& status) {
+    const c10::optional<Tensor>& ext_idx, double scale, int64_t impl, const c10::optional<Tensor>& status, int64_t ext_block,
+    bool ext_causal) {
   // impl 0: mma.sync kernels; 1: tcgen05 kernels (head_dim 128; `status` receives a code if a bounded wait ran out)
   sb200::AttnParams p = make_params(q, k, v, lo, hi, ke, ve, ext_idx, scale);
+  TORCH_CHECK(ext_block <= 0 || impl == 1, "block-structured extras run on the tcgen05 kernels only");
+  use_block_extras(p, q, ext_block, ext_causal);
   const int64_t hd = q.size(2);
   if (impl == 1) {
     TORCH_CHECK(hd == 128, "attn_bwd: the tcgen05 kernels need head_dim 128");
@@ -754,7 +773,7 @@ std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> attn_bwd(
   Tensor dv = at::empty({k.size(0), k.size(1), hd}, q.options());
   Tensor delta = at::empty({q.size(1), q.size(0)}, lse2.options());
   Tensor dke, dve;
-  if (p.E > 0) {
+  if (p.E > 0 || p.ext_block > 0) {
     dke = at::zeros({p.Te, p.nkv, hd}, lse2.options());
     dve = at::zeros({p.Te, p.nkv, hd}, lse2.options());
     p.dke = dke.data_ptr<float>();

@@ -101,6 +101,29 @@ def op_gemm_wgrad_cublas(a):
     return (lambda: out.addmm_(x.t(), w)), 2.0 * a.m * a.n * a.k, 2.0 * (a.m * a.k + a.n * a.k + 2 * a.m * a.n), dict
 
 
+def _head_inputs(a):
+    T, H, V = a.t, a.hidden, a.vocab
+    hidden, weight, targets = _bf16(T, H, scale=0.7), _bf16(V, H, scale=0.05), _bf16(T, V, scale=3.0)
+    active = torch.ones(T, dtype=torch.bool, device="cuda")
+    return hidden, weight, targets, active, 2.0 * T * V * H, 2.0 * (T * H + V * H + 2 * T * V)
+
+
+def op_lmhead_fused(a):
+    """lm_head GEMM whose epilogue reduces the tiles for the KL loss + the per-row combine kernel."""
+    from speculators_b200 import ops
+
+    hidden, weight, targets, active, flops, nbytes = _head_inputs(a)
+    return _no_grad(lambda: ops.lm_head_loss_raw("kl_div", hidden, weight, targets, 0, a.t, active)), flops, nbytes, dict
+
+
+def op_lmhead_unfused(a):
+    """The same result as two steps: lm_head GEMM, then the row-loss forward kernel over logits and targets."""
+    from speculators_b200 import ops
+
+    hidden, weight, targets, active, flops, nbytes = _head_inputs(a)
+    return _no_grad(lambda: ops.fused_row_loss_raw("kl_div", ops.linear(hidden, weight), targets, 0, a.t, active)), flops, nbytes + 2.0 * 2 * a.t * a.vocab, dict
+
+
 def _attn_inputs(a):
     from speculators_b200.models.eagle3.attention import ttt_attn_spec
 
@@ -173,7 +196,7 @@ def op_adamw(a):
 
 
 OPS = {"gemm": op_gemm, "gemm_cublas": op_gemm_cublas, "gemm_dgrad": op_gemm_dgrad, "gemm_dgrad_cublas": op_gemm_dgrad_cublas,
-       "gemm_wgrad": op_gemm_wgrad, "gemm_wgrad_cublas": op_gemm_wgrad_cublas, "attn_fwd": op_attn_fwd, "attn_bwd": op_attn_bwd, "loss": op_loss,
+       "gemm_wgrad": op_gemm_wgrad, "gemm_wgrad_cublas": op_gemm_wgrad_cublas, "lmhead_fused": op_lmhead_fused, "lmhead_unfused": op_lmhead_unfused, "attn_fwd": op_attn_fwd, "attn_bwd": op_attn_bwd, "loss": op_loss,
        "rmsnorm": op_rmsnorm, "rmsnorm_bwd": op_rmsnorm_bwd, "adamw": op_adamw}
 
 

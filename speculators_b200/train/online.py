@@ -82,6 +82,7 @@ class OnlineSplit:
                                                    dtype=torch.bfloat16 if device.type == "cuda" else torch.float32,
                                                    resident=resident, sliced_init=sliced_init)
         self._seq = 0
+        self._loader: RingBatchLoader | None = None  # one per trainer rank for the whole job: sequence numbers run on across ``run`` calls
 
     # ------------------------------------------------------------------ data
     def tokens(self, step: int, trainer_index: int) -> torch.Tensor:
@@ -115,7 +116,9 @@ class OnlineSplit:
         """``trainer_step(batch)`` on trainer ranks; returns the K timed steps' milliseconds (max over all
         ranks: verifier and trainer halves overlap, the slower one sets the pace)."""
         cuda = self.device.type == "cuda"
-        loader = self.loader(warmup + steps) if not self.topo.is_verifier else None
+        if self._loader is None and not self.topo.is_verifier:
+            self._loader = self.loader(2**31)
+        loader = self._loader
 
         def one(step):
             if self.topo.is_verifier:

@@ -154,3 +154,45 @@ def test_tc_kernels_with_separate_query_and_context_lengths_and_many_extras():
         tol = 3e-2 * float(b.grad.abs().max()) + 2e-2
         assert float((a.grad.float() - b.grad).abs().max()) < tol, name
     check_gemm_status()
+
+
+@pytest.mark.parametrize("window,non_causal", [(None, False), (64, False), (64, True)])
+@pytest.mark.parametrize("n_anchors,block", [(24, 16), (21, 8), (8, 16)])
+def test_anchored_blocks_run_their_block_keys_as_a_tile(window, non_causal, n_anchors, block):
+    """DFlash / DSpark masks: the block keys of a query tile as one block-diagonal key tile on the tensor
+    cores (forward, dQ, and the extra keys' dK / dV) against the fp32 oracle and the per-row extra-key path."""
+    from speculators_b200.models.dflash.attention import anchor_block_attn_spec
+    from speculators_b200.ops import attention_cuda
+
+    torch.manual_seed(0)
+    T, nh, nkv, hd = 300, 4, 2, 128
+    doc = _docs(T, "multi_pad").to(DEV)
+    real = torch.nonzero(doc != -1).squeeze(1)
+    anchors = real[torch.randperm(real.numel(), device=DEV)[:n_anchors]].sort().values
+    spec = anchor_block_attn_spec(doc, anchors, block, window, non_causal)
+    assert spec.extra_block == block and spec.extra_block_causal == (window is not None and not non_causal)
+    Tq = n_anchors * block
+    base = [torch.randn(n, h, hd, device=DEV).to(torch.bfloat16) for n, h in ((Tq, nh), (T, nkv), (T, nkv), (Tq, nkv), (Tq, nkv))]
+    dout = torch.randn(Tq, nh, hd, device=DEV).to(torch.bfloat16)
+
+    def run(block_path):
+        attention_cuda.BLOCK_EXTRAS = block_path
+        try:
+            leaves = [t.detach().clone().requires_grad_() for t in base]
+            out = masked_attention(leaves[0], leaves[1], leaves[2], spec, leaves[3], leaves[4])
+            out.backward(dout)
+            return out, [t.grad for t in leaves]
+        finally:
+            attention_cuda.BLOCK_EXTRAS = True
+
+    out_b, g_b = run(True)
+    out_r, g_r = run(False)
+    ref_leaves = [t.detach().float().requires_grad_() for t in base]
+    ref = masked_attention_reference(ref_leaves[0], ref_leaves[1], ref_leaves[2], spec, ref_leaves[3], ref_leaves[4])
+    ref.backward(dout.float())
+    torch.testing.assert_close(out_b.float(), ref, atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(out_b.float(), out_r.float(), atol=2e-2, rtol=2e-2)
+    for name, a, b, c in zip(["dq", "dk", "dv", "dk_ext", "dv_ext"], g_b, ref_leaves, g_r):
+        tol = 3e-2 * float(b.grad.abs().max()) + 2e-2
+        assert float((a.float() - b.grad).abs().max()) < tol, (name, float((a.float() - b.grad).abs().max()), tol)
+        assert float((a.float() - c.float()).abs().max()) < tol, (name, "vs per-row path")
