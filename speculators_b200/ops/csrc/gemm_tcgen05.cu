@@ -60,7 +60,7 @@ enum Status : int { kOk = kStatusOk, kTimeoutProducer = 1, kTimeoutMma = 2, kTim
 // floats at partial[(row * tiles_n + tile_n) * kStatWords].  A second kernel merges a row's
 // records.  The statistics are taken from the bf16-rounded logits, i.e. from the values the
 // backward pass reads back.
-constexpr int kStatWords = 12;  // m_d z_d best_d idx_d | m_t z_t A best_t | idx_t - - -
+constexpr int kStatWords = 12;  // m_d z_d best_d idx_d | m_t z_t A best_t | idx_t - - -   (one record per row and 128-column half tile)
 struct RowStatsOut {
   const __nv_bfloat16* targets;  // nullptr: plain GEMM
   int64_t ldt;
@@ -151,6 +151,7 @@ __device__ __forceinline__ void st32(__nv_bfloat16* ptr, const bf16x8& a, const 
 
 // Epilogue of one thread: TMEM lane `taddr` (its 256 fp32 columns) -> row `row`, columns
 // n0 .. n0+255 of C, with the configured epilogue.
+template <int W>
 __device__ __forceinline__ void store_accumulator(const Params& p, uint32_t taddr, int row, int n0, int row_end, bool zero) {
   __nv_bfloat16* crow = p.c + (int64_t)row * p.ldc + n0;
   const __nv_bfloat16* rrow = p.residual ? p.residual + (int64_t)row * p.ldr + n0 : nullptr;
@@ -158,7 +159,7 @@ __device__ __forceinline__ void store_accumulator(const Params& p, uint32_t tadd
                       (p.epilogue != kAddResidual || (((p.ldr & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0)));
   const bool wide_ok = vec_ok && ((p.ldc & 15) == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 31) == 0);
 #pragma unroll 1
-  for (int c = 0; c < BN / 32; ++c) {
+  for (int c = 0; c < W / 32; ++c) {
     uint32_t r[32];
     tmem_ld32(taddr + c * 32, r);
     tmem_ld_wait();
@@ -214,36 +215,40 @@ __device__ __forceinline__ void store_accumulator(const Params& p, uint32_t tadd
 // thread waits for the accumulator, so the loads' latency is spent while the tensor core still
 // works on the tile.  With a short contraction (weight gradients: K = tokens of one step) the
 // time per tile is otherwise set by eight dependent load round trips per thread.
+template <int W>
 struct RowPrefetch {
-  uint4 v[BN / 8];
+  uint4 v[W / 8];
   bool tile_ok;  // the same for every thread of the warp: selects the epilogue (its tcgen05.ld is warp-collective)
   bool valid;    // this thread's row exists (its loads were issued, its stores may be)
 };
 
+template <int W>
 __device__ __forceinline__ bool tile_reads_vectorised(const Params& p, int n0) {
-  if (p.epilogue == kStore || n0 + BN > p.N || (p.ldc & 7) || (reinterpret_cast<uintptr_t>(p.c) & 15)) return false;
+  if (p.epilogue == kStore || n0 + W > p.N || (p.ldc & 7) || (reinterpret_cast<uintptr_t>(p.c) & 15)) return false;
   if (p.epilogue == kAddResidual && ((p.ldr & 7) || (reinterpret_cast<uintptr_t>(p.residual) & 15))) return false;
   return true;
 }
 
-__device__ __forceinline__ void prefetch_addend(const Params& p, int row, int n0, int row_end, RowPrefetch& pre) {
-  pre.tile_ok = tile_reads_vectorised(p, n0);
+template <int W>
+__device__ __forceinline__ void prefetch_addend(const Params& p, int row, int n0, int row_end, RowPrefetch<W>& pre) {
+  pre.tile_ok = tile_reads_vectorised<W>(p, n0);
   pre.valid = pre.tile_ok && row < row_end;
   if (pre.valid) {
     const __nv_bfloat16* src = p.epilogue == kAccumulate ? p.c + (int64_t)row * p.ldc + n0 : p.residual + (int64_t)row * p.ldr + n0;
 #pragma unroll
-    for (int i = 0; i < BN / 8; ++i) pre.v[i] = __ldg(reinterpret_cast<const uint4*>(src) + i);
+    for (int i = 0; i < W / 8; ++i) pre.v[i] = __ldg(reinterpret_cast<const uint4*>(src) + i);
   }
 }
 
 // Same result as store_accumulator for a tile whose addend rows are already in registers.  Called
 // by whole warps (pre.tile_ok); a thread whose row does not exist takes part in the tensor-memory
 // loads and stores nothing.
-__device__ __forceinline__ void store_accumulator_prefetched(const Params& p, uint32_t taddr, int row, int n0, const RowPrefetch& pre, bool zero) {
+template <int W>
+__device__ __forceinline__ void store_accumulator_prefetched(const Params& p, uint32_t taddr, int row, int n0, const RowPrefetch<W>& pre, bool zero) {
   __nv_bfloat16* crow = p.c + (int64_t)row * p.ldc + n0;
   const bool wide_ok = ((p.ldc & 15) == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 31) == 0);
 #pragma unroll
-  for (int c = 0; c < BN / 32; ++c) {
+  for (int c = 0; c < W / 32; ++c) {
     uint32_t r[32];
     tmem_ld32(taddr + c * 32, r);
     tmem_ld_wait();
@@ -268,26 +273,28 @@ __device__ __forceinline__ void store_accumulator_prefetched(const Params& p, ui
 }
 
 // ---- logits tile + row statistics ------------------------------------------------------------
-__device__ __forceinline__ void prefetch_targets(const Params& p, int row, int n0, RowPrefetch& pre) {
+template <int W>
+__device__ __forceinline__ void prefetch_targets(const Params& p, int row, int n0, RowPrefetch<W>& pre) {
   const int trow = row + p.rs.shift;
   pre.tile_ok = true;
   pre.valid = row < p.M && trow < p.rs.t_rows;
   const __nv_bfloat16* src = p.rs.targets + (int64_t)trow * p.rs.ldt + n0;
 #pragma unroll
-  for (int i = 0; i < BN / 8; ++i) {
+  for (int i = 0; i < W / 8; ++i) {
     if (pre.valid && n0 + i * 8 + 8 <= p.N) pre.v[i] = __ldg(reinterpret_cast<const uint4*>(src) + i);
     else pre.v[i] = make_uint4(0u, 0u, 0u, 0u);
   }
 }
 
 // Requires N % 8 == 0, ldc % 8 == 0 and 16-byte aligned C / target rows (checked on the host).
-__device__ __forceinline__ void store_accumulator_with_stats(const Params& p, uint32_t taddr, int row, int n0, int tile_n, int tiles_n,
-                                                             const RowPrefetch& pre) {
+template <int W>
+__device__ __forceinline__ void store_accumulator_with_stats(const Params& p, uint32_t taddr, int row, int n0, int record, int records_per_row,
+                                                             const RowPrefetch<W>& pre) {
   __nv_bfloat16* crow = p.c + (int64_t)row * p.ldc + n0;
   RowStats sd{-INFINITY, 0.f, -INFINITY, 0x7fffffff}, st{-INFINITY, 0.f, -INFINITY, 0x7fffffff};
   float A = 0.f;
 #pragma unroll
-  for (int c = 0; c < BN / 32; ++c) {
+  for (int c = 0; c < W / 32; ++c) {
     uint32_t r[32];
     tmem_ld32(taddr + c * 32, r);
     tmem_ld_wait();
@@ -308,7 +315,7 @@ __device__ __forceinline__ void store_accumulator_with_stats(const Params& p, ui
     }
   }
   if (pre.valid) {
-    float4* out = reinterpret_cast<float4*>(p.rs.partial + ((int64_t)row * tiles_n + tile_n) * kStatWords);
+    float4* out = reinterpret_cast<float4*>(p.rs.partial + ((int64_t)row * records_per_row + record) * kStatWords);
     out[0] = make_float4(sd.m, sd.z, sd.best, __int_as_float(sd.best_idx));
     out[1] = make_float4(st.m, st.z, A, st.best);
     out[2] = make_float4(__int_as_float(st.best_idx), 0.f, 0.f, 0.f);
@@ -402,14 +409,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
       const int acc = local & 1;
       const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
-      RowPrefetch pre;
-      prefetch_addend(p, m0 + quarter * 32 + lane, n0, p.M, pre);
+      RowPrefetch<BN> pre;
+      prefetch_addend<BN>(p, m0 + quarter * 32 + lane, n0, p.M, pre);
       ok = mbar_wait(smem_addr(&bar_acc_full[acc]), (local >> 1) & 1, p.status, kTimeoutEpilogue);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       fence_after_sync();
-      if (pre.tile_ok) store_accumulator_prefetched(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, m0 + quarter * 32 + lane, n0, pre, false);
-      else store_accumulator(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, m0 + quarter * 32 + lane, n0, p.M, false);
+      if (pre.tile_ok) store_accumulator_prefetched<BN>(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, m0 + quarter * 32 + lane, n0, pre, false);
+      else store_accumulator<BN>(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN, m0 + quarter * 32 + lane, n0, p.M, false);
       fence_before_sync();
       mbar_arrive(smem_addr(&bar_acc_empty[acc]));
     }
@@ -435,9 +442,13 @@ constexpr int P_HALF = 128;                                    // rows of A and 
 constexpr int P_A_BYTES = P_HALF * BK * 2, P_B_BYTES = P_HALF * BK * 2, P_SUB_BYTES = P_A_BYTES + P_B_BYTES;
 constexpr int P_TILE_M = 2 * P_HALF, P_TILE_N = 2 * P_HALF;
 constexpr int P_RING_BYTES = 6 * P_SUB_BYTES;
+// The pair kernel runs eight epilogue warps: warps w and w + 4 reach the same 32 TMEM lanes (rows) and take 128 of the
+// tile's 256 columns each, so two warps per scheduler share the epilogue's instruction stream (with four warps the row
+// statistics of the lm_head epilogue, and the addend of short-contraction weight gradients, set the pace of the tile).
+constexpr int P_THREADS = 320, P_EPI_COLS = 128;
 
 template <int KSUB, bool A_MN = false, bool B_MN = false>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -465,7 +476,7 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_addr(&bar_acc_full[a]), 1);
-      mbar_init(smem_addr(&bar_acc_empty[a]), 256);  // the epilogue threads of both CTAs (used in the leader only)
+      mbar_init(smem_addr(&bar_acc_empty[a]), 512);  // the epilogue threads of both CTAs (used in the leader only)
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -548,28 +559,29 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
-    const int quarter = warp & 3;
+    // ------------------------------------------------------------------ epilogue (warps 2..9, both CTAs)
+    const int quarter = warp & 3;         // TMEM lanes 32 * quarter .. + 31
+    const int chalf = (warp - 2) >> 2;    // columns 128 * chalf .. + 127 of the tile
     const uint32_t acc_empty_leader[2] = {map_to_cta(smem_addr(&bar_acc_empty[0]), 0), map_to_cta(smem_addr(&bar_acc_empty[1]), 0)};
     bool ok = true;
     int local = 0;
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
       const int acc = local & 1;
       const TileInfo ti = decode_tile<B_MN>(p, tile, tiles_m, tiles_n, num_kb, (int)rank);
-      const int row = ti.c_row0 + quarter * 32 + lane, n0 = ti.n0;
+      const int row = ti.c_row0 + quarter * 32 + lane, n0 = ti.n0 + chalf * P_EPI_COLS;
       const bool zero = ti.num_kb == 0;
-      RowPrefetch pre;
+      RowPrefetch<P_EPI_COLS> pre;
       const bool with_stats = p.rs.targets != nullptr;
-      if (with_stats) prefetch_targets(p, row, n0, pre);
-      else prefetch_addend(p, row, n0, ti.row_end, pre);
+      if (with_stats) prefetch_targets<P_EPI_COLS>(p, row, n0, pre);
+      else prefetch_addend<P_EPI_COLS>(p, row, n0, ti.row_end, pre);
       ok = mbar_wait(smem_addr(&bar_acc_full[acc]), (local >> 1) & 1, p.status, kTimeoutEpilogue);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       fence_after_sync();
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
-      if (with_stats) store_accumulator_with_stats(p, taddr, row, n0, ti.tile_n, tiles_n, pre);
-      else if (pre.tile_ok) store_accumulator_prefetched(p, taddr, row, n0, pre, zero);
-      else store_accumulator(p, taddr, row, n0, ti.row_end, zero);
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + chalf * P_EPI_COLS;
+      if (with_stats) store_accumulator_with_stats<P_EPI_COLS>(p, taddr, row, n0, ti.tile_n * 2 + chalf, tiles_n * 2, pre);
+      else if (pre.tile_ok) store_accumulator_prefetched<P_EPI_COLS>(p, taddr, row, n0, pre, zero);
+      else store_accumulator<P_EPI_COLS>(p, taddr, row, n0, ti.row_end, zero);
       fence_before_sync();
       mbar_arrive_cluster(acc_empty_leader[acc]);
     }
@@ -645,11 +657,11 @@ static int launch_gemm_impl(const void* a, const void* b, void* c, const void* r
     // grouped: the number of tiles is known on the device only; every pair looks for work
     const int tiles = grp != nullptr ? max_pairs : ((M + P_TILE_M - 1) / P_TILE_M) * ((N + P_TILE_N - 1) / P_TILE_N);
     const int grid = 2 * (tiles < max_pairs ? tiles : max_pairs);
-    if (a_mn && b_mn) gemm_tn_2cta_kernel<2, true, true><<<grid, THREADS, smem2, stream>>>(map_a, map_b, p);
-    else if (a_mn) gemm_tn_2cta_kernel<2, true, false><<<grid, THREADS, smem2, stream>>>(map_a, map_b, p);
-    else if (b_mn) gemm_tn_2cta_kernel<2, false, true><<<grid, THREADS, smem2, stream>>>(map_a, map_b, p);
-    else if (variant == 3) gemm_tn_2cta_kernel<2><<<grid, THREADS, smem2, stream>>>(map_a, map_b, p);
-    else gemm_tn_2cta_kernel<1><<<grid, THREADS, smem2, stream>>>(map_a, map_b, p);
+    if (a_mn && b_mn) gemm_tn_2cta_kernel<2, true, true><<<grid, P_THREADS, smem2, stream>>>(map_a, map_b, p);
+    else if (a_mn) gemm_tn_2cta_kernel<2, true, false><<<grid, P_THREADS, smem2, stream>>>(map_a, map_b, p);
+    else if (b_mn) gemm_tn_2cta_kernel<2, false, true><<<grid, P_THREADS, smem2, stream>>>(map_a, map_b, p);
+    else if (variant == 3) gemm_tn_2cta_kernel<2><<<grid, P_THREADS, smem2, stream>>>(map_a, map_b, p);
+    else gemm_tn_2cta_kernel<1><<<grid, P_THREADS, smem2, stream>>>(map_a, map_b, p);
     return cudaGetLastError() == cudaSuccess ? 0 : -3;
   }
   static bool configured = false;
@@ -711,7 +723,8 @@ int launch_gemm_grouped(const void* a, const void* b, void* c, int M, int N, int
 
 // ---- lm_head product fused with the row loss (KL divergence / cross-entropy on the argmax) -----
 int lmhead_stat_words() { return tc::kStatWords; }
-int lmhead_tiles_n(int N) { return (N + tc::P_TILE_N - 1) / tc::P_TILE_N; }
+// records per logits row: two per 256-column tile (one per 128-column epilogue half)
+int lmhead_tiles_n(int N) { return 2 * ((N + tc::P_TILE_N - 1) / tc::P_TILE_N); }
 
 // logits[M,N] = x[M,K] * w[N,K]^T (stored, bf16) and, per (row, 256-column tile), the statistics of the logits
 // row and of targets[row + shift] over those columns into partial[M, tiles_n, kStatWords].
