@@ -605,11 +605,14 @@ FUSED_HEAD_OPS = ("kl_div", "ce")
 def lm_head_loss_raw(op: str, hidden: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor, shift: int, rows: int, active):
     """Per-row loss between ``(hidden @ weight.T)[r]`` and ``targets[r + shift]`` for ``r < rows``
     plus both argmaxes (int32), like ``fused_row_loss_raw`` on the product; ``None`` when the
-    fused head does not apply (other loss, other dtype / layout, switched off with
-    ``SB200_FUSED_HEAD=0``) and the caller should form the logits itself."""
+    fused head does not apply (other loss, other dtype / layout, not switched on) and the caller
+    should form the logits itself.  Opt-in (``SB200_FUSED_HEAD=1``): at 2048 x 32000 x 4096 the
+    fused kernel measured 0.466 ms against 0.443 ms for the GEMM followed by the row-loss
+    kernel (its statistics epilogue holds the tensor pipe at 70 % active against 88 % for the
+    plain store epilogue), so the two-kernel form is the default."""
     import os
 
-    if (op not in FUSED_HEAD_OPS or not _own_gemm_enabled() or os.environ.get("SB200_FUSED_HEAD", "1") == "0"
+    if (op not in FUSED_HEAD_OPS or not _own_gemm_enabled() or os.environ.get("SB200_FUSED_HEAD", "0") != "1"
             or not (_gemm_operand_ok(hidden) and _gemm_operand_ok(weight) and _gemm_operand_ok(targets))
             or weight.shape[0] % 8 or hidden.shape[0] <= 128):
         return None

@@ -112,6 +112,9 @@ def op_lmhead_fused(a):
     """lm_head GEMM whose epilogue reduces the tiles for the KL loss + the per-row combine kernel."""
     from speculators_b200 import ops
 
+    import os
+
+    os.environ["SB200_FUSED_HEAD"] = "1"
     hidden, weight, targets, active, flops, nbytes = _head_inputs(a)
     return _no_grad(lambda: ops.lm_head_loss_raw("kl_div", hidden, weight, targets, 0, a.t, active)), flops, nbytes, dict
 

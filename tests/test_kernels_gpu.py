@@ -202,10 +202,11 @@ def test_token_cross_entropy_fwd_bwd(T, V):
 
 @pytest.mark.parametrize("op", ["kl_div", "ce"])
 @pytest.mark.parametrize("T,H,V,shift", [(300, 256, 1024, 0), (520, 192, 1000, 2), (2048, 512, 32000, 1), (257, 136, 264, 0)])
-def test_lm_head_fused_with_row_loss(op, T, H, V, shift):
+def test_lm_head_fused_with_row_loss(op, T, H, V, shift, monkeypatch):
     """``lm_head_loss_raw`` (head GEMM whose epilogue reduces the tiles for the loss) against the
     head GEMM followed by the row-loss kernel, and against the fp32 formula: row losses, both
     argmaxes, the gradient of the hidden states; inactive rows and zero upstream rows included."""
+    monkeypatch.setenv("SB200_FUSED_HEAD", "1")
     torch.manual_seed(0)
     hidden = (torch.randn(T, H, device=DEV) * 0.7).to(torch.bfloat16).requires_grad_()
     weight = (torch.randn(V, H, device=DEV) * 0.2).to(torch.bfloat16)
@@ -237,7 +238,8 @@ def test_lm_head_fused_with_row_loss(op, T, H, V, shift):
     assert (loss[~active] == 0).all() and (am_d[~active] == -1).all() and (am_t[~active] == -2).all()
 
 
-def test_lm_head_fused_saturated_rows():
+def test_lm_head_fused_saturated_rows(monkeypatch):
+    monkeypatch.setenv("SB200_FUSED_HEAD", "1")
     T, H, V = 256, 128, 512
     hidden = torch.zeros(T, H, device=DEV, dtype=torch.bfloat16)
     hidden[:, 0] = 1.0
