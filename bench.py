@@ -341,7 +341,7 @@ def run_ours_online(args, c):
     torch.manual_seed(0)
     root = bench_inputs.ensure_inputs(cfg, inputs_tag(c, device.type), seq_len=c["seq_len"], draft_vocab=draft_vocab, layer_ids=c["aux"], rank=rank,
                                       local_rank=local_rank, n_batches=0, device=device, verifier_forward=False, barrier=dist.barrier)
-    split = OnlineSplit(cfg, c["aux"], c["seq_len"], device, n_slots=4, timeout_s=300.0)
+    split = OnlineSplit(cfg, c["aux"], c["seq_len"], device, n_slots=4, timeout_s=60.0)
     topo = split.topo
     trainer = None
     last = {}
