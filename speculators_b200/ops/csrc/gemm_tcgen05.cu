@@ -108,12 +108,20 @@ struct TileInfo {
   int tile_n;      // column-tile index (row statistics)
 };
 
+constexpr int kBandRows = 8;
+
 template <bool B_MN>
 __device__ __forceinline__ TileInfo decode_tile(const Params& p, int tile, int tiles_m, int tiles_n, int num_kb, int rank) {
   TileInfo t;
   if (p.grp.mode == kGroupNone) {
-    const int m0 = (tile % tiles_m) * 256 + rank * 128;
-    t.tile_n = tile / tiles_m;
+    // Tiles run down a band of kBandRows tile rows, column after column, then the next band: the
+    // CTA pairs working at the same time cover a near-square patch of C (8 x 9 tiles on 74 pairs),
+    // so a wave touches about 17 operand panels instead of 75 and a tall output (a weight
+    // gradient of a wide layer) no longer re-reads its whole A operand once per tile column.
+    const int band = tile / (kBandRows * tiles_n), first = band * kBandRows;
+    const int rows = min(kBandRows, tiles_m - first), local = tile - band * kBandRows * tiles_n;
+    const int m0 = (first + local % rows) * 256 + rank * 128;
+    t.tile_n = local / rows;
     t.n0 = t.tile_n * 256;
     t.a_m = m0; t.a_k0 = 0; t.b_n = t.n0 + rank * 128; t.b_k0 = 0; t.num_kb = num_kb; t.c_row0 = m0; t.row_end = p.M;
   } else if (p.grp.mode == kGroupRows) {

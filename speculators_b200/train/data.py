@@ -1,24 +1,33 @@
 """Datasets and the packing collate function.
 
-``ArrowDataset`` reads a preprocessed Hugging Face dataset (``input_ids``,
-``loss_mask``, ``seq_len`` [, ``messages``]) and pairs each row with verifier
-hidden states from a ``HiddenStatesTransfer``: cached, or generated on the fly by a
-verifier server (``on_missing``: generate | skip | warn | raise; ``on_generate``:
-cache | delete).  Stored hidden states are ``[seq, layers, H]``: the last layer slot
-is the verifier's final hidden state, the others are concatenated into the aux
-input (src/speculators/train/data.py:146-304).
+Three pieces, each usable on its own:
 
-``CollateFn`` packs the samples of a batch into one ``[1, max_len, ...]`` row
-(zero padded, hidden states cast to the training dtype), clips lengths at
-``max_len`` and emits ``document_ids`` (0, 1, ... per sample, -1 for padding);
-a batch with no usable sample becomes one empty sample so every rank still steps
-(:306-393).
+* ``RowWindow``: which rows of the preprocessed dataset a split owns, and the file index a
+  row's hidden states are stored under (the index in the whole dataset, so train and
+  validation share one hidden-state directory).
+* ``HiddenStateResolver``: where a row's verifier hidden states come from: the cache of a
+  ``HiddenStatesTransfer``, or a verifier server asked on the fly, governed by two policies
+  (``on_missing``: generate | skip | warn | raise; ``on_generate``: cache | delete).
+* ``ArrowDataset``: a Hugging Face dataset on disk (``input_ids``, ``loss_mask``, ``seq_len``
+  [, ``messages``]) joined with the resolver.  Stored hidden states are ``[seq, layers, H]``:
+  the last layer slot is the verifier's final hidden state, the others are concatenated into
+  the draft's auxiliary input.
+
+``CollateFn`` packs the samples of a batch into one ``[1, max_len, ...]`` row: it first plans
+how many positions each sample contributes (clipping at ``max_len``), then fills every key from
+that plan (zero padded, hidden states cast to the training dtype) and derives ``document_ids``
+(0, 1, ... per sample, -1 for padding) from the same plan.  A batch with no usable sample
+becomes one empty sample so every rank still steps.
+
+Behaviour follows src/speculators/train/data.py:146-393 of the reference (dataset row format,
+policies, warning texts, collate output keys).
 """
 
 from __future__ import annotations
 
 import warnings
 from collections.abc import Callable, Sequence
+from dataclasses import dataclass
 from os import PathLike
 from pathlib import Path
 from typing import Any, Literal
@@ -34,18 +43,20 @@ from speculators_b200.hs_connectors import FileTransfer, HiddenStatesTransfer
 
 BatchType = dict[str, Any]
 
-__all__ = ["ArrowDataset", "BaseDataset", "BatchType", "CollateFn", "build_client_item", "create_empty_sample", "split_hidden_state_layers"]
+__all__ = ["ArrowDataset", "BaseDataset", "BatchType", "CollateFn", "HiddenStateResolver", "RowWindow", "build_client_item",
+           "create_empty_sample", "split_hidden_state_layers"]
 
 
+# ---------------------------------------------------------------------------------------------
+# sample-level helpers
+# ---------------------------------------------------------------------------------------------
 def create_empty_sample(hidden_size: int, num_target_layers: int = 3, dtype: torch.dtype = torch.bfloat16) -> BatchType:
-    return {
-        "hidden_states": torch.empty(0, num_target_layers * hidden_size, dtype=dtype),
-        "input_ids": torch.empty(0, dtype=torch.long),
-        "verifier_last_hidden_states": torch.empty(0, hidden_size, dtype=dtype),
-        "loss_mask": torch.empty(0, dtype=torch.bool),
-        "lengths": torch.tensor([0], dtype=torch.long),
-        "position_ids": torch.arange(0, dtype=torch.long),
-    }
+    """A sample of zero tokens with the key set and trailing shapes of a real one."""
+    widths = {"hidden_states": num_target_layers * hidden_size, "verifier_last_hidden_states": hidden_size}
+    sample: BatchType = {k: torch.empty(0, w, dtype=dtype) for k, w in widths.items()}
+    sample.update(input_ids=torch.empty(0, dtype=torch.long), loss_mask=torch.empty(0, dtype=torch.bool),
+                  lengths=torch.zeros(1, dtype=torch.long), position_ids=torch.empty(0, dtype=torch.long))
+    return sample
 
 
 def build_client_item(dataset_item: dict) -> ClientItem:
@@ -66,24 +77,127 @@ def split_hidden_state_layers(stored: torch.Tensor) -> tuple[torch.Tensor, torch
     return stored[:, :-1].flatten(1), stored[:, -1]
 
 
+# ---------------------------------------------------------------------------------------------
+# which rows a split owns
+# ---------------------------------------------------------------------------------------------
+@dataclass(frozen=True)
+class RowWindow:
+    """Rows ``[start, stop)`` of a dataset of ``total`` rows."""
+
+    start: int
+    stop: int
+    total: int
+
+    @classmethod
+    def of(cls, total: int, train_ratio: float, split: str) -> "RowWindow":
+        if not 0.0 < train_ratio <= 1.0:
+            raise ValueError(f"train_ratio must be in (0.0, 1.0], got {train_ratio}")
+        if split == "val" and train_ratio == 1.0:
+            raise ValueError("train_ratio=1.0 leaves no validation split")
+        cut = int(total * train_ratio)
+        window = cls(0, cut, total) if split == "train" else cls(cut, total, total)
+        if len(window) <= 0:
+            raise ValueError(f"{split} split is empty (dataset has {total} rows, train_ratio={train_ratio} gives split_idx={cut})")
+        return window
+
+    def __len__(self) -> int:
+        return self.stop - self.start
+
+    def file_index(self, index: int) -> int:
+        """Index in the whole dataset (the name the hidden-state cache stores the row under)."""
+        return int(index) + self.start
+
+
+# ---------------------------------------------------------------------------------------------
+# where hidden states come from
+# ---------------------------------------------------------------------------------------------
+class HiddenStateResolver:
+    """Cached hidden states of a row, or freshly generated ones, or ``None`` - by policy.
+
+    The verifier server is contacted on first use only (a dataset that finds every row cached
+    never opens a connection); the model name the server reports must equal an explicitly
+    requested one."""
+
+    def __init__(self, transfer: HiddenStatesTransfer, endpoint: str, on_missing: str, on_generate: str, model: str | None,
+                 request_timeout: float | None, max_retries: int):
+        if on_missing not in ("generate", "skip", "warn", "raise"):
+            raise ValueError(f"on_missing must be generate, skip, warn or raise, got {on_missing!r}")
+        if on_generate not in ("cache", "delete"):
+            raise ValueError(f"on_generate must be cache or delete, got {on_generate!r}")
+        self.transfer, self.endpoint, self.on_missing, self.on_generate = transfer, endpoint, on_missing, on_generate
+        self.model, self.request_timeout, self.max_retries = model, request_timeout, max_retries
+        self.client = None
+
+    # -- server ---------------------------------------------------------------------------------
+    def connect(self) -> None:
+        import openai
+
+        self.client = openai.OpenAI(base_url=self.endpoint, api_key="EMPTY", max_retries=0)
+        served = self.client.models.list().data[0].id
+        if self.model and self.model != served:
+            raise ValueError(
+                f"An explicit model name was passed ({self.model}) which doesn't match found model_id {served}. "
+                "Please make sure --endpoint is set to the correct vllm instance."
+            )
+        self.model = served
+        self.transfer.setup()
+
+    def generate(self, index: int, file_index: int, row: dict) -> dict[str, torch.Tensor] | None:
+        """Ask the server for ``row``'s hidden states, verify them against its token ids, then keep
+        or drop the server-side copy.  Any failure costs the sample, not the epoch."""
+        try:
+            if self.client is None:
+                self.connect()
+            handle = generate_hidden_states(self.client, self.model, build_client_item(row), timeout=self.request_timeout,
+                                            max_retries=self.max_retries, kv_transfer_params=self.transfer.request_params())
+            loaded = self.transfer.get_generated(handle)
+            if loaded is None:
+                raise ValueError(f"Failed to load hidden states for handle {handle}")
+            check_hidden_states(loaded, row["input_ids"].tolist())
+            (self.transfer.cache(handle, file_index) if self.on_generate == "cache" else self.transfer.delete(handle))
+            return loaded
+        except Exception as err:  # noqa: BLE001 - a failed sample must not kill the epoch
+            warnings.warn(f"Failed to load/cache hidden states for sample {index}: {err}", stacklevel=1)
+            return None
+
+    # -- policy ---------------------------------------------------------------------------------
+    def resolve(self, index: int, file_index: int, row_of: Callable[[], dict]) -> dict[str, torch.Tensor] | None:
+        loaded = self.transfer.get_cached(file_index)
+        if loaded is not None:
+            return loaded
+        if self.on_missing == "generate":
+            return self.generate(index, file_index, row_of())
+        if self.on_missing == "raise":
+            raise RuntimeError(f"Failed to load hidden states for sample {index}.")
+        if self.on_missing == "warn":
+            warnings.warn(f"Failed to load hidden states for sample {index}. Skipping...", stacklevel=1)
+        return None
+
+
+# ---------------------------------------------------------------------------------------------
+# datasets
+# ---------------------------------------------------------------------------------------------
 class BaseDataset(Dataset):
+    """Sample = raw tensors + ``lengths`` / ``position_ids`` (+ ``transform``).  Subclasses give
+    ``sample_lengths()`` (token counts used by the packing sampler) and ``load(index)`` (the raw
+    tensors of a row, or ``None`` to drop it)."""
+
     def __init__(self, max_len: int, transform=None, hidden_states_dtype=torch.bfloat16):
         self.max_len, self.transform, self.hidden_states_dtype = max_len, transform, hidden_states_dtype
-        self.approx_lengths = self._compute_approx_lengths()
+        self.approx_lengths = self.sample_lengths()
 
-    def _compute_approx_lengths(self):
+    def sample_lengths(self) -> list[int]:
         raise NotImplementedError
 
-    def _get_raw_data(self, index):
+    def load(self, index: int) -> BatchType | None:
         raise NotImplementedError
 
     def __getitem__(self, index) -> BatchType | None:
-        data = self._get_raw_data(index)
+        data = self.load(index)
         if data is None:
             return None
         n = data["input_ids"].shape[0]
-        data["lengths"] = torch.tensor([n], dtype=torch.long)
-        data["position_ids"] = torch.arange(n, dtype=torch.long)
+        data.update(lengths=torch.tensor([n], dtype=torch.long), position_ids=torch.arange(n, dtype=torch.long))
         return self.transform(data) if self.transform else data
 
 
@@ -95,95 +209,52 @@ class ArrowDataset(BaseDataset):
                  request_timeout: float | None = DEFAULT_REQUEST_TIMEOUT, max_retries: int = DEFAULT_MAX_RETRIES):
         from datasets import load_from_disk
 
-        data = load_from_disk(str(datapath))
-        if not 0.0 < train_ratio <= 1.0:
-            raise ValueError(f"train_ratio must be in (0.0, 1.0], got {train_ratio}")
-        if split == "val" and train_ratio == 1.0:
-            raise ValueError("train_ratio=1.0 leaves no validation split")
-        cut = int(len(data) * train_ratio)
-        start, stop = (0, cut) if split == "train" else (cut, len(data))
-        if start >= stop:
-            raise ValueError(f"{split} split is empty (dataset has {len(data)} rows, train_ratio={train_ratio} gives split_idx={cut})")
-        self.start_file_idx = start
-        # rows are converted to tensors here rather than through the datasets "torch"
-        # formatter, which drags in optional torchvision video readers
-        self.data = data.select(range(start, stop)).with_format(None)
-        self.transfer = transfer or FileTransfer(Path(datapath) / "hidden_states")
-        self.vllm_endpoint, self.on_missing, self.on_generate = vllm_endpoint, on_missing, on_generate
-        self.client = None
-        self.model, self.request_timeout, self.max_retries = model, request_timeout, max_retries
+        table = load_from_disk(str(datapath))
+        self.window = RowWindow.of(len(table), train_ratio, split)
+        # plain python rows (tensors are made in ``row``): the datasets "torch" formatter
+        # drags in optional torchvision video readers
+        self.data = table.select(range(self.window.start, self.window.stop)).with_format(None)
+        self.resolver = HiddenStateResolver(transfer or FileTransfer(Path(datapath) / "hidden_states"), vllm_endpoint, on_missing,
+                                            on_generate, model, request_timeout, max_retries)
         super().__init__(max_len, transform, hidden_states_dtype)
 
+    # names other parts of the package (and users' scripts) read
+    start_file_idx = property(lambda self: self.window.start)
+    transfer = property(lambda self: self.resolver.transfer)
+
     def __len__(self) -> int:
-        return len(self.data)
+        return len(self.window)
 
-    def _map_to_file_idx(self, index: int) -> int:
-        return index + self.start_file_idx
-
-    def _compute_approx_lengths(self) -> list[int]:
+    def sample_lengths(self) -> list[int]:
         return [int(v) for v in self.data["seq_len"]]
 
-    def _row(self, index: int) -> dict:
-        row = dict(self.data[int(index)])
-        row["input_ids"] = torch.as_tensor(row["input_ids"], dtype=torch.long)
-        row["loss_mask"] = torch.as_tensor(row["loss_mask"])
-        return row
+    def row(self, index: int) -> dict:
+        r = dict(self.data[int(index)])
+        r["input_ids"] = torch.as_tensor(r["input_ids"], dtype=torch.long)
+        r["loss_mask"] = torch.as_tensor(r["loss_mask"])
+        return r
 
-    def _setup_client(self) -> None:
-        import openai
+    def load(self, index: int) -> BatchType | None:
+        cached_row: list[dict] = []
 
-        self.client = openai.OpenAI(base_url=self.vllm_endpoint, api_key="EMPTY", max_retries=0)
-        served = self.client.models.list().data[0].id
-        if self.model and self.model != served:
-            raise ValueError(
-                f"An explicit model name was passed ({self.model}) which doesn't match found model_id {served}. "
-                "Please make sure --endpoint is set to the correct vllm instance."
-            )
-        self.model = served
-        self.transfer.setup()
+        def row_of() -> dict:
+            if not cached_row:
+                cached_row.append(self.row(index))
+            return cached_row[0]
 
-    def _maybe_generate_hs(self, index: int) -> dict[str, torch.Tensor] | None:
-        if self.client is None:
-            self._setup_client()
-        row = self._row(index)
-        try:
-            handle = generate_hidden_states(self.client, self.model, build_client_item(row), timeout=self.request_timeout,
-                                            max_retries=self.max_retries, kv_transfer_params=self.transfer.request_params())
-            loaded = self.transfer.get_generated(handle)
-            if loaded is None:
-                raise ValueError(f"Failed to load hidden states for handle {handle}")
-            check_hidden_states(loaded, row["input_ids"].tolist())
-            if self.on_generate == "cache":
-                self.transfer.cache(handle, self._map_to_file_idx(index))
-            else:
-                self.transfer.delete(handle)
-        except Exception as err:  # noqa: BLE001 - a failed sample must not kill the epoch
-            warnings.warn(f"Failed to load/cache hidden states for sample {index}: {err}", stacklevel=1)
-            return None
-        return loaded
-
-    def _get_raw_data(self, index):
-        loaded = self.transfer.get_cached(self._map_to_file_idx(index))
-        if loaded is None:
-            if self.on_missing == "generate":
-                loaded = self._maybe_generate_hs(index)
-            elif self.on_missing == "skip":
-                return None
-            elif self.on_missing == "warn":
-                warnings.warn(f"Failed to load hidden states for sample {index}. Skipping...", stacklevel=1)
-                return None
-            else:
-                raise RuntimeError(f"Failed to load hidden states for sample {index}.")
+        loaded = self.resolver.resolve(index, self.window.file_index(index), row_of)
         if loaded is None:
             return None
-        row = self._row(index)
-        if not torch.equal(loaded["token_ids"].long(), row["input_ids"]):
+        if not torch.equal(loaded["token_ids"].long(), row_of()["input_ids"]):
             warnings.warn(f"Loaded token ids for index {index} don't match the dataset's input ids", stacklevel=1)
             return None
         aux, last = split_hidden_state_layers(loaded["hidden_states"])
-        return {"hidden_states": aux, "input_ids": loaded["token_ids"], "verifier_last_hidden_states": last, "loss_mask": row["loss_mask"]}
+        return {"hidden_states": aux, "input_ids": loaded["token_ids"], "verifier_last_hidden_states": last, "loss_mask": row_of()["loss_mask"]}
 
 
+# ---------------------------------------------------------------------------------------------
+# packing
+# ---------------------------------------------------------------------------------------------
 class CollateFn:
     """Picklable (usable with spawned DataLoader workers)."""
 
@@ -192,37 +263,32 @@ class CollateFn:
         self.max_len, self.hidden_size, self.num_target_layers = max_len, hidden_size, num_target_layers
         self.dtype, self.preprocess = dtype, preprocess
 
+    def plan(self, lengths: Sequence[int]) -> list[tuple[int, int, int]]:
+        """``(sample, offset in the packed row, positions taken)`` for the samples that fit;
+        the one that crosses ``max_len`` is clipped and ends the row."""
+        placed, used = [], 0
+        for i, n in enumerate(lengths):
+            take = min(int(n), self.max_len - used)
+            placed.append((i, used, take))
+            used += take
+            if used >= self.max_len:
+                break
+        return placed
+
     def __call__(self, batch: Sequence[BatchType | None]) -> BatchType:
-        pre = self.preprocess
-        samples = [pre(b) if pre else b for b in batch if b is not None]
-        if not samples:
-            empty = create_empty_sample(self.hidden_size, self.num_target_layers, dtype=self.dtype)
-            samples = [pre(empty) if pre else empty]
-        max_len = self.max_len
+        pre = self.preprocess if self.preprocess is not None else (lambda s: s)
+        samples = [pre(b) for b in batch if b is not None] or [pre(create_empty_sample(self.hidden_size, self.num_target_layers, dtype=self.dtype))]
+        placed = self.plan([int(s["lengths"].sum()) for s in samples])
         out: BatchType = {}
         for key, first in samples[0].items():
             if key == "lengths":
                 continue
-            dtype = self.dtype if "hidden_states" in key else first.dtype
-            buf = torch.zeros((max_len, *first.shape[1:]), dtype=dtype)
-            filled = 0
-            for s in samples:
-                take = min(s[key].shape[0], max_len - filled)
-                buf[filled : filled + take] = s[key][:take]
-                filled += take
-                if filled == max_len:
-                    break
-            out[key] = buf.unsqueeze(0)
-        lengths: list[int] = []
-        used = 0
-        for n in torch.cat([s["lengths"] for s in samples]).tolist():
-            if used + n >= max_len:
-                lengths.append(max_len - used)
-                used = max_len
-                break
-            lengths.append(n)
-            used += n
-        doc = torch.full((max_len,), -1, dtype=torch.long)
-        doc[:used] = torch.repeat_interleave(torch.arange(len(lengths)), torch.tensor(lengths, dtype=torch.long))
+            packed = torch.zeros((self.max_len, *first.shape[1:]), dtype=self.dtype if "hidden_states" in key else first.dtype)
+            for i, at, take in placed:
+                packed[at : at + take] = samples[i][key][:take]
+            out[key] = packed.unsqueeze(0)
+        doc = torch.full((self.max_len,), -1, dtype=torch.long)
+        for i, at, take in placed:
+            doc[at : at + take] = i
         out["document_ids"] = doc.unsqueeze(0)
         return out
