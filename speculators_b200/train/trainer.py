@@ -380,6 +380,8 @@ class Trainer:
         use_graph = cfg.use_cuda_graph if cfg.use_cuda_graph is not None else self.device_type == "cuda"
         # only models whose forward has fixed shapes and no host synchronisation can be replayed
         use_graph = use_graph and bool(getattr(self.model, "cuda_graph_safe", False))
+        if use_graph and hasattr(self.model, "graph_safe_with"):
+            use_graph = bool(self.model.graph_safe_with(dict(cfg.train_call_kwargs or {})))
         if os.environ.get("SB200_DISABLE_CUDA_GRAPH") == "1":
             use_graph = False
         self._graphed = None
