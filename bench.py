@@ -341,7 +341,8 @@ def run_ours_online(args, c):
     torch.manual_seed(0)
     root = bench_inputs.ensure_inputs(cfg, inputs_tag(c, device.type), seq_len=c["seq_len"], draft_vocab=draft_vocab, layer_ids=c["aux"], rank=rank,
                                       local_rank=local_rank, n_batches=0, device=device, verifier_forward=False, barrier=dist.barrier)
-    split = OnlineSplit(cfg, c["aux"], c["seq_len"], device, n_slots=4, timeout_s=60.0)
+    # the verifier runs seq_len tokens per sample (a multiple of the GEMM tile); the pairing shift leaves seq_len - 1 trained positions
+    split = OnlineSplit(cfg, c["aux"], c["seq_len"], device, n_slots=4, timeout_s=60.0, sample_tokens=c["seq_len"])
     topo = split.topo
     trainer = None
     last = {}
@@ -381,7 +382,7 @@ def run_ours_online(args, c):
     loss_t = torch.tensor([last.get("loss") or 0.0, 0.0 if topo.is_verifier else 1.0], dtype=torch.float64, device=device)
     dist.all_reduce(loss_t)
     ms = statistics.median(region_ms)
-    tokens = topo.n_trainer * c["seq_len"]
+    tokens = topo.n_trainer * (c["seq_len"] - 1)
     value = tokens * args.steps / (ms / 1000.0)
     if rank == 0:
         record = {
@@ -391,10 +392,12 @@ def run_ours_online(args, c):
             "data": "synthetic (seeded uniform tokens; hidden states computed by the random-init verifier during the run; seeded draft init)",
             "impl": "ours", "config": dict(config_record(c, world, args.regions), parallelism=f"tp{topo.n_verifier} verifier + dp{topo.n_trainer}-sharded trainer",
                                             global_batch=topo.n_trainer),
-            "impl_detail": {"verifier": f"TensorParallelVerifier over {topo.n_verifier} GPUs, weights resident", "handoff": "NVLink peer-memory ring, batch built on the trainer GPU",
+            "impl_detail": {"verifier": f"TensorParallelVerifier over {topo.n_verifier} GPUs, weights resident",
+                            "verifier_comm": os.environ.get("SB200_TP_COMM", "peer (GEMM epilogue scatter + reduce / broadcast kernel) where the sizes allow"),
+                            "handoff": "NVLink peer-memory ring, batch built on the trainer GPU",
                             "optimizer_comm": os.environ.get("SB200_COMM"), "path": "speculators_b200.train.online.OnlineSplit.run / Trainer.train_step_async"},
             "regions_ms_per_step": spread([m / args.steps for m in region_ms]), "clocks": clocks,
-            "e2e": {"value": value, "unit": "tokens/s", "ms_per_step": ms / args.steps, "h2d_bytes_per_step": 8 * (c["seq_len"] + 1) * topo.n_trainer,
+            "e2e": {"value": value, "unit": "tokens/s", "ms_per_step": ms / args.steps, "h2d_bytes_per_step": 8 * c["seq_len"] * topo.n_trainer,
                     "d2h_bytes_per_step": 4 * topo.n_trainer,
                     "note": "the timed region is end to end already: token ids are the only host input, hidden states go GPU to GPU, every step's loss is read on the host"},
             "last_loss": float(loss_t[0] / max(1.0, float(loss_t[1]))), "gpu_launches": launches,

@@ -61,9 +61,14 @@ class Linear(nn.Module):
         self.in_features, self.out_features = in_features, out_features
         self.weight = nn.Parameter(torch.empty(out_features, in_features))
         self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
+        # tensor parallelism (inference): ``row_parallel(x, weight, residual) -> sum over the ranks'
+        # partial products + residual`` replaces the local product of a layer whose input is split
+        self.row_parallel = None
         _init_linear_(self.weight, std)
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        if self.row_parallel is not None and self.bias is None:
+            return self.row_parallel(x, self.weight, residual)
         return ops.linear(x, self.weight, self.bias, residual=residual)
 
     def extra_repr(self) -> str:

@@ -52,6 +52,9 @@ int fused_optim_ctl_words();
 int fused_optim_num_partials();
 int launch_fused_sharded_adamw(int, int, int64_t, const void* const*, void* const*, void* const*, const void*, void*, float*, float*,
                                float*, float*, float*, const float*, int*, uint32_t, cudaStream_t);
+int launch_gemm_scatter(const void*, const void*, void* const*, int, int, int, int, int, int64_t, int64_t, int*, cudaStream_t);
+int tp_allreduce_ctl_words();
+int launch_tp_reduce_broadcast(int, int, int, int, const void*, void* const*, void*, const void*, void* const*, int, int*, uint32_t, cudaStream_t);
 int hs_ring_ctl_words_per_slot();
 int launch_hs_push(const void*, int64_t, void*, uint32_t*, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t*, int*, cudaStream_t);
 int launch_hs_pop(void*, int64_t, const void*, uint32_t*, uint32_t, uint32_t, uint32_t*, int*, cudaStream_t);
@@ -509,6 +512,57 @@ void fused_sharded_adamw(int64_t world, int64_t rank, int64_t shard, const Tenso
   TORCH_CHECK(rc == 0, "fused_sharded_adamw launch failed (", rc, ")");
 }
 
+// ---- row-parallel product of a tensor-parallel layer ------------------------------------------
+// partial = x[M, K] . w[N, K]^T; the tile columns owned by rank o (N / world columns each, a multiple of 256) are stored
+// into slot `rank` of stage_ptrs[o] ([world][M][N / world] on rank o; int64 CPU tensor of addresses valid on this device).
+void gemm_scatter(const Tensor& x, const Tensor& w, const Tensor& stage_ptrs, int64_t rank, Tensor status) {
+  check_rows(x, "x");
+  check_rows(w, "w");
+  const int64_t world = stage_ptrs.numel(), M = x.size(0), K = x.size(1), N = w.size(0);
+  TORCH_CHECK(world >= 1 && world <= 8 && rank >= 0 && rank < world, "gemm_scatter: need 1 <= world <= 8 and 0 <= rank < world");
+  TORCH_CHECK(stage_ptrs.device().is_cpu() && stage_ptrs.scalar_type() == at::kLong);
+  TORCH_CHECK(w.size(1) == K && N % world == 0 && (N / world) % 256 == 0, "gemm_scatter: N / world must be a multiple of 256");
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == at::kInt && status.numel() >= 1);
+  c10::cuda::CUDAGuard guard(x.device());
+  void* stage[8];
+  for (int q = 0; q < world; ++q) stage[q] = reinterpret_cast<void*>(stage_ptrs.data_ptr<int64_t>()[q]);
+  const int rc = sb200::launch_gemm_scatter(x.data_ptr(), w.data_ptr(), stage, (int)world, (int)rank, (int)M, (int)N, (int)K, x.stride(0),
+                                            w.stride(0), status.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(rc == 0, "gemm_scatter launch failed (", rc, ")");
+}
+
+int64_t tp_allreduce_ctl_words() { return sb200::tp_allreduce_ctl_words(); }
+
+// Reduces this rank's column slice of the staged partial products (stage: local [world, rows, cols]), adds the residual's
+// slice (local [rows, world * cols], optional) and writes the slice into every rank's output (out_ptrs / out_mc).
+void tp_reduce_broadcast(const Tensor& stage, const Tensor& out_ptrs, int64_t out_mc, const c10::optional<Tensor>& residual,
+                         const Tensor& ctl_ptrs, int64_t rank, bool barrier, Tensor status, int64_t spin_limit) {
+  TORCH_CHECK(stage.is_cuda() && stage.scalar_type() == at::kBFloat16 && stage.dim() == 3 && stage.is_contiguous(), "stage must be bf16 [world, rows, cols]");
+  const int64_t world = stage.size(0), rows = stage.size(1), cols = stage.size(2);
+  TORCH_CHECK(world >= 1 && world <= 8 && rank >= 0 && rank < world && cols % 8 == 0, "tp_reduce_broadcast: need 1 <= world <= 8 and cols % 8 == 0");
+  TORCH_CHECK(spin_limit > 0 && spin_limit <= 0xFFFFFFF0LL, "tp_reduce_broadcast: spin_limit out of range");
+  TORCH_CHECK(out_ptrs.device().is_cpu() && out_ptrs.scalar_type() == at::kLong && out_ptrs.numel() == world);
+  TORCH_CHECK(ctl_ptrs.device().is_cpu() && ctl_ptrs.scalar_type() == at::kLong && ctl_ptrs.numel() == world);
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == at::kInt && status.numel() >= 1);
+  const void* res = nullptr;
+  if (residual.has_value()) {
+    TORCH_CHECK(residual->is_cuda() && residual->scalar_type() == at::kBFloat16 && residual->is_contiguous() && residual->numel() == rows * world * cols &&
+                (reinterpret_cast<uintptr_t>(residual->data_ptr()) & 15) == 0, "residual must be contiguous bf16 [rows, world * cols]");
+    res = residual->data_ptr();
+  }
+  c10::cuda::CUDAGuard guard(stage.device());
+  void* out[8];
+  void* ctl[8];
+  for (int q = 0; q < world; ++q) {
+    out[q] = reinterpret_cast<void*>(out_ptrs.data_ptr<int64_t>()[q]);
+    ctl[q] = reinterpret_cast<void*>(ctl_ptrs.data_ptr<int64_t>()[q]);
+    TORCH_CHECK((reinterpret_cast<uintptr_t>(out[q]) & 15) == 0 && ctl[q] != nullptr, "tp_reduce_broadcast: misaligned output / missing control block");
+  }
+  const int rc = sb200::launch_tp_reduce_broadcast((int)world, (int)rank, (int)rows, (int)cols, stage.data_ptr(), out, reinterpret_cast<void*>(out_mc), res,
+                                                   ctl, barrier ? 1 : 0, status.data_ptr<int>(), (uint32_t)spin_limit, cur_stream());
+  TORCH_CHECK(rc == 0, "tp_reduce_broadcast launch failed (", rc, ")");
+}
+
 // ---- debug build: index checks -------------------------------------------------------------
 bool checked_build() {
 #ifdef SB200_CHECK_BOUNDS
@@ -834,6 +888,9 @@ TORCH_LIBRARY(sb200, m) {
   m.def("peer_tensor", &peer_tensor);
   m.def("fused_optim_ctl_words", &fused_optim_ctl_words);
   m.def("fused_sharded_adamw", &fused_sharded_adamw);
+  m.def("gemm_scatter", &gemm_scatter);
+  m.def("tp_allreduce_ctl_words", &tp_allreduce_ctl_words);
+  m.def("tp_reduce_broadcast", &tp_reduce_broadcast);
   m.def("step_tail", &step_tail);
   m.def("checked_build", &checked_build);
   m.def("bounds_report", &bounds_report);

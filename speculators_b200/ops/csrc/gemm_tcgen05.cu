@@ -86,6 +86,21 @@ struct Grouping {
   const int* tile_start;  // [num_groups + 1] prefix sum of ceil(rows_e / 256) (kGroupRows); tiles of expert e: that x tiles_n
 };
 
+// Row-parallel product of a tensor-parallel layer: the ranks hold slices of the contraction, so
+// every rank's product is a partial sum of the whole [M, N] output.  Rank `owner = column /
+// cols` reduces the columns owner * cols .. + cols - 1; instead of storing its partial tile at home
+// and handing the buffer to a collective, the epilogue stores each tile straight into the owner's
+// staging area over NVLink (plain stores to peer-mapped memory, issued while the tensor core works
+// on the next tile): stage of rank o = [world][M][cols], slot `rank` written by this rank.
+// cols is a multiple of 256, so a tile has one owner.
+constexpr int kMaxScatterRanks = 8;
+struct Scatter {
+  int world;  // 0: off
+  int rank;
+  int cols;   // N / world
+  __nv_bfloat16* stage[kMaxScatterRanks];
+};
+
 struct Params {
   __nv_bfloat16* c;
   const __nv_bfloat16* residual;
@@ -95,7 +110,17 @@ struct Params {
   int* status;
   RowStatsOut rs;
   Grouping grp;
+  Scatter sc;
 };
+
+// First element of the W-column chunk at (row, n0) of the output.
+__device__ __forceinline__ __nv_bfloat16* c_chunk(const Params& p, int row, int n0) {
+  if (p.sc.world > 0) {
+    const int owner = n0 / p.sc.cols;
+    return p.sc.stage[owner] + ((int64_t)p.sc.rank * p.M + row) * p.sc.cols + (n0 - owner * p.sc.cols);
+  }
+  return p.c + (int64_t)row * p.ldc + n0;
+}
 
 // Where one 256x256 tile (or this CTA's half of it) sits in the operands.
 struct TileInfo {
@@ -161,7 +186,7 @@ __device__ __forceinline__ void st32(__nv_bfloat16* ptr, const bf16x8& a, const 
 // n0 .. n0+255 of C, with the configured epilogue.
 template <int W>
 __device__ __forceinline__ void store_accumulator(const Params& p, uint32_t taddr, int row, int n0, int row_end, bool zero) {
-  __nv_bfloat16* crow = p.c + (int64_t)row * p.ldc + n0;
+  __nv_bfloat16* crow = c_chunk(p, row, n0);
   const __nv_bfloat16* rrow = p.residual ? p.residual + (int64_t)row * p.ldr + n0 : nullptr;
   const bool vec_ok = ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0) &&
                       (p.epilogue != kAddResidual || (((p.ldr & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0)));
@@ -619,7 +644,7 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 static int launch_gemm_impl(const void* a, const void* b, void* c, const void* residual, int M, int N, int K, int64_t lda,
                             int64_t ldb, int64_t ldc, int64_t ldr, int epilogue, int a_mn, int b_mn, int* status, int variant,
                             const void* stats_targets, int64_t stats_ldt, int stats_t_rows, int stats_shift, float* stats_partial,
-                            const tc::Grouping* grp, cudaStream_t stream) {
+                            const tc::Grouping* grp, cudaStream_t stream, const tc::Scatter* scatter = nullptr) {
   using namespace tc;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda & 7) || (ldb & 7) || (reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15)) return -1;
@@ -635,7 +660,17 @@ static int launch_gemm_impl(const void* a, const void* b, void* c, const void* r
   rc = b_mn ? make_map_bf16(&map_b, b, b_stack * K, N, ldb, 2 * BK) : make_map_bf16(&map_b, b, b_stack * N, K, ldb, pairs ? P_HALF : BN);
   if (rc) return rc;
   Params p{(__nv_bfloat16*)c, (const __nv_bfloat16*)residual, M, N, K, ldc, ldr, epilogue, status, RowStatsOut{nullptr, 0, 0, 0, nullptr},
-           Grouping{kGroupNone, 0, nullptr, nullptr}};
+           Grouping{kGroupNone, 0, nullptr, nullptr}, Scatter{}};
+  if (scatter != nullptr) {
+    if (!pairs || grp != nullptr || stats_targets != nullptr || epilogue != kStore || scatter->world < 1 || scatter->world > kMaxScatterRanks ||
+        scatter->cols * scatter->world != N || (scatter->cols & 255))
+      return -7;
+    p.sc = *scatter;
+    p.c = scatter->stage[scatter->rank];  // alignment checks of the store path look at c / ldc
+    p.ldc = scatter->cols;
+    for (int q = 0; q < scatter->world; ++q)
+      if (reinterpret_cast<uintptr_t>(scatter->stage[q]) & 31) return -7;
+  }
   if (grp != nullptr) {
     if (!pairs || variant != 3 || stats_targets != nullptr || residual != nullptr) return -6;
     if (grp->mode == kGroupRows && (a_mn || (K & 127) || (N & 255))) return -6;  // experts' matrices must not share a box
@@ -693,6 +728,19 @@ int launch_gemm_tcgen05(const void* a, const void* b, void* c, const void* resid
 int launch_gemm_tn_tcgen05(const void* a, const void* b, void* c, const void* residual, int M, int N, int K, int64_t lda,
                            int64_t ldb, int64_t ldc, int64_t ldr, int epilogue, int* status, int variant, cudaStream_t stream) {
   return launch_gemm_tcgen05(a, b, c, residual, M, N, K, lda, ldb, ldc, ldr, epilogue, 0, 0, status, variant, stream);
+}
+
+// ---- row-parallel product with the reduce-scatter's transfer in the epilogue -----------------
+// partial[M, N] = a[M, K] . b[N, K]^T, tile columns stored into slot `rank` of their owner's staging
+// area stage[owner] = [world][M][N / world] (addresses valid on this device: peer-mapped for the
+// other ranks).  N / world must be a multiple of 256.
+int launch_gemm_scatter(const void* a, const void* b, void* const* stage, int world, int rank, int M, int N, int K, int64_t lda, int64_t ldb,
+                        int* status, cudaStream_t stream) {
+  if (world < 1 || world > tc::kMaxScatterRanks || rank < 0 || rank >= world || N % world) return -7;
+  tc::Scatter sc{world, rank, N / world, {}};
+  for (int q = 0; q < world; ++q) sc.stage[q] = static_cast<__nv_bfloat16*>(stage[q]);
+  return launch_gemm_impl(a, b, stage[rank], nullptr, M, N, K, lda, ldb, N / world, 0, tc::kStore, 0, 0, status, 3, nullptr, 0, 0, 0, nullptr, nullptr,
+                          stream, &sc);
 }
 
 // ---- grouped products for mixture-of-experts layers -----------------------------------------

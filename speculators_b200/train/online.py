@@ -56,20 +56,26 @@ class SplitTopology:
 
 class OnlineSplit:
     def __init__(self, verifier_config: dict, aux_layers: list[int], seq_len: int, device: torch.device, *, n_verifier: int | None = None,
-                 n_slots: int = 4, timeout_s: float = 120.0, seed: int = 0, resident: bool = True, sliced_init: bool = True):
+                 n_slots: int = 4, timeout_s: float = 120.0, seed: int = 0, resident: bool = True, sliced_init: bool = True,
+                 sample_tokens: int | None = None, verifier_comm: str | None = None):
+        """``sample_tokens``: length of the sequences the verifier runs (default ``seq_len + 1``: the pairing
+        shift consumes one token, so the trainer's ``seq_len`` positions are all real; ``seq_len`` keeps the
+        verifier's row count a multiple of the GEMM tile and leaves the trainer one masked position).
+        ``verifier_comm``: see ``TensorParallelVerifier`` (``None``: fused peer-memory exchange where possible)."""
         if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() < 2:
             raise RuntimeError("OnlineSplit needs at least two ranks (one verifier, one trainer)")
         world, rank = dist.get_world_size(), dist.get_rank()
         self.topo = SplitTopology(world, rank, n_verifier if n_verifier is not None else world // 2)
         t = self.topo
         self.device, self.seq_len, self.aux_layers, self.timeout_s, self.seed = device, int(seq_len), list(aux_layers), timeout_s, seed
+        self.sample_tokens = int(sample_tokens) if sample_tokens is not None else self.seq_len + 1
         self.hidden = int(verifier_config["hidden_size"])
         self.vocab = int(verifier_config["vocab_size"])
         # both groups are created by every rank (a collective of the whole job)
         self.verifier_group = dist.new_group(list(range(t.n_verifier)))
         self.trainer_group = dist.new_group(list(range(t.n_verifier, world)))
         width = (len(self.aux_layers) + 1) * self.hidden
-        self.ring = HiddenStateRing(n_slots, self.seq_len + 1, width, device) if not t.is_verifier else None
+        self.ring = HiddenStateRing(n_slots, self.sample_tokens, width, device) if not t.is_verifier else None
         described: list = [None] * world
         dist.all_gather_object(described, self.ring.describe() if self.ring is not None else None)
         self.writers: dict[int, HiddenStateRingWriter] = {}
@@ -80,16 +86,15 @@ class OnlineSplit:
                     self.writers[ti] = HiddenStateRingWriter(described[t.n_verifier + ti], device)
             self.verifier = TensorParallelVerifier(verifier_config, group=self.verifier_group, seed=seed, device=device,
                                                    dtype=torch.bfloat16 if device.type == "cuda" else torch.float32,
-                                                   resident=resident, sliced_init=sliced_init)
+                                                   resident=resident, sliced_init=sliced_init, max_tokens=self.sample_tokens, comm=verifier_comm)
         self._seq = 0
         self._loader: RingBatchLoader | None = None  # one per trainer rank for the whole job: sequence numbers run on across ``run`` calls
 
     # ------------------------------------------------------------------ data
     def tokens(self, step: int, trainer_index: int) -> torch.Tensor:
-        """The sequence trainer ``trainer_index`` trains on at ``step`` (seeded; ``seq_len + 1`` tokens: the
-        pairing shift consumes one)."""
+        """The sequence trainer ``trainer_index`` trains on at ``step`` (seeded, ``sample_tokens`` long)."""
         gen = torch.Generator().manual_seed(self.seed * 1_000_003 + step * 1009 + trainer_index)
-        return torch.randint(0, self.vocab, (self.seq_len + 1,), generator=gen)
+        return torch.randint(0, self.vocab, (self.sample_tokens,), generator=gen)
 
     # ------------------------------------------------------------------ verifier side
     def verifier_step(self, step: int) -> None:
@@ -106,6 +111,8 @@ class OnlineSplit:
     def check_verifier(self) -> None:
         for w in self.writers.values():
             w.check_status()
+        if self.verifier is not None and self.verifier.comm is not None:
+            self.verifier.comm.check_status()
 
     # ------------------------------------------------------------------ trainer side
     def loader(self, num_steps: int) -> RingBatchLoader:
@@ -158,3 +165,6 @@ class OnlineSplit:
             w.close()
         if self.ring is not None:
             self.ring.close()
+        if self.verifier is not None and self.verifier.comm is not None:
+            self.verifier.comm.check_status()
+            self.verifier.comm.close()

@@ -9,7 +9,11 @@ Llama / Qwen3 verifiers: the ranks of a process group split every layer Megatron
   KV heads and ``intermediate / R`` MLP columns),
 * o and down row-parallel: every rank multiplies its slice and the partial sums are all-reduced,
 
-so a layer costs two all-reduces of ``[T, H]``.  All products run on the package's GEMM and
+so a layer costs two all-reduces of ``[T, H]``.  On CUDA devices with peer access these are not
+library calls: the row-parallel GEMM's epilogue stores its tiles into the owning rank's staging
+area over NVLink and a second kernel reduces, adds the residual stream and writes every rank's
+copy (``parallel/tp_comm.py``; ``SB200_TP_COMM=nccl`` keeps the NCCL all-reduce, the twin the
+result is tested against).  All products run on the package's GEMM and
 attention kernels through the same ``DecoderLayer`` the draft models use (built for the local
 head / column counts).  Weights are the rank's slices of exactly the tensors ``RandomVerifier``
 generates for a seed, so the result equals the single-device forward (tested with two gloo ranks).
@@ -31,7 +35,7 @@ __all__ = ["TensorParallelVerifier"]
 
 class TensorParallelVerifier:
     def __init__(self, config: TransformerLayerConfig | dict, group=None, seed: int = 0, device="cpu", dtype=torch.float32,
-                 resident: bool = False, sliced_init: bool = False):
+                 resident: bool = False, sliced_init: bool = False, max_tokens: int | None = None, comm: str | None = None):
         """``resident``: keep every layer's slices on the device after the first forward (a 70B-class
         verifier over 4 GPUs holds 35 GB per GPU) instead of regenerating them per call.
         ``sliced_init``: draw each rank's slices directly from a seed of their own instead of
@@ -55,6 +59,27 @@ class TensorParallelVerifier:
         })
         with torch.device("meta"):  # names, shapes and order of a full layer's tensors (what the seeds are tied to)
             self._full_shapes = [(n, tuple(p.shape)) for n, p in DecoderLayer(self.cfg, 0).named_parameters()]
+        self.comm = self._make_comm(comm, max_tokens)
+
+    def _make_comm(self, choice: str | None, max_tokens: int | None):
+        """The fused row-parallel exchange, or ``None`` for the library all-reduce.  Every rank of the
+        group takes the same branch (the inputs of the decision are the same everywhere)."""
+        import os
+
+        from speculators_b200.parallel.tp_comm import TpComm
+
+        choice = choice or os.environ.get("SB200_TP_COMM") or "auto"
+        if choice not in ("auto", "peer", "nccl"):
+            raise ValueError(f"comm must be 'peer', 'nccl' or None, got {choice!r}")
+        able = (self.world > 1 and self.device.type == "cuda" and self.dtype == torch.bfloat16 and max_tokens is not None
+                and TpComm.supported(int(self.cfg.hidden_size), self.world))
+        if choice == "nccl" or (choice == "auto" and not able):
+            return None
+        if not able:
+            raise ValueError("comm='peer' needs a CUDA device, bf16 weights, max_tokens and hidden_size / world a multiple of 256")
+        comm = TpComm(self.group, int(max_tokens), int(self.cfg.hidden_size), self.device)
+        comm.connect()
+        return comm
 
     def embed_weight(self) -> torch.Tensor:
         return _seeded((self.cfg.vocab_size, self.cfg.hidden_size), 0.02, self.seed * 1000 + 900, self.device, self.dtype)
@@ -90,6 +115,9 @@ class TensorParallelVerifier:
                     del full
                 else:
                     p.data = p.data.to(device=self.device, dtype=self.dtype)
+        if self.comm is not None:
+            layer.self_attn.o_proj.row_parallel = self.comm.row_parallel
+            layer.mlp.down_proj.row_parallel = self.comm.row_parallel
         if self.resident:
             self._layers[idx] = layer
         return layer
@@ -116,11 +144,20 @@ class TensorParallelVerifier:
         else:
             h = torch.nn.functional.embedding(ids, self.embed_weight())
         taken: dict[int, torch.Tensor] = {}
+        fused = self.comm is not None
         for i in range(int(self.cfg.num_hidden_layers)):
             layer = self._layer(i)
-            h = h + self._reduce(layer.self_attn(layer.input_layernorm(h), pos, self.rotary, spec))
-            h = h + self._reduce(layer.mlp(layer.post_attention_layernorm(h)))
+            if fused:
+                # o_proj / down_proj: product, sum over the ranks and residual add in two kernels; the result
+                # alternates between two peer buffers, so what is kept beyond the next call is copied
+                h = layer.self_attn(layer.input_layernorm(h), pos, self.rotary, spec, residual=h)
+                h = layer.mlp(layer.post_attention_layernorm(h), residual=h)
+            else:
+                h = h + self._reduce(layer.self_attn(layer.input_layernorm(h), pos, self.rotary, spec))
+                h = h + self._reduce(layer.mlp(layer.post_attention_layernorm(h)))
             if i in layer_ids:
-                taken[i] = h
+                taken[i] = h.clone() if fused else h
             del layer
+        if fused:
+            h = h.clone()
         return {"hidden_states": torch.cat([taken[i] for i in layer_ids], dim=-1), "verifier_last_hidden_states": h}

@@ -328,3 +328,45 @@ def test_online_split_hands_hidden_states_gpu_to_gpu(tmp_path):
     mp.spawn(_online_worker, args=(2, 29681, str(out)), nprocs=2, join=True)
     res = json.loads(out.read_text())
     assert res["ok"] == [True, True] and res["ms"] > 0
+
+
+# ---- tensor-parallel verifier: fused row-parallel products against the library all-reduce ---------------------
+def _tp_worker(rank, world, port, out_path):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from speculators_b200.verifier.tp import TensorParallelVerifier
+
+    cfg = dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=512, intermediate_size=1024, num_hidden_layers=4,
+               num_attention_heads=8, num_key_value_heads=2, head_dim=64, vocab_size=512, max_position_embeddings=1024, rms_norm_eps=1e-5,
+               rope_theta=10000.0, hidden_act="silu")
+    dev = torch.device("cuda", rank)
+    aux, T = [1, 2, 3], 300
+    ids = torch.randint(0, 512, (T,), generator=torch.Generator().manual_seed(5))
+    fused = TensorParallelVerifier(cfg, seed=3, device=dev, dtype=torch.bfloat16, resident=True, max_tokens=T, comm="peer")
+    twin = TensorParallelVerifier(cfg, seed=3, device=dev, dtype=torch.bfloat16, resident=True, comm="nccl")
+    assert fused.comm is not None and twin.comm is None
+    a = [fused.forward(ids, aux) for _ in range(3)][-1]  # repeated calls reuse the buffers and the barrier generations
+    b = twin.forward(ids, aux)
+    torch.cuda.synchronize()
+    fused.comm.check_status()
+    ok = all(torch.allclose(a[k].float(), b[k].float(), atol=4e-2, rtol=4e-2) for k in ("hidden_states", "verifier_last_hidden_states"))
+    ok = ok and bool(torch.isfinite(a["hidden_states"].float()).all())
+    gathered = [torch.empty_like(a["verifier_last_hidden_states"]) for _ in range(world)]
+    dist.all_gather(gathered, a["verifier_last_hidden_states"].contiguous())
+    same = all(torch.equal(g, gathered[0]) for g in gathered)  # every rank holds the same bits
+    flags = [None] * world
+    dist.all_gather_object(flags, bool(ok and same))
+    if rank == 0:
+        with open(out_path, "w") as fh:
+            json.dump({"ok": flags}, fh)
+    dist.barrier()
+    fused.comm.close()
+    dist.destroy_process_group()
+
+
+def test_tensor_parallel_verifier_fused_exchange_matches_all_reduce(tmp_path):
+    _need_two()
+    out = tmp_path / "tp.json"
+    mp.spawn(_tp_worker, args=(2, 29691, str(out)), nprocs=2, join=True)
+    assert json.loads(out.read_text())["ok"] == [True, True]
