@@ -37,7 +37,7 @@ def test_scatter_product_and_reduce_broadcast_match_fp32_sum(world, T, N, K, wit
         if residual is not None:
             ref = ref + residual.float()
         for out in outs:  # every rank holds the complete result
-            torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)
+            torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=6e-2)  # one bf16 rounding of sums of magnitude up to 8
             assert torch.equal(out, outs[0])
         # a second round lands in the other buffer and leaves the first result intact
         first = outs[0].clone()
@@ -45,7 +45,7 @@ def test_scatter_product_and_reduce_broadcast_match_fp32_sum(world, T, N, K, wit
             c.scatter_product(x, w)
         again = [c.reduce_broadcast(T, outs[i]) for i, c in enumerate(comms)]
         assert torch.equal(outs[0], first)
-        torch.testing.assert_close(again[0].float(), (ref - (residual.float() if residual is not None else 0)) + first.float(), rtol=2e-2, atol=4e-2)
+        torch.testing.assert_close(again[0].float(), (ref - (residual.float() if residual is not None else 0)) + first.float(), rtol=2e-2, atol=1.2e-1)
     finally:
         for c in comms:
             c.close()
