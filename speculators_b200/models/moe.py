@@ -190,7 +190,8 @@ class SparseMoeBlock(nn.Module):
         sorted_e = flat_e[order]
         xs = x[token_of[order]]
         if self.ep_size == 1:
-            counts = torch.bincount(sorted_e, minlength=self.num_experts)
+            # rows per expert without a host read (``bincount`` sizes its result from the largest id)
+            counts = torch.zeros(self.num_experts, dtype=torch.long, device=x.device).index_add_(0, sorted_e, torch.ones_like(sorted_e))
             ys = _grouped_expert_forward(xs, counts, self.experts.gate_up_proj, self.experts.down_proj)
         else:
             ys = self._expert_parallel(xs, sorted_e)

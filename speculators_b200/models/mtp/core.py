@@ -66,9 +66,10 @@ class MTPDraftModel(DraftVocabMixin, SpeculatorModel):
             raise NotImplementedError("Vocab reduction is not supported for MTP speculators")
         tc = config.transformer_layer_config
         self.mtp_layers = nn.ModuleList([build_mtp_layer(tc, 0, ep_group=ep_group)])
-        # expert routing sizes its buffers from counts read on the host (bincount, exchange plans):
-        # a layer with experts runs eagerly, a dense one as a CUDA graph
-        self.cuda_graph_safe = type(self.mtp_layers[0]).__name__ != "MoEMTPLayer"
+        # a dense layer has fixed shapes; so has a layer with experts that all live on this rank (the grouped
+        # GEMMs take the routing counts from device memory).  The expert-parallel exchange sizes its plan from
+        # counts read on the host, so those steps run eagerly.
+        self.cuda_graph_safe = type(self.mtp_layers[0]).__name__ != "MoEMTPLayer" or ep_group is None
         self.rotary_emb = RotaryTable(tc)
 
     @property

@@ -405,7 +405,20 @@ class Trainer:
         dict that the following call will receive) has its host-to-device copy started
         on a side stream so that it overlaps this step's compute."""
         lr = self._current_lr()
-        if self._graphed is not None:
+        if self._graphed is not None and not self._graphed.cache:
+            # first capture of this trainer: a model whose step turns out not to be capturable (a host read
+            # in a rarely used branch) falls back to eager steps instead of ending the run
+            try:
+                with nvtx_range("step (graph capture)"):
+                    loss, metrics = self._graphed.run(batch, lr, next_batch)
+            except RuntimeError as err:
+                if "captur" not in str(err).lower():
+                    raise
+                root_logger.warning("CUDA graph capture of the training step failed (%s); running eager steps", str(err).splitlines()[0])
+                self._graphed = None
+                torch.cuda.synchronize(self.device)
+                return self.train_step(batch, next_batch)
+        elif self._graphed is not None:
             with nvtx_range("step (graph replay)"):
                 loss, metrics = self._graphed.run(batch, lr, next_batch)
         else:

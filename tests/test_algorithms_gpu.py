@@ -150,4 +150,5 @@ def test_moe_mtp_gpu_loss_and_training_step(tmp_path, head_dim):
                       SyntheticLoader([batch], 6))
     losses = [float(trainer.train_step(batch)[0]) for _ in range(6)]
     assert all(l == l for l in losses) and losses[-1] < losses[0], losses
+    assert trainer._graphed is not None and len(trainer._graphed.cache) == 1  # noqa: SLF001 - experts on one rank: the step is captured
     trainer.check_device_status()
