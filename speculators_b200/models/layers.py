@@ -297,8 +297,13 @@ class MLP(nn.Module):
         self.down_proj = Linear(inter, config.hidden_size, bias=bool(config.mlp_bias))
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        silu = self.hidden_act in ("silu", "swish")
+        if silu and self.gate_up_proj.bias is None:
+            hidden = ops.linear_swiglu(x, self.gate_up_proj.weight)  # activation in the GEMM's epilogue
+            if hidden is not None:
+                return self.down_proj(hidden, residual=residual)
         gate_up = self.gate_up_proj(x)
-        if self.hidden_act in ("silu", "swish"):
+        if silu:
             hidden = ops.swiglu(gate_up)
         else:
             gate, up = gate_up.chunk(2, dim=-1)

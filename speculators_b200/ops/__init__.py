@@ -33,6 +33,7 @@ __all__ = [
     "grouped_linear",
     "grouped_linear_ok",
     "linear",
+    "linear_swiglu",
     "lm_head_loss_raw",
     "masked_attention",
     "matmul_nn",
@@ -442,6 +443,39 @@ class _SwiGLUFn(torch.autograd.Function):
     def backward(ctx, dh):
         (gate_up,) = ctx.saved_tensors
         return native().swiglu_bwd(dh.contiguous(), gate_up)
+
+
+class _GateUpSwiGLUFn(torch.autograd.Function):
+    """``h = silu(x @ Wg.T) * (x @ Wu.T)`` with ``W = [Wg; Wu]``: one GEMM whose epilogue stores the
+    gate | up product (saved for the backward pass) and the activated product."""
+
+    @staticmethod
+    def forward(ctx, x2, weight):
+        gate_up, h = native().gemm_swiglu(x2, weight, gemm_status(x2.device))
+        ctx.save_for_backward(x2, weight, gate_up)
+        return h
+
+    @staticmethod
+    def backward(ctx, dh):
+        x2, weight, gate_up = ctx.saved_tensors
+        dgu = native().swiglu_bwd(dh.contiguous(), gate_up)
+        dx, dw = _linear_backward(x2, weight, (None, None), dgu, ctx.needs_input_grad[0], ctx.needs_input_grad[1])
+        return dx, dw
+
+
+def linear_swiglu(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor | None:
+    """``swiglu(linear(x, weight))`` for a stacked ``[gate; up]`` weight in one launch: the
+    activation is formed in the GEMM's epilogue from the accumulator (``SB200_FUSED_SWIGLU=0``
+    switches it off).  ``None`` when the operands do not suit the kernel (other dtype or device,
+    intermediate size not a multiple of 128) and the caller should run the two steps."""
+    import os
+
+    x2 = x.reshape(-1, x.shape[-1])
+    if (not _own_gemm_enabled() or os.environ.get("SB200_FUSED_SWIGLU", "0") != "1" or not _gemm_operand_ok(x2) or not _gemm_operand_ok(weight)
+            or weight.shape[0] % 256 or weight.shape[1] != x2.shape[1]):
+        return None
+    h = _GateUpSwiGLUFn.apply(x2, weight)
+    return h.view(*x.shape[:-1], h.shape[-1])
 
 
 def swiglu(gate_up: torch.Tensor) -> torch.Tensor:

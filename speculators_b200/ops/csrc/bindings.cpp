@@ -52,6 +52,7 @@ int fused_optim_ctl_words();
 int fused_optim_num_partials();
 int launch_fused_sharded_adamw(int, int, int64_t, const void* const*, void* const*, void* const*, const void*, void*, float*, float*,
                                float*, float*, float*, const float*, int*, uint32_t, cudaStream_t);
+int launch_gemm_swiglu(const void*, const void*, void*, void*, int, int, int, int64_t, int64_t, int64_t, int64_t, int*, cudaStream_t);
 int launch_gemm_scatter(const void*, const void*, void* const*, int, int, int, int, int, int64_t, int64_t, int*, cudaStream_t);
 int tp_allreduce_ctl_words();
 int launch_tp_reduce_broadcast(int, int, int, int, const void*, void* const*, void*, const void*, void* const*, int, int*, uint32_t, cudaStream_t);
@@ -512,6 +513,23 @@ void fused_sharded_adamw(int64_t world, int64_t rank, int64_t shard, const Tenso
   TORCH_CHECK(rc == 0, "fused_sharded_adamw launch failed (", rc, ")");
 }
 
+// ---- gated MLP: gate | up product with the activation in the GEMM epilogue ------------------------
+// w: [2 I, K], gate rows first.  Returns (gate_up [M, 2 I], h [M, I] = silu(gate) * up).
+std::tuple<Tensor, Tensor> gemm_swiglu(const Tensor& x, const Tensor& w, Tensor status) {
+  check_rows(x, "x");
+  check_rows(w, "w");
+  const int64_t M = x.size(0), K = x.size(1), I = w.size(0) / 2;
+  TORCH_CHECK(w.size(1) == K && w.size(0) == 2 * I && I % 128 == 0, "gemm_swiglu: w must be [2 I, K] with I a multiple of 128");
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == at::kInt && status.numel() >= 1);
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor gate_up = at::empty({M, 2 * I}, x.options());
+  Tensor h = at::empty({M, I}, x.options());
+  const int rc = sb200::launch_gemm_swiglu(x.data_ptr(), w.data_ptr(), gate_up.data_ptr(), h.data_ptr(), (int)M, (int)I, (int)K, x.stride(0), w.stride(0),
+                                           2 * I, I, status.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(rc == 0, "gemm_swiglu launch failed (", rc, ")");
+  return {gate_up, h};
+}
+
 // ---- row-parallel product of a tensor-parallel layer ------------------------------------------
 // partial = x[M, K] . w[N, K]^T; the tile columns owned by rank o (N / world columns each, a multiple of 256) are stored
 // into slot `rank` of stage_ptrs[o] ([world][M][N / world] on rank o; int64 CPU tensor of addresses valid on this device).
@@ -888,6 +906,7 @@ TORCH_LIBRARY(sb200, m) {
   m.def("peer_tensor", &peer_tensor);
   m.def("fused_optim_ctl_words", &fused_optim_ctl_words);
   m.def("fused_sharded_adamw", &fused_sharded_adamw);
+  m.def("gemm_swiglu", &gemm_swiglu);
   m.def("gemm_scatter", &gemm_scatter);
   m.def("tp_allreduce_ctl_words", &tp_allreduce_ctl_words);
   m.def("tp_reduce_broadcast", &tp_reduce_broadcast);

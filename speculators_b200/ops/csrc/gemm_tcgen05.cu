@@ -50,7 +50,11 @@ constexpr int THREADS = 192;
 constexpr int TMEM_COLS = 512;
 constexpr int kDefaultPairVariant = 3;
 
-enum Epilogue : int { kStore = 0, kAccumulate = 1, kAddResidual = 2 };
+// kSwiGLU: the weight is the stack [gate rows | up rows] of a gated MLP (N = 2 I).  A tile pairs 128 gate columns
+// with the same 128 up columns (the leader CTA loads the gate rows, its peer the up rows, so the accumulator holds
+// gate in columns 0..127 and up in 128..255); the epilogue stores both halves into C[M, 2 I] (kept for the backward
+// pass) and silu(gate) * up into h[M, I].
+enum Epilogue : int { kStore = 0, kAccumulate = 1, kAddResidual = 2, kSwiGLU = 3 };
 enum Status : int { kOk = kStatusOk, kTimeoutProducer = 1, kTimeoutMma = 2, kTimeoutEpilogue = 3 };
 
 // Row statistics in the epilogue (the lm_head product fused with the row loss): next to
@@ -111,6 +115,8 @@ struct Params {
   RowStatsOut rs;
   Grouping grp;
   Scatter sc;
+  __nv_bfloat16* h;  // kSwiGLU: [M, N / 2] output, row stride ldh
+  int64_t ldh;
 };
 
 // First element of the W-column chunk at (row, n0) of the output.
@@ -149,6 +155,10 @@ __device__ __forceinline__ TileInfo decode_tile(const Params& p, int tile, int t
     t.tile_n = local / rows;
     t.n0 = t.tile_n * 256;
     t.a_m = m0; t.a_k0 = 0; t.b_n = t.n0 + rank * 128; t.b_k0 = 0; t.num_kb = num_kb; t.c_row0 = m0; t.row_end = p.M;
+    if (p.epilogue == kSwiGLU) {  // 128 gate rows for the leader, the matching up rows for its peer
+      t.n0 = t.tile_n * 128;
+      t.b_n = t.n0 + rank * (p.N >> 1);
+    }
   } else if (p.grp.mode == kGroupRows) {
     int lo = 0, hi = p.grp.num_groups - 1;  // last e with tile_start[e] <= tile
     while (lo < hi) {
@@ -240,6 +250,49 @@ __device__ __forceinline__ void store_accumulator(const Params& p, uint32_t tadd
         }
       }
     }
+  }
+}
+
+// ---- gated MLP: gate | up product with silu(gate) * up formed in the epilogue -------------------
+// One thread = one row; `tlane` = TMEM address of its lane at the first of the 64 gate columns it handles
+// (the matching up columns sit 128 columns further), col0 = their column in [0, I).  The activation is
+// taken from the bf16-rounded gate and up (what the backward pass reads back), in the element-wise
+// kernel's order: silu(gate) rounded to bf16, times up.  Needs I % 128 == 0, ldc / ldh multiples of 16
+// and 32-byte aligned bases (checked on the host).
+__device__ __forceinline__ void store_accumulator_swiglu(const Params& p, uint32_t tlane, int row, int col0, int row_end) {
+  const int I = p.N >> 1;
+  __nv_bfloat16* grow = p.c + (int64_t)row * p.ldc + col0;
+  __nv_bfloat16* hrow = p.h + (int64_t)row * p.ldh + col0;
+#pragma unroll 1
+  for (int c = 0; c < 2; ++c) {
+    uint32_t g[32], u[32];
+    tmem_ld32(tlane + c * 32, g);
+    tmem_ld32(tlane + 128 + c * 32, u);
+    tmem_ld_wait();
+    if (row >= row_end) continue;
+    bf16x8 gp[4], up[4], hp[4];
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      float gf[8], uf[8], o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { gf[j] = __uint_as_float(g[v * 8 + j]); uf[j] = __uint_as_float(u[v * 8 + j]); }
+      gp[v] = pack8(gf);
+      up[v] = pack8(uf);
+      unpack8(gp[v], gf);
+      unpack8(up[v], uf);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float sg = 1.f / (1.f + __expf(-gf[j]));
+        o[j] = __bfloat162float(__float2bfloat16(gf[j] * sg)) * uf[j];
+      }
+      hp[v] = pack8(o);
+    }
+    st32(grow + c * 32, gp[0], gp[1]);
+    st32(grow + c * 32 + 16, gp[2], gp[3]);
+    st32(grow + I + c * 32, up[0], up[1]);
+    st32(grow + I + c * 32 + 16, up[2], up[3]);
+    st32(hrow + c * 32, hp[0], hp[1]);
+    st32(hrow + c * 32 + 16, hp[2], hp[3]);
   }
 }
 
@@ -604,15 +657,17 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int row = ti.c_row0 + quarter * 32 + lane, n0 = ti.n0 + chalf * P_EPI_COLS;
       const bool zero = ti.num_kb == 0;
       RowPrefetch<P_EPI_COLS> pre;
-      const bool with_stats = p.rs.targets != nullptr;
+      const bool with_stats = p.rs.targets != nullptr, gated = p.epilogue == kSwiGLU;
       if (with_stats) prefetch_targets<P_EPI_COLS>(p, row, n0, pre);
-      else prefetch_addend<P_EPI_COLS>(p, row, n0, ti.row_end, pre);
+      else if (!gated) prefetch_addend<P_EPI_COLS>(p, row, n0, ti.row_end, pre);
       ok = mbar_wait(smem_addr(&bar_acc_full[acc]), (local >> 1) & 1, p.status, kTimeoutEpilogue);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       fence_after_sync();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + chalf * P_EPI_COLS;
-      if (with_stats) store_accumulator_with_stats<P_EPI_COLS>(p, taddr, row, n0, ti.tile_n * 2 + chalf, tiles_n * 2, pre);
+      if (gated)  // this warp: gate columns 64 * chalf .. + 63 of the tile and the same up columns
+        store_accumulator_swiglu(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + chalf * 64, row, ti.n0 + chalf * 64, ti.row_end);
+      else if (with_stats) store_accumulator_with_stats<P_EPI_COLS>(p, taddr, row, n0, ti.tile_n * 2 + chalf, tiles_n * 2, pre);
       else if (pre.tile_ok) store_accumulator_prefetched<P_EPI_COLS>(p, taddr, row, n0, pre, zero);
       else store_accumulator<P_EPI_COLS>(p, taddr, row, n0, ti.row_end, zero);
       fence_before_sync();
@@ -644,7 +699,8 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 static int launch_gemm_impl(const void* a, const void* b, void* c, const void* residual, int M, int N, int K, int64_t lda,
                             int64_t ldb, int64_t ldc, int64_t ldr, int epilogue, int a_mn, int b_mn, int* status, int variant,
                             const void* stats_targets, int64_t stats_ldt, int stats_t_rows, int stats_shift, float* stats_partial,
-                            const tc::Grouping* grp, cudaStream_t stream, const tc::Scatter* scatter = nullptr) {
+                            const tc::Grouping* grp, cudaStream_t stream, const tc::Scatter* scatter = nullptr, void* gated_h = nullptr,
+                            int64_t gated_ldh = 0) {
   using namespace tc;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda & 7) || (ldb & 7) || (reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15)) return -1;
@@ -660,7 +716,12 @@ static int launch_gemm_impl(const void* a, const void* b, void* c, const void* r
   rc = b_mn ? make_map_bf16(&map_b, b, b_stack * K, N, ldb, 2 * BK) : make_map_bf16(&map_b, b, b_stack * N, K, ldb, pairs ? P_HALF : BN);
   if (rc) return rc;
   Params p{(__nv_bfloat16*)c, (const __nv_bfloat16*)residual, M, N, K, ldc, ldr, epilogue, status, RowStatsOut{nullptr, 0, 0, 0, nullptr},
-           Grouping{kGroupNone, 0, nullptr, nullptr}, Scatter{}};
+           Grouping{kGroupNone, 0, nullptr, nullptr}, Scatter{}, (__nv_bfloat16*)gated_h, gated_ldh};
+  if (epilogue == kSwiGLU) {
+    if (!pairs || a_mn || b_mn || grp != nullptr || stats_targets != nullptr || scatter != nullptr || gated_h == nullptr || (N & 255) || (ldc & 15) ||
+        (gated_ldh & 15) || (reinterpret_cast<uintptr_t>(c) & 31) || (reinterpret_cast<uintptr_t>(gated_h) & 31))
+      return -8;
+  }
   if (scatter != nullptr) {
     if (!pairs || grp != nullptr || stats_targets != nullptr || epilogue != kStore || scatter->world < 1 || scatter->world > kMaxScatterRanks ||
         scatter->cols * scatter->world != N || (scatter->cols & 255))
@@ -741,6 +802,14 @@ int launch_gemm_scatter(const void* a, const void* b, void* const* stage, int wo
   for (int q = 0; q < world; ++q) sc.stage[q] = static_cast<__nv_bfloat16*>(stage[q]);
   return launch_gemm_impl(a, b, stage[rank], nullptr, M, N, K, lda, ldb, N / world, 0, tc::kStore, 0, 0, status, 3, nullptr, 0, 0, 0, nullptr, nullptr,
                           stream, &sc);
+}
+
+// ---- gate | up product of a gated MLP with the activation in the epilogue ---------------------
+// gate_up[M, 2 I] = x[M, K] . w[2 I, K]^T (gate rows first) and h[M, I] = silu(gate) * up.  I % 128 == 0.
+int launch_gemm_swiglu(const void* x, const void* w, void* gate_up, void* h, int M, int I, int K, int64_t ldx, int64_t ldw, int64_t ldc, int64_t ldh,
+                       int* status, cudaStream_t stream) {
+  return launch_gemm_impl(x, w, gate_up, nullptr, M, 2 * I, K, ldx, ldw, ldc, 0, tc::kSwiGLU, 0, 0, status, 3, nullptr, 0, 0, 0, nullptr, nullptr, stream,
+                          nullptr, h, ldh);
 }
 
 // ---- grouped products for mixture-of-experts layers -----------------------------------------

@@ -108,7 +108,13 @@ class TrainEngine:
         self.distributed = dist.is_available() and dist.is_initialized()
         self.world = dist.get_world_size(self.group) if self.distributed else 1
         self.rank = dist.get_rank(self.group) if self.distributed else 0
-        self.sharded = bool(config.shard) and self.world > 1
+        # Replicated data parallelism (no ``shard``) with AdamW in bf16 on CUDA takes the sharded step too: reduce-scatter +
+        # update of 1 / world of the state + all-gather of the weights gives the result of all-reduce + full update
+        # on every rank, moves the same bytes, runs as the fused peer-memory kernels where those apply, and holds
+        # 1 / world of the optimizer state.  ``SB200_AUTO_SHARD=0`` keeps the all-reduce form.
+        auto_shard = (not config.shard and self.world > 1 and self.device.type == "cuda" and config.optimizer == "adamw"
+                      and config.compute_dtype == torch.bfloat16 and os.environ.get("SB200_AUTO_SHARD", "1") != "0")
+        self.sharded = (bool(config.shard) or auto_shard) and self.world > 1
         self.nvls = False
         self.p2p = self._want_p2p()
         self.step_count = 0

@@ -209,3 +209,36 @@ def test_moe_block_runs_its_experts_on_the_grouped_kernel():
     assert (xg.grad.float().cpu() - xr.grad).abs().max() < 0.05 * gmax + 1e-4
     wr, wg = ref.experts.gate_up_proj.grad, gpu.experts.gate_up_proj.grad.float().cpu()
     assert (wg - wr).abs().max() < 0.05 * wr.abs().max() + 1e-4
+
+
+# ---- gate | up product with SwiGLU in the epilogue ---------------------------------------------------
+@pytest.mark.parametrize("T,H,I", [(300, 256, 384), (2048, 512, 1024), (130, 128, 128), (257, 384, 1792)])
+def test_gate_up_product_with_swiglu_epilogue_matches_two_step_form(T, H, I, monkeypatch):
+    from speculators_b200 import ops
+
+    torch.manual_seed(T + I)
+    x = (torch.randn(T, H, device="cuda") * 0.8).to(torch.bfloat16)
+    w = (torch.randn(2 * I, H, device="cuda") * 0.08).to(torch.bfloat16)
+    dh = (torch.randn(T, I, device="cuda")).to(torch.bfloat16)
+
+    def run(fused):
+        monkeypatch.setenv("SB200_FUSED_SWIGLU", "1" if fused else "0")
+        xa, wa = x.clone().requires_grad_(), w.clone().requires_grad_()
+        h = ops.linear_swiglu(xa, wa) if fused else None
+        if not fused:
+            assert ops.linear_swiglu(xa, wa) is None
+            h = ops.swiglu(ops.linear(xa, wa))
+        h.backward(dh)
+        return h.detach(), xa.grad, wa.grad
+
+    h1, dx1, dw1 = run(True)
+    h0, dx0, dw0 = run(False)
+    ops.check_gemm_status()
+    # fp32 reference of the op: silu(x Wg^T) * (x Wu^T) from bf16-rounded gate / up
+    gu = (x.float() @ w.float().t()).to(torch.bfloat16).float()
+    g, u = gu[:, :I], gu[:, I:]
+    ref = (torch.nn.functional.silu(g).to(torch.bfloat16).float() * u)
+    torch.testing.assert_close(h1.float(), ref, rtol=2e-2, atol=2e-2)
+    # same accumulation and the same rounding points as the two-step form
+    assert torch.equal(h1, h0)
+    assert torch.equal(dx1, dx0) and torch.equal(dw1, dw0)

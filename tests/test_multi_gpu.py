@@ -68,6 +68,10 @@ def _engine_worker(rank, world, port, out_path):
         assert (comm_ms is not None and comm_ms > 0) if mode == "nccl" else comm_ms is None, (mode, comm_ms)
         results[mode] = (eng.flat_w.float().clone(), eng.master.clone(), eng.lo, eng.hi)
         eng.close()
+    # replicated data parallelism (no shard flag) takes the sharded, fused step as well
+    auto = TrainEngine(make(), EngineConfig(lr=lr, shard=False, compute_dtype=torch.bfloat16), device=f"cuda:{rank}")
+    assert auto.sharded and auto.p2p
+    auto.close()
     lo, hi = results["p2p"][2:]
     # the fused path sums the ranks' gradients in fp32; NCCL sums them in bf16
     p2p_err = (results["p2p"][1] - ref_w[lo:hi]).abs().max().item()
