@@ -21,6 +21,9 @@ generates for a seed, so the result equals the single-device forward (tested wit
 
 from __future__ import annotations
 
+import json
+from pathlib import Path
+
 import torch
 import torch.distributed as dist
 
@@ -33,6 +36,45 @@ from speculators_b200.verifier.model import _seeded
 __all__ = ["TensorParallelVerifier"]
 
 
+class _ShardedCheckpoint:
+    """Slices of the tensors of a Hugging Face safetensors checkpoint (single file or sharded with an
+    index): a rank reads only the rows / columns it owns."""
+
+    def __init__(self, path: str | Path):
+        from speculators_b200.utils.loading import _weight_map, resolve_checkpoint_file
+
+        self.path = Path(path)
+        self.files = _weight_map(self.path)  # tensor name -> file
+        self._resolve = resolve_checkpoint_file
+        self._open: dict[str, object] = {}
+
+    def _handle(self, key: str):
+        from safetensors import safe_open
+
+        file = self.files[key]
+        if file not in self._open:
+            self._open[file] = safe_open(str(self._resolve(self.path, file)), framework="pt", device="cpu")
+        return self._open[file]
+
+    def key(self, name: str) -> str | None:
+        """The checkpoint's spelling of ``name`` (exact, or with a prefix such as ``language_model.``)."""
+        if name in self.files:
+            return name
+        hits = [k for k in self.files if k.endswith("." + name) or k.endswith(name)]
+        return min(hits, key=len) if hits else None
+
+    def read(self, key: str, rows: tuple[int, int] | None = None, cols: tuple[int, int] | None = None) -> torch.Tensor:
+        view = self._handle(key).get_slice(key)
+        if rows is not None:
+            return view[rows[0] : rows[1]]
+        if cols is not None:
+            return view[:, cols[0] : cols[1]]
+        return view[:]
+
+    def close(self) -> None:
+        self._open.clear()
+
+
 class TensorParallelVerifier:
     def __init__(self, config: TransformerLayerConfig | dict, group=None, seed: int = 0, device="cpu", dtype=torch.float32,
                  resident: bool = False, sliced_init: bool = False, max_tokens: int | None = None, comm: str | None = None):
@@ -43,6 +85,7 @@ class TensorParallelVerifier:
         from ``RandomVerifier``'s for the same seed, which only matters to tests)."""
         self.resident, self.sliced_init = bool(resident), bool(sliced_init)
         self._layers: dict[int, DecoderLayer] = {}
+        self._checkpoint: _ShardedCheckpoint | None = None  # set by ``from_pretrained``: weights come from files, not from seeds
         self.cfg = TransformerLayerConfig.from_any(config)
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -81,8 +124,48 @@ class TensorParallelVerifier:
         comm.connect()
         return comm
 
+    @classmethod
+    def from_pretrained(cls, path: str | Path, group=None, device="cuda", dtype=torch.bfloat16, max_tokens: int | None = None,
+                        comm: str | None = None) -> "TensorParallelVerifier":
+        """A verifier with the weights of a Hugging Face checkpoint directory (``config.json`` + safetensors):
+        dense Llama / Qwen3 style decoders.  Every rank reads only its slices (query / KV heads and MLP columns
+        by rows, ``o_proj`` / ``down_proj`` by columns), layer by layer at the first forward, and keeps them on
+        the device."""
+        root = Path(path)
+        config = json.loads((root / "config.json").read_text())
+        config = config.get("text_config", config)
+        self = cls(config, group=group, device=device, dtype=dtype, resident=True, max_tokens=max_tokens, comm=comm)
+        self._checkpoint = _ShardedCheckpoint(root)
+        return self
+
     def embed_weight(self) -> torch.Tensor:
+        if self._checkpoint is not None:
+            key = self._checkpoint.key("embed_tokens.weight")
+            if key is None:
+                raise KeyError("the checkpoint holds no embed_tokens.weight")
+            return self._checkpoint.read(key).to(device=self.device, dtype=self.dtype)
         return _seeded((self.cfg.vocab_size, self.cfg.hidden_size), 0.02, self.seed * 1000 + 900, self.device, self.dtype)
+
+    def _checkpoint_layer_state(self, idx: int, names: list[str]) -> dict[str, torch.Tensor]:
+        """This rank's slices of layer ``idx`` under the layer's own (Hugging Face) tensor names."""
+        ck, R, r = self._checkpoint, self.world, self.rank
+        state = {}
+        for name in names:
+            key = ck.key(f"layers.{idx}.{name}")
+            if key is None:
+                raise KeyError(f"layers.{idx}.{name} is not in the checkpoint at {ck.path}")
+            module, kind = name.rsplit(".", 2)[-2:]
+            if module in ("q_proj", "k_proj", "v_proj", "gate_proj", "up_proj"):  # column parallel: split the output features
+                n = ck._handle(key).get_slice(key).get_shape()[0]  # noqa: SLF001
+                state[name] = ck.read(key, rows=(r * n // R, (r + 1) * n // R))
+            elif module in ("o_proj", "down_proj"):  # row parallel: split the input features
+                if kind == "bias":
+                    raise ValueError(f"{name}: a bias on a row-parallel projection is not supported by the tensor-parallel verifier")
+                n = ck._handle(key).get_slice(key).get_shape()[1]  # noqa: SLF001
+                state[name] = ck.read(key, cols=(r * n // R, (r + 1) * n // R))
+            else:  # norms: replicated
+                state[name] = ck.read(key)
+        return state
 
     def _slice(self, name: str, full: torch.Tensor) -> torch.Tensor:
         """This rank's part of a full layer tensor."""
@@ -104,8 +187,12 @@ class TensorParallelVerifier:
             return self._layers[idx]
         layer = DecoderLayer(self.local_cfg, idx)
         own = dict(layer.named_parameters())
+        if self._checkpoint is not None:
+            # the layer's state dict speaks the checkpoint's names (fused projections are split on save / merged on load)
+            layer.load_state_dict(self._checkpoint_layer_state(idx, list(layer.state_dict().keys())), strict=True)
+            layer.to(device=self.device, dtype=self.dtype)
         with torch.no_grad():
-            for j, (name, shape) in enumerate(self._full_shapes):
+            for j, (name, shape) in enumerate(self._full_shapes if self._checkpoint is None else []):
                 p = own[name]
                 if len(shape) == 2 and self.sliced_init:
                     p.data = _seeded(tuple(p.shape), 0.02, ((self.seed * 1000 + idx) * 64 + j) * 16 + self.rank, self.device, self.dtype)

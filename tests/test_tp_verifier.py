@@ -45,3 +45,74 @@ def test_two_rank_tensor_parallel_forward_equals_single_device(tmp_path):
         for key in ("hidden_states", "verifier_last_hidden_states"):
             assert got[key].shape == want[key].shape
             assert torch.allclose(got[key], want[key], atol=2e-5, rtol=1e-4), (rank, key, float((got[key] - want[key]).abs().max()))
+
+
+# ---- weights from a Hugging Face style checkpoint -----------------------------------------------------
+def _write_checkpoint(path):
+    """Three full layers and the embedding, saved under Hugging Face names in two shards with an index."""
+    import json
+
+    from safetensors.torch import save_file
+
+    from speculators_b200.layer_config import TransformerLayerConfig
+    from speculators_b200.models.layers import DecoderLayer
+
+    torch.manual_seed(11)
+    cfg = TransformerLayerConfig(**CFG)
+    tensors = {"model.embed_tokens.weight": torch.randn(CFG["vocab_size"], CFG["hidden_size"]) * 0.05}
+    layers = []
+    for i in range(CFG["num_hidden_layers"]):
+        layer = DecoderLayer(cfg, i)
+        with torch.no_grad():
+            for p in layer.parameters():
+                p.copy_(torch.randn_like(p) * (0.05 if p.ndim == 2 else 0.2) + (1.0 if p.ndim == 1 else 0.0))
+        layers.append(layer)
+        tensors.update({f"model.layers.{i}.{k}": v.clone() for k, v in layer.state_dict().items()})
+    os.makedirs(path, exist_ok=True)
+    names = sorted(tensors)
+    shards = {"model-00001-of-00002.safetensors": names[::2], "model-00002-of-00002.safetensors": names[1::2]}
+    for file, keys in shards.items():
+        save_file({k: tensors[k].contiguous() for k in keys}, os.path.join(path, file))
+    with open(os.path.join(path, "model.safetensors.index.json"), "w") as fh:
+        json.dump({"weight_map": {k: f for f, keys in shards.items() for k in keys}}, fh)
+    with open(os.path.join(path, "config.json"), "w") as fh:
+        json.dump(CFG, fh)
+    return tensors["model.embed_tokens.weight"], layers
+
+
+def _checkpoint_worker(rank, world, port, ckpt, out_path):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    ids, doc, pos = _inputs()
+    tp = TensorParallelVerifier.from_pretrained(ckpt, device="cpu", dtype=torch.float32)
+    out = tp.forward(ids, [0, 2], document_ids=doc, position_ids=pos)
+    torch.save(out, f"{out_path}.{rank}")
+    dist.barrier()
+    dist.destroy_process_group()
+    os._exit(0)
+
+
+def test_tensor_parallel_verifier_loads_checkpoint_slices(tmp_path):
+    from speculators_b200.models.eagle3.attention import causal_document_interval
+    from speculators_b200.models.layers import RotaryTable
+    from speculators_b200.layer_config import TransformerLayerConfig
+    from speculators_b200.ops import AttnSpec
+
+    ckpt = str(tmp_path / "ckpt")
+    embed, layers = _write_checkpoint(ckpt)
+    ids, doc, pos = _inputs()
+    lo, hi = causal_document_interval(doc)
+    rotary = RotaryTable(TransformerLayerConfig(**CFG))
+    with torch.no_grad():  # the plain single-device forward over the full layers
+        h = torch.nn.functional.embedding(ids, embed)
+        kept = {}
+        for i, layer in enumerate(layers):
+            h = layer(h, pos, rotary, AttnSpec(lo=lo, hi=hi))
+            kept[i] = h
+    want = {"hidden_states": torch.cat([kept[0], kept[2]], dim=-1), "verifier_last_hidden_states": h}
+    out = tmp_path / "tpck"
+    mp.spawn(_checkpoint_worker, args=(2, 29683, ckpt, str(out)), nprocs=2, join=True)
+    for rank in range(2):
+        got = torch.load(f"{out}.{rank}")
+        for key in want:
+            assert torch.allclose(got[key], want[key], atol=2e-5, rtol=1e-4), (rank, key, float((got[key] - want[key]).abs().max()))
