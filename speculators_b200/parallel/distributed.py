@@ -41,6 +41,7 @@ class _Topology:
         self.dp_rank = 0
         self.sp_group = None
         self.dp_group = None
+        self.train_group = None  # the ranks that train, when they are a sub-group of the job (online verifier / trainer split)
 
 
 _T = _Topology()
@@ -60,6 +61,33 @@ def get_world_size() -> int:
 
 def is_distributed() -> bool:
     return _T.distributed
+
+
+def set_training_group(group) -> None:
+    """Declare the process group of the training ranks when other ranks of the job do something else (run
+    the verifier): "rank 0" duties (checkpoint files, progress bar, metric sinks) and the barriers around
+    them then refer to this group."""
+    _T.train_group = group
+
+
+def get_training_group():
+    return _T.train_group
+
+
+def training_rank() -> int:
+    """Rank inside the training group (the job's rank when none is declared); -1 outside of it."""
+    if _T.train_group is None or not (dist.is_available() and dist.is_initialized()):
+        return dist.get_rank() if (dist.is_available() and dist.is_initialized()) else _T.rank
+    return dist.get_rank(_T.train_group)
+
+
+def training_barrier() -> None:
+    if not (dist.is_available() and dist.is_initialized()):
+        return
+    if _T.train_group is None:
+        dist.barrier()
+    elif dist.get_rank(_T.train_group) >= 0:
+        dist.barrier(group=_T.train_group)
 
 
 def get_sp_group():

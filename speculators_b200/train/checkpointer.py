@@ -43,12 +43,17 @@ TRAIN_COMMAND_FILENAME = "train_command.txt"
 
 
 def _is_rank0() -> bool:
-    return not (dist.is_available() and dist.is_initialized()) or dist.get_rank() == 0
+    """The writer of checkpoint files: rank 0 of the training ranks (of the whole job unless a training
+    sub-group is declared, ``parallel.distributed.set_training_group``)."""
+    from speculators_b200.parallel.distributed import training_rank
+
+    return not (dist.is_available() and dist.is_initialized()) or training_rank() == 0
 
 
 def _barrier() -> None:
-    if dist.is_available() and dist.is_initialized():
-        dist.barrier()
+    from speculators_b200.parallel.distributed import training_barrier
+
+    training_barrier()
 
 
 def convert_float_dtype(obj, dtype: torch.dtype):

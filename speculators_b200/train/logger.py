@@ -85,6 +85,11 @@ class IsRank0Filter(logging.Filter):
     def _rank(self) -> int:
         if self.rank_val is not None:
             return self.rank_val
+        if not self.local_rank:
+            from speculators_b200.parallel.distributed import get_training_group, training_rank
+
+            if get_training_group() is not None:  # the training ranks are a sub-group of the job: its first rank speaks
+                return training_rank()
         return int(os.environ.get("LOCAL_RANK" if self.local_rank else "RANK", "0"))
 
     def filter(self, record: logging.LogRecord) -> bool:

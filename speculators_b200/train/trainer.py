@@ -30,7 +30,7 @@ import torch
 import torch.distributed as dist
 
 from speculators_b200.model import SpeculatorModel
-from speculators_b200.parallel.distributed import get_local_rank, get_rank, is_distributed
+from speculators_b200.parallel.distributed import get_local_rank, get_rank, is_distributed, set_training_group, training_rank
 from speculators_b200.parallel.engine import EngineConfig, TrainEngine
 from speculators_b200.train.checkpointer import Checkpointer
 from speculators_b200.train.graceful_shutdown import with_graceful_shutdown
@@ -272,7 +272,9 @@ class Trainer:
         self.model = model
         self.config = config
         self.local_rank = get_local_rank()
-        self.rank = get_rank()
+        if config.process_group is not None:
+            set_training_group(config.process_group)
+        self.rank = training_rank() if config.process_group is not None else get_rank()
         self.train_loader = train_loader
         self.val_loader = val_loader
         self.is_distributed = is_distributed() or (dist.is_available() and dist.is_initialized())
@@ -295,7 +297,7 @@ class Trainer:
         return self.checkpointer.path / str(epoch) / "training_state.json"
 
     def _save_training_state(self, epoch: int, local_step: int) -> None:
-        if not self.is_distributed or dist.get_rank() == 0:
+        if not self.is_distributed or training_rank() == 0:
             path = self._training_state_path(epoch)
             path.parent.mkdir(parents=True, exist_ok=True)
             path.write_text(json.dumps({"epoch": epoch, "local_step": local_step, "global_step": self.global_step}))
@@ -542,7 +544,8 @@ class Trainer:
             stacked = torch.stack(entries) if entries else torch.zeros(0, device=self.device)
             if self.is_distributed and n_metrics:
                 head = stacked[:n_metrics].clone()
-                dist.reduce(head, dst=0, op=dist.ReduceOp.SUM)
+                group = self.config.process_group
+                dist.reduce(head, dst=dist.get_global_rank(group, 0) if group is not None else 0, op=dist.ReduceOp.SUM, group=group)
                 stacked = torch.cat([head, stacked[n_metrics:]])
             if status is not None:
                 stacked = torch.cat([stacked, status])
@@ -612,7 +615,7 @@ class Trainer:
             if comm is not None:
                 profile["comm_ms"] = comm
                 profile["comm_frac"] = comm / profile["step_ms"] if profile["step_ms"] > 0 else 0.0
-        world = dist.get_world_size() if self.is_distributed else 1
+        world = dist.get_world_size(self.config.process_group) if self.is_distributed else 1
         metric_logger.info(
             {"train": normalize_counted_metrics(values, world), "profile": profile, "epoch": pending["epoch"], "lr": pending["lr"],
              "global_step": pending["global_step"]},
@@ -623,7 +626,7 @@ class Trainer:
         if not self.is_distributed or _VAL_SYNC_INTERVAL <= 0:
             return
         if batch_index > 0 and batch_index % _VAL_SYNC_INTERVAL == 0:
-            dist.barrier()
+            dist.barrier(group=self.config.process_group)
 
     @torch.no_grad()
     def val_epoch(self, epoch: int) -> dict[str, float] | None:
@@ -645,9 +648,9 @@ class Trainer:
         if accumulated:
             stacked = torch.stack([v.reshape(()) for v in accumulated.values()])
             if self.is_distributed:
-                dist.all_reduce(stacked, op=dist.ReduceOp.SUM)
+                dist.all_reduce(stacked, op=dist.ReduceOp.SUM, group=self.config.process_group)
             val_metrics = dict(zip(accumulated, stacked.tolist(), strict=True))
-        world = dist.get_world_size() if self.is_distributed else 1
+        world = dist.get_world_size(self.config.process_group) if self.is_distributed else 1
         val_metrics = {k: v / max(1, num_batches) for k, v in val_metrics.items()}
         val_metrics = {f"{k}_epoch": v for k, v in normalize_counted_metrics(val_metrics, world).items()}
         metric_logger.info({"val": val_metrics, "epoch": epoch}, extra={"step": self.global_step})
@@ -669,7 +672,7 @@ class Trainer:
             self.checkpointer.save_scheduler_state_dict(self.schedulers, epoch)
         if isinstance(epoch, int):
             self._save_training_state(epoch, local_step)
-            if not self.is_distributed or dist.get_rank() == 0:
+            if not self.is_distributed or training_rank() == 0:
                 root = self.checkpointer.path
                 for old in root.glob(f"epoch{epoch}_*"):
                     if old.is_symlink():
@@ -699,7 +702,7 @@ class Trainer:
 
     def _barrier(self) -> None:
         if self.is_distributed:
-            dist.barrier()
+            dist.barrier(group=self.config.process_group)
 
     @with_graceful_shutdown()
     def run_training(self) -> None:
