@@ -105,6 +105,9 @@ class GenerationArgs(_Group):
     on_generate: Literal["cache", "delete"] = Field(default="delete", description="Keep or drop hidden states generated on the fly.")
     request_timeout: float = Field(default=DEFAULT_REQUEST_TIMEOUT, description="Seconds per generation request.")
     max_retries: int = Field(default=DEFAULT_MAX_RETRIES, description="Retries per generation request.")
+    online_verifier_gpus: int = Field(default=0, description="Run the verifier inside the job, tensor-parallel on the first N ranks; the other ranks train on hidden states handed GPU to GPU (0: off).")
+    online_ring_slots: int = Field(default=4, description="Samples the in-job verifier may run ahead of a trainer rank.")
+    online_timeout: float = Field(default=600.0, description="Seconds a rank of the in-job verifier / trainer split waits for the other side.")
 
 
 class LossArgs(_Group):

@@ -223,6 +223,63 @@ def build_draft_model(args: argparse.Namespace, model_class: type[SpeculatorMode
     return model_class.from_training_args(verifier_config=layer_config, t2d=t2d, d2t=d2t, **vars(args))
 
 
+def _trainer_config(args, model_class, dtype, **extra) -> TrainerConfig:
+    train_kwargs, val_kwargs = model_class.get_trainer_kwargs(**vars(args))
+    return TrainerConfig(
+        num_epochs=args.epochs, save_path=args.save_path, lr=args.lr, resume_from_checkpoint=not args.no_resume_from_checkpoint,
+        train_call_kwargs=train_kwargs, val_call_kwargs=val_kwargs, optimizer=args.optimizer, weight_decay=args.weight_decay,
+        muon_lr=args.muon_lr, muon_momentum=args.muon_momentum, muon_weight_decay=args.muon_weight_decay,
+        muon_ns_steps=args.muon_ns_steps, muon_adjust_lr_fn=args.muon_adjust_lr_fn, scheduler_type=args.scheduler_type,
+        scheduler_warmup_steps=args.scheduler_warmup_steps, scheduler_warmup_ratio=args.scheduler_warmup_ratio,
+        scheduler_total_steps=args.scheduler_total_steps, scheduler_num_cosine_cycles=args.scheduler_num_cosine_cycles,
+        checkpoint_freq=args.checkpoint_freq, save_best=args.save_best, hidden_states_dtype=dtype, log_freq=args.log_freq,
+        fsdp_shard=args.fsdp_shard, max_steps=args.max_steps, **extra,
+    )
+
+
+def _run_online(args, model, model_class, dtype) -> None:
+    """``--online-verifier-gpus N``: no hidden-state files and no server.  The first N ranks load the verifier
+    (tensor-parallel, each its slices of the checkpoint) and run the packed rows of the dataset in the order the
+    multipack sampler gives the trainer ranks; the other ranks train on the states that arrive in their NVLink
+    rings.  The reference reaches the same end with a vLLM server on part of the GPUs and ``--on-missing
+    generate`` (scripts/launch_vllm.py, docs/user_guide/tutorials/train.md:165-170)."""
+    import torch.distributed as dist
+
+    from speculators_b200.train.noise_transforms import AddUniformNoise
+    from speculators_b200.train.online import OnlineSplit
+    from speculators_b200.train.online_data import OnlineBatchPlan
+
+    if args.speculator_type not in ("eagle3", "peagle"):
+        raise ValueError("--online-verifier-gpus supports the eagle3 and peagle speculator types (hidden states paired token by token)")
+    if not is_distributed() or dist.get_world_size() <= args.online_verifier_gpus:
+        raise ValueError("--online-verifier-gpus N needs a torchrun job of more than N ranks (N verifier ranks, the rest train)")
+    if not torch.cuda.is_available():
+        raise ValueError("--online-verifier-gpus needs CUDA devices with peer access (the hidden states travel over NVLink)")
+    world, n_ver = dist.get_world_size(), int(args.online_verifier_gpus)
+    device = torch.device("cuda", torch.cuda.current_device())
+    plan = OnlineBatchPlan(args.data_path, args.total_seq_len, world - n_ver, seed=args.seed, train_ratio=args.train_data_ratio)
+    verifier_cfg = read_config_json(args.verifier_name_or_path)
+    verifier_cfg = verifier_cfg.get("text_config", verifier_cfg)
+    split = OnlineSplit(verifier_cfg, list(model.target_layer_ids), args.total_seq_len, device, n_verifier=n_ver, n_slots=args.online_ring_slots,
+                        timeout_s=args.online_timeout, verifier_path=args.verifier_name_or_path, plan=plan,
+                        transform=AddUniformNoise(std=args.noise_std) if args.noise_std > 0 else None)
+    first_trainer = n_ver
+    progress: list = [None, None]  # epoch and optimizer steps the trainer resumes from
+    if split.topo.is_verifier:
+        del model
+        dist.broadcast_object_list(progress, src=first_trainer)
+        budget = None if args.max_steps is None else max(0, int(args.max_steps) - int(progress[1])) + 1  # + the batch a trainer looks ahead
+        served = split.serve(int(progress[0]), int(args.epochs), budget)
+        log.info("in-job verifier served %d steps", served, extra={"override_rank0_filter": True})
+    else:
+        trainer = Trainer(model, _trainer_config(args, model_class, dtype, process_group=split.trainer_group), split.training_loader(), None)
+        progress = [int(trainer.current_epoch), int(trainer.global_step)]
+        dist.broadcast_object_list(progress, src=first_trainer)
+        trainer.run_training()
+        del trainer
+    split.close()
+
+
 def main(cfg: TrainConfig) -> None:
     args = argparse.Namespace(**cfg.flatten())
     set_seed(args.seed, args.deterministic_cuda)
@@ -259,6 +316,11 @@ def main(cfg: TrainConfig) -> None:
         maybe_destroy_distributed()
         return
 
+    if args.online_verifier_gpus > 0:
+        _run_online(args, model, model_class, dtype)
+        maybe_destroy_distributed()
+        return
+
     hidden_size = model.config.transformer_layer_config.hidden_size
     preprocess = {"eagle3": shift_batch, "peagle": shift_batch, "mtp": shift_batch_mtp}.get(args.speculator_type)
     transfer = HiddenStatesBackend.registry[args.hidden_states_backend].from_train_args(args, args.data_path)
@@ -269,17 +331,7 @@ def main(cfg: TrainConfig) -> None:
         hidden_size=hidden_size, num_target_layers=num_target_layers, num_workers=args.num_workers,
         prefetch_factor=args.prefetch_factor, preprocess=preprocess, train_data_ratio=args.train_data_ratio,
     )
-    train_kwargs, val_kwargs = model_class.get_trainer_kwargs(**vars(args))
-    trainer = Trainer(model, TrainerConfig(
-        num_epochs=args.epochs, save_path=args.save_path, lr=args.lr, resume_from_checkpoint=not args.no_resume_from_checkpoint,
-        train_call_kwargs=train_kwargs, val_call_kwargs=val_kwargs, optimizer=args.optimizer, weight_decay=args.weight_decay,
-        muon_lr=args.muon_lr, muon_momentum=args.muon_momentum, muon_weight_decay=args.muon_weight_decay,
-        muon_ns_steps=args.muon_ns_steps, muon_adjust_lr_fn=args.muon_adjust_lr_fn, scheduler_type=args.scheduler_type,
-        scheduler_warmup_steps=args.scheduler_warmup_steps, scheduler_warmup_ratio=args.scheduler_warmup_ratio,
-        scheduler_total_steps=args.scheduler_total_steps, scheduler_num_cosine_cycles=args.scheduler_num_cosine_cycles,
-        checkpoint_freq=args.checkpoint_freq, save_best=args.save_best, hidden_states_dtype=dtype, log_freq=args.log_freq,
-        fsdp_shard=args.fsdp_shard, max_steps=args.max_steps,
-    ), train_loader, val_loader)
+    trainer = Trainer(model, _trainer_config(args, model_class, dtype), train_loader, val_loader)
     trainer.run_training()
     del trainer, model
     gc.collect()

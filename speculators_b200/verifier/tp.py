@@ -86,6 +86,10 @@ class TensorParallelVerifier:
         self.resident, self.sliced_init = bool(resident), bool(sliced_init)
         self._layers: dict[int, DecoderLayer] = {}
         self._checkpoint: _ShardedCheckpoint | None = None  # set by ``from_pretrained``: weights come from files, not from seeds
+        # what a layer id names: False = the output of decoder layer ``id`` (``RandomVerifier``'s numbering); True = the
+        # state after ``id`` layers, i.e. Hugging Face ``hidden_states[id]`` and the numbering of vLLM's
+        # ``eagle_aux_hidden_state_layer_ids`` (0 = embeddings, ``num_hidden_layers`` = the last layer's output)
+        self.layers_counted = False
         self.cfg = TransformerLayerConfig.from_any(config)
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -136,6 +140,7 @@ class TensorParallelVerifier:
         config = config.get("text_config", config)
         self = cls(config, group=group, device=device, dtype=dtype, resident=True, max_tokens=max_tokens, comm=comm)
         self._checkpoint = _ShardedCheckpoint(root)
+        self.layers_counted = True  # a real verifier's states must be the ones a vLLM server hands out for the same ids
         return self
 
     def embed_weight(self) -> torch.Tensor:
@@ -232,6 +237,9 @@ class TensorParallelVerifier:
             h = torch.nn.functional.embedding(ids, self.embed_weight())
         taken: dict[int, torch.Tensor] = {}
         fused = self.comm is not None
+        shift = 1 if self.layers_counted else 0
+        if self.layers_counted and 0 in layer_ids:
+            taken[0] = h
         for i in range(int(self.cfg.num_hidden_layers)):
             layer = self._layer(i)
             if fused:
@@ -242,8 +250,8 @@ class TensorParallelVerifier:
             else:
                 h = h + self._reduce(layer.self_attn(layer.input_layernorm(h), pos, self.rotary, spec))
                 h = h + self._reduce(layer.mlp(layer.post_attention_layernorm(h)))
-            if i in layer_ids:
-                taken[i] = h.clone() if fused else h
+            if i + shift in layer_ids:
+                taken[i + shift] = h.clone() if fused else h
             del layer
         if fused:
             h = h.clone()

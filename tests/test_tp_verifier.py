@@ -85,7 +85,7 @@ def _checkpoint_worker(rank, world, port, ckpt, out_path):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     ids, doc, pos = _inputs()
     tp = TensorParallelVerifier.from_pretrained(ckpt, device="cpu", dtype=torch.float32)
-    out = tp.forward(ids, [0, 2], document_ids=doc, position_ids=pos)
+    out = tp.forward(ids, [1, 3], document_ids=doc, position_ids=pos)  # counted ids: states after 1 and after 3 layers
     torch.save(out, f"{out_path}.{rank}")
     dist.barrier()
     dist.destroy_process_group()
