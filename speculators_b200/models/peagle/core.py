@@ -30,16 +30,16 @@ from speculators_b200.proposals.greedy import GreedyTokenProposalConfig
 __all__ = ["PEagleDraftModel"]
 
 
-def _fixed_shape_default(explicit: bool | None) -> bool | None:
-    """COD sampling with argument-only shapes: the explicit choice, else ``SB200_PEAGLE_FIXED_SHAPE``
-    (``1`` / ``0``), else ``None`` = decided by the device of the batch (CUDA: fixed shapes, so the
-    step replays as a CUDA graph; CPU: the variable-shape sampler, no padded rows)."""
+def _fixed_shape_default(explicit: bool | None) -> bool:
+    """COD sampling with argument-only shapes: the explicit choice, else ``SB200_PEAGLE_FIXED_SHAPE=1``.
+
+    Opt-in because the fixed shapes are sized for a full loss mask: on the 70B-shaped benchmark row
+    (about half of the positions inside the mask) the padded sampler's step, replayed as a CUDA graph, took
+    53.9 ms against 44.1 ms for the variable-shape sampler's eager step on the same GPU - the padding rows cost
+    more than the launch gaps save.  It pays when most positions are supervised."""
     import os
 
-    if explicit is not None:
-        return bool(explicit)
-    env = os.environ.get("SB200_PEAGLE_FIXED_SHAPE")
-    return None if env not in ("0", "1") else env == "1"
+    return bool(explicit) if explicit is not None else os.environ.get("SB200_PEAGLE_FIXED_SHAPE") == "1"
 
 
 @SpeculatorModel.register("peagle")
@@ -51,28 +51,25 @@ class PEagleDraftModel(Eagle3DraftModel):
 
     def __init__(self, config: PEagleSpeculatorConfig):
         super().__init__(config)
-        # with the fixed-shape sampler (the default on CUDA) every tensor shape of the step is static
-        self.cuda_graph_safe = _fixed_shape_default(None) is not False
+        # with the fixed-shape sampler every tensor shape of the step is static (decided per call: ``graph_safe_with``)
+        self.cuda_graph_safe = True
         self.mask_token_id = config.mask_token_id
         self.mask_hidden = nn.Parameter(torch.randn(1, 1, self.num_aux * self.hidden_size))
 
     def forward(
         self, hidden_states, input_ids, document_ids, position_ids=None, loss_mask=None, verifier_last_hidden_states=None,
         loss_config: LossConfig | None = None, max_anchors: int | None = None, num_depths: int = 8,
-        down_sample_ratio: float = 0.7, down_sample_ratio_min: float = 0.2, fixed_shape: bool | None = None, cod_sample=None, **_,
+        down_sample_ratio: float = 0.7, down_sample_ratio_min: float = 0.2, fixed_shape: bool = False, cod_sample=None, **_,
     ):
         """``fixed_shape``: draw the COD sample with shapes that depend only on the
         arguments (rows the mask rules out are carried as inert padding), which makes the
-        step capturable in a CUDA graph; ``None``: fixed shapes on CUDA batches.  ``cod_sample``: a ready
+        step capturable in a CUDA graph.  ``cod_sample``: a ready
         ``(anchor_pos, depth[, row_valid])`` to use instead of drawing one."""
         if verifier_last_hidden_states is None:
             raise ValueError("verifier_last_hidden_states required for training")
         if self.mask_token_id is None:
             raise ValueError("mask_token_id is not set on the config; pass --mask-token-id")
         device = hidden_states.device
-        if fixed_shape is None:
-            fixed_shape = _fixed_shape_default(None)
-            fixed_shape = hidden_states.is_cuda if fixed_shape is None else fixed_shape
         T = input_ids.shape[1]
         dtype = self.fc.weight.dtype
         if loss_mask is None:
@@ -147,9 +144,8 @@ class PEagleDraftModel(Eagle3DraftModel):
         return model
 
     def graph_safe_with(self, call_kwargs: dict) -> bool:
-        """Whether a step called with ``call_kwargs`` has static shapes (an explicit
-        ``fixed_shape=False`` asks for the variable-shape sampler)."""
-        return self.cuda_graph_safe and call_kwargs.get("fixed_shape") is not False
+        """Whether a step called with ``call_kwargs`` has static shapes: only with the fixed-shape sampler."""
+        return bool(call_kwargs.get("fixed_shape"))
 
     @staticmethod
     def get_trainer_kwargs(**kwargs) -> tuple[dict, dict]:

@@ -471,7 +471,7 @@ def linear_swiglu(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor | None:
     import os
 
     x2 = x.reshape(-1, x.shape[-1])
-    if (not _own_gemm_enabled() or os.environ.get("SB200_FUSED_SWIGLU", "0") != "1" or not _gemm_operand_ok(x2) or not _gemm_operand_ok(weight)
+    if (not _own_gemm_enabled() or os.environ.get("SB200_FUSED_SWIGLU", "1") == "0" or not _gemm_operand_ok(x2) or not _gemm_operand_ok(weight)
             or weight.shape[0] % 256 or weight.shape[1] != x2.shape[1]):
         return None
     h = _GateUpSwiGLUFn.apply(x2, weight)

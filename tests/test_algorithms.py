@@ -131,8 +131,8 @@ def test_cod_fixed_shape_sampler_and_inert_padding(tiny_verifier_dir, tiny_vocab
     torch.testing.assert_close(loss_fix, loss_var, rtol=1e-5, atol=1e-6)
     for key in m_var:
         torch.testing.assert_close(m_fix[key].float(), m_var[key].float(), rtol=1e-5, atol=1e-6)
-    assert kw["fixed_shape"] is None  # decided by the batch's device; cod_fixed_shape / SB200_PEAGLE_FIXED_SHAPE force it
-    assert model.graph_safe_with(kw) and not model.graph_safe_with({**kw, "fixed_shape": False})
+    assert kw["fixed_shape"] is False  # opt-in: cod_fixed_shape=True or SB200_PEAGLE_FIXED_SHAPE=1
+    assert not model.graph_safe_with(kw) and model.graph_safe_with({**kw, "fixed_shape": True})
     kw_fixed, _ = PEagleDraftModel.get_trainer_kwargs(loss_fn="kl_div", num_depths=D, cod_fixed_shape=True)
     _, loss_drawn, _ = model(**batch, **kw_fixed)
     loss_drawn.backward()

@@ -82,8 +82,8 @@ def test_gpu_loss_matches_cpu_fp32(algo, head_dim, tmp_path):
 
 @pytest.mark.parametrize("algo", ["dflash", "dspark", "peagle"])
 def test_cuda_graph_steps(algo, tmp_path, monkeypatch):
-    # P-EAGLE's step is graph-capturable because CUDA batches get the fixed-shape COD sampler
-    monkeypatch.delenv("SB200_PEAGLE_FIXED_SHAPE", raising=False)
+    # P-EAGLE's step is graph-capturable only with the fixed-shape COD sampler (opt-in)
+    monkeypatch.setenv("SB200_PEAGLE_FIXED_SHAPE", "1")
     model, kwargs = _build(algo, tmp_path, 128)
     batch = _batch()
     trainer = Trainer(model, TrainerConfig(lr=1e-3, num_epochs=1, save_path=tempfile.mkdtemp(), train_call_kwargs=kwargs, scheduler_type="none",

@@ -374,3 +374,103 @@ def test_tensor_parallel_verifier_fused_exchange_matches_all_reduce(tmp_path):
     out = tmp_path / "tp.json"
     mp.spawn(_tp_worker, args=(2, 29691, str(out)), nprocs=2, join=True)
     assert json.loads(out.read_text())["ok"] == [True, True]
+
+
+# ---- online training from a dataset: verifier on GPU 0, trainer on GPU 1, against the file path ----------------
+_ONLINE_CFG = dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=256, intermediate_size=512, num_hidden_layers=4,
+                   num_attention_heads=4, num_key_value_heads=2, head_dim=64, vocab_size=512, max_position_embeddings=1024, rms_norm_eps=1e-5,
+                   rope_theta=10000.0, hidden_act="silu")
+
+
+def _write_full_verifier(path):
+    """A complete tiny checkpoint (embeddings, layers, norm, lm_head) under Hugging Face names."""
+    from safetensors.torch import save_file
+
+    from speculators_b200.layer_config import TransformerLayerConfig
+    from speculators_b200.models.layers import DecoderLayer
+
+    torch.manual_seed(21)
+    cfg = TransformerLayerConfig(**_ONLINE_CFG)
+    tensors = {"model.embed_tokens.weight": torch.randn(512, 256) * 0.05, "lm_head.weight": torch.randn(512, 256) * 0.05,
+               "model.norm.weight": torch.ones(256)}
+    for i in range(4):
+        layer = DecoderLayer(cfg, i)
+        with torch.no_grad():
+            for p in layer.parameters():
+                p.copy_(torch.randn_like(p) * 0.04 if p.ndim == 2 else torch.ones_like(p))
+        tensors.update({f"model.layers.{i}.{k}": v.clone().contiguous() for k, v in layer.state_dict().items()})
+    os.makedirs(path, exist_ok=True)
+    save_file({k: v.to(torch.bfloat16) for k, v in tensors.items()}, os.path.join(path, "model.safetensors"))
+    with open(os.path.join(path, "config.json"), "w") as fh:
+        json.dump(_ONLINE_CFG, fh)
+
+
+def _write_token_dataset(root, n=10):
+    from datasets import Dataset
+
+    g = torch.Generator().manual_seed(4)
+    rows = []
+    for _ in range(n):
+        L = int(torch.randint(40, 120, (1,), generator=g))
+        rows.append({"input_ids": torch.randint(0, 512, (L,), generator=g).tolist(), "loss_mask": [0] * 4 + [1] * (L - 4), "seq_len": L})
+    Dataset.from_list(rows).save_to_disk(str(root))
+    freq: dict[int, int] = {}
+    for r in rows:
+        for t in r["input_ids"]:
+            freq[t] = freq.get(t, 0) + 1
+    torch.save(freq, root / "token_freq.pt")
+    return rows
+
+
+def _online_train_worker(rank, world, port, verifier, data, save_online, save_files):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0", SB200_NO_TQDM="1")
+    from speculators_b200.train.config import TrainConfig
+    from speculators_b200.train.entrypoint import main
+
+    def argv(save, *extra):
+        return ["--verifier-name-or-path", verifier, "--data-path", data, "--save-path", save, "--total-seq-len", "256", "--num-workers", "0",
+                "--optimizer", "adamw", "--lr", "1e-3", "--draft-vocab-size", "128", "--target-layer-ids", "1", "2", "3", "--train-data-ratio", "0.8",
+                "--noise-std", "0", "--epochs", "1", "--ttt-steps", "2", "--log-freq", "1", "--scheduler-type", "none", *extra]
+
+    main(TrainConfig.resolve(argv(save_online, "--online-verifier-gpus", "1")))
+    if rank == 1:
+        # the file path on the same data: hidden states written by the same verifier, then a one-GPU run
+        for key in ("RANK", "LOCAL_RANK", "WORLD_SIZE"):
+            os.environ.pop(key)
+        torch.cuda.set_device(0)  # a plain one-GPU run uses the first device
+        from datasets import load_from_disk
+        from safetensors.torch import save_file
+
+        from speculators_b200.verifier.tp import TensorParallelVerifier
+
+        ver = TensorParallelVerifier.from_pretrained(verifier, device="cuda:0", dtype=torch.bfloat16)
+        os.makedirs(os.path.join(data, "hidden_states"), exist_ok=True)
+        for i, row in enumerate(load_from_disk(data)):
+            ids = torch.tensor(row["input_ids"])
+            out = ver.forward(ids, [1, 2, 3])
+            stored = torch.cat([out["hidden_states"], out["verifier_last_hidden_states"]], dim=-1).view(len(ids), 4, 256)
+            save_file({"hidden_states": stored.cpu().contiguous(), "token_ids": ids}, os.path.join(data, "hidden_states", f"hs_{i}.safetensors"))
+        main(TrainConfig.resolve(argv(save_files, "--on-missing", "raise")))
+
+
+def test_online_training_inside_the_job_matches_the_file_path(tmp_path):
+    _need_two()
+    from safetensors.torch import load_file
+
+    verifier, data = str(tmp_path / "verifier"), str(tmp_path / "data")
+    _write_full_verifier(verifier)
+    _write_token_dataset(tmp_path / "data")
+    save_online, save_files = str(tmp_path / "online"), str(tmp_path / "files")
+    mp.spawn(_online_train_worker, args=(2, 29701, verifier, data, save_online, save_files), nprocs=2, join=True)
+    a, b = load_file(os.path.join(save_online, "0", "model.safetensors")), load_file(os.path.join(save_files, "0", "model.safetensors"))
+    assert set(a) == set(b)
+    # the two runs see the same batches in the same order from the same initial weights; what differs is the
+    # rounding inside the verifier's attention (packed rows against single documents), so the trained weights
+    # agree far below the distance the few optimizer steps moved them (about lr per step and element)
+    for key in a:
+        if a[key].is_floating_point() and a[key].numel() > 1:
+            diff = (a[key].float() - b[key].float()).abs()
+            assert float(diff.mean()) < 4e-4 and float(diff.max()) < 2e-2, (key, float(diff.mean()), float(diff.max()))
+    state = json.loads(open(os.path.join(save_online, "0", "training_state.json")).read())
+    assert state["global_step"] >= 2
