@@ -765,10 +765,10 @@ static size_t bwd_smem() {
 
 template <int HD>
 static int launch_fwd_t(const AttnParams& p, cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.needed()) {
     if (cudaFuncSetAttribute(attn_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fwd_smem<HD>()) != cudaSuccess) return -2;
-    configured = true;
+    configured.mark();
   }
   dim3 grid((p.Tq + kBM - 1) / kBM, p.nh);
   count_launch(1);
@@ -778,11 +778,11 @@ static int launch_fwd_t(const AttnParams& p, cudaStream_t stream) {
 
 template <int HD>
 static int launch_bwd_t(const AttnParams& p, int* tile_qmin, int* tile_qmax, cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.needed()) {
     if (cudaFuncSetAttribute(attn_bwd_dq_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bwd_smem<HD>()) != cudaSuccess) return -2;
     if (cudaFuncSetAttribute(attn_bwd_dkv_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bwd_smem<HD>()) != cudaSuccess) return -2;
-    configured = true;
+    configured.mark();
   }
   const int n_kv_tiles = (p.Tc + kBN - 1) / kBN;
   count_launch(3);

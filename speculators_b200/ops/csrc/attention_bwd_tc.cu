@@ -773,11 +773,11 @@ int launch_attn_bwd_tc(const AttnParams& p, int* tile_qmin, int* tile_qmax, int*
     rc = tc::make_map_bf16(&map_ve, p.ve, p.Te, (int64_t)p.nkv * HD, p.ve_rs, BN);
     if (rc) return rc;
   }
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.needed()) {
     if (cudaFuncSetAttribute(attn_bwd_dq_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -2;
     if (cudaFuncSetAttribute(attn_bwd_dkv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -2;
-    configured = true;
+    configured.mark();
   }
   count_launch(3);
   {

@@ -435,10 +435,10 @@ int launch_attn_fwd_tc(const AttnParams& p, int* status, cudaStream_t stream) {
     if (rc) return rc;
   }
   constexpr int smem_bytes = 5 * TILE_BYTES + 1024;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.needed()) {
     if (cudaFuncSetAttribute(attn_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return -2;
-    configured = true;
+    configured.mark();
   }
   dim3 grid(p.nh, (p.Tq + BM - 1) / BM);
   count_launch(1);

@@ -51,6 +51,18 @@ constexpr int kWarp = 32;
 // B200: 148 SMs.  Persistent / grid-stride kernels size their grids from this.
 constexpr int kNumSM = 148;
 
+// Kernel attributes (the dynamic shared memory limit) belong to a device: a launcher sets them the first time it
+// runs on each device of the process, not once per process.
+struct PerDeviceOnce {
+  bool done[64] = {};
+  static int device() {
+    int d = 0;
+    return cudaGetDevice(&d) == cudaSuccess && d >= 0 && d < 64 ? d : -1;
+  }
+  bool needed() const { const int d = device(); return d < 0 || !done[d]; }
+  void mark() { const int d = device(); if (d >= 0) done[d] = true; }
+};
+
 struct alignas(16) bf16x8 {
   __nv_bfloat162 v[4];
 };

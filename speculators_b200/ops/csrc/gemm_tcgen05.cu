@@ -746,16 +746,16 @@ static int launch_gemm_impl(const void* a, const void* b, void* c, const void* r
   }
   count_launch(1);
   if (pairs) {
-    static bool configured2 = false;
+    static PerDeviceOnce configured2;
     constexpr int smem2 = P_RING_BYTES + 1024;
-    if (!configured2) {
+    if (configured2.needed()) {
       bool ok = cudaFuncSetAttribute(gemm_tn_2cta_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) == cudaSuccess;
       ok = ok && cudaFuncSetAttribute(gemm_tn_2cta_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) == cudaSuccess;
       ok = ok && cudaFuncSetAttribute(gemm_tn_2cta_kernel<2, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) == cudaSuccess;
       ok = ok && cudaFuncSetAttribute(gemm_tn_2cta_kernel<2, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) == cudaSuccess;
       ok = ok && cudaFuncSetAttribute(gemm_tn_2cta_kernel<2, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) == cudaSuccess;
       if (!ok) return -2;
-      configured2 = true;
+      configured2.mark();
     }
     const int max_pairs = kNumSM / 2;
     // grouped: the number of tiles is known on the device only; every pair looks for work
@@ -768,11 +768,11 @@ static int launch_gemm_impl(const void* a, const void* b, void* c, const void* r
     else gemm_tn_2cta_kernel<1><<<grid, P_THREADS, smem2, stream>>>(map_a, map_b, p);
     return cudaGetLastError() == cudaSuccess ? 0 : -3;
   }
-  static bool configured = false;
+  static PerDeviceOnce configured;
   constexpr int smem_bytes = STAGES * STAGE_BYTES + 1024;
-  if (!configured) {
+  if (configured.needed()) {
     if (cudaFuncSetAttribute(gemm_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return -2;
-    configured = true;
+    configured.mark();
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < kNumSM ? tiles : kNumSM;

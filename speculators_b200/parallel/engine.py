@@ -120,8 +120,6 @@ class TrainEngine:
         self.step_count = 0
         self._flatten()
         self._init_state()
-        import os
-
         self._lazy_zero = self.device.type == "cuda" and os.environ.get("SB200_EAGER_ZERO_GRAD") != "1"
         if self._lazy_zero:
             self._install_lazy_zero_hooks()
