@@ -422,36 +422,41 @@ def _write_token_dataset(root, n=10):
     return rows
 
 
-def _online_train_worker(rank, world, port, verifier, data, save_online, save_files):
+def _online_argv(verifier, data, save, *extra):
+    return ["--verifier-name-or-path", verifier, "--data-path", data, "--save-path", save, "--total-seq-len", "256", "--num-workers", "0",
+            "--optimizer", "adamw", "--lr", "1e-3", "--draft-vocab-size", "128", "--target-layer-ids", "1", "2", "3", "--train-data-ratio", "0.8",
+            "--noise-std", "0", "--epochs", "1", "--ttt-steps", "2", "--log-freq", "1", "--scheduler-type", "none", *extra]
+
+
+def _online_train_worker(rank, world, port, verifier, data, save_online):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world),
                       NCCL_NVLS_ENABLE="0", SB200_NO_TQDM="1")
     from speculators_b200.train.config import TrainConfig
     from speculators_b200.train.entrypoint import main
 
-    def argv(save, *extra):
-        return ["--verifier-name-or-path", verifier, "--data-path", data, "--save-path", save, "--total-seq-len", "256", "--num-workers", "0",
-                "--optimizer", "adamw", "--lr", "1e-3", "--draft-vocab-size", "128", "--target-layer-ids", "1", "2", "3", "--train-data-ratio", "0.8",
-                "--noise-std", "0", "--epochs", "1", "--ttt-steps", "2", "--log-freq", "1", "--scheduler-type", "none", *extra]
+    main(TrainConfig.resolve(_online_argv(verifier, data, save_online, "--online-verifier-gpus", "1")))
 
-    main(TrainConfig.resolve(argv(save_online, "--online-verifier-gpus", "1")))
-    if rank == 1:
-        # the file path on the same data: hidden states written by the same verifier, then a one-GPU run
-        for key in ("RANK", "LOCAL_RANK", "WORLD_SIZE"):
-            os.environ.pop(key)
-        torch.cuda.set_device(0)  # a plain one-GPU run uses the first device
-        from datasets import load_from_disk
-        from safetensors.torch import save_file
 
-        from speculators_b200.verifier.tp import TensorParallelVerifier
+def _file_path_worker(_rank, verifier, data, save_files):
+    """The file path on the same data in a fresh one-GPU process: hidden states written by the same verifier."""
+    os.environ["SB200_NO_TQDM"] = "1"
+    for key in ("RANK", "LOCAL_RANK", "WORLD_SIZE"):
+        os.environ.pop(key, None)
+    from datasets import load_from_disk
+    from safetensors.torch import save_file
 
-        ver = TensorParallelVerifier.from_pretrained(verifier, device="cuda:0", dtype=torch.bfloat16)
-        os.makedirs(os.path.join(data, "hidden_states"), exist_ok=True)
-        for i, row in enumerate(load_from_disk(data)):
-            ids = torch.tensor(row["input_ids"])
-            out = ver.forward(ids, [1, 2, 3])
-            stored = torch.cat([out["hidden_states"], out["verifier_last_hidden_states"]], dim=-1).view(len(ids), 4, 256)
-            save_file({"hidden_states": stored.cpu().contiguous(), "token_ids": ids}, os.path.join(data, "hidden_states", f"hs_{i}.safetensors"))
-        main(TrainConfig.resolve(argv(save_files, "--on-missing", "raise")))
+    from speculators_b200.train.config import TrainConfig
+    from speculators_b200.train.entrypoint import main
+    from speculators_b200.verifier.tp import TensorParallelVerifier
+
+    ver = TensorParallelVerifier.from_pretrained(verifier, device="cuda:0", dtype=torch.bfloat16)
+    os.makedirs(os.path.join(data, "hidden_states"), exist_ok=True)
+    for i, row in enumerate(load_from_disk(data)):
+        ids = torch.tensor(row["input_ids"])
+        out = ver.forward(ids, [1, 2, 3])
+        stored = torch.cat([out["hidden_states"], out["verifier_last_hidden_states"]], dim=-1).view(len(ids), 4, 256)
+        save_file({"hidden_states": stored.cpu().contiguous(), "token_ids": ids}, os.path.join(data, "hidden_states", f"hs_{i}.safetensors"))
+    main(TrainConfig.resolve(_online_argv(verifier, data, save_files, "--on-missing", "raise")))
 
 
 def test_online_training_inside_the_job_matches_the_file_path(tmp_path):
@@ -462,7 +467,8 @@ def test_online_training_inside_the_job_matches_the_file_path(tmp_path):
     _write_full_verifier(verifier)
     _write_token_dataset(tmp_path / "data")
     save_online, save_files = str(tmp_path / "online"), str(tmp_path / "files")
-    mp.spawn(_online_train_worker, args=(2, 29701, verifier, data, save_online, save_files), nprocs=2, join=True)
+    mp.spawn(_online_train_worker, args=(2, 29701, verifier, data, save_online), nprocs=2, join=True)
+    mp.spawn(_file_path_worker, args=(verifier, data, save_files), nprocs=1, join=True)
     a, b = load_file(os.path.join(save_online, "0", "model.safetensors")), load_file(os.path.join(save_files, "0", "model.safetensors"))
     assert set(a) == set(b)
     # the two runs see the same batches in the same order from the same initial weights; what differs is the
