@@ -101,6 +101,32 @@ def op_gemm_wgrad_cublas(a):
     return (lambda: out.addmm_(x.t(), w)), 2.0 * a.m * a.n * a.k, 2.0 * (a.m * a.k + a.n * a.k + 2 * a.m * a.n), dict
 
 
+def op_gemm_swiglu(a):
+    """gate | up product of a gated MLP with silu(gate) * up formed in the GEMM's epilogue: x[M,K], w[2N,K] -> [M,2N] and [M,N]."""
+    from speculators_b200 import ops
+
+    M, I, K = a.m, a.n, a.k
+    x, w = _bf16(M, K), _bf16(2 * I, K, scale=0.05)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    fn = lambda: ops.native().gemm_swiglu(x, w, status)  # noqa: E731
+    return fn, 4.0 * M * I * K, 2.0 * (M * K + 2 * I * K + 3 * M * I), lambda: {"status": int(status.item())}
+
+
+def op_gemm_swiglu_unfused(a):
+    """The same as two launches: the plain GEMM, then the element-wise SwiGLU kernel."""
+    from speculators_b200 import ops
+
+    M, I, K = a.m, a.n, a.k
+    x, w, out = _bf16(M, K), _bf16(2 * I, K, scale=0.05), torch.empty(M, 2 * I, device="cuda", dtype=torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def fn():
+        ops.native().gemm(x, w, out, 0, False, False, status)
+        ops.native().swiglu_fwd(out)
+
+    return fn, 4.0 * M * I * K, 2.0 * (M * K + 2 * I * K + 5 * M * I), lambda: {"status": int(status.item())}
+
+
 def _head_inputs(a):
     T, H, V = a.t, a.hidden, a.vocab
     hidden, weight, targets = _bf16(T, H, scale=0.7), _bf16(V, H, scale=0.05), _bf16(T, V, scale=3.0)
@@ -198,7 +224,7 @@ def op_adamw(a):
     return fn, 0.0, n * (3 * 4 * 2 + 2 + 2.0), dict
 
 
-OPS = {"gemm": op_gemm, "gemm_cublas": op_gemm_cublas, "gemm_dgrad": op_gemm_dgrad, "gemm_dgrad_cublas": op_gemm_dgrad_cublas,
+OPS = {"gemm_swiglu": op_gemm_swiglu, "gemm_swiglu_unfused": op_gemm_swiglu_unfused, "gemm": op_gemm, "gemm_cublas": op_gemm_cublas, "gemm_dgrad": op_gemm_dgrad, "gemm_dgrad_cublas": op_gemm_dgrad_cublas,
        "gemm_wgrad": op_gemm_wgrad, "gemm_wgrad_cublas": op_gemm_wgrad_cublas, "lmhead_fused": op_lmhead_fused, "lmhead_unfused": op_lmhead_unfused, "attn_fwd": op_attn_fwd, "attn_bwd": op_attn_bwd, "loss": op_loss,
        "rmsnorm": op_rmsnorm, "rmsnorm_bwd": op_rmsnorm_bwd, "adamw": op_adamw}
 
