@@ -290,3 +290,40 @@ def test_optimizer_state_formats(tiny_verifier_dir, tiny_vocab_maps, tmp_path, c
     assert "matches none" in caplog.text and eng.step_count == 2
     eng.load_optimizer_state_dict(own)
     assert eng.step_count == 5
+
+
+# ---- "rank 0" duties follow the training sub-group when one is declared ------------------------------
+def _training_group_worker(rank, world, port, out_dir):
+    import os
+
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from speculators_b200.parallel import distributed as topo
+    from speculators_b200.train import checkpointer
+    from speculators_b200.train.logger import IsRank0Filter
+
+    before = (topo.training_rank(), checkpointer._is_rank0())  # noqa: SLF001
+    group = dist.new_group([1, 2])  # every rank takes part in the creation
+    topo.set_training_group(group)
+    topo.training_barrier()  # members only; rank 0 returns at once
+    after = (topo.training_rank(), checkpointer._is_rank0(), IsRank0Filter()._rank())  # noqa: SLF001
+    topo.set_training_group(None)
+    with open(os.path.join(out_dir, f"{rank}.txt"), "w") as fh:
+        fh.write(repr((before, after)))
+    dist.barrier()
+    dist.destroy_process_group()
+    os._exit(0)
+
+
+def test_rank0_duties_follow_the_training_group(tmp_path):
+    import ast
+
+    import torch.multiprocessing as mp
+
+    mp.spawn(_training_group_worker, args=(3, 29771, str(tmp_path)), nprocs=3, join=True)
+    seen = {r: ast.literal_eval((tmp_path / f"{r}.txt").read_text()) for r in range(3)}
+    assert [seen[r][0] for r in range(3)] == [(0, True), (1, False), (2, False)]  # the job's rank 0 before a group is declared
+    assert seen[0][1] == (-1, False, -1)  # outside the training group: no duties
+    assert seen[1][1] == (0, True, 0) and seen[2][1] == (1, False, 1)
