@@ -425,7 +425,7 @@ class Trainer:
                 loss, metrics = self._graphed.run(batch, lr, next_batch)
         else:
             with nvtx_range("fetch"):
-                dev_batch = {k: v.to(self.device, non_blocking=True) if isinstance(v, torch.Tensor) else v for k, v in batch.items()}
+                dev_batch = self._eager_inputs(batch)
             self.timer.mark("fetch")
             with nvtx_range("forward"):
                 self.engine.zero_grad()
@@ -437,10 +437,56 @@ class Trainer:
             with nvtx_range("optimizer"):
                 self.engine.account_comm(self.timer.enabled)  # collectives of a logged step are timed
                 self.engine.step(lr)
+            stage = self.__dict__.get("_eager_stage")
+            if stage is not None and stage.get("in_use") is not None:  # this step read a staged set: free once its work has run
+                freed = torch.cuda.Event()
+                freed.record()
+                stage["free"][stage["in_use"]] = freed
+                stage["in_use"] = None
+            if next_batch is not None:
+                self._eager_prefetch(next_batch)
         for sched in self.schedulers:
             sched.step()
         self.timer.mark("opt")
         return loss, metrics
+
+    # ------------------------------------------------------------------ eager steps: input prefetch
+    # A step that is not replayed from a CUDA graph reads its device inputs until its backward pass ends, so the
+    # copy of the following batch cannot reuse the same buffers: two sets alternate, and a set is written again
+    # only after the step that read it has finished (an event on the training stream).
+    def _eager_prefetch(self, batch: dict) -> None:
+        """Start the host-to-device copy of ``batch`` (host tensors, ideally pinned) on a side stream; the next
+        ``train_step`` given this same dict picks the copy up instead of copying on the training stream."""
+        if self.device_type != "cuda" or any(isinstance(v, torch.Tensor) and v.is_cuda for v in batch.values()):
+            return
+        state = self.__dict__.setdefault("_eager_stage", {"stream": torch.cuda.Stream(device=self.device), "sets": [{}, {}], "free": [None, None],
+                                                           "turn": 0, "ready": None, "in_use": None})
+        turn = state["turn"]
+        state["turn"] = turn ^ 1
+        sig = _GraphedStep.signature(batch)
+        slot = state["sets"][turn]
+        if slot.get("sig") != sig:
+            slot.clear()
+            slot.update(sig=sig, tensors={k: torch.empty(v.shape, dtype=v.dtype, device=self.device) for k, v in batch.items() if isinstance(v, torch.Tensor)})
+        if state["free"][turn] is not None:  # the step that read this set two steps ago must have ended
+            state["stream"].wait_event(state["free"][turn])
+        with torch.cuda.stream(state["stream"]):
+            for k, v in slot["tensors"].items():
+                v.copy_(batch[k], non_blocking=True)
+            done = torch.cuda.Event()
+            done.record()
+        state["ready"] = (batch, turn, done)
+
+    def _eager_inputs(self, batch: dict) -> dict:
+        state = self.__dict__.get("_eager_stage")
+        if state is not None and state["ready"] is not None and state["ready"][0] is batch:
+            _, turn, done = state["ready"]
+            state["ready"] = None
+            torch.cuda.current_stream().wait_event(done)
+            staged = state["sets"][turn]["tensors"]
+            state["in_use"] = turn  # ``train_step`` records the event that frees the set after the step's last kernel
+            return {k: staged.get(k, v) if isinstance(v, torch.Tensor) else v for k, v in batch.items()}
+        return {k: v.to(self.device, non_blocking=True) if isinstance(v, torch.Tensor) else v for k, v in batch.items()}
 
     def train_step_async(self, batch: dict, next_batch: dict | None = None) -> "LossHandle":
         """``train_step`` that does not make the host wait for the step: the loss is copied to

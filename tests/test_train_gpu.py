@@ -102,15 +102,17 @@ def test_fused_step_tail_matches_op_by_op_metrics():
     assert mo["cond_acc_1_total"] < mo["cond_acc_0_total"] and mo["full_acc_0_sum"] > 0
 
 
-def test_prefetched_inputs_give_the_same_steps(tiny_verifier_dir, tiny_vocab_maps):
-    """``train_step(batch, next_batch)`` stages the next batch on a side stream; the
-    losses must equal those of the plain call sequence, also when the announced batch is
-    not the one that arrives."""
+@pytest.mark.parametrize("graph", [True, False])
+def test_prefetched_inputs_give_the_same_steps(tiny_verifier_dir, tiny_vocab_maps, graph):
+    """``train_step(batch, next_batch)`` stages the next batch on a side stream (graph replay: one staging set
+    copied into the graph's inputs; eager steps: two alternating sets, since a step reads its inputs until its
+    backward pass ends); the losses must equal those of the plain call sequence, also when the announced batch
+    is not the one that arrives."""
     base = make_tiny_eagle3(tiny_verifier_dir, tiny_vocab_maps)
     seq = [{k: v.pin_memory() for k, v in make_tiny_batch(T=64, docs=(20, 30, 10), pad=4, seed=s).items()} for s in (0, 1, 2)]
-    order = [0, 1, 2, 1, 0, 2]
-    plain = _trainer(copy.deepcopy(base), seq[0], graph=True)
-    ahead = _trainer(copy.deepcopy(base), seq[0], graph=True)
+    order = [0, 1, 2, 1, 0, 2, 2, 1]
+    plain = _trainer(copy.deepcopy(base), seq[0], graph=graph)
+    ahead = _trainer(copy.deepcopy(base), seq[0], graph=graph)
     want = [float(plain.train_step(seq[i])[0].item()) for i in order]
     got = []
     for n, i in enumerate(order):
