@@ -226,6 +226,7 @@ class _GraphedStep:
         if stage is None:
             stage = {k: torch.empty(v.shape, dtype=v.dtype, device=self.trainer.device) for k, v in batch.items() if isinstance(v, torch.Tensor)}
             self._staging[sig] = stage
+            self._copy_stream.wait_stream(torch.cuda.current_stream())  # the fresh memory may have belonged to work still queued on the training stream
         # the staging buffers may still be read by the device-to-device copy of the step
         # that consumed the previous prefetch (only that copy: not the step's compute)
         if self._consumed is not None:
@@ -457,7 +458,8 @@ class Trainer:
     def _eager_prefetch(self, batch: dict) -> None:
         """Start the host-to-device copy of ``batch`` (host tensors, ideally pinned) on a side stream; the next
         ``train_step`` given this same dict picks the copy up instead of copying on the training stream."""
-        if self.device_type != "cuda" or any(isinstance(v, torch.Tensor) and v.is_cuda for v in batch.values()):
+        if (self.device_type != "cuda" or os.environ.get("SB200_EAGER_PREFETCH", "1") == "0"
+                or any(isinstance(v, torch.Tensor) and v.is_cuda for v in batch.values())):
             return
         state = self.__dict__.setdefault("_eager_stage", {"stream": torch.cuda.Stream(device=self.device), "sets": [{}, {}], "free": [None, None],
                                                            "turn": 0, "ready": None, "in_use": None})
@@ -468,6 +470,9 @@ class Trainer:
         if slot.get("sig") != sig:
             slot.clear()
             slot.update(sig=sig, tensors={k: torch.empty(v.shape, dtype=v.dtype, device=self.device) for k, v in batch.items() if isinstance(v, torch.Tensor)})
+            # The allocator may hand out memory that temporaries of the step in flight gave back in the training stream's
+            # order: another stream may write it only after that stream has caught up (once per set, at its allocation).
+            state["stream"].wait_stream(torch.cuda.current_stream(self.device))
         if state["free"][turn] is not None:  # the step that read this set two steps ago must have ended
             state["stream"].wait_event(state["free"][turn])
         with torch.cuda.stream(state["stream"]):
