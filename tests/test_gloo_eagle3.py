@@ -49,7 +49,9 @@ def _worker(rank, world, port, vdir, out_path, shard):
     else:
         assert state["state"] == {}  # the full state is assembled on the writer only
     dist.barrier()  # nobody tears its connections down while a peer still talks
+    dist.barrier()
     dist.destroy_process_group()
+    os._exit(0)  # skip interpreter teardown: gloo aborts there now and then
 
 
 def _single(vdir):
