@@ -40,7 +40,7 @@ def test_train_command_defaults_and_overwrite(tmp_path):
 
 # ---------------------------------------------------------------- validation re-sync
 def _barrier_indices(n_batches, *, is_distributed, interval):
-    stand_in = SimpleNamespace(is_distributed=is_distributed)
+    stand_in = SimpleNamespace(is_distributed=is_distributed, config=SimpleNamespace(process_group=None))
     hit = []
     with patch.object(trainer_mod, "_VAL_SYNC_INTERVAL", interval), patch.object(trainer_mod.dist, "barrier") as barrier:
         for i in range(n_batches):
