@@ -36,7 +36,7 @@ from torch import nn
 
 from speculators_b200 import ops
 from speculators_b200.layer_config import TransformerLayerConfig
-from speculators_b200.models.layers import Linear, RotaryTable
+from speculators_b200.models.layers import FusedLinear, Linear, RotaryTable
 from speculators_b200.models.mtp.model_definitions import _MTPMixin
 from speculators_b200.ops import AttnSpec
 
@@ -93,12 +93,19 @@ class _Experts(nn.Module):
 
 
 class _SharedExpert(nn.Module):
+    """The always-on expert: a gated MLP with the gate | up projections stored as one weight (one GEMM with the
+    activation in its epilogue on CUDA); its state dict keeps the ``gate_proj`` / ``up_proj`` / ``down_proj`` names."""
+
     def __init__(self, hidden: int, inter: int):
         super().__init__()
-        self.gate_proj, self.up_proj, self.down_proj = Linear(hidden, inter), Linear(hidden, inter), Linear(inter, hidden)
+        self.gate_up_proj = FusedLinear(hidden, ["gate_proj", "up_proj"], [inter, inter]).attach(self, "gate_up_proj")
+        self.down_proj = Linear(inter, hidden)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.down_proj(F.silu(self.gate_proj(x)) * self.up_proj(x))
+        hidden = ops.linear_swiglu(x, self.gate_up_proj.weight)
+        if hidden is None:
+            hidden = ops.swiglu(self.gate_up_proj(x))
+        return self.down_proj(hidden)
 
 
 def expert_forward(x: torch.Tensor, expert_ids: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor) -> torch.Tensor:
@@ -110,6 +117,49 @@ def expert_forward(x: torch.Tensor, expert_ids: torch.Tensor, gate_up: torch.Ten
         g, u = gu.chunk(2, dim=-1)
         out[rows] = (F.silu(g) * u) @ down[e].t()
     return out
+
+
+class _DispatchRows(torch.autograd.Function):
+    """``x[order // k]``: every token's row copied to the ``k`` places its experts' sorted order gives it.  The
+    backward is a gather through the inverse permutation and a sum over each token's ``k`` copies - no atomics
+    (autograd's ``index_add`` for the same gather ran at 250 GB/s on 40960 x 2048 rows)."""
+
+    @staticmethod
+    def forward(ctx, x, order, inv, k):
+        ctx.save_for_backward(inv)
+        ctx.k = k
+        return x.index_select(0, torch.div(order, k, rounding_mode="floor"))
+
+    @staticmethod
+    def backward(ctx, dxs):
+        (inv,) = ctx.saved_tensors
+        T = inv.numel() // ctx.k
+        return dxs.index_select(0, inv).view(T, ctx.k, dxs.shape[-1]).sum(1), None, None, None
+
+
+class _CombineRows(torch.autograd.Function):
+    """``out[t] = sum_j top_p[t, j] * ys[inv[t * k + j]]``: each token gathers its ``k`` expert outputs from the
+    expert-sorted order and forms the weighted sum (instead of scattering weighted rows with atomic adds)."""
+
+    @staticmethod
+    def forward(ctx, ys, order, inv, top_p):
+        T, k = top_p.shape
+        gathered = ys.index_select(0, inv).view(T, k, ys.shape[-1])
+        ctx.save_for_backward(ys, order, inv, top_p)
+        return (gathered * top_p.unsqueeze(-1)).sum(1)
+
+    @staticmethod
+    def backward(ctx, dout):
+        ys, order, inv, top_p = ctx.saved_tensors
+        T, k = top_p.shape
+        H = ys.shape[-1]
+        dys = dtop = None
+        if ctx.needs_input_grad[0]:
+            dys = (dout.unsqueeze(1) * top_p.unsqueeze(-1)).view(T * k, H).index_select(0, order)
+        if ctx.needs_input_grad[3]:
+            gathered = ys.index_select(0, inv).view(T, k, H)
+            dtop = (gathered * dout.unsqueeze(1)).sum(-1).to(top_p.dtype)
+        return dys, None, None, dtop
 
 
 def _grouped_expert_forward(x_sorted: torch.Tensor, counts: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor) -> torch.Tensor:
@@ -185,18 +235,18 @@ class SparseMoeBlock(nn.Module):
                 out = out + torch.sigmoid(self.shared_expert_gate(x)) * self.shared_expert(x)
             return out
         flat_e = top_e.reshape(-1)  # [T*k]
-        token_of = torch.arange(T, device=x.device).repeat_interleave(self.top_k)
-        order = torch.argsort(flat_e, stable=True)
+        order = torch.argsort(flat_e, stable=True)  # sorted place -> slot (token * k + j)
+        inv = torch.empty_like(order)
+        inv[order] = torch.arange(order.numel(), device=x.device)  # slot -> sorted place
         sorted_e = flat_e[order]
-        xs = x[token_of[order]]
+        xs = _DispatchRows.apply(x, order, inv, self.top_k)
         if self.ep_size == 1:
             # rows per expert without a host read (``bincount`` sizes its result from the largest id)
             counts = torch.zeros(self.num_experts, dtype=torch.long, device=x.device).index_add_(0, sorted_e, torch.ones_like(sorted_e))
             ys = _grouped_expert_forward(xs, counts, self.experts.gate_up_proj, self.experts.down_proj)
         else:
             ys = self._expert_parallel(xs, sorted_e)
-        weighted = ys * top_p.reshape(-1)[order].unsqueeze(-1)
-        out = torch.zeros_like(x).index_add_(0, token_of[order], weighted)
+        out = _CombineRows.apply(ys, order, inv, top_p)
         if self.shared_expert is not None:
             out = out + torch.sigmoid(self.shared_expert_gate(x)) * self.shared_expert(x)
         return out

@@ -183,7 +183,23 @@ class GroupPlan:
         return out.index_copy(0, self.dest, x_sorted)
 
     def unpad(self, y_padded: torch.Tensor) -> torch.Tensor:
-        return y_padded.index_select(0, self.dest)
+        return _UnpadRowsFn.apply(y_padded, self.dest)
+
+
+class _UnpadRowsFn(torch.autograd.Function):
+    """``y_padded[dest]`` for distinct ``dest``: the gradient is a row copy into zeros, where autograd's
+    ``index_select`` backward would add with atomics (0.67 ms against 0.23 ms for 40960 x 2048 rows)."""
+
+    @staticmethod
+    def forward(ctx, y_padded, dest):
+        ctx.save_for_backward(dest)
+        ctx.rows = y_padded.shape[0]
+        return y_padded.index_select(0, dest)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (dest,) = ctx.saved_tensors
+        return dy.new_zeros((ctx.rows, dy.shape[1])).index_copy_(0, dest, dy), None
 
 
 class _GroupedLinearFn(torch.autograd.Function):
