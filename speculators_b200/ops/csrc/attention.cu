@@ -551,9 +551,17 @@ kv_tile_range_kernel(const int* __restrict__ lo, const int* __restrict__ hi, int
 // group * n_qt): the tail of light CTAs fills the SMs the heavy ones leave.  With grouped
 // queries the CTAs of a group write fp32 partials that dkv_reduce_kernel sums in fixed
 // order (deterministic), otherwise the bf16 result is written directly.
+// At head dim 256 a warp's dK and dV rows would need 256 fp32 accumulators per thread (they spilled: 1.6 KB of
+// stores and 2 KB of loads per thread and tile): the head dim of the *outputs* is split over blockIdx.z, each CTA
+// recomputes the score tile over the whole head dim and accumulates kDkvCols<HD> of the dK / dV columns.
+template <int HD>
+constexpr int kDkvCols = HD > 128 ? 128 : HD;
+
 template <int HD>
 __global__ void __launch_bounds__(kAttnThreads)
 attn_bwd_dkv_kernel(const AttnParams p) {
+  constexpr int HDO = kDkvCols<HD>;
+  const int c0 = blockIdx.z * HDO;  // first dK / dV column of this CTA
   constexpr int LD = SmemLayout<HD>::LD;
   constexpr int kTile = SmemLayout<HD>::kTile;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -595,9 +603,9 @@ attn_bwd_dkv_kernel(const AttnParams p) {
     }
   };
 
-  float dk_acc[HD / 8][4], dv_acc[HD / 8][4];
+  float dk_acc[HDO / 8][4], dv_acc[HDO / 8][4];
 #pragma unroll
-  for (int i = 0; i < HD / 8; ++i)
+  for (int i = 0; i < HDO / 8; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       dk_acc[i][j] = 0.f;
@@ -687,10 +695,10 @@ attn_bwd_dkv_kernel(const AttnParams p) {
         as_[2] = pack_bf16(dpt[2 * kk + 1][0], dpt[2 * kk + 1][1]);
         as_[3] = pack_bf16(dpt[2 * kk + 1][2], dpt[2 * kk + 1][3]);
 #pragma unroll
-        for (int n2 = 0; n2 < HD / 16; ++n2) {
+        for (int n2 = 0; n2 < HDO / 16; ++n2) {
           uint32_t bo[4], bq[4];
-          ldmatrix_x4_trans(bo, ldb_kn_addr(dOt, LD, kk * 16, n2 * 16, lane));
-          ldmatrix_x4_trans(bq, ldb_kn_addr(Qt, LD, kk * 16, n2 * 16, lane));
+          ldmatrix_x4_trans(bo, ldb_kn_addr(dOt, LD, kk * 16, c0 + n2 * 16, lane));
+          ldmatrix_x4_trans(bq, ldb_kn_addr(Qt, LD, kk * 16, c0 + n2 * 16, lane));
           mma_16816(dv_acc[2 * n2], ap, bo[0], bo[1]);
           mma_16816(dv_acc[2 * n2 + 1], ap, bo[2], bo[3]);
           mma_16816(dk_acc[2 * n2], as_, bq[0], bq[1]);
@@ -709,10 +717,10 @@ attn_bwd_dkv_kernel(const AttnParams p) {
     for (int half = 0; half < 2; ++half) {
       const int key = half ? kb : ka;
       if (key >= p.Tc) continue;
-      float* rk = base + ((int64_t)key * p.nkv + kvh) * HD;
+      float* rk = base + ((int64_t)key * p.nkv + kvh) * HD + c0;
       float* rv = rk + plane;
 #pragma unroll
-      for (int nt = 0; nt < HD / 8; ++nt) {
+      for (int nt = 0; nt < HDO / 8; ++nt) {
         *reinterpret_cast<float2*>(rk + nt * 8 + 2 * t) = make_float2(dk_acc[nt][2 * half] * p.scale, dk_acc[nt][2 * half + 1] * p.scale);
         *reinterpret_cast<float2*>(rv + nt * 8 + 2 * t) = make_float2(dv_acc[nt][2 * half], dv_acc[nt][2 * half + 1]);
       }
@@ -723,10 +731,10 @@ attn_bwd_dkv_kernel(const AttnParams p) {
   for (int half = 0; half < 2; ++half) {
     const int key = half ? kb : ka;
     if (key >= p.Tc) continue;
-    __nv_bfloat16* rk = p.dk + ((int64_t)key * p.nkv + kvh) * HD;
-    __nv_bfloat16* rv = p.dv + ((int64_t)key * p.nkv + kvh) * HD;
+    __nv_bfloat16* rk = p.dk + ((int64_t)key * p.nkv + kvh) * HD + c0;
+    __nv_bfloat16* rv = p.dv + ((int64_t)key * p.nkv + kvh) * HD + c0;
 #pragma unroll
-    for (int nt = 0; nt < HD / 8; ++nt) {
+    for (int nt = 0; nt < HDO / 8; ++nt) {
       *reinterpret_cast<__nv_bfloat162*>(rk + nt * 8 + 2 * t) =
           __floats2bfloat162_rn(dk_acc[nt][2 * half] * p.scale, dk_acc[nt][2 * half + 1] * p.scale);
       *reinterpret_cast<__nv_bfloat162*>(rv + nt * 8 + 2 * t) = __floats2bfloat162_rn(dv_acc[nt][2 * half], dv_acc[nt][2 * half + 1]);
@@ -789,7 +797,7 @@ static int launch_bwd_t(const AttnParams& p, int* tile_qmin, int* tile_qmax, cud
   dim3 grid_q((p.Tq + kBM - 1) / kBM, p.nh);
   attn_bwd_dq_kernel<HD><<<grid_q, kAttnThreads, bwd_smem<HD>(), stream>>>(p);
   kv_tile_range_kernel<<<n_kv_tiles, 256, 0, stream>>>(p.lo, p.hi, p.Tq, p.Tc, tile_qmin, tile_qmax);
-  dim3 grid_kv(p.nh, n_kv_tiles);  // x = head: all heads of the heaviest tile are dispatched first
+  dim3 grid_kv(p.nh, n_kv_tiles, HD / kDkvCols<HD>);  // x = head: all heads of the heaviest tile are dispatched first; z = output column part
   attn_bwd_dkv_kernel<HD><<<grid_kv, kAttnThreads, bwd_smem<HD>(), stream>>>(p);
   if (p.dkv_part != nullptr) {
     const int64_t n = (int64_t)p.Tc * p.nkv * HD;
