@@ -154,7 +154,7 @@ class TrainEngine:
 
     def _peer_memory_unavailable(self) -> str | None:
         """Why the ranks of this group cannot map one another's memory (None: they can).  Every
-        rank publishes its host name and device index; the verdict is formed from the gathered
+        rank publishes its host name and device index; the outcome is formed from the gathered
         lists, so all ranks take the same branch."""
         import socket
 
@@ -166,9 +166,9 @@ class TrainEngine:
         ok = all(q == self.rank or d == mine[1] or _can_access_peer(mine[1], d) for q, (_, d) in enumerate(everyone))
         if len({d for _, d in everyone}) < self.world:
             ok = False  # two ranks on one device: kernels that wait on one another must not share a GPU
-        verdicts: list = [None] * self.world
-        dist.all_gather_object(verdicts, bool(ok), group=self.group)
-        if not all(verdicts):
+        answers: list = [None] * self.world
+        dist.all_gather_object(answers, bool(ok), group=self.group)
+        if not all(answers):
             return "a rank has no peer access to another rank's GPU (or two ranks share one GPU)"
         return None
 
