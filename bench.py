@@ -636,9 +636,13 @@ def run_reference(args):
     Nothing of this framework is imported here: the inputs come from ``bench_inputs`` (plain
     PyTorch) as files that the other arm reads too."""
     ref_root = os.path.join(REPO, "baseline", "_ref")
+
+    def unavailable(why: str) -> None:
+        if int(os.environ.get("RANK", "0")) == 0:  # one line per job
+            print(json.dumps({"impl": "reference", "unavailable": why[:300]}))
+
     if not os.path.isdir(os.path.join(ref_root, "speculators")):
-        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed (pip --target install of the reference missing)"}))
-        return
+        return unavailable("baseline/_ref is not installed (pip --target install of the reference missing)")
     sys.path[:] = [p for p in sys.path if os.path.abspath(p or ".") != REPO]  # the repo root must not shadow or leak packages
     sys.path.insert(0, ref_root)
     try:
@@ -658,11 +662,9 @@ def run_reference(args):
         from speculators.train.distributed import maybe_destroy_distributed, maybe_setup_distributed
         from speculators.train.trainer import Trainer, TrainerConfig
     except Exception as err:  # noqa: BLE001
-        print(json.dumps({"impl": "reference", "unavailable": f"reference import failed: {type(err).__name__}: {err}"[:300]}))
-        return
+        return unavailable(f"reference import failed: {type(err).__name__}: {err}")
     if not torch.cuda.is_available():
-        print(json.dumps({"impl": "reference", "unavailable": "no CUDA device (the reference trainer places the model on an accelerator)"}))
-        return
+        return unavailable("no CUDA device (the reference trainer places the model on an accelerator)")
 
     rank, local_rank, world = dist_env()
     if resolve_config(args).get("online"):
