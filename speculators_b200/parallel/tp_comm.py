@@ -129,9 +129,12 @@ class TpComm:
             raise RuntimeError(f"tensor-parallel exchange gave up (code {code}): {_STATUS.get(code, 'unknown wait')}")
 
     def close(self) -> None:
+        mapped_any = bool(self._mapped)
         for ptr in self._mapped:
             self._nat.peer_close(ptr)
         self._mapped.clear()
+        if mapped_any and dist.is_available() and dist.is_initialized():
+            dist.barrier(group=self.group)  # nobody frees a buffer that a peer still has mapped
         self.stage = self.ctl = None
         self.out = []
         for ptr in self._own.values():
