@@ -95,6 +95,9 @@ class TensorParallelVerifier:
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         c, R = self.cfg, self.world
+        if R > 1 and (bool(c.attention_bias) or bool(c.mlp_bias)):
+            # the bias of a row-parallel projection (o_proj, down_proj) would be added once per rank by the sum over the ranks
+            raise ValueError("the tensor-parallel verifier does not support attention_bias / mlp_bias")
         if c.num_attention_heads % R or c.num_key_value_heads % R or c.intermediate_size % R:
             raise ValueError(f"heads ({c.num_attention_heads} / {c.num_key_value_heads}) and intermediate size ({c.intermediate_size}) "
                              f"must be divisible by the tensor-parallel size ({R})")

@@ -116,3 +116,18 @@ def test_tensor_parallel_verifier_loads_checkpoint_slices(tmp_path):
         got = torch.load(f"{out}.{rank}")
         for key in want:
             assert torch.allclose(got[key], want[key], atol=2e-5, rtol=1e-4), (rank, key, float((got[key] - want[key]).abs().max()))
+
+
+def test_row_parallel_biases_are_refused(monkeypatch):
+    import pytest
+
+    from speculators_b200.verifier import tp as tp_mod
+
+    assert TensorParallelVerifier(dict(CFG, attention_bias=True)).world == 1  # one rank: nothing is summed over ranks
+    monkeypatch.setattr(tp_mod.dist, "is_initialized", lambda: True)
+    monkeypatch.setattr(tp_mod.dist, "get_world_size", lambda group=None: 2)
+    monkeypatch.setattr(tp_mod.dist, "get_rank", lambda group=None: 0)
+    with pytest.raises(ValueError, match="attention_bias"):
+        TensorParallelVerifier(dict(CFG, attention_bias=True))
+    with pytest.raises(ValueError, match="mlp_bias"):
+        TensorParallelVerifier(dict(CFG, mlp_bias=True))
