@@ -105,3 +105,18 @@ def test_decoder_config_from_verifier(tiny_verifier_dir):
         create_transformer_layer_config(tiny_verifier_dir, 2, "llama", None, 128, [5])
     with pytest.raises(ValueError):
         create_transformer_layer_config(tiny_verifier_dir, 2, "mamba", None, 128, [])
+
+
+def test_in_job_online_mode_states_what_it_needs():
+    """``--online-verifier-gpus`` refuses what it cannot do before touching a GPU."""
+    from types import SimpleNamespace
+
+    from speculators_b200.train.entrypoint import _run_online
+
+    with pytest.raises(ValueError, match="eagle3 and peagle"):
+        _run_online(SimpleNamespace(speculator_type="dflash", online_verifier_gpus=2), None, None, torch.bfloat16)
+    with pytest.raises(ValueError, match="torchrun job of more than N ranks"):
+        _run_online(SimpleNamespace(speculator_type="eagle3", online_verifier_gpus=2), None, None, torch.bfloat16)
+    cfg = TrainConfig.resolve(["--verifier-name-or-path", "x", "--online-verifier-gpus", "4", "--online-ring-slots", "8"])
+    flat = cfg.flatten()
+    assert flat["online_verifier_gpus"] == 4 and flat["online_ring_slots"] == 8 and flat["online_timeout"] == 600.0
