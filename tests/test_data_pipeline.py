@@ -379,3 +379,24 @@ print("ok")
 """
     proc = subprocess.run([sys.executable, "-c", code], cwd=ROOT, capture_output=True, text=True, timeout=300)
     assert proc.returncode == 0 and proc.stdout.strip().endswith("ok"), proc.stderr[-2000:]
+
+
+def test_datasets_written_against_the_reference_hooks_still_work():
+    """A ``BaseDataset`` subclass that defines the reference's hook names (``_compute_approx_lengths``,
+    ``_get_raw_data``) runs unchanged."""
+    from speculators_b200.train.data import BaseDataset
+
+    class Theirs(BaseDataset):
+        def __len__(self):
+            return 2
+
+        def _compute_approx_lengths(self):
+            return [3, 4]
+
+        def _get_raw_data(self, index):
+            n = 3 + index
+            return {"hidden_states": torch.zeros(n, 12), "input_ids": torch.arange(n), "verifier_last_hidden_states": torch.zeros(n, 4),
+                    "loss_mask": torch.ones(n, dtype=torch.bool)}
+
+    ds = Theirs(max_len=8)
+    assert ds.approx_lengths == [3, 4] and ds[1]["lengths"].item() == 4 and ds[0]["position_ids"].tolist() == [0, 1, 2]
