@@ -228,6 +228,9 @@ class ArrowDataset(BaseDataset):
     start_file_idx = property(lambda self: self.window.start)
     transfer = property(lambda self: self.resolver.transfer)
 
+    def _map_to_file_idx(self, index: int) -> int:  # the reference's name for ``window.file_index``
+        return self.window.file_index(index)
+
     def __len__(self) -> int:
         return len(self.window)
 

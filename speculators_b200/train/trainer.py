@@ -677,7 +677,7 @@ class Trainer:
         if not self.is_distributed or _VAL_SYNC_INTERVAL <= 0:
             return
         if batch_index > 0 and batch_index % _VAL_SYNC_INTERVAL == 0:
-            dist.barrier(group=self.config.process_group)
+            dist.barrier(group=getattr(getattr(self, "config", None), "process_group", None))
 
     @torch.no_grad()
     def val_epoch(self, epoch: int) -> dict[str, float] | None:
@@ -689,9 +689,12 @@ class Trainer:
             sampler.set_epoch(epoch)
         accumulated: dict[str, torch.Tensor] = {}
         num_batches = len(self.val_loader)
+        device = getattr(self, "device", None)
+        if device is None:  # a trainer assembled by hand (tests): what ``__init__`` would have chosen
+            device = torch.device("cuda", self.local_rank) if self.device_type == "cuda" else torch.device(self.device_type)
         for i, batch in enumerate(self.val_loader):
             self._maybe_val_sync(i)
-            dev_batch = {k: v.to(self.device, non_blocking=True) if isinstance(v, torch.Tensor) else v for k, v in batch.items()}
+            dev_batch = {k: v.to(device, non_blocking=True) if isinstance(v, torch.Tensor) else v for k, v in batch.items()}
             _, _loss, metrics = self.model(**dev_batch, **(self.config.val_call_kwargs or {}))
             for k, v in metrics.items():
                 accumulated[k] = v.float() if k not in accumulated else accumulated[k] + v.float()
