@@ -43,6 +43,8 @@ class MTPConverter:
                 return dst + key[len(src):]
         return key
 
+    _remap_key = remap_key  # the reference's spelling of the two helpers
+
     @staticmethod
     def fuse_moe_experts(weights: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
         groups: dict[str, dict[int, dict[str, torch.Tensor]]] = {}
@@ -64,6 +66,8 @@ class MTPConverter:
             rest[f"{prefix}.gate_up_proj"] = torch.stack([torch.cat([by_idx[i]["gate_proj"], by_idx[i]["up_proj"]], dim=0) for i in range(n)])
             rest[f"{prefix}.down_proj"] = torch.stack([by_idx[i]["down_proj"] for i in range(n)])
         return rest
+
+    _fuse_moe_experts = fuse_moe_experts
 
     def convert_to_state_dict(self, input_path, cache_dir=None) -> dict[str, torch.Tensor]:
         local = ensure_checkpoint_is_local(input_path, cache_dir)
