@@ -140,8 +140,32 @@ class SpeculatorModelConfig(PydanticClassRegistryMixin):
         return SpeculatorModelConfig.model_validate(merged) if cls is SpeculatorModelConfig else cls.model_validate(merged)
 
     @classmethod
+    def get_config_dict(cls, pretrained_model_name_or_path: str | os.PathLike, cache_dir: str | None = None, force_download: bool = False,
+                        local_files_only: bool = False, token: str | None = None, revision: str = "main",
+                        **unused: Any) -> tuple[dict[str, Any], dict[str, Any]]:
+        """``(config dict, unused kwargs)`` like ``transformers.PretrainedConfig.get_config_dict``: a local
+        directory (or a path to a json file) is read directly; anything else is taken for a hub id and its
+        ``config.json`` fetched through ``huggingface_hub`` when that package and a network are available."""
+        path = os.fspath(pretrained_model_name_or_path)
+        if os.path.isdir(path) or os.path.isfile(path):
+            return read_config_json(path), dict(unused)
+        try:
+            from huggingface_hub import hf_hub_download
+        except ImportError:
+            return read_config_json(path), dict(unused)  # raises the FileNotFoundError that names what was looked for
+        try:
+            file = hf_hub_download(repo_id=path, filename="config.json", cache_dir=cache_dir, force_download=force_download,
+                                   local_files_only=local_files_only, token=token, revision=revision)
+        except Exception as err:  # noqa: BLE001 - the hub client raises several unrelated types when offline
+            raise FileNotFoundError(f"no config.json at {path!r} and the hub could not provide one ({type(err).__name__})") from err
+        return read_config_json(file), dict(unused)
+
+    @classmethod
     def from_pretrained(cls, pretrained_model_name_or_path: str | os.PathLike, **kwargs: Any) -> "SpeculatorModelConfig":
-        data = read_config_json(pretrained_model_name_or_path)
+        data, _ = cls.get_config_dict(
+            pretrained_model_name_or_path, cache_dir=kwargs.pop("cache_dir", None), force_download=kwargs.pop("force_download", False),
+            local_files_only=kwargs.pop("local_files_only", False), token=kwargs.pop("token", None), revision=kwargs.pop("revision", "main"),
+        )
         if "speculators_model_type" not in data:
             raise NotImplementedError(
                 "config.json has no 'speculators_model_type'. Loading a non-speculator model config "

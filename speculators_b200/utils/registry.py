@@ -36,7 +36,7 @@ class ClassRegistryMixin:
     @classmethod
     def register(cls, name: str | None = None) -> Callable[[type[Any]], type[Any]]:
         if name is not None and not isinstance(name, str):
-            raise ValueError(f"register_decorator must be used as a class decorator with a string name or none; got name={name!r}")
+            raise ValueError(f"register: name must be a string or None; got name={name!r}")
 
         def _apply(klass: type[Any]) -> type[Any]:
             return cls.register_decorator(klass, name=name)
@@ -51,7 +51,7 @@ class ClassRegistryMixin:
                 "Use @Base.register('name') or @Base.register_decorator."
             )
         if name is not None and not isinstance(name, str):
-            raise ValueError(f"register_decorator must be used as a class decorator with a string name or none; got name={name!r}")
+            raise ValueError(f"register_decorator must be used as a class decorator with a name that is a string or None; got name={name!r}")
         key = name or clazz.__name__
         table = cls._table(create=True)
         assert table is not None
