@@ -230,8 +230,8 @@ class SpeculatorModel(ClassRegistryMixin, nn.Module):
                     pretrained_model_name_or_path, verifier=verifier, config_dict=raw
                 )
             config = SpeculatorModelConfig.from_pretrained(pretrained_model_name_or_path)
-        elif isinstance(config, (str, os.PathLike)):
-            config = SpeculatorModelConfig.from_pretrained(config)
+        elif isinstance(config, (str, os.PathLike)) and os.path.exists(os.fspath(config)):
+            config = SpeculatorModelConfig.from_pretrained(config)  # a config directory / file on disk; anything else must be a config object
         if not isinstance(config, SpeculatorModelConfig):
             raise TypeError(f"Expected config to be an instance of SpeculatorModelConfig, got {type(config)}.")
         if not pretrained_model_name_or_path and not state_dict:
@@ -276,5 +276,5 @@ def _read_safetensors_dir(path: str | os.PathLike) -> dict[str, torch.Tensor]:
         return out
     single = os.path.join(root, "model.safetensors")
     if not os.path.exists(single):
-        raise FileNotFoundError(f"no model.safetensors (or shard index) under {root}")
+        raise FileNotFoundError(f"no model.safetensors (or shard index) under '{root}'.")
     return load_file(single)
