@@ -257,7 +257,8 @@ def _run_online(args, model, model_class, dtype) -> None:
         raise ValueError("--online-verifier-gpus needs CUDA devices with peer access (the hidden states travel over NVLink)")
     world, n_ver = dist.get_world_size(), int(args.online_verifier_gpus)
     device = torch.device("cuda", torch.cuda.current_device())
-    plan = OnlineBatchPlan(args.data_path, args.total_seq_len, world - n_ver, seed=args.seed, train_ratio=args.train_data_ratio)
+    # seed 0: the multipack sampler's own default, i.e. the batches the file path forms for the same data and rank count
+    plan = OnlineBatchPlan(args.data_path, args.total_seq_len, world - n_ver, seed=0, train_ratio=args.train_data_ratio)
     verifier_cfg = read_config_json(args.verifier_name_or_path)
     verifier_cfg = verifier_cfg.get("text_config", verifier_cfg)
     split = OnlineSplit(verifier_cfg, list(model.target_layer_ids), args.total_seq_len, device, n_verifier=n_ver, n_slots=args.online_ring_slots,
