@@ -16,6 +16,7 @@ import argparse
 import copy
 import gc
 import logging
+import os
 import random
 import warnings
 from pathlib import Path
@@ -256,6 +257,9 @@ def _run_online(args, model, model_class, dtype) -> None:
     if not torch.cuda.is_available():
         raise ValueError("--online-verifier-gpus needs CUDA devices with peer access (the hidden states travel over NVLink)")
     world, n_ver = dist.get_world_size(), int(args.online_verifier_gpus)
+    # the trainer ranks are a sub-group of the job: their optimizer step uses the library collectives unless told otherwise
+    # (the peer-memory step is exercised on whole jobs)
+    os.environ.setdefault("SB200_COMM", "nccl")
     device = torch.device("cuda", torch.cuda.current_device())
     # seed 0: the multipack sampler's own default, i.e. the batches the file path forms for the same data and rank count
     plan = OnlineBatchPlan(args.data_path, args.total_seq_len, world - n_ver, seed=0, train_ratio=args.train_data_ratio)
